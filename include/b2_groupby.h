@@ -1,0 +1,263 @@
+/*
+ * b2_groupby.h — C ABI of the B200-native hash groupby-aggregate engine.
+ *
+ * The library is a drop-in for ONE path of NVIDIA/cudf:
+ *     cudf::groupby::groupby(keys, null_policy).aggregate(requests)
+ * (reference: cpp/include/cudf/groupby.hpp:54-57 aggregation_request, :81-84
+ * aggregation_result, :121-125 constructor, :181-184 aggregate;
+ * cpp/src/groupby/groupby.cu:39-50,219-236; hash back end cpp/src/groupby/hash/).
+ *
+ * Everything crossing this boundary is a plain pointer, an integer or a POD
+ * struct.  All `data`, `null_mask` and child pointers are DEVICE pointers on the
+ * current CUDA device unless a comment says "host".  Inputs are non-owning views
+ * (the caller keeps them alive until the stream work has finished, like
+ * cudf::column_view); outputs are owning buffers obtained from the caller's
+ * allocator (the stand-in for rmm::device_async_resource_ref).
+ *
+ * Error model: every entry point returns a b2_status.  The codes map 1:1 onto
+ * the exception classes the reference throws (cpp/include/cudf/utilities/error.hpp:35-97);
+ * b2_last_error() returns the message of the calling thread's last failure.
+ */
+#ifndef B2_GROUPBY_H
+#define B2_GROUPBY_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+typedef enum b2_status {
+  B2_SUCCESS          = 0,
+  B2_LOGIC_ERROR      = 1, /* cudf::logic_error      (precondition violated, e.g. size mismatch) */
+  B2_INVALID_ARGUMENT = 2, /* std::invalid_argument                                              */
+  B2_DATA_TYPE_ERROR  = 3, /* cudf::data_type_error  (invalid type/aggregation combination)      */
+  B2_CUDA_ERROR       = 4, /* cudf::cuda_error                                                   */
+  B2_UNSUPPORTED      = 5, /* valid for the reference's sort path, not handled by this hash path;
+                              an adapter falls through to the reference for these               */
+  B2_OUT_OF_MEMORY    = 6, /* std::bad_alloc / rmm::out_of_memory                                */
+  B2_INTERNAL_ERROR   = 7
+} b2_status;
+
+/* ---- element types: numeric values of cudf::type_id (cpp/include/cudf/types.hpp:185-217) */
+typedef enum b2_type_id {
+  B2_EMPTY = 0, B2_INT8 = 1, B2_INT16 = 2, B2_INT32 = 3, B2_INT64 = 4,
+  B2_UINT8 = 5, B2_UINT16 = 6, B2_UINT32 = 7, B2_UINT64 = 8,
+  B2_FLOAT32 = 9, B2_FLOAT64 = 10, B2_BOOL8 = 11,
+  B2_TIMESTAMP_DAYS = 12, B2_TIMESTAMP_SECONDS = 13, B2_TIMESTAMP_MILLISECONDS = 14,
+  B2_TIMESTAMP_MICROSECONDS = 15, B2_TIMESTAMP_NANOSECONDS = 16,
+  B2_DURATION_DAYS = 17, B2_DURATION_SECONDS = 18, B2_DURATION_MILLISECONDS = 19,
+  B2_DURATION_MICROSECONDS = 20, B2_DURATION_NANOSECONDS = 21,
+  B2_DICTIONARY32 = 22, B2_STRING = 23, B2_LIST = 24,
+  B2_DECIMAL32 = 25, B2_DECIMAL64 = 26, B2_DECIMAL128 = 27, B2_STRUCT = 28
+} b2_type_id;
+
+/* ---- aggregation kinds: numeric values of cudf::aggregation::Kind
+ *      (cpp/include/cudf/aggregation.hpp:78-121).  Only the kinds the reference's
+ *      hash path serves are listed (cpp/src/groupby/hash/groupby.cu:63-131). */
+typedef enum b2_agg_kind {
+  B2_AGG_SUM = 0, B2_AGG_PRODUCT = 2, B2_AGG_MIN = 3, B2_AGG_MAX = 4,
+  B2_AGG_COUNT_VALID = 5, B2_AGG_COUNT_ALL = 6, B2_AGG_SUM_OF_SQUARES = 9,
+  B2_AGG_MEAN = 10, B2_AGG_M2 = 11, B2_AGG_VARIANCE = 12, B2_AGG_STD = 13
+} b2_agg_kind;
+
+/* cudf::null_policy (cpp/include/cudf/types.hpp:115-118) */
+typedef enum b2_null_policy { B2_NULL_EXCLUDE = 0, B2_NULL_INCLUDE = 1 } b2_null_policy;
+
+/* ---- non-owning column view: field-for-field cudf::column_view
+ *      (cpp/include/cudf/column/column_view.hpp:236-243 base fields, :469 children).
+ *      Element i lives at data[(offset+i)] and its validity bit is bit (offset+i)%32 of
+ *      null_mask[(offset+i)/32], 1 = valid (cpp/include/cudf/utilities/bit.hpp:47-104);
+ *      null_mask == NULL means all valid.  STRING: data = chars, children[0] = offsets
+ *      column of size+1 entries typed INT32 or INT64
+ *      (cpp/include/cudf/strings/strings_column_view.hpp:53). */
+typedef struct b2_column_view {
+  int32_t type_id;                        /* b2_type_id                                */
+  int32_t scale;                          /* decimal scale; 0 otherwise                */
+  int32_t size;                           /* number of elements (cudf::size_type)      */
+  int32_t null_count;                     /* number of nulls, or -1 if unknown         */
+  const void* data;                       /* device                                    */
+  const uint32_t* null_mask;              /* device; NULL = no nulls                   */
+  int32_t offset;                         /* element offset of a sliced view           */
+  int32_t num_children;
+  const struct b2_column_view* children;  /* host array                                */
+} b2_column_view;
+
+/* One aggregation to compute on a values column: stands for
+ * std::unique_ptr<cudf::groupby_aggregation> (kind + the one parameter the
+ * supported kinds carry: ddof of VARIANCE/STD, cpp/include/cudf/aggregation.hpp:293,305). */
+typedef struct b2_aggregation {
+  int32_t kind; /* b2_agg_kind                            */
+  int32_t ddof; /* VARIANCE / STD only; reference default 1 */
+} b2_aggregation;
+
+/* cudf::groupby::aggregation_request (cpp/include/cudf/groupby.hpp:54-57) */
+typedef struct b2_aggregation_request {
+  b2_column_view values;
+  int32_t num_aggregations;
+  const b2_aggregation* aggregations; /* host array */
+} b2_aggregation_request;
+
+/* ---- allocator: stands for rmm::device_async_resource_ref.  Stream-ordered on
+ *      `stream` (a cudaStream_t).  NULL allocator ⇒ the library's own stream-ordered pool. */
+typedef struct b2_allocator {
+  void* (*allocate)(size_t bytes, void* stream, void* ctx);
+  void (*deallocate)(void* ptr, size_t bytes, void* stream, void* ctx);
+  void* ctx;
+} b2_allocator;
+
+/* ---- owning output column: stands for cudf::column
+ *      (cpp/include/cudf/column/column.hpp:37,249-270).  `data`, `null_mask` come from the
+ *      allocator passed to the producing call and are released by b2_result_free (or adopted
+ *      by the caller, who then sets them to NULL first). */
+typedef struct b2_owned_column {
+  int32_t type_id;
+  int32_t scale;
+  int32_t size;
+  int32_t null_count;
+  void* data;
+  size_t data_bytes;
+  uint32_t* null_mask; /* NULL when the column is not nullable */
+  size_t null_mask_bytes;
+  int32_t num_children;
+  struct b2_owned_column* children; /* host array (STRING: children[0] = offsets) */
+} b2_owned_column;
+
+/* Return value of aggregate: std::pair<std::unique_ptr<table>, std::vector<aggregation_result>>
+ * (cpp/include/cudf/groupby.hpp:181-184).  results[r][a] is the column for aggregation a of
+ * request r, in request order (groupby.hpp:139-146).  Group order is unspecified (:148-150). */
+typedef struct b2_groupby_result {
+  int32_t num_groups;
+  int32_t num_keys;
+  b2_owned_column* keys; /* host array, num_keys */
+  int32_t num_requests;
+  int32_t* num_results;       /* host array, per request */
+  b2_owned_column** results;  /* host array of host arrays */
+  b2_allocator allocator;     /* the allocator that owns the device buffers */
+  void* stream;
+} b2_groupby_result;
+
+/* ---- tuning knobs (the reference keeps these as compile-time constants,
+ *      cpp/src/groupby/hash/helpers.cuh:19-40, cpp/include/cudf/detail/cuco_helpers.hpp:16) */
+typedef struct b2_groupby_options {
+  int64_t expected_groups;  /* hint; <= 0 = unknown (engine speculates, then estimates)        */
+  int32_t table_variant;    /* 0 auto, 1 force global-memory table only, 2 shared-memory cache */
+  int32_t shared_table_bytes; /* <= 0 = auto                                                   */
+  /* Fused drop_nulls pre-filter (cpp/src/stream_compaction/drop_nulls.cu:56-96): a row takes
+   * part only if it is valid in every one of these masks (bit i = row i, same bit layout and
+   * the same `offset` convention as a column sliced at `row_filter_offsets[j]`). */
+  int32_t num_row_filters;
+  const uint32_t* const* row_filter_masks; /* host array of device pointers */
+  const int32_t* row_filter_offsets;       /* host array or NULL (all zero) */
+} b2_groupby_options;
+
+typedef struct b2_groupby b2_groupby;             /* cudf::groupby::groupby          */
+typedef struct b2_groupby_state b2_groupby_state; /* partial-aggregate state, below */
+
+/* ---- the drop-in path -------------------------------------------------- */
+
+/* groupby::groupby(table_view const& keys, null_policy) — cpp/include/cudf/groupby.hpp:121-125,
+ * cpp/src/groupby/groupby.cu:39-50.  The views are copied; the device data is not. */
+b2_status b2_groupby_create(const b2_column_view* keys, int32_t num_keys, int32_t null_policy,
+                            const b2_groupby_options* options /* may be NULL */, b2_groupby** out);
+
+/* groupby::aggregate(requests, stream, mr) — cpp/include/cudf/groupby.hpp:181-184,
+ * cpp/src/groupby/groupby.cu:219-236 → detail::hash::groupby (cpp/src/groupby/hash/groupby.cu:134-147).
+ * Work is enqueued on `stream`; the call synchronises the stream once to learn the group count.
+ * Errors: B2_LOGIC_ERROR "Size mismatch between request values and groupby keys."
+ * (groupby.cu:225-229); B2_DATA_TYPE_ERROR "Invalid type/aggregation combination."
+ * (groupby.cu:188-201); B2_UNSUPPORTED for requests only the reference's sort path serves. */
+b2_status b2_groupby_aggregate(b2_groupby* gb, const b2_aggregation_request* requests,
+                               int32_t num_requests, void* stream, const b2_allocator* allocator,
+                               b2_groupby_result* out);
+
+/* ~groupby() */
+void b2_groupby_destroy(b2_groupby* gb);
+
+/* Releases every device buffer and host array of a result (what ~table / ~column do). */
+void b2_result_free(b2_groupby_result* result);
+
+/* ---- partial-aggregate state: the multi-GPU / batch-wise decomposition ---
+ * The reference ships partial aggregates between GPUs and merges them
+ * (python/cudf_polars/cudf_polars/streaming/actor_graph/groupby.py:339-456; stateful form
+ * cudf::groupby::streaming_groupby, cpp/include/cudf/groupby.hpp:478-598,
+ * cpp/src/groupby/streaming_groupby/merge.cu:91-142).  A state holds one hash table of
+ * {key, n, Σx, Σx², min, max …} cells for a fixed (key schema, request list). */
+
+/* Creates an empty state for the key schema of `gb` and the given requests (values pointers
+ * are read at update time from `requests` passed to b2_state_update). */
+b2_status b2_state_create(const b2_groupby* gb, const b2_aggregation_request* requests,
+                          int32_t num_requests, b2_groupby_state** out);
+
+/* Aggregates the rows of (gb keys, requests values) into the state: the local pass of a
+ * multi-GPU groupby, or one batch of streaming_groupby::aggregate (groupby.hpp:539-541). */
+b2_status b2_state_update(b2_groupby_state* st, const b2_groupby* gb,
+                          const b2_aggregation_request* requests, int32_t num_requests,
+                          void* stream);
+
+/* Size in bytes of one packed partial record ({key cell, accumulator cells…}, 8-byte cells). */
+int32_t b2_state_record_bytes(const b2_groupby_state* st);
+
+/* Hash-partitions the state's groups by owner = hash(key) % num_parts (the role of
+ * cudf::hash_partition on the partial table, cpp/src/partitioning/partitioning.cu:569-750):
+ * writes the records destination-major into a device buffer owned by the state and the
+ * per-destination record counts into `counts` (host array, num_parts).  Synchronises `stream`. */
+b2_status b2_state_pack(b2_groupby_state* st, int32_t num_parts, void* stream,
+                        const void** records_out, int64_t* counts);
+
+/* Merges `num_records` packed records (device memory, any origin with the same schema) into
+ * the state: streaming_groupby::merge (groupby.hpp:548-556). */
+b2_status b2_state_merge(b2_groupby_state* st, const void* records, int64_t num_records,
+                         void* stream);
+
+/* Drops all groups but keeps the schema; `expected_groups` sizes the next table (<=0 unknown). */
+b2_status b2_state_reset(b2_groupby_state* st, int64_t expected_groups, void* stream);
+
+/* Number of groups currently held (synchronises `stream`). */
+b2_status b2_state_num_groups(b2_groupby_state* st, void* stream, int64_t* out);
+
+/* Compacts keys and finalises the compound aggregations (mean = Σx/n; M2 = Σx² − (Σx)²/n;
+ * var = M2/(n−ddof); std = sqrt(var)) — cpp/src/groupby/hash/hash_compound_agg_finalizer.cu:93-186,
+ * cpp/src/groupby/common/m2_var_std.cu:49-59,160-187; streaming_groupby::finalize
+ * (groupby.hpp:566-568).  The state stays valid. */
+b2_status b2_state_finalize(b2_groupby_state* st, void* stream, const b2_allocator* allocator,
+                            b2_groupby_result* out);
+
+void b2_state_destroy(b2_groupby_state* st);
+
+/* ---- row-level hash partition: the multi-GPU pre-step for high-cardinality inputs ---
+ * cudf::hash_partition(table, columns_to_hash, num_partitions)
+ * (cpp/include/cudf/partitioning.hpp; cpp/src/partitioning/partitioning.cu:950-975):
+ * reorders the rows of `columns` (fixed-width columns; the first `num_key_columns` are hashed)
+ * so that partition p occupies rows [offsets[p], offsets[p+1]).  Output columns come from the
+ * allocator; `offsets` is a host array of num_parts+1 entries.  The partition of a key equals
+ * the owner used by b2_state_pack.  Synchronises `stream`. */
+b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns,
+                            int32_t num_key_columns, int32_t num_parts, void* stream,
+                            const b2_allocator* allocator, b2_owned_column* out_columns,
+                            int64_t* offsets);
+
+/* Releases the buffers of one owned column obtained from b2_hash_partition. */
+void b2_column_free(b2_owned_column* col, const b2_allocator* allocator, void* stream);
+
+/* ---- introspection ------------------------------------------------------ */
+const char* b2_last_error(void);   /* message of this thread's last failure */
+const char* b2_version(void);
+/* Counters of the calling thread's last aggregate/update call: kernels launched, table
+ * attempts (1 = first table size was enough), bytes of scratch used. */
+typedef struct b2_call_stats {
+  int32_t kernel_launches;
+  int32_t table_attempts;
+  int64_t table_capacity;
+  int64_t scratch_bytes;
+  int32_t used_shared_table;
+  int32_t reserved;
+} b2_call_stats;
+void b2_get_last_stats(b2_call_stats* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2_GROUPBY_H */
