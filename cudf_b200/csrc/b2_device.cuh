@@ -1,0 +1,351 @@
+// b2_device.cuh — device-side data model of the groupby engine: the plan a kernel receives,
+// row loading, key packing / hashing / equality, and the accumulator-cell operations.
+//
+// Data layout in HBM
+//   * inputs: Arrow-layout columns exactly as cudf::column_view describes them
+//     (cpp/include/cudf/column/column_view.hpp:236-243): element i at data[offset+i], validity bit
+//     offset+i of the uint32 mask words, LSB first (cpp/include/cudf/utilities/bit.hpp:47-104).
+//   * hash table: an array of slots of `stride` 8-byte cells, AoS so that one probe touches one or
+//     two 32-byte sectors:  cell 0 = key cell, cells 1.. = accumulators.
+//       packed keys : key cell = all fixed-width key columns concatenated into <= 64 bits
+//                     (+ one null bit per nullable column under null_policy::INCLUDE);
+//       row keys    : key cell = (32-bit hash tag << 32) | representative row index, equality
+//                     decided by comparing the rows' key columns (what the reference does for every
+//                     key, cpp/src/groupby/hash/helpers.cuh:87-93,
+//                     cpp/include/cudf/detail/row_operator/equality.cuh:59-89).
+//     An unused slot has key cell == EMPTY; the one packed key whose bits equal EMPTY lives in an
+//     extra slot at index `capacity`.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace b2 {
+
+using u64 = unsigned long long;
+using i64 = long long;
+using u32 = unsigned int;
+
+constexpr u64 EMPTY = 0xFFFFFFFFFFFFFFFFull;
+
+constexpr int MAX_KEYS    = 16;
+constexpr int MAX_VALS    = 16;
+constexpr int MAX_CELLS   = 40;
+constexpr int MAX_FILTERS = 8;
+
+enum KeyMode : int { KM_PACKED = 0, KM_ROWS = 1 };
+
+// type classes used on the device (host maps b2_type_id onto these)
+enum ValClass : int {
+  VC_I8 = 0, VC_I16, VC_I32, VC_I64, VC_U8, VC_U16, VC_U32, VC_U64, VC_F32, VC_F64, VC_BOOL,
+  VC_STRING, VC_NONE /* only the validity mask is used (COUNT of a non-numeric column) */
+};
+
+// accumulator cell operations; the decomposition of the requested aggregations into these follows
+// cpp/src/groupby/hash/extract_single_pass_aggs.cpp:63-109
+enum CellOp : int {
+  OP_SUM_I = 0, OP_SUM_F, OP_SSQ_I, OP_SSQ_F, OP_MIN_I, OP_MIN_U, OP_MIN_F, OP_MAX_I, OP_MAX_U,
+  OP_MAX_F, OP_CNT_V, OP_CNT_A, OP_PROD_I, OP_PROD_F
+};
+
+struct DKeyCol {
+  const unsigned char* data;
+  const u32* mask;      // nullptr = no nulls
+  const void* offsets;  // strings
+  i64 offset;           // element offset of the view
+  int vclass;           // ValClass
+  int width;            // bytes (fixed width)
+  int shift;            // packed mode: bit position of the value
+  int nullbit;          // packed mode + INCLUDE + nullable: bit position of the null flag, else -1
+  int offs64;           // strings: 1 = INT64 offsets
+  int pad;
+};
+
+struct DValCol {
+  const unsigned char* data;
+  const u32* mask;
+  i64 offset;
+  int vclass;
+  int pad;
+};
+
+struct DCell {
+  unsigned char op;   // CellOp
+  unsigned char col;  // value column index
+};
+
+struct DPlan {
+  i64 nrows;
+  int nkeys, nvals, ncells, key_mode;
+  int include_nulls;  // null_policy::INCLUDE
+  int nfilters;
+  int stride;         // cells per slot = 1 + ncells
+  int pad;
+  DKeyCol keys[MAX_KEYS];
+  DValCol vals[MAX_VALS];
+  DCell cells[MAX_CELLS];
+  const u32* filters[MAX_FILTERS];
+  i64 filter_offsets[MAX_FILTERS];
+};
+
+// control block shared by the kernels of one table
+struct DCtrl {
+  u32 overflow;      // set when the table ran out of room or a probe sequence hit its limit
+  u32 special_used;  // the slot of the key whose bits equal EMPTY is in use
+  u64 nclaimed;      // slots claimed in [0, capacity)
+  u64 claim_limit;   // nclaimed above this sets overflow
+  u64 out_cursor;    // finalize: next dense output index
+  u64 stat_smem_rows;
+  u64 stat_gmem_rows;
+  u64 reserved;
+};
+
+// ---------------------------------------------------------------------------------- hashing
+__host__ __device__ __forceinline__ u64 mix64(u64 x)
+{
+  x ^= x >> 33; x *= 0xff51afd7ed558ccdull;
+  x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ull;
+  x ^= x >> 33;
+  return x;
+}
+// second, independent hash: decides the owner partition/rank of a key so that the keys one rank
+// receives still spread over its whole table
+__host__ __device__ __forceinline__ u64 owner_hash(u64 h) { return mix64(h * 0x9E3779B97F4A7C15ull + 0x7F4A7C15ull); }
+__host__ __device__ __forceinline__ u32 owner_of(u64 h, u32 nparts)
+{
+  return (u32)(((owner_hash(h) >> 32) * (u64)nparts) >> 32);
+}
+__device__ __forceinline__ u32 reduce32(u32 h, u32 n) { return __umulhi(h, n); }
+__device__ __forceinline__ u64 reduce64(u64 h, u64 n) { return __umul64hi(h, n); }
+
+// ---------------------------------------------------------------------------------- bit tests
+__device__ __forceinline__ bool bit_valid(const u32* mask, i64 i)
+{
+  return (__ldg(mask + (i >> 5)) >> (i & 31)) & 1u;
+}
+
+// a row takes part unless a row filter (fused drop_nulls) or, under EXCLUDE, a null key says no
+// (cpp/src/groupby/common/utils.cpp:14-32)
+__device__ __forceinline__ bool row_active(const DPlan& P, i64 row)
+{
+  bool ok = true;
+  for (int f = 0; f < P.nfilters; ++f) ok = ok && bit_valid(P.filters[f], P.filter_offsets[f] + row);
+  if (!P.include_nulls) {
+    for (int k = 0; k < P.nkeys; ++k)
+      if (P.keys[k].mask) ok = ok && bit_valid(P.keys[k].mask, P.keys[k].offset + row);
+  }
+  return ok;
+}
+
+// ---------------------------------------------------------------------------------- packed keys
+__device__ __forceinline__ u64 load_fixed_bits(const unsigned char* data, i64 idx, int width)
+{
+  switch (width) {
+    case 1: return (u64) * (data + idx);
+    case 2: return (u64)__ldg((const unsigned short*)data + idx);
+    case 4: return (u64)__ldg((const u32*)data + idx);
+    default: return (u64)__ldg((const u64*)data + idx);
+  }
+}
+
+__device__ __forceinline__ u64 pack_key(const DPlan& P, i64 row)
+{
+  u64 key = 0;
+  for (int k = 0; k < P.nkeys; ++k) {
+    const DKeyCol& c = P.keys[k];
+    const i64 idx    = c.offset + row;
+    if (c.nullbit >= 0 && !bit_valid(c.mask, idx)) {
+      key |= 1ull << c.nullbit;  // null == null whatever the payload
+    } else {
+      key |= load_fixed_bits(c.data, idx, c.width) << c.shift;
+    }
+  }
+  return key;
+}
+
+// ---------------------------------------------------------------------------------- row keys
+__device__ __forceinline__ i64 str_offset(const DKeyCol& c, i64 idx)
+{
+  return c.offs64 ? (i64)__ldg((const i64*)c.offsets + idx) : (i64)__ldg((const int*)c.offsets + idx);
+}
+
+// canonical bits of a fixed-width key element: -0 -> +0 and one NaN, so that hashing agrees with
+// equality (cpp/include/cudf/hashing/detail/hash_functions.cuh:31-37)
+__device__ __forceinline__ u64 canonical_bits(const DKeyCol& c, i64 idx)
+{
+  u64 b = load_fixed_bits(c.data, idx, c.width);
+  if (c.vclass == VC_F32) {
+    float f = __uint_as_float((u32)b);
+    if (f == 0.0f) b = 0;
+    if (f != f) b = 0x7fc00000u;
+  } else if (c.vclass == VC_F64) {
+    double d = __longlong_as_double((i64)b);
+    if (d == 0.0) b = 0;
+    if (d != d) b = 0x7ff8000000000000ull;
+  }
+  return b;
+}
+
+__device__ inline u64 hash_bytes(const unsigned char* p, i64 len, u64 h)
+{
+  i64 i = 0;
+  // 8 bytes per step; the tail is zero padded and the length mixed in, so "ab" != "ab\0"
+  for (; i + 8 <= len; i += 8) {
+    u64 w = 0;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) w |= (u64)p[i + b] << (8 * b);
+    h = mix64(h ^ w) + 0x9E3779B97F4A7C15ull;
+  }
+  u64 w = 0;
+  for (int b = 0; i + b < len; ++b) w |= (u64)p[i + b] << (8 * b);
+  return mix64(h ^ w ^ ((u64)len << 56));
+}
+
+__device__ inline u64 hash_row(const DPlan& P, i64 row)
+{
+  u64 h = 0x243F6A8885A308D3ull;
+  for (int k = 0; k < P.nkeys; ++k) {
+    const DKeyCol& c = P.keys[k];
+    const i64 idx    = c.offset + row;
+    if (c.mask && !bit_valid(c.mask, idx)) {
+      h = mix64(h ^ 0xA5A5A5A5DEADBEEFull) + k;  // null element
+    } else if (c.vclass == VC_STRING) {
+      const i64 b = str_offset(c, idx), e = str_offset(c, idx + 1);
+      h = hash_bytes(c.data + b, e - b, h);
+    } else {
+      h = mix64(h ^ canonical_bits(c, idx)) + 0x9E3779B97F4A7C15ull;
+    }
+  }
+  return mix64(h);
+}
+
+// row i == row j over the key columns; null == null (nulls only reach here under INCLUDE),
+// NaN == NaN, +0 == -0, strings byte-wise with equal length
+// (cpp/include/cudf/detail/row_operator/equality.cuh:59-89,243-261, string_view.cuh:306-326)
+__device__ inline bool rows_equal(const DPlan& P, i64 a, i64 b)
+{
+  if (a == b) return true;
+  for (int k = 0; k < P.nkeys; ++k) {
+    const DKeyCol& c = P.keys[k];
+    const i64 ia = c.offset + a, ib = c.offset + b;
+    if (c.mask) {
+      const bool va = bit_valid(c.mask, ia), vb = bit_valid(c.mask, ib);
+      if (va != vb) return false;
+      if (!va) continue;
+    }
+    if (c.vclass == VC_STRING) {
+      const i64 ba = str_offset(c, ia), ea = str_offset(c, ia + 1);
+      const i64 bb = str_offset(c, ib), eb = str_offset(c, ib + 1);
+      if (ea - ba != eb - bb) return false;
+      const unsigned char* pa = c.data + ba;
+      const unsigned char* pb = c.data + bb;
+      for (i64 i = 0; i < ea - ba; ++i)
+        if (pa[i] != pb[i]) return false;
+    } else {
+      if (canonical_bits(c, ia) != canonical_bits(c, ib)) return false;
+    }
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------------------------- values
+// A value is carried as 64 bits: integers sign/zero-extended to int64, floats widened to double.
+__device__ __forceinline__ u64 load_value(const DValCol& c, i64 row)
+{
+  const i64 idx = c.offset + row;
+  switch (c.vclass) {
+    case VC_I8: return (u64)(i64) * ((const signed char*)c.data + idx);
+    case VC_I16: return (u64)(i64)__ldg((const short*)c.data + idx);
+    case VC_I32: return (u64)(i64)__ldg((const int*)c.data + idx);
+    case VC_I64: case VC_U64: return __ldg((const u64*)c.data + idx);
+    case VC_U8: return (u64) * (c.data + idx);
+    case VC_BOOL: return (u64)(*(c.data + idx) != 0);
+    case VC_U16: return (u64)__ldg((const unsigned short*)c.data + idx);
+    case VC_U32: return (u64)__ldg((const u32*)c.data + idx);
+    case VC_F32: return (u64)__double_as_longlong((double)__ldg((const float*)c.data + idx));
+    case VC_F64: return __ldg((const u64*)c.data + idx);
+    default: return 0;
+  }
+}
+__device__ __forceinline__ bool value_valid(const DValCol& c, i64 row)
+{
+  return c.mask == nullptr || bit_valid(c.mask, c.offset + row);
+}
+
+// order-preserving map double -> u64 (so float min/max are single integer atomics instead of the
+// reference's compare-and-swap loop, cpp/include/cudf/detail/utilities/device_atomics.cuh:226-337;
+// a NaN can never make the loop spin: cpp/tests/groupby/min_tests.cpp:518-541)
+__host__ __device__ __forceinline__ u64 f64_ordered(u64 bits)
+{
+  return (bits >> 63) ? ~bits : (bits | 0x8000000000000000ull);
+}
+__host__ __device__ __forceinline__ u64 f64_unordered(u64 enc)
+{
+  return (enc >> 63) ? (enc & 0x7FFFFFFFFFFFFFFFull) : ~enc;
+}
+
+// identity of a cell (cpp/include/cudf/detail/aggregation/aggregation.cuh:121-174,
+// cpp/include/cudf/detail/utilities/device_operators.cuh:51-83,114-139,172-197)
+__host__ __device__ __forceinline__ u64 cell_identity(int op)
+{
+  switch (op) {
+    case OP_MIN_I: return 0x7FFFFFFFFFFFFFFFull;
+    case OP_MIN_U: case OP_MIN_F: return 0xFFFFFFFFFFFFFFFFull;
+    case OP_MAX_I: return 0x8000000000000000ull;
+    case OP_PROD_I: return 1ull;
+    case OP_PROD_F: return 0x3FF0000000000000ull;  // 1.0
+    default: return 0ull;                          // sums, counts, MAX_U, MAX_F
+  }
+}
+
+// fold one input value into a cell (cpp/include/cudf/detail/aggregation/device_aggregators.cuh:
+// 99-112 SUM/MIN/MAX, :309-361 SUM_OF_SQUARES/COUNT)
+__device__ __forceinline__ void cell_update(u64* cell, int op, u64 v)
+{
+  switch (op) {
+    case OP_SUM_I: atomicAdd(cell, v); break;
+    case OP_SUM_F: atomicAdd((double*)cell, __longlong_as_double((i64)v)); break;
+    case OP_SSQ_I: atomicAdd(cell, v * v); break;
+    case OP_SSQ_F: { const double d = __longlong_as_double((i64)v); atomicAdd((double*)cell, d * d); break; }
+    case OP_MIN_I: atomicMin((i64*)cell, (i64)v); break;
+    case OP_MIN_U: atomicMin(cell, v); break;
+    case OP_MIN_F: atomicMin(cell, f64_ordered(v)); break;
+    case OP_MAX_I: atomicMax((i64*)cell, (i64)v); break;
+    case OP_MAX_U: atomicMax(cell, v); break;
+    case OP_MAX_F: atomicMax(cell, f64_ordered(v)); break;
+    case OP_CNT_V: case OP_CNT_A: atomicAdd(cell, 1ull); break;
+    case OP_PROD_I: {
+      u64 old = *cell, assumed;
+      do { assumed = old; old = atomicCAS(cell, assumed, assumed * v); } while (old != assumed);
+      break;
+    }
+    case OP_PROD_F: {
+      u64 old = *cell, assumed;
+      do {
+        assumed = old;
+        const double r = __longlong_as_double((i64)assumed) * __longlong_as_double((i64)v);
+        old = atomicCAS(cell, assumed, (u64)__double_as_longlong(r));
+      } while (old != assumed);
+      break;
+    }
+    default: break;
+  }
+}
+
+// fold a partial cell (same representation as the table's) into a cell: the merge of partial
+// aggregates (cpp/src/groupby/streaming_groupby/merge.cu:30-61)
+__device__ __forceinline__ void cell_merge(u64* cell, int op, u64 part)
+{
+  switch (op) {
+    case OP_SUM_I: case OP_SSQ_I: case OP_CNT_V: case OP_CNT_A: atomicAdd(cell, part); break;
+    case OP_SUM_F: case OP_SSQ_F: atomicAdd((double*)cell, __longlong_as_double((i64)part)); break;
+    case OP_MIN_I: atomicMin((i64*)cell, (i64)part); break;
+    case OP_MIN_U: case OP_MIN_F: atomicMin(cell, part); break;
+    case OP_MAX_I: atomicMax((i64*)cell, (i64)part); break;
+    case OP_MAX_U: case OP_MAX_F: atomicMax(cell, part); break;
+    case OP_PROD_I: cell_update(cell, OP_PROD_I, part); break;
+    case OP_PROD_F: cell_update(cell, OP_PROD_F, part); break;
+    default: break;
+  }
+}
+
+}  // namespace b2

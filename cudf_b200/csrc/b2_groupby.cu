@@ -1,0 +1,1185 @@
+// b2_groupby.cu — host side of the engine and the C ABI declared in include/b2_groupby.h.
+//
+// Host flow of one aggregate call (reference flow: cpp/src/groupby/groupby.cu:219-236 →
+// cpp/src/groupby/hash/groupby.cu:134-147 → compute_groupby.cu:51-155):
+//   validate → plan (key packing, accumulator cells, outputs) → size the global table →
+//   k_table_init → k_aggregate → read the control block (ONE stream sync: group count and the
+//   overflow flag) → allocate outputs from the caller's allocator → k_finalize → null counts.
+// If the first table is too small the pass is repeated with a table sized for the row count.
+#include "../../include/b2_groupby.h"
+#include "b2_kernels.cuh"
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+using namespace b2;
+
+namespace {
+
+thread_local std::string g_last_error;
+thread_local b2_call_stats g_stats{};
+
+struct Err {
+  b2_status code;
+  std::string msg;
+};
+#define B2_FAIL(code, msg) throw Err{code, msg}
+#define CUDA_TRY(expr)                                                                          \
+  do {                                                                                          \
+    cudaError_t e_ = (expr);                                                                    \
+    if (e_ != cudaSuccess) {                                                                    \
+      B2_FAIL(e_ == cudaErrorMemoryAllocation ? B2_OUT_OF_MEMORY : B2_CUDA_ERROR,               \
+              std::string("CUDA error at " #expr ": ") + cudaGetErrorName(e_) + " " +           \
+                cudaGetErrorString(e_));                                                        \
+    }                                                                                           \
+  } while (0)
+
+template <typename F>
+b2_status guarded(F&& f)
+{
+  try {
+    f();
+    return B2_SUCCESS;
+  } catch (const Err& e) {
+    g_last_error = e.msg;
+    return e.code;
+  } catch (const std::bad_alloc&) {
+    g_last_error = "host allocation failed";
+    return B2_OUT_OF_MEMORY;
+  } catch (const std::exception& e) {
+    g_last_error = e.what();
+    return B2_INTERNAL_ERROR;
+  }
+}
+
+// ------------------------------------------------------------------------------ device facts
+struct DeviceInfo {
+  int sms = 0;
+  int smem_optin = 0;
+};
+const DeviceInfo& device_info()
+{
+  static thread_local int cached_dev = -1;
+  static thread_local DeviceInfo info;
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev != cached_dev) {
+    CUDA_TRY(cudaDeviceGetAttribute(&info.sms, cudaDevAttrMultiProcessorCount, dev));
+    CUDA_TRY(cudaDeviceGetAttribute(&info.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+      unsigned long long keep = ~0ull;  // keep scratch memory cached between calls
+      cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    cached_dev = dev;
+  }
+  return info;
+}
+
+// ------------------------------------------------------------------------------ memory
+void* default_alloc(size_t bytes, void* stream, void*)
+{
+  void* p = nullptr;
+  if (bytes == 0) bytes = 8;
+  if (cudaMallocAsync(&p, bytes, (cudaStream_t)stream) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  return p;
+}
+void default_free(void* p, size_t, void* stream, void*)
+{
+  if (p) cudaFreeAsync(p, (cudaStream_t)stream);
+}
+b2_allocator resolve(const b2_allocator* a)
+{
+  if (a && a->allocate && a->deallocate) return *a;
+  return b2_allocator{default_alloc, default_free, nullptr};
+}
+
+struct Scratch {  // stream-ordered temporary, freed on scope exit
+  void* p = nullptr;
+  size_t bytes = 0;
+  cudaStream_t stream = nullptr;
+  Scratch() = default;
+  Scratch(size_t n, cudaStream_t s) : bytes(n), stream(s)
+  {
+    p = default_alloc(n, s, nullptr);
+    if (!p) B2_FAIL(B2_OUT_OF_MEMORY, "out of device memory allocating " + std::to_string(n) + " bytes of scratch");
+    g_stats.scratch_bytes += (int64_t)n;
+  }
+  Scratch(Scratch&& o) noexcept { *this = std::move(o); }
+  Scratch& operator=(Scratch&& o) noexcept
+  {
+    release();
+    p = o.p; bytes = o.bytes; stream = o.stream; o.p = nullptr;
+    return *this;
+  }
+  Scratch(const Scratch&) = delete;
+  Scratch& operator=(const Scratch&) = delete;
+  void release() { if (p) { cudaFreeAsync(p, stream); p = nullptr; } }
+  ~Scratch() { release(); }
+};
+
+// ------------------------------------------------------------------------------ type facts
+bool is_float_t(int t) { return t == B2_FLOAT32 || t == B2_FLOAT64; }
+bool is_duration_t(int t) { return t >= B2_DURATION_DAYS && t <= B2_DURATION_NANOSECONDS; }
+bool is_timestamp_t(int t) { return t >= B2_TIMESTAMP_DAYS && t <= B2_TIMESTAMP_NANOSECONDS; }
+bool is_numeric_t(int t) { return t >= B2_INT8 && t <= B2_BOOL8; }
+
+int width_of(int t)
+{
+  switch (t) {
+    case B2_INT8: case B2_UINT8: case B2_BOOL8: return 1;
+    case B2_INT16: case B2_UINT16: return 2;
+    case B2_INT32: case B2_UINT32: case B2_FLOAT32: case B2_TIMESTAMP_DAYS: case B2_DURATION_DAYS:
+    case B2_DECIMAL32: return 4;
+    case B2_INT64: case B2_UINT64: case B2_FLOAT64: case B2_TIMESTAMP_SECONDS: case B2_TIMESTAMP_MILLISECONDS:
+    case B2_TIMESTAMP_MICROSECONDS: case B2_TIMESTAMP_NANOSECONDS: case B2_DURATION_SECONDS:
+    case B2_DURATION_MILLISECONDS: case B2_DURATION_MICROSECONDS: case B2_DURATION_NANOSECONDS:
+    case B2_DECIMAL64: return 8;
+    default: return 0;
+  }
+}
+int vclass_of(int t)
+{
+  switch (t) {
+    case B2_INT8: return VC_I8;
+    case B2_INT16: return VC_I16;
+    case B2_INT32: case B2_TIMESTAMP_DAYS: case B2_DURATION_DAYS: case B2_DECIMAL32: return VC_I32;
+    case B2_UINT8: return VC_U8;
+    case B2_UINT16: return VC_U16;
+    case B2_UINT32: return VC_U32;
+    case B2_UINT64: return VC_U64;
+    case B2_FLOAT32: return VC_F32;
+    case B2_FLOAT64: return VC_F64;
+    case B2_BOOL8: return VC_BOOL;
+    case B2_STRING: return VC_STRING;
+    default: return width_of(t) == 8 ? VC_I64 : VC_NONE;
+  }
+}
+
+// result element type: cpp/include/cudf/detail/aggregation/aggregation.hpp:884-1013
+int result_type(int src, int kind)
+{
+  switch (kind) {
+    case B2_AGG_COUNT_VALID: case B2_AGG_COUNT_ALL: return B2_INT32;
+    case B2_AGG_MIN: case B2_AGG_MAX: return src;
+    case B2_AGG_SUM: return (is_float_t(src) || is_duration_t(src)) ? src : B2_INT64;
+    case B2_AGG_SUM_OF_SQUARES: case B2_AGG_PRODUCT: return is_float_t(src) ? src : B2_INT64;
+    case B2_AGG_MEAN: return is_duration_t(src) ? src : B2_FLOAT64;
+    default: return B2_FLOAT64;
+  }
+}
+
+// 0 = served here, 1 = invalid combination (the reference throws), 2 = valid in the reference but
+// only its sort path / ARGMIN path serves it
+int classify_request(int src, int kind)
+{
+  switch (kind) {
+    case B2_AGG_COUNT_VALID: case B2_AGG_COUNT_ALL: return 0;
+    case B2_AGG_MIN: case B2_AGG_MAX:
+      if (is_numeric_t(src) || is_timestamp_t(src) || is_duration_t(src)) return 0;
+      if (src == B2_STRING || src == B2_DECIMAL32 || src == B2_DECIMAL64 || src == B2_DECIMAL128 ||
+          src == B2_DICTIONARY32 || src == B2_STRUCT || src == B2_LIST)
+        return 2;
+      return 1;
+    case B2_AGG_SUM: case B2_AGG_MEAN:
+      if (is_numeric_t(src) || is_duration_t(src)) return 0;
+      if (src == B2_DECIMAL32 || src == B2_DECIMAL64 || src == B2_DECIMAL128 || src == B2_DICTIONARY32) return 2;
+      return 1;
+    case B2_AGG_SUM_OF_SQUARES: case B2_AGG_PRODUCT: case B2_AGG_M2: case B2_AGG_VARIANCE: case B2_AGG_STD:
+      if (is_numeric_t(src)) return 0;
+      if (src == B2_DICTIONARY32) return 2;
+      return 1;
+    default:
+      return (kind >= 0 && kind <= 40) ? 2 : 1;  // other reference kinds: sort path
+  }
+}
+
+// ------------------------------------------------------------------------------ views
+struct ColView {  // deep copy of a b2_column_view (children included)
+  b2_column_view v{};
+  std::vector<ColView> kids;
+  std::vector<b2_column_view> kid_views;
+  explicit ColView(const b2_column_view& in) : v(in)
+  {
+    for (int i = 0; i < in.num_children; ++i) kids.emplace_back(in.children[i]);
+    for (auto& k : kids) kid_views.push_back(k.v);
+    v.children = kid_views.empty() ? nullptr : kid_views.data();
+  }
+  ColView(const ColView& o) : ColView(o.v) {}
+  ColView& operator=(const ColView& o)
+  {
+    if (this != &o) { ColView t(o.v); v = t.v; kids = t.kids; kid_views.clear(); for (auto& k : kids) kid_views.push_back(k.v); v.children = kid_views.empty() ? nullptr : kid_views.data(); }
+    return *this;
+  }
+  bool has_nulls() const { return v.null_mask != nullptr && v.null_count != 0; }
+};
+
+}  // namespace
+
+// ------------------------------------------------------------------------------ objects
+struct b2_groupby {
+  std::vector<ColView> keys;
+  int null_policy = B2_NULL_EXCLUDE;
+  int64_t expected_groups = 0;
+  int table_variant = 0;
+  int shared_table_bytes = 0;
+  std::vector<const uint32_t*> filters;
+  std::vector<int32_t> filter_offsets;
+};
+
+namespace {
+
+struct OutSpec {  // one requested aggregation → one result column
+  int req, agg;
+  int kind;      // OutKind
+  int rtype;     // b2_type_id of the result
+  int c_a = -1, c_b = -1, c_cnt = -1;
+  int ddof = 1;
+  int src_float = 0;
+  bool nullable = false;
+};
+
+struct Schema {  // everything that is fixed by (key types, requests): cells and outputs
+  int key_mode = KM_PACKED;
+  int nkeys = 0;
+  int include_nulls = 0;
+  int key_types[MAX_KEYS]{};
+  int key_width[MAX_KEYS]{};
+  int key_shift[MAX_KEYS]{};
+  int key_nullbit[MAX_KEYS]{};
+  bool key_nullable[MAX_KEYS]{};
+  int nvals = 0;
+  int val_types[MAX_VALS]{};
+  int ncells = 0;
+  DCell cells[MAX_CELLS]{};
+  std::vector<OutSpec> outs;
+  std::vector<int> req_nouts;
+  std::vector<int> req_val;  // request → value column slot
+  bool f32mean = false;      // cells == {Σ of a FLOAT32 column, n of it}: compact shared-memory layout
+};
+
+}  // namespace
+
+struct b2_groupby_state {
+  Schema sc;
+  DPlan plan{};          // schema part filled; pointers filled per update
+  u64* table = nullptr;  // (cap + 1) * stride cells
+  int64_t cap = 0;
+  DCtrl* ctrl = nullptr;
+  DCtrl host_ctrl{};     // last read-back
+  bool ctrl_fresh = false;
+  bool has_rows = false;     // a row-keyed table references the rows of one update
+  std::vector<ColView> row_keys;  // key views of that update (row-key mode output gather)
+  int64_t expected_groups = 0;
+  cudaStream_t last_stream = nullptr;
+};
+
+namespace {
+
+// ------------------------------------------------------------------------------ planning
+void validate_requests(const b2_groupby& gb, const b2_aggregation_request* reqs, int nreqs)
+{
+  if (nreqs < 0 || (nreqs > 0 && !reqs)) B2_FAIL(B2_INVALID_ARGUMENT, "requests is null");
+  const int n = gb.keys.empty() ? 0 : gb.keys[0].v.size;
+  for (int r = 0; r < nreqs; ++r) {
+    // cpp/src/groupby/groupby.cu:225-229
+    if (reqs[r].values.size != n) B2_FAIL(B2_LOGIC_ERROR, "Size mismatch between request values and groupby keys.");
+    if (reqs[r].num_aggregations < 0 || (reqs[r].num_aggregations > 0 && !reqs[r].aggregations))
+      B2_FAIL(B2_INVALID_ARGUMENT, "aggregations is null");
+  }
+  bool unsupported = false;
+  for (int r = 0; r < nreqs; ++r)
+    for (int a = 0; a < reqs[r].num_aggregations; ++a) {
+      const int c = classify_request(reqs[r].values.type_id, reqs[r].aggregations[a].kind);
+      // cpp/src/groupby/groupby.cu:188-201
+      if (c == 1) B2_FAIL(B2_DATA_TYPE_ERROR, "Invalid type/aggregation combination.");
+      if (c == 2) unsupported = true;
+    }
+  if (unsupported)
+    B2_FAIL(B2_UNSUPPORTED, "request is served by the reference's sort-based groupby, not by the hash path");
+}
+
+Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int nreqs)
+{
+  Schema sc;
+  sc.nkeys = (int)gb.keys.size();
+  if (sc.nkeys == 0) B2_FAIL(B2_LOGIC_ERROR, "groupby needs at least one key column");
+  if (sc.nkeys > MAX_KEYS) B2_FAIL(B2_UNSUPPORTED, "more than 16 key columns");
+  sc.include_nulls = gb.null_policy == B2_NULL_INCLUDE;
+
+  bool packed = true;
+  int bits = 0;
+  for (int k = 0; k < sc.nkeys; ++k) {
+    const b2_column_view& c = gb.keys[k].v;
+    const int w = width_of(c.type_id);
+    if (c.type_id == B2_STRING) {
+      if (c.size > 0 && (c.num_children < 1 || !c.children ||
+                         (c.children[0].type_id != B2_INT32 && c.children[0].type_id != B2_INT64)))
+        B2_FAIL(B2_INVALID_ARGUMENT, "STRING key column needs an INT32 or INT64 offsets child");
+      packed = false;
+    } else if (w == 0) {
+      B2_FAIL(B2_UNSUPPORTED, "key column type is not served by the hash path of this engine");
+    } else if (is_float_t(c.type_id)) {
+      packed = false;  // keys compare by value (+0 == -0, NaN == NaN) but are output verbatim
+    }
+    sc.key_types[k] = c.type_id;
+    sc.key_width[k] = w;
+    sc.key_shift[k] = bits;
+    sc.key_nullable[k] = c.null_mask != nullptr;
+    bits += 8 * w;
+  }
+  for (int k = 0; k < sc.nkeys; ++k) {
+    sc.key_nullbit[k] = -1;
+    if (sc.include_nulls && sc.key_nullable[k]) sc.key_nullbit[k] = bits++;
+  }
+  if (bits > 64) packed = false;
+  sc.key_mode = packed ? KM_PACKED : KM_ROWS;
+
+  // value columns: identical views share one slot
+  struct VKey { const void* d; const void* m; int off, type; };
+  std::vector<VKey> seen;
+  struct Need { bool sum = false, cnt = false, ssq = false, mn = false, mx = false, prod = false, nulls = false; };
+  std::vector<Need> need;
+  sc.req_val.resize((size_t)nreqs);
+  bool need_cnt_all = false;
+  for (int r = 0; r < nreqs; ++r) {
+    const b2_column_view& v = reqs[r].values;
+    int slot = -1;
+    for (size_t i = 0; i < seen.size(); ++i)
+      if (seen[i].d == v.data && seen[i].m == v.null_mask && seen[i].off == v.offset && seen[i].type == v.type_id)
+        slot = (int)i;
+    if (slot < 0) {
+      if ((int)seen.size() >= MAX_VALS) B2_FAIL(B2_UNSUPPORTED, "more than 16 distinct value columns");
+      slot = (int)seen.size();
+      seen.push_back(VKey{v.data, v.null_mask, v.offset, v.type_id});
+      need.emplace_back();
+      sc.val_types[slot] = v.type_id;
+    }
+    sc.req_val[(size_t)r] = slot;
+    Need& nd = need[(size_t)slot];
+    const bool has_nulls = v.null_mask != nullptr && v.null_count != 0;
+    nd.nulls = nd.nulls || has_nulls;
+    for (int a = 0; a < reqs[r].num_aggregations; ++a) {
+      switch (reqs[r].aggregations[a].kind) {
+        case B2_AGG_SUM: nd.sum = true; break;
+        case B2_AGG_COUNT_VALID: nd.cnt = true; break;
+        case B2_AGG_COUNT_ALL: need_cnt_all = true; break;
+        case B2_AGG_MIN: nd.mn = true; break;
+        case B2_AGG_MAX: nd.mx = true; break;
+        case B2_AGG_PRODUCT: nd.prod = true; break;
+        case B2_AGG_SUM_OF_SQUARES: nd.ssq = true; break;
+        case B2_AGG_MEAN: nd.sum = nd.cnt = true; break;
+        default: nd.sum = nd.cnt = nd.ssq = true; break;  // M2, VARIANCE, STD
+      }
+    }
+  }
+  sc.nvals = (int)seen.size();
+
+  // cells, per value column in the order Σ, n, Σx², min, max, Π; the row count last
+  struct CellIdx { int sum = -1, cnt = -1, ssq = -1, mn = -1, mx = -1, prod = -1; };
+  std::vector<CellIdx> idx((size_t)sc.nvals);
+  auto add_cell = [&](int op, int col) {
+    if (sc.ncells >= MAX_CELLS) B2_FAIL(B2_UNSUPPORTED, "too many accumulators in one aggregate call");
+    sc.cells[sc.ncells] = DCell{(unsigned char)op, (unsigned char)col};
+    return sc.ncells++;
+  };
+  for (int s = 0; s < sc.nvals; ++s) {
+    Need& nd = need[(size_t)s];
+    const int t = sc.val_types[s];
+    const bool f = is_float_t(t);
+    const bool uns = t == B2_UINT64;
+    if (nd.nulls && (nd.sum || nd.ssq || nd.mn || nd.mx || nd.prod)) nd.cnt = true;  // decides validity
+    if (nd.sum) idx[(size_t)s].sum = add_cell(f ? OP_SUM_F : OP_SUM_I, s);
+    if (nd.cnt) idx[(size_t)s].cnt = add_cell(OP_CNT_V, s);
+    if (nd.ssq) idx[(size_t)s].ssq = add_cell(f ? OP_SSQ_F : OP_SSQ_I, s);
+    if (nd.mn) idx[(size_t)s].mn = add_cell(f ? OP_MIN_F : uns ? OP_MIN_U : OP_MIN_I, s);
+    if (nd.mx) idx[(size_t)s].mx = add_cell(f ? OP_MAX_F : uns ? OP_MAX_U : OP_MAX_I, s);
+    if (nd.prod) idx[(size_t)s].prod = add_cell(f ? OP_PROD_F : OP_PROD_I, s);
+  }
+  int cnt_all = -1;
+  if (need_cnt_all) cnt_all = add_cell(OP_CNT_A, 0);
+
+  // outputs
+  sc.req_nouts.resize((size_t)nreqs);
+  for (int r = 0; r < nreqs; ++r) {
+    const int s = sc.req_val[(size_t)r];
+    const int t = reqs[r].values.type_id;
+    const bool f = is_float_t(t);
+    const bool has_nulls = reqs[r].values.null_mask != nullptr && reqs[r].values.null_count != 0;
+    const CellIdx& ci = idx[(size_t)s];
+    sc.req_nouts[(size_t)r] = reqs[r].num_aggregations;
+    for (int a = 0; a < reqs[r].num_aggregations; ++a) {
+      OutSpec o;
+      o.req = r; o.agg = a;
+      const int kind = reqs[r].aggregations[a].kind;
+      o.rtype = result_type(t, kind);
+      o.ddof = reqs[r].aggregations[a].ddof;
+      o.src_float = f;
+      o.c_cnt = has_nulls ? ci.cnt : -1;
+      o.nullable = has_nulls;  // cpp/src/groupby/hash/output_utils.cu:61-68
+      switch (kind) {
+        case B2_AGG_COUNT_VALID: o.kind = OK_COUNT; o.c_a = ci.cnt; o.c_cnt = -1; o.nullable = false; break;
+        case B2_AGG_COUNT_ALL: o.kind = OK_COUNT; o.c_a = cnt_all; o.c_cnt = -1; o.nullable = false; break;
+        case B2_AGG_SUM: o.kind = f ? OK_FLT : OK_INT; o.c_a = ci.sum; break;
+        case B2_AGG_SUM_OF_SQUARES: o.kind = f ? OK_FLT : OK_INT; o.c_a = ci.ssq; break;
+        case B2_AGG_PRODUCT: o.kind = f ? OK_FLT : OK_INT; o.c_a = ci.prod; break;
+        case B2_AGG_MIN: o.kind = f ? OK_MINMAX_F : OK_INT; o.c_a = ci.mn; break;
+        case B2_AGG_MAX: o.kind = f ? OK_MINMAX_F : OK_INT; o.c_a = ci.mx; break;
+        case B2_AGG_MEAN: o.kind = OK_MEAN; o.c_a = ci.sum; o.c_cnt = ci.cnt; break;
+        case B2_AGG_M2: o.kind = OK_M2; o.c_a = ci.sum; o.c_b = ci.ssq; o.c_cnt = ci.cnt; o.nullable = false; break;
+        case B2_AGG_VARIANCE: o.kind = OK_VAR; o.c_a = ci.sum; o.c_b = ci.ssq; o.c_cnt = ci.cnt; o.nullable = true; break;
+        default: o.kind = OK_STD; o.c_a = ci.sum; o.c_b = ci.ssq; o.c_cnt = ci.cnt; o.nullable = true; break;
+      }
+      sc.outs.push_back(o);
+    }
+  }
+  if ((int)sc.outs.size() > MAX_OUTS) B2_FAIL(B2_UNSUPPORTED, "more than 64 aggregations in one aggregate call");
+  sc.f32mean = sc.key_mode == KM_PACKED && sc.ncells == 2 && sc.cells[0].op == OP_SUM_F && sc.cells[1].op == OP_CNT_V &&
+               sc.cells[0].col == sc.cells[1].col && sc.val_types[sc.cells[0].col] == B2_FLOAT32;
+  return sc;
+}
+
+// schema part of the device plan
+void fill_plan_schema(DPlan& P, const Schema& sc)
+{
+  std::memset(&P, 0, sizeof(P));
+  P.nkeys = sc.nkeys; P.nvals = sc.nvals; P.ncells = sc.ncells; P.key_mode = sc.key_mode;
+  P.include_nulls = sc.include_nulls; P.stride = 1 + sc.ncells;
+  for (int k = 0; k < sc.nkeys; ++k) {
+    P.keys[k].vclass = vclass_of(sc.key_types[k]);
+    P.keys[k].width = sc.key_width[k];
+    P.keys[k].shift = sc.key_shift[k];
+    P.keys[k].nullbit = sc.key_nullbit[k];
+  }
+  for (int s = 0; s < sc.nvals; ++s) P.vals[s].vclass = vclass_of(sc.val_types[s]);
+  for (int c = 0; c < sc.ncells; ++c) P.cells[c] = sc.cells[c];
+}
+
+// pointer part: the views of one update
+void bind_plan_inputs(DPlan& P, const Schema& sc, const b2_groupby& gb, const b2_aggregation_request* reqs, int nreqs)
+{
+  if ((int)gb.keys.size() != sc.nkeys) B2_FAIL(B2_LOGIC_ERROR, "key schema differs from the state's");
+  P.nrows = gb.keys[0].v.size;
+  for (int k = 0; k < sc.nkeys; ++k) {
+    const b2_column_view& c = gb.keys[k].v;
+    if (c.type_id != sc.key_types[k]) B2_FAIL(B2_LOGIC_ERROR, "key schema differs from the state's");
+    if (sc.key_mode == KM_PACKED && sc.key_nullbit[k] < 0 && sc.include_nulls && c.null_mask)
+      B2_FAIL(B2_LOGIC_ERROR, "key column gained a null mask after the state was created");
+    P.keys[k].data = (const unsigned char*)c.data;
+    P.keys[k].mask = c.null_mask;
+    P.keys[k].offset = c.offset;
+    P.keys[k].offsets = nullptr;
+    P.keys[k].offs64 = 0;
+    if (c.type_id == B2_STRING && c.num_children > 0) {
+      const b2_column_view& o = c.children[0];
+      P.keys[k].offsets = (const unsigned char*)o.data + (size_t)o.offset * (o.type_id == B2_INT64 ? 8 : 4);
+      P.keys[k].offs64 = o.type_id == B2_INT64;
+    }
+  }
+  std::vector<bool> bound((size_t)sc.nvals, false);
+  for (int r = 0; r < nreqs; ++r) {
+    const int s = sc.req_val[(size_t)r];
+    const b2_column_view& v = reqs[r].values;
+    if (v.type_id != sc.val_types[s]) B2_FAIL(B2_LOGIC_ERROR, "request schema differs from the state's");
+    if (bound[(size_t)s]) continue;
+    bound[(size_t)s] = true;
+    P.vals[s].data = (const unsigned char*)v.data;
+    P.vals[s].mask = (v.null_mask && v.null_count != 0) ? v.null_mask : nullptr;
+    P.vals[s].offset = v.offset;
+  }
+  P.nfilters = (int)gb.filters.size();
+  for (int f = 0; f < P.nfilters; ++f) {
+    P.filters[f] = gb.filters[(size_t)f];
+    P.filter_offsets[f] = gb.filter_offsets[(size_t)f];
+  }
+}
+
+// ------------------------------------------------------------------------------ table management
+int grid_for(int64_t items, int block, int per_sm)
+{
+  const int64_t want = (items + block - 1) / block;
+  const int64_t cap = (int64_t)device_info().sms * per_sm;
+  return (int)std::max<int64_t>(1, std::min(want, cap));
+}
+
+void free_table(b2_groupby_state& st, cudaStream_t stream)
+{
+  if (st.table) { cudaFreeAsync(st.table, stream); st.table = nullptr; }
+  st.cap = 0;
+}
+
+void alloc_table(b2_groupby_state& st, int64_t cap, double max_load, cudaStream_t stream)
+{
+  free_table(st, stream);
+  if (cap > 0x7FFFFFF0ll) B2_FAIL(B2_UNSUPPORTED, "hash table would need more than 2^31 slots");
+  const size_t bytes = (size_t)(cap + 1) * (size_t)st.plan.stride * 8;
+  st.table = (u64*)default_alloc(bytes, stream, nullptr);
+  if (!st.table) B2_FAIL(B2_OUT_OF_MEMORY, "out of device memory allocating a " + std::to_string(bytes) + "-byte hash table");
+  g_stats.scratch_bytes += (int64_t)bytes;
+  st.cap = cap;
+  if (!st.ctrl) {
+    st.ctrl = (DCtrl*)default_alloc(sizeof(DCtrl), stream, nullptr);
+    if (!st.ctrl) B2_FAIL(B2_OUT_OF_MEMORY, "out of device memory");
+  }
+  DCtrl h{};
+  h.claim_limit = (u64)((double)cap * max_load);
+  st.host_ctrl = h;
+  CUDA_TRY(cudaMemcpyAsync(st.ctrl, &st.host_ctrl, sizeof(DCtrl), cudaMemcpyHostToDevice, stream));
+  k_table_init<<<grid_for(cap + 1, 256, 16), 256, 0, stream>>>(st.table, cap + 1, st.plan);
+  CUDA_TRY(cudaGetLastError());
+  g_stats.kernel_launches++;
+  g_stats.table_capacity = cap;
+  st.ctrl_fresh = true;
+}
+
+void read_ctrl(b2_groupby_state& st, cudaStream_t stream)
+{
+  if (st.ctrl_fresh || !st.ctrl) return;
+  CUDA_TRY(cudaMemcpyAsync(&st.host_ctrl, st.ctrl, sizeof(DCtrl), cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  st.ctrl_fresh = true;
+}
+
+int64_t num_groups(const b2_groupby_state& st) { return (int64_t)st.host_ctrl.nclaimed + (st.host_ctrl.special_used ? 1 : 0); }
+
+template <int KM, int LAYOUT>
+void launch_aggregate(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, int S, int fill_limit, size_t smem,
+                      cudaStream_t stream)
+{
+  auto kern = k_aggregate<KM, LAYOUT>;
+  static thread_local size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  const int64_t tile = (int64_t)AGG_BLOCK * AGG_ROWS;
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((P.nrows + tile - 1) / tile, device_info().sms));
+  kern<<<grid, AGG_BLOCK, smem, stream>>>(P, tbl, cap, ctrl, S, fill_limit);
+  CUDA_TRY(cudaGetLastError());
+  g_stats.kernel_launches++;
+}
+
+struct EventPair {  // times the fused kernel on the caller's stream; read after the call's sync
+  cudaEvent_t a = nullptr, b = nullptr;
+  EventPair() { cudaEventCreate(&a); cudaEventCreate(&b); }
+  ~EventPair() { if (a) cudaEventDestroy(a); if (b) cudaEventDestroy(b); }
+};
+EventPair& kernel_events()
+{
+  static thread_local EventPair ev;
+  return ev;
+}
+
+// one pass of the fused kernel over the bound inputs into st.table
+void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stream)
+{
+  const Schema& sc = st.sc;
+  int layout = SL_NONE;
+  int S = 0, fill_limit = 0;
+  size_t smem = 0;
+  if (gb.table_variant != 1) {
+    const int budget = gb.shared_table_bytes > 0 ? std::min(gb.shared_table_bytes, device_info().smem_optin - 1024)
+                                                 : device_info().smem_optin - 1024;
+    const int per_slot = sc.f32mean ? 16 : 8 * (1 + sc.ncells);
+    S = budget / per_slot - 1;
+    if (S >= 256) {
+      layout = sc.f32mean ? SL_F32MEAN : SL_GENERIC;
+      fill_limit = (int)(S * (sc.f32mean ? 0.80 : 0.75));
+      smem = (size_t)(S + 1) * per_slot;
+    }
+  }
+  g_stats.used_shared_table = layout != SL_NONE;
+  const DPlan& P = st.plan;
+  EventPair& ev = kernel_events();
+  cudaEventRecord(ev.a, stream);
+  if (sc.key_mode == KM_PACKED) {
+    if (layout == SL_F32MEAN) launch_aggregate<KM_PACKED, SL_F32MEAN>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream);
+    else if (layout == SL_GENERIC) launch_aggregate<KM_PACKED, SL_GENERIC>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream);
+    else launch_aggregate<KM_PACKED, SL_NONE>(P, st.table, st.cap, st.ctrl, 0, 0, 0, stream);
+  } else {
+    if (layout == SL_GENERIC) launch_aggregate<KM_ROWS, SL_GENERIC>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream);
+    else launch_aggregate<KM_ROWS, SL_NONE>(P, st.table, st.cap, st.ctrl, 0, 0, 0, stream);
+  }
+  cudaEventRecord(ev.b, stream);
+  st.ctrl_fresh = false;
+}
+
+constexpr int64_t SPECULATIVE_CAP = 1 << 20;  // first table when nothing is known about the cardinality
+constexpr double MAX_LOAD = 0.70;
+
+// aggregates the bound inputs into an EMPTY state, growing the table until it fits
+void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stream)
+{
+  const int64_t n = st.plan.nrows;
+  const int64_t hint = st.expected_groups > 0 ? st.expected_groups : gb.expected_groups;
+  const int64_t full = std::max<int64_t>(1024, (int64_t)((double)n / 0.6) + 64);  // groups <= rows
+  int64_t cap;
+  if (hint > 0) cap = std::min(full, std::max<int64_t>(1024, (int64_t)((double)hint / 0.5) + 64));
+  else if (n <= SPECULATIVE_CAP / 2) cap = std::max<int64_t>(1024, 2 * n + 64);
+  else cap = SPECULATIVE_CAP;
+  for (int attempt = 1;; ++attempt) {
+    g_stats.table_attempts = attempt;
+    alloc_table(st, cap, cap >= full ? 1.0 : MAX_LOAD, stream);
+    run_aggregate(st, gb, stream);
+    read_ctrl(st, stream);
+    {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, kernel_events().a, kernel_events().b) == cudaSuccess) g_stats.aggregate_kernel_ms += ms;
+      else cudaGetLastError();
+    }
+    if (!st.host_ctrl.overflow) break;
+    if (cap >= full) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow at full capacity");
+    cap = (attempt == 1 && hint > 0 && cap * 4 < full) ? cap * 4 : full;
+  }
+}
+
+// all groups of a table as packed records, destination-major by owner; counts on the host
+void pack_table(b2_groupby_state& st, int nparts, cudaStream_t stream, Scratch& out, std::vector<int64_t>& counts)
+{
+  if (st.sc.key_mode != KM_PACKED)
+    B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys are not transferable; partition the rows instead");
+  counts.assign((size_t)nparts, 0);
+  if (!st.table) { out = Scratch(8, stream); return; }
+  read_ctrl(st, stream);
+  const int64_t G = num_groups(st);
+  Scratch dcounts((size_t)nparts * 2 * sizeof(u64), stream);
+  CUDA_TRY(cudaMemsetAsync(dcounts.p, 0, dcounts.bytes, stream));
+  u64* d_counts = (u64*)dcounts.p;
+  u64* d_cursor = d_counts + nparts;
+  const int grid = grid_for(st.cap + 1, 256, 8);
+  k_pack_count<<<grid, 256, (size_t)nparts * sizeof(u64), stream>>>(st.table, st.cap, st.plan.stride, nparts, st.ctrl, d_counts);
+  CUDA_TRY(cudaGetLastError());
+  std::vector<u64> h((size_t)nparts);
+  CUDA_TRY(cudaMemcpyAsync(h.data(), d_counts, (size_t)nparts * sizeof(u64), cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  std::vector<u64> starts((size_t)nparts);
+  u64 run = 0;
+  for (int p = 0; p < nparts; ++p) { starts[(size_t)p] = run; run += h[(size_t)p]; counts[(size_t)p] = (int64_t)h[(size_t)p]; }
+  if ((int64_t)run != G) B2_FAIL(B2_INTERNAL_ERROR, "pack: group count mismatch");
+  CUDA_TRY(cudaMemcpyAsync(d_cursor, starts.data(), (size_t)nparts * sizeof(u64), cudaMemcpyHostToDevice, stream));
+  out = Scratch(std::max<size_t>(8, (size_t)G * st.plan.stride * 8), stream);
+  k_pack_scatter<<<grid, 256, 0, stream>>>(st.table, st.cap, st.plan.stride, nparts, st.ctrl, d_cursor, (u64*)out.p);
+  CUDA_TRY(cudaGetLastError());
+  CUDA_TRY(cudaStreamSynchronize(stream));  // `starts` is read by the copy above
+  g_stats.kernel_launches += 2;
+}
+
+void merge_records(b2_groupby_state& st, const u64* recs, int64_t nrecs, cudaStream_t stream)
+{
+  if (st.sc.key_mode != KM_PACKED)
+    B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys are not transferable; partition the rows instead");
+  if (nrecs <= 0) return;
+  read_ctrl(st, stream);
+  const int64_t G = st.table ? num_groups(st) : 0;
+  const int64_t need = std::max<int64_t>(1024, (int64_t)((double)(G + nrecs) / 0.6) + 64);
+  if (!st.table) {
+    alloc_table(st, std::max<int64_t>(need, st.expected_groups > 0 ? (int64_t)(st.expected_groups / 0.5) : 0), 1.0, stream);
+  } else if (st.cap < need) {
+    // grow: move the present groups into a larger table
+    Scratch old;
+    std::vector<int64_t> cnt;
+    pack_table(st, 1, stream, old, cnt);
+    alloc_table(st, need * 2, 1.0, stream);
+    if (cnt[0] > 0) {
+      k_merge<<<grid_for(cnt[0], 256, 8), 256, 0, stream>>>(st.plan, st.table, st.cap, st.ctrl, (const u64*)old.p, cnt[0]);
+      CUDA_TRY(cudaGetLastError());
+      g_stats.kernel_launches++;
+    }
+  } else {
+    // the existing table stays; its claim limit must allow the new records
+    DCtrl h = st.host_ctrl;
+    h.claim_limit = (u64)st.cap;
+    CUDA_TRY(cudaMemcpyAsync(&st.ctrl->claim_limit, &h.claim_limit, sizeof(u64), cudaMemcpyHostToDevice, stream));
+    CUDA_TRY(cudaStreamSynchronize(stream));
+  }
+  k_merge<<<grid_for(nrecs, 256, 8), 256, 0, stream>>>(st.plan, st.table, st.cap, st.ctrl, recs, nrecs);
+  CUDA_TRY(cudaGetLastError());
+  g_stats.kernel_launches++;
+  st.ctrl_fresh = false;
+  read_ctrl(st, stream);
+  if (st.host_ctrl.overflow) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow while merging partial records");
+}
+
+// ------------------------------------------------------------------------------ outputs
+struct OwnedGuard {  // frees partially built results on failure
+  b2_groupby_result* r;
+  bool armed = true;
+  ~OwnedGuard() { if (armed && r) b2_result_free(r); }
+};
+
+void* out_alloc(const b2_allocator& al, size_t bytes, cudaStream_t stream)
+{
+  void* p = al.allocate(bytes ? bytes : 8, stream, al.ctx);
+  if (!p) B2_FAIL(B2_OUT_OF_MEMORY, "the allocator returned null for " + std::to_string(bytes) + " bytes");
+  return p;
+}
+
+void init_owned(b2_owned_column& c, int type_id, int64_t n, bool nullable, const b2_allocator& al, cudaStream_t stream)
+{
+  std::memset(&c, 0, sizeof(c));
+  c.type_id = type_id;
+  c.size = (int32_t)n;
+  const int w = width_of(type_id);
+  if (w > 0) {
+    // results narrower than 4 bytes are padded to whole words like the reference's
+    // (cpp/src/groupby/hash/output_utils.cu:71-82)
+    c.data_bytes = ((size_t)n * w + 3) / 4 * 4;
+    c.data = out_alloc(al, c.data_bytes, stream);
+  }
+  if (nullable) {
+    c.null_mask_bytes = (size_t)((n + 511) / 512) * 64;  // 64-byte padded, cpp/include/cudf/null_mask.hpp:52-57
+    if (c.null_mask_bytes == 0) c.null_mask_bytes = 64;
+    c.null_mask = (uint32_t*)out_alloc(al, c.null_mask_bytes, stream);
+    CUDA_TRY(cudaMemsetAsync(c.null_mask, 0xFF, c.null_mask_bytes, stream));
+  }
+}
+
+void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocator* allocator, b2_groupby_result* out)
+{
+  const Schema& sc = st.sc;
+  const b2_allocator al = resolve(allocator);
+  std::memset(out, 0, sizeof(*out));
+  out->allocator = al;
+  out->stream = stream;
+  OwnedGuard guard{out};
+
+  read_ctrl(st, stream);
+  const int64_t G = st.table ? num_groups(st) : 0;
+  if (G > 0x7FFFFFFFll) B2_FAIL(B2_UNSUPPORTED, "more than 2^31-1 groups");
+  out->num_groups = (int32_t)G;
+  out->num_keys = sc.nkeys;
+  out->keys = (b2_owned_column*)std::calloc((size_t)std::max(1, sc.nkeys), sizeof(b2_owned_column));
+  const int nreqs = (int)sc.req_nouts.size();
+  out->num_requests = nreqs;
+  out->num_results = (int32_t*)std::calloc((size_t)std::max(1, nreqs), sizeof(int32_t));
+  out->results = (b2_owned_column**)std::calloc((size_t)std::max(1, nreqs), sizeof(b2_owned_column*));
+  for (int r = 0; r < nreqs; ++r) {
+    out->num_results[r] = sc.req_nouts[(size_t)r];
+    out->results[r] = (b2_owned_column*)std::calloc((size_t)std::max(1, sc.req_nouts[(size_t)r]), sizeof(b2_owned_column));
+  }
+
+  // result columns
+  auto plan = std::make_unique<DOutPlan>();
+  std::memset(plan.get(), 0, sizeof(DOutPlan));
+  plan->nouts = (int)sc.outs.size();
+  for (size_t i = 0; i < sc.outs.size(); ++i) {
+    const OutSpec& o = sc.outs[i];
+    b2_owned_column& c = out->results[o.req][o.agg];
+    init_owned(c, o.rtype, G, o.nullable, al, stream);
+    DOutCol& d = plan->outs[i];
+    d.data = c.data; d.mask = c.null_mask; d.kind = o.kind; d.rclass = vclass_of(o.rtype);
+    d.c_a = o.c_a; d.c_b = o.c_b; d.c_cnt = o.c_cnt; d.ddof = o.ddof; d.src_float = o.src_float;
+    d.null_slot = (int)i;
+  }
+  // key columns
+  Scratch rep_rows;
+  for (int k = 0; k < sc.nkeys; ++k) {
+    b2_owned_column& c = out->keys[k];
+    const bool nullable = sc.include_nulls && sc.key_nullable[k];
+    if (sc.key_types[k] == B2_STRING) {
+      std::memset(&c, 0, sizeof(c));
+      c.type_id = B2_STRING;
+      c.size = (int32_t)G;
+      if (nullable) {
+        c.null_mask_bytes = (size_t)std::max<int64_t>(1, (G + 511) / 512) * 64;
+        c.null_mask = (uint32_t*)out_alloc(al, c.null_mask_bytes, stream);
+        CUDA_TRY(cudaMemsetAsync(c.null_mask, 0xFF, c.null_mask_bytes, stream));
+      }
+    } else {
+      init_owned(c, sc.key_types[k], G, nullable, al, stream);
+    }
+    plan->kdata[k] = c.data;
+    plan->kmask[k] = c.null_mask;
+  }
+  Scratch null_counts((MAX_OUTS + MAX_KEYS) * sizeof(u32), stream);
+  CUDA_TRY(cudaMemsetAsync(null_counts.p, 0, null_counts.bytes, stream));
+  plan->null_counts = (u32*)null_counts.p;
+  if (sc.key_mode == KM_ROWS) {
+    rep_rows = Scratch(std::max<size_t>(8, (size_t)G * sizeof(int)), stream);
+    plan->rep_rows = (int*)rep_rows.p;
+  }
+
+  std::vector<u32> h_nulls(MAX_OUTS + MAX_KEYS, 0);
+  if (G > 0) {
+    u64 zero = 0;
+    CUDA_TRY(cudaMemcpyAsync(&st.ctrl->out_cursor, &zero, sizeof(u64), cudaMemcpyHostToDevice, stream));
+    k_finalize<<<grid_for(st.cap + 1, 256, 8), 256, 0, stream>>>(st.plan, *plan, st.table, st.cap, st.ctrl);
+    CUDA_TRY(cudaGetLastError());
+    g_stats.kernel_launches++;
+
+    if (sc.key_mode == KM_ROWS) {
+      if ((int)st.row_keys.size() != sc.nkeys) B2_FAIL(B2_INTERNAL_ERROR, "row-keyed state without bound key views");
+      for (int k = 0; k < sc.nkeys; ++k) {
+        b2_owned_column& c = out->keys[k];
+        const DKeyCol& kc = st.plan.keys[k];
+        if (sc.key_types[k] != B2_STRING) {
+          DGather gth{kc.data, kc.mask, kc.offset, kc.width, (unsigned char*)c.data, c.null_mask,
+                      plan->null_counts + MAX_OUTS + k};
+          k_gather_fixed<<<grid_for(G, 256, 8), 256, 0, stream>>>(gth, plan->rep_rows, G);
+          CUDA_TRY(cudaGetLastError());
+          g_stats.kernel_launches++;
+          continue;
+        }
+        // strings: lengths → offsets → bytes
+        Scratch lens((size_t)(G + 1) * sizeof(i64), stream), offs((size_t)(G + 1) * sizeof(i64), stream);
+        k_string_lengths<<<grid_for(G, 256, 8), 256, 0, stream>>>(kc, plan->rep_rows, G, (i64*)lens.p, c.null_mask,
+                                                                  plan->null_counts + MAX_OUTS + k);
+        k_exclusive_scan<<<1, 1024, 0, stream>>>((const i64*)lens.p, (i64*)offs.p, G);
+        CUDA_TRY(cudaGetLastError());
+        i64 total = 0;
+        CUDA_TRY(cudaMemcpyAsync(&total, (i64*)offs.p + G, sizeof(i64), cudaMemcpyDeviceToHost, stream));
+        CUDA_TRY(cudaStreamSynchronize(stream));
+        // INT64 offsets once the chars pass the reference's large-strings threshold
+        // (cpp/src/strings/utilities.cu:150-157)
+        const bool big = total > 0x7FFFFFFFll;
+        c.data_bytes = (size_t)std::max<i64>(total, 1);
+        c.data = out_alloc(al, c.data_bytes, stream);
+        c.num_children = 1;
+        c.children = (b2_owned_column*)std::calloc(1, sizeof(b2_owned_column));
+        b2_owned_column& oc = c.children[0];
+        oc.type_id = big ? B2_INT64 : B2_INT32;
+        oc.size = (int32_t)(G + 1);
+        oc.data_bytes = (size_t)(G + 1) * (big ? 8 : 4);
+        oc.data = out_alloc(al, oc.data_bytes, stream);
+        if (big) k_string_copy<i64><<<grid_for(G * 32, 256, 8), 256, 0, stream>>>(kc, plan->rep_rows, G, (const i64*)offs.p, (i64*)oc.data, (unsigned char*)c.data);
+        else k_string_copy<int><<<grid_for(G * 32, 256, 8), 256, 0, stream>>>(kc, plan->rep_rows, G, (const i64*)offs.p, (int*)oc.data, (unsigned char*)c.data);
+        CUDA_TRY(cudaGetLastError());
+        g_stats.kernel_launches += 3;
+      }
+    }
+    CUDA_TRY(cudaMemcpyAsync(h_nulls.data(), null_counts.p, null_counts.bytes, cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaStreamSynchronize(stream));
+  } else {
+    // empty result: STRING keys still carry a one-entry offsets child
+    for (int k = 0; k < sc.nkeys; ++k)
+      if (sc.key_types[k] == B2_STRING) {
+        b2_owned_column& c = out->keys[k];
+        c.num_children = 1;
+        c.children = (b2_owned_column*)std::calloc(1, sizeof(b2_owned_column));
+        c.children[0].type_id = B2_INT32;
+        c.children[0].size = 1;
+        c.children[0].data_bytes = 4;
+        c.children[0].data = out_alloc(al, 4, stream);
+        CUDA_TRY(cudaMemsetAsync(c.children[0].data, 0, 4, stream));
+      }
+    CUDA_TRY(cudaStreamSynchronize(stream));
+  }
+  for (size_t i = 0; i < sc.outs.size(); ++i) out->results[sc.outs[i].req][sc.outs[i].agg].null_count = (int32_t)h_nulls[i];
+  for (int k = 0; k < sc.nkeys; ++k) out->keys[k].null_count = (int32_t)h_nulls[(size_t)MAX_OUTS + k];
+  guard.armed = false;
+}
+
+b2_groupby_state* make_state(const b2_groupby& gb, const b2_aggregation_request* reqs, int nreqs)
+{
+  validate_requests(gb, reqs, nreqs);
+  auto st = std::make_unique<b2_groupby_state>();
+  st->sc = make_schema(gb, reqs, nreqs);
+  fill_plan_schema(st->plan, st->sc);
+  st->expected_groups = gb.expected_groups;
+  return st.release();
+}
+
+void update_state(b2_groupby_state& st, const b2_groupby& gb, const b2_aggregation_request* reqs, int nreqs,
+                  cudaStream_t stream)
+{
+  validate_requests(gb, reqs, nreqs);
+  if ((int)st.sc.req_val.size() != nreqs) B2_FAIL(B2_LOGIC_ERROR, "request list differs from the state's");
+  st.last_stream = stream;
+  if (gb.keys[0].v.size == 0) return;
+  if (!st.table) {
+    bind_plan_inputs(st.plan, st.sc, gb, reqs, nreqs);
+    aggregate_fresh(st, gb, stream);
+    if (st.sc.key_mode == KM_ROWS) { st.has_rows = true; st.row_keys = gb.keys; }
+    return;
+  }
+  if (st.sc.key_mode != KM_PACKED)
+    B2_FAIL(B2_UNSUPPORTED, "a state keyed on string / float / wide keys takes one update only");
+  // batch-local table, then merge (a failed pass must not leave half a batch in the state)
+  b2_groupby_state tmp;
+  tmp.sc = st.sc;
+  tmp.plan = st.plan;
+  bind_plan_inputs(tmp.plan, tmp.sc, gb, reqs, nreqs);
+  try {
+    aggregate_fresh(tmp, gb, stream);
+    Scratch recs;
+    std::vector<int64_t> cnt;
+    pack_table(tmp, 1, stream, recs, cnt);
+    merge_records(st, (const u64*)recs.p, cnt[0], stream);
+  } catch (...) {
+    free_table(tmp, stream);
+    if (tmp.ctrl) cudaFreeAsync(tmp.ctrl, stream);
+    throw;
+  }
+  free_table(tmp, stream);
+  if (tmp.ctrl) cudaFreeAsync(tmp.ctrl, stream);
+}
+
+}  // namespace
+
+// ================================================================================ C ABI
+extern "C" {
+
+b2_status b2_groupby_create(const b2_column_view* keys, int32_t num_keys, int32_t null_policy,
+                            const b2_groupby_options* options, b2_groupby** out)
+{
+  return guarded([&] {
+    if (!out) B2_FAIL(B2_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    if (num_keys < 0 || (num_keys > 0 && !keys)) B2_FAIL(B2_INVALID_ARGUMENT, "keys is null");
+    if (null_policy != B2_NULL_EXCLUDE && null_policy != B2_NULL_INCLUDE) B2_FAIL(B2_INVALID_ARGUMENT, "bad null_policy");
+    auto gb = std::make_unique<b2_groupby>();
+    for (int k = 0; k < num_keys; ++k) {
+      if (keys[k].size != keys[0].size) B2_FAIL(B2_LOGIC_ERROR, "key columns differ in size");
+      gb->keys.emplace_back(keys[k]);
+    }
+    gb->null_policy = null_policy;
+    if (options) {
+      gb->expected_groups = options->expected_groups;
+      gb->table_variant = options->table_variant;
+      gb->shared_table_bytes = options->shared_table_bytes;
+      if (options->num_row_filters > MAX_FILTERS) B2_FAIL(B2_UNSUPPORTED, "more than 8 row filters");
+      for (int f = 0; f < options->num_row_filters; ++f) {
+        if (!options->row_filter_masks || !options->row_filter_masks[f]) continue;
+        gb->filters.push_back(options->row_filter_masks[f]);
+        gb->filter_offsets.push_back(options->row_filter_offsets ? options->row_filter_offsets[f] : 0);
+      }
+    }
+    *out = gb.release();
+  });
+}
+
+void b2_groupby_destroy(b2_groupby* gb) { delete gb; }
+
+b2_status b2_groupby_aggregate(b2_groupby* gb, const b2_aggregation_request* requests, int32_t num_requests,
+                               void* stream, const b2_allocator* allocator, b2_groupby_result* out)
+{
+  return guarded([&] {
+    if (!gb || !out) B2_FAIL(B2_INVALID_ARGUMENT, "null argument");
+    g_stats = b2_call_stats{};
+    std::memset(out, 0, sizeof(*out));
+    if (gb->keys.empty()) B2_FAIL(B2_LOGIC_ERROR, "groupby needs at least one key column");
+    device_info();
+    std::unique_ptr<b2_groupby_state, void (*)(b2_groupby_state*)> st(make_state(*gb, requests, num_requests),
+                                                                      b2_state_destroy);
+    update_state(*st, *gb, requests, num_requests, (cudaStream_t)stream);
+    finalize_state(*st, (cudaStream_t)stream, allocator, out);
+  });
+}
+
+void b2_result_free(b2_groupby_result* r)
+{
+  if (!r) return;
+  const b2_allocator al = resolve(&r->allocator);
+  auto free_col = [&](b2_owned_column& c, auto&& self) -> void {
+    if (c.data) al.deallocate(c.data, c.data_bytes, r->stream, al.ctx);
+    if (c.null_mask) al.deallocate(c.null_mask, c.null_mask_bytes, r->stream, al.ctx);
+    for (int i = 0; i < c.num_children; ++i) self(c.children[i], self);
+    std::free(c.children);
+    c = b2_owned_column{};
+  };
+  if (r->keys) for (int k = 0; k < r->num_keys; ++k) free_col(r->keys[k], free_col);
+  std::free(r->keys);
+  if (r->results)
+    for (int q = 0; q < r->num_requests; ++q) {
+      if (!r->results[q]) continue;
+      for (int a = 0; a < r->num_results[q]; ++a) free_col(r->results[q][a], free_col);
+      std::free(r->results[q]);
+    }
+  std::free(r->results);
+  std::free(r->num_results);
+  std::memset(r, 0, sizeof(*r));
+}
+
+b2_status b2_state_create(const b2_groupby* gb, const b2_aggregation_request* requests, int32_t num_requests,
+                          b2_groupby_state** out)
+{
+  return guarded([&] {
+    if (!gb || !out) B2_FAIL(B2_INVALID_ARGUMENT, "null argument");
+    *out = nullptr;
+    if (gb->keys.empty()) B2_FAIL(B2_LOGIC_ERROR, "groupby needs at least one key column");
+    *out = make_state(*gb, requests, num_requests);
+  });
+}
+
+b2_status b2_state_update(b2_groupby_state* st, const b2_groupby* gb, const b2_aggregation_request* requests,
+                          int32_t num_requests, void* stream)
+{
+  return guarded([&] {
+    if (!st || !gb) B2_FAIL(B2_INVALID_ARGUMENT, "null argument");
+    g_stats = b2_call_stats{};
+    device_info();
+    update_state(*st, *gb, requests, num_requests, (cudaStream_t)stream);
+  });
+}
+
+int32_t b2_state_record_bytes(const b2_groupby_state* st) { return st ? st->plan.stride * 8 : 0; }
+
+b2_status b2_state_pack(b2_groupby_state* st, int32_t num_parts, void* stream, const b2_allocator* allocator,
+                        void** records_out, size_t* records_bytes, int64_t* counts)
+{
+  return guarded([&] {
+    if (!st || !records_out || !records_bytes || !counts || num_parts < 1 || num_parts > 4096)
+      B2_FAIL(B2_INVALID_ARGUMENT, "bad argument");
+    device_info();
+    std::vector<int64_t> c;
+    Scratch recs;
+    pack_table(*st, num_parts, (cudaStream_t)stream, recs, c);
+    int64_t total = 0;
+    for (int p = 0; p < num_parts; ++p) { counts[p] = c[(size_t)p]; total += c[(size_t)p]; }
+    const b2_allocator al = resolve(allocator);
+    *records_bytes = (size_t)total * st->plan.stride * 8;
+    *records_out = out_alloc(al, *records_bytes, (cudaStream_t)stream);
+    if (total > 0) {
+      CUDA_TRY(cudaMemcpyAsync(*records_out, recs.p, *records_bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+      CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    }
+  });
+}
+
+b2_status b2_state_merge(b2_groupby_state* st, const void* records, int64_t num_records, void* stream)
+{
+  return guarded([&] {
+    if (!st || (num_records > 0 && !records)) B2_FAIL(B2_INVALID_ARGUMENT, "bad argument");
+    device_info();
+    merge_records(*st, (const u64*)records, num_records, (cudaStream_t)stream);
+  });
+}
+
+b2_status b2_state_reset(b2_groupby_state* st, int64_t expected_groups, void* stream)
+{
+  return guarded([&] {
+    if (!st) B2_FAIL(B2_INVALID_ARGUMENT, "null argument");
+    free_table(*st, (cudaStream_t)stream);
+    st->host_ctrl = DCtrl{};
+    st->ctrl_fresh = true;
+    st->has_rows = false;
+    st->row_keys.clear();
+    st->expected_groups = expected_groups;
+  });
+}
+
+b2_status b2_state_num_groups(b2_groupby_state* st, void* stream, int64_t* out)
+{
+  return guarded([&] {
+    if (!st || !out) B2_FAIL(B2_INVALID_ARGUMENT, "null argument");
+    *out = 0;
+    if (!st->table) return;
+    read_ctrl(*st, (cudaStream_t)stream);
+    *out = num_groups(*st);
+  });
+}
+
+b2_status b2_state_finalize(b2_groupby_state* st, void* stream, const b2_allocator* allocator, b2_groupby_result* out)
+{
+  return guarded([&] {
+    if (!st || !out) B2_FAIL(B2_INVALID_ARGUMENT, "null argument");
+    device_info();
+    finalize_state(*st, (cudaStream_t)stream, allocator, out);
+  });
+}
+
+void b2_state_destroy(b2_groupby_state* st)
+{
+  if (!st) return;
+  if (st->table) cudaFreeAsync(st->table, st->last_stream);
+  if (st->ctrl) cudaFreeAsync(st->ctrl, st->last_stream);
+  delete st;
+}
+
+b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, int32_t num_key_columns,
+                            int32_t num_parts, void* stream_, const b2_allocator* allocator,
+                            b2_owned_column* out_columns, int64_t* offsets)
+{
+  return guarded([&] {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!columns || !out_columns || !offsets || num_columns < 1 || num_key_columns < 1 ||
+        num_key_columns > num_columns || num_parts < 1 || num_parts > 4096)
+      B2_FAIL(B2_INVALID_ARGUMENT, "bad argument");
+    if (num_columns > MAX_PART_COLS) B2_FAIL(B2_UNSUPPORTED, "more than 32 columns");
+    device_info();
+    const b2_allocator al = resolve(allocator);
+    const int64_t n = columns[0].size;
+    for (int c = 0; c < num_columns; ++c) {
+      if (columns[c].size != n) B2_FAIL(B2_LOGIC_ERROR, "columns differ in size");
+      if (width_of(columns[c].type_id) == 0) B2_FAIL(B2_UNSUPPORTED, "hash_partition serves fixed-width columns only");
+    }
+    // hashing plan over the key columns: nulls hash as nulls (they are rows like any other here)
+    b2_groupby gb;
+    for (int k = 0; k < num_key_columns; ++k) gb.keys.emplace_back(columns[k]);
+    gb.null_policy = B2_NULL_INCLUDE;
+    Schema sc = make_schema(gb, nullptr, 0);
+    DPlan P;
+    fill_plan_schema(P, sc);
+    bind_plan_inputs(P, sc, gb, nullptr, 0);
+
+    DPartPlan Q{};
+    Q.ncols = num_columns;
+    Q.nparts = num_parts;
+    const int64_t want = std::max<int64_t>(1, (n + 8191) / 8192);
+    const int grid = (int)std::min<int64_t>(want, (int64_t)device_info().sms * 4);
+    Q.rows_per_cta = ((n + grid - 1) / grid + PART_BLOCK - 1) / PART_BLOCK * PART_BLOCK;
+    for (int c = 0; c < num_columns; ++c) std::memset(&out_columns[c], 0, sizeof(b2_owned_column));
+    struct Guard {
+      b2_owned_column* cols; int n; const b2_allocator* al; cudaStream_t s; bool armed = true;
+      ~Guard() { if (armed) for (int i = 0; i < n; ++i) b2_column_free(&cols[i], al, s); }
+    } guard{out_columns, num_columns, &al, stream};
+    for (int c = 0; c < num_columns; ++c) {
+      const bool nullable = columns[c].null_mask != nullptr;
+      init_owned(out_columns[c], columns[c].type_id, n, nullable, al, stream);
+      out_columns[c].scale = columns[c].scale;
+      out_columns[c].null_count = nullable ? columns[c].null_count : 0;
+      if (nullable) CUDA_TRY(cudaMemsetAsync(out_columns[c].null_mask, 0, out_columns[c].null_mask_bytes, stream));
+      DPartCol& d = Q.cols[c];
+      d.src = (const unsigned char*)columns[c].data; d.mask = columns[c].null_mask; d.offset = columns[c].offset;
+      d.width = width_of(columns[c].type_id); d.dst = (unsigned char*)out_columns[c].data;
+      d.dst_mask = out_columns[c].null_mask;
+    }
+    for (int p = 0; p <= num_parts; ++p) offsets[p] = 0;
+    if (n == 0) { guard.armed = false; return; }
+
+    const size_t cells = (size_t)grid * num_parts;
+    Scratch counts(cells * sizeof(u32), stream), starts(cells * sizeof(i64), stream);
+    const size_t smem = (size_t)num_parts * sizeof(u32);
+    k_partition_count<<<grid, PART_BLOCK, smem, stream>>>(P, Q, (u32*)counts.p);
+    CUDA_TRY(cudaGetLastError());
+    std::vector<u32> h_counts(cells);
+    CUDA_TRY(cudaMemcpyAsync(h_counts.data(), counts.p, cells * sizeof(u32), cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaStreamSynchronize(stream));
+    std::vector<i64> h_starts(cells);
+    int64_t run = 0;
+    for (int p = 0; p < num_parts; ++p) {
+      offsets[p] = run;
+      for (int b = 0; b < grid; ++b) { h_starts[(size_t)b * num_parts + p] = run; run += h_counts[(size_t)b * num_parts + p]; }
+    }
+    offsets[num_parts] = run;
+    if (run != n) B2_FAIL(B2_INTERNAL_ERROR, "hash_partition: row count mismatch");
+    CUDA_TRY(cudaMemcpyAsync(starts.p, h_starts.data(), cells * sizeof(i64), cudaMemcpyHostToDevice, stream));
+    k_partition_scatter<<<grid, PART_BLOCK, smem, stream>>>(P, Q, (const i64*)starts.p);
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaStreamSynchronize(stream));
+    g_stats.kernel_launches += 2;
+    guard.armed = false;
+  });
+}
+
+void b2_column_free(b2_owned_column* c, const b2_allocator* allocator, void* stream)
+{
+  if (!c) return;
+  const b2_allocator al = resolve(allocator);
+  if (c->data) al.deallocate(c->data, c->data_bytes, stream, al.ctx);
+  if (c->null_mask) al.deallocate(c->null_mask, c->null_mask_bytes, stream, al.ctx);
+  for (int i = 0; i < c->num_children; ++i) b2_column_free(&c->children[i], allocator, stream);
+  std::free(c->children);
+  std::memset(c, 0, sizeof(*c));
+}
+
+const char* b2_last_error(void) { return g_last_error.c_str(); }
+const char* b2_version(void) { return "b2-groupby 0.1 (sm_100a)"; }
+void b2_get_last_stats(b2_call_stats* out) { if (out) *out = g_stats; }
+
+}  // extern "C"

@@ -1,0 +1,122 @@
+"""Multi-GPU groupby: one process per GPU, hash partition + all-to-all + local aggregation.
+
+The reference has no NCCL path; its multi-GPU groupby is the cudf-polars streaming executor:
+local aggregation, hash shuffle of the PARTIAL aggregates keyed on the group keys, then a reduction
+groupby on each owner (python/cudf_polars/cudf_polars/streaming/actor_graph/groupby.py:339-456),
+with the shuffle built on cudf::hash_partition (cpp/libcudf_streaming/src/partition_utils.cpp:72-100).
+Here the exchange is ``torch.distributed.all_to_all_single`` (NCCL over NVLink/NVSwitch on GPUs,
+gloo on CPU for tests); everything else is the CUDA library.
+
+Two strategies, as §"partials vs rows" of the design notes explains:
+  * ``partials``: aggregate locally, partition the partial records {key, n, Σx, Σx², min, max …} by
+    owner = hash(key) % world, exchange, merge, finalise.  Wire bytes ∝ local groups.
+  * ``rows``: partition the raw rows by owner, exchange the columns, aggregate locally.  Wire bytes
+    ∝ rows; used when almost every row is its own group.
+Each rank ends up with the complete results of the groups it owns (disjoint across ranks).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def plan_exchange(send_counts: Sequence[int], recv_counts: Sequence[int], unit_bytes: int):
+    """Split sizes (bytes) of a variable all-to-all and the receive offsets (in units)."""
+    in_splits = [int(c) * unit_bytes for c in send_counts]
+    out_splits = [int(c) * unit_bytes for c in recv_counts]
+    recv_offsets = [0]
+    for c in recv_counts:
+        recv_offsets.append(recv_offsets[-1] + int(c))
+    return in_splits, out_splits, recv_offsets
+
+
+def exchange_counts(send_counts: Sequence[int], device, group=None) -> List[int]:
+    """Every rank tells every other rank how many units it will send (the count matrix column)."""
+    t = torch.tensor(list(send_counts), dtype=torch.int64, device=device)
+    r = torch.empty_like(t)
+    dist.all_to_all_single(r, t, group=group)
+    return [int(x) for x in r.tolist()]
+
+
+def exchange_buffer(buf: torch.Tensor, send_counts: Sequence[int], recv_counts: Sequence[int], unit_bytes: int,
+                    group=None) -> torch.Tensor:
+    """Variable-size all-to-all of a destination-major uint8 buffer; returns the source-major buffer."""
+    in_splits, out_splits, _ = plan_exchange(send_counts, recv_counts, unit_bytes)
+    buf = buf.contiguous().view(torch.uint8).reshape(-1)
+    assert buf.numel() >= sum(in_splits)
+    out = torch.empty(max(sum(out_splits), 0), dtype=torch.uint8, device=buf.device)
+    dist.all_to_all_single(out, buf[: sum(in_splits)], output_split_sizes=out_splits, input_split_sizes=in_splits,
+                           group=group)
+    return out
+
+
+def exchange_records(records: torch.Tensor, counts: Sequence[int], record_bytes: int, group=None
+                     ) -> Tuple[torch.Tensor, int]:
+    """Exchange of packed partial records: returns (received records, number received)."""
+    recv_counts = exchange_counts(counts, records.device, group)
+    out = exchange_buffer(records, counts, recv_counts, record_bytes, group)
+    return out, sum(recv_counts)
+
+
+class DistributedGroupBy:
+    """``GroupBy`` over row-sharded inputs: every rank passes its own rows; every rank receives the
+    finished groups it owns."""
+
+    def __init__(self, keys, null_handling=0, *, strategy: str = "partials", group=None, **options):
+        from .groupby import GroupBy
+        if strategy not in ("partials", "rows"):
+            raise ValueError("strategy must be 'partials' or 'rows'")
+        self._keys = keys
+        self._null_handling = null_handling
+        self._options = options
+        self._strategy = strategy
+        self._group = group
+        self._gb = GroupBy(keys, null_handling, **options)
+
+    def aggregate(self, requests):
+        world = dist.get_world_size(self._group) if dist.is_initialized() else 1
+        if world == 1:
+            return self._gb.aggregate(requests)
+        if self._strategy == "partials":
+            return self._aggregate_partials(requests, world)
+        return self._aggregate_rows(requests, world)
+
+    def _aggregate_partials(self, requests, world):
+        from .groupby import GroupByState
+        st = GroupByState(self._gb, requests)
+        st.update()
+        records, counts = st.pack(world)
+        recv, nrecv = exchange_records(records, counts, st.record_bytes, self._group)
+        st.reset(expected_groups=max(nrecv, 1))
+        st.merge(recv, nrecv)
+        return st.finalize()
+
+    def _aggregate_rows(self, requests, world):
+        from .column import Column, Table
+        from .groupby import GroupBy, GroupByRequest
+        from .partition import hash_partition
+        nkeys = self._keys.num_columns()
+        vals, seen = [], {}
+        for r in requests:
+            if id(r._values) not in seen:
+                seen[id(r._values)] = len(vals)
+                vals.append(r._values)
+        cols = self._keys.columns() + vals
+        if any(c.mask is not None for c in cols):
+            raise NotImplementedError("rows strategy: nullable columns are exchanged by the partials strategy")
+        parts, offsets = hash_partition(Table(cols), nkeys, world)
+        send_counts = [offsets[p + 1] - offsets[p] for p in range(world)]
+        recv_counts = exchange_counts(send_counts, cols[0].data.device, self._group)
+        nrecv = sum(recv_counts)
+        new_cols = []
+        for c in parts.columns():
+            w = c.data.numel() // max(c.size, 1) if c.size else 1
+            from .types import type_width
+            w = type_width(c.type_id)
+            buf = exchange_buffer(c.data, send_counts, recv_counts, w, self._group)
+            new_cols.append(Column(c.type_id, nrecv, buf, None, 0, 0))
+        gb = GroupBy(Table(new_cols[:nkeys]), self._null_handling, **self._options)
+        new_reqs = [GroupByRequest(new_cols[nkeys + seen[id(r._values)]], r._aggregations) for r in requests]
+        return gb.aggregate(new_reqs)

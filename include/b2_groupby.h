@@ -202,10 +202,12 @@ int32_t b2_state_record_bytes(const b2_groupby_state* st);
 
 /* Hash-partitions the state's groups by owner = hash(key) % num_parts (the role of
  * cudf::hash_partition on the partial table, cpp/src/partitioning/partitioning.cu:569-750):
- * writes the records destination-major into a device buffer owned by the state and the
- * per-destination record counts into `counts` (host array, num_parts).  Synchronises `stream`. */
+ * writes the records destination-major into ONE device buffer obtained from `allocator` (owned by
+ * the caller: *records_out, *records_bytes) and the per-destination record counts into `counts`
+ * (host array, num_parts).  Synchronises `stream`. */
 b2_status b2_state_pack(b2_groupby_state* st, int32_t num_parts, void* stream,
-                        const void** records_out, int64_t* counts);
+                        const b2_allocator* allocator, void** records_out, size_t* records_bytes,
+                        int64_t* counts);
 
 /* Merges `num_records` packed records (device memory, any origin with the same schema) into
  * the state: streaming_groupby::merge (groupby.hpp:548-556). */
@@ -253,7 +255,8 @@ typedef struct b2_call_stats {
   int64_t table_capacity;
   int64_t scratch_bytes;
   int32_t used_shared_table;
-  int32_t reserved;
+  float aggregate_kernel_ms; /* device time of the fused aggregate kernel(s), CUDA events on the
+                                call's stream, read after the call's own synchronisation */
 } b2_call_stats;
 void b2_get_last_stats(b2_call_stats* out);
 

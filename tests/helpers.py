@@ -74,31 +74,51 @@ def assert_column_equal(got: HostColumn, exp: HostColumn, order_got, order_exp, 
     assert got.size == exp.size, f"{what}: size {got.size} != {exp.size}"
     if check_nullable:
         assert (got.mask is None) == (exp.mask is None), f"{what}: nullability differs"
-    g, e = take(got, order_got), take(exp, order_exp)
+    if got.size == 0:
+        return
+    vg, ve = got.valid()[order_got], exp.valid()[order_exp]
+    assert np.array_equal(vg, ve), f"{what}: validity differs at {np.flatnonzero(vg != ve)[:8]}"
+    assert got.null_count == exp.null_count, f"{what}: null_count {got.null_count} != {exp.null_count}"
+    a, b = got.values()[order_got][vg], exp.values()[order_exp][ve]
     if is_floating(got.type_id):
-        for i, (a, b) in enumerate(zip(g, e)):
-            if a is None or b is None:
-                assert a is None and b is None, f"{what}[{i}]: {a} vs {b}"
-            elif math.isnan(b) or math.isnan(a):
-                assert math.isnan(a) and math.isnan(b), f"{what}[{i}]: {a} vs {b}"
-            elif math.isinf(b) or math.isinf(a):
-                assert a == b, f"{what}[{i}]: {a} vs {b}"
-            else:
-                assert abs(a - b) <= rtol * max(abs(b), abs(a)) + 1e-300, f"{what}[{i}]: {a} vs {b} (rtol {rtol})"
+        a, b = a.astype(np.float64), b.astype(np.float64)
+        nan_a, nan_b = np.isnan(a), np.isnan(b)
+        assert np.array_equal(nan_a, nan_b), f"{what}: NaN positions differ"
+        inf = np.isinf(a) | np.isinf(b)
+        assert np.array_equal(a[inf], b[inf]), f"{what}: infinities differ"
+        fin = ~(nan_a | inf)
+        err = np.abs(a[fin] - b[fin])
+        tol = rtol * np.maximum(np.abs(a[fin]), np.abs(b[fin])) + 1e-300
+        bad = np.flatnonzero(err > tol)
+        assert bad.size == 0, (f"{what}: {bad.size} values beyond rtol {rtol}; first {a[fin][bad[:4]]} vs "
+                               f"{b[fin][bad[:4]]}")
     else:
-        assert g == e, f"{what}: {g[:16]} vs {e[:16]}"
+        bad = np.flatnonzero(a != b)
+        assert bad.size == 0, f"{what}: {bad.size} values differ; first {a[bad[:8]]} vs {b[bad[:8]]}"
 
 
 def assert_keys_equal(got: List[HostColumn], exp: List[HostColumn], order_got, order_exp):
     assert len(got) == len(exp)
     for i, (a, b) in enumerate(zip(got, exp)):
-        assert TypeId(a.type_id) == TypeId(b.type_id)
-        ga, gb = take(a, order_got), take(b, order_exp)
+        assert TypeId(a.type_id) == TypeId(b.type_id), f"key column {i}: type differs"
+        assert a.size == b.size, f"key column {i}: {a.size} vs {b.size} groups"
+        if a.size == 0:
+            continue
+        if a.type_id == TypeId.STRING:
+            ga, gb = take(a, order_got), take(b, order_exp)
+            assert ga == gb, f"key column {i}: {ga[:8]} vs {gb[:8]}"
+            continue
+        va, vb = a.valid()[order_got], b.valid()[order_exp]
+        assert np.array_equal(va, vb), f"key column {i}: validity differs"
+        xa, xb = a.values()[order_got][va], b.values()[order_exp][vb]
         if is_floating(a.type_id):
             # +0 == -0 and NaN == NaN as keys
-            norm = lambda x: None if x is None else ("nan" if math.isnan(x) else x + 0.0)
-            ga, gb = [norm(x) for x in ga], [norm(x) for x in gb]
-        assert ga == gb, f"key column {i}: {ga[:16]} vs {gb[:16]}"
+            assert np.array_equal(np.isnan(xa), np.isnan(xb)), f"key column {i}: NaN keys differ"
+            ok = ~np.isnan(xa)
+            assert np.array_equal(xa[ok] + 0.0, xb[ok] + 0.0), f"key column {i}: values differ"
+        else:
+            bad = np.flatnonzero(xa != xb)
+            assert bad.size == 0, f"key column {i}: {bad.size} keys differ; first {xa[bad[:8]]} vs {xb[bad[:8]]}"
 
 
 def rtol_for(source_type: int) -> float:
@@ -120,3 +140,38 @@ def golden_instances(case: dict):
         ekeys = make_column(case["expect_keys"], case["key_type"])
         evals = make_column(case["expect_vals"], rt.name)
         yield f'{case["name"]}[{vt}]', keys, vals, kind, case["ddof"], policy, ekeys, evals
+
+
+# ------------------------------------------------------------------------------------ GPU side
+def gpu_groupby(keys: Sequence[HostColumn], requests, null_policy=NullPolicy.EXCLUDE, row_filters=(), **opts):
+    """Runs the CUDA engine through its public host API (which calls the C ABI) on host columns.
+    ``requests`` is a list of (values HostColumn, [kind | (kind, ddof), ...])."""
+    import cudf_b200 as cb
+    from cudf_b200.aggregation import Aggregation
+
+    dkeys = cb.Table([cb.Column.from_host(k) for k in keys])
+    dreqs = []
+    cache = {}
+    for vals, aggs in requests:
+        if id(vals) not in cache:
+            cache[id(vals)] = cb.Column.from_host(vals)
+        al = [Aggregation(Kind(a[0]), a[1]) if isinstance(a, tuple) else Aggregation(Kind(a)) for a in aggs]
+        dreqs.append(cb.GroupByRequest(cache[id(vals)], al))
+    filt = [cb.Column.from_host(f) for f in row_filters]
+    gb = cb.GroupBy(dkeys, null_policy, row_filters=filt, **opts)
+    okeys, ores = gb.aggregate(dreqs)
+    return [c.to_host() for c in okeys.columns()], [[c.to_host() for c in t.columns()] for t in ores]
+
+
+def assert_same_result(got, exp, requests, check_nullable=True):
+    """Compares two (keys, results) pairs after sorting both by key: keys, counts, integer results
+    bit-exact; float results within the north-star tolerance of their SOURCE type."""
+    gk, gr = got
+    ek, er = exp
+    og, oe = sort_order(gk), sort_order(ek)
+    assert gk[0].size == ek[0].size, f"group count {gk[0].size} != {ek[0].size}"
+    assert_keys_equal(gk, ek, og, oe)
+    for q, (vals, aggs) in enumerate(requests):
+        for a in range(len(aggs)):
+            assert_column_equal(gr[q][a], er[q][a], og, oe, rtol_for(vals.type_id), f"request {q} agg {aggs[a]}",
+                                check_nullable=check_nullable)

@@ -1,0 +1,257 @@
+"""Parity of the CUDA engine (through its host API and C ABI) with the CPU oracle on seeded inputs:
+the five benchmark configurations at oracle-sized row counts, every table path, and the edge
+cases the reference's tests pin (empty / ragged sizes, nulls, slices, collisions, NaN)."""
+import numpy as np
+import pytest
+
+import workloads
+from cudf_b200.types import HostColumn, Kind, NullPolicy, TypeId
+from oracle import oracle
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+ALL_AGGS = [Kind.SUM, Kind.COUNT_VALID, Kind.COUNT_ALL, Kind.MEAN, Kind.MIN, Kind.MAX, Kind.SUM_OF_SQUARES,
+            Kind.M2, Kind.VARIANCE, (Kind.STD, 2)]
+
+
+def check(keys, requests, policy=NullPolicy.EXCLUDE, row_filters=(), **opts):
+    got = H.gpu_groupby(keys, requests, policy, row_filters=row_filters, **opts)
+    exp = oracle.groupby(keys, requests, policy, row_filters=[f.mask for f in row_filters if f.mask is not None],
+                         row_filter_offsets=[f.offset for f in row_filters if f.mask is not None])
+    H.assert_same_result(got, exp, requests)
+    return got
+
+
+@pytest.mark.parametrize("config,n", [(1, 400_000), (2, 600_000), (3, 300_000), (4, 500_000), (5, 120_000)])
+@pytest.mark.parametrize("variant", [0, 1])
+def test_benchmark_configs_match_oracle(config, n, variant):
+    w = workloads.make(config, n, scale_domain=(config in (3, 4)))
+    check(w.keys, w.requests, w.null_policy, w.row_filters, table_variant=variant)
+
+
+def test_config2_full_domain_uses_compact_shared_table():
+    import cudf_b200 as cb
+    w = workloads.make(2, 1_500_000)
+    got = check(w.keys, w.requests, w.null_policy, w.row_filters)
+    st = cb.last_call_stats()
+    assert st.used_shared_table and st.table_attempts == 1
+    assert got[0][0].size == 10_000
+
+
+@pytest.mark.parametrize("n", [0, 1, 2, 31, 32, 33, 127, 128, 129, 1023, 1024, 1025, 4095, 4096, 4097, 12289])
+def test_ragged_sizes(n):
+    rng = np.random.default_rng(n)
+    k = HostColumn.from_numpy(rng.integers(0, 7, n).astype(np.int32), valid=rng.random(n) > 0.1)
+    v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.2)
+    check([k], [(v, ALL_AGGS)])
+    check([k], [(v, ALL_AGGS)], NullPolicy.INCLUDE)
+
+
+@pytest.mark.parametrize("vt", ["INT8", "INT16", "INT32", "INT64", "UINT8", "UINT16", "UINT32", "UINT64",
+                                "FLOAT32", "FLOAT64", "BOOL8"])
+def test_value_types_all_aggregations(vt):
+    rng = np.random.default_rng(11)
+    n = 50_000
+    t = TypeId[vt]
+    if vt.startswith("FLOAT"):
+        vals = (rng.standard_normal(n) * 100).astype(np.float32 if vt == "FLOAT32" else np.float64)
+    elif vt == "BOOL8":
+        vals = rng.integers(0, 2, n).astype(np.uint8)
+    elif vt == "UINT64":
+        vals = rng.integers(0, 2**63, n).astype(np.uint64) * 2 + 1
+    else:
+        info = np.iinfo(getattr(np, vt.lower()))
+        vals = rng.integers(max(info.min, -10**9), min(info.max, 10**9), n).astype(getattr(np, vt.lower()))
+    k = HostColumn.from_numpy(rng.integers(-50, 50, n).astype(np.int16))
+    v = HostColumn.from_numpy(vals, valid=rng.random(n) > 0.3, type_id=t)
+    aggs = [a for a in ALL_AGGS]
+    check([k], [(v, aggs)])
+    v2 = HostColumn.from_numpy(vals, type_id=t)  # no nulls: results are not nullable
+    check([k], [(v2, aggs)])
+
+
+@pytest.mark.parametrize("kt", ["INT8", "INT16", "INT32", "INT64", "UINT8", "UINT32", "UINT64", "FLOAT32", "FLOAT64",
+                                "BOOL8", "TIMESTAMP_DAYS", "TIMESTAMP_NANOSECONDS", "DURATION_SECONDS"])
+@pytest.mark.parametrize("policy", [NullPolicy.EXCLUDE, NullPolicy.INCLUDE])
+def test_key_types(kt, policy):
+    rng = np.random.default_rng(3)
+    n = 20_000
+    raw = rng.integers(0, 2 if kt == "BOOL8" else 40, n)
+    k = HostColumn.from_numpy(raw, valid=rng.random(n) > 0.05, type_id=TypeId[kt])
+    v = HostColumn.from_numpy(rng.integers(-1000, 1000, n).astype(np.int32), valid=rng.random(n) > 0.1)
+    check([k], [(v, [Kind.SUM, Kind.MIN, Kind.MAX, Kind.COUNT_VALID, Kind.COUNT_ALL, Kind.MEAN])], policy)
+
+
+def test_float_keys_zero_nan_equivalence():
+    # +0 == -0 and NaN == NaN as keys (cpp/include/cudf/detail/row_operator/equality.cuh:59-89)
+    keys = np.array([0.0, -0.0, np.nan, np.nan, 1.5, -1.5, 1.5, np.inf, -np.inf, np.inf] * 50, dtype=np.float64)
+    vals = np.arange(keys.size, dtype=np.int64)
+    got = check([HostColumn.from_numpy(keys)], [(HostColumn.from_numpy(vals), [Kind.SUM, Kind.COUNT_VALID])])
+    assert got[0][0].size == 6
+    check([HostColumn.from_numpy(keys.astype(np.float32))], [(HostColumn.from_numpy(vals), [Kind.SUM])])
+
+
+def test_key_equal_to_empty_sentinel():
+    # an int64 key of -1 has the bit pattern the table uses for "empty slot"
+    rng = np.random.default_rng(9)
+    n = 100_000
+    k = rng.integers(-3, 3, n).astype(np.int64)
+    v = rng.integers(-100, 100, n).astype(np.int64)
+    for variant in (0, 1):
+        got = check([HostColumn.from_numpy(k)], [(HostColumn.from_numpy(v), [Kind.SUM, Kind.MIN, Kind.COUNT_VALID])],
+                    table_variant=variant)
+        assert got[0][0].size == 6
+    ku = np.where(rng.random(n) < 0.5, np.uint64(2**64 - 1), np.uint64(5)).astype(np.uint64)
+    check([HostColumn.from_numpy(ku)], [(HostColumn.from_numpy(v), [Kind.SUM])])
+
+
+def test_composite_keys_with_nulls_include_and_exclude():
+    rng = np.random.default_rng(21)
+    n = 80_000
+    a = HostColumn.from_numpy(rng.integers(0, 5, n).astype(np.int8), valid=rng.random(n) > 0.2)
+    b = HostColumn.from_numpy(rng.integers(0, 4, n).astype(np.int32), valid=rng.random(n) > 0.2)
+    c = HostColumn.from_numpy(rng.integers(0, 3, n).astype(np.int16))
+    v = HostColumn.from_numpy(rng.standard_normal(n).astype(np.float32), valid=rng.random(n) > 0.5)
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        check([a, b, c], [(v, [Kind.SUM, Kind.MEAN, Kind.COUNT_VALID, Kind.COUNT_ALL, Kind.MAX])], policy)
+
+
+def test_wide_composite_keys_use_row_comparison():
+    # 3 x int64 = 192 key bits: cannot be packed, rows are compared column by column
+    rng = np.random.default_rng(22)
+    n = 60_000
+    ks = [HostColumn.from_numpy(rng.integers(0, 6, n).astype(np.int64), valid=rng.random(n) > 0.1) for _ in range(3)]
+    v = HostColumn.from_numpy(rng.integers(0, 100, n).astype(np.int32))
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        check(ks, [(v, [Kind.SUM, Kind.COUNT_VALID])], policy)
+
+
+def test_string_keys_with_nulls_and_duplicates():
+    rng = np.random.default_rng(23)
+    words = ["", "a", "ab", "abc", "abd", "año", "₹1", "x" * 40, "x" * 41, "hello world", None]
+    n = 30_000
+    pick = rng.integers(0, len(words), n)
+    s = HostColumn.from_strings([words[i] for i in pick])
+    k2 = HostColumn.from_numpy(rng.integers(0, 3, n).astype(np.int32))
+    v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.1)
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        check([s, k2], [(v, [Kind.SUM, Kind.COUNT_VALID, Kind.MIN, Kind.MAX, Kind.MEAN])], policy)
+    s64 = HostColumn.from_strings([words[i] for i in pick], large_offsets=True)
+    check([s64], [(v, [Kind.SUM])])
+
+
+def test_sliced_inputs():
+    # views with a non-zero element offset (cudf::slice): data and validity bits both shift
+    rng = np.random.default_rng(24)
+    n = 10_000
+    kraw = rng.integers(0, 9, n).astype(np.int32)
+    vraw = rng.standard_normal(n)
+    kv, vv = rng.random(n) > 0.1, rng.random(n) > 0.1
+    for off in (1, 10, 32, 45):
+        k = HostColumn.from_numpy(kraw, valid=kv, offset=off)
+        v = HostColumn.from_numpy(vraw, valid=vv, offset=off + 3)
+        check([k], [(v, ALL_AGGS)])
+        check([k], [(v, ALL_AGGS)], NullPolicy.INCLUDE)
+
+
+def test_high_cardinality_grows_the_table():
+    import cudf_b200 as cb
+    rng = np.random.default_rng(25)
+    n = 1_400_000
+    k = HostColumn.from_numpy(rng.permutation(n).astype(np.int64) * 7919)  # all distinct
+    v = HostColumn.from_numpy(rng.integers(-5, 5, n).astype(np.int64))
+    got = check([k], [(v, [Kind.SUM, Kind.MIN, Kind.MAX, Kind.COUNT_VALID])])
+    assert got[0][0].size == n
+    assert cb.last_call_stats().table_attempts == 2  # the speculative table overflowed, the sized one fit
+    got = check([k], [(v, [Kind.SUM])], expected_groups=n)
+    assert cb.last_call_stats().table_attempts == 1
+
+
+def test_skewed_keys_hot_group():
+    w = workloads.make(4, 800_000, scale_domain=True)
+    check(w.keys, w.requests)
+    # one key holds 90 % of the rows
+    rng = np.random.default_rng(26)
+    n = 500_000
+    k = np.where(rng.random(n) < 0.9, 7, rng.integers(0, 100_000, n)).astype(np.int64)
+    v = HostColumn.from_numpy(rng.lognormal(0, 1, n), valid=rng.random(n) > 0.01)
+    check([HostColumn.from_numpy(k)], [(v, [Kind.SUM, Kind.MEAN, Kind.VARIANCE, Kind.MIN, Kind.MAX])])
+
+
+def test_float32_sum_spills_to_fp64():
+    # one group with far more than 1024 addends per CTA exercises the fp32 -> fp64 spill of the
+    # compact shared-memory layout; the mean must stay within the fp32 tolerance of the exact one
+    rng = np.random.default_rng(27)
+    n = 3_000_000
+    k = HostColumn.from_numpy(np.zeros(n, dtype=np.int32))
+    k2 = HostColumn.from_numpy((rng.random(n) < 0.001).astype(np.int32))
+    v = HostColumn.from_numpy((rng.random(n) * 1000).astype(np.float32), valid=rng.random(n) > 0.02)
+    check([k, k2], [(v, [Kind.MEAN])], row_filters=[v])
+    check([k, k2], [(v, [Kind.SUM, Kind.COUNT_VALID])])
+
+
+def test_min_max_with_nan_and_infinity_terminate():
+    # cpp/tests/groupby/min_tests.cpp:518-541, max_tests.cpp:526-549: all-NaN groups must not hang
+    keys = HostColumn.from_numpy(np.array([1, 1, 2, 2, 2], dtype=np.int32))
+    vals = HostColumn.from_numpy(np.array([np.nan, np.nan, 1.0, -np.inf, np.inf]))
+    gk, gr = H.gpu_groupby([keys], [(vals, [Kind.MIN, Kind.MAX])])
+    order = H.sort_order(gk)
+    assert gk[0].size == 2
+    assert H.take(gr[0][0], order)[1] == -np.inf and H.take(gr[0][1], order)[1] == np.inf
+
+
+def test_multiple_requests_and_duplicates():
+    # cpp/tests/groupby/keys_tests.cpp:355-409: repeated aggregations / repeated columns
+    rng = np.random.default_rng(28)
+    n = 40_000
+    k = HostColumn.from_numpy(rng.integers(0, 50, n).astype(np.int32))
+    v1 = HostColumn.from_numpy(rng.integers(0, 100, n).astype(np.int32))
+    v2 = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.2)
+    check([k], [(v1, [Kind.SUM, Kind.SUM]), (v1, [Kind.SUM, Kind.MAX]), (v2, [Kind.MEAN, Kind.STD]), (v2, [Kind.MIN])])
+
+
+def test_many_value_columns_generic_shared_layout():
+    rng = np.random.default_rng(29)
+    n = 200_000
+    k = HostColumn.from_numpy(rng.integers(0, 300, n).astype(np.int32))
+    reqs = []
+    for i in range(6):
+        v = HostColumn.from_numpy(rng.standard_normal(n) * (i + 1), valid=rng.random(n) > 0.1 * i if i else None)
+        reqs.append((v, [Kind.SUM, Kind.MIN, Kind.MAX, Kind.MEAN, Kind.VARIANCE]))
+    check([k], reqs)
+
+
+def test_row_filters_drop_rows():
+    rng = np.random.default_rng(30)
+    n = 100_000
+    k = HostColumn.from_numpy(rng.integers(0, 20, n).astype(np.int32))
+    v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.3)
+    w = HostColumn.from_numpy(rng.integers(0, 9, n).astype(np.int64), valid=rng.random(n) > 0.3)
+    check([k], [(v, [Kind.SUM, Kind.COUNT_ALL]), (w, [Kind.SUM, Kind.COUNT_VALID])], row_filters=[v, w])
+
+
+def test_error_statuses_mirror_the_reference():
+    import cudf_b200 as cb
+    from cudf_b200 import aggregation as agg
+    k = cb.Column.from_host(HostColumn.from_numpy(np.arange(4, dtype=np.int32)))
+    v5 = cb.Column.from_host(HostColumn.from_numpy(np.arange(5, dtype=np.int32)))
+    s = cb.Column.from_host(HostColumn.from_strings(["a", "b", "c", "d"]))
+    gb = cb.GroupBy(cb.Table([k]))
+    with pytest.raises(cb.LogicError, match="Size mismatch between request values and groupby keys."):
+        gb.aggregate([cb.GroupByRequest(v5, [agg.sum()])])
+    with pytest.raises(cb.DataTypeError, match="Invalid type/aggregation combination."):
+        gb.aggregate([cb.GroupByRequest(s, [agg.sum()])])
+    with pytest.raises(cb.UnsupportedError):
+        gb.aggregate([cb.GroupByRequest(k, [agg.median()])])
+    with pytest.raises(cb.UnsupportedError):
+        gb.aggregate([cb.GroupByRequest(s, [agg.min()])])
+
+
+def test_results_are_deterministic_for_integers():
+    w = workloads.make(3, 400_000, scale_domain=True)
+    a = H.gpu_groupby(w.keys, w.requests)
+    b = H.gpu_groupby(w.keys, w.requests)
+    oa, ob = H.sort_order(a[0]), H.sort_order(b[0])
+    for x, y in zip(a[1][0], b[1][0]):
+        assert H.take(x, oa) == H.take(y, ob)
