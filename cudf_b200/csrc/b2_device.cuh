@@ -57,7 +57,7 @@ struct DKeyCol {
   int shift;            // packed mode: bit position of the value
   int nullbit;          // packed mode + INCLUDE + nullable: bit position of the null flag, else -1
   int offs64;           // strings: 1 = INT64 offsets
-  int pad;
+  int is_signed;        // fixed width: values order as signed integers
 };
 
 struct DValCol {
@@ -79,12 +79,29 @@ struct DPlan {
   int include_nulls;  // null_policy::INCLUDE
   int nfilters;
   int stride;         // cells per slot = 1 + ncells
-  int pad;
+  int flags;          // PF_* below
   DKeyCol keys[MAX_KEYS];
   DValCol vals[MAX_VALS];
   DCell cells[MAX_CELLS];
   const u32* filters[MAX_FILTERS];
   i64 filter_offsets[MAX_FILTERS];
+};
+
+enum PlanFlags : int {
+  PF_VEC_KEYS = 1,  // every key column may be read 4 rows at a time with one 16-byte load
+  PF_VEC_VAL0 = 2   // value column 0 likewise (compact FLOAT32 layout)
+};
+
+// Dense key mapping of one aggregate pass, written on the device by k_sample_ranges: when the keys
+// seen in a sample span a small box [min_k, min_k + range_k) per key column, a key's shared-memory
+// slot is its position in that box — no probing and no key storage.  Keys outside the box (the
+// sample missed them) take the global-table path, so the result stays exact.
+struct DDense {
+  int enabled;
+  u32 total;               // slots = product of ranges
+  i64 min[MAX_KEYS];
+  u64 range[MAX_KEYS];     // includes one extra value for "null" on nullable INCLUDE columns
+  u32 mult[MAX_KEYS];
 };
 
 // control block shared by the kernels of one table
@@ -97,6 +114,7 @@ struct DCtrl {
   u64 stat_smem_rows;
   u64 stat_gmem_rows;
   u64 reserved;
+  DDense dense;
 };
 
 // ---------------------------------------------------------------------------------- hashing
@@ -121,6 +139,16 @@ __device__ __forceinline__ u64 reduce64(u64 h, u64 n) { return __umul64hi(h, n);
 __device__ __forceinline__ bool bit_valid(const u32* mask, i64 i)
 {
   return (__ldg(mask + (i >> 5)) >> (i & 31)) & 1u;
+}
+
+// validity bits of 4 consecutive elements starting at bit `pos` (`nvalid` of them exist)
+__device__ __forceinline__ u32 valid_nibble(const u32* mask, i64 pos, int nvalid)
+{
+  const u32 sh  = (u32)pos & 31u;
+  const u32* w  = mask + (pos >> 5);
+  u32 bits      = __ldg(w) >> sh;
+  if (sh + (u32)nvalid > 32u) bits |= __ldg(w + 1) << (32u - sh);
+  return bits & 0xFu;
 }
 
 // a row takes part unless a row filter (fused drop_nulls) or, under EXCLUDE, a null key says no

@@ -455,6 +455,8 @@ void fill_plan_schema(DPlan& P, const Schema& sc)
     P.keys[k].width = sc.key_width[k];
     P.keys[k].shift = sc.key_shift[k];
     P.keys[k].nullbit = sc.key_nullbit[k];
+    const int t = sc.key_types[k];
+    P.keys[k].is_signed = !(t == B2_UINT8 || t == B2_UINT16 || t == B2_UINT32 || t == B2_UINT64 || t == B2_BOOL8);
   }
   for (int s = 0; s < sc.nvals; ++s) P.vals[s].vclass = vclass_of(sc.val_types[s]);
   for (int c = 0; c < sc.ncells; ++c) P.cells[c] = sc.cells[c];
@@ -492,6 +494,18 @@ void bind_plan_inputs(DPlan& P, const Schema& sc, const b2_groupby& gb, const b2
     P.vals[s].mask = (v.null_mask && v.null_count != 0) ? v.null_mask : nullptr;
     P.vals[s].offset = v.offset;
   }
+  // 16-byte vector loads of 4 consecutive rows need aligned column starts
+  auto aligned = [](const void* base, int64_t offset, int width) {
+    const uintptr_t a = (uintptr_t)base + (uintptr_t)offset * (uintptr_t)width;
+    return a % (uintptr_t)std::min(16, 4 * width) == 0;
+  };
+  P.flags = 0;
+  if (sc.key_mode == KM_PACKED) {
+    bool ok = true;
+    for (int k = 0; k < sc.nkeys; ++k) ok = ok && aligned(P.keys[k].data, P.keys[k].offset, P.keys[k].width);
+    if (ok) P.flags |= PF_VEC_KEYS;
+  }
+  if (sc.f32mean && aligned(P.vals[sc.cells[0].col].data, P.vals[sc.cells[0].col].offset, 4)) P.flags |= PF_VEC_VAL0;
   P.nfilters = (int)gb.filters.size();
   for (int f = 0; f < P.nfilters; ++f) {
     P.filters[f] = gb.filters[(size_t)f];
@@ -582,21 +596,30 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
   int layout = SL_NONE;
   int S = 0, fill_limit = 0;
   size_t smem = 0;
+  u32 cap_dense = 0;
   if (gb.table_variant != 1) {
     const int budget = gb.shared_table_bytes > 0 ? std::min(gb.shared_table_bytes, device_info().smem_optin - 1024)
                                                  : device_info().smem_optin - 1024;
-    const int per_slot = sc.f32mean ? 16 : 8 * (1 + sc.ncells);
-    S = budget / per_slot - 1;
+    const int cell_bytes = sc.f32mean ? 8 : 8 * sc.ncells;  // accumulators of one slot
+    S = budget / (8 + cell_bytes) - 1;                      // hashed mode: key cell + accumulators
     if (S >= 256) {
       layout = sc.f32mean ? SL_F32MEAN : SL_GENERIC;
-      fill_limit = (int)(S * (sc.f32mean ? 0.80 : 0.75));
-      smem = (size_t)(S + 1) * per_slot;
+      fill_limit = (int)(S * 0.75);
+      smem = (size_t)budget;
+      // dense mode: accumulators + one occupancy bit per slot
+      if (sc.key_mode == KM_PACKED && gb.table_variant != 3)
+        cap_dense = (u32)(((int64_t)budget - 64) * 8 / ((int64_t)cell_bytes * 8 + 1));
     }
   }
   g_stats.used_shared_table = layout != SL_NONE;
   const DPlan& P = st.plan;
   EventPair& ev = kernel_events();
   cudaEventRecord(ev.a, stream);
+  if (cap_dense > 0 && P.nrows >= 4096) {
+    k_sample_ranges<<<1, 1024, 0, stream>>>(P, st.ctrl, cap_dense);
+    CUDA_TRY(cudaGetLastError());
+    g_stats.kernel_launches++;
+  }
   if (sc.key_mode == KM_PACKED) {
     if (layout == SL_F32MEAN) launch_aggregate<KM_PACKED, SL_F32MEAN>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream);
     else if (layout == SL_GENERIC) launch_aggregate<KM_PACKED, SL_GENERIC>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream);

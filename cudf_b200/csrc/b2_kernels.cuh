@@ -115,206 +115,407 @@ __device__ __forceinline__ int smem_find_insert(const DPlan& P, u64* skeys, int 
   return -1;
 }
 
+// ------------------------------------------------------------------------------ dense key box
+// ordered value of key column k inside a packed key
+__device__ __forceinline__ i64 key_field(const DKeyCol& c, u64 key)
+{
+  u64 v = key >> c.shift;
+  if (c.width < 8) {
+    const int sh = 64 - 8 * c.width;
+    v <<= sh;
+    v = c.is_signed ? (u64)((i64)v >> sh) : (v >> sh);
+  }
+  return (i64)v;
+}
+
+// slot of a packed key inside the sampled box, -1 when the key lies outside it
+__device__ __forceinline__ int dense_index(const DPlan& P, const DDense& D, u64 key)
+{
+  u32 idx = 0;
+  for (int k = 0; k < P.nkeys; ++k) {
+    const DKeyCol& c = P.keys[k];
+    u64 f;
+    if (c.nullbit >= 0 && ((key >> c.nullbit) & 1ull)) {
+      f = D.range[k] - 1;
+    } else {
+      f = (u64)(key_field(c, key) - D.min[k]);
+      if (f >= D.range[k] - (c.nullbit >= 0 ? 1ull : 0ull)) return -1;
+    }
+    idx += (u32)f * D.mult[k];
+  }
+  return (int)idx;
+}
+
+// inverse of dense_index
+__device__ __forceinline__ u64 dense_key(const DPlan& P, const DDense& D, u32 idx)
+{
+  u64 key = 0;
+  for (int k = 0; k < P.nkeys; ++k) {
+    const DKeyCol& c = P.keys[k];
+    const u64 f = (u64)(idx / D.mult[k]) % D.range[k];
+    if (c.nullbit >= 0 && f == D.range[k] - 1) {
+      key |= 1ull << c.nullbit;
+    } else {
+      const u64 v = (u64)((i64)f + D.min[k]);
+      key |= (c.width == 8 ? v : (v & ((1ull << (8 * c.width)) - 1ull))) << c.shift;
+    }
+  }
+  return key;
+}
+
+// One CTA looks at up to 16K evenly spaced rows and writes the dense box into ctrl->dense (or
+// disables it when the box would not fit `cap_slots` shared-memory slots).  No host round trip:
+// the fused kernel reads the decision from device memory.
+__global__ void __launch_bounds__(1024) k_sample_ranges(const __grid_constant__ DPlan P, DCtrl* ctrl, u32 cap_slots)
+{
+  __shared__ i64 s_min[MAX_KEYS], s_max[MAX_KEYS];
+  if (threadIdx.x < MAX_KEYS) { s_min[threadIdx.x] = 0x7FFFFFFFFFFFFFFFll; s_max[threadIdx.x] = (i64)0x8000000000000000ull; }
+  __syncthreads();
+  const i64 nsamp  = P.nrows < 16384 ? P.nrows : 16384;
+  const i64 stride = P.nrows / (nsamp > 0 ? nsamp : 1);
+  if (P.key_mode == KM_PACKED) {
+    for (i64 i = threadIdx.x; i < nsamp; i += blockDim.x) {
+      const i64 row = i * stride + (stride > 1 ? (i * 7919) % stride : 0);
+      if (!row_active(P, row)) continue;
+      const u64 key = pack_key(P, row);
+      for (int k = 0; k < P.nkeys; ++k) {
+        const DKeyCol& c = P.keys[k];
+        if (c.nullbit >= 0 && ((key >> c.nullbit) & 1ull)) continue;
+        const i64 v = key_field(c, key);
+        if (v < s_min[k]) atomicMin(&s_min[k], v);
+        if (v > s_max[k]) atomicMax(&s_max[k], v);
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    DDense D;
+    D.enabled = 0;
+    D.total   = 0;
+    bool ok   = P.key_mode == KM_PACKED && nsamp >= 1024 && cap_slots > 0;
+    for (int pass = 0; pass < 2 && ok && !D.enabled; ++pass) {  // pass 0: padded box, pass 1: tight box
+      u64 total = 1;
+      bool fits = true;
+      for (int k = 0; k < P.nkeys && fits; ++k) {
+        i64 lo = s_min[k], hi = s_max[k];
+        if (lo > hi) { lo = 0; hi = 0; }
+        const u64 span = (u64)(hi - lo);
+        if (span >= (u64)cap_slots) { fits = false; break; }
+        u64 pad = pass == 0 ? (span / 8 + 1 < 32 ? span / 8 + 1 : 32) : 0;
+        if (lo < (i64)0x8000000000000000ull + (i64)pad || hi > 0x7FFFFFFFFFFFFFFFll - (i64)pad) pad = 0;
+        D.min[k]   = lo - (i64)pad;
+        D.range[k] = span + 1 + 2 * pad + (P.keys[k].nullbit >= 0 ? 1 : 0);
+        D.mult[k]  = (u32)total;
+        total *= D.range[k];
+        if (total > (u64)cap_slots) fits = false;
+      }
+      if (fits) { D.enabled = 1; D.total = (u32)total; }
+    }
+    ctrl->dense = D;
+  }
+}
+
 // ------------------------------------------------------------------------------ fused aggregate
-// One pass over the input.  Each CTA owns a shared-memory table (cache) of S slots; a row whose key
-// is cached is folded into shared memory, every other row goes to the global table.  The cache
-// fills first-come until `fill_limit`; a CTA whose cache stops paying off (mostly misses) turns it
-// off.  At the end each CTA merges its cache into the global table.
+// ONE pass over keys + values + bitmasks.  Each thread takes 4 consecutive rows per tile (16-byte
+// vector loads when the columns allow, validity read as 4-bit nibbles of the mask words).  Each CTA
+// owns a shared-memory table in front of the global table:
+//   dense mode  : slot = position of the key in the sampled key box (k_sample_ranges), accumulators
+//                 only, no probing;
+//   hashed mode : open addressing with linear probing on the 64-bit key cell, first come first
+//                 cached until `fill_limit`; a CTA whose cache stops paying off turns it off.
+// Rows whose key is not in shared memory go to the global table with global atomics.  At the end
+// every CTA merges its table into the global one.  There is no barrier inside the row loop.
 template <int KM, int LAYOUT>
 __global__ void __launch_bounds__(AGG_BLOCK, 1)
-k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* ctrl, int S, int fill_limit)
+k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* ctrl, int S_hash, int fill_limit)
 {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int s_fill, s_new, s_cache_on, s_abort, s_hit, s_miss;
+  __shared__ DDense s_dense;
 
-  u64* skeys  = (u64*)smem_raw;            // [S+1]
-  u64* scells = skeys + (S + 1);           // SL_GENERIC: [ncells][S+1]; SL_F32MEAN: [S+1] packed {f32,u32}
   const int stride = P.stride;
   const int tid    = threadIdx.x;
+  if (LAYOUT != SL_NONE && KM == KM_PACKED) {
+    const int nw = (int)(sizeof(DDense) / 4);
+    for (int i = tid; i < nw; i += blockDim.x) ((u32*)&s_dense)[i] = ((const u32*)&ctrl->dense)[i];
+  }
+  if (tid == 0) { s_fill = 0; s_new = 0; s_cache_on = (LAYOUT != SL_NONE); s_abort = 0; s_hit = 0; s_miss = 0; }
+  __syncthreads();
+  const bool dense = (LAYOUT != SL_NONE) && KM == KM_PACKED && s_dense.enabled;
+  const int S      = dense ? (int)s_dense.total : S_hash;  // slots (hashed mode: + the special slot at S)
+  const int NS     = dense ? S : S + 1;                    // allocated slots per array
+
+  // shared-memory arrays
+  u64* skeys  = (u64*)smem_raw;                            // hashed mode only: [NS]
+  u64* scells = dense ? (u64*)smem_raw : skeys + NS;       // SL_GENERIC: [ncells][NS]
+  float* ssum = (float*)scells;                            // SL_F32MEAN: [NS] fp32 partial sums
+  u32* scnt   = (u32*)(ssum + NS);                         // SL_F32MEAN: [NS] counts
+  u32* socc   = (u32*)(scells + (size_t)(LAYOUT == SL_F32MEAN ? 1 : P.ncells) * NS);  // dense mode: occupancy bits
 
   if (LAYOUT != SL_NONE) {
-    for (int i = tid; i <= S; i += blockDim.x) skeys[i] = EMPTY;
+    if (!dense) for (int i = tid; i < NS; i += blockDim.x) skeys[i] = EMPTY;
     if (LAYOUT == SL_GENERIC) {
       for (int c = 0; c < P.ncells; ++c) {
         const u64 id = cell_identity(P.cells[c].op);
-        for (int i = tid; i <= S; i += blockDim.x) scells[(size_t)c * (S + 1) + i] = id;
+        for (int i = tid; i < NS; i += blockDim.x) scells[(size_t)c * NS + i] = id;
       }
     } else {
-      for (int i = tid; i <= S; i += blockDim.x) scells[i] = 0;
+      for (int i = tid; i < NS; i += blockDim.x) scells[i] = 0;  // {sum, count} arrays together
     }
+    if (dense) for (int i = tid; i < (NS + 31) / 32; i += blockDim.x) socc[i] = 0;
   }
-  if (tid == 0) { s_fill = 0; s_new = 0; s_cache_on = (LAYOUT != SL_NONE); s_abort = 0; s_hit = 0; s_miss = 0; }
   __syncthreads();
 
   const i64 tile_rows = (i64)blockDim.x * AGG_ROWS;
   const i64 ntiles    = (P.nrows + tile_rows - 1) / tile_rows;
+  u32 my_hit = 0, my_miss = 0, tot_hit = 0, tot_miss = 0;
 
   for (i64 tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-    const i64 base = tile * tile_rows;
-    const bool cache_on = (LAYOUT != SL_NONE) && s_cache_on;
+    if (*(volatile int*)&s_abort) break;
+    const i64 row0 = tile * tile_rows + (i64)tid * AGG_ROWS;
+    const int nv   = (int)max((i64)0, min((i64)AGG_ROWS, P.nrows - row0));
+    const bool cache_on = (LAYOUT != SL_NONE) && (dense || *(volatile int*)&s_cache_on);
 
-    // ---- phase A: key -> slot
+    // ---- loads first, all independent of each other, so that one DRAM round trip covers the tile
+    const bool full = nv == AGG_ROWS;
+    const bool vec  = KM == KM_PACKED && full && (P.flags & PF_VEC_KEYS);
+    u32 act = nv > 0 ? ((1u << nv) - 1u) : 0u;
     int sl[AGG_ROWS];
     u64 kk[AGG_ROWS];
-    bool act[AGG_ROWS];
+    u32 di[AGG_ROWS];   // dense mode: slot inside the key box
+    u32 dout = 0;       // dense mode: rows whose key lies outside the box
 #pragma unroll
-    for (int j = 0; j < AGG_ROWS; ++j) {
-      const i64 row = base + (i64)j * blockDim.x + tid;
-      act[j]        = row < P.nrows && row_active(P, row);
-      kk[j]         = 0;
-      if (act[j]) kk[j] = (KM == KM_PACKED) ? pack_key(P, row) : hash_row(P, row);
+    for (int j = 0; j < AGG_ROWS; ++j) { sl[j] = SLOT_NONE; kk[j] = 0; di[j] = 0; }
+    float fx[AGG_ROWS] = {0.f, 0.f, 0.f, 0.f};  // SL_F32MEAN: the values
+    u32 fvn = 0xFu;                              // SL_F32MEAN: their validity
+    if (LAYOUT == SL_F32MEAN && full && (P.flags & PF_VEC_VAL0)) {
+      const DValCol& vc = P.vals[P.cells[0].col];
+      const float4 q = __ldg((const float4*)((const float*)vc.data + vc.offset + row0));
+      fx[0] = q.x; fx[1] = q.y; fx[2] = q.z; fx[3] = q.w;
+      if (vc.mask) fvn = valid_nibble(vc.mask, vc.offset + row0, nv);
     }
-    int n_hit = 0, n_miss = 0;
+    if (vec) {
+      for (int k = 0; k < P.nkeys; ++k) {
+        const DKeyCol& c = P.keys[k];
+        const unsigned char* src = c.data + (c.offset + row0) * c.width;
+        u64 f[AGG_ROWS];
+        if (c.width == 4) {
+          const uint4 q = __ldg((const uint4*)src);
+          f[0] = q.x; f[1] = q.y; f[2] = q.z; f[3] = q.w;
+        } else if (c.width == 8) {
+          const ulonglong2 q0 = __ldg((const ulonglong2*)src), q1 = __ldg((const ulonglong2*)src + 1);
+          f[0] = q0.x; f[1] = q0.y; f[2] = q1.x; f[3] = q1.y;
+        } else if (c.width == 2) {
+          const uint2 q = __ldg((const uint2*)src);
+          f[0] = q.x & 0xFFFFu; f[1] = q.x >> 16; f[2] = q.y & 0xFFFFu; f[3] = q.y >> 16;
+        } else {
+          const u32 q = __ldg((const u32*)src);
+          f[0] = q & 0xFFu; f[1] = (q >> 8) & 0xFFu; f[2] = (q >> 16) & 0xFFu; f[3] = q >> 24;
+        }
+        u32 vn = 0xFu;
+        if (c.mask) {
+          vn = valid_nibble(c.mask, c.offset + row0, nv);
+          if (!P.include_nulls) act &= vn;  // EXCLUDE: a null key drops the row
+        }
+        const int sh = 64 - 8 * c.width;
 #pragma unroll
-    for (int j = 0; j < AGG_ROWS; ++j) {
-      sl[j] = SLOT_NONE;
-      if (!act[j]) continue;
-      const i64 row = base + (i64)j * blockDim.x + tid;
-      const u64 h   = (KM == KM_PACKED) ? mix64(kk[j]) : kk[j];
-      int s = -1;
-      if (cache_on) s = smem_find_insert<KM>(P, skeys, S, fill_limit, &s_fill, kk[j], h, row);
-      if (s >= 0) {
-        sl[j] = s;
-        ++n_hit;
-      } else {
-        const i64 g = (KM == KM_PACKED) ? gmem_find_insert_packed(tbl, cap, stride, kk[j], h, ctrl, &s_new)
-                                        : gmem_find_insert_rows(P, tbl, cap, stride, row, h, ctrl, &s_new);
-        if (g >= 0) sl[j] = -2 - (int)g;
-        ++n_miss;
+        for (int j = 0; j < AGG_ROWS; ++j) {
+          const bool isnull = c.nullbit >= 0 && !((vn >> j) & 1u);
+          kk[j] |= isnull ? (1ull << c.nullbit) : (f[j] << c.shift);
+          if (dense) {
+            const i64 ov = c.is_signed ? ((i64)(f[j] << sh) >> sh) : (i64)f[j];
+            u64 d = (u64)(ov - s_dense.min[k]);
+            const u64 lim = s_dense.range[k] - (c.nullbit >= 0 ? 1ull : 0ull);
+            if (isnull) d = lim;
+            else if (d >= lim) dout |= 1u << j;
+            di[j] += (u32)d * s_dense.mult[k];
+          }
+        }
+      }
+    } else if (act && !P.include_nulls) {
+      for (int k = 0; k < P.nkeys; ++k)
+        if (P.keys[k].mask) act &= valid_nibble(P.keys[k].mask, P.keys[k].offset + row0, nv);
+    }
+    if (act)
+      for (int f = 0; f < P.nfilters; ++f) act &= valid_nibble(P.filters[f], P.filter_offsets[f] + row0, nv);
+
+    // ---- phase A: keys -> slots
+    if (act) {
+      if (!vec) {
+#pragma unroll
+        for (int j = 0; j < AGG_ROWS; ++j)
+          if ((act >> j) & 1u) {
+            kk[j] = (KM == KM_PACKED) ? pack_key(P, row0 + j) : hash_row(P, row0 + j);
+            if (dense) {
+              const int s = dense_index(P, s_dense, kk[j]);
+              if (s < 0) dout |= 1u << j; else di[j] = (u32)s;
+            }
+          }
+      }
+#pragma unroll
+      for (int j = 0; j < AGG_ROWS; ++j) {
+        if (!((act >> j) & 1u)) continue;
+        int s = -1;
+        u64 h = 0;
+        if (dense) {
+          if (!((dout >> j) & 1u)) {
+            s = (int)di[j];
+            if (!((socc[s >> 5] >> (s & 31)) & 1u)) atomicOr(&socc[s >> 5], 1u << (s & 31));
+          }
+        } else {
+          h = (KM == KM_PACKED) ? mix64(kk[j]) : kk[j];
+          if (cache_on) s = smem_find_insert<KM>(P, skeys, S, fill_limit, &s_fill, kk[j], h, row0 + j);
+        }
+        if (s >= 0) {
+          sl[j] = s;
+          ++my_hit;
+        } else {
+          if (dense) h = mix64(kk[j]);
+          const i64 g = (KM == KM_PACKED) ? gmem_find_insert_packed(tbl, cap, stride, kk[j], h, ctrl, &s_new)
+                                          : gmem_find_insert_rows(P, tbl, cap, stride, row0 + j, h, ctrl, &s_new);
+          if (g >= 0) sl[j] = -2 - (int)g;
+          ++my_miss;
+        }
       }
     }
+    __syncwarp();  // reconverge after the divergent probe loops before the accumulate phase
 
     // ---- phase B: fold the values
     if (LAYOUT == SL_F32MEAN) {
       // cells: [0] = Σx of a FLOAT32 column, [1] = n of the same column
       const DValCol& vc = P.vals[P.cells[0].col];
+      if (act) {
+        u32 vn = act;
+        float x[AGG_ROWS];
+        if (full && (P.flags & PF_VEC_VAL0)) {
+          vn &= fvn;
 #pragma unroll
-      for (int j = 0; j < AGG_ROWS; ++j) {
-        if (sl[j] == SLOT_NONE) continue;
-        const i64 row = base + (i64)j * blockDim.x + tid;
-        if (!value_valid(vc, row)) continue;
-        const float x = __ldg((const float*)vc.data + vc.offset + row);
-        if (sl[j] >= 0) {
-          u64* cell = scells + sl[j];
-          u64 old = *(volatile u64*)cell, assumed, next;
-          float spill_sum = 0.f;
-          bool spill;
-          do {
-            assumed         = old;
-            const float s   = __uint_as_float((u32)assumed) + x;
-            const u32 n     = (u32)(assumed >> 32) + 1u;
-            spill           = n >= F32_SPILL_AT;
-            spill_sum       = s;
-            next            = spill ? 0ull : (((u64)n << 32) | (u64)__float_as_uint(s));
-            old             = atomicCAS(cell, assumed, next);
-          } while (old != assumed);
-          if (spill) {
-            // move the fp32 partial of this key to the fp64 global cells so that no fp32 sum
-            // ever holds more than F32_SPILL_AT addends
-            const u64 key = skeys[sl[j]];
-            const i64 g   = (sl[j] == S) ? cap
-                                         : gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
-            if (sl[j] == S && ctrl->special_used == 0) ctrl->special_used = 1;
-            if (g >= 0) {
-              atomicAdd((double*)(tbl + g * stride + 1), (double)spill_sum);
-              atomicAdd(tbl + g * stride + 2, (u64)F32_SPILL_AT);
-            }
-          }
+          for (int j = 0; j < AGG_ROWS; ++j) x[j] = fx[j];
         } else {
-          u64* slot = tbl + (i64)(-2 - sl[j]) * stride;
-          atomicAdd((double*)(slot + 1), (double)x);
-          atomicAdd(slot + 2, 1ull);
+          if (vc.mask) vn &= valid_nibble(vc.mask, vc.offset + row0, nv);
+#pragma unroll
+          for (int j = 0; j < AGG_ROWS; ++j) x[j] = ((vn >> j) & 1u) ? __ldg((const float*)vc.data + vc.offset + row0 + j) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < AGG_ROWS; ++j) {
+          if (sl[j] == SLOT_NONE || !((vn >> j) & 1u)) continue;
+          if (sl[j] >= 0) {
+            atomicAdd(ssum + sl[j], x[j]);
+            const u32 old = atomicAdd(scnt + sl[j], 1u);
+            if (((old + 1u) & (F32_SPILL_AT - 1u)) == 0u) {
+              // every F32_SPILL_AT-th addend moves the fp32 partial of this key to the fp64 global
+              // cell, so that no fp32 sum ever holds many more addends than that
+              const float part = atomicExch(ssum + sl[j], 0.f);
+              const u64 key = dense ? dense_key(P, s_dense, (u32)sl[j]) : (sl[j] == S ? EMPTY : skeys[sl[j]]);
+              const i64 g   = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
+              if (g >= 0) atomicAdd((double*)(tbl + g * stride + 1), (double)part);
+            }
+          } else {
+            u64* slot = tbl + (i64)(-2 - sl[j]) * stride;
+            atomicAdd((double*)(slot + 1), (double)x[j]);
+            atomicAdd(slot + 2, 1ull);
+          }
         }
       }
     } else {
       int cur_col = -1;
       u64 v[AGG_ROWS];
-      bool ok[AGG_ROWS];
+      u32 vn = 0;
       for (int c = 0; c < P.ncells; ++c) {
         const int op  = P.cells[c].op;
         const int col = P.cells[c].col;
         if (op != OP_CNT_A && col != cur_col) {
           cur_col = col;
           const DValCol& vc = P.vals[col];
+          vn = act;
+          if (vn && vc.mask) vn &= valid_nibble(vc.mask, vc.offset + row0, nv);
 #pragma unroll
-          for (int j = 0; j < AGG_ROWS; ++j) {
-            const i64 row = base + (i64)j * blockDim.x + tid;
-            ok[j]         = sl[j] != SLOT_NONE && value_valid(vc, row);
-            v[j]          = ok[j] ? load_value(vc, row) : 0;
-          }
+          for (int j = 0; j < AGG_ROWS; ++j) v[j] = ((vn >> j) & 1u) && sl[j] != SLOT_NONE ? load_value(vc, row0 + j) : 0;
         }
+        const u32 use = (op == OP_CNT_A) ? act : vn;
 #pragma unroll
         for (int j = 0; j < AGG_ROWS; ++j) {
-          if (sl[j] == SLOT_NONE) continue;
-          if (op != OP_CNT_A && !ok[j]) continue;
-          u64* cell = (LAYOUT == SL_GENERIC && sl[j] >= 0) ? scells + (size_t)c * (S + 1) + sl[j]
+          if (sl[j] == SLOT_NONE || !((use >> j) & 1u)) continue;
+          u64* cell = (LAYOUT == SL_GENERIC && sl[j] >= 0) ? scells + (size_t)c * NS + sl[j]
                                                           : tbl + (i64)(-2 - sl[j]) * stride + 1 + c;
           cell_update(cell, op, v[j]);
         }
       }
     }
 
-    // ---- per-tile bookkeeping: claims, overflow, cache pay-off
-    n_hit  = __reduce_add_sync(0xFFFFFFFFu, n_hit);
-    n_miss = __reduce_add_sync(0xFFFFFFFFu, n_miss);
-    if ((tid & 31) == 0) { if (n_hit) atomicAdd(&s_hit, n_hit); if (n_miss) atomicAdd(&s_miss, n_miss); }
-    __syncthreads();
-    if (tid == 0) {
-      if (s_new) {
-        const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)s_new) + (u64)s_new;
+    // ---- bookkeeping by one lane per CTA, no barrier: claims, overflow, cache pay-off
+    if (LAYOUT != SL_NONE && !dense) {
+      const u32 wh = __reduce_add_sync(0xFFFFFFFFu, my_hit), wm = __reduce_add_sync(0xFFFFFFFFu, my_miss);
+      if ((tid & 31) == 0) { if (wh) atomicAdd(&s_hit, (int)wh); if (wm) atomicAdd(&s_miss, (int)wm); }
+      tot_hit += my_hit; tot_miss += my_miss;
+      my_hit = 0; my_miss = 0;
+    }
+    if (tid == 0 && (*(volatile int*)&s_new != 0 || ((tile / gridDim.x) & 7) == 7)) {
+      const int c = atomicExch(&s_new, 0);
+      if (c) {
+        const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)c) + (u64)c;
         if (tot > ctrl->claim_limit) ctrl->overflow = 1;
-        s_new = 0;
       }
       if (*(volatile u32*)&ctrl->overflow) s_abort = 1;
-      if (LAYOUT != SL_NONE && s_cache_on && s_fill >= fill_limit && s_miss > 3 * s_hit) s_cache_on = 0;
-      atomicAdd(&ctrl->stat_smem_rows, (u64)s_hit);
-      atomicAdd(&ctrl->stat_gmem_rows, (u64)s_miss);
-      s_hit = 0; s_miss = 0;
+      if (LAYOUT != SL_NONE && !dense && s_cache_on && s_fill >= fill_limit) {
+        const int h = atomicExch(&s_hit, 0), m = atomicExch(&s_miss, 0);
+        if (m > 3 * h && m > 1024) s_cache_on = 0;
+      }
     }
-    __syncthreads();
-    if (s_abort) break;
   }
 
-  // ---- merge this CTA's cache into the global table
-  if (LAYOUT != SL_NONE) {
-    __syncthreads();
-    if (!s_abort) {
-      for (int i = tid; i <= S; i += blockDim.x) {
-        const u64 k = skeys[i];
-        if (k == EMPTY) continue;
-        i64 g;
-        if (i == S) {
-          g = cap;
-          if (ctrl->special_used == 0) ctrl->special_used = 1;
-        } else if (KM == KM_PACKED) {
-          g = gmem_find_insert_packed(tbl, cap, stride, k, mix64(k), ctrl, &s_new);
-        } else {
-          const i64 row = (i64)(u32)k;
-          g = gmem_find_insert_rows(P, tbl, cap, stride, row, hash_row(P, row), ctrl, &s_new);
+  // ---- statistics: rows folded in shared memory / sent to the global table
+  tot_hit  = __reduce_add_sync(0xFFFFFFFFu, tot_hit + my_hit);
+  tot_miss = __reduce_add_sync(0xFFFFFFFFu, tot_miss + my_miss);
+  if ((tid & 31) == 0) {
+    if (tot_hit) atomicAdd(&ctrl->stat_smem_rows, (u64)tot_hit);
+    if (tot_miss) atomicAdd(&ctrl->stat_gmem_rows, (u64)tot_miss);
+  }
+
+  // ---- merge this CTA's table into the global table
+  __syncthreads();
+  if (LAYOUT != SL_NONE && !s_abort) {
+    for (int i = tid; i < NS; i += blockDim.x) {
+      u64 key;
+      if (dense) {
+        if (!((socc[i >> 5] >> (i & 31)) & 1u)) continue;
+        key = dense_key(P, s_dense, (u32)i);
+      } else {
+        key = skeys[i];
+        if (key == EMPTY) continue;
+        if (i == S) key = EMPTY;  // the special slot holds the key whose bits equal EMPTY
+      }
+      i64 g;
+      if (KM == KM_PACKED) {
+        g = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
+      } else {
+        const i64 row = (i64)(u32)key;
+        g = gmem_find_insert_rows(P, tbl, cap, stride, row, hash_row(P, row), ctrl, &s_new);
+      }
+      if (g < 0) continue;
+      u64* slot = tbl + g * stride;
+      if (LAYOUT == SL_F32MEAN) {
+        const u32 n = scnt[i];
+        if (n) {
+          atomicAdd((double*)(slot + 1), (double)ssum[i]);
+          atomicAdd(slot + 2, (u64)n);
         }
-        if (g < 0) continue;
-        u64* slot = tbl + g * stride;
-        if (LAYOUT == SL_F32MEAN) {
-          const u64 a = scells[i];
-          const u32 n = (u32)(a >> 32);
-          if (n) {
-            atomicAdd((double*)(slot + 1), (double)__uint_as_float((u32)a));
-            atomicAdd(slot + 2, (u64)n);
-          }
-        } else {
-          for (int c = 0; c < P.ncells; ++c) {
-            const int op = P.cells[c].op;
-            const u64 a  = scells[(size_t)c * (S + 1) + i];
-            if (a != cell_identity(op)) cell_merge(slot + 1 + c, op, a);
-          }
+      } else {
+        for (int c = 0; c < P.ncells; ++c) {
+          const int op = P.cells[c].op;
+          const u64 a  = scells[(size_t)c * NS + i];
+          if (a != cell_identity(op)) cell_merge(slot + 1 + c, op, a);
         }
       }
     }
-    __syncthreads();
-    if (tid == 0 && s_new) {
+  }
+  __syncthreads();
+  if (tid == 0) {
+    if (s_new) {
       const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)s_new) + (u64)s_new;
       if (tot > ctrl->claim_limit) ctrl->overflow = 1;
     }
+    if (dense) atomicAdd(&ctrl->reserved, 1ull);  // CTAs that ran with the dense key box
   }
 }
 

@@ -143,7 +143,8 @@ typedef struct b2_groupby_result {
  *      cpp/src/groupby/hash/helpers.cuh:19-40, cpp/include/cudf/detail/cuco_helpers.hpp:16) */
 typedef struct b2_groupby_options {
   int64_t expected_groups;  /* hint; <= 0 = unknown (engine speculates, then estimates)        */
-  int32_t table_variant;    /* 0 auto, 1 force global-memory table only, 2 shared-memory cache */
+  int32_t table_variant;    /* 0 auto; 1 global-memory table only; 3 shared-memory table with
+                               hashing only (no dense key box)                               */
   int32_t shared_table_bytes; /* <= 0 = auto                                                   */
   /* Fused drop_nulls pre-filter (cpp/src/stream_compaction/drop_nulls.cu:56-96): a row takes
    * part only if it is valid in every one of these masks (bit i = row i, same bit layout and

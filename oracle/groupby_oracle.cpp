@@ -411,7 +411,11 @@ Result* run(const Col* keys, int nkeys, int null_policy, const Req* reqs, int nr
   res->results.resize((size_t)nreqs);
   for (int q = 0; q < nreqs; ++q) {
     const int32_t st = reqs[q].values.type_id;
-    const bool src_has_nulls = reqs[q].values.mask != nullptr;
+    // has_nulls() in the reference means null_count > 0, not "a mask is allocated"
+    bool src_has_nulls = false;
+    if (reqs[q].values.mask != nullptr)
+      for (int64_t r = 0; r < n && !src_has_nulls; ++r)
+        src_has_nulls = !bit(reqs[q].values.mask, (int64_t)reqs[q].values.offset + r);
     const bool flt = is_float(st);
     res->results[(size_t)q].resize((size_t)reqs[q].naggs);
     for (int a = 0; a < reqs[q].naggs; ++a) {

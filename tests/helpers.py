@@ -56,7 +56,12 @@ def sort_order(keys: List[HostColumn]) -> np.ndarray:
         else:
             vals = k.values().copy()
             if is_floating(k.type_id):
-                vals = np.where(np.isnan(vals), np.inf, vals) + 0.0  # -0 -> +0, NaN last
+                nan = np.isnan(vals)
+                vals = np.where(nan, 0.0, vals) + 0.0  # -0 -> +0; NaN keys sort after all numbers
+                cols.append(np.where(v, vals, 0.0))
+                cols.append((nan & v).astype(np.int8))
+                cols.append(v.astype(np.int8))
+                continue
         vals = np.where(v, vals, vals.dtype.type(0))
         cols.append(vals)
         cols.append(v.astype(np.int8))
@@ -69,13 +74,13 @@ def take(col: HostColumn, order: np.ndarray) -> list:
 
 
 def assert_column_equal(got: HostColumn, exp: HostColumn, order_got, order_exp, rtol: float, what: str,
-                        check_nullable: bool = False):
+                        check_nullable: bool = False, scale=None):
     assert TypeId(got.type_id) == TypeId(exp.type_id), f"{what}: type {got.type_id!r} != {exp.type_id!r}"
     assert got.size == exp.size, f"{what}: size {got.size} != {exp.size}"
-    if check_nullable:
-        assert (got.mask is None) == (exp.mask is None), f"{what}: nullability differs"
     if got.size == 0:
         return
+    if check_nullable:
+        assert (got.mask is None) == (exp.mask is None), f"{what}: nullability differs"
     vg, ve = got.valid()[order_got], exp.valid()[order_exp]
     assert np.array_equal(vg, ve), f"{what}: validity differs at {np.flatnonzero(vg != ve)[:8]}"
     assert got.null_count == exp.null_count, f"{what}: null_count {got.null_count} != {exp.null_count}"
@@ -88,7 +93,10 @@ def assert_column_equal(got: HostColumn, exp: HostColumn, order_got, order_exp, 
         assert np.array_equal(a[inf], b[inf]), f"{what}: infinities differ"
         fin = ~(nan_a | inf)
         err = np.abs(a[fin] - b[fin])
-        tol = rtol * np.maximum(np.abs(a[fin]), np.abs(b[fin])) + 1e-300
+        mag = np.maximum(np.abs(a[fin]), np.abs(b[fin]))
+        if scale is not None:
+            mag = np.maximum(mag, np.asarray(scale, dtype=np.float64)[order_exp][ve][fin])
+        tol = rtol * mag + 1e-300
         bad = np.flatnonzero(err > tol)
         assert bad.size == 0, (f"{what}: {bad.size} values beyond rtol {rtol}; first {a[fin][bad[:4]]} vs "
                                f"{b[fin][bad[:4]]}")
@@ -163,9 +171,54 @@ def gpu_groupby(keys: Sequence[HostColumn], requests, null_policy=NullPolicy.EXC
     return [c.to_host() for c in okeys.columns()], [[c.to_host() for c in t.columns()] for t in ores]
 
 
-def assert_same_result(got, exp, requests, check_nullable=True):
+def result_scales(keys, requests, null_policy, row_filters=(), row_filter_offsets=()):
+    """Per request, the magnitudes that bound the rounding error of its floating-point results, in
+    the oracle's group order: (Σ|x|, Σx², n).  A sum of n floats is only determined up to
+    ~eps·Σ|x| (any summation order, the reference's atomics included), and Σx² − (Σx)²/n up to
+    ~eps·Σx², so the north-star tolerances are applied relative to these, not to a result that
+    cancellation may have driven towards zero."""
+    from oracle import oracle
+    reqs = []
+    for vals, _ in requests:
+        if vals.type_id == TypeId.STRING or vals.type_id not in STORAGE_DTYPE:
+            x = np.zeros(vals.size)
+        else:
+            x = vals.values().astype(np.float64)
+        x = np.where(np.isfinite(x), x, 0.0)
+        valid = vals.valid() if vals.mask is not None else None
+        reqs.append((HostColumn.from_numpy(np.abs(x), valid), [Kind.SUM, Kind.COUNT_VALID]))
+        reqs.append((HostColumn.from_numpy(x * x, valid), [Kind.SUM]))
+    _, res = oracle.groupby(keys, reqs, null_policy, row_filters=row_filters, row_filter_offsets=row_filter_offsets)
+    out = []
+    for q in range(len(requests)):
+        sa = np.where(res[2 * q][0].valid(), res[2 * q][0].values(), 0.0)
+        n = res[2 * q][1].values().astype(np.float64)
+        ss = np.where(res[2 * q + 1][0].valid(), res[2 * q + 1][0].values(), 0.0)
+        out.append((sa, ss, n))
+    return out
+
+
+def _scale_for(kind, ddof, sa, ss, n):
+    kind = Kind(kind)
+    df = np.maximum(n - ddof, 1.0)
+    if kind == Kind.SUM:
+        return sa
+    if kind == Kind.MEAN:
+        return sa / np.maximum(n, 1.0)
+    if kind in (Kind.SUM_OF_SQUARES, Kind.M2):
+        return ss
+    if kind == Kind.VARIANCE:
+        return ss / df
+    if kind == Kind.STD:
+        return np.sqrt(ss / df)
+    return np.zeros_like(sa)
+
+
+def assert_same_result(got, exp, requests, check_nullable=True, scales=None):
     """Compares two (keys, results) pairs after sorting both by key: keys, counts, integer results
-    bit-exact; float results within the north-star tolerance of their SOURCE type."""
+    bit-exact; float results within the north-star tolerance of their SOURCE type (1e-12 for
+    fp64 sources, 1e-5 for fp32), relative to max(|result|, error scale of the group) when
+    ``scales`` (from result_scales, in ``exp``'s group order) is given."""
     gk, gr = got
     ek, er = exp
     og, oe = sort_order(gk), sort_order(ek)
@@ -173,5 +226,9 @@ def assert_same_result(got, exp, requests, check_nullable=True):
     assert_keys_equal(gk, ek, og, oe)
     for q, (vals, aggs) in enumerate(requests):
         for a in range(len(aggs)):
+            kind, ddof = (aggs[a] if isinstance(aggs[a], tuple) else (aggs[a], 1))
+            scale = None
+            if scales is not None and is_floating(er[q][a].type_id):
+                scale = _scale_for(kind, ddof, *scales[q])
             assert_column_equal(gr[q][a], er[q][a], og, oe, rtol_for(vals.type_id), f"request {q} agg {aggs[a]}",
-                                check_nullable=check_nullable)
+                                check_nullable=check_nullable, scale=scale)

@@ -17,14 +17,15 @@ ALL_AGGS = [Kind.SUM, Kind.COUNT_VALID, Kind.COUNT_ALL, Kind.MEAN, Kind.MIN, Kin
 
 def check(keys, requests, policy=NullPolicy.EXCLUDE, row_filters=(), **opts):
     got = H.gpu_groupby(keys, requests, policy, row_filters=row_filters, **opts)
-    exp = oracle.groupby(keys, requests, policy, row_filters=[f.mask for f in row_filters if f.mask is not None],
-                         row_filter_offsets=[f.offset for f in row_filters if f.mask is not None])
-    H.assert_same_result(got, exp, requests)
+    fm = [f.mask for f in row_filters if f.mask is not None]
+    fo = [f.offset for f in row_filters if f.mask is not None]
+    exp = oracle.groupby(keys, requests, policy, row_filters=fm, row_filter_offsets=fo)
+    H.assert_same_result(got, exp, requests, scales=H.result_scales(keys, requests, policy, fm, fo))
     return got
 
 
 @pytest.mark.parametrize("config,n", [(1, 400_000), (2, 600_000), (3, 300_000), (4, 500_000), (5, 120_000)])
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 3])
 def test_benchmark_configs_match_oracle(config, n, variant):
     w = workloads.make(config, n, scale_domain=(config in (3, 4)))
     check(w.keys, w.requests, w.null_policy, w.row_filters, table_variant=variant)
@@ -177,6 +178,25 @@ def test_skewed_keys_hot_group():
     k = np.where(rng.random(n) < 0.9, 7, rng.integers(0, 100_000, n)).astype(np.int64)
     v = HostColumn.from_numpy(rng.lognormal(0, 1, n), valid=rng.random(n) > 0.01)
     check([HostColumn.from_numpy(k)], [(v, [Kind.SUM, Kind.MEAN, Kind.VARIANCE, Kind.MIN, Kind.MAX])])
+
+
+def test_dense_key_box_with_outliers_and_negative_keys():
+    # the shared-memory slot of a key is its position in a box found from a row sample; keys the
+    # sample missed (here: 30 far-away keys at unsampled rows) must still aggregate exactly
+    rng = np.random.default_rng(31)
+    n = 2_000_000
+    a = rng.integers(-40, 40, n).astype(np.int32)
+    b = rng.integers(1000, 1050, n).astype(np.int64)
+    odd = rng.choice(n, 30, replace=False)
+    a[odd] = rng.integers(-2**31, 2**31 - 1, 30)
+    b[odd[:10]] = rng.integers(-2**62, 2**62, 10)
+    v = HostColumn.from_numpy(rng.standard_normal(n).astype(np.float32), valid=rng.random(n) > 0.1)
+    w = HostColumn.from_numpy(rng.integers(-100, 100, n).astype(np.int64), valid=rng.random(n) > 0.1)
+    ka = HostColumn.from_numpy(a, valid=rng.random(n) > 0.01)
+    kb = HostColumn.from_numpy(b)
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        check([ka, kb], [(v, [Kind.MEAN])], policy)
+        check([ka, kb], [(v, [Kind.SUM, Kind.MIN, Kind.MAX]), (w, [Kind.SUM, Kind.COUNT_ALL, Kind.VARIANCE])], policy)
 
 
 def test_float32_sum_spills_to_fp64():
