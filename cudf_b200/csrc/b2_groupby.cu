@@ -507,10 +507,16 @@ void bind_plan_inputs(DPlan& P, const Schema& sc, const b2_groupby& gb, const b2
   }
   if (sc.f32mean && aligned(P.vals[sc.cells[0].col].data, P.vals[sc.cells[0].col].offset, 4)) P.flags |= PF_VEC_VAL0;
   P.nfilters = (int)gb.filters.size();
+  bool fast = true;
   for (int f = 0; f < P.nfilters; ++f) {
     P.filters[f] = gb.filters[(size_t)f];
     P.filter_offsets[f] = gb.filter_offsets[(size_t)f];
+    fast = fast && (P.filter_offsets[f] % 4 == 0);
   }
+  for (int k = 0; k < sc.nkeys; ++k)
+    fast = fast && (P.keys[k].width == 4 || P.keys[k].width == 8) && (!P.keys[k].mask || P.keys[k].offset % 4 == 0);
+  for (int v = 0; v < sc.nvals; ++v) fast = fast && (!P.vals[v].mask || P.vals[v].offset % 4 == 0);
+  if (fast) P.flags |= PF_FAST;
 }
 
 // ------------------------------------------------------------------------------ table management
@@ -561,11 +567,11 @@ void read_ctrl(b2_groupby_state& st, cudaStream_t stream)
 
 int64_t num_groups(const b2_groupby_state& st) { return (int64_t)st.host_ctrl.nclaimed + (st.host_ctrl.special_used ? 1 : 0); }
 
-template <int KM, int LAYOUT>
+template <int KM, int LAYOUT, int NKF = 0>
 void launch_aggregate(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, int S, int fill_limit, size_t smem,
                       cudaStream_t stream)
 {
-  auto kern = k_aggregate<KM, LAYOUT>;
+  auto kern = k_aggregate<KM, LAYOUT, NKF>;
   static thread_local size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -621,8 +627,15 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
     g_stats.kernel_launches++;
   }
   if (sc.key_mode == KM_PACKED) {
-    if (layout == SL_F32MEAN) launch_aggregate<KM_PACKED, SL_F32MEAN>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream);
-    else if (layout == SL_GENERIC) launch_aggregate<KM_PACKED, SL_GENERIC>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream);
+    if (layout == SL_F32MEAN) {
+      // the number of key columns is a template parameter of the lean path (1..3), 0 = generic loops
+      switch ((P.flags & PF_FAST) ? sc.nkeys : 0) {
+        case 1: launch_aggregate<KM_PACKED, SL_F32MEAN, 1>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream); break;
+        case 2: launch_aggregate<KM_PACKED, SL_F32MEAN, 2>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream); break;
+        case 3: launch_aggregate<KM_PACKED, SL_F32MEAN, 3>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream); break;
+        default: launch_aggregate<KM_PACKED, SL_F32MEAN, 0>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream); break;
+      }
+    } else if (layout == SL_GENERIC) launch_aggregate<KM_PACKED, SL_GENERIC>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream);
     else launch_aggregate<KM_PACKED, SL_NONE>(P, st.table, st.cap, st.ctrl, 0, 0, 0, stream);
   } else {
     if (layout == SL_GENERIC) launch_aggregate<KM_ROWS, SL_GENERIC>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream);
@@ -632,7 +645,7 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
   st.ctrl_fresh = false;
 }
 
-constexpr int64_t SPECULATIVE_CAP = 1 << 20;  // first table when nothing is known about the cardinality
+constexpr int64_t SPECULATIVE_CAP = 1 << 17;  // first table when nothing is known about the cardinality
 constexpr double MAX_LOAD = 0.70;
 
 // aggregates the bound inputs into an EMPTY state, growing the table until it fits
@@ -657,7 +670,7 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
     }
     if (!st.host_ctrl.overflow) break;
     if (cap >= full) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow at full capacity");
-    cap = (attempt == 1 && hint > 0 && cap * 4 < full) ? cap * 4 : full;
+    cap = (cap * 16 < full) ? cap * 16 : full;  // 2^17 -> 2^21 -> sized for the row count
   }
 }
 
