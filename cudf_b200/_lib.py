@@ -95,6 +95,10 @@ PROTOTYPES = {
     "b2_hash_partition": (C.c_int, [C.POINTER(ColumnView), C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                     C.POINTER(Allocator), C.POINTER(OwnedColumn), C.POINTER(C.c_int64)]),
     "b2_column_free": (None, [C.POINTER(OwnedColumn), C.POINTER(Allocator), C.c_void_p]),
+    "b2_groupby_aggregate_noalloc": (C.c_int, [C.c_void_p, C.POINTER(AggregationRequest), C.c_int32, C.c_void_p,
+                                               C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                               C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int32),
+                                               C.POINTER(C.c_int32)]),
     "b2_last_error": (C.c_char_p, []),
     "b2_version": (C.c_char_p, []),
     "b2_get_last_stats": (None, [C.POINTER(CallStats)]),

@@ -957,6 +957,134 @@ void update_state(b2_groupby_state& st, const b2_groupby& gb, const b2_aggregati
 
 }  // namespace
 
+// ------------------------------------------------------------------------------ no-allocation variant
+// Scratch of b2_groupby_aggregate_noalloc: table + control block + null counters.  Lives in the
+// library image on every device that loads it.  In host code this name is only a handle for
+// cudaGetSymbolAddress; kernels get the device address looked up below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[B2_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+unsigned char* g_noalloc_addr[MAX_DEVICES] = {};
+std::mutex g_noalloc_mutex;
+
+// device address of the scratch array on the current device (looked up once per device)
+unsigned char* noalloc_scratch()
+{
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) B2_FAIL(B2_UNSUPPORTED, "device ordinal beyond 63");
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_addr[dev]) {
+    void* p = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    g_noalloc_addr[dev] = (unsigned char*)p;
+  }
+  return g_noalloc_addr[dev];
+}
+}  // namespace
+
+extern "C" b2_status b2_groupby_aggregate_noalloc(b2_groupby* gb, const b2_aggregation_request* requests,
+                                                  int32_t num_requests, void* stream_, int32_t max_groups,
+                                                  void* const* key_data, uint32_t* const* key_masks,
+                                                  void* const* result_data, uint32_t* const* result_masks,
+                                                  int32_t* num_groups_out, int32_t* null_counts_out)
+{
+  return guarded([&] {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!gb || !key_data || !result_data || !num_groups_out || max_groups < 1)
+      B2_FAIL(B2_INVALID_ARGUMENT, "null argument or max_groups < 1");
+    *num_groups_out = 0;
+    g_stats = b2_call_stats{};
+    if (gb->keys.empty()) B2_FAIL(B2_LOGIC_ERROR, "groupby needs at least one key column");
+    validate_requests(*gb, requests, num_requests);
+    Schema sc = make_schema(*gb, requests, num_requests);
+    if (sc.key_mode != KM_PACKED)
+      B2_FAIL(B2_UNSUPPORTED, "the no-allocation variant serves keys that pack into 64 bits (no string / float / wide keys)");
+    DPlan P;
+    fill_plan_schema(P, sc);
+    bind_plan_inputs(P, sc, *gb, requests, num_requests);
+
+    // carve the scratch array: [control block | null counters | table]
+    unsigned char* base = noalloc_scratch();
+    const size_t ctrl_bytes = (sizeof(DCtrl) + 255) / 256 * 256;
+    const size_t nulls_bytes = ((MAX_OUTS + MAX_KEYS) * sizeof(u32) + 255) / 256 * 256;
+    const int64_t cap = 2 * (int64_t)max_groups;
+    const size_t table_bytes = (size_t)(cap + 1) * P.stride * 8;
+    if (ctrl_bytes + nulls_bytes + table_bytes > B2_NOALLOC_SCRATCH_BYTES)
+      B2_FAIL(B2_INVALID_ARGUMENT, "max_groups = " + std::to_string(max_groups) + " needs a " + std::to_string(table_bytes) +
+                                     "-byte table; the fixed scratch array holds " +
+                                     std::to_string(B2_NOALLOC_SCRATCH_BYTES - ctrl_bytes - nulls_bytes) + " bytes (" +
+                                     std::to_string((B2_NOALLOC_SCRATCH_BYTES - ctrl_bytes - nulls_bytes) / ((size_t)P.stride * 8) / 2 - 1) +
+                                     " groups for this request)");
+    DCtrl* ctrl = (DCtrl*)base;
+    u32* null_counts = (u32*)(base + ctrl_bytes);
+    u64* table = (u64*)(base + ctrl_bytes + nulls_bytes);
+    for (int k = 0; k < sc.nkeys; ++k) {
+      if (!key_data[k]) B2_FAIL(B2_INVALID_ARGUMENT, "key_data entry is null");
+      if (sc.include_nulls && sc.key_nullable[k] && (!key_masks || !key_masks[k]))
+        B2_FAIL(B2_INVALID_ARGUMENT, "a nullable key column needs a key_masks entry");
+    }
+    for (size_t i = 0; i < sc.outs.size(); ++i) {
+      if (!result_data[i]) B2_FAIL(B2_INVALID_ARGUMENT, "result_data entry is null");
+      if (sc.outs[i].nullable && (!result_masks || !result_masks[i]))
+        B2_FAIL(B2_INVALID_ARGUMENT, "a nullable result column needs a result_masks entry");
+    }
+
+    // everything the kernels read is written first: the previous call's contents are irrelevant
+    DCtrl h{};
+    h.claim_limit = (u64)max_groups;  // one more claim than this sets the overflow flag
+    CUDA_TRY(cudaMemcpyAsync(ctrl, &h, sizeof(DCtrl), cudaMemcpyHostToDevice, stream));
+    CUDA_TRY(cudaMemsetAsync(null_counts, 0, nulls_bytes, stream));
+    CUDA_TRY(cudaStreamSynchronize(stream));  // `h` is a stack object
+    k_table_init<<<grid_for(cap + 1, 256, 16), 256, 0, stream>>>(table, cap + 1, P);
+    CUDA_TRY(cudaGetLastError());
+    int64_t G = 0;
+    if (P.nrows > 0) {
+      launch_aggregate<KM_PACKED, SL_NONE>(P, table, cap, ctrl, 0, 0, 0, stream);
+      CUDA_TRY(cudaMemcpyAsync(&h, ctrl, sizeof(DCtrl), cudaMemcpyDeviceToHost, stream));
+      CUDA_TRY(cudaStreamSynchronize(stream));
+      G = (int64_t)h.nclaimed + (h.special_used ? 1 : 0);
+      if (h.overflow || G > max_groups) B2_FAIL(B2_LOGIC_ERROR, "the input holds more than max_groups groups");
+    }
+    g_stats.kernel_launches += 1;
+
+    auto plan = std::make_unique<DOutPlan>();
+    std::memset(plan.get(), 0, sizeof(DOutPlan));
+    plan->nouts = (int)sc.outs.size();
+    const size_t mask_bytes = (size_t)((max_groups + 31) / 32) * 4;
+    for (size_t i = 0; i < sc.outs.size(); ++i) {
+      const OutSpec& o = sc.outs[i];
+      DOutCol& d = plan->outs[i];
+      d.data = result_data[i];
+      d.mask = o.nullable ? result_masks[i] : nullptr;
+      d.kind = o.kind; d.rclass = vclass_of(o.rtype);
+      d.c_a = o.c_a; d.c_b = o.c_b; d.c_cnt = o.c_cnt; d.ddof = o.ddof; d.src_float = o.src_float;
+      d.null_slot = (int)i;
+      if (d.mask) CUDA_TRY(cudaMemsetAsync(d.mask, 0xFF, mask_bytes, stream));
+    }
+    for (int k = 0; k < sc.nkeys; ++k) {
+      plan->kdata[k] = key_data[k];
+      plan->kmask[k] = (sc.include_nulls && sc.key_nullable[k]) ? key_masks[k] : nullptr;
+      if (plan->kmask[k]) CUDA_TRY(cudaMemsetAsync(plan->kmask[k], 0xFF, mask_bytes, stream));
+    }
+    plan->null_counts = null_counts;
+    u32 h_nulls[MAX_OUTS + MAX_KEYS] = {};
+    if (G > 0) {
+      k_finalize<<<grid_for(cap + 1, 256, 8), 256, 0, stream>>>(P, *plan, table, cap, ctrl);
+      CUDA_TRY(cudaGetLastError());
+      g_stats.kernel_launches += 1;
+      CUDA_TRY(cudaMemcpyAsync(h_nulls, null_counts, sizeof(h_nulls), cudaMemcpyDeviceToHost, stream));
+    }
+    CUDA_TRY(cudaStreamSynchronize(stream));
+    *num_groups_out = (int32_t)G;
+    if (null_counts_out) {
+      for (int k = 0; k < sc.nkeys; ++k) null_counts_out[k] = (int32_t)h_nulls[MAX_OUTS + k];
+      for (size_t i = 0; i < sc.outs.size(); ++i) null_counts_out[sc.nkeys + i] = (int32_t)h_nulls[i];
+    }
+  });
+}
+
 // ================================================================================ C ABI
 extern "C" {
 

@@ -245,6 +245,45 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns,
 /* Releases the buffers of one owned column obtained from b2_hash_partition. */
 void b2_column_free(b2_owned_column* col, const b2_allocator* allocator, void* stream);
 
+/* ---- aggregate without any device allocation -----------------------------
+ * No counterpart in the reference (libcudf always allocates through an rmm resource).
+ *
+ * For callers that must not allocate device memory while they run: code inside a latency-critical
+ * serving loop or a real-time pipeline where a cudaMalloc (an implicit device-wide
+ * synchronisation) is not acceptable, plug-ins that run under a host framework owning all device
+ * memory and handing out fixed buffers, and processes whose memory pool has been frozen.  The
+ * whole aggregate runs inside buffers the caller passes plus ONE fixed scratch array that lives in
+ * the library image: a file-scope __device__ array of B2_NOALLOC_SCRATCH_BYTES that every GPU
+ * loading the library holds until the process exits.  The hash table, the control block and the
+ * null counters are carved out of it.
+ *
+ * Same semantics and result types as b2_groupby_aggregate, with these limits:
+ *   - keys must be packable into 64 bits (fixed-width, non-float key columns; no strings);
+ *   - the table needs 2*max_groups+1 slots of (1 + number of accumulator cells) * 8 bytes; a call
+ *     whose table would not fit the scratch array is rejected with B2_INVALID_ARGUMENT and a
+ *     message that names both sizes (e.g. one SUM+COUNT request: up to 174,000 groups);
+ *   - if the input holds more than max_groups groups the call fails with B2_LOGIC_ERROR and the
+ *     output buffers hold garbage.
+ * Outputs: key_data[k] and result_data[i] are device buffers of max_groups elements of the
+ * column's result type (result i = aggregations in request order, request after request);
+ * key_masks[k] / result_masks[i] are device buffers of ceil(max_groups/32) words, required where
+ * the column is nullable (key: INCLUDE policy and a masked key column; result: see
+ * b2_groupby_aggregate), otherwise they may be NULL.  *num_groups_out (host) receives the group
+ * count; null_counts_out (host, may be NULL) receives num_keys + total-aggregations null counts.
+ *
+ * The first call on each device looks up the scratch array's device address
+ * (cudaGetSymbolAddress, with that device current); make that first call before any stream
+ * capture begins.  The call uses no cudaMalloc / cudaFree / cudaMallocAsync and no memory pool.
+ * Every call reuses the same scratch array and re-initialises the parts it reads, so the previous
+ * call's contents never leak into a result — but two calls that overlap in time on one GPU (other
+ * streams, other host threads) race on it: serialise them.  Synchronises `stream` twice. */
+#define B2_NOALLOC_SCRATCH_BYTES (8u << 20)
+b2_status b2_groupby_aggregate_noalloc(b2_groupby* gb, const b2_aggregation_request* requests,
+                                       int32_t num_requests, void* stream, int32_t max_groups,
+                                       void* const* key_data, uint32_t* const* key_masks,
+                                       void* const* result_data, uint32_t* const* result_masks,
+                                       int32_t* num_groups_out, int32_t* null_counts_out);
+
 /* ---- introspection ------------------------------------------------------ */
 const char* b2_last_error(void);   /* message of this thread's last failure */
 const char* b2_version(void);
