@@ -1,0 +1,177 @@
+"""Partial-aggregate state (pack / merge / finalize), batch-wise updates and the row-level hash
+partition on ONE GPU, emulating the ranks of a multi-GPU run: the merge of partials must equal a
+one-shot groupby (the rules of cpp/tests/groupby/streaming_groupby_test.cpp:300,884,912,942)."""
+import numpy as np
+import pytest
+
+import workloads
+from cudf_b200.types import HostColumn, Kind, NullPolicy, TypeId
+from oracle import oracle
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+def _device_objects(keys, requests, policy, lo, hi, **opts):
+    import cudf_b200 as cb
+    from cudf_b200.aggregation import Aggregation
+
+    def cut(c):
+        valid = c.valid()[lo:hi] if c.mask is not None else None
+        return HostColumn.from_numpy(c.values()[lo:hi], valid, type_id=c.type_id)
+
+    dk = cb.Table([cb.Column.from_host(cut(k)) for k in keys])
+    cache = {}
+    reqs = []
+    for v, aggs in requests:
+        if id(v) not in cache:
+            cache[id(v)] = cb.Column.from_host(cut(v))
+        reqs.append(cb.GroupByRequest(cache[id(v)], [Aggregation(Kind(a[0]), a[1]) if isinstance(a, tuple)
+                                                     else Aggregation(Kind(a)) for a in aggs]))
+    return cb.GroupBy(dk, policy, **opts), reqs
+
+
+def _to_host(res):
+    okeys, ores = res
+    return [c.to_host() for c in okeys.columns()], [[c.to_host() for c in t.columns()] for t in ores]
+
+
+def _concat(parts):
+    """Union of per-rank results (disjoint groups)."""
+    keys = [HostColumn.from_numpy(np.concatenate([p[0][k].values() for p in parts]),
+                                  np.concatenate([p[0][k].valid() for p in parts]) if parts[0][0][k].mask is not None else None,
+                                  type_id=parts[0][0][k].type_id) for k in range(len(parts[0][0]))]
+    res = []
+    for q in range(len(parts[0][1])):
+        row = []
+        for a in range(len(parts[0][1][q])):
+            cols = [p[1][q][a] for p in parts]
+            valid = np.concatenate([c.valid() for c in cols]) if cols[0].mask is not None else None
+            row.append(HostColumn.from_numpy(np.concatenate([c.values() for c in cols]), valid, type_id=cols[0].type_id))
+        res.append(row)
+    return keys, res
+
+
+AGGS = [Kind.SUM, Kind.COUNT_VALID, Kind.COUNT_ALL, Kind.MEAN, Kind.MIN, Kind.MAX, Kind.VARIANCE, Kind.M2]
+
+
+@pytest.mark.parametrize("ranks", [2, 4])
+@pytest.mark.parametrize("config", [1, 2, 4])
+def test_emulated_ranks_partials_shuffle_equals_one_shot(config, ranks):
+    import cudf_b200 as cb
+    n = 240_000
+    w = workloads.make(config, n, scale_domain=(config == 4))
+    reqs = [(v, AGGS) for v, _ in w.requests]
+    filt = []  # row filters are per-shard views; leave them out of this emulation
+    states, packed = [], []
+    for r in range(ranks):
+        gb, dreqs = _device_objects(w.keys, reqs, w.null_policy, r * n // ranks, (r + 1) * n // ranks)
+        st = cb.GroupByState(gb, dreqs)
+        st.update()
+        records, counts = st.pack(ranks)
+        assert sum(counts) == st.num_groups()
+        packed.append((records, counts, st.record_bytes))
+        states.append((st, gb, dreqs))
+    parts = []
+    for dst in range(ranks):
+        st, gb, dreqs = states[dst]
+        st.reset()
+        for records, counts, rb in packed:
+            start = sum(counts[:dst]) * rb
+            st.merge(records[start:start + counts[dst] * rb], counts[dst])
+        parts.append(_to_host(st.finalize()))
+    got = _concat(parts)
+    exp = oracle.groupby(w.keys, reqs, w.null_policy)
+    H.assert_same_result(got, exp, reqs, scales=H.result_scales(w.keys, reqs, w.null_policy))
+    # ownership is disjoint: no key on two ranks
+    assert got[0][0].size == exp[0][0].size
+
+
+def test_batchwise_updates_equal_one_shot():
+    import cudf_b200 as cb
+    rng = np.random.default_rng(41)
+    n = 300_000
+    # (an int64 key with nulls under INCLUDE needs 65 bits: such states are row-keyed and take one update)
+    k = HostColumn.from_numpy(rng.integers(0, 5000, n).astype(np.int32), valid=rng.random(n) > 0.02)
+    v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.1)
+    reqs = [(v, AGGS)]
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        st = None
+        for b in range(3):
+            gb, dreqs = _device_objects([k], reqs, policy, b * n // 3, (b + 1) * n // 3)
+            if st is None:
+                st = cb.GroupByState(gb, dreqs)
+            st.update(gb, dreqs)
+        got = _to_host(st.finalize())
+        exp = oracle.groupby([k], reqs, policy)
+        H.assert_same_result(got, exp, reqs, scales=H.result_scales([k], reqs, policy))
+
+
+def test_state_with_string_keys_reports_unsupported_for_pack():
+    import cudf_b200 as cb
+    from cudf_b200 import aggregation as agg
+    s = cb.Column.from_host(HostColumn.from_strings(["a", "b", "a", "c"] * 100))
+    v = cb.Column.from_host(HostColumn.from_numpy(np.arange(400, dtype=np.int32)))
+    gb = cb.GroupBy(cb.Table([s]))
+    st = cb.GroupByState(gb, [cb.GroupByRequest(v, [agg.sum()])])
+    st.update()
+    assert st.num_groups() == 3
+    with pytest.raises(cb.UnsupportedError):
+        st.pack(2)
+    keys, res = _to_host(st.finalize())
+    assert sorted(keys[0].to_pylist()) == [b"a", b"b", b"c"]
+
+
+@pytest.mark.parametrize("nparts", [1, 2, 8, 13])
+def test_hash_partition_rows(nparts):
+    import cudf_b200 as cb
+    from cudf_b200.partition import hash_partition
+    rng = np.random.default_rng(42)
+    n = 100_003
+    a = HostColumn.from_numpy(rng.integers(0, 1000, n).astype(np.int64))
+    b = HostColumn.from_numpy(rng.integers(-5, 5, n).astype(np.int32))
+    v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.2)
+    w = HostColumn.from_numpy(rng.integers(0, 255, n).astype(np.uint8))
+    table = cb.Table([cb.Column.from_host(c) for c in (a, b, v, w)])
+    out, offsets = hash_partition(table, 2, nparts)
+    assert offsets[0] == 0 and offsets[-1] == n and len(offsets) == nparts + 1
+    cols = [c.to_host() for c in out.columns()]
+    ka, kb = cols[0].values(), cols[1].values()
+    # every key lands in exactly one partition
+    part_of = np.repeat(np.arange(nparts), np.diff(offsets))
+    keyid = ka * 100 + kb
+    first = {}
+    order = np.argsort(keyid, kind="stable")
+    sk, sp = keyid[order], part_of[order]
+    change = np.flatnonzero(np.diff(sk)) + 1
+    for seg in np.split(sp, change):
+        assert seg.min() == seg.max()
+    # the rows are a permutation of the input, validity travelling with the values
+    def rows(cols4):
+        vv = np.where(cols4[2].valid(), cols4[2].values(), np.nan)
+        return sorted(zip(cols4[0].values().tolist(), cols4[1].values().tolist(),
+                          [None if np.isnan(x) else x for x in vv.tolist()], cols4[3].values().tolist()),
+                      key=lambda t: (t[0], t[1], t[3], -1e300 if t[2] is None else t[2]))
+    assert rows(cols) == rows([a, b, v, w])
+    assert cols[2].null_count == v.null_count
+
+
+def test_rows_strategy_matches_partials_on_emulated_ranks():
+    """hash_partition of raw rows, then per-partition groupby == one-shot groupby."""
+    import cudf_b200 as cb
+    from cudf_b200.aggregation import Aggregation
+    from cudf_b200.partition import hash_partition
+    w = workloads.make(3, 200_000, scale_domain=True)
+    table = cb.Table([cb.Column.from_host(c) for c in (w.keys[0], w.requests[0][0])])
+    out, offsets = hash_partition(table, 1, 4)
+    parts = []
+    for p in range(4):
+        lo, hi = offsets[p], offsets[p + 1]
+        kc, vc = out.columns()
+        k = cb.Column(kc.type_id, hi - lo, kc.data[lo * 8:hi * 8].clone(), None, 0, 0)
+        v = cb.Column(vc.type_id, hi - lo, vc.data[lo * 8:hi * 8].clone(), None, 0, 0)
+        gb = cb.GroupBy(cb.Table([k]))
+        parts.append(_to_host(gb.aggregate([cb.GroupByRequest(v, [Aggregation(Kind(a)) for a in w.requests[0][1]])])))
+    got = _concat(parts)
+    exp = oracle.groupby(w.keys, w.requests)
+    H.assert_same_result(got, exp, w.requests)
