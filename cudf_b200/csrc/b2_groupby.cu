@@ -670,7 +670,7 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
     }
     if (!st.host_ctrl.overflow) break;
     if (cap >= full) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow at full capacity");
-    cap = (cap * 16 < full) ? cap * 16 : full;  // 2^17 -> 2^21 -> sized for the row count
+    cap = (cap * 16 < full) ? cap * 16 : full;  // 2^17 -> 2^21 -> 2^25 -> 2^29 -> sized for the row count
   }
 }
 
