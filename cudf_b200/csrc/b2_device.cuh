@@ -91,7 +91,7 @@ enum PlanFlags : int {
   PF_VEC_KEYS = 1,  // every key column may be read 4 rows at a time with one 16-byte load
   PF_VEC_VAL0 = 2,  // value column 0 likewise (compact FLOAT32 layout)
   PF_FAST     = 4   // every key column is 4 or 8 bytes wide and every mask / filter offset is a
-                    // multiple of 4, so 4 validity bits never straddle a mask word
+                    // multiple of 4, so the validity bits of 4 consecutive rows never straddle a mask word
 };
 
 // Dense key mapping of one aggregate pass, written on the device by k_sample_ranges: when the keys

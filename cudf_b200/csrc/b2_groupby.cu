@@ -577,9 +577,10 @@ void launch_aggregate(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, int S,
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
-  const int64_t tile = (int64_t)AGG_BLOCK * AGG_ROWS;
+  const int block = NKF > 0 ? LEAN_BLOCK : AGG_BLOCK;
+  const int64_t tile = (int64_t)block * AGG_ROWS;
   const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((P.nrows + tile - 1) / tile, device_info().sms));
-  kern<<<grid, AGG_BLOCK, smem, stream>>>(P, tbl, cap, ctrl, S, fill_limit);
+  kern<<<grid, block, smem, stream>>>(P, tbl, cap, ctrl, S, fill_limit);
   CUDA_TRY(cudaGetLastError());
   g_stats.kernel_launches++;
 }

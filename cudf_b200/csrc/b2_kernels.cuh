@@ -20,6 +20,9 @@
 namespace b2 {
 
 constexpr int AGG_BLOCK      = 1024;  // threads per CTA of the fused kernel (one CTA per SM)
+constexpr int LEAN_BLOCK     = 1024;  // threads per CTA of the lean instantiations (512 measured 1.6x slower:
+                                      // too few warps to cover the shared-memory atomics' latency)
+constexpr int LEAN_ROWS      = 4;     // rows per thread per tile in the lean loop
 constexpr int AGG_ROWS       = 4;     // rows per thread per tile
 constexpr int SMEM_PROBES    = 48;    // probe limit of the shared-memory table
 constexpr int GMEM_PROBES    = 2048;  // probe limit of the global table before "overflow"
@@ -259,7 +262,7 @@ __device__ __forceinline__ u32 nibble_aligned(const u32* mask, u32 pos)
 // Rows whose key is not in shared memory go to the global table with global atomics.  At the end
 // every CTA merges its table into the global one.  There is no barrier inside the row loop.
 template <int KM, int LAYOUT, int NKF>
-__global__ void __launch_bounds__(AGG_BLOCK, 1)
+__global__ void __launch_bounds__(NKF > 0 ? LEAN_BLOCK : AGG_BLOCK, 1)
 k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* ctrl, int S_hash, int fill_limit)
 {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -299,54 +302,47 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
   }
   __syncthreads();
 
-  const i64 tile_rows = (i64)blockDim.x * AGG_ROWS;
-  const i64 ntiles    = (P.nrows + tile_rows - 1) / tile_rows;
   u32 my_hit = 0, my_miss = 0, tot_hit = 0, tot_miss = 0;
   const bool fast_ok = NKF > 0 && dense && (P.flags & PF_VEC_KEYS) && (P.flags & PF_VEC_VAL0) && (P.flags & PF_FAST);
 
-  for (i64 tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-    if (*(volatile int*)&s_abort) break;
-    const i64 row0 = tile * tile_rows + (i64)tid * AGG_ROWS;
-    const int nv   = (int)max((i64)0, min((i64)AGG_ROWS, P.nrows - row0));
-    const bool cache_on = (LAYOUT != SL_NONE) && (dense || *(volatile int*)&s_cache_on);
+  // ---- lean loop: dense key box + compact FLOAT32 layout.  4 consecutive rows per thread per tile,
+  // 16-byte vector loads all issued before the first use, 32-bit arithmetic, two native
+  // shared-memory atomics per row.  It consumes all full tiles; the generic loop below takes the
+  // remaining rows.
+  i64 rows_done = 0;
+  if (LAYOUT == SL_F32MEAN && NKF > 0 && fast_ok) {
+    constexpr int NK = NKF > 0 ? NKF : 1;
+    const u32 lean_tile = (u32)blockDim.x * LEAN_ROWS;
+    const u32 nfull     = (u32)(P.nrows / lean_tile);
+    rows_done           = (i64)nfull * lean_tile;
+    const DValCol& vc   = P.vals[P.cells[0].col];
+    const u32 ssum_a = (u32)__cvta_generic_to_shared(ssum), scnt_a = (u32)__cvta_generic_to_shared(scnt);
+    const bool filt_is_val = P.nfilters == 1 && P.filters[0] == vc.mask && P.filter_offsets[0] == vc.offset;
 
-    // ---- lean path: dense key box + compact FLOAT32 layout + vector loads, 32-bit arithmetic
-    // (taken or not by whole warps: the generic path below synchronises the warp)
-    bool handled = false;
-    const i64 warp_last = tile * tile_rows + (i64)((tid | 31) + 1) * AGG_ROWS;  // one past the warp's rows
-    if (LAYOUT == SL_F32MEAN && fast_ok && warp_last <= P.nrows) {
-      handled = true;
-      const u32 r0 = (u32)row0;
-      const DValCol& vc = P.vals[P.cells[0].col];
+    for (u32 tile = blockIdx.x; tile < nfull; tile += gridDim.x) {
+      const u32 r0 = tile * lean_tile + (u32)tid * LEAN_ROWS;
+      // loads
       const u32 ve = (u32)vc.offset + r0;
       const float4 q = __ldg((const float4*)((const float*)vc.data + ve));
       const u32 vn = vc.mask ? nibble_aligned(vc.mask, ve) : 0xFu;
       u32 act = 0xFu;
-      for (int f = 0; f < P.nfilters; ++f) {
-        const u32 fe = (u32)P.filter_offsets[f] + r0;
-        act &= (P.filters[f] == vc.mask && fe == ve) ? vn : nibble_aligned(P.filters[f], fe);
-      }
-      u32 d0 = 0, d1 = 0, d2 = 0, d3 = 0, bad = 0;
-      // all key loads of the tile are issued before the first one is used (NKF is the compile-time
-      // number of key columns, so both loops unroll and the loads overlap in one DRAM round trip)
-      uint4 ka[NKF > 0 ? NKF : 1], kb[NKF > 0 ? NKF : 1];
-      u32 kn[NKF > 0 ? NKF : 1];
+      if (filt_is_val) act = vn;
+      else for (int f = 0; f < P.nfilters; ++f) act &= nibble_aligned(P.filters[f], (u32)P.filter_offsets[f] + r0);
+      uint4 ka[NK], kb[NK];
+      u32 kn[NK];
 #pragma unroll
-      for (int k = 0; k < NKF; ++k) {
+      for (int k = 0; k < NK; ++k) {
         const DKeyCol& c = P.keys[k];
         const u32 e = (u32)c.offset + r0;
-        kn[k] = 0xFu;
-        if (c.mask) kn[k] = nibble_aligned(c.mask, e);
-        if (c.width == 4) {
-          ka[k] = __ldg((const uint4*)(c.data + (u64)e * 4));
-          kb[k] = make_uint4(0, 0, 0, 0);
-        } else {
-          ka[k] = __ldg((const uint4*)(c.data + (u64)e * 8));
-          kb[k] = __ldg((const uint4*)(c.data + (u64)e * 8) + 1);
-        }
+        kn[k] = c.mask ? nibble_aligned(c.mask, e) : 0xFu;
+        const uint4* kp = (const uint4*)(c.data + (u64)e * (u32)c.width);
+        ka[k] = __ldg(kp);
+        if (c.width == 8) kb[k] = __ldg(kp + 1);
       }
+      // dense slots
+      u32 d0 = 0, d1 = 0, d2 = 0, d3 = 0, bad = 0;
 #pragma unroll
-      for (int k = 0; k < NKF; ++k) {
+      for (int k = 0; k < NK; ++k) {
         const DKeyCol& c = P.keys[k];
         if (c.mask && !P.include_nulls) act &= kn[k];
         const u32 mult = s_dense.mult[k];
@@ -375,39 +371,62 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
         bad |= o;
         d0 += x0 * mult; d1 += x1 * mult; d2 += x2 * mult; d3 += x3 * mult;
       }
-      const u32 ds[AGG_ROWS] = {d0, d1, d2, d3};
-      const float xs[AGG_ROWS] = {q.x, q.y, q.z, q.w};
-      const u32 ssum_a = (u32)__cvta_generic_to_shared(ssum), scnt_a = (u32)__cvta_generic_to_shared(scnt);
+      const u32 take = act & ~bad & vn;  // rows folded in shared memory
+#define B2_LEAN_FOLD(J, D, X)                                                                       \
+      if (take & (1u << J)) {                                                                       \
+        sred_add_f32(ssum_a + 4u * (D), (X));                                                       \
+        const u32 old = satom_add_u32(scnt_a + 4u * (D), 1u);                                       \
+        if (((old + 1u) & (F32_SPILL_AT - 1u)) == 0u) {                                             \
+          /* every F32_SPILL_AT-th addend moves the fp32 partial of this key to the fp64 global */  \
+          /* cell, so that no fp32 sum ever holds many more addends than that */                   \
+          const float part = atomicExch(ssum + (D), 0.f);                                           \
+          const u64 key = dense_key(P, s_dense, (D));                                               \
+          const i64 g   = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new); \
+          if (g >= 0) atomicAdd((double*)(tbl + g * stride + 1), (double)part);                     \
+        }                                                                                           \
+      }
+      B2_LEAN_FOLD(0, d0, q.x) B2_LEAN_FOLD(1, d1, q.y) B2_LEAN_FOLD(2, d2, q.z) B2_LEAN_FOLD(3, d3, q.w)
+#undef B2_LEAN_FOLD
+      // rare rows: active but (a) null value -> only mark the group as present, (b) key outside the box
+      const u32 rare = act & (bad | ~vn);
+      if (rare) {
+        const u32 ds[LEAN_ROWS]  = {d0, d1, d2, d3};
+        const float xs[LEAN_ROWS] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-      for (int j = 0; j < AGG_ROWS; ++j) {
-        if (!((act >> j) & 1u)) continue;
-        if (!((bad >> j) & 1u)) {
-          const u32 s = ds[j];
-          if (!((socc[s >> 5] >> (s & 31u)) & 1u)) atomicOr(&socc[s >> 5], 1u << (s & 31u));
-          ++my_hit;
-          if ((vn >> j) & 1u) {
-            sred_add_f32(ssum_a + 4u * s, xs[j]);
-            const u32 old = satom_add_u32(scnt_a + 4u * s, 1u);
-            if (((old + 1u) & (F32_SPILL_AT - 1u)) == 0u) {
-              const float part = atomicExch(ssum + s, 0.f);
-              const u64 key = dense_key(P, s_dense, s);
-              const i64 g   = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
-              if (g >= 0) atomicAdd((double*)(tbl + g * stride + 1), (double)part);
+        for (int j = 0; j < LEAN_ROWS; ++j) {  // unrolled: no dynamic indexing
+          if (!((rare >> j) & 1u)) continue;
+          if (!((bad >> j) & 1u)) {
+            const u32 s = ds[j];
+            if (!((socc[s >> 5] >> (s & 31u)) & 1u)) atomicOr(&socc[s >> 5], 1u << (s & 31u));
+          } else {
+            const u64 key = pack_key(P, (i64)r0 + j);
+            const i64 g   = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
+            ++my_miss;
+            if (g >= 0 && ((vn >> j) & 1u)) {
+              atomicAdd((double*)(tbl + g * stride + 1), (double)xs[j]);
+              atomicAdd(tbl + g * stride + 2, 1ull);
             }
-          }
-        } else {
-          // the sample missed this key: global table
-          const u64 key = pack_key(P, row0 + j);
-          const i64 g   = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
-          ++my_miss;
-          if (g >= 0 && ((vn >> j) & 1u)) {
-            atomicAdd((double*)(tbl + g * stride + 1), (double)xs[j]);
-            atomicAdd(tbl + g * stride + 2, 1ull);
           }
         }
       }
+      my_hit += __popc(act & ~bad);
+      if (tid == 0 && *(volatile int*)&s_new != 0) {
+        const int c = atomicExch(&s_new, 0);
+        const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)c) + (u64)c;
+        if (tot > ctrl->claim_limit) ctrl->overflow = 1;
+      }
     }
-    if (!handled) {
+  }
+
+  const i64 tile_rows = (i64)blockDim.x * AGG_ROWS;
+  const i64 ntiles    = (P.nrows - rows_done + tile_rows - 1) / tile_rows;
+
+  for (i64 tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    if (*(volatile int*)&s_abort) break;
+    const i64 row0 = rows_done + tile * tile_rows + (i64)tid * AGG_ROWS;
+    const int nv   = (int)max((i64)0, min((i64)AGG_ROWS, P.nrows - row0));
+    const bool cache_on = (LAYOUT != SL_NONE) && (dense || *(volatile int*)&s_cache_on);
+
     // ---- loads first, all independent of each other, so that one DRAM round trip covers the tile
     const bool full = nv == AGG_ROWS;
     const bool vec  = KM == KM_PACKED && full && (P.flags & PF_VEC_KEYS);
@@ -575,8 +594,6 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
       }
     }
 
-    }  // !handled
-
     // ---- bookkeeping by one lane per CTA, no barrier: claims, overflow, cache pay-off
     if (LAYOUT != SL_NONE && !dense) {
       const u32 wh = __reduce_add_sync(0xFFFFFFFFu, my_hit), wm = __reduce_add_sync(0xFFFFFFFFu, my_miss);
@@ -612,7 +629,9 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
     for (int i = tid; i < NS; i += blockDim.x) {
       u64 key;
       if (dense) {
-        if (!((socc[i >> 5] >> (i & 31)) & 1u)) continue;
+        // present = occupancy bit (set by rows with a null value / by the generic loop) or a count
+        const bool present = ((socc[i >> 5] >> (i & 31)) & 1u) || (LAYOUT == SL_F32MEAN && scnt[i] != 0u);
+        if (!present) continue;
         key = dense_key(P, s_dense, (u32)i);
       } else {
         key = skeys[i];
