@@ -144,3 +144,16 @@ class TorchAllocator:
 
     def adopt(self, ptr) -> Optional[torch.Tensor]:
         return None if not ptr else self.live.pop(ptr)
+
+
+_ALLOCATORS = {}
+
+
+def allocator_for(device) -> TorchAllocator:
+    """One allocator per device, reused across calls (building the ctypes callbacks is the
+    expensive part; the allocator itself only keeps the buffers of calls in flight)."""
+    key = str(device)
+    a = _ALLOCATORS.get(key)
+    if a is None:
+        a = _ALLOCATORS[key] = TorchAllocator(device)
+    return a

@@ -16,6 +16,7 @@
 //     An unused slot has key cell == EMPTY; the one packed key whose bits equal EMPTY lives in an
 //     extra slot at index `capacity`.
 #pragma once
+#include <cstddef>
 #include <cstdint>
 #include <cuda_runtime.h>
 

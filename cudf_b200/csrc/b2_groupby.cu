@@ -549,8 +549,8 @@ void alloc_table(b2_groupby_state& st, int64_t cap, double max_load, cudaStream_
   DCtrl h{};
   h.claim_limit = (u64)((double)cap * max_load);
   st.host_ctrl = h;
-  CUDA_TRY(cudaMemcpyAsync(st.ctrl, &st.host_ctrl, sizeof(DCtrl), cudaMemcpyHostToDevice, stream));
-  k_table_init<<<grid_for(cap + 1, 256, 16), 256, 0, stream>>>(st.table, cap + 1, st.plan);
+  static_assert(sizeof(DCtrl) / 4 <= 256, "the control block is initialised by one CTA of k_table_init");
+  k_table_init<<<grid_for(cap + 1, 256, 16), 256, 0, stream>>>(st.table, cap + 1, st.plan, st.ctrl, h.claim_limit);
   CUDA_TRY(cudaGetLastError());
   g_stats.kernel_launches++;
   g_stats.table_capacity = cap;
@@ -843,8 +843,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
 
   std::vector<u32> h_nulls(MAX_OUTS + MAX_KEYS, 0);
   if (G > 0) {
-    u64 zero = 0;
-    CUDA_TRY(cudaMemcpyAsync(&st.ctrl->out_cursor, &zero, sizeof(u64), cudaMemcpyHostToDevice, stream));
+    CUDA_TRY(cudaMemsetAsync(&st.ctrl->out_cursor, 0, sizeof(u64), stream));
     k_finalize<<<grid_for(st.cap + 1, 256, 8), 256, 0, stream>>>(st.plan, *plan, st.table, st.cap, st.ctrl);
     CUDA_TRY(cudaGetLastError());
     g_stats.kernel_launches++;
@@ -1038,7 +1037,7 @@ extern "C" b2_status b2_groupby_aggregate_noalloc(b2_groupby* gb, const b2_aggre
     CUDA_TRY(cudaMemcpyAsync(ctrl, &h, sizeof(DCtrl), cudaMemcpyHostToDevice, stream));
     CUDA_TRY(cudaMemsetAsync(null_counts, 0, nulls_bytes, stream));
     CUDA_TRY(cudaStreamSynchronize(stream));  // `h` is a stack object
-    k_table_init<<<grid_for(cap + 1, 256, 16), 256, 0, stream>>>(table, cap + 1, P);
+    k_table_init<<<grid_for(cap + 1, 256, 16), 256, 0, stream>>>(table, cap + 1, P, nullptr, 0);
     CUDA_TRY(cudaGetLastError());
     int64_t G = 0;
     if (P.nrows > 0) {

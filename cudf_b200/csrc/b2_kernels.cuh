@@ -32,8 +32,16 @@ constexpr int SLOT_NONE      = -1;
 enum SmemLayout : int { SL_NONE = 0, SL_GENERIC = 1, SL_F32MEAN = 2 };
 
 // ------------------------------------------------------------------------------ table init
-__global__ void k_table_init(u64* __restrict__ tbl, i64 nslots, const __grid_constant__ DPlan P)
+__global__ void k_table_init(u64* __restrict__ tbl, i64 nslots, const __grid_constant__ DPlan P, DCtrl* ctrl,
+                             u64 claim_limit)
 {
+  if (ctrl && blockIdx.x == 0 && threadIdx.x < sizeof(DCtrl) / 4) {
+    // a fresh control block: all zero except the claim limit
+    u32 v = 0;
+    if (threadIdx.x == offsetof(DCtrl, claim_limit) / 4) v = (u32)claim_limit;
+    if (threadIdx.x == offsetof(DCtrl, claim_limit) / 4 + 1) v = (u32)(claim_limit >> 32);
+    ((u32*)ctrl)[threadIdx.x] = v;
+  }
   const int stride = P.stride;
   for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s < nslots; s += (i64)gridDim.x * blockDim.x) {
     u64* slot = tbl + s * stride;
@@ -626,7 +634,10 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
   // ---- merge this CTA's table into the global table
   __syncthreads();
   if (LAYOUT != SL_NONE && !s_abort) {
-    for (int i = tid; i < NS; i += blockDim.x) {
+    // CTAs start their merge at different slots so that they do not all hit the same global cells at once
+    const int rot = (int)(((u64)blockIdx.x * 2654435761ull) % (u64)NS);
+    for (int i0 = tid; i0 < NS; i0 += blockDim.x) {
+      const int i = i0 + rot < NS ? i0 + rot : i0 + rot - NS;
       u64 key;
       if (dense) {
         // present = occupancy bit (set by rows with a null value / by the generic loop) or a count

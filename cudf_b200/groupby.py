@@ -14,7 +14,7 @@ import torch
 
 from . import _lib
 from .aggregation import Aggregation
-from .column import Column, Table, TorchAllocator
+from .column import Column, Table, TorchAllocator, allocator_for
 from .types import Kind, NullPolicy, TypeId
 
 
@@ -166,7 +166,7 @@ class GroupBy:
         lib = _lib.load()
         keep: list = []
         creqs = _requests_to_c(requests, keep)
-        alloc = TorchAllocator(self._device)
+        alloc = allocator_for(self._device)
         res = _lib.GroupbyResult()
         stream = torch.cuda.current_stream(self._device).cuda_stream
         _check(lib.b2_groupby_aggregate(self._handle, creqs, len(requests), C.c_void_p(stream),
@@ -220,7 +220,7 @@ class GroupByState:
         ptr = C.c_void_p()
         nbytes = C.c_size_t()
         counts = (C.c_int64 * num_parts)()
-        alloc = TorchAllocator(self._device)
+        alloc = allocator_for(self._device)
         _check(lib.b2_state_pack(self._handle, num_parts, self._stream(), C.byref(alloc.struct), C.byref(ptr),
                                  C.byref(nbytes), counts))
         buf = alloc.adopt(ptr.value)
@@ -241,7 +241,7 @@ class GroupByState:
 
     def finalize(self) -> Tuple[Table, List[Table]]:
         lib = _lib.load()
-        alloc = TorchAllocator(self._device)
+        alloc = allocator_for(self._device)
         res = _lib.GroupbyResult()
         _check(lib.b2_state_finalize(self._handle, self._stream(), C.byref(alloc.struct), C.byref(res)))
         return _adopt_result(res, alloc)
