@@ -198,6 +198,21 @@ def result_scales(keys, requests, null_policy, row_filters=(), row_filter_offset
     return out
 
 
+def reorder_scales(scales, from_keys, to_keys):
+    """Scales given in the group order of ``from_keys`` re-expressed in the group order of ``to_keys``
+    (same key set, different order)."""
+    of, ot = sort_order(from_keys), sort_order(to_keys)
+    out = []
+    for triple in scales:
+        new = []
+        for arr in triple:
+            a = np.empty_like(arr)
+            a[ot] = arr[of]
+            new.append(a)
+        out.append(tuple(new))
+    return out
+
+
 def _scale_for(kind, ddof, sa, ss, n):
     kind = Kind(kind)
     df = np.maximum(n - ddof, 1.0)
