@@ -35,6 +35,9 @@ import workloads  # noqa: E402
 
 METRIC = "groupby-aggregate rows/sec"
 FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per input row of k_aggregate on C2, from the ncu capture summarised in
+# profiles/k_aggregate_c2.md (20M-row case: (243.74 + 3.89) MB / 20M rows), scaled by the rows of a launch
+C2_TRAFFIC_BYTES_PER_ROW = 12.38
 
 
 def measured_peak():
@@ -300,7 +303,8 @@ def run_b2(args):
                     "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": (achieved / peak) if achieved else None, "traffic": None,
+                         "frac": (achieved / peak) if achieved else None,
+                         "traffic": (C2_TRAFFIC_BYTES_PER_ROW * w.rows) if args.config == 2 else None,
                          "kernel": "k_aggregate", "kernel_ms": kms, "peak_kind": f"of {peak_kind}",
                          "step_GBps": alg_bytes / (ms / args.steps / 1e3) / 1e9},
         }
