@@ -87,6 +87,9 @@ PROTOTYPES = {
     "b2_state_record_bytes": (C.c_int32, [C.c_void_p]),
     "b2_state_pack": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.POINTER(Allocator), C.POINTER(C.c_void_p),
                             C.POINTER(C.c_size_t), C.POINTER(C.c_int64)]),
+    "b2_state_chunk_bytes": (C.c_int64, [C.c_void_p, C.c_int64]),
+    "b2_state_pack_chunks": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p]),
+    "b2_state_merge_chunks": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p]),
     "b2_state_merge": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "b2_state_reset": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p]),
     "b2_state_num_groups": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]),

@@ -117,6 +117,7 @@ struct DCtrl {
   u64 stat_smem_rows;
   u64 stat_gmem_rows;
   u64 reserved;
+  u64 chunk_overflow;  // a sender of merged chunks had more records than a chunk holds
   DDense dense;
 };
 

@@ -786,6 +786,8 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
   OwnedGuard guard{out};
 
   read_ctrl(st, stream);
+  if (st.table && st.host_ctrl.chunk_overflow) B2_FAIL(B2_LOGIC_ERROR, "partial-record chunk overflow");
+  if (st.table && st.host_ctrl.overflow) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow while merging partial records");
   const int64_t G = st.table ? num_groups(st) : 0;
   if (G > 0x7FFFFFFFll) B2_FAIL(B2_UNSUPPORTED, "more than 2^31-1 groups");
   out->num_groups = (int32_t)G;
@@ -1205,6 +1207,59 @@ b2_status b2_state_pack(b2_groupby_state* st, int32_t num_parts, void* stream, c
   });
 }
 
+int64_t b2_state_chunk_bytes(const b2_groupby_state* st, int64_t chunk_records)
+{
+  return st ? 16 + chunk_records * (int64_t)st->plan.stride * 8 : 0;
+}
+
+b2_status b2_state_pack_chunks(b2_groupby_state* st, int32_t num_parts, int64_t chunk_records, void* stream_, void* out)
+{
+  return guarded([&] {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!st || !out || num_parts < 1 || num_parts > 4096 || chunk_records < 1) B2_FAIL(B2_INVALID_ARGUMENT, "bad argument");
+    if (st->sc.key_mode != KM_PACKED)
+      B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys are not transferable; partition the rows instead");
+    device_info();
+    const int64_t chunk_words = 2 + chunk_records * st->plan.stride;
+    if (!st->table) {  // no groups: empty chunks
+      for (int p = 0; p < num_parts; ++p)
+        CUDA_TRY(cudaMemsetAsync((u64*)out + p * chunk_words, 0, 16, stream));
+      return;
+    }
+    Scratch dcounts((size_t)num_parts * 2 * sizeof(u64), stream);
+    CUDA_TRY(cudaMemsetAsync(dcounts.p, 0, dcounts.bytes, stream));
+    u64* d_counts = (u64*)dcounts.p;
+    const int grid = grid_for(st->cap + 1, 256, 8);
+    k_pack_count<<<grid, 256, (size_t)num_parts * sizeof(u64), stream>>>(st->table, st->cap, st->plan.stride, num_parts,
+                                                                           st->ctrl, d_counts);
+    k_pack_chunks<<<grid, 256, 0, stream>>>(st->table, st->cap, st->plan.stride, num_parts, st->ctrl, d_counts,
+                                            d_counts + num_parts, (u64*)out, chunk_records);
+    CUDA_TRY(cudaGetLastError());
+    g_stats.kernel_launches += 2;
+  });
+}
+
+b2_status b2_state_merge_chunks(b2_groupby_state* st, const void* chunks, int32_t num_chunks, int64_t chunk_records,
+                                void* stream_)
+{
+  return guarded([&] {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!st || !chunks || num_chunks < 1 || chunk_records < 1) B2_FAIL(B2_INVALID_ARGUMENT, "bad argument");
+    if (st->sc.key_mode != KM_PACKED)
+      B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys are not transferable; partition the rows instead");
+    if (st->table) B2_FAIL(B2_LOGIC_ERROR, "b2_state_merge_chunks needs an empty state");
+    device_info();
+    st->last_stream = stream;
+    const int64_t worst = (int64_t)num_chunks * chunk_records;
+    alloc_table(*st, std::max<int64_t>(1024, (int64_t)((double)worst / 0.6) + 64), 1.0, stream);
+    k_merge_chunks<<<grid_for(worst, 256, 8), 256, 0, stream>>>(st->plan, st->table, st->cap, st->ctrl,
+                                                                (const u64*)chunks, num_chunks, chunk_records);
+    CUDA_TRY(cudaGetLastError());
+    g_stats.kernel_launches++;
+    st->ctrl_fresh = false;
+  });
+}
+
 b2_status b2_state_merge(b2_groupby_state* st, const void* records, int64_t num_records, void* stream)
 {
   return guarded([&] {
@@ -1234,6 +1289,7 @@ b2_status b2_state_num_groups(b2_groupby_state* st, void* stream, int64_t* out)
     *out = 0;
     if (!st->table) return;
     read_ctrl(*st, (cudaStream_t)stream);
+    if (st->host_ctrl.chunk_overflow) B2_FAIL(B2_LOGIC_ERROR, "partial-record chunk overflow");
     *out = num_groups(*st);
   });
 }

@@ -936,6 +936,71 @@ __global__ void k_pack_scatter(const u64* __restrict__ tbl, i64 cap, int stride,
   }
 }
 
+// fixed-size chunks: chunk d = { count, overflow, records[chunk_records] }
+__global__ void k_pack_chunks(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, const DCtrl* ctrl,
+                              const u64* __restrict__ counts, u64* __restrict__ cursors /* zeroed */,
+                              u64* __restrict__ out, i64 chunk_records)
+{
+  __shared__ int s_over;
+  if (threadIdx.x == 0) s_over = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < nparts; p += blockDim.x)
+    if (counts[p] > (u64)chunk_records) s_over = 1;
+  __syncthreads();
+  const bool over = s_over != 0;
+  const i64 chunk_words = 2 + chunk_records * stride;
+  if (blockIdx.x == 0)
+    for (int p = threadIdx.x; p < nparts; p += blockDim.x) {
+      out[p * chunk_words]     = over ? 0ull : counts[p];
+      out[p * chunk_words + 1] = over ? 1ull : 0ull;
+    }
+  if (over) return;
+  for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s <= cap; s += (i64)gridDim.x * blockDim.x) {
+    const u64 key = s < cap ? tbl[s * stride] : EMPTY;
+    const bool occ = s < cap ? key != EMPTY : ctrl->special_used != 0;
+    if (!occ) continue;
+    const u32 p   = owner_of(mix64(key), (u32)nparts);
+    const u64 pos = atomicAdd(&cursors[p], 1ull);
+    u64* dst = out + p * chunk_words + 2 + pos * stride;
+    const u64* src = tbl + s * stride;
+    dst[0] = key;
+    for (int c = 1; c < stride; ++c) dst[c] = src[c];
+  }
+}
+
+__global__ void __launch_bounds__(256)
+k_merge_chunks(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* ctrl,
+               const u64* __restrict__ chunks, int nchunks, i64 chunk_records)
+{
+  __shared__ int s_new;
+  if (threadIdx.x == 0) s_new = 0;
+  __syncthreads();
+  const int stride = P.stride;
+  const i64 chunk_words = 2 + chunk_records * stride;
+  const i64 total = (i64)nchunks * chunk_records;
+  for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (i64)gridDim.x * blockDim.x) {
+    const i64 c = i / chunk_records, r = i - c * chunk_records;
+    const u64* chunk = chunks + c * chunk_words;
+    if (r == 0 && chunk[1] != 0) ctrl->chunk_overflow = 1;
+    if ((u64)r >= chunk[0] || chunk[1] != 0) continue;
+    const u64* rec = chunk + 2 + r * stride;
+    const u64 key  = rec[0];
+    const i64 g    = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
+    if (g < 0) continue;
+    u64* slot = tbl + g * stride;
+    for (int k = 0; k < P.ncells; ++k) {
+      const int op = P.cells[k].op;
+      const u64 a  = rec[1 + k];
+      if (a != cell_identity(op)) cell_merge(slot + 1 + k, op, a);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && s_new) {
+    const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)s_new) + (u64)s_new;
+    if (tot > ctrl->claim_limit) ctrl->overflow = 1;
+  }
+}
+
 // merge packed partial records into a table (packed keys)
 __global__ void __launch_bounds__(256)
 k_merge(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* ctrl, const u64* __restrict__ recs,

@@ -83,10 +83,26 @@ class DistributedGroupBy:
             return self._aggregate_partials(requests, world)
         return self._aggregate_rows(requests, world)
 
+    # records per destination of the fixed-size exchange (one all-to-all, no host round trip)
+    CHUNK_RECORDS = 16384
+
     def _aggregate_partials(self, requests, world):
-        from .groupby import GroupByState
+        from .groupby import GroupByState, LogicError
         st = GroupByState(self._gb, requests)
         st.update()
+        if st.chunk_bytes(self.CHUNK_RECORDS) * world <= (64 << 20):
+            # small states: equal-split all-to-all of fixed chunks; a sender with too many records
+            # marks every chunk it sends, so all ranks take the fallback below together
+            send = st.pack_chunks(world, self.CHUNK_RECORDS)
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send, group=self._group)
+            merged = GroupByState(self._gb, requests)
+            merged.merge_chunks(recv, world, self.CHUNK_RECORDS)
+            try:
+                return merged.finalize()
+            except LogicError as e:
+                if "chunk overflow" not in str(e):
+                    raise
         records, counts = st.pack(world)
         recv, nrecv = exchange_records(records, counts, st.record_bytes, self._group)
         st.reset(expected_groups=max(nrecv, 1))

@@ -226,6 +226,22 @@ class GroupByState:
         buf = alloc.adopt(ptr.value)
         return buf[:nbytes.value], [int(c) for c in counts]
 
+    def chunk_bytes(self, chunk_records: int) -> int:
+        return int(_lib.load().b2_state_chunk_bytes(self._handle, int(chunk_records)))
+
+    def pack_chunks(self, num_parts: int, chunk_records: int) -> torch.Tensor:
+        """Fixed-size partition of the partial records (one chunk per destination, no host sync)."""
+        out = torch.empty(num_parts * self.chunk_bytes(chunk_records), dtype=torch.uint8, device=self._device)
+        _check(_lib.load().b2_state_pack_chunks(self._handle, num_parts, int(chunk_records), self._stream(),
+                                                C.c_void_p(out.data_ptr())))
+        return out
+
+    def merge_chunks(self, chunks: torch.Tensor, num_chunks: int, chunk_records: int):
+        chunks = chunks.contiguous()
+        self._chunks_keepalive = chunks
+        _check(_lib.load().b2_state_merge_chunks(self._handle, C.c_void_p(chunks.data_ptr()), int(num_chunks),
+                                                 int(chunk_records), self._stream()))
+
     def merge(self, records: torch.Tensor, num_records: int):
         lib = _lib.load()
         records = records.contiguous()

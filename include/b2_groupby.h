@@ -210,6 +210,22 @@ b2_status b2_state_pack(b2_groupby_state* st, int32_t num_parts, void* stream,
                         const b2_allocator* allocator, void** records_out, size_t* records_bytes,
                         int64_t* counts);
 
+/* Fixed-size form of the same partition for small states: no host round trip.  The records of
+ * destination d go to chunk d of `out` (device memory, num_parts * b2_state_chunk_bytes()):
+ * chunk = { uint64 count, uint64 overflow, records[chunk_records] }.  If any destination holds more
+ * than `chunk_records` records, every chunk carries overflow = 1 and no records, so that all
+ * receivers of an all-to-all with equal splits learn it and the caller falls back to
+ * b2_state_pack.  Enqueues on `stream` without synchronising it. */
+int64_t b2_state_chunk_bytes(const b2_groupby_state* st, int64_t chunk_records);
+b2_status b2_state_pack_chunks(b2_groupby_state* st, int32_t num_parts, int64_t chunk_records,
+                               void* stream, void* out);
+
+/* Merges `num_chunks` received chunks into an EMPTY state.  Does not synchronise; a sender's
+ * overflow mark surfaces as B2_LOGIC_ERROR "partial-record chunk overflow" from the next
+ * b2_state_finalize / b2_state_num_groups on this state. */
+b2_status b2_state_merge_chunks(b2_groupby_state* st, const void* chunks, int32_t num_chunks,
+                                int64_t chunk_records, void* stream);
+
 /* Merges `num_records` packed records (device memory, any origin with the same schema) into
  * the state: streaming_groupby::merge (groupby.hpp:548-556). */
 b2_status b2_state_merge(b2_groupby_state* st, const void* records, int64_t num_records,

@@ -175,3 +175,50 @@ def test_rows_strategy_matches_partials_on_emulated_ranks():
     got = _concat(parts)
     exp = oracle.groupby(w.keys, w.requests)
     H.assert_same_result(got, exp, w.requests)
+
+
+@pytest.mark.parametrize("ranks", [2, 8])
+def test_fixed_chunk_exchange_equals_one_shot(ranks):
+    """pack_chunks / merge_chunks (the equal-split all-to-all form) on emulated ranks."""
+    import torch
+    import cudf_b200 as cb
+    n, chunk = 160_000, 8192
+    w = workloads.make(2, n)
+    reqs = [(v, AGGS) for v, _ in w.requests]
+    sent, keep = [], []
+    for r in range(ranks):
+        gb, dreqs = _device_objects(w.keys, reqs, w.null_policy, r * n // ranks, (r + 1) * n // ranks)
+        st = cb.GroupByState(gb, dreqs)
+        st.update()
+        sent.append(st.pack_chunks(ranks, chunk))
+        keep.append((st, gb, dreqs))
+    cb_bytes = keep[0][0].chunk_bytes(chunk)
+    parts = []
+    for dst in range(ranks):
+        recv = torch.cat([s[dst * cb_bytes:(dst + 1) * cb_bytes] for s in sent])  # what all_to_all delivers
+        _, gb, dreqs = keep[dst]
+        merged = cb.GroupByState(gb, dreqs)
+        merged.merge_chunks(recv, ranks, chunk)
+        parts.append(_to_host(merged.finalize()))
+    got = _concat(parts)
+    exp = oracle.groupby(w.keys, reqs, w.null_policy)
+    H.assert_same_result(got, exp, reqs, scales=H.result_scales(w.keys, reqs, w.null_policy))
+
+
+def test_fixed_chunk_overflow_is_reported_to_every_receiver():
+    import torch
+    import cudf_b200 as cb
+    n = 50_000
+    w = workloads.make(2, n)
+    reqs = [(v, [Kind.SUM]) for v, _ in w.requests]
+    gb, dreqs = _device_objects(w.keys, reqs, w.null_policy, 0, n)
+    st = cb.GroupByState(gb, dreqs)
+    st.update()
+    ranks, chunk = 4, 64   # ~2500 groups per destination do not fit 64 records
+    send = st.pack_chunks(ranks, chunk)
+    cbytes = st.chunk_bytes(chunk)
+    for dst in range(ranks):
+        merged = cb.GroupByState(gb, dreqs)
+        merged.merge_chunks(send[dst * cbytes:(dst + 1) * cbytes].clone(), 1, chunk)
+        with pytest.raises(cb.LogicError, match="chunk overflow"):
+            merged.finalize()
