@@ -101,7 +101,10 @@ enum PlanFlags : int {
 // sample missed them) take the global-table path, so the result stays exact.
 struct DDense {
   int enabled;
-  u32 total;               // slots = product of ranges
+  u32 total;               // slots of one copy = product of ranges
+  u32 copies;              // replicas of the table in shared memory (warp w uses copy w % copies):
+                           // few groups mean many rows per slot, and same-address atomics serialise
+  u32 pad;
   i64 min[MAX_KEYS];
   u64 range[MAX_KEYS];     // includes one extra value for "null" on nullable INCLUDE columns
   u32 mult[MAX_KEYS];

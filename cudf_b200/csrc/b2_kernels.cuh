@@ -218,6 +218,8 @@ __global__ void __launch_bounds__(1024) k_sample_ranges(const __grid_constant__ 
     DDense D;
     D.enabled = 0;
     D.total   = 0;
+    D.copies  = 1;
+    D.pad     = 0;
     bool ok   = P.key_mode == KM_PACKED && nsamp >= SAMPLE_ROWS && cap_slots > 0;
     for (int pass = 0; pass < 2 && ok && !D.enabled; ++pass) {  // pass 0: padded box, pass 1: tight box
       u64 total = 1;
@@ -235,7 +237,12 @@ __global__ void __launch_bounds__(1024) k_sample_ranges(const __grid_constant__ 
         total *= D.range[k];
         if (total > (u64)cap_slots) fits = false;
       }
-      if (fits) { D.enabled = 1; D.total = (u32)total; }
+      if (fits) {
+        D.enabled = 1;
+        D.total   = (u32)total;
+        const u32 r = cap_slots / (u32)total;
+        D.copies  = r < 1 ? 1u : (r > 32u ? 32u : r);
+      }
     }
     ctrl->dense = D;
   }
@@ -287,7 +294,9 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
   __syncthreads();
   const bool dense = (LAYOUT != SL_NONE) && KM == KM_PACKED && s_dense.enabled;
   const int S      = dense ? (int)s_dense.total : S_hash;  // slots (hashed mode: + the special slot at S)
-  const int NS     = dense ? S : S + 1;                    // allocated slots per array
+  const int NS     = dense ? S * (int)s_dense.copies : S + 1;  // allocated slots per array
+  // dense mode: this warp's replica of the table
+  const u32 copy_off = dense ? (u32)((threadIdx.x >> 5) % s_dense.copies) * (u32)S : 0u;
 
   // shared-memory arrays
   u64* skeys  = (u64*)smem_raw;                            // hashed mode only: [NS]
@@ -348,7 +357,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
         if (c.width == 8) kb[k] = __ldg(kp + 1);
       }
       // dense slots
-      u32 d0 = 0, d1 = 0, d2 = 0, d3 = 0, bad = 0;
+      u32 d0 = copy_off, d1 = copy_off, d2 = copy_off, d3 = copy_off, bad = 0;
 #pragma unroll
       for (int k = 0; k < NK; ++k) {
         const DKeyCol& c = P.keys[k];
@@ -388,7 +397,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
           /* every F32_SPILL_AT-th addend moves the fp32 partial of this key to the fp64 global */  \
           /* cell, so that no fp32 sum ever holds many more addends than that */                   \
           const float part = atomicExch(ssum + (D), 0.f);                                           \
-          const u64 key = dense_key(P, s_dense, (D));                                               \
+          const u64 key = dense_key(P, s_dense, (D) - copy_off);                                    \
           const i64 g   = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new); \
           if (g >= 0) atomicAdd((double*)(tbl + g * stride + 1), (double)part);                     \
         }                                                                                           \
@@ -444,7 +453,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
     u32 di[AGG_ROWS];   // dense mode: slot inside the key box
     u32 dout = 0;       // dense mode: rows whose key lies outside the box
 #pragma unroll
-    for (int j = 0; j < AGG_ROWS; ++j) { sl[j] = SLOT_NONE; kk[j] = 0; di[j] = 0; }
+    for (int j = 0; j < AGG_ROWS; ++j) { sl[j] = SLOT_NONE; kk[j] = 0; di[j] = copy_off; }
     float fx[AGG_ROWS] = {0.f, 0.f, 0.f, 0.f};  // SL_F32MEAN: the values
     u32 fvn = 0xFu;                              // SL_F32MEAN: their validity
     if (LAYOUT == SL_F32MEAN && full && (P.flags & PF_VEC_VAL0)) {
@@ -507,7 +516,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
             kk[j] = (KM == KM_PACKED) ? pack_key(P, row0 + j) : hash_row(P, row0 + j);
             if (dense) {
               const int s = dense_index(P, s_dense, kk[j]);
-              if (s < 0) dout |= 1u << j; else di[j] = (u32)s;
+              if (s < 0) dout |= 1u << j; else di[j] = copy_off + (u32)s;
             }
           }
       }
@@ -565,7 +574,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
               // every F32_SPILL_AT-th addend moves the fp32 partial of this key to the fp64 global
               // cell, so that no fp32 sum ever holds many more addends than that
               const float part = atomicExch(ssum + sl[j], 0.f);
-              const u64 key = dense ? dense_key(P, s_dense, (u32)sl[j]) : (sl[j] == S ? EMPTY : skeys[sl[j]]);
+              const u64 key = dense ? dense_key(P, s_dense, (u32)sl[j] - copy_off) : (sl[j] == S ? EMPTY : skeys[sl[j]]);
               const i64 g   = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
               if (g >= 0) atomicAdd((double*)(tbl + g * stride + 1), (double)part);
             }
@@ -643,7 +652,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
         // present = occupancy bit (set by rows with a null value / by the generic loop) or a count
         const bool present = ((socc[i >> 5] >> (i & 31)) & 1u) || (LAYOUT == SL_F32MEAN && scnt[i] != 0u);
         if (!present) continue;
-        key = dense_key(P, s_dense, (u32)i);
+        key = dense_key(P, s_dense, (u32)(i % S));
       } else {
         key = skeys[i];
         if (key == EMPTY) continue;
