@@ -14,7 +14,9 @@
 //                     key, cpp/src/groupby/hash/helpers.cuh:87-93,
 //                     cpp/include/cudf/detail/row_operator/equality.cuh:59-89).
 //     An unused slot has key cell == EMPTY; the one packed key whose bits equal EMPTY lives in an
-//     extra slot at index `capacity`.
+//     extra slot at index `capacity`.  Behind it an optional dense region of `dense_slots` slots is
+//     addressed directly by a key's position in the sampled key box (no probing): the CTAs merge
+//     their dense shared-memory tables into it with coalesced atomics.
 #pragma once
 #include <cstddef>
 #include <cstdint>
@@ -121,6 +123,7 @@ struct DCtrl {
   u64 stat_gmem_rows;
   u64 reserved;
   u64 chunk_overflow;  // a sender of merged chunks had more records than a chunk holds
+  u64 dense_slots;     // slots after the special slot that are addressed directly by dense-box position
   DDense dense;
 };
 
@@ -363,6 +366,24 @@ __device__ __forceinline__ void cell_update(u64* cell, int op, u64 v)
       break;
     }
     default: break;
+  }
+}
+
+// partial (+) partial in registers: the operator cell_merge applies atomically
+__device__ __forceinline__ u64 cell_combine(int op, u64 a, u64 b)
+{
+  switch (op) {
+    case OP_SUM_I: case OP_SSQ_I: case OP_CNT_V: case OP_CNT_A: return a + b;
+    case OP_SUM_F: case OP_SSQ_F:
+      return (u64)__double_as_longlong(__longlong_as_double((i64)a) + __longlong_as_double((i64)b));
+    case OP_MIN_I: return (i64)a < (i64)b ? a : b;
+    case OP_MIN_U: case OP_MIN_F: return a < b ? a : b;
+    case OP_MAX_I: return (i64)a > (i64)b ? a : b;
+    case OP_MAX_U: case OP_MAX_F: return a > b ? a : b;
+    case OP_PROD_I: return a * b;
+    case OP_PROD_F:
+      return (u64)__double_as_longlong(__longlong_as_double((i64)a) * __longlong_as_double((i64)b));
+    default: return a;
   }
 }
 

@@ -270,6 +270,7 @@ struct b2_groupby_state {
   DPlan plan{};          // schema part filled; pointers filled per update
   u64* table = nullptr;  // (cap + 1) * stride cells
   int64_t cap = 0;
+  int64_t dense_slots = 0;  // directly addressed slots behind the special slot
   DCtrl* ctrl = nullptr;
   DCtrl host_ctrl{};     // last read-back
   bool ctrl_fresh = false;
@@ -533,11 +534,14 @@ void free_table(b2_groupby_state& st, cudaStream_t stream)
   st.cap = 0;
 }
 
-void alloc_table(b2_groupby_state& st, int64_t cap, double max_load, cudaStream_t stream)
+constexpr int64_t DENSE_REGION_SLOTS = 32768;  // >= the largest dense box the shared memory can hold
+
+void alloc_table(b2_groupby_state& st, int64_t cap, double max_load, cudaStream_t stream, bool dense_region = false)
 {
   free_table(st, stream);
   if (cap > 0x7FFFFFF0ll) B2_FAIL(B2_UNSUPPORTED, "hash table would need more than 2^31 slots");
-  const size_t bytes = (size_t)(cap + 1) * (size_t)st.plan.stride * 8;
+  st.dense_slots = (dense_region && st.sc.key_mode == KM_PACKED) ? DENSE_REGION_SLOTS : 0;
+  const size_t bytes = (size_t)(cap + 1 + st.dense_slots) * (size_t)st.plan.stride * 8;
   st.table = (u64*)default_alloc(bytes, stream, nullptr);
   if (!st.table) B2_FAIL(B2_OUT_OF_MEMORY, "out of device memory allocating a " + std::to_string(bytes) + "-byte hash table");
   g_stats.scratch_bytes += (int64_t)bytes;
@@ -550,7 +554,10 @@ void alloc_table(b2_groupby_state& st, int64_t cap, double max_load, cudaStream_
   h.claim_limit = (u64)((double)cap * max_load);
   st.host_ctrl = h;
   static_assert(sizeof(DCtrl) / 4 <= 256, "the control block is initialised by one CTA of k_table_init");
-  k_table_init<<<grid_for(cap + 1, 256, 16), 256, 0, stream>>>(st.table, cap + 1, st.plan, st.ctrl, h.claim_limit);
+  h.dense_slots = (u64)st.dense_slots;
+  st.host_ctrl = h;
+  k_table_init<<<grid_for(cap + 1 + st.dense_slots, 256, 16), 256, 0, stream>>>(st.table, cap + 1 + st.dense_slots, st.plan, st.ctrl,
+                                                                                  h.claim_limit, h.dense_slots);
   CUDA_TRY(cudaGetLastError());
   g_stats.kernel_launches++;
   g_stats.table_capacity = cap;
@@ -615,7 +622,7 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
       smem = (size_t)budget;
       // dense mode: accumulators + one occupancy bit per slot
       if (sc.key_mode == KM_PACKED && gb.table_variant != 3)
-        cap_dense = (u32)(((int64_t)budget - 64) * 8 / ((int64_t)cell_bytes * 8 + 1));
+        cap_dense = (u32)std::min<int64_t>(st.dense_slots, ((int64_t)budget - 64) * 8 / ((int64_t)cell_bytes * 8 + 1));
     }
   }
   g_stats.used_shared_table = layout != SL_NONE;
@@ -661,7 +668,7 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
   else cap = SPECULATIVE_CAP;
   for (int attempt = 1;; ++attempt) {
     g_stats.table_attempts = attempt;
-    alloc_table(st, cap, cap >= full ? 1.0 : MAX_LOAD, stream);
+    alloc_table(st, cap, cap >= full ? 1.0 : MAX_LOAD, stream, gb.table_variant != 1 && gb.table_variant != 3);
     run_aggregate(st, gb, stream);
     read_ctrl(st, stream);
     {
@@ -688,7 +695,7 @@ void pack_table(b2_groupby_state& st, int nparts, cudaStream_t stream, Scratch& 
   CUDA_TRY(cudaMemsetAsync(dcounts.p, 0, dcounts.bytes, stream));
   u64* d_counts = (u64*)dcounts.p;
   u64* d_cursor = d_counts + nparts;
-  const int grid = grid_for(st.cap + 1, 256, 8);
+  const int grid = grid_for(st.cap + 1 + st.dense_slots, 256, 8);
   k_pack_count<<<grid, 256, (size_t)nparts * sizeof(u64), stream>>>(st.table, st.cap, st.plan.stride, nparts, st.ctrl, d_counts);
   CUDA_TRY(cudaGetLastError());
   std::vector<u64> h((size_t)nparts);
@@ -846,7 +853,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
   std::vector<u32> h_nulls(MAX_OUTS + MAX_KEYS, 0);
   if (G > 0) {
     CUDA_TRY(cudaMemsetAsync(&st.ctrl->out_cursor, 0, sizeof(u64), stream));
-    k_finalize<<<grid_for(st.cap + 1, 256, 8), 256, 0, stream>>>(st.plan, *plan, st.table, st.cap, st.ctrl);
+    k_finalize<<<grid_for(st.cap + 1 + st.dense_slots, 256, 8), 256, 0, stream>>>(st.plan, *plan, st.table, st.cap, st.ctrl);
     CUDA_TRY(cudaGetLastError());
     g_stats.kernel_launches++;
 
@@ -1229,7 +1236,7 @@ b2_status b2_state_pack_chunks(b2_groupby_state* st, int32_t num_parts, int64_t 
     Scratch dcounts((size_t)num_parts * 2 * sizeof(u64), stream);
     CUDA_TRY(cudaMemsetAsync(dcounts.p, 0, dcounts.bytes, stream));
     u64* d_counts = (u64*)dcounts.p;
-    const int grid = grid_for(st->cap + 1, 256, 8);
+    const int grid = grid_for(st->cap + 1 + st->dense_slots, 256, 8);
     k_pack_count<<<grid, 256, (size_t)num_parts * sizeof(u64), stream>>>(st->table, st->cap, st->plan.stride, num_parts,
                                                                            st->ctrl, d_counts);
     k_pack_chunks<<<grid, 256, 0, stream>>>(st->table, st->cap, st->plan.stride, num_parts, st->ctrl, d_counts,

@@ -33,13 +33,14 @@ enum SmemLayout : int { SL_NONE = 0, SL_GENERIC = 1, SL_F32MEAN = 2 };
 
 // ------------------------------------------------------------------------------ table init
 __global__ void k_table_init(u64* __restrict__ tbl, i64 nslots, const __grid_constant__ DPlan P, DCtrl* ctrl,
-                             u64 claim_limit)
+                             u64 claim_limit, u64 dense_slots = 0)
 {
   if (ctrl && blockIdx.x == 0 && threadIdx.x < sizeof(DCtrl) / 4) {
     // a fresh control block: all zero except the claim limit
     u32 v = 0;
     if (threadIdx.x == offsetof(DCtrl, claim_limit) / 4) v = (u32)claim_limit;
     if (threadIdx.x == offsetof(DCtrl, claim_limit) / 4 + 1) v = (u32)(claim_limit >> 32);
+    if (threadIdx.x == offsetof(DCtrl, dense_slots) / 4) v = (u32)dense_slots;
     ((u32*)ctrl)[threadIdx.x] = v;
   }
   const int stride = P.stride;
@@ -297,6 +298,9 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
   const int NS     = dense ? S * (int)s_dense.copies : S + 1;  // allocated slots per array
   // dense mode: this warp's replica of the table
   const u32 copy_off = dense ? (u32)((threadIdx.x >> 5) % s_dense.copies) * (u32)S : 0u;
+  // global slot of dense-box position i: the dense region behind the special slot (the one key whose
+  // bits equal EMPTY cannot mark a key cell as used and goes to the special slot instead)
+  auto dense_gslot = [&](u32 i) -> i64 { return dense_key(P, s_dense, i) == EMPTY ? cap : cap + 1 + (i64)i; };
 
   // shared-memory arrays
   u64* skeys  = (u64*)smem_raw;                            // hashed mode only: [NS]
@@ -397,9 +401,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
           /* every F32_SPILL_AT-th addend moves the fp32 partial of this key to the fp64 global */  \
           /* cell, so that no fp32 sum ever holds many more addends than that */                   \
           const float part = atomicExch(ssum + (D), 0.f);                                           \
-          const u64 key = dense_key(P, s_dense, (D) - copy_off);                                    \
-          const i64 g   = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new); \
-          if (g >= 0) atomicAdd((double*)(tbl + g * stride + 1), (double)part);                     \
+          atomicAdd((double*)(tbl + dense_gslot((D) - copy_off) * stride + 1), (double)part);       \
         }                                                                                           \
       }
       B2_LEAN_FOLD(0, d0, q.x) B2_LEAN_FOLD(1, d1, q.y) B2_LEAN_FOLD(2, d2, q.z) B2_LEAN_FOLD(3, d3, q.w)
@@ -574,8 +576,13 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
               // every F32_SPILL_AT-th addend moves the fp32 partial of this key to the fp64 global
               // cell, so that no fp32 sum ever holds many more addends than that
               const float part = atomicExch(ssum + sl[j], 0.f);
-              const u64 key = dense ? dense_key(P, s_dense, (u32)sl[j] - copy_off) : (sl[j] == S ? EMPTY : skeys[sl[j]]);
-              const i64 g   = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
+              i64 g;
+              if (dense) {
+                g = dense_gslot((u32)sl[j] - copy_off);
+              } else {
+                const u64 key = sl[j] == S ? EMPTY : skeys[sl[j]];
+                g = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
+              }
               if (g >= 0) atomicAdd((double*)(tbl + g * stride + 1), (double)part);
             }
           } else {
@@ -644,20 +651,49 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
   __syncthreads();
   if (LAYOUT != SL_NONE && !s_abort) {
     // CTAs start their merge at different slots so that they do not all hit the same global cells at once
-    const int rot = (int)(((u64)blockIdx.x * 2654435761ull) % (u64)NS);
-    for (int i0 = tid; i0 < NS; i0 += blockDim.x) {
-      const int i = i0 + rot < NS ? i0 + rot : i0 + rot - NS;
-      u64 key;
+    const int NM  = dense ? S : NS;  // dense mode: one pass over box positions, replicas reduced on the fly
+    const int rot = (int)(((u64)blockIdx.x * 2654435761ull) % (u64)NM);
+    for (int i0 = tid; i0 < NM; i0 += blockDim.x) {
+      const int i = i0 + rot < NM ? i0 + rot : i0 + rot - NM;
       if (dense) {
-        // present = occupancy bit (set by rows with a null value / by the generic loop) or a count
-        const bool present = ((socc[i >> 5] >> (i & 31)) & 1u) || (LAYOUT == SL_F32MEAN && scnt[i] != 0u);
+        // reduce the replicas of box position i in registers, then ONE merge into the dense region of
+        // the global table: no hashing, consecutive threads -> consecutive slots
+        const int copies = (int)s_dense.copies;
+        bool present = false;
+        for (int r = 0; r < copies; ++r) {
+          const int q = r * S + i;
+          present = present || ((socc[q >> 5] >> (q & 31)) & 1u) || (LAYOUT == SL_F32MEAN && scnt[q] != 0u);
+        }
         if (!present) continue;
-        key = dense_key(P, s_dense, (u32)(i % S));
-      } else {
-        key = skeys[i];
-        if (key == EMPTY) continue;
-        if (i == S) key = EMPTY;  // the special slot holds the key whose bits equal EMPTY
+        const u64 key = dense_key(P, s_dense, (u32)i);
+        i64 g;
+        if (key == EMPTY) {
+          g = cap;
+          if (ctrl->special_used == 0) ctrl->special_used = 1;
+        } else {
+          g = cap + 1 + (i64)i;
+          u64* kp = tbl + g * stride;
+          if (*(volatile u64*)kp == EMPTY && atomicCAS(kp, EMPTY, key) == EMPTY) atomicAdd(&s_new, 1);
+        }
+        u64* slot = tbl + g * stride;
+        if (LAYOUT == SL_F32MEAN) {
+          double sum = 0.0;
+          u64 n = 0;
+          for (int r = 0; r < copies; ++r) { sum += (double)ssum[r * S + i]; n += scnt[r * S + i]; }
+          if (n) { atomicAdd((double*)(slot + 1), sum); atomicAdd(slot + 2, n); }
+        } else {
+          for (int c = 0; c < P.ncells; ++c) {
+            const int op = P.cells[c].op;
+            u64 a = cell_identity(op);
+            for (int r = 0; r < copies; ++r) a = cell_combine(op, a, scells[(size_t)c * NS + r * S + i]);
+            if (a != cell_identity(op)) cell_merge(slot + 1 + c, op, a);
+          }
+        }
+        continue;
       }
+      u64 key = skeys[i];
+      if (key == EMPTY) continue;
+      if (i == S) key = EMPTY;  // the special slot holds the key whose bits equal EMPTY
       i64 g;
       if (KM == KM_PACKED) {
         g = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
@@ -750,7 +786,7 @@ __global__ void k_finalize(const __grid_constant__ DPlan P, const __grid_constan
                            const u64* __restrict__ tbl, i64 cap, DCtrl* ctrl)
 {
   const int stride = P.stride;
-  const i64 nslots = cap + 1;
+  const i64 nslots = cap + 1 + (i64)ctrl->dense_slots;
   const i64 nwarp_iters = (nslots + 31) / 32;
   const int lane = threadIdx.x & 31;
   const i64 warp0 = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -759,7 +795,7 @@ __global__ void k_finalize(const __grid_constant__ DPlan P, const __grid_constan
     const i64 s = w * 32 + lane;
     u64 key = EMPTY;
     bool occ = false;
-    if (s < cap) { key = tbl[s * stride]; occ = key != EMPTY; }
+    if (s < nslots && s != cap) { key = tbl[s * stride]; occ = key != EMPTY; }
     else if (s == cap) { occ = ctrl->special_used != 0; }
     const u32 m = __ballot_sync(0xFFFFFFFFu, occ);
     if (m == 0) continue;
@@ -920,9 +956,10 @@ __global__ void k_pack_count(const u64* __restrict__ tbl, i64 cap, int stride, i
   extern __shared__ u64 s_cnt[];
   for (int p = threadIdx.x; p < nparts; p += blockDim.x) s_cnt[p] = 0;
   __syncthreads();
-  for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s <= cap; s += (i64)gridDim.x * blockDim.x) {
-    const u64 key = s < cap ? tbl[s * stride] : EMPTY;
-    const bool occ = s < cap ? key != EMPTY : ctrl->special_used != 0;
+  const i64 last = cap + (i64)ctrl->dense_slots;
+  for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s <= last; s += (i64)gridDim.x * blockDim.x) {
+    const u64 key = s != cap ? tbl[s * stride] : EMPTY;
+    const bool occ = s != cap ? key != EMPTY : ctrl->special_used != 0;
     if (occ) atomicAdd(&s_cnt[owner_of(mix64(key), (u32)nparts)], 1ull);
   }
   __syncthreads();
@@ -933,9 +970,10 @@ __global__ void k_pack_count(const u64* __restrict__ tbl, i64 cap, int stride, i
 __global__ void k_pack_scatter(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, const DCtrl* ctrl,
                                u64* __restrict__ cursors /* start offsets, advanced */, u64* __restrict__ out)
 {
-  for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s <= cap; s += (i64)gridDim.x * blockDim.x) {
-    const u64 key = s < cap ? tbl[s * stride] : EMPTY;
-    const bool occ = s < cap ? key != EMPTY : ctrl->special_used != 0;
+  const i64 last = cap + (i64)ctrl->dense_slots;
+  for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s <= last; s += (i64)gridDim.x * blockDim.x) {
+    const u64 key = s != cap ? tbl[s * stride] : EMPTY;
+    const bool occ = s != cap ? key != EMPTY : ctrl->special_used != 0;
     if (!occ) continue;
     const u64 pos = atomicAdd(&cursors[owner_of(mix64(key), (u32)nparts)], 1ull);
     u64* dst = out + pos * stride;
@@ -964,9 +1002,10 @@ __global__ void k_pack_chunks(const u64* __restrict__ tbl, i64 cap, int stride, 
       out[p * chunk_words + 1] = over ? 1ull : 0ull;
     }
   if (over) return;
-  for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s <= cap; s += (i64)gridDim.x * blockDim.x) {
-    const u64 key = s < cap ? tbl[s * stride] : EMPTY;
-    const bool occ = s < cap ? key != EMPTY : ctrl->special_used != 0;
+  const i64 last = cap + (i64)ctrl->dense_slots;
+  for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s <= last; s += (i64)gridDim.x * blockDim.x) {
+    const u64 key = s != cap ? tbl[s * stride] : EMPTY;
+    const bool occ = s != cap ? key != EMPTY : ctrl->special_used != 0;
     if (!occ) continue;
     const u32 p   = owner_of(mix64(key), (u32)nparts);
     const u64 pos = atomicAdd(&cursors[p], 1ull);
