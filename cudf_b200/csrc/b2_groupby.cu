@@ -10,6 +10,7 @@
 #include "b2_kernels.cuh"
 
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <memory>
@@ -216,7 +217,6 @@ struct ColView {  // deep copy of a b2_column_view (children included)
     if (this != &o) { ColView t(o.v); v = t.v; kids = t.kids; kid_views.clear(); for (auto& k : kids) kid_views.push_back(k.v); v.children = kid_views.empty() ? nullptr : kid_views.data(); }
     return *this;
   }
-  bool has_nulls() const { return v.null_mask != nullptr && v.null_count != 0; }
 };
 
 }  // namespace
@@ -653,6 +653,28 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
   st.ctrl_fresh = false;
 }
 
+// distinct keys among the participating rows, from a HyperLogLog pass (k_hll); synchronises the stream
+int64_t estimate_groups(const b2_groupby_state& st, cudaStream_t stream)
+{
+  Scratch regs(HLL_REGS * sizeof(u32), stream);
+  CUDA_TRY(cudaMemsetAsync(regs.p, 0, regs.bytes, stream));
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((st.plan.nrows + 4095) / 4096, (int64_t)device_info().sms * 2));
+  k_hll<<<grid, 1024, 0, stream>>>(st.plan, (u32*)regs.p);
+  CUDA_TRY(cudaGetLastError());
+  g_stats.kernel_launches++;
+  std::vector<u32> h(HLL_REGS);
+  CUDA_TRY(cudaMemcpyAsync(h.data(), regs.p, regs.bytes, cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  const double m = (double)HLL_REGS;
+  double sum = 0.0;
+  int zeros = 0;
+  for (u32 r : h) { sum += std::ldexp(1.0, -(int)r); zeros += r == 0; }
+  const double alpha = 0.7213 / (1.0 + 1.079 / m);
+  double e = alpha * m * m / sum;
+  if (e <= 2.5 * m && zeros > 0) e = m * std::log(m / (double)zeros);  // small-range correction
+  return (int64_t)e;
+}
+
 constexpr int64_t SPECULATIVE_CAP = 1 << 17;  // first table when nothing is known about the cardinality
 constexpr double MAX_LOAD = 0.70;
 
@@ -678,7 +700,14 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
     }
     if (!st.host_ctrl.overflow) break;
     if (cap >= full) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow at full capacity");
-    cap = (cap * 16 < full) ? cap * 16 : full;  // 2^17 -> 2^21 -> 2^25 -> 2^29 -> sized for the row count
+    if (attempt == 1) {
+      // the speculative table was too small: count the distinct keys (HyperLogLog, one pass over the
+      // key columns) and size the table for them
+      const int64_t est = estimate_groups(st, stream);
+      cap = std::min(full, std::max<int64_t>(cap * 16, (int64_t)((double)est * 1.10 / 0.6) + 1024));
+    } else {
+      cap = (cap * 4 < full) ? cap * 4 : full;  // the estimate fell short (it is within a few percent: rare)
+    }
   }
 }
 

@@ -728,6 +728,31 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
   }
 }
 
+// ------------------------------------------------------------------------------ cardinality estimate
+// HyperLogLog over the keys of all participating rows (one streaming pass over the key columns):
+// 2^13 registers, each the largest "leading zeros + 1" seen among the hashes that select it.  The host
+// turns the registers into a distinct-count estimate (±~1 %) that sizes the table after the small
+// speculative table overflowed — instead of growing it by trial and error.
+constexpr int HLL_BITS = 13;  // 8192 registers (32 KB of static shared memory), standard error 1.15 %
+constexpr int HLL_REGS = 1 << HLL_BITS;
+
+__global__ void __launch_bounds__(1024) k_hll(const __grid_constant__ DPlan P, u32* __restrict__ regs)
+{
+  __shared__ u32 s_regs[HLL_REGS];
+  for (int i = threadIdx.x; i < HLL_REGS; i += blockDim.x) s_regs[i] = 0;
+  __syncthreads();
+  for (i64 row = (i64)blockIdx.x * blockDim.x + threadIdx.x; row < P.nrows; row += (i64)gridDim.x * blockDim.x) {
+    if (!row_active(P, row)) continue;
+    const u64 h = (P.key_mode == KM_PACKED) ? mix64(pack_key(P, row) ^ 0x5bd1e9955bd1e995ull) : hash_row(P, row);
+    const u32 idx  = (u32)(h >> (64 - HLL_BITS));
+    const u32 rank = (u32)__clzll((i64)((h << HLL_BITS) | (1ull << (HLL_BITS - 1)))) + 1u;
+    if (s_regs[idx] < rank) atomicMax(&s_regs[idx], rank);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < HLL_REGS; i += blockDim.x)
+    if (s_regs[i]) atomicMax(&regs[i], s_regs[i]);
+}
+
 // ------------------------------------------------------------------------------ finalize
 enum OutKind : int {
   OK_COUNT = 0,  // int32 from a count cell

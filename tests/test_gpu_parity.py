@@ -164,7 +164,7 @@ def test_high_cardinality_grows_the_table():
     v = HostColumn.from_numpy(rng.integers(-5, 5, n).astype(np.int64))
     got = check([k], [(v, [Kind.SUM, Kind.MIN, Kind.MAX, Kind.COUNT_VALID])])
     assert got[0][0].size == n
-    assert cb.last_call_stats().table_attempts == 2  # the speculative table overflowed, the sized one fit
+    assert cb.last_call_stats().table_attempts == 2  # the speculative table overflowed, the estimated one fit
     got = check([k], [(v, [Kind.SUM])], expected_groups=n)
     assert cb.last_call_stats().table_attempts == 1
 
