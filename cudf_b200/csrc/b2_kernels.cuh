@@ -76,6 +76,26 @@ __device__ __forceinline__ i64 gmem_find_insert_packed(u64* tbl, i64 cap, int st
   return -1;
 }
 
+// Same, when the key cell of the home slot `idx` was already loaded (`k`): the loads of several rows
+// are issued together so that their DRAM latencies overlap, then each row finishes here.
+__device__ __forceinline__ i64 gmem_finish_packed(u64* tbl, i64 cap, int stride, u64 key, i64 idx, u64 k,
+                                                  DCtrl* ctrl, int* s_new)
+{
+  for (int p = 0; p < GMEM_PROBES; ++p) {
+    u64* kp = tbl + idx * stride;
+    if (p > 0) k = *(volatile u64*)kp;
+    if (k == key) return idx;
+    if (k == EMPTY) {
+      const u64 old = atomicCAS(kp, EMPTY, key);
+      if (old == EMPTY) { atomicAdd(s_new, 1); return idx; }
+      if (old == key) return idx;
+    }
+    if (++idx == cap) idx = 0;
+  }
+  ctrl->overflow = 1;
+  return -1;
+}
+
 // Global table, row keys: key cell = (tag << 32) | representative row.
 __device__ __forceinline__ i64 gmem_find_insert_rows(const DPlan& P, u64* tbl, i64 cap, int stride, i64 row,
                                                      u64 h, DCtrl* ctrl, int* s_new)
@@ -522,29 +542,63 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
             }
           }
       }
+      // shared-memory table first
+      u32 miss = 0;
+      u64 hh[AGG_ROWS];
 #pragma unroll
       for (int j = 0; j < AGG_ROWS; ++j) {
+        hh[j] = 0;
         if (!((act >> j) & 1u)) continue;
         int s = -1;
-        u64 h = 0;
         if (dense) {
           if (!((dout >> j) & 1u)) {
             s = (int)di[j];
             if (!((socc[s >> 5] >> (s & 31)) & 1u)) atomicOr(&socc[s >> 5], 1u << (s & 31));
           }
         } else {
-          h = (KM == KM_PACKED) ? mix64(kk[j]) : kk[j];
-          if (cache_on) s = smem_find_insert<KM>(P, skeys, S, fill_limit, &s_fill, kk[j], h, row0 + j);
+          hh[j] = (KM == KM_PACKED) ? mix64(kk[j]) : kk[j];
+          if (cache_on) s = smem_find_insert<KM>(P, skeys, S, fill_limit, &s_fill, kk[j], hh[j], row0 + j);
         }
         if (s >= 0) {
           sl[j] = s;
           ++my_hit;
         } else {
-          if (dense) h = mix64(kk[j]);
-          const i64 g = (KM == KM_PACKED) ? gmem_find_insert_packed(tbl, cap, stride, kk[j], h, ctrl, &s_new)
-                                          : gmem_find_insert_rows(P, tbl, cap, stride, row0 + j, h, ctrl, &s_new);
-          if (g >= 0) sl[j] = -2 - (int)g;
+          if (dense) hh[j] = mix64(kk[j]);
+          miss |= 1u << j;
           ++my_miss;
+        }
+      }
+      // then the global table: the home slots of all my missing rows are loaded together (their
+      // DRAM latencies overlap), then each row finishes its probe sequence
+      if (miss) {
+        if (KM == KM_PACKED) {
+          i64 gi[AGG_ROWS];
+          u64 gk[AGG_ROWS];
+#pragma unroll
+          for (int j = 0; j < AGG_ROWS; ++j) {
+            gi[j] = (i64)reduce64(hh[j], (u64)cap);
+            gk[j] = 0;
+            if (((miss >> j) & 1u) && kk[j] != EMPTY) gk[j] = *(volatile u64*)(tbl + gi[j] * stride);
+          }
+#pragma unroll
+          for (int j = 0; j < AGG_ROWS; ++j) {
+            if (!((miss >> j) & 1u)) continue;
+            i64 g;
+            if (kk[j] == EMPTY) {
+              if (ctrl->special_used == 0) ctrl->special_used = 1;
+              g = cap;
+            } else {
+              g = gmem_finish_packed(tbl, cap, stride, kk[j], gi[j], gk[j], ctrl, &s_new);
+            }
+            if (g >= 0) sl[j] = -2 - (int)g;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < AGG_ROWS; ++j) {
+            if (!((miss >> j) & 1u)) continue;
+            const i64 g = gmem_find_insert_rows(P, tbl, cap, stride, row0 + j, hh[j], ctrl, &s_new);
+            if (g >= 0) sl[j] = -2 - (int)g;
+          }
         }
       }
     }
@@ -611,9 +665,9 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
 #pragma unroll
         for (int j = 0; j < AGG_ROWS; ++j) {
           if (sl[j] == SLOT_NONE || !((use >> j) & 1u)) continue;
-          u64* cell = (LAYOUT == SL_GENERIC && sl[j] >= 0) ? scells + (size_t)c * NS + sl[j]
-                                                          : tbl + (i64)(-2 - sl[j]) * stride + 1 + c;
-          cell_update(cell, op, v[j]);
+          // two call sites so that each atomic knows its address space (shared vs global reduction)
+          if (LAYOUT == SL_GENERIC && sl[j] >= 0) cell_update(scells + (size_t)c * NS + sl[j], op, v[j]);
+          else cell_update(tbl + (i64)(-2 - sl[j]) * stride + 1 + c, op, v[j]);
         }
       }
     }

@@ -156,8 +156,8 @@ class GroupBy:
 
     def __del__(self):
         h = getattr(self, "_handle", None)
-        if h:
-            _lib.load().b2_groupby_destroy(h)
+        if h and _lib is not None and getattr(_lib, "_lib", None) is not None:  # not during interpreter shutdown
+            _lib._lib.b2_groupby_destroy(h)
             self._handle = None
 
     def aggregate(self, requests: Sequence[GroupByRequest]) -> Tuple[Table, List[Table]]:
@@ -191,8 +191,8 @@ class GroupByState:
 
     def __del__(self):
         h = getattr(self, "_handle", None)
-        if h:
-            _lib.load().b2_state_destroy(h)
+        if h and _lib is not None and getattr(_lib, "_lib", None) is not None:  # not during interpreter shutdown
+            _lib._lib.b2_state_destroy(h)
             self._handle = None
 
     def _stream(self):
