@@ -574,11 +574,11 @@ void read_ctrl(b2_groupby_state& st, cudaStream_t stream)
 
 int64_t num_groups(const b2_groupby_state& st) { return (int64_t)st.host_ctrl.nclaimed + (st.host_ctrl.special_used ? 1 : 0); }
 
-template <int KM, int LAYOUT, int NKF = 0>
+template <int KM, int LAYOUT, int NKF = 0, bool K8 = true>
 void launch_aggregate(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, int S, int fill_limit, size_t smem,
                       cudaStream_t stream)
 {
-  auto kern = k_aggregate<KM, LAYOUT, NKF>;
+  auto kern = k_aggregate<KM, LAYOUT, NKF, K8>;
   static thread_local size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -637,12 +637,16 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
   if (sc.key_mode == KM_PACKED) {
     if (layout == SL_F32MEAN) {
       // the number of key columns is a template parameter of the lean path (1..3), 0 = generic loops
+      bool k8 = false;  // any 8-byte key column?
+      for (int k = 0; k < sc.nkeys; ++k) k8 = k8 || sc.key_width[k] == 8;
+#define B2_LEAN(N, W) launch_aggregate<KM_PACKED, SL_F32MEAN, N, W>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream)
       switch ((P.flags & PF_FAST) ? sc.nkeys : 0) {
-        case 1: launch_aggregate<KM_PACKED, SL_F32MEAN, 1>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream); break;
-        case 2: launch_aggregate<KM_PACKED, SL_F32MEAN, 2>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream); break;
-        case 3: launch_aggregate<KM_PACKED, SL_F32MEAN, 3>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream); break;
-        default: launch_aggregate<KM_PACKED, SL_F32MEAN, 0>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream); break;
+        case 1: if (k8) B2_LEAN(1, true); else B2_LEAN(1, false); break;
+        case 2: if (k8) B2_LEAN(2, true); else B2_LEAN(2, false); break;
+        case 3: if (k8) B2_LEAN(3, true); else B2_LEAN(3, false); break;
+        default: B2_LEAN(0, true); break;
       }
+#undef B2_LEAN
     } else if (layout == SL_GENERIC) launch_aggregate<KM_PACKED, SL_GENERIC>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream);
     else launch_aggregate<KM_PACKED, SL_NONE>(P, st.table, st.cap, st.ctrl, 0, 0, 0, stream);
   } else {

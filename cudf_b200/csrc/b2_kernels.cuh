@@ -297,7 +297,7 @@ __device__ __forceinline__ u32 nibble_aligned(const u32* mask, u32 pos)
 //                 cached until `fill_limit`; a CTA whose cache stops paying off turns it off.
 // Rows whose key is not in shared memory go to the global table with global atomics.  At the end
 // every CTA merges its table into the global one.  There is no barrier inside the row loop.
-template <int KM, int LAYOUT, int NKF>
+template <int KM, int LAYOUT, int NKF, bool K8 = true>
 __global__ void __launch_bounds__(NKF > 0 ? LEAN_BLOCK : AGG_BLOCK, 1)
 k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* ctrl, int S_hash, int fill_limit)
 {
@@ -360,17 +360,15 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
     const u32 ssum_a = (u32)__cvta_generic_to_shared(ssum), scnt_a = (u32)__cvta_generic_to_shared(scnt);
     const bool filt_is_val = P.nfilters == 1 && P.filters[0] == vc.mask && P.filter_offsets[0] == vc.offset;
 
-    for (u32 tile = blockIdx.x; tile < nfull; tile += gridDim.x) {
+    // the loads of one tile: value vector + validity, activity nibble, key vectors + validity
+    auto load_tile = [&](u32 tile, float4& q, u32& vn, u32& act, uint4 (&ka)[NK], uint4 (&kb)[NK], u32 (&kn)[NK]) {
       const u32 r0 = tile * lean_tile + (u32)tid * LEAN_ROWS;
-      // loads
       const u32 ve = (u32)vc.offset + r0;
-      const float4 q = __ldg((const float4*)((const float*)vc.data + ve));
-      const u32 vn = vc.mask ? nibble_aligned(vc.mask, ve) : 0xFu;
-      u32 act = 0xFu;
+      q  = __ldg((const float4*)((const float*)vc.data + ve));
+      vn = vc.mask ? nibble_aligned(vc.mask, ve) : 0xFu;
+      act = 0xFu;
       if (filt_is_val) act = vn;
       else for (int f = 0; f < P.nfilters; ++f) act &= nibble_aligned(P.filters[f], (u32)P.filter_offsets[f] + r0);
-      uint4 ka[NK], kb[NK];
-      u32 kn[NK];
 #pragma unroll
       for (int k = 0; k < NK; ++k) {
         const DKeyCol& c = P.keys[k];
@@ -378,8 +376,19 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
         kn[k] = c.mask ? nibble_aligned(c.mask, e) : 0xFu;
         const uint4* kp = (const uint4*)(c.data + (u64)e * (u32)c.width);
         ka[k] = __ldg(kp);
-        if (c.width == 8) kb[k] = __ldg(kp + 1);
+        if (K8 && c.width == 8) kb[k] = __ldg(kp + 1);  // K8 = false: every key column is 4 bytes wide
       }
+    };
+    float4 q, nq;
+    u32 vn = 0, act = 0, nvn = 0, nact = 0;
+    uint4 ka[NK], kb[NK], nka[NK], nkb[NK];
+    u32 kn[NK], nkn[NK];
+    if (blockIdx.x < nfull) load_tile(blockIdx.x, q, vn, act, ka, kb, kn);
+    for (u32 tile = blockIdx.x; tile < nfull; tile += gridDim.x) {
+      const u32 r0 = tile * lean_tile + (u32)tid * LEAN_ROWS;
+      // software pipelining: the next tile's loads are in flight while this tile is folded
+      const u32 next = tile + gridDim.x;
+      if (next < nfull) load_tile(next, nq, nvn, nact, nka, nkb, nkn);
       // dense slots
       u32 d0 = copy_off, d1 = copy_off, d2 = copy_off, d3 = copy_off, bad = 0;
 #pragma unroll
@@ -388,7 +397,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
         if (c.mask && !P.include_nulls) act &= kn[k];
         const u32 mult = s_dense.mult[k];
         u32 x0, x1, x2, x3, o;
-        if (c.width == 4) {
+        if (!K8 || c.width == 4) {
           const u32 mn = (u32)s_dense.min[k];
           const u32 lim = (u32)s_dense.range[k] - (c.nullbit >= 0 ? 1u : 0u);
           x0 = ka[k].x - mn; x1 = ka[k].y - mn; x2 = ka[k].z - mn; x3 = ka[k].w - mn;
@@ -454,6 +463,9 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
         const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)c) + (u64)c;
         if (tot > ctrl->claim_limit) ctrl->overflow = 1;
       }
+      q = nq; vn = nvn; act = nact;
+#pragma unroll
+      for (int k = 0; k < NK; ++k) { ka[k] = nka[k]; if (K8) kb[k] = nkb[k]; kn[k] = nkn[k]; }
     }
   }
 
