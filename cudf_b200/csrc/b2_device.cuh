@@ -97,7 +97,7 @@ enum PlanFlags : int {
                     // multiple of 4, so the validity bits of 4 consecutive rows never straddle a mask word
 };
 
-// Dense key mapping of one aggregate pass, written on the device by k_sample_ranges: when the keys
+// Dense key mapping of one aggregate pass, derived on the device by sample_dense_box: when the keys
 // seen in a sample span a small box [min_k, min_k + range_k) per key column, a key's shared-memory
 // slot is its position in that box — no probing and no key storage.  Keys outside the box (the
 // sample missed them) take the global-table path, so the result stays exact.

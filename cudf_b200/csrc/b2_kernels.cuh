@@ -195,11 +195,13 @@ __device__ __forceinline__ u64 dense_key(const DPlan& P, const DDense& D, u32 id
   return key;
 }
 
-// One CTA looks at 4096 evenly spaced rows (4 per thread, their loads issued together) and writes
-// the dense box into ctrl->dense (or disables it when the box would not fit `cap_slots`
-// shared-memory slots).  No host round trip: the fused kernel reads the decision from device memory.
+// Every CTA of the fused kernel looks at the same 4096 evenly spaced rows (4 per thread, their loads
+// issued together; after the first CTA they come from L2) and derives the dense key box, or disables
+// it when the box would not fit `cap_slots` shared-memory slots.  All CTAs compute the same box
+// (min / max are order independent), so there is no extra launch and no host round trip.
+// Must be called by all 1024 threads of the CTA.
 constexpr int SAMPLE_ROWS = 4096;
-__global__ void __launch_bounds__(1024) k_sample_ranges(const __grid_constant__ DPlan P, DCtrl* ctrl, u32 cap_slots)
+__device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, DDense* out)
 {
   __shared__ i64 s_min[MAX_KEYS], s_max[MAX_KEYS];
   if (threadIdx.x < MAX_KEYS) { s_min[threadIdx.x] = 0x7FFFFFFFFFFFFFFFll; s_max[threadIdx.x] = (i64)0x8000000000000000ull; }
@@ -236,7 +238,7 @@ __global__ void __launch_bounds__(1024) k_sample_ranges(const __grid_constant__ 
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    DDense D;
+    DDense& D = *out;
     D.enabled = 0;
     D.total   = 0;
     D.copies  = 1;
@@ -265,8 +267,8 @@ __global__ void __launch_bounds__(1024) k_sample_ranges(const __grid_constant__ 
         D.copies  = r < 1 ? 1u : (r > 32u ? 32u : r);
       }
     }
-    ctrl->dense = D;
   }
+  __syncthreads();
 }
 
 // shared-memory atomics on 32-bit shared addresses (native on sm_100a; measured at ~73 % of the
@@ -291,7 +293,7 @@ __device__ __forceinline__ u32 nibble_aligned(const u32* mask, u32 pos)
 // ONE pass over keys + values + bitmasks.  Each thread takes 4 consecutive rows per tile (16-byte
 // vector loads when the columns allow, validity read as 4-bit nibbles of the mask words).  Each CTA
 // owns a shared-memory table in front of the global table:
-//   dense mode  : slot = position of the key in the sampled key box (k_sample_ranges), accumulators
+//   dense mode  : slot = position of the key in the sampled key box (sample_dense_box), accumulators
 //                 only, no probing;
 //   hashed mode : open addressing with linear probing on the 64-bit key cell, first come first
 //                 cached until `fill_limit`; a CTA whose cache stops paying off turns it off.
@@ -299,7 +301,8 @@ __device__ __forceinline__ u32 nibble_aligned(const u32* mask, u32 pos)
 // every CTA merges its table into the global one.  There is no barrier inside the row loop.
 template <int KM, int LAYOUT, int NKF, bool K8 = true>
 __global__ void __launch_bounds__(NKF > 0 ? LEAN_BLOCK : AGG_BLOCK, 1)
-k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* ctrl, int S_hash, int fill_limit)
+k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* ctrl, int S_hash, int fill_limit,
+            u32 cap_dense)
 {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int s_fill, s_new, s_cache_on, s_abort, s_hit, s_miss;
@@ -307,9 +310,11 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
 
   const int stride = P.stride;
   const int tid    = threadIdx.x;
-  if (LAYOUT != SL_NONE && KM == KM_PACKED) {
-    const int nw = (int)(sizeof(DDense) / 4);
-    for (int i = tid; i < nw; i += blockDim.x) ((u32*)&s_dense)[i] = ((const u32*)&ctrl->dense)[i];
+  if (LAYOUT != SL_NONE && KM == KM_PACKED && cap_dense > 0 && P.nrows >= SAMPLE_ROWS && blockDim.x == 1024) {
+    sample_dense_box(P, cap_dense, &s_dense);
+    if (blockIdx.x == 0 && tid == 0) ctrl->dense = s_dense;  // for the host's statistics
+  } else if (tid == 0) {
+    s_dense.enabled = 0;
   }
   if (tid == 0) { s_fill = 0; s_new = 0; s_cache_on = (LAYOUT != SL_NONE); s_abort = 0; s_hit = 0; s_miss = 0; }
   __syncthreads();
