@@ -1359,9 +1359,17 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
     device_info();
     const b2_allocator al = resolve(allocator);
     const int64_t n = columns[0].size;
+    int str_col = -1;
     for (int c = 0; c < num_columns; ++c) {
       if (columns[c].size != n) B2_FAIL(B2_LOGIC_ERROR, "columns differ in size");
-      if (width_of(columns[c].type_id) == 0) B2_FAIL(B2_UNSUPPORTED, "hash_partition serves fixed-width columns only");
+      if (columns[c].type_id == B2_STRING) {
+        if (str_col >= 0) B2_FAIL(B2_UNSUPPORTED, "hash_partition serves at most one STRING column");
+        if (n > 0 && (columns[c].num_children < 1 || !columns[c].children))
+          B2_FAIL(B2_INVALID_ARGUMENT, "STRING column needs an offsets child");
+        str_col = c;
+      } else if (width_of(columns[c].type_id) == 0) {
+        B2_FAIL(B2_UNSUPPORTED, "hash_partition serves fixed-width and STRING columns");
+      }
     }
     // hashing plan over the key columns: nulls hash as nulls (they are rows like any other here)
     b2_groupby gb;
@@ -1372,9 +1380,12 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
     fill_plan_schema(P, sc);
     bind_plan_inputs(P, sc, gb, nullptr, 0);
 
-    DPartPlan Q{};
+    auto Qp = std::make_unique<DPartPlan>();
+    DPartPlan& Q = *Qp;
+    std::memset(&Q, 0, sizeof(Q));
     Q.ncols = num_columns;
     Q.nparts = num_parts;
+    Q.str_col = str_col;
     const int64_t want = std::max<int64_t>(1, (n + 8191) / 8192);
     const int grid = (int)std::min<int64_t>(want, (int64_t)device_info().sms * 4);
     Q.rows_per_cta = ((n + grid - 1) / grid + PART_BLOCK - 1) / PART_BLOCK * PART_BLOCK;
@@ -1385,40 +1396,116 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
     } guard{out_columns, num_columns, &al, stream};
     for (int c = 0; c < num_columns; ++c) {
       const bool nullable = columns[c].null_mask != nullptr;
-      init_owned(out_columns[c], columns[c].type_id, n, nullable, al, stream);
+      DPartCol& d = Q.cols[c];
+      if (c == str_col) {
+        b2_owned_column& oc = out_columns[c];
+        oc.type_id = B2_STRING;
+        oc.size = (int32_t)n;
+        if (nullable) {
+          oc.null_mask_bytes = (size_t)std::max<int64_t>(1, (n + 511) / 512) * 64;
+          oc.null_mask = (uint32_t*)out_alloc(al, oc.null_mask_bytes, stream);
+        }
+        if (n > 0) {
+          const b2_column_view& o = columns[c].children[0];
+          Q.str_offsets = (const unsigned char*)o.data + (size_t)o.offset * (o.type_id == B2_INT64 ? 8 : 4);
+          Q.str_offs64 = o.type_id == B2_INT64;
+        }
+        d.width = 0;
+      } else {
+        init_owned(out_columns[c], columns[c].type_id, n, nullable, al, stream);
+        d.width = width_of(columns[c].type_id);
+      }
       out_columns[c].scale = columns[c].scale;
       out_columns[c].null_count = nullable ? columns[c].null_count : 0;
       if (nullable) CUDA_TRY(cudaMemsetAsync(out_columns[c].null_mask, 0, out_columns[c].null_mask_bytes, stream));
-      DPartCol& d = Q.cols[c];
       d.src = (const unsigned char*)columns[c].data; d.mask = columns[c].null_mask; d.offset = columns[c].offset;
-      d.width = width_of(columns[c].type_id); d.dst = (unsigned char*)out_columns[c].data;
+      d.dst = (unsigned char*)out_columns[c].data;
       d.dst_mask = out_columns[c].null_mask;
     }
     for (int p = 0; p <= num_parts; ++p) offsets[p] = 0;
-    if (n == 0) { guard.armed = false; return; }
 
     const size_t cells = (size_t)grid * num_parts;
-    Scratch counts(cells * sizeof(u32), stream), starts(cells * sizeof(i64), stream);
-    const size_t smem = (size_t)num_parts * sizeof(u32);
-    k_partition_count<<<grid, PART_BLOCK, smem, stream>>>(P, Q, (u32*)counts.p);
-    CUDA_TRY(cudaGetLastError());
-    std::vector<u32> h_counts(cells);
-    CUDA_TRY(cudaMemcpyAsync(h_counts.data(), counts.p, cells * sizeof(u32), cudaMemcpyDeviceToHost, stream));
-    CUDA_TRY(cudaStreamSynchronize(stream));
-    std::vector<i64> h_starts(cells);
-    int64_t run = 0;
-    for (int p = 0; p < num_parts; ++p) {
-      offsets[p] = run;
-      for (int b = 0; b < grid; ++b) { h_starts[(size_t)b * num_parts + p] = run; run += h_counts[(size_t)b * num_parts + p]; }
+    Scratch counts(std::max<size_t>(8, cells * sizeof(u32)), stream), starts(std::max<size_t>(8, cells * sizeof(i64)), stream);
+    Scratch chars, char_starts;
+    if (str_col >= 0) {
+      chars = Scratch(std::max<size_t>(8, cells * sizeof(u64)), stream);
+      char_starts = Scratch(std::max<size_t>(8, cells * sizeof(i64)), stream);
     }
-    offsets[num_parts] = run;
-    if (run != n) B2_FAIL(B2_INTERNAL_ERROR, "hash_partition: row count mismatch");
+    const size_t smem = (size_t)num_parts * 12;
+    int64_t total_chars = 0;
+    std::vector<i64> h_starts(cells), h_cstarts(cells);
+    if (n > 0) {
+      k_partition_count<<<grid, PART_BLOCK, smem, stream>>>(P, Q, (u32*)counts.p, (u64*)chars.p);
+      CUDA_TRY(cudaGetLastError());
+      std::vector<u32> h_counts(cells);
+      std::vector<u64> h_chars(cells, 0);
+      CUDA_TRY(cudaMemcpyAsync(h_counts.data(), counts.p, cells * sizeof(u32), cudaMemcpyDeviceToHost, stream));
+      if (str_col >= 0) CUDA_TRY(cudaMemcpyAsync(h_chars.data(), chars.p, cells * sizeof(u64), cudaMemcpyDeviceToHost, stream));
+      CUDA_TRY(cudaStreamSynchronize(stream));
+      int64_t run = 0;
+      for (int p = 0; p < num_parts; ++p) {
+        offsets[p] = run;
+        for (int b = 0; b < grid; ++b) {
+          h_starts[(size_t)b * num_parts + p] = run;
+          run += h_counts[(size_t)b * num_parts + p];
+          h_cstarts[(size_t)b * num_parts + p] = total_chars;
+          total_chars += (int64_t)h_chars[(size_t)b * num_parts + p];
+        }
+      }
+      offsets[num_parts] = run;
+      if (run != n) B2_FAIL(B2_INTERNAL_ERROR, "hash_partition: row count mismatch");
+    }
+    if (str_col >= 0) {
+      // chars + offsets of the partitioned STRING column; INT64 offsets beyond the reference's
+      // large-strings threshold (cpp/src/strings/utilities.cu:150-157)
+      b2_owned_column& oc = out_columns[str_col];
+      const bool big = total_chars > 0x7FFFFFFFll;
+      oc.data_bytes = (size_t)std::max<int64_t>(total_chars, 1);
+      oc.data = out_alloc(al, oc.data_bytes, stream);
+      oc.num_children = 1;
+      oc.children = (b2_owned_column*)std::calloc(1, sizeof(b2_owned_column));
+      oc.children[0].type_id = big ? B2_INT64 : B2_INT32;
+      oc.children[0].size = (int32_t)(n + 1);
+      oc.children[0].data_bytes = (size_t)(n + 1) * (big ? 8 : 4);
+      oc.children[0].data = out_alloc(al, oc.children[0].data_bytes, stream);
+      Q.cols[str_col].dst = (unsigned char*)oc.data;
+      Q.out_offsets = oc.children[0].data;
+      Q.out_offs64 = big;
+      // the closing offset
+      if (big) { const i64 t = total_chars; CUDA_TRY(cudaMemcpyAsync((i64*)oc.children[0].data + n, &t, 8, cudaMemcpyHostToDevice, stream)); CUDA_TRY(cudaStreamSynchronize(stream)); }
+      else { const int t = (int)total_chars; CUDA_TRY(cudaMemcpyAsync((int*)oc.children[0].data + n, &t, 4, cudaMemcpyHostToDevice, stream)); CUDA_TRY(cudaStreamSynchronize(stream)); }
+    }
+    if (n == 0) { guard.armed = false; return; }
     CUDA_TRY(cudaMemcpyAsync(starts.p, h_starts.data(), cells * sizeof(i64), cudaMemcpyHostToDevice, stream));
-    k_partition_scatter<<<grid, PART_BLOCK, smem, stream>>>(P, Q, (const i64*)starts.p);
+    if (str_col >= 0) CUDA_TRY(cudaMemcpyAsync(char_starts.p, h_cstarts.data(), cells * sizeof(i64), cudaMemcpyHostToDevice, stream));
+    k_partition_scatter<<<grid, PART_BLOCK, (size_t)num_parts * 8, stream>>>(P, Q, (const i64*)starts.p, (const i64*)char_starts.p);
     CUDA_TRY(cudaGetLastError());
     CUDA_TRY(cudaStreamSynchronize(stream));
     g_stats.kernel_launches += 2;
     guard.armed = false;
+  });
+}
+
+b2_status b2_mask_to_bytes(const uint32_t* mask, int64_t offset, int64_t size, void* stream, uint8_t* out)
+{
+  return guarded([&] {
+    if (!mask || !out || size < 0) B2_FAIL(B2_INVALID_ARGUMENT, "bad argument");
+    if (size == 0) return;
+    device_info();
+    k_mask_to_bytes<<<grid_for(size, 256, 16), 256, 0, (cudaStream_t)stream>>>(mask, offset, size, out);
+    CUDA_TRY(cudaGetLastError());
+  });
+}
+
+b2_status b2_bytes_to_mask(const uint8_t* bytes, int64_t size, void* stream, uint32_t* mask, int32_t* null_count_device)
+{
+  return guarded([&] {
+    if (!bytes || !mask || !null_count_device || size < 0) B2_FAIL(B2_INVALID_ARGUMENT, "bad argument");
+    CUDA_TRY(cudaMemsetAsync(null_count_device, 0, 4, (cudaStream_t)stream));
+    if (size == 0) return;
+    device_info();
+    k_bytes_to_mask<<<grid_for(size, 256, 16), 256, 0, (cudaStream_t)stream>>>(bytes, size, mask, (u32*)null_count_device);
+    CUDA_TRY(cudaGetLastError());
   });
 }
 

@@ -1188,6 +1188,14 @@ struct DPartCol {
 struct DPartPlan {
   int ncols; int nparts;
   i64 rows_per_cta;
+  // at most one STRING column: chars + offsets in, chars + offsets out (rows and bytes of a partition
+  // keep the same order, so the output offsets are monotone)
+  int str_col;        // index in cols[], -1 = none
+  int str_offs64;     // input offsets are INT64
+  int out_offs64;     // output offsets are INT64
+  int pad;
+  const void* str_offsets;
+  void* out_offsets;
   DPartCol cols[MAX_PART_COLS];
 };
 
@@ -1196,44 +1204,112 @@ __device__ __forceinline__ u32 row_partition(const DPlan& P, i64 row, u32 nparts
   const u64 h = (P.key_mode == KM_PACKED) ? mix64(pack_key(P, row)) : hash_row(P, row);
   return owner_of(h, nparts);
 }
-
-__global__ void __launch_bounds__(PART_BLOCK)
-k_partition_count(const __grid_constant__ DPlan P, DPartPlan Q, u32* __restrict__ cta_counts /* [grid][nparts] */)
+__device__ __forceinline__ i64 part_str_offset(const DPartPlan& Q, i64 idx)
 {
-  extern __shared__ u32 s_hist[];
-  for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) s_hist[p] = 0;
-  __syncthreads();
-  const i64 lo = (i64)blockIdx.x * Q.rows_per_cta;
-  const i64 hi = min(P.nrows, lo + Q.rows_per_cta);
-  for (i64 r = lo + threadIdx.x; r < hi; r += blockDim.x) atomicAdd(&s_hist[row_partition(P, r, (u32)Q.nparts)], 1u);
-  __syncthreads();
-  for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) cta_counts[(size_t)blockIdx.x * Q.nparts + p] = s_hist[p];
+  return Q.str_offs64 ? (i64)__ldg((const i64*)Q.str_offsets + idx) : (i64)__ldg((const int*)Q.str_offsets + idx);
 }
 
 __global__ void __launch_bounds__(PART_BLOCK)
-k_partition_scatter(const __grid_constant__ DPlan P, const __grid_constant__ DPartPlan Q,
-                    const i64* __restrict__ cta_starts /* [grid][nparts] */)
+k_partition_count(const __grid_constant__ DPlan P, const __grid_constant__ DPartPlan Q,
+                  u32* __restrict__ cta_counts /* [grid][nparts] */, u64* __restrict__ cta_chars /* [grid][nparts] or null */)
 {
-  extern __shared__ u32 s_hist[];  // cursor inside this CTA's share of each partition
-  for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) s_hist[p] = 0;
+  extern __shared__ u64 s_part[];  // [nparts] string bytes, then [nparts] u32 row counts
+  u64* s_chars = s_part;
+  u32* s_hist  = (u32*)(s_part + Q.nparts);
+  for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) { s_hist[p] = 0; s_chars[p] = 0; }
   __syncthreads();
   const i64 lo = (i64)blockIdx.x * Q.rows_per_cta;
   const i64 hi = min(P.nrows, lo + Q.rows_per_cta);
   for (i64 r = lo + threadIdx.x; r < hi; r += blockDim.x) {
-    const u32 p   = row_partition(P, r, (u32)Q.nparts);
-    const i64 dst = cta_starts[(size_t)blockIdx.x * Q.nparts + p] + atomicAdd(&s_hist[p], 1u);
+    const u32 p = row_partition(P, r, (u32)Q.nparts);
+    atomicAdd(&s_hist[p], 1u);
+    if (Q.str_col >= 0) {
+      const DPartCol& col = Q.cols[Q.str_col];
+      const i64 idx = col.offset + r;
+      if (!col.mask || bit_valid(col.mask, idx)) {
+        const i64 len = part_str_offset(Q, idx + 1) - part_str_offset(Q, idx);
+        if (len > 0) atomicAdd(&s_chars[p], (u64)len);
+      }
+    }
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) {
+    cta_counts[(size_t)blockIdx.x * Q.nparts + p] = s_hist[p];
+    if (cta_chars) cta_chars[(size_t)blockIdx.x * Q.nparts + p] = s_chars[p];
+  }
+}
+
+__global__ void __launch_bounds__(PART_BLOCK)
+k_partition_scatter(const __grid_constant__ DPlan P, const __grid_constant__ DPartPlan Q,
+                    const i64* __restrict__ cta_starts /* [grid][nparts] */,
+                    const i64* __restrict__ cta_char_starts /* [grid][nparts] or null */)
+{
+  // cursor inside this CTA's share of each partition: rows in the high 24 bits, string bytes in the
+  // low 40 bits, advanced by ONE atomic per row so that rows and bytes keep the same order
+  extern __shared__ u64 s_part[];
+  u64* s_cur = s_part;
+  for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) s_cur[p] = 0;
+  __syncthreads();
+  const i64 lo = (i64)blockIdx.x * Q.rows_per_cta;
+  const i64 hi = min(P.nrows, lo + Q.rows_per_cta);
+  for (i64 r = lo + threadIdx.x; r < hi; r += blockDim.x) {
+    const u32 p = row_partition(P, r, (u32)Q.nparts);
+    i64 len = 0, sbeg = 0;
+    if (Q.str_col >= 0) {
+      const DPartCol& col = Q.cols[Q.str_col];
+      const i64 idx = col.offset + r;
+      if (!col.mask || bit_valid(col.mask, idx)) {
+        sbeg = part_str_offset(Q, idx);
+        len  = part_str_offset(Q, idx + 1) - sbeg;
+      }
+    }
+    const u64 cur = atomicAdd(&s_cur[p], (1ull << 40) | (u64)len);
+    const i64 dst = cta_starts[(size_t)blockIdx.x * Q.nparts + p] + (i64)(cur >> 40);
     for (int c = 0; c < Q.ncols; ++c) {
       const DPartCol& col = Q.cols[c];
       const i64 idx = col.offset + r;
-      switch (col.width) {
-        case 1: col.dst[dst] = col.src[idx]; break;
-        case 2: ((unsigned short*)col.dst)[dst] = ((const unsigned short*)col.src)[idx]; break;
-        case 4: ((u32*)col.dst)[dst] = ((const u32*)col.src)[idx]; break;
-        default: ((u64*)col.dst)[dst] = ((const u64*)col.src)[idx]; break;
+      if (c == Q.str_col) {
+        const i64 cdst = cta_char_starts[(size_t)blockIdx.x * Q.nparts + p] + (i64)(cur & ((1ull << 40) - 1));
+        if (Q.out_offs64) ((i64*)Q.out_offsets)[dst] = cdst; else ((int*)Q.out_offsets)[dst] = (int)cdst;
+        for (i64 b = 0; b < len; ++b) col.dst[cdst + b] = col.src[sbeg + b];
+      } else {
+        switch (col.width) {
+          case 1: col.dst[dst] = col.src[idx]; break;
+          case 2: ((unsigned short*)col.dst)[dst] = ((const unsigned short*)col.src)[idx]; break;
+          case 4: ((u32*)col.dst)[dst] = ((const u32*)col.src)[idx]; break;
+          default: ((u64*)col.dst)[dst] = ((const u64*)col.src)[idx]; break;
+        }
       }
       if (col.dst_mask && bit_valid(col.mask, idx)) atomicOr(col.dst_mask + (dst >> 5), 1u << (dst & 31));
     }
   }
+}
+
+// validity bitmask <-> one byte per row (a row exchange moves validity as bytes: partitions start at
+// arbitrary bit positions)
+__global__ void k_mask_to_bytes(const u32* __restrict__ mask, i64 offset, i64 n, unsigned char* __restrict__ out)
+{
+  for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (i64)gridDim.x * blockDim.x)
+    out[i] = bit_valid(mask, offset + i) ? 1 : 0;
+}
+__global__ void k_bytes_to_mask(const unsigned char* __restrict__ bytes, i64 n, u32* __restrict__ mask, u32* null_count)
+{
+  const i64 nwords = (n + 31) / 32;
+  const int lane = threadIdx.x & 31;
+  const i64 warp0 = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
+  u32 nulls = 0;
+  for (i64 w = warp0; w < nwords; w += nwarps) {
+    const i64 i = w * 32 + lane;
+    const bool v = i < n && bytes[i] != 0;
+    const u32 word = __ballot_sync(0xFFFFFFFFu, v);
+    if (lane == 0) {
+      mask[w] = word;
+      const int valid_bits = (int)min((i64)32, n - w * 32);
+      nulls += (u32)(valid_bits - __popc(word));
+    }
+  }
+  if (lane == 0 && nulls) atomicAdd(null_count, nulls);
 }
 
 }  // namespace b2

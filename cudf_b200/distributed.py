@@ -110,7 +110,7 @@ class DistributedGroupBy:
         return st.finalize()
 
     def _aggregate_rows(self, requests, world):
-        from .column import Column, Table
+        from .column import Table
         from .groupby import GroupBy, GroupByRequest
         from .partition import hash_partition
         nkeys = self._keys.num_columns()
@@ -120,19 +120,51 @@ class DistributedGroupBy:
                 seen[id(r._values)] = len(vals)
                 vals.append(r._values)
         cols = self._keys.columns() + vals
-        if any(c.mask is not None for c in cols):
-            raise NotImplementedError("rows strategy: nullable columns are exchanged by the partials strategy")
         parts, offsets = hash_partition(Table(cols), nkeys, world)
-        send_counts = [offsets[p + 1] - offsets[p] for p in range(world)]
-        recv_counts = exchange_counts(send_counts, cols[0].data.device, self._group)
-        nrecv = sum(recv_counts)
-        new_cols = []
-        for c in parts.columns():
-            w = c.data.numel() // max(c.size, 1) if c.size else 1
-            from .types import type_width
-            w = type_width(c.type_id)
-            buf = exchange_buffer(c.data, send_counts, recv_counts, w, self._group)
-            new_cols.append(Column(c.type_id, nrecv, buf, None, 0, 0))
+        new_cols = exchange_rows(parts, offsets, world, self._group)
         gb = GroupBy(Table(new_cols[:nkeys]), self._null_handling, **self._options)
         new_reqs = [GroupByRequest(new_cols[nkeys + seen[id(r._values)]], r._aggregations) for r in requests]
         return gb.aggregate(new_reqs)
+
+
+def exchange_rows(parts, offsets, world, group=None):
+    """All-to-all of a hash-partitioned table (partition p goes to rank p): data as bytes, validity
+    as one byte per row (a partition starts at an arbitrary bit of its mask), strings as offsets +
+    chars with the received offsets rebased segment by segment.  Returns the received columns."""
+    from .column import Column
+    from .partition import bytes_to_mask, mask_to_bytes
+    from .types import TypeId, type_width
+    device = parts.columns()[0].data.device
+    send_counts = [offsets[p + 1] - offsets[p] for p in range(world)]
+    recv_counts = exchange_counts(send_counts, device, group)
+    nrecv = sum(recv_counts)
+    out = []
+    for c in parts.columns():
+        mask, nulls = None, 0
+        if c.mask is not None:
+            vb = exchange_buffer(mask_to_bytes(c), send_counts, recv_counts, 1, group)
+            mask, nulls = bytes_to_mask(vb)
+        if c.type_id == TypeId.STRING:
+            odt = torch.int64 if c.offsets_type == TypeId.INT64 else torch.int32
+            offs = c.offsets.view(odt)[: c.size + 1].to(torch.int64)
+            bounds = offs[torch.tensor(offsets, device=device)].tolist()          # char range of every partition
+            send_chars = [bounds[p + 1] - bounds[p] for p in range(world)]
+            recv_chars = exchange_counts(send_chars, device, group)
+            chars = exchange_buffer(c.data if c.data is not None else torch.zeros(0, dtype=torch.uint8, device=device),
+                                    send_chars, recv_chars, 1, group)
+            roffs = exchange_buffer(offs[: c.size].contiguous().view(torch.uint8), send_counts, recv_counts, 8,
+                                    group).view(torch.int64)
+            new_offs = torch.empty(nrecv + 1, dtype=torch.int64, device=device)
+            row0, char0 = 0, 0
+            for s in range(world):                                                   # rebase each sender's segment
+                if recv_counts[s]:
+                    seg = roffs[row0:row0 + recv_counts[s]]
+                    new_offs[row0:row0 + recv_counts[s]] = seg - seg[0] + char0
+                row0 += recv_counts[s]
+                char0 += recv_chars[s]
+            new_offs[nrecv] = char0
+            out.append(Column(TypeId.STRING, nrecv, chars, mask, 0, nulls, new_offs.view(torch.uint8), TypeId.INT64))
+        else:
+            buf = exchange_buffer(c.data, send_counts, recv_counts, type_width(c.type_id), group)
+            out.append(Column(c.type_id, nrecv, buf, mask, 0, nulls))
+    return out

@@ -1,6 +1,7 @@
 """``hash_partition``: mirror of ``pylibcudf.partitioning.hash_partition`` /
 ``cudf::hash_partition`` (cpp/include/cudf/partitioning.hpp, cpp/src/partitioning/partitioning.cu:950-975)
-for fixed-width tables, through the C ABI (b2_hash_partition)."""
+for tables of fixed-width columns and at most one STRING column, through the C ABI
+(b2_hash_partition), plus the validity bitmask <-> byte helpers a row exchange needs."""
 from __future__ import annotations
 
 import ctypes as C
@@ -9,8 +10,9 @@ from typing import List, Tuple
 import torch
 
 from . import _lib
-from .column import Column, Table, TorchAllocator
+from .column import Column, Table, allocator_for
 from .groupby import _check
+from .types import TypeId
 
 
 def hash_partition(table: Table, num_key_columns: int, num_partitions: int) -> Tuple[Table, List[int]]:
@@ -23,7 +25,7 @@ def hash_partition(table: Table, num_key_columns: int, num_partitions: int) -> T
     for i, c in enumerate(cols):
         views[i] = c.c_view(keep)
     device = cols[0].data.device if cols[0].data is not None else torch.device("cuda")
-    alloc = TorchAllocator(device)
+    alloc = allocator_for(device)
     out = (_lib.OwnedColumn * len(cols))()
     offsets = (C.c_int64 * (num_partitions + 1))()
     stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
@@ -32,5 +34,37 @@ def hash_partition(table: Table, num_key_columns: int, num_partitions: int) -> T
     res = []
     for i in range(len(cols)):
         oc = out[i]
-        res.append(Column(oc.type_id, oc.size, alloc.adopt(oc.data), alloc.adopt(oc.null_mask), 0, oc.null_count))
+        offs, offs_t = None, TypeId.INT32
+        if oc.num_children:
+            child = oc.children[0]
+            offs = alloc.adopt(child.data)
+            offs_t = TypeId(child.type_id)
+            child.data = None
+        res.append(Column(oc.type_id, oc.size, alloc.adopt(oc.data), alloc.adopt(oc.null_mask), 0, oc.null_count,
+                          offs, offs_t))
+        oc.data = None
+        oc.null_mask = None
+        lib.b2_column_free(C.byref(oc), C.byref(alloc.struct), stream)  # host arrays of the descriptor
     return Table(res), [int(o) for o in offsets]
+
+
+def mask_to_bytes(col: Column) -> torch.Tensor:
+    """One byte per row (1 = valid) from the column's validity bitmask."""
+    out = torch.empty(max(col.size, 1), dtype=torch.uint8, device=col.mask.device)
+    stream = C.c_void_p(torch.cuda.current_stream(out.device).cuda_stream)
+    _check(_lib.load().b2_mask_to_bytes(C.c_void_p(col.mask.data_ptr()), col.offset, col.size, stream,
+                                        C.c_void_p(out.data_ptr())))
+    return out[:col.size]
+
+
+def bytes_to_mask(valid: torch.Tensor) -> Tuple[torch.Tensor, int]:
+    """cudf bitmask words (as a uint8 tensor, 64-byte padded) and the null count from validity bytes."""
+    n = valid.numel()
+    valid = valid.contiguous()
+    words = max(16, ((n + 31) // 32 + 15) // 16 * 16)
+    mask = torch.zeros(words * 4, dtype=torch.uint8, device=valid.device)
+    nulls = torch.zeros(1, dtype=torch.int32, device=valid.device)
+    stream = C.c_void_p(torch.cuda.current_stream(valid.device).cuda_stream)
+    _check(_lib.load().b2_bytes_to_mask(C.c_void_p(valid.data_ptr() if n else mask.data_ptr()), n, stream,
+                                        C.c_void_p(mask.data_ptr()), C.c_void_p(nulls.data_ptr())))
+    return mask, int(nulls.item())

@@ -249,7 +249,8 @@ void b2_state_destroy(b2_groupby_state* st);
 /* ---- row-level hash partition: the multi-GPU pre-step for high-cardinality inputs ---
  * cudf::hash_partition(table, columns_to_hash, num_partitions)
  * (cpp/include/cudf/partitioning.hpp; cpp/src/partitioning/partitioning.cu:950-975):
- * reorders the rows of `columns` (fixed-width columns; the first `num_key_columns` are hashed)
+ * reorders the rows of `columns` (fixed-width columns and at most one STRING column, nullable or
+ * not; the first `num_key_columns` are hashed)
  * so that partition p occupies rows [offsets[p], offsets[p+1]).  Output columns come from the
  * allocator; `offsets` is a host array of num_parts+1 entries.  The partition of a key equals
  * the owner used by b2_state_pack.  Synchronises `stream`. */
@@ -257,6 +258,15 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns,
                             int32_t num_key_columns, int32_t num_parts, void* stream,
                             const b2_allocator* allocator, b2_owned_column* out_columns,
                             int64_t* offsets);
+
+/* Validity bitmask <-> one byte per row (1 = valid).  A row exchange between ranks moves validity
+ * as bytes because a partition starts at an arbitrary bit of its mask
+ * (the reference copies bitmask ranges with cudf::copy_bitmask / concatenate_masks,
+ * cpp/include/cudf/null_mask.hpp).  b2_bytes_to_mask writes ceil(size/32) words and the number of
+ * nulls to *null_count_device (device memory).  Both enqueue on `stream` without synchronising. */
+b2_status b2_mask_to_bytes(const uint32_t* mask, int64_t offset, int64_t size, void* stream, uint8_t* out);
+b2_status b2_bytes_to_mask(const uint8_t* bytes, int64_t size, void* stream, uint32_t* mask,
+                           int32_t* null_count_device);
 
 /* Releases the buffers of one owned column obtained from b2_hash_partition. */
 void b2_column_free(b2_owned_column* col, const b2_allocator* allocator, void* stream);

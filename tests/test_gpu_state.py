@@ -222,3 +222,61 @@ def test_fixed_chunk_overflow_is_reported_to_every_receiver():
         merged.merge_chunks(send[dst * cbytes:(dst + 1) * cbytes].clone(), 1, chunk)
         with pytest.raises(cb.LogicError, match="chunk overflow"):
             merged.finalize()
+
+
+def test_hash_partition_with_string_and_nullable_columns():
+    import cudf_b200 as cb
+    from cudf_b200.partition import hash_partition
+    rng = np.random.default_rng(43)
+    n = 50_001
+    words = ["", "a", "bb", "año", "x" * 37, "hello", "₹1", None]
+    pick = rng.integers(0, len(words), n)
+    s = HostColumn.from_strings([words[i] for i in pick])
+    k2 = HostColumn.from_numpy(rng.integers(0, 5, n).astype(np.int32))
+    v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.3)
+    table = cb.Table([cb.Column.from_host(c) for c in (s, k2, v)])
+    for nparts in (1, 3, 8):
+        out, offsets = hash_partition(table, 2, nparts)
+        assert offsets[0] == 0 and offsets[-1] == n
+        hs, hk, hv = (c.to_host() for c in out.columns())
+        got = sorted(zip([x if x is not None else b"\xff" for x in hs.to_pylist()], hk.values().tolist(),
+                         [(-1e300 if x is None else x) for x in hv.to_pylist()]))
+        exp = sorted(zip([x if x is not None else b"\xff" for x in s.to_pylist()], k2.values().tolist(),
+                         [(-1e300 if x is None else x) for x in v.to_pylist()]))
+        assert got == exp
+        # a key lives in one partition only
+        part_of = np.repeat(np.arange(nparts), np.diff(offsets))
+        seen = {}
+        for key, p in zip(zip(hs.to_pylist(), hk.values().tolist()), part_of.tolist()):
+            assert seen.setdefault(key, p) == p
+
+
+def test_row_exchange_with_strings_and_nulls_single_rank_group():
+    """exchange_rows over a one-rank NCCL group (every partition comes back to this rank), then the
+    groupby on the received columns equals the one-shot result: C5-shaped input."""
+    import os
+    import torch
+    import torch.distributed as dist
+    import cudf_b200 as cb
+    from cudf_b200.aggregation import Aggregation
+    from cudf_b200.distributed import exchange_rows
+    from cudf_b200.partition import hash_partition
+    w = workloads.make(5, 60_000)
+    created = False
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29541")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+        created = True
+    try:
+        cols = [cb.Column.from_host(c) for c in w.keys + [v for v, _ in w.requests]]
+        parts, offsets = hash_partition(cb.Table(cols), len(w.keys), 1)
+        recv = exchange_rows(parts, offsets, 1)
+        gb = cb.GroupBy(cb.Table(recv[:2]))
+        reqs = [cb.GroupByRequest(recv[2 + i], [Aggregation(Kind(a)) for a in aggs]) for i, (_, aggs) in enumerate(w.requests)]
+        got = _to_host(gb.aggregate(reqs))
+    finally:
+        if created:
+            dist.destroy_process_group()
+    exp = oracle.groupby(w.keys, w.requests)
+    H.assert_same_result(got, exp, w.requests, scales=H.result_scales(w.keys, w.requests, w.null_policy))
