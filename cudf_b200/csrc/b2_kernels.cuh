@@ -1079,6 +1079,24 @@ __global__ void k_pack_scatter(const u64* __restrict__ tbl, i64 cap, int stride,
   }
 }
 
+// Slot of a packed key in a table that may hold a dense region (a table filled by the fused kernel in
+// dense mode keeps the in-box keys there): in-box keys are addressed directly, the rest is hashed, so
+// that a key never ends up in both regions.
+__device__ __forceinline__ i64 table_slot_packed(const DPlan& P, u64* tbl, i64 cap, int stride, u64 key, DCtrl* ctrl,
+                                                 int* s_new)
+{
+  if (ctrl->dense_slots != 0 && ctrl->dense.enabled && key != EMPTY) {
+    const int di = dense_index(P, ctrl->dense, key);
+    if (di >= 0) {
+      const i64 g = cap + 1 + (i64)di;
+      u64* kp = tbl + g * stride;
+      if (*(volatile u64*)kp == EMPTY && atomicCAS(kp, EMPTY, key) == EMPTY) atomicAdd(s_new, 1);
+      return g;
+    }
+  }
+  return gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, s_new);
+}
+
 // fixed-size chunks: chunk d = { count, overflow, records[chunk_records] }
 __global__ void k_pack_chunks(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, const DCtrl* ctrl,
                               const u64* __restrict__ counts, u64* __restrict__ cursors /* zeroed */,
@@ -1129,7 +1147,7 @@ k_merge_chunks(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, 
     if ((u64)r >= chunk[0] || chunk[1] != 0) continue;
     const u64* rec = chunk + 2 + r * stride;
     const u64 key  = rec[0];
-    const i64 g    = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
+    const i64 g    = table_slot_packed(P, tbl, cap, stride, key, ctrl, &s_new);
     if (g < 0) continue;
     u64* slot = tbl + g * stride;
     for (int k = 0; k < P.ncells; ++k) {
@@ -1157,7 +1175,7 @@ k_merge(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* 
   for (i64 r = (i64)blockIdx.x * blockDim.x + threadIdx.x; r < nrecs; r += (i64)gridDim.x * blockDim.x) {
     const u64* rec = recs + r * stride;
     const u64 key  = rec[0];
-    const i64 g    = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
+    const i64 g    = table_slot_packed(P, tbl, cap, stride, key, ctrl, &s_new);
     if (g < 0) continue;
     u64* slot = tbl + g * stride;
     for (int c = 0; c < P.ncells; ++c) {
