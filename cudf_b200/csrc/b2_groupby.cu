@@ -735,7 +735,8 @@ void pack_table(b2_groupby_state& st, int nparts, cudaStream_t stream, Scratch& 
   if ((int64_t)run != G) B2_FAIL(B2_INTERNAL_ERROR, "pack: group count mismatch");
   CUDA_TRY(cudaMemcpyAsync(d_cursor, starts.data(), (size_t)nparts * sizeof(u64), cudaMemcpyHostToDevice, stream));
   out = Scratch(std::max<size_t>(8, (size_t)G * st.plan.stride * 8), stream);
-  k_pack_scatter<<<grid, 256, 0, stream>>>(st.table, st.cap, st.plan.stride, nparts, st.ctrl, d_cursor, (u64*)out.p);
+  k_pack_scatter<<<grid, 256, (size_t)nparts * 2 * sizeof(u64), stream>>>(st.table, st.cap, st.plan.stride, nparts, st.ctrl, d_cursor,
+                                                                          (u64*)out.p);
   CUDA_TRY(cudaGetLastError());
   CUDA_TRY(cudaStreamSynchronize(stream));  // `starts` is read by the copy above
   g_stats.kernel_launches += 2;

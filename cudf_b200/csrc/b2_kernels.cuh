@@ -1063,15 +1063,40 @@ __global__ void k_pack_count(const u64* __restrict__ tbl, i64 cap, int stride, i
     if (s_cnt[p]) atomicAdd(&counts[p], s_cnt[p]);
 }
 
-__global__ void k_pack_scatter(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, const DCtrl* ctrl,
-                               u64* __restrict__ cursors /* start offsets, advanced */, u64* __restrict__ out)
+// Scatter of the occupied slots into destination-major order.  Each CTA owns a contiguous range of
+// slots: it counts its records per destination in shared memory, reserves its output ranges with ONE
+// global atomic per destination, then scatters with shared-memory cursors (one global atomic per
+// record on a handful of addresses serialised: 3.5 ms for 5.4M records).
+__global__ void __launch_bounds__(256)
+k_pack_scatter(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, const DCtrl* ctrl,
+               u64* __restrict__ cursors /* start offsets, advanced */, u64* __restrict__ out)
 {
-  const i64 last = cap + (i64)ctrl->dense_slots;
-  for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s <= last; s += (i64)gridDim.x * blockDim.x) {
+  extern __shared__ u64 s_pack[];  // [nparts] counts, then [nparts] bases
+  u64* s_cnt  = s_pack;
+  u64* s_base = s_pack + nparts;
+  const i64 last  = cap + (i64)ctrl->dense_slots;
+  const i64 per   = (last + 1 + gridDim.x - 1) / gridDim.x;
+  const i64 lo    = (i64)blockIdx.x * per;
+  const i64 hi    = min(last + 1, lo + per);
+  for (int p = threadIdx.x; p < nparts; p += blockDim.x) s_cnt[p] = 0;
+  __syncthreads();
+  for (i64 s = lo + threadIdx.x; s < hi; s += blockDim.x) {
+    const u64 key = s != cap ? tbl[s * stride] : EMPTY;
+    const bool occ = s != cap ? key != EMPTY : ctrl->special_used != 0;
+    if (occ) atomicAdd(&s_cnt[owner_of(mix64(key), (u32)nparts)], 1ull);
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < nparts; p += blockDim.x) {
+    s_base[p] = s_cnt[p] ? atomicAdd(&cursors[p], s_cnt[p]) : 0;
+    s_cnt[p]  = 0;
+  }
+  __syncthreads();
+  for (i64 s = lo + threadIdx.x; s < hi; s += blockDim.x) {
     const u64 key = s != cap ? tbl[s * stride] : EMPTY;
     const bool occ = s != cap ? key != EMPTY : ctrl->special_used != 0;
     if (!occ) continue;
-    const u64 pos = atomicAdd(&cursors[owner_of(mix64(key), (u32)nparts)], 1ull);
+    const u32 p   = owner_of(mix64(key), (u32)nparts);
+    const u64 pos = s_base[p] + atomicAdd(&s_cnt[p], 1ull);
     u64* dst = out + pos * stride;
     const u64* src = tbl + s * stride;
     dst[0] = key;
