@@ -223,19 +223,35 @@ __device__ __forceinline__ u64 canonical_bits(const DKeyCol& c, i64 idx)
   return b;
 }
 
+// up to 8 bytes starting at an arbitrarily aligned address, as a little-endian word; bytes beyond
+// `nbytes` are zero.  Reads whole aligned 8-byte words (one or two), never a word without a wanted byte.
+__device__ __forceinline__ u64 load_bytes8(const unsigned char* p, int nbytes)
+{
+  const unsigned long long a = (unsigned long long)p;
+  const u64* w  = (const u64*)(a & ~7ull);
+  const int sh  = (int)(a & 7ull) * 8;
+  u64 v = __ldg(w) >> sh;
+  if (sh != 0 && (sh >> 3) + nbytes > 8) v |= __ldg(w + 1) << (64 - sh);
+  return nbytes >= 8 ? v : (v & ((1ull << (8 * nbytes)) - 1ull));
+}
+
 __device__ inline u64 hash_bytes(const unsigned char* p, i64 len, u64 h)
 {
-  i64 i = 0;
   // 8 bytes per step; the tail is zero padded and the length mixed in, so "ab" != "ab\0"
-  for (; i + 8 <= len; i += 8) {
-    u64 w = 0;
-#pragma unroll
-    for (int b = 0; b < 8; ++b) w |= (u64)p[i + b] << (8 * b);
-    h = mix64(h ^ w) + 0x9E3779B97F4A7C15ull;
+  for (i64 i = 0; i < len; i += 8) {
+    const int nb = (int)(len - i < 8 ? len - i : 8);
+    h = mix64(h ^ load_bytes8(p + i, nb)) + 0x9E3779B97F4A7C15ull;
   }
-  u64 w = 0;
-  for (int b = 0; i + b < len; ++b) w |= (u64)p[i + b] << (8 * b);
-  return mix64(h ^ w ^ ((u64)len << 56));
+  return mix64(h ^ ((u64)len << 56));
+}
+
+__device__ inline bool bytes_equal(const unsigned char* a, const unsigned char* b, i64 len)
+{
+  for (i64 i = 0; i < len; i += 8) {
+    const int nb = (int)(len - i < 8 ? len - i : 8);
+    if (load_bytes8(a + i, nb) != load_bytes8(b + i, nb)) return false;
+  }
+  return true;
 }
 
 __device__ inline u64 hash_row(const DPlan& P, i64 row)
@@ -274,10 +290,7 @@ __device__ inline bool rows_equal(const DPlan& P, i64 a, i64 b)
       const i64 ba = str_offset(c, ia), ea = str_offset(c, ia + 1);
       const i64 bb = str_offset(c, ib), eb = str_offset(c, ib + 1);
       if (ea - ba != eb - bb) return false;
-      const unsigned char* pa = c.data + ba;
-      const unsigned char* pb = c.data + bb;
-      for (i64 i = 0; i < ea - ba; ++i)
-        if (pa[i] != pb[i]) return false;
+      if (!bytes_equal(c.data + ba, c.data + bb, ea - ba)) return false;
     } else {
       if (canonical_bits(c, ia) != canonical_bits(c, ib)) return false;
     }
