@@ -903,7 +903,14 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
         Scratch lens((size_t)(G + 1) * sizeof(i64), stream), offs((size_t)(G + 1) * sizeof(i64), stream);
         k_string_lengths<<<grid_for(G, 256, 8), 256, 0, stream>>>(kc, plan->rep_rows, G, (i64*)lens.p, c.null_mask,
                                                                   plan->null_counts + MAX_OUTS + k);
-        k_exclusive_scan<<<1, 1024, 0, stream>>>((const i64*)lens.p, (i64*)offs.p, G);
+        {
+          const int64_t per = (int64_t)SCAN_BLOCK * SCAN_ITEMS;
+          const int nblocks = (int)((G + per - 1) / per);
+          Scratch totals((size_t)(nblocks + 1) * sizeof(i64), stream), bases((size_t)(nblocks + 1) * sizeof(i64), stream);
+          k_scan_block_totals<<<nblocks, SCAN_BLOCK, 0, stream>>>((const i64*)lens.p, G, (i64*)totals.p);
+          k_exclusive_scan<<<1, 1024, 0, stream>>>((const i64*)totals.p, (i64*)bases.p, nblocks);
+          k_scan_apply<<<nblocks, SCAN_BLOCK, 0, stream>>>((const i64*)lens.p, G, (const i64*)bases.p, (i64*)offs.p);
+        }
         CUDA_TRY(cudaGetLastError());
         i64 total = 0;
         CUDA_TRY(cudaMemcpyAsync(&total, (i64*)offs.p + G, sizeof(i64), cudaMemcpyDeviceToHost, stream));

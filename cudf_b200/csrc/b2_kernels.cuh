@@ -1024,6 +1024,59 @@ __global__ void __launch_bounds__(1024) k_exclusive_scan(const i64* __restrict__
   if (threadIdx.x == 0) out[n] = s_carry;
 }
 
+// exclusive scan of many elements in three steps: per-block totals, scan of the totals (one CTA),
+// per-block scan with the block's base added
+constexpr int SCAN_BLOCK = 1024;
+constexpr int SCAN_ITEMS = 4;  // elements per thread
+__global__ void __launch_bounds__(SCAN_BLOCK) k_scan_block_totals(const i64* __restrict__ in, i64 n, i64* __restrict__ totals)
+{
+  __shared__ i64 s_warp[32];
+  const i64 base = (i64)blockIdx.x * SCAN_BLOCK * SCAN_ITEMS;
+  i64 v = 0;
+  for (int j = 0; j < SCAN_ITEMS; ++j) {
+    const i64 i = base + (i64)threadIdx.x * SCAN_ITEMS + j;
+    if (i < n) v += in[i];
+  }
+  for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, d);
+  if ((threadIdx.x & 31) == 0) s_warp[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    i64 w = s_warp[threadIdx.x];
+    for (int d = 16; d > 0; d >>= 1) w += __shfl_xor_sync(0xFFFFFFFFu, w, d);
+    if (threadIdx.x == 0) totals[blockIdx.x] = w;
+  }
+}
+__global__ void __launch_bounds__(SCAN_BLOCK)
+k_scan_apply(const i64* __restrict__ in, i64 n, const i64* __restrict__ block_bases, i64* __restrict__ out)
+{
+  __shared__ i64 s_warp[32];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const i64 base = (i64)blockIdx.x * SCAN_BLOCK * SCAN_ITEMS;
+  i64 x[SCAN_ITEMS], mine = 0;
+  for (int j = 0; j < SCAN_ITEMS; ++j) {
+    const i64 i = base + (i64)threadIdx.x * SCAN_ITEMS + j;
+    x[j] = i < n ? in[i] : 0;
+    mine += x[j];
+  }
+  i64 v = mine;
+  for (int d = 1; d < 32; d <<= 1) { const i64 t = __shfl_up_sync(0xFFFFFFFFu, v, d); if (lane >= d) v += t; }
+  if (lane == 31) s_warp[wid] = v;
+  __syncthreads();
+  if (wid == 0) {
+    i64 w = s_warp[lane];
+    for (int d = 1; d < 32; d <<= 1) { const i64 t = __shfl_up_sync(0xFFFFFFFFu, w, d); if (lane >= d) w += t; }
+    s_warp[lane] = w;
+  }
+  __syncthreads();
+  i64 run = block_bases[blockIdx.x] + (wid ? s_warp[wid - 1] : 0) + (v - mine);
+  for (int j = 0; j < SCAN_ITEMS; ++j) {
+    const i64 i = base + (i64)threadIdx.x * SCAN_ITEMS + j;
+    if (i < n) out[i] = run;
+    run += x[j];
+  }
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == SCAN_BLOCK - 1) out[n] = run;
+}
+
 template <typename OffT>
 __global__ void k_string_copy(DKeyCol c, const int* __restrict__ rows, i64 ngroups, const i64* __restrict__ offs,
                               OffT* __restrict__ out_offs, unsigned char* __restrict__ chars)
