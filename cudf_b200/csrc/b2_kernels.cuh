@@ -52,6 +52,21 @@ __global__ void k_table_init(u64* __restrict__ tbl, i64 nslots, const __grid_con
 }
 
 // ------------------------------------------------------------------------------ probing
+// Every 64th probe of a long chain: publish this CTA's unreported claims and give up when the table
+// is over its claim limit.  A table that is too small fills up within the first wave of tiles, before
+// any CTA reaches its per-tile bookkeeping; without this every row of that wave would walk the full
+// probe limit through a full table.
+__device__ __forceinline__ bool probe_gave_up(int p, DCtrl* ctrl, int* s_new)
+{
+  if ((p & 63) != 63) return false;
+  const int c = atomicExch(s_new, 0);
+  if (c) {
+    const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)c) + (u64)c;
+    if (tot > ctrl->claim_limit) ctrl->overflow = 1;
+  }
+  return *(volatile u32*)&ctrl->overflow != 0;
+}
+
 // Global table, packed keys.  Returns the slot index, or -1 after setting ctrl->overflow.
 __device__ __forceinline__ i64 gmem_find_insert_packed(u64* tbl, i64 cap, int stride, u64 key, u64 h,
                                                        DCtrl* ctrl, int* s_new)
@@ -70,6 +85,7 @@ __device__ __forceinline__ i64 gmem_find_insert_packed(u64* tbl, i64 cap, int st
       if (old == EMPTY) { atomicAdd(s_new, 1); return idx; }
       if (old == key) return idx;
     }
+    if (probe_gave_up(p, ctrl, s_new)) return -1;
     if (++idx == cap) idx = 0;
   }
   ctrl->overflow = 1;
@@ -90,6 +106,7 @@ __device__ __forceinline__ i64 gmem_finish_packed(u64* tbl, i64 cap, int stride,
       if (old == EMPTY) { atomicAdd(s_new, 1); return idx; }
       if (old == key) return idx;
     }
+    if (probe_gave_up(p, ctrl, s_new)) return -1;
     if (++idx == cap) idx = 0;
   }
   ctrl->overflow = 1;
@@ -111,6 +128,7 @@ __device__ __forceinline__ i64 gmem_find_insert_rows(const DPlan& P, u64* tbl, i
       if (k == EMPTY) { atomicAdd(s_new, 1); return idx; }
     }
     if ((k & 0xFFFFFFFF00000000ull) == tag && rows_equal(P, row, (i64)(u32)k)) return idx;
+    if (probe_gave_up(p, ctrl, s_new)) return -1;
     if (++idx == cap) idx = 0;
   }
   ctrl->overflow = 1;
