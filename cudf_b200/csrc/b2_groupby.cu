@@ -618,7 +618,7 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
     S = budget / (8 + cell_bytes) - 1;                      // hashed mode: key cell + accumulators
     if (S >= 256) {
       layout = sc.f32mean ? SL_F32MEAN : SL_GENERIC;
-      fill_limit = (int)(S * 0.75);
+      fill_limit = (int)(S * SMEM_FILL);
       smem = (size_t)budget;
       // dense mode: accumulators + one occupancy bit per slot
       if (sc.key_mode == KM_PACKED && gb.table_variant != 3)
