@@ -696,6 +696,7 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
       float ms = 0.f;
       if (cudaEventElapsedTime(&ms, kernel_events().a, kernel_events().b) == cudaSuccess) g_stats.aggregate_kernel_ms += ms;
       else cudaGetLastError();
+      if (getenv("B2_TRACE")) fprintf(stderr, "[b2] attempt %d cap %lld kernel %.3f ms overflow %d claimed %llu\n", attempt, (long long)cap, ms, (int)st.host_ctrl.overflow, (unsigned long long)st.host_ctrl.nclaimed);
     }
     if (!st.host_ctrl.overflow) break;
     if (cap >= full) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow at full capacity");

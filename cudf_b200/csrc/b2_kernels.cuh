@@ -57,17 +57,19 @@ __global__ void k_table_init(u64* __restrict__ tbl, i64 nslots, const __grid_con
 }
 
 // ------------------------------------------------------------------------------ probing
-// Every 64th probe of a long chain: publish this CTA's unreported claims and give up when the table
-// is over its claim limit.  A table that is too small fills up within the first wave of tiles, before
-// any CTA reaches its per-tile bookkeeping; without this every row of that wave would walk the full
-// probe limit through a full table.
+// Long probe chains: every 8th probe looks at the overflow flag and gives up when it is set (the table
+// is over its claim limit and this attempt will be discarded); every 64th probe also publishes this
+// CTA's unreported claims, so that a table that fills up within the first wave of tiles — before any
+// CTA reaches its per-tile bookkeeping — is noticed.
 __device__ __forceinline__ bool probe_gave_up(int p, DCtrl* ctrl, int* s_new)
 {
-  if ((p & 63) != 63) return false;
-  const int c = atomicExch(s_new, 0);
-  if (c) {
-    const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)c) + (u64)c;
-    if (tot > ctrl->claim_limit) ctrl->overflow = 1;
+  if ((p & 7) != 7) return false;
+  if ((p & 63) == 63) {
+    const int c = atomicExch(s_new, 0);
+    if (c) {
+      const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)c) + (u64)c;
+      if (tot > ctrl->claim_limit) ctrl->overflow = 1;
+    }
   }
   return *(volatile u32*)&ctrl->overflow != 0;
 }
@@ -719,7 +721,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
       tot_hit += my_hit; tot_miss += my_miss;
       my_hit = 0; my_miss = 0;
     }
-    if (tid == 0 && (*(volatile int*)&s_new != 0 || ((tile / gridDim.x) & 7) == 7)) {
+    if (tid == 0) {
       const int c = atomicExch(&s_new, 0);
       if (c) {
         const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)c) + (u64)c;
@@ -830,17 +832,65 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
 constexpr int HLL_BITS = 13;  // 8192 registers (32 KB of static shared memory), standard error 1.15 %
 constexpr int HLL_REGS = 1 << HLL_BITS;
 
+// packed keys of 4 consecutive rows through one vector load per key column (requires PF_VEC_KEYS and
+// a full group of 4 rows); clears the bits of dropped rows in `act`
+__device__ __forceinline__ void packed_keys4(const DPlan& P, i64 row0, u64 (&kk)[4], u32& act)
+{
+#pragma unroll
+  for (int j = 0; j < 4; ++j) kk[j] = 0;
+  for (int k = 0; k < P.nkeys; ++k) {
+    const DKeyCol& c = P.keys[k];
+    const unsigned char* src = c.data + (c.offset + row0) * c.width;
+    u64 f[4];
+    if (c.width == 4) {
+      const uint4 q = __ldg((const uint4*)src);
+      f[0] = q.x; f[1] = q.y; f[2] = q.z; f[3] = q.w;
+    } else if (c.width == 8) {
+      const ulonglong2 q0 = __ldg((const ulonglong2*)src), q1 = __ldg((const ulonglong2*)src + 1);
+      f[0] = q0.x; f[1] = q0.y; f[2] = q1.x; f[3] = q1.y;
+    } else if (c.width == 2) {
+      const uint2 q = __ldg((const uint2*)src);
+      f[0] = q.x & 0xFFFFu; f[1] = q.x >> 16; f[2] = q.y & 0xFFFFu; f[3] = q.y >> 16;
+    } else {
+      const u32 q = __ldg((const u32*)src);
+      f[0] = q & 0xFFu; f[1] = (q >> 8) & 0xFFu; f[2] = (q >> 16) & 0xFFu; f[3] = q >> 24;
+    }
+    u32 vn = 0xFu;
+    if (c.mask) {
+      vn = valid_nibble(c.mask, c.offset + row0, 4);
+      if (!P.include_nulls) act &= vn;  // EXCLUDE: a null key drops the row
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool isnull = c.nullbit >= 0 && !((vn >> j) & 1u);
+      kk[j] |= isnull ? (1ull << c.nullbit) : (f[j] << c.shift);
+    }
+  }
+  for (int f = 0; f < P.nfilters; ++f) act &= valid_nibble(P.filters[f], P.filter_offsets[f] + row0, 4);
+}
+
 __global__ void __launch_bounds__(1024) k_hll(const __grid_constant__ DPlan P, u32* __restrict__ regs)
 {
   __shared__ u32 s_regs[HLL_REGS];
   for (int i = threadIdx.x; i < HLL_REGS; i += blockDim.x) s_regs[i] = 0;
   __syncthreads();
-  for (i64 row = (i64)blockIdx.x * blockDim.x + threadIdx.x; row < P.nrows; row += (i64)gridDim.x * blockDim.x) {
-    if (!row_active(P, row)) continue;
-    const u64 h = (P.key_mode == KM_PACKED) ? mix64(pack_key(P, row) ^ 0x5bd1e9955bd1e995ull) : hash_row(P, row);
+  auto fold = [&](u64 h) {
     const u32 idx  = (u32)(h >> (64 - HLL_BITS));
     const u32 rank = (u32)__clzll((i64)((h << HLL_BITS) | (1ull << (HLL_BITS - 1)))) + 1u;
     if (s_regs[idx] < rank) atomicMax(&s_regs[idx], rank);
+  };
+  const i64 nquads = (P.key_mode == KM_PACKED && (P.flags & PF_VEC_KEYS)) ? P.nrows / 4 : 0;
+  for (i64 q = (i64)blockIdx.x * blockDim.x + threadIdx.x; q < nquads; q += (i64)gridDim.x * blockDim.x) {
+    u64 kk[4];
+    u32 act = 0xFu;
+    packed_keys4(P, q * 4, kk, act);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if ((act >> j) & 1u) fold(mix64(kk[j] ^ 0x5bd1e9955bd1e995ull));
+  }
+  for (i64 row = nquads * 4 + (i64)blockIdx.x * blockDim.x + threadIdx.x; row < P.nrows; row += (i64)gridDim.x * blockDim.x) {
+    if (!row_active(P, row)) continue;
+    fold((P.key_mode == KM_PACKED) ? mix64(pack_key(P, row) ^ 0x5bd1e9955bd1e995ull) : hash_row(P, row));
   }
   __syncthreads();
   for (int i = threadIdx.x; i < HLL_REGS; i += blockDim.x)
