@@ -12,6 +12,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <chrono>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -521,6 +522,26 @@ void bind_plan_inputs(DPlan& P, const Schema& sc, const b2_groupby& gb, const b2
 }
 
 // ------------------------------------------------------------------------------ table management
+// B2_TRACE=1 in the environment prints phase times to stderr (each mark synchronises the stream, so
+// the traced call itself is slower)
+struct Trace {
+  bool on;
+  cudaStream_t stream;
+  std::chrono::steady_clock::time_point t0;
+  explicit Trace(cudaStream_t s) : on(getenv("B2_TRACE") != nullptr), stream(s)
+  {
+    if (on) { cudaStreamSynchronize(stream); t0 = std::chrono::steady_clock::now(); }
+  }
+  void mark(const char* what)
+  {
+    if (!on) return;
+    cudaStreamSynchronize(stream);
+    const auto t1 = std::chrono::steady_clock::now();
+    fprintf(stderr, "[b2]   %-28s %8.3f ms\n", what, std::chrono::duration<double, std::milli>(t1 - t0).count());
+    t0 = t1;
+  }
+};
+
 int grid_for(int64_t items, int block, int per_sm)
 {
   const int64_t want = (items + block - 1) / block;
@@ -556,7 +577,7 @@ void alloc_table(b2_groupby_state& st, int64_t cap, double max_load, cudaStream_
   static_assert(sizeof(DCtrl) / 4 <= 256, "the control block is initialised by one CTA of k_table_init");
   h.dense_slots = (u64)st.dense_slots;
   st.host_ctrl = h;
-  k_table_init<<<grid_for(cap + 1 + st.dense_slots, 256, 16), 256, 0, stream>>>(st.table, cap + 1 + st.dense_slots, st.plan, st.ctrl,
+  k_table_init<<<grid_for((cap + 1 + st.dense_slots) * st.plan.stride / 2 + 1, 256, 16), 256, 0, stream>>>(st.table, cap + 1 + st.dense_slots, st.plan, st.ctrl,
                                                                                   h.claim_limit, h.dense_slots);
   CUDA_TRY(cudaGetLastError());
   g_stats.kernel_launches++;
@@ -689,7 +710,9 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
   else cap = SPECULATIVE_CAP;
   for (int attempt = 1;; ++attempt) {
     g_stats.table_attempts = attempt;
+    Trace trace(stream);
     alloc_table(st, cap, cap >= full ? 1.0 : MAX_LOAD, stream, gb.table_variant != 1 && gb.table_variant != 3);
+    trace.mark("table allocation + init");
     run_aggregate(st, gb, stream);
     read_ctrl(st, stream);
     {
@@ -704,6 +727,7 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
       // the speculative table was too small: count the distinct keys (HyperLogLog, one pass over the
       // key columns) and size the table for them
       const int64_t est = estimate_groups(st, stream);
+      trace.mark("HyperLogLog estimate");
       cap = std::min(full, std::max<int64_t>(cap * 16, (int64_t)((double)est * 1.10 / 0.6) + 1024));
     } else {
       cap = (cap * 4 < full) ? cap * 4 : full;  // the estimate fell short (it is within a few percent: rare)
@@ -822,6 +846,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
   out->stream = stream;
   OwnedGuard guard{out};
 
+  Trace trace(stream);
   read_ctrl(st, stream);
   if (st.table && st.host_ctrl.chunk_overflow) B2_FAIL(B2_LOGIC_ERROR, "partial-record chunk overflow");
   if (st.table && st.host_ctrl.overflow) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow while merging partial records");
@@ -881,11 +906,13 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
   }
 
   std::vector<u32> h_nulls(MAX_OUTS + MAX_KEYS, 0);
+  trace.mark("finalize: output allocation");
   if (G > 0) {
     CUDA_TRY(cudaMemsetAsync(&st.ctrl->out_cursor, 0, sizeof(u64), stream));
-    k_finalize<<<grid_for(st.cap + 1 + st.dense_slots, 256, 8), 256, 0, stream>>>(st.plan, *plan, st.table, st.cap, st.ctrl);
+    k_finalize<<<grid_for((st.cap + 1 + st.dense_slots + FIN_ITEMS - 1) / FIN_ITEMS, FIN_BLOCK, 8), FIN_BLOCK, 0, stream>>>(st.plan, *plan, st.table, st.cap, st.ctrl);
     CUDA_TRY(cudaGetLastError());
     g_stats.kernel_launches++;
+    trace.mark("finalize: k_finalize");
 
     if (sc.key_mode == KM_ROWS) {
       if ((int)st.row_keys.size() != sc.nkeys) B2_FAIL(B2_INTERNAL_ERROR, "row-keyed state without bound key views");
@@ -916,6 +943,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
         i64 total = 0;
         CUDA_TRY(cudaMemcpyAsync(&total, (i64*)offs.p + G, sizeof(i64), cudaMemcpyDeviceToHost, stream));
         CUDA_TRY(cudaStreamSynchronize(stream));
+        trace.mark("finalize: string lengths+scan");
         // INT64 offsets once the chars pass the reference's large-strings threshold
         // (cpp/src/strings/utilities.cu:150-157)
         const bool big = total > 0x7FFFFFFFll;
@@ -936,6 +964,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
     }
     CUDA_TRY(cudaMemcpyAsync(h_nulls.data(), null_counts.p, null_counts.bytes, cudaMemcpyDeviceToHost, stream));
     CUDA_TRY(cudaStreamSynchronize(stream));
+    trace.mark("finalize: key gather + nulls");
   } else {
     // empty result: STRING keys still carry a one-entry offsets child
     for (int k = 0; k < sc.nkeys; ++k)
@@ -1083,7 +1112,7 @@ extern "C" b2_status b2_groupby_aggregate_noalloc(b2_groupby* gb, const b2_aggre
     CUDA_TRY(cudaMemcpyAsync(ctrl, &h, sizeof(DCtrl), cudaMemcpyHostToDevice, stream));
     CUDA_TRY(cudaMemsetAsync(null_counts, 0, nulls_bytes, stream));
     CUDA_TRY(cudaStreamSynchronize(stream));  // `h` is a stack object
-    k_table_init<<<grid_for(cap + 1, 256, 16), 256, 0, stream>>>(table, cap + 1, P, nullptr, 0);
+    k_table_init<<<grid_for((cap + 1) * P.stride / 2 + 1, 256, 16), 256, 0, stream>>>(table, cap + 1, P, nullptr, 0);
     CUDA_TRY(cudaGetLastError());
     int64_t G = 0;
     if (P.nrows > 0) {
@@ -1117,7 +1146,7 @@ extern "C" b2_status b2_groupby_aggregate_noalloc(b2_groupby* gb, const b2_aggre
     plan->null_counts = null_counts;
     u32 h_nulls[MAX_OUTS + MAX_KEYS] = {};
     if (G > 0) {
-      k_finalize<<<grid_for(cap + 1, 256, 8), 256, 0, stream>>>(P, *plan, table, cap, ctrl);
+      k_finalize<<<grid_for((cap + 1 + FIN_ITEMS - 1) / FIN_ITEMS, FIN_BLOCK, 8), FIN_BLOCK, 0, stream>>>(P, *plan, table, cap, ctrl);
       CUDA_TRY(cudaGetLastError());
       g_stats.kernel_launches += 1;
       CUDA_TRY(cudaMemcpyAsync(h_nulls, null_counts, sizeof(h_nulls), cudaMemcpyDeviceToHost, stream));

@@ -48,11 +48,24 @@ __global__ void k_table_init(u64* __restrict__ tbl, i64 nslots, const __grid_con
     if (threadIdx.x == offsetof(DCtrl, dense_slots) / 4) v = (u32)dense_slots;
     ((u32*)ctrl)[threadIdx.x] = v;
   }
-  const int stride = P.stride;
-  for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s < nslots; s += (i64)gridDim.x * blockDim.x) {
-    u64* slot = tbl + s * stride;
-    slot[0]   = EMPTY;
-    for (int c = 0; c < P.ncells; ++c) slot[1 + c] = cell_identity(P.cells[c].op);
+  // the table is written as one linear run of 8-byte words, two per thread and step (16-byte stores):
+  // word w belongs to cell (w mod stride) of slot (w div stride); cell 0 is the key
+  __shared__ u64 s_init[MAX_CELLS + 1];
+  const u32 stride = (u32)P.stride;
+  if (threadIdx.x <= (u32)P.ncells) s_init[threadIdx.x] = threadIdx.x == 0 ? EMPTY : cell_identity(P.cells[threadIdx.x - 1].op);
+  __syncthreads();
+  const i64 nwords = nslots * (i64)stride;
+  const i64 span   = (i64)blockDim.x * 2;
+  for (i64 base = (i64)blockIdx.x * span; base < nwords; base += (i64)gridDim.x * span) {
+    const u32 c0 = (u32)(base % stride);  // same for the whole CTA: one 64-bit division per step
+    const i64 w  = base + 2 * (i64)threadIdx.x;
+    const u32 c  = (c0 + 2u * threadIdx.x) % stride;
+    const u32 c1 = c + 1u == stride ? 0u : c + 1u;
+    if (w + 1 < nwords) {
+      *(ulonglong2*)(tbl + w) = make_ulonglong2(s_init[c], s_init[c1]);
+    } else if (w < nwords) {
+      tbl[w] = s_init[c];
+    }
   }
 }
 
@@ -951,28 +964,53 @@ __device__ __forceinline__ void clear_bit(u32* mask, i64 g, u32* counter)
   atomicAdd(counter, 1u);
 }
 
-__global__ void k_finalize(const __grid_constant__ DPlan P, const __grid_constant__ DOutPlan O,
-                           const u64* __restrict__ tbl, i64 cap, DCtrl* ctrl)
+constexpr int FIN_BLOCK = 256;
+constexpr int FIN_ITEMS = 8;  // slots per thread per chunk
+
+// Occupied slots are compacted chunk by chunk: a CTA counts the occupied slots of its chunk
+// (FIN_BLOCK x FIN_ITEMS slots), reserves that many output rows with ONE atomic on the cursor, and its
+// threads write their groups at the reserved positions.  (One reservation per warp and 32 slots made
+// the single cursor the bottleneck of large tables: 6M atomics on one address for 200M slots.)
+__global__ void __launch_bounds__(FIN_BLOCK) k_finalize(const __grid_constant__ DPlan P, const __grid_constant__ DOutPlan O,
+                                                        const u64* __restrict__ tbl, i64 cap, DCtrl* ctrl)
 {
+  __shared__ u32 s_wcount[FIN_BLOCK / 32];
+  __shared__ u32 s_ballot[FIN_BLOCK / 32][FIN_ITEMS];
+  __shared__ u64 s_base;
   const int stride = P.stride;
   const i64 nslots = cap + 1 + (i64)ctrl->dense_slots;
-  const i64 nwarp_iters = (nslots + 31) / 32;
-  const int lane = threadIdx.x & 31;
-  const i64 warp0 = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
-  for (i64 w = warp0; w < nwarp_iters; w += nwarps) {
-    const i64 s = w * 32 + lane;
-    u64 key = EMPTY;
-    bool occ = false;
-    if (s < nslots && s != cap) { key = tbl[s * stride]; occ = key != EMPTY; }
-    else if (s == cap) { occ = ctrl->special_used != 0; }
-    const u32 m = __ballot_sync(0xFFFFFFFFu, occ);
-    if (m == 0) continue;
-    u64 base = 0;
-    if (lane == 0) base = atomicAdd(&ctrl->out_cursor, (u64)__popc(m));
-    base = __shfl_sync(0xFFFFFFFFu, base, 0);
-    if (!occ) continue;
-    const i64 g = (i64)base + __popc(m & ((1u << lane) - 1u));
+  const i64 chunk  = (i64)FIN_BLOCK * FIN_ITEMS;
+  const i64 nchunks = (nslots + chunk - 1) / chunk;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  for (i64 ch = blockIdx.x; ch < nchunks; ch += gridDim.x) {
+    u32 wtotal = 0;
+#pragma unroll
+    for (int j = 0; j < FIN_ITEMS; ++j) {
+      const i64 s = ch * chunk + (i64)j * FIN_BLOCK + threadIdx.x;
+      bool occ = false;
+      if (s < nslots && s != cap) occ = tbl[s * stride] != EMPTY;
+      else if (s == cap) occ = ctrl->special_used != 0;
+      const u32 m = __ballot_sync(0xFFFFFFFFu, occ);
+      if (lane == 0) s_ballot[wid][j] = m;
+      wtotal += __popc(m);
+    }
+    if (lane == 0) s_wcount[wid] = wtotal;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      u32 tot = 0;
+      for (int w = 0; w < FIN_BLOCK / 32; ++w) { const u32 c = s_wcount[w]; s_wcount[w] = tot; tot += c; }
+      s_base = tot ? atomicAdd(&ctrl->out_cursor, (u64)tot) : 0ull;
+    }
+    __syncthreads();
+    u64 next = s_base + s_wcount[wid];  // first output row of this warp's groups
+#pragma unroll 1
+    for (int j = 0; j < FIN_ITEMS; ++j) {
+      const u32 m = s_ballot[wid][j];
+      const i64 g = (i64)next + __popc(m & ((1u << lane) - 1u));
+      next += __popc(m);
+      if (!((m >> lane) & 1u)) continue;
+      const i64 s = ch * chunk + (i64)j * FIN_BLOCK + threadIdx.x;
+      const u64 key = s == cap ? EMPTY : tbl[s * stride];
     const u64* cells = tbl + s * stride + 1;
 
     // keys
@@ -1029,6 +1067,8 @@ __global__ void k_finalize(const __grid_constant__ DPlan P, const __grid_constan
       }
       if (!valid && oc.mask) clear_bit(oc.mask, g, O.null_counts + oc.null_slot);
     }
+    }
+    __syncthreads();  // the shared arrays are rewritten by the next chunk
   }
 }
 
