@@ -124,6 +124,8 @@ struct DCtrl {
   u64 reserved;
   u64 chunk_overflow;  // a sender of merged chunks had more records than a chunk holds
   u64 dense_slots;     // slots after the special slot that are addressed directly by dense-box position
+  u64 t_phase[5];      // CTA 0 of the fused kernel: %globaltimer at start, after sampling, after the
+                       // shared-table init, after the row loop, after the merge (diagnostics)
   DDense dense;
 };
 

@@ -719,6 +719,12 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
       float ms = 0.f;
       if (cudaEventElapsedTime(&ms, kernel_events().a, kernel_events().b) == cudaSuccess) g_stats.aggregate_kernel_ms += ms;
       else cudaGetLastError();
+      if (getenv("B2_TRACE") && st.host_ctrl.t_phase[4] > st.host_ctrl.t_phase[0]) {
+        const u64* t = st.host_ctrl.t_phase;
+        fprintf(stderr, "[b2]   CTA 0: sample %.1f us, shared init %.1f us, row loop %.1f us, merge %.1f us\n",
+                (t[1] > t[0] ? t[1] - t[0] : 0) * 1e-3, ((t[1] > t[0] ? t[2] - t[1] : t[2] - t[0])) * 1e-3, (t[3] - t[2]) * 1e-3,
+                (t[4] - t[3]) * 1e-3);
+      }
       if (getenv("B2_TRACE")) fprintf(stderr, "[b2] attempt %d cap %lld kernel %.3f ms overflow %d claimed %llu\n", attempt, (long long)cap, ms, (int)st.host_ctrl.overflow, (unsigned long long)st.host_ctrl.nclaimed);
     }
     if (!st.host_ctrl.overflow) break;

@@ -222,7 +222,7 @@ __device__ __forceinline__ u64 dense_key(const DPlan& P, const DDense& D, u32 id
   u64 key = 0;
   for (int k = 0; k < P.nkeys; ++k) {
     const DKeyCol& c = P.keys[k];
-    const u64 f = (u64)(idx / D.mult[k]) % D.range[k];
+    const u64 f = (u64)((idx / D.mult[k]) % (u32)D.range[k]);  // ranges fit 32 bits (their product does)
     if (c.nullbit >= 0 && f == D.range[k] - 1) {
       key |= 1ull << c.nullbit;
     } else {
@@ -247,22 +247,46 @@ __device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, 
   const i64 nsamp  = P.nrows < SAMPLE_ROWS ? P.nrows : SAMPLE_ROWS;
   const i64 stride = P.nrows / (nsamp > 0 ? nsamp : 1);
   if (P.key_mode == KM_PACKED) {
-    u64 key[4];
-    bool ok[4];
+    // Column by column, the 4 loads of a column issued together: the number of dependent DRAM round
+    // trips is the number of columns and masks, not 4 x that (row-major order serialised every load
+    // behind the previous one's use and cost 24 us per launch).
+    i64 rows[4];
+    u32 ok = 0;  // bit j: sample j of this thread takes part
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const i64 i   = (i64)threadIdx.x + (i64)j * blockDim.x;
-      const i64 row = i < nsamp ? i * stride + (stride > 1 ? (i * 7919) % stride : 0) : 0;
-      ok[j]  = i < nsamp && row_active(P, row);
-      key[j] = i < nsamp ? pack_key(P, row) : 0;
+      const i64 i = (i64)threadIdx.x + (i64)j * blockDim.x;
+      rows[j] = i < nsamp ? i * stride + (stride > 1 ? (i64)(((u64)i * 7919ull) % (u64)stride) : 0) : 0;
+      if (i < nsamp) ok |= 1u << j;
+    }
+    for (int f = 0; f < P.nfilters; ++f) {
+      u32 w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = __ldg(P.filters[f] + ((P.filter_offsets[f] + rows[j]) >> 5));
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (!((w[j] >> ((P.filter_offsets[f] + rows[j]) & 31)) & 1u)) ok &= ~(1u << j);
     }
     for (int k = 0; k < P.nkeys; ++k) {
       const DKeyCol& c = P.keys[k];
+      u32 valid = 0xFu;
+      if (c.mask) {
+        u32 w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w[j] = __ldg(c.mask + ((c.offset + rows[j]) >> 5));
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (!((w[j] >> ((c.offset + rows[j]) & 31)) & 1u)) valid &= ~(1u << j);
+        if (!P.include_nulls) ok &= valid;  // EXCLUDE: a null key drops the row (for every column)
+      }
+      u64 bits[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bits[j] = load_fixed_bits(c.data, c.offset + rows[j], c.width);
+      const int sh = 64 - 8 * c.width;
       i64 lo = 0x7FFFFFFFFFFFFFFFll, hi = (i64)0x8000000000000000ull;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        if (!ok[j] || (c.nullbit >= 0 && ((key[j] >> c.nullbit) & 1ull))) continue;
-        const i64 v = key_field(c, key[j]);
+        if (!((ok >> j) & 1u) || !((valid >> j) & 1u)) continue;
+        const i64 v = c.is_signed ? ((i64)(bits[j] << sh) >> sh) : (i64)bits[j];
         lo = v < lo ? v : lo;
         hi = v > hi ? v : hi;
       }
@@ -337,6 +361,13 @@ __device__ __forceinline__ u32 nibble_aligned(const u32* mask, u32 pos)
 //                 cached until `fill_limit`; a CTA whose cache stops paying off turns it off.
 // Rows whose key is not in shared memory go to the global table with global atomics.  At the end
 // every CTA merges its table into the global one.  There is no barrier inside the row loop.
+__device__ __forceinline__ u64 global_timer_ns()
+{
+  u64 t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
 template <int KM, int LAYOUT, int NKF, bool K8 = true>
 __global__ void __launch_bounds__(NKF > 0 ? LEAN_BLOCK : AGG_BLOCK, 1)
 k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* ctrl, int S_hash, int fill_limit,
@@ -348,9 +379,11 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
 
   const int stride = P.stride;
   const int tid    = threadIdx.x;
+  const bool timekeeper = blockIdx.x == 0 && tid == 0;
+  if (timekeeper) ctrl->t_phase[0] = global_timer_ns();
   if (LAYOUT != SL_NONE && KM == KM_PACKED && cap_dense > 0 && P.nrows >= SAMPLE_ROWS && blockDim.x == 1024) {
     sample_dense_box(P, cap_dense, &s_dense);
-    if (blockIdx.x == 0 && tid == 0) ctrl->dense = s_dense;  // for the host's statistics
+    if (timekeeper) { ctrl->dense = s_dense; ctrl->t_phase[1] = global_timer_ns(); }  // for the host's statistics
   } else if (tid == 0) {
     s_dense.enabled = 0;
   }
@@ -385,6 +418,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
     if (dense) for (int i = tid; i < (NS + 31) / 32; i += blockDim.x) socc[i] = 0;
   }
   __syncthreads();
+  if (timekeeper) ctrl->t_phase[2] = global_timer_ns();
 
   u32 my_hit = 0, my_miss = 0, tot_hit = 0, tot_miss = 0;
   const bool fast_ok = NKF > 0 && dense && (P.flags & PF_VEC_KEYS) && (P.flags & PF_VEC_VAL0) && (P.flags & PF_FAST);
@@ -465,19 +499,28 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
         d0 += x0 * mult; d1 += x1 * mult; d2 += x2 * mult; d3 += x3 * mult;
       }
       const u32 take = act & ~bad & vn;  // rows folded in shared memory
-#define B2_LEAN_FOLD(J, D, X)                                                                       \
+      // the four rows' shared-memory atomics are issued back to back; the counts they return are
+      // looked at afterwards, so that the warp waits for one round trip, not four
+      u32 o0 = 0, o1 = 0, o2 = 0, o3 = 0;
+#define B2_LEAN_FOLD(J, D, X, O)                                                                    \
       if (take & (1u << J)) {                                                                       \
         sred_add_f32(ssum_a + 4u * (D), (X));                                                       \
-        const u32 old = satom_add_u32(scnt_a + 4u * (D), 1u);                                       \
-        if (((old + 1u) & (F32_SPILL_AT - 1u)) == 0u) {                                             \
-          /* every F32_SPILL_AT-th addend moves the fp32 partial of this key to the fp64 global */  \
-          /* cell, so that no fp32 sum ever holds many more addends than that */                   \
-          const float part = atomicExch(ssum + (D), 0.f);                                           \
-          atomicAdd((double*)(tbl + dense_gslot((D) - copy_off) * stride + 1), (double)part);       \
-        }                                                                                           \
+        O = satom_add_u32(scnt_a + 4u * (D), 1u);                                                   \
       }
-      B2_LEAN_FOLD(0, d0, q.x) B2_LEAN_FOLD(1, d1, q.y) B2_LEAN_FOLD(2, d2, q.z) B2_LEAN_FOLD(3, d3, q.w)
+      B2_LEAN_FOLD(0, d0, q.x, o0) B2_LEAN_FOLD(1, d1, q.y, o1) B2_LEAN_FOLD(2, d2, q.z, o2) B2_LEAN_FOLD(3, d3, q.w, o3)
 #undef B2_LEAN_FOLD
+      // every F32_SPILL_AT-th addend moves the fp32 partial of this key to the fp64 global cell, so
+      // that no fp32 sum ever holds many more addends than that (rows not taken keep O = 0)
+#define B2_LEAN_SPILL(D, O)                                                                         \
+      if (((O + 1u) & (F32_SPILL_AT - 1u)) == 0u) {                                                 \
+        const float part = atomicExch(ssum + (D), 0.f);                                             \
+        atomicAdd((double*)(tbl + dense_gslot((D) - copy_off) * stride + 1), (double)part);         \
+      }
+      if ((((o0 + 1u) & (F32_SPILL_AT - 1u)) == 0u) | (((o1 + 1u) & (F32_SPILL_AT - 1u)) == 0u) |
+          (((o2 + 1u) & (F32_SPILL_AT - 1u)) == 0u) | (((o3 + 1u) & (F32_SPILL_AT - 1u)) == 0u)) {
+        B2_LEAN_SPILL(d0, o0) B2_LEAN_SPILL(d1, o1) B2_LEAN_SPILL(d2, o2) B2_LEAN_SPILL(d3, o3)
+      }
+#undef B2_LEAN_SPILL
       // rare rows: active but (a) null value -> only mark the group as present, (b) key outside the box
       const u32 rare = act & (bad | ~vn);
       if (rare) {
@@ -758,15 +801,20 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
 
   // ---- merge this CTA's table into the global table
   __syncthreads();
+  if (timekeeper) ctrl->t_phase[3] = global_timer_ns();
   if (LAYOUT != SL_NONE && !s_abort) {
     // CTAs start their merge at different slots so that they do not all hit the same global cells at once
     const int NM  = dense ? S : NS;  // dense mode: one pass over box positions, replicas reduced on the fly
     const int rot = (int)(((u64)blockIdx.x * 2654435761ull) % (u64)NM);
+    int dense_new = 0;  // dense-region key cells this thread was the first to claim
+#pragma unroll 2
     for (int i0 = tid; i0 < NM; i0 += blockDim.x) {
       const int i = i0 + rot < NM ? i0 + rot : i0 + rot - NM;
       if (dense) {
         // reduce the replicas of box position i in registers, then ONE merge into the dense region of
-        // the global table: no hashing, consecutive threads -> consecutive slots
+        // the global table: no hashing, consecutive threads -> consecutive slots.  The key cell is
+        // claimed with an unconditional exchange (every CTA writes the same key there), whose result
+        // is only counted after the accumulators' reductions are issued: no dependent round trip.
         const int copies = (int)s_dense.copies;
         bool present = false;
         for (int r = 0; r < copies; ++r) {
@@ -776,13 +824,13 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
         if (!present) continue;
         const u64 key = dense_key(P, s_dense, (u32)i);
         i64 g;
+        u64 old = 0;
         if (key == EMPTY) {
           g = cap;
           if (ctrl->special_used == 0) ctrl->special_used = 1;
         } else {
           g = cap + 1 + (i64)i;
-          u64* kp = tbl + g * stride;
-          if (*(volatile u64*)kp == EMPTY && atomicCAS(kp, EMPTY, key) == EMPTY) atomicAdd(&s_new, 1);
+          old = atomicExch(tbl + g * stride, key);
         }
         u64* slot = tbl + g * stride;
         if (LAYOUT == SL_F32MEAN) {
@@ -798,6 +846,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
             if (a != cell_identity(op)) cell_merge(slot + 1 + c, op, a);
           }
         }
+        if (old == EMPTY && key != EMPTY) ++dense_new;
         continue;
       }
       u64 key = skeys[i];
@@ -826,6 +875,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
         }
       }
     }
+    if (dense_new) atomicAdd(&s_new, dense_new);
   }
   __syncthreads();
   if (tid == 0) {
@@ -834,6 +884,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
       if (tot > ctrl->claim_limit) ctrl->overflow = 1;
     }
     if (dense) atomicAdd(&ctrl->reserved, 1ull);  // CTAs that ran with the dense key box
+    if (timekeeper) ctrl->t_phase[4] = global_timer_ns();
   }
 }
 
