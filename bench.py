@@ -5,7 +5,7 @@
 
 A "step" is one complete ``GroupBy(keys).aggregate(requests)`` call over one batch of synthetic input
 (table sizing + init, the fused aggregate pass, the group-count read-back, output allocation and
-finalisation).  At N = 1 the workload is configuration C2 of BASELINE.json (100M rows, composite
+finalisation).  At N = 1 the workload is configuration C2 of the benchmark specification (100M rows, composite
 int32 keys, float32 values with 2 % nulls, dropna() then mean, ~10K groups).  At N > 1 every rank
 holds its own C2-sized shard (weak scaling), aggregates it, hash-partitions its partial aggregates
 by owner, exchanges them with one all-to-all over NCCL and merges / finalises the groups it owns.

@@ -549,6 +549,15 @@ int grid_for(int64_t items, int block, int per_sm)
   return (int)std::max<int64_t>(1, std::min(want, cap));
 }
 
+// small tables: one slot per thread so that the chunks cover all SMs; large ones: 8 per thread
+void launch_finalize(const DPlan& P, const DOutPlan& O, const u64* table, int64_t cap, int64_t nslots, DCtrl* ctrl,
+                     cudaStream_t stream)
+{
+  const int64_t big = (int64_t)device_info().sms * 8 * FIN_BLOCK * FIN_ITEMS;
+  if (nslots >= big) k_finalize<FIN_ITEMS><<<grid_for((nslots + FIN_ITEMS - 1) / FIN_ITEMS, FIN_BLOCK, 8), FIN_BLOCK, 0, stream>>>(P, O, table, cap, ctrl);
+  else k_finalize<1><<<grid_for(nslots, FIN_BLOCK, 8), FIN_BLOCK, 0, stream>>>(P, O, table, cap, ctrl);
+}
+
 void free_table(b2_groupby_state& st, cudaStream_t stream)
 {
   if (st.table) { cudaFreeAsync(st.table, stream); st.table = nullptr; }
@@ -915,7 +924,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
   trace.mark("finalize: output allocation");
   if (G > 0) {
     CUDA_TRY(cudaMemsetAsync(&st.ctrl->out_cursor, 0, sizeof(u64), stream));
-    k_finalize<<<grid_for((st.cap + 1 + st.dense_slots + FIN_ITEMS - 1) / FIN_ITEMS, FIN_BLOCK, 8), FIN_BLOCK, 0, stream>>>(st.plan, *plan, st.table, st.cap, st.ctrl);
+    launch_finalize(st.plan, *plan, st.table, st.cap, st.cap + 1 + st.dense_slots, st.ctrl, stream);
     CUDA_TRY(cudaGetLastError());
     g_stats.kernel_launches++;
     trace.mark("finalize: k_finalize");
@@ -1152,7 +1161,7 @@ extern "C" b2_status b2_groupby_aggregate_noalloc(b2_groupby* gb, const b2_aggre
     plan->null_counts = null_counts;
     u32 h_nulls[MAX_OUTS + MAX_KEYS] = {};
     if (G > 0) {
-      k_finalize<<<grid_for((cap + 1 + FIN_ITEMS - 1) / FIN_ITEMS, FIN_BLOCK, 8), FIN_BLOCK, 0, stream>>>(P, *plan, table, cap, ctrl);
+      launch_finalize(P, *plan, table, cap, cap + 1, ctrl, stream);
       CUDA_TRY(cudaGetLastError());
       g_stats.kernel_launches += 1;
       CUDA_TRY(cudaMemcpyAsync(h_nulls, null_counts, sizeof(h_nulls), cudaMemcpyDeviceToHost, stream));

@@ -1058,27 +1058,28 @@ __device__ __forceinline__ void clear_bit(u32* mask, i64 g, u32* counter)
 }
 
 constexpr int FIN_BLOCK = 256;
-constexpr int FIN_ITEMS = 8;  // slots per thread per chunk
+constexpr int FIN_ITEMS = 8;  // slots per thread per chunk (1 for small tables, which otherwise fill few SMs)
 
 // Occupied slots are compacted chunk by chunk: a CTA counts the occupied slots of its chunk
 // (FIN_BLOCK x FIN_ITEMS slots), reserves that many output rows with ONE atomic on the cursor, and its
 // threads write their groups at the reserved positions.  (One reservation per warp and 32 slots made
 // the single cursor the bottleneck of large tables: 6M atomics on one address for 200M slots.)
+template <int ITEMS>
 __global__ void __launch_bounds__(FIN_BLOCK) k_finalize(const __grid_constant__ DPlan P, const __grid_constant__ DOutPlan O,
                                                         const u64* __restrict__ tbl, i64 cap, DCtrl* ctrl)
 {
   __shared__ u32 s_wcount[FIN_BLOCK / 32];
-  __shared__ u32 s_ballot[FIN_BLOCK / 32][FIN_ITEMS];
+  __shared__ u32 s_ballot[FIN_BLOCK / 32][ITEMS];
   __shared__ u64 s_base;
   const int stride = P.stride;
   const i64 nslots = cap + 1 + (i64)ctrl->dense_slots;
-  const i64 chunk  = (i64)FIN_BLOCK * FIN_ITEMS;
+  const i64 chunk  = (i64)FIN_BLOCK * ITEMS;
   const i64 nchunks = (nslots + chunk - 1) / chunk;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   for (i64 ch = blockIdx.x; ch < nchunks; ch += gridDim.x) {
     u32 wtotal = 0;
 #pragma unroll
-    for (int j = 0; j < FIN_ITEMS; ++j) {
+    for (int j = 0; j < ITEMS; ++j) {
       const i64 s = ch * chunk + (i64)j * FIN_BLOCK + threadIdx.x;
       bool occ = false;
       if (s < nslots && s != cap) occ = tbl[s * stride] != EMPTY;
@@ -1097,7 +1098,7 @@ __global__ void __launch_bounds__(FIN_BLOCK) k_finalize(const __grid_constant__ 
     __syncthreads();
     u64 next = s_base + s_wcount[wid];  // first output row of this warp's groups
 #pragma unroll 1
-    for (int j = 0; j < FIN_ITEMS; ++j) {
+    for (int j = 0; j < ITEMS; ++j) {
       const u32 m = s_ballot[wid][j];
       const i64 g = (i64)next + __popc(m & ((1u << lane) - 1u));
       next += __popc(m);
@@ -1305,6 +1306,22 @@ __global__ void k_string_copy(DKeyCol c, const int* __restrict__ rows, i64 ngrou
 
 // ------------------------------------------------------------------------------ partial records
 // owner partition of every occupied slot: counts, then scatter into destination-major order
+// Lanes of a warp headed for the same destination add to its counter ONCE (with few destinations
+// every lane of a CTA would otherwise hit the same two or eight shared-memory words).  Returns this
+// lane's position among the destination's records as counted by `counter`, or nothing useful for
+// lanes with `dest` = NO_DEST.  Must be called by all 32 lanes.
+constexpr u32 NO_DEST = 0xFFFFFFFFu;
+__device__ __forceinline__ u64 warp_add_by_dest(u64* counters, u32 dest)
+{
+  const u32 lane  = threadIdx.x & 31u;
+  const u32 peers = __match_any_sync(0xFFFFFFFFu, dest);
+  const int lead  = __ffs(peers) - 1;
+  u64 base = 0;
+  if (dest != NO_DEST && (int)lane == lead) base = atomicAdd(&counters[dest], (u64)__popc(peers));
+  base = __shfl_sync(0xFFFFFFFFu, base, lead);
+  return base + (u64)__popc(peers & ((1u << lane) - 1u));
+}
+
 __global__ void k_pack_count(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, const DCtrl* ctrl,
                              u64* __restrict__ counts)
 {
@@ -1312,10 +1329,16 @@ __global__ void k_pack_count(const u64* __restrict__ tbl, i64 cap, int stride, i
   for (int p = threadIdx.x; p < nparts; p += blockDim.x) s_cnt[p] = 0;
   __syncthreads();
   const i64 last = cap + (i64)ctrl->dense_slots;
-  for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s <= last; s += (i64)gridDim.x * blockDim.x) {
-    const u64 key = s != cap ? tbl[s * stride] : EMPTY;
-    const bool occ = s != cap ? key != EMPTY : ctrl->special_used != 0;
-    if (occ) atomicAdd(&s_cnt[owner_of(mix64(key), (u32)nparts)], 1ull);
+  const u32 lane = threadIdx.x & 31u;
+  for (i64 s0 = (i64)blockIdx.x * blockDim.x + (threadIdx.x - lane); s0 <= last; s0 += (i64)gridDim.x * blockDim.x) {
+    const i64 s = s0 + lane;
+    u32 dest = NO_DEST;
+    if (s <= last) {
+      const u64 key = s != cap ? tbl[s * stride] : EMPTY;
+      const bool occ = s != cap ? key != EMPTY : ctrl->special_used != 0;
+      if (occ) dest = owner_of(mix64(key), (u32)nparts);
+    }
+    warp_add_by_dest(s_cnt, dest);
   }
   __syncthreads();
   for (int p = threadIdx.x; p < nparts; p += blockDim.x)
@@ -1337,12 +1360,18 @@ k_pack_scatter(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, con
   const i64 per   = (last + 1 + gridDim.x - 1) / gridDim.x;
   const i64 lo    = (i64)blockIdx.x * per;
   const i64 hi    = min(last + 1, lo + per);
+  const u32 lane  = threadIdx.x & 31u;
+  auto dest_of = [&](i64 s, u64& key) -> u32 {
+    if (s >= hi) return NO_DEST;
+    key = s != cap ? tbl[s * stride] : EMPTY;
+    const bool occ = s != cap ? key != EMPTY : ctrl->special_used != 0;
+    return occ ? owner_of(mix64(key), (u32)nparts) : NO_DEST;
+  };
   for (int p = threadIdx.x; p < nparts; p += blockDim.x) s_cnt[p] = 0;
   __syncthreads();
-  for (i64 s = lo + threadIdx.x; s < hi; s += blockDim.x) {
-    const u64 key = s != cap ? tbl[s * stride] : EMPTY;
-    const bool occ = s != cap ? key != EMPTY : ctrl->special_used != 0;
-    if (occ) atomicAdd(&s_cnt[owner_of(mix64(key), (u32)nparts)], 1ull);
+  for (i64 s0 = lo + (threadIdx.x - lane); s0 < hi; s0 += blockDim.x) {
+    u64 key = 0;
+    warp_add_by_dest(s_cnt, dest_of(s0 + lane, key));
   }
   __syncthreads();
   for (int p = threadIdx.x; p < nparts; p += blockDim.x) {
@@ -1350,12 +1379,13 @@ k_pack_scatter(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, con
     s_cnt[p]  = 0;
   }
   __syncthreads();
-  for (i64 s = lo + threadIdx.x; s < hi; s += blockDim.x) {
-    const u64 key = s != cap ? tbl[s * stride] : EMPTY;
-    const bool occ = s != cap ? key != EMPTY : ctrl->special_used != 0;
-    if (!occ) continue;
-    const u32 p   = owner_of(mix64(key), (u32)nparts);
-    const u64 pos = s_base[p] + atomicAdd(&s_cnt[p], 1ull);
+  for (i64 s0 = lo + (threadIdx.x - lane); s0 < hi; s0 += blockDim.x) {
+    const i64 s = s0 + lane;
+    u64 key = 0;
+    const u32 p = dest_of(s, key);
+    const u64 r = warp_add_by_dest(s_cnt, p);
+    if (p == NO_DEST) continue;
+    const u64 pos = s_base[p] + r;
     u64* dst = out + pos * stride;
     const u64* src = tbl + s * stride;
     dst[0] = key;

@@ -7,7 +7,7 @@ with the shuffle built on cudf::hash_partition (cpp/libcudf_streaming/src/partit
 Here the exchange is ``torch.distributed.all_to_all_single`` (NCCL over NVLink/NVSwitch on GPUs,
 gloo on CPU for tests); everything else is the CUDA library.
 
-Two strategies, as §"partials vs rows" of the design notes explains:
+Two strategies:
   * ``partials``: aggregate locally, partition the partial records {key, n, Σx, Σx², min, max …} by
     owner = hash(key) % world, exchange, merge, finalise.  Wire bytes ∝ local groups.
   * ``rows``: partition the raw rows by owner, exchange the columns, aggregate locally.  Wire bytes
@@ -74,6 +74,8 @@ class DistributedGroupBy:
         self._strategy = strategy
         self._group = group
         self._gb = GroupBy(keys, null_handling, **options)
+        self._chunks_overflowed = False   # the fixed-size exchange overflowed before (same on every rank)
+        self._local_groups_hint = 0       # local groups of the previous variable-size call
 
     def aggregate(self, requests):
         world = dist.get_world_size(self._group) if dist.is_initialized() else 1
@@ -89,10 +91,15 @@ class DistributedGroupBy:
     def _aggregate_partials(self, requests, world):
         from .groupby import GroupByState, LogicError
         st = GroupByState(self._gb, requests)
+        # table sizing from the previous call on this object (a stream of similar batches): skips the
+        # speculative table and the cardinality estimate; a wrong hint only costs a regrowth
+        if self._local_groups_hint > 0 and "expected_groups" not in self._options:
+            st.reset(expected_groups=self._local_groups_hint + self._local_groups_hint // 8)
         st.update()
-        if st.chunk_bytes(self.CHUNK_RECORDS) * world <= (64 << 20):
+        if not self._chunks_overflowed and st.chunk_bytes(self.CHUNK_RECORDS) * world <= (64 << 20):
             # small states: equal-split all-to-all of fixed chunks; a sender with too many records
-            # marks every chunk it sends, so all ranks take the fallback below together
+            # marks every chunk it sends, so all ranks take the fallback below together — and, having
+            # all seen the same flag, all skip the fixed-size attempt on their next calls
             send = st.pack_chunks(world, self.CHUNK_RECORDS)
             recv = torch.empty_like(send)
             dist.all_to_all_single(recv, send, group=self._group)
@@ -103,7 +110,9 @@ class DistributedGroupBy:
             except LogicError as e:
                 if "chunk overflow" not in str(e):
                     raise
+                self._chunks_overflowed = True
         records, counts = st.pack(world)
+        self._local_groups_hint = int(sum(counts))
         recv, nrecv = exchange_records(records, counts, st.record_bytes, self._group)
         st.reset(expected_groups=max(nrecv, 1))
         st.merge(recv, nrecv)

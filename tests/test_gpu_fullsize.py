@@ -1,4 +1,4 @@
-"""The benchmark configurations at their FULL BASELINE sizes on one B200, inputs generated on the
+"""The benchmark configurations at their FULL benchmark sizes on one B200, inputs generated on the
 device (seeded torch generators), checked against an independent sort-based computation in torch
 (exact for integers) and through size-independent properties (group count, Σ counts, Σ sums,
 min <= mean <= max, idempotence of re-aggregating the result)."""

@@ -1,4 +1,4 @@
-"""Seeded synthetic inputs of the five benchmark configurations (BASELINE.json `configs`).
+"""Seeded synthetic inputs of the five benchmark configurations (C1-C5 of the benchmark specification).
 
 No public dataset is involved: these generators ARE the workloads.  Every generator is
 counter-seeded (seed = 42 + config index, optionally + rank) and produces Arrow-layout host columns
