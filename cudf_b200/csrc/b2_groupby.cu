@@ -790,8 +790,25 @@ void merge_records(b2_groupby_state& st, const u64* recs, int64_t nrecs, cudaStr
   read_ctrl(st, stream);
   const int64_t G = st.table ? num_groups(st) : 0;
   const int64_t need = std::max<int64_t>(1024, (int64_t)((double)(G + nrecs) / 0.6) + 64);
+  auto run_merge = [&] {
+    k_merge<<<grid_for(nrecs, 256, 8), 256, 0, stream>>>(st.plan, st.table, st.cap, st.ctrl, recs, nrecs);
+    CUDA_TRY(cudaGetLastError());
+    g_stats.kernel_launches++;
+    st.ctrl_fresh = false;
+    read_ctrl(st, stream);
+  };
   if (!st.table) {
-    alloc_table(st, std::max<int64_t>(need, st.expected_groups > 0 ? (int64_t)(st.expected_groups / 0.5) : 0), 1.0, stream);
+    // An empty state with an estimate of the distinct keys among the records (records of the same key
+    // from several senders): a table sized for the estimate stays in L2 and is cheaper to finalise
+    // than one sized for one group per record.  The records are still all here, so an estimate that
+    // turns out too small only costs a second pass into the full-size table.
+    const int64_t hinted = st.expected_groups > 0 ? (int64_t)((double)st.expected_groups / 0.5) + 64 : 0;
+    if (hinted > 0 && hinted < need) {
+      alloc_table(st, std::max<int64_t>(1024, hinted), 0.85, stream);
+      run_merge();
+      if (!st.host_ctrl.overflow) return;
+    }
+    alloc_table(st, std::max<int64_t>(need, hinted), 1.0, stream);
   } else if (st.cap < need) {
     // grow: move the present groups into a larger table
     Scratch old;
@@ -810,11 +827,7 @@ void merge_records(b2_groupby_state& st, const u64* recs, int64_t nrecs, cudaStr
     CUDA_TRY(cudaMemcpyAsync(&st.ctrl->claim_limit, &h.claim_limit, sizeof(u64), cudaMemcpyHostToDevice, stream));
     CUDA_TRY(cudaStreamSynchronize(stream));
   }
-  k_merge<<<grid_for(nrecs, 256, 8), 256, 0, stream>>>(st.plan, st.table, st.cap, st.ctrl, recs, nrecs);
-  CUDA_TRY(cudaGetLastError());
-  g_stats.kernel_launches++;
-  st.ctrl_fresh = false;
-  read_ctrl(st, stream);
+  run_merge();
   if (st.host_ctrl.overflow) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow while merging partial records");
 }
 

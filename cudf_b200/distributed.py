@@ -76,6 +76,7 @@ class DistributedGroupBy:
         self._gb = GroupBy(keys, null_handling, **options)
         self._chunks_overflowed = False   # the fixed-size exchange overflowed before (same on every rank)
         self._local_groups_hint = 0       # local groups of the previous variable-size call
+        self._owned_groups_hint = 0       # groups this rank owned after the previous variable-size call
 
     def aggregate(self, requests):
         world = dist.get_world_size(self._group) if dist.is_initialized() else 1
@@ -114,9 +115,14 @@ class DistributedGroupBy:
         records, counts = st.pack(world)
         self._local_groups_hint = int(sum(counts))
         recv, nrecv = exchange_records(records, counts, st.record_bytes, self._group)
-        st.reset(expected_groups=max(nrecv, 1))
+        # the merged table is sized from the number of groups this rank owned last time, if known
+        # (a too small estimate costs a second merge pass, never a wrong result)
+        own = self._owned_groups_hint
+        st.reset(expected_groups=max(own + own // 8 if own > 0 else nrecv, 1))
         st.merge(recv, nrecv)
-        return st.finalize()
+        out = st.finalize()
+        self._owned_groups_hint = out[0].num_rows()
+        return out
 
     def _aggregate_rows(self, requests, world):
         from .column import Table

@@ -87,6 +87,35 @@ def test_emulated_ranks_partials_shuffle_equals_one_shot(config, ranks):
     assert got[0][0].size == exp[0][0].size
 
 
+@pytest.mark.parametrize("estimate", [3, 4000, 6000, 10**7])
+def test_merge_into_a_table_sized_from_an_estimate(estimate):
+    """An empty state sized from an estimate of the distinct keys: too small an estimate (3, 4000 for
+    5000 keys) must fall back to the full-size table without losing or doubling a record."""
+    import cudf_b200 as cb
+    rng = np.random.default_rng(43)
+    n = 200_000
+    k = HostColumn.from_numpy(rng.integers(0, 5000, n).astype(np.int64))
+    v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.1)
+    reqs = [(v, AGGS)]
+    packed = []
+    for r in range(4):
+        gb, dreqs = _device_objects([k], reqs, NullPolicy.EXCLUDE, r * n // 4, (r + 1) * n // 4)
+        st = cb.GroupByState(gb, dreqs)
+        st.update()
+        records, counts = st.pack(1)
+        packed.append((records, counts[0], st, gb, dreqs))
+    import torch
+    allrec = torch.cat([p[0][: p[1] * p[2].record_bytes] for p in packed])
+    total = sum(p[1] for p in packed)
+    st = packed[0][2]
+    st.reset(expected_groups=estimate)
+    st.merge(allrec, total)
+    assert st.num_groups() == 5000
+    got = _to_host(st.finalize())
+    exp = oracle.groupby([k], reqs, NullPolicy.EXCLUDE)
+    H.assert_same_result(got, exp, reqs, scales=H.result_scales([k], reqs, NullPolicy.EXCLUDE))
+
+
 def test_batchwise_updates_equal_one_shot():
     import cudf_b200 as cb
     rng = np.random.default_rng(41)
