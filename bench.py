@@ -187,11 +187,17 @@ def run_b2(args):
     reqs = [cb.GroupByRequest(dev[id(v)], [Aggregation(Kind(a)) for a in aggs]) for v, aggs in w.requests]
     filt = [dev[id(f)] for f in w.row_filters]
 
+    kept = []  # --reuse-groupby: one DistributedGroupBy for all steps (it sizes its tables from its previous call)
+
     def step_resident():
         if world == 1:
             gb = cb.GroupBy(keys, w.null_policy, row_filters=filt)
+        elif args.reuse_groupby and kept:
+            gb = kept[0]
         else:
             gb = DistributedGroupBy(keys, w.null_policy, row_filters=filt, strategy=args.strategy)
+            if args.reuse_groupby:
+                kept.append(gb)
         return gb.aggregate(reqs)
 
     def barrier():
@@ -295,7 +301,8 @@ def run_b2(args):
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
             "config": {"workload": workload_desc(args.config, w.rows), "groups_rank0": groups,
-                       "strategy": "single GPU" if world == 1 else f"{args.strategy} shuffle over NCCL all-to-all",
+                       "strategy": "single GPU" if world == 1 else f"{args.strategy} shuffle over NCCL all-to-all"
+                                   + (", one DistributedGroupBy reused across steps" if args.reuse_groupby else ""),
                        "l2": f"inputs ({in_bytes / 1e6:.0f} MB per GPU) larger than the 126 MB L2; no flush needed",
                        "algorithmic_bytes_per_step": alg_bytes},
             "clocks": sampler.summary(),
@@ -332,6 +339,8 @@ def main():
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--rows", type=int, default=0, help="rows per GPU (0 = the configuration's full size)")
     ap.add_argument("--strategy", default="partials", choices=["partials", "rows"])
+    ap.add_argument("--reuse-groupby", action="store_true",
+                    help="N > 1: keep one DistributedGroupBy across the steps instead of a fresh one per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.rows <= 0:

@@ -129,6 +129,27 @@ struct DCtrl {
   DDense dense;
 };
 
+// ---------------------------------------------------------------------------------- table addressing
+// Slots 0..cap (hashed region + the special slot at `cap`) are array-of-structures: {key, cells...},
+// `stride` words each, so that one probe touches one or two sectors.  The `dense` slots behind them
+// (addressed by key-box position, never probed) are structure-of-arrays: all keys, then all cells 0,
+// all cells 1, ... so that consecutive threads merging consecutive box positions update consecutive
+// words (4 updates per 32-byte sector instead of one request per slot).
+struct SlotRef {
+  u64* key;    // the key cell
+  u64* cells;  // cell c is cells[c * step]
+  i64 step;
+};
+__device__ __forceinline__ SlotRef slot_ref(u64* tbl, i64 cap, int stride, i64 dense, i64 s)
+{
+  if (s <= cap) {
+    u64* p = tbl + s * stride;
+    return SlotRef{p, p + 1, 1};
+  }
+  u64* p = tbl + (cap + 1) * stride + (s - cap - 1);
+  return SlotRef{p, p + dense, dense};
+}
+
 // ---------------------------------------------------------------------------------- hashing
 __host__ __device__ __forceinline__ u64 mix64(u64 x)
 {

@@ -606,7 +606,7 @@ int64_t num_groups(const b2_groupby_state& st) { return (int64_t)st.host_ctrl.nc
 
 template <int KM, int LAYOUT, int NKF = 0, bool K8 = true>
 void launch_aggregate(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, int S, int fill_limit, size_t smem,
-                      cudaStream_t stream, u32 cap_dense = 0)
+                      cudaStream_t stream, u32 cap_dense = 0, u32 region_slots = 0)
 {
   auto kern = k_aggregate<KM, LAYOUT, NKF, K8>;
   static thread_local size_t configured = 0;
@@ -617,7 +617,7 @@ void launch_aggregate(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, int S,
   const int block = NKF > 0 ? LEAN_BLOCK : AGG_BLOCK;
   const int64_t tile = (int64_t)block * AGG_ROWS;
   const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((P.nrows + tile - 1) / tile, device_info().sms));
-  kern<<<grid, block, smem, stream>>>(P, tbl, cap, ctrl, S, fill_limit, cap_dense);
+  kern<<<grid, block, smem, stream>>>(P, tbl, cap, ctrl, S, fill_limit, cap_dense, region_slots);
   CUDA_TRY(cudaGetLastError());
   g_stats.kernel_launches++;
 }
@@ -664,7 +664,7 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
       // the number of key columns is a template parameter of the lean path (1..3), 0 = generic loops
       bool k8 = false;  // any 8-byte key column?
       for (int k = 0; k < sc.nkeys; ++k) k8 = k8 || sc.key_width[k] == 8;
-#define B2_LEAN(N, W) launch_aggregate<KM_PACKED, SL_F32MEAN, N, W>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream, cap_dense)
+#define B2_LEAN(N, W) launch_aggregate<KM_PACKED, SL_F32MEAN, N, W>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream, cap_dense, (u32)st.dense_slots)
       switch ((P.flags & PF_FAST) ? sc.nkeys : 0) {
         case 1: if (k8) B2_LEAN(1, true); else B2_LEAN(1, false); break;
         case 2: if (k8) B2_LEAN(2, true); else B2_LEAN(2, false); break;
@@ -672,7 +672,7 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
         default: B2_LEAN(0, true); break;
       }
 #undef B2_LEAN
-    } else if (layout == SL_GENERIC) launch_aggregate<KM_PACKED, SL_GENERIC>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream, cap_dense);
+    } else if (layout == SL_GENERIC) launch_aggregate<KM_PACKED, SL_GENERIC>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream, cap_dense, (u32)st.dense_slots);
     else launch_aggregate<KM_PACKED, SL_NONE>(P, st.table, st.cap, st.ctrl, 0, 0, 0, stream);
   } else {
     if (layout == SL_GENERIC) launch_aggregate<KM_ROWS, SL_GENERIC>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream);

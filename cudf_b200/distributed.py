@@ -101,17 +101,28 @@ class DistributedGroupBy:
             # small states: equal-split all-to-all of fixed chunks; a sender with too many records
             # marks every chunk it sends, so all ranks take the fallback below together — and, having
             # all seen the same flag, all skip the fixed-size attempt on their next calls
-            send = st.pack_chunks(world, self.CHUNK_RECORDS)
+            certain = st.num_groups() > world * self.CHUNK_RECORDS  # cannot fit whatever the split
+            if certain:
+                # still take part in the collective (the other ranks cannot know), with empty flagged chunks
+                words = st.chunk_bytes(self.CHUNK_RECORDS) // 8
+                flagged = torch.zeros(world * words, dtype=torch.int64, device=self._keys.columns()[0].data.device)
+                flagged[1::words] = 1
+                send = flagged.view(torch.uint8)
+            else:
+                send = st.pack_chunks(world, self.CHUNK_RECORDS)
             recv = torch.empty_like(send)
             dist.all_to_all_single(recv, send, group=self._group)
-            merged = GroupByState(self._gb, requests)
-            merged.merge_chunks(recv, world, self.CHUNK_RECORDS)
-            try:
-                return merged.finalize()
-            except LogicError as e:
-                if "chunk overflow" not in str(e):
-                    raise
+            if certain:
                 self._chunks_overflowed = True
+            else:
+                merged = GroupByState(self._gb, requests)
+                merged.merge_chunks(recv, world, self.CHUNK_RECORDS)
+                try:
+                    return merged.finalize()
+                except LogicError as e:
+                    if "chunk overflow" not in str(e):
+                        raise
+                    self._chunks_overflowed = True
         records, counts = st.pack(world)
         self._local_groups_hint = int(sum(counts))
         recv, nrecv = exchange_records(records, counts, st.record_bytes, self._group)
