@@ -30,8 +30,9 @@ class Column:
 
     def __init__(self, type_id: int, size: int, data: Optional[torch.Tensor], mask: Optional[torch.Tensor] = None,
                  offset: int = 0, null_count: int = -1, offsets: Optional[torch.Tensor] = None,
-                 offsets_type: TypeId = TypeId.INT32):
+                 offsets_type: TypeId = TypeId.INT32, scale: int = 0):
         self.type_id = TypeId(type_id)
+        self.scale = int(scale)  # DECIMAL32/64 only
         self.size = int(size)
         self.data = data
         self.mask = mask
@@ -50,7 +51,7 @@ class Column:
             offs_t = TypeId.INT64
         return Column(hc.type_id, hc.size, _to_device(hc.data, device, pinned), _to_device(hc.mask, device, pinned),
                       hc.offset, hc.null_count if hc.mask is not None else 0, _to_device(hc.offsets, device, pinned),
-                      offs_t)
+                      offs_t, getattr(hc, "scale", 0))
 
     @staticmethod
     def from_tensor(values: torch.Tensor, mask_words: Optional[torch.Tensor] = None, type_id: Optional[int] = None,
@@ -76,14 +77,14 @@ class Column:
             return HostColumn(self.type_id, self.size, chars, mask, self.offset, np_of(self.offsets, od))
         dt = np.dtype(STORAGE_DTYPE[self.type_id])
         data = np.zeros(0, dt) if self.data is None else self.data.cpu().numpy()[: (self.offset + self.size) * dt.itemsize].view(dt).copy()
-        return HostColumn(self.type_id, self.size, data, mask, self.offset)
+        return HostColumn(self.type_id, self.size, data, mask, self.offset, None, self.scale)
 
     # -- C view ---------------------------------------------------------------------------
     def c_view(self, keep: list) -> _lib.ColumnView:
         """The b2_column_view of this column; objects that must outlive the call go to ``keep``."""
         v = _lib.ColumnView()
         v.type_id = int(self.type_id)
-        v.scale = 0
+        v.scale = self.scale
         v.size = self.size
         v.null_count = self.null_count if self.mask is not None else 0
         v.data = self.data.data_ptr() if self.data is not None and self.data.numel() else None

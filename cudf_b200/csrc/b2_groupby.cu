@@ -130,6 +130,8 @@ bool is_float_t(int t) { return t == B2_FLOAT32 || t == B2_FLOAT64; }
 bool is_duration_t(int t) { return t >= B2_DURATION_DAYS && t <= B2_DURATION_NANOSECONDS; }
 bool is_timestamp_t(int t) { return t >= B2_TIMESTAMP_DAYS && t <= B2_TIMESTAMP_NANOSECONDS; }
 bool is_numeric_t(int t) { return t >= B2_INT8 && t <= B2_BOOL8; }
+// DECIMAL32/64 are served as their integer representation + scale; DECIMAL128 is not (no 16-byte atomics here)
+bool is_decimal_t(int t) { return t == B2_DECIMAL32 || t == B2_DECIMAL64; }
 
 int width_of(int t)
 {
@@ -169,7 +171,7 @@ int result_type(int src, int kind)
   switch (kind) {
     case B2_AGG_COUNT_VALID: case B2_AGG_COUNT_ALL: return B2_INT32;
     case B2_AGG_MIN: case B2_AGG_MAX: return src;
-    case B2_AGG_SUM: return (is_float_t(src) || is_duration_t(src)) ? src : B2_INT64;
+    case B2_AGG_SUM: return (is_float_t(src) || is_duration_t(src) || is_decimal_t(src)) ? src : B2_INT64;  // decimals keep type and scale
     case B2_AGG_SUM_OF_SQUARES: case B2_AGG_PRODUCT: return is_float_t(src) ? src : B2_INT64;
     case B2_AGG_MEAN: return is_duration_t(src) ? src : B2_FLOAT64;
     default: return B2_FLOAT64;
@@ -183,12 +185,17 @@ int classify_request(int src, int kind)
   switch (kind) {
     case B2_AGG_COUNT_VALID: case B2_AGG_COUNT_ALL: return 0;
     case B2_AGG_MIN: case B2_AGG_MAX:
-      if (is_numeric_t(src) || is_timestamp_t(src) || is_duration_t(src)) return 0;
-      if (src == B2_STRING || src == B2_DECIMAL32 || src == B2_DECIMAL64 || src == B2_DECIMAL128 ||
-          src == B2_DICTIONARY32 || src == B2_STRUCT || src == B2_LIST)
+      if (is_numeric_t(src) || is_timestamp_t(src) || is_duration_t(src) || is_decimal_t(src)) return 0;
+      if (src == B2_STRING || src == B2_DECIMAL128 || src == B2_DICTIONARY32 || src == B2_STRUCT || src == B2_LIST)
         return 2;
       return 1;
-    case B2_AGG_SUM: case B2_AGG_MEAN:
+    case B2_AGG_SUM:
+      // decimal SUM / MIN / MAX run on the hash path of the reference too
+      // (cpp/tests/groupby/sum_tests.cpp:220-248, min_tests.cpp:271-292, max_tests.cpp:279-300)
+      if (is_numeric_t(src) || is_duration_t(src) || is_decimal_t(src)) return 0;
+      if (src == B2_DECIMAL128 || src == B2_DICTIONARY32) return 2;
+      return 1;
+    case B2_AGG_MEAN:
       if (is_numeric_t(src) || is_duration_t(src)) return 0;
       if (src == B2_DECIMAL32 || src == B2_DECIMAL64 || src == B2_DECIMAL128 || src == B2_DICTIONARY32) return 2;
       return 1;
@@ -239,6 +246,7 @@ struct OutSpec {  // one requested aggregation → one result column
   int req, agg;
   int kind;      // OutKind
   int rtype;     // b2_type_id of the result
+  int scale = 0; // decimal results: the source column's scale
   int c_a = -1, c_b = -1, c_cnt = -1;
   int ddof = 1;
   int src_float = 0;
@@ -254,6 +262,7 @@ struct Schema {  // everything that is fixed by (key types, requests): cells and
   int key_shift[MAX_KEYS]{};
   int key_nullbit[MAX_KEYS]{};
   bool key_nullable[MAX_KEYS]{};
+  int key_scale[MAX_KEYS]{};  // decimal keys keep their scale
   int nvals = 0;
   int val_types[MAX_VALS]{};
   int ncells = 0;
@@ -299,7 +308,7 @@ void validate_requests(const b2_groupby& gb, const b2_aggregation_request* reqs,
     for (int a = 0; a < reqs[r].num_aggregations; ++a) {
       const int c = classify_request(reqs[r].values.type_id, reqs[r].aggregations[a].kind);
       // cpp/src/groupby/groupby.cu:188-201
-      if (c == 1) B2_FAIL(B2_DATA_TYPE_ERROR, "Invalid type/aggregation combination.");
+      if (c == 1) B2_FAIL(B2_LOGIC_ERROR, "Invalid type/aggregation combination.");  // CUDF_EXPECTS default: cudf::logic_error
       if (c == 2) unsupported = true;
     }
   if (unsupported)
@@ -330,6 +339,7 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
       packed = false;  // keys compare by value (+0 == -0, NaN == NaN) but are output verbatim
     }
     sc.key_types[k] = c.type_id;
+    sc.key_scale[k] = c.scale;
     sc.key_width[k] = w;
     sc.key_shift[k] = bits;
     sc.key_nullable[k] = c.null_mask != nullptr;
@@ -420,6 +430,7 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
       o.req = r; o.agg = a;
       const int kind = reqs[r].aggregations[a].kind;
       o.rtype = result_type(t, kind);
+      o.scale = is_decimal_t(o.rtype) ? reqs[r].values.scale : 0;
       o.ddof = reqs[r].aggregations[a].ddof;
       o.src_float = f;
       o.c_cnt = has_nulls ? ci.cnt : -1;
@@ -900,6 +911,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
     const OutSpec& o = sc.outs[i];
     b2_owned_column& c = out->results[o.req][o.agg];
     init_owned(c, o.rtype, G, o.nullable, al, stream);
+    c.scale = o.scale;
     DOutCol& d = plan->outs[i];
     d.data = c.data; d.mask = c.null_mask; d.kind = o.kind; d.rclass = vclass_of(o.rtype);
     d.c_a = o.c_a; d.c_b = o.c_b; d.c_cnt = o.c_cnt; d.ddof = o.ddof; d.src_float = o.src_float;
@@ -921,6 +933,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
       }
     } else {
       init_owned(c, sc.key_types[k], G, nullable, al, stream);
+      c.scale = sc.key_scale[k];
     }
     plan->kdata[k] = c.data;
     plan->kmask[k] = c.null_mask;
@@ -1479,6 +1492,7 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
         d.width = 0;
       } else {
         init_owned(out_columns[c], columns[c].type_id, n, nullable, al, stream);
+        out_columns[c].scale = columns[c].scale;
         d.width = width_of(columns[c].type_id);
       }
       out_columns[c].scale = columns[c].scale;

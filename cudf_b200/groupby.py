@@ -81,7 +81,7 @@ def _adopt_column(oc: _lib.OwnedColumn, alloc: TorchAllocator) -> Column:
         child.data = None
     oc.data = None
     oc.null_mask = None
-    return Column(oc.type_id, oc.size, data, mask, 0, oc.null_count, offsets, offs_t)
+    return Column(oc.type_id, oc.size, data, mask, 0, oc.null_count, offsets, offs_t, oc.scale)
 
 
 def _adopt_result(res: _lib.GroupbyResult, alloc: TorchAllocator) -> Tuple[Table, List[Table]]:

@@ -112,6 +112,10 @@ def is_timestamp(t: int) -> bool:
     return TypeId.TIMESTAMP_DAYS <= TypeId(t) <= TypeId.TIMESTAMP_NANOSECONDS
 
 
+def is_decimal(t: int) -> bool:
+    return TypeId(t) in (TypeId.DECIMAL32, TypeId.DECIMAL64, TypeId.DECIMAL128)
+
+
 def result_type(source: int, kind: int) -> TypeId:
     """Result element type of aggregation ``kind`` over ``source``
     (cpp/include/cudf/detail/aggregation/aggregation.hpp:884-1013)."""
@@ -121,7 +125,8 @@ def result_type(source: int, kind: int) -> TypeId:
     if kind in (Kind.MIN, Kind.MAX):
         return source
     if kind == Kind.SUM:
-        return source if (is_floating(source) or is_duration(source)) else TypeId.INT64
+        # decimals keep their type and scale (aggregation.hpp:956-963)
+        return source if (is_floating(source) or is_duration(source) or is_decimal(source)) else TypeId.INT64
     if kind in (Kind.SUM_OF_SQUARES, Kind.PRODUCT):
         return source if is_floating(source) else TypeId.INT64
     if kind == Kind.MEAN:
@@ -163,13 +168,14 @@ class HostColumn:
     mask: Optional[np.ndarray] = None     # uint32 words or None
     offset: int = 0
     offsets: Optional[np.ndarray] = None  # STRING: int32 or int64, offset+size+1 entries
+    scale: int = 0                        # DECIMAL32/64: value = data * 10**scale (cpp/include/cudf/types.hpp data_type)
 
     @property
     def null_count(self) -> int:
         return int(self.size - unpack_mask(self.mask, self.size, self.offset).sum())
 
     @staticmethod
-    def from_numpy(values, valid=None, type_id: Optional[int] = None, offset: int = 0) -> "HostColumn":
+    def from_numpy(values, valid=None, type_id: Optional[int] = None, offset: int = 0, scale: int = 0) -> "HostColumn":
         """Fixed-width column from an array; ``valid`` is an optional boolean array (False = null).
         ``offset`` > 0 builds a sliced view: the first ``offset`` elements are padding."""
         values = np.ascontiguousarray(values)
@@ -187,7 +193,7 @@ class HostColumn:
         mask = None
         if valid is not None:
             mask = pack_mask(np.asarray(valid, dtype=bool), offset)
-        return HostColumn(type_id, n, values, mask, offset)
+        return HostColumn(type_id, n, values, mask, offset, None, int(scale))
 
     @staticmethod
     def from_strings(strings: Sequence[Optional[str]], large_offsets: bool = False) -> "HostColumn":

@@ -33,7 +33,7 @@ typedef enum b2_status {
   B2_SUCCESS          = 0,
   B2_LOGIC_ERROR      = 1, /* cudf::logic_error      (precondition violated, e.g. size mismatch) */
   B2_INVALID_ARGUMENT = 2, /* std::invalid_argument                                              */
-  B2_DATA_TYPE_ERROR  = 3, /* cudf::data_type_error  (invalid type/aggregation combination)      */
+  B2_DATA_TYPE_ERROR  = 3, /* cudf::data_type_error  (a column of a type the call cannot read)    */
   B2_CUDA_ERROR       = 4, /* cudf::cuda_error                                                   */
   B2_UNSUPPORTED      = 5, /* valid for the reference's sort path, not handled by this hash path;
                               an adapter falls through to the reference for these               */
@@ -168,8 +168,8 @@ b2_status b2_groupby_create(const b2_column_view* keys, int32_t num_keys, int32_
  * cpp/src/groupby/groupby.cu:219-236 → detail::hash::groupby (cpp/src/groupby/hash/groupby.cu:134-147).
  * Work is enqueued on `stream`; the call synchronises the stream once to learn the group count.
  * Errors: B2_LOGIC_ERROR "Size mismatch between request values and groupby keys."
- * (groupby.cu:225-229); B2_DATA_TYPE_ERROR "Invalid type/aggregation combination."
- * (groupby.cu:188-201); B2_UNSUPPORTED for requests only the reference's sort path serves. */
+ * (groupby.cu:225-229); B2_LOGIC_ERROR "Invalid type/aggregation combination."
+ * (groupby.cu:185-201, a CUDF_EXPECTS with the default exception type); B2_UNSUPPORTED for requests only the reference's sort path serves. */
 b2_status b2_groupby_aggregate(b2_groupby* gb, const b2_aggregation_request* requests,
                                int32_t num_requests, void* stream, const b2_allocator* allocator,
                                b2_groupby_result* out);

@@ -53,7 +53,8 @@ namespace {
 enum TypeId : int32_t {
   T_EMPTY = 0, T_INT8, T_INT16, T_INT32, T_INT64, T_UINT8, T_UINT16, T_UINT32, T_UINT64,
   T_FLOAT32, T_FLOAT64, T_BOOL8, T_TS_DAYS, T_TS_S, T_TS_MS, T_TS_US, T_TS_NS,
-  T_DUR_DAYS, T_DUR_S, T_DUR_MS, T_DUR_US, T_DUR_NS, T_DICT32, T_STRING
+  T_DUR_DAYS, T_DUR_S, T_DUR_MS, T_DUR_US, T_DUR_NS, T_DICT32, T_STRING, T_LIST,
+  T_DEC32, T_DEC64  // fixed point: the integer representation; the scale is metadata the caller keeps
 };
 enum Kind : int32_t {
   K_SUM = 0, K_PRODUCT = 2, K_MIN = 3, K_MAX = 4, K_COUNT_VALID = 5, K_COUNT_ALL = 6,
@@ -79,15 +80,16 @@ int width_of(int32_t t)
   switch (t) {
     case T_INT8: case T_UINT8: case T_BOOL8: return 1;
     case T_INT16: case T_UINT16: return 2;
-    case T_INT32: case T_UINT32: case T_FLOAT32: case T_TS_DAYS: case T_DUR_DAYS: return 4;
+    case T_INT32: case T_UINT32: case T_FLOAT32: case T_TS_DAYS: case T_DUR_DAYS: case T_DEC32: return 4;
     case T_INT64: case T_UINT64: case T_FLOAT64: case T_TS_S: case T_TS_MS: case T_TS_US:
-    case T_TS_NS: case T_DUR_S: case T_DUR_MS: case T_DUR_US: case T_DUR_NS: return 8;
+    case T_TS_NS: case T_DUR_S: case T_DUR_MS: case T_DUR_US: case T_DUR_NS: case T_DEC64: return 8;
     default: return 0;
   }
 }
 bool is_float(int32_t t) { return t == T_FLOAT32 || t == T_FLOAT64; }
 bool is_duration(int32_t t) { return t >= T_DUR_DAYS && t <= T_DUR_NS; }
 bool is_timestamp(int32_t t) { return t >= T_TS_DAYS && t <= T_TS_NS; }
+bool is_decimal(int32_t t) { return t == T_DEC32 || t == T_DEC64; }
 
 // value of element i as (int64 bit pattern | double)
 struct Val { int64_t i; double f; };
@@ -98,9 +100,9 @@ inline Val load(const Col& c, int64_t r)
   switch (c.type_id) {
     case T_INT8: v.i = ((const int8_t*)c.data)[k]; break;
     case T_INT16: v.i = ((const int16_t*)c.data)[k]; break;
-    case T_INT32: case T_TS_DAYS: case T_DUR_DAYS: v.i = ((const int32_t*)c.data)[k]; break;
+    case T_INT32: case T_TS_DAYS: case T_DUR_DAYS: case T_DEC32: v.i = ((const int32_t*)c.data)[k]; break;
     case T_INT64: case T_TS_S: case T_TS_MS: case T_TS_US: case T_TS_NS: case T_DUR_S:
-    case T_DUR_MS: case T_DUR_US: case T_DUR_NS: v.i = ((const int64_t*)c.data)[k]; break;
+    case T_DUR_MS: case T_DUR_US: case T_DUR_NS: case T_DEC64: v.i = ((const int64_t*)c.data)[k]; break;
     case T_UINT8: v.i = ((const uint8_t*)c.data)[k]; break;
     case T_BOOL8: v.i = ((const uint8_t*)c.data)[k] != 0; break;
     case T_UINT16: v.i = ((const uint16_t*)c.data)[k]; break;
@@ -197,7 +199,8 @@ int32_t result_type(int32_t src, int32_t kind)
     case K_COUNT_VALID: case K_COUNT_ALL: return T_INT32;
     case K_MIN: case K_MAX: return src;
     case K_SUM:
-      if (is_float(src) || is_duration(src)) return src;
+      // fixed point sums keep their type (aggregation.hpp:956-963): a DECIMAL32 sum wraps at 32 bits
+      if (is_float(src) || is_duration(src) || is_decimal(src)) return src;
       return T_INT64;
     case K_SUMSQ: case K_PRODUCT: return is_float(src) ? src : T_INT64;
     case K_MEAN: return is_duration(src) ? src : T_FLOAT64;
@@ -211,8 +214,8 @@ int check_combo(int32_t src, int32_t kind)
   const bool numeric = (src >= T_INT8 && src <= T_BOOL8);
   switch (kind) {
     case K_COUNT_VALID: case K_COUNT_ALL: return 0;
-    case K_MIN: case K_MAX: return (numeric || is_timestamp(src) || is_duration(src)) ? 0 : 1;
-    case K_SUM: return (numeric || is_duration(src)) ? 0 : 1;
+    case K_MIN: case K_MAX: return (numeric || is_timestamp(src) || is_duration(src) || is_decimal(src)) ? 0 : 1;
+    case K_SUM: return (numeric || is_duration(src) || is_decimal(src)) ? 0 : 1;  // PRODUCT of decimals throws (sum_tests.cpp:245-246)
     case K_MEAN: return (numeric || is_duration(src)) ? 0 : 1;
     case K_SUMSQ: case K_PRODUCT: case K_M2: case K_VAR: case K_STD: return numeric ? 0 : 1;
     default: return 1;
@@ -310,7 +313,7 @@ void write_typed(OutCol& c, int64_t g, int32_t type, int64_t iv, long double fv)
     case T_UINT8: case T_BOOL8: put<uint8_t>(c, g, (uint8_t)iv); break;
     case T_INT16: put<int16_t>(c, g, (int16_t)iv); break;
     case T_UINT16: put<uint16_t>(c, g, (uint16_t)iv); break;
-    case T_INT32: case T_TS_DAYS: case T_DUR_DAYS: put<int32_t>(c, g, (int32_t)iv); break;
+    case T_INT32: case T_TS_DAYS: case T_DUR_DAYS: case T_DEC32: put<int32_t>(c, g, (int32_t)iv); break;
     case T_UINT32: put<uint32_t>(c, g, (uint32_t)iv); break;
     case T_FLOAT32: put<float>(c, g, (float)fv); break;
     case T_FLOAT64: put<double>(c, g, (double)fv); break;

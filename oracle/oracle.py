@@ -118,7 +118,7 @@ def groupby(keys: Sequence[HostColumn], requests: Sequence[Tuple[HostColumn, Seq
             raise OracleError(err.decode())
         ngroups = lib.orc_num_groups(h)
 
-        def fetch(req: int, idx: int) -> HostColumn:
+        def fetch(req: int, idx: int, scale: int = 0) -> HostColumn:
             t = TypeId(lib.orc_col_type(h, req, idx))
             nbytes = lib.orc_col_bytes(h, req, idx)
             raw = np.ctypeslib.as_array((C.c_uint8 * nbytes).from_address(lib.orc_col_data(h, req, idx))).copy() \
@@ -132,10 +132,13 @@ def groupby(keys: Sequence[HostColumn], requests: Sequence[Tuple[HostColumn, Seq
                 op = lib.orc_col_offsets(h, req, idx)
                 offs = np.ctypeslib.as_array((C.c_int64 * (ngroups + 1)).from_address(op)).copy()
                 return HostColumn(t, int(ngroups), raw, mask, 0, offs)
-            return HostColumn(t, int(ngroups), raw.view(STORAGE_DTYPE[t]), mask, 0)
+            # decimal columns (keys, SUM / MIN / MAX results) keep the scale of their source
+            dec = t in (TypeId.DECIMAL32, TypeId.DECIMAL64)
+            return HostColumn(t, int(ngroups), raw.view(STORAGE_DTYPE[t]), mask, 0, None, scale if dec else 0)
 
-        out_keys = [fetch(-1, i) for i in range(len(keys))]
-        out_res = [[fetch(q, a) for a in range(len(aggs))] for q, (_, aggs) in enumerate(requests)]
+        out_keys = [fetch(-1, i, getattr(keys[i], "scale", 0)) for i in range(len(keys))]
+        out_res = [[fetch(q, a, getattr(vals, "scale", 0)) for a in range(len(aggs))]
+                   for q, (vals, aggs) in enumerate(requests)]
         return out_keys, out_res
     finally:
         lib.orc_free(h)

@@ -39,10 +39,10 @@ cases = []
 
 
 def case(name, ref, keys, vals, agg, expect_keys, expect_vals, value_types=None, key_type="INT32",
-         null_policy="EXCLUDE", ddof=1, value_type=None):
+         null_policy="EXCLUDE", ddof=1, value_type=None, scale=0):
     cases.append(dict(name=name, ref=ref, key_type=key_type, keys=keys, vals=vals, agg=agg, ddof=ddof,
                       null_policy=null_policy, expect_keys=expect_keys, expect_vals=expect_vals,
-                      value_types=value_types or [value_type or "INT32"]))
+                      value_types=value_types or [value_type or "INT32"], scale=scale))
 
 
 def family(agg, file, lines, basic, nullcase, nullvals, value_types, zero_valid_values=None):
@@ -86,6 +86,17 @@ family("SUM_OF_SQUARES", "cpp/tests/groupby/sum_of_squares_tests.cpp", [26, 44, 
        [45, 98, 68, None], V11_D, NUMERIC)
 family("PRODUCT", "cpp/tests/groupby/product_tests.cpp", [24, 47, 66, 85, 104], [0, 180, 112],
        [18, 36, 16, None], V11_D, NUMERIC)
+
+# fixed point values on the hash path: the representation is aggregated, type and scale are kept
+# (TYPED over decimal32/64/128 and scales 2..-2 in the reference; 128-bit is not served here)
+DECIMALS = ["DECIMAL32", "DECIMAL64"]
+for sc in (2, 1, 0, -1, -2):
+    case(f"SUM.decimal_hash[scale={sc}]", "cpp/tests/groupby/sum_tests.cpp:220", K10, V10, "SUM", [1, 2, 3],
+         [9, 19, 17], DECIMALS, scale=sc)
+    case(f"MIN.decimal_hash[scale={sc}]", "cpp/tests/groupby/min_tests.cpp:271", K10, V10, "MIN", [1, 2, 3],
+         [0, 1, 2], DECIMALS, scale=sc)
+    case(f"MAX.decimal_hash[scale={sc}]", "cpp/tests/groupby/max_tests.cpp:279", K10, V10, "MAX", [1, 2, 3],
+         [6, 9, 8], DECIMALS, scale=sc)
 
 # M2: cpp/tests/groupby/m2_tests.cpp (keys are typed like the values there; int32 keys here, the
 # key type is covered by the KEYS cases)

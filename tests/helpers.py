@@ -28,7 +28,7 @@ def _num(x):
     return x
 
 
-def make_column(values: Sequence, type_name: str, offset: int = 0) -> HostColumn:
+def make_column(values: Sequence, type_name: str, offset: int = 0, scale: int = 0) -> HostColumn:
     """Column of the named type from a Python list where ``None`` is a null element."""
     t = TypeId[type_name]
     valid = np.array([v is not None for v in values], dtype=bool)
@@ -37,7 +37,7 @@ def make_column(values: Sequence, type_name: str, offset: int = 0) -> HostColumn
     filled = [0 if v is None else _num(v) for v in values]
     arr = np.array(filled, dtype=np.float64 if is_floating(t) else np.int64).astype(STORAGE_DTYPE[t])
     return HostColumn.from_numpy(arr, None if valid.all() and len(values) else (valid if len(values) else None),
-                                 type_id=t, offset=offset)
+                                 type_id=t, offset=offset, scale=scale)
 
 
 def sort_order(keys: List[HostColumn]) -> np.ndarray:
@@ -77,6 +77,7 @@ def assert_column_equal(got: HostColumn, exp: HostColumn, order_got, order_exp, 
                         check_nullable: bool = False, scale=None):
     assert TypeId(got.type_id) == TypeId(exp.type_id), f"{what}: type {got.type_id!r} != {exp.type_id!r}"
     assert got.size == exp.size, f"{what}: size {got.size} != {exp.size}"
+    assert getattr(got, "scale", 0) == getattr(exp, "scale", 0), f"{what}: decimal scale differs"
     if got.size == 0:
         return
     if check_nullable:
@@ -143,10 +144,11 @@ def golden_instances(case: dict):
                 and vt.startswith("UINT"):
             continue
         keys = make_column(case["keys"], case["key_type"])
-        vals = make_column(case["vals"], vt)
+        scale = case.get("scale", 0)
+        vals = make_column(case["vals"], vt, scale=scale)
         rt = TypeId.INT32 if vt == "STRING" else result_type(TypeId[vt], kind)
         ekeys = make_column(case["expect_keys"], case["key_type"])
-        evals = make_column(case["expect_vals"], rt.name)
+        evals = make_column(case["expect_vals"], rt.name, scale=scale if rt.name.startswith("DECIMAL") else 0)
         yield f'{case["name"]}[{vt}]', keys, vals, kind, case["ddof"], policy, ekeys, evals
 
 

@@ -251,6 +251,26 @@ def test_row_filters_drop_rows():
     check([k], [(v, [Kind.SUM, Kind.COUNT_ALL]), (w, [Kind.SUM, Kind.COUNT_VALID])], row_filters=[v, w])
 
 
+@pytest.mark.parametrize("policy", [NullPolicy.EXCLUDE, NullPolicy.INCLUDE])
+def test_decimal_values_and_keys_keep_type_and_scale(policy):
+    """Fixed point columns are aggregated on their integer representation; SUM / MIN / MAX results
+    and decimal keys keep type and scale; a DECIMAL32 sum wraps at 32 bits like the reference's
+    int32 accumulator (cpp/include/cudf/detail/aggregation/aggregation.hpp:956-963)."""
+    rng = np.random.default_rng(77)
+    n = 200_000
+    k = HostColumn.from_numpy(rng.integers(-500, 500, n).astype(np.int64), valid=rng.random(n) > 0.01,
+                              type_id=TypeId.DECIMAL64, scale=-3)
+    v32 = HostColumn.from_numpy(rng.integers(-2**30, 2**30, n).astype(np.int32), valid=rng.random(n) > 0.1,
+                                type_id=TypeId.DECIMAL32, scale=-2)
+    v64 = HostColumn.from_numpy(rng.integers(-10**12, 10**12, n).astype(np.int64), type_id=TypeId.DECIMAL64, scale=4)
+    reqs = [(v32, [Kind.SUM, Kind.MIN, Kind.MAX, Kind.COUNT_VALID]), (v64, [Kind.SUM, Kind.MIN, Kind.MAX, Kind.COUNT_ALL])]
+    gkeys, gres = check([k], reqs, policy)
+    assert gkeys[0].type_id == TypeId.DECIMAL64 and gkeys[0].scale == -3
+    assert [c.type_id for c in gres[0]] == [TypeId.DECIMAL32, TypeId.DECIMAL32, TypeId.DECIMAL32, TypeId.INT32]
+    assert [c.scale for c in gres[0]] == [-2, -2, -2, 0]
+    assert [c.scale for c in gres[1]] == [4, 4, 4, 0]
+
+
 def test_error_statuses_mirror_the_reference():
     import cudf_b200 as cb
     from cudf_b200 import aggregation as agg
@@ -260,8 +280,15 @@ def test_error_statuses_mirror_the_reference():
     gb = cb.GroupBy(cb.Table([k]))
     with pytest.raises(cb.LogicError, match="Size mismatch between request values and groupby keys."):
         gb.aggregate([cb.GroupByRequest(v5, [agg.sum()])])
-    with pytest.raises(cb.DataTypeError, match="Invalid type/aggregation combination."):
+    # CUDF_EXPECTS with the default exception type: cudf::logic_error (cpp/src/groupby/groupby.cu:185-201)
+    with pytest.raises(cb.LogicError, match="Invalid type/aggregation combination."):
         gb.aggregate([cb.GroupByRequest(s, [agg.sum()])])
+    # fixed point: SUM / MIN / MAX are served, PRODUCT throws (cpp/tests/groupby/sum_tests.cpp:245-246)
+    d = cb.Column.from_host(HostColumn.from_numpy(np.arange(4, dtype=np.int32), type_id=TypeId.DECIMAL32, scale=-2))
+    with pytest.raises(cb.LogicError, match="Invalid type/aggregation combination."):
+        gb.aggregate([cb.GroupByRequest(d, [agg.product()])])
+    with pytest.raises(cb.UnsupportedError):
+        gb.aggregate([cb.GroupByRequest(d, [agg.mean()])])
     with pytest.raises(cb.UnsupportedError):
         gb.aggregate([cb.GroupByRequest(k, [agg.median()])])
     with pytest.raises(cb.UnsupportedError):
