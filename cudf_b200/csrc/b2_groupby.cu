@@ -1431,16 +1431,19 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
 {
   return guarded([&] {
     cudaStream_t stream = (cudaStream_t)stream_;
-    if (!columns || !out_columns || !offsets || num_columns < 1 || num_key_columns < 1 ||
-        num_key_columns > num_columns || num_parts < 1 || num_parts > 4096)
+    if (!offsets || num_columns < 0 || (num_columns > 0 && (!columns || !out_columns)) || num_key_columns < 0 ||
+        num_key_columns > num_columns || num_parts < 0 || num_parts > (1 << 20))
       B2_FAIL(B2_INVALID_ARGUMENT, "bad argument");
     if (num_columns > MAX_PART_COLS) B2_FAIL(B2_UNSUPPORTED, "more than 32 columns");
     device_info();
     const b2_allocator al = resolve(allocator);
-    const int64_t n = columns[0].size;
+    // nothing to hash, or nowhere to put the rows: an empty table of the same column types and
+    // num_parts + 1 zero offsets (cpp/tests/partitioning/hash_partition_test.cpp:72-142)
+    const bool empty_result = num_key_columns == 0 || num_parts == 0 || num_columns == 0;
+    const int64_t n = (empty_result || num_columns == 0) ? 0 : columns[0].size;
     int str_col = -1;
     for (int c = 0; c < num_columns; ++c) {
-      if (columns[c].size != n) B2_FAIL(B2_LOGIC_ERROR, "columns differ in size");
+      if (!empty_result && columns[c].size != n) B2_FAIL(B2_LOGIC_ERROR, "columns differ in size");
       if (columns[c].type_id == B2_STRING) {
         if (str_col >= 0) B2_FAIL(B2_UNSUPPORTED, "hash_partition serves at most one STRING column");
         if (n > 0 && (columns[c].num_children < 1 || !columns[c].children))
@@ -1454,10 +1457,12 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
     b2_groupby gb;
     for (int k = 0; k < num_key_columns; ++k) gb.keys.emplace_back(columns[k]);
     gb.null_policy = B2_NULL_INCLUDE;
-    Schema sc = make_schema(gb, nullptr, 0);
-    DPlan P;
-    fill_plan_schema(P, sc);
-    bind_plan_inputs(P, sc, gb, nullptr, 0);
+    DPlan P{};
+    if (!empty_result) {
+      Schema sc = make_schema(gb, nullptr, 0);
+      fill_plan_schema(P, sc);
+      bind_plan_inputs(P, sc, gb, nullptr, 0);
+    }
 
     auto Qp = std::make_unique<DPartPlan>();
     DPartPlan& Q = *Qp;
@@ -1466,7 +1471,11 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
     Q.nparts = num_parts;
     Q.str_col = str_col;
     const int64_t want = std::max<int64_t>(1, (n + 8191) / 8192);
-    const int grid = (int)std::min<int64_t>(want, (int64_t)device_info().sms * 4);
+    int grid = (int)std::min<int64_t>(want, (int64_t)device_info().sms * 4);
+    // per-CTA counters fit shared memory up to 4096 partitions; beyond that they live in global
+    // memory, with fewer CTAs so that grid x partitions stays bounded
+    Q.counters_in_global = num_parts > 4096;
+    if (Q.counters_in_global) grid = (int)std::max<int64_t>(1, std::min<int64_t>(grid, (int64_t)(1 << 22) / num_parts));
     Q.rows_per_cta = ((n + grid - 1) / grid + PART_BLOCK - 1) / PART_BLOCK * PART_BLOCK;
     for (int c = 0; c < num_columns; ++c) std::memset(&out_columns[c], 0, sizeof(b2_owned_column));
     struct Guard {
@@ -1474,7 +1483,7 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
       ~Guard() { if (armed) for (int i = 0; i < n; ++i) b2_column_free(&cols[i], al, s); }
     } guard{out_columns, num_columns, &al, stream};
     for (int c = 0; c < num_columns; ++c) {
-      const bool nullable = columns[c].null_mask != nullptr;
+      const bool nullable = columns[c].null_mask != nullptr && !empty_result;
       DPartCol& d = Q.cols[c];
       if (c == str_col) {
         b2_owned_column& oc = out_columns[c];
@@ -1496,7 +1505,7 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
         d.width = width_of(columns[c].type_id);
       }
       out_columns[c].scale = columns[c].scale;
-      out_columns[c].null_count = nullable ? columns[c].null_count : 0;
+      out_columns[c].null_count = (nullable && n > 0) ? columns[c].null_count : 0;
       if (nullable) CUDA_TRY(cudaMemsetAsync(out_columns[c].null_mask, 0, out_columns[c].null_mask_bytes, stream));
       d.src = (const unsigned char*)columns[c].data; d.mask = columns[c].null_mask; d.offset = columns[c].offset;
       d.dst = (unsigned char*)out_columns[c].data;
@@ -1511,7 +1520,14 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
       chars = Scratch(std::max<size_t>(8, cells * sizeof(u64)), stream);
       char_starts = Scratch(std::max<size_t>(8, cells * sizeof(i64)), stream);
     }
-    const size_t smem = (size_t)num_parts * 12;
+    const size_t smem = Q.counters_in_global ? 0 : (size_t)num_parts * 12;
+    Scratch cursors;
+    if (Q.counters_in_global) {
+      cursors = Scratch(std::max<size_t>(8, cells * sizeof(u64)), stream);
+      CUDA_TRY(cudaMemsetAsync(counts.p, 0, counts.bytes, stream));
+      CUDA_TRY(cudaMemsetAsync(cursors.p, 0, cursors.bytes, stream));
+      if (str_col >= 0) CUDA_TRY(cudaMemsetAsync(chars.p, 0, chars.bytes, stream));
+    }
     int64_t total_chars = 0;
     std::vector<i64> h_starts(cells), h_cstarts(cells);
     if (n > 0) {
@@ -1558,7 +1574,8 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
     if (n == 0) { guard.armed = false; return; }
     CUDA_TRY(cudaMemcpyAsync(starts.p, h_starts.data(), cells * sizeof(i64), cudaMemcpyHostToDevice, stream));
     if (str_col >= 0) CUDA_TRY(cudaMemcpyAsync(char_starts.p, h_cstarts.data(), cells * sizeof(i64), cudaMemcpyHostToDevice, stream));
-    k_partition_scatter<<<grid, PART_BLOCK, (size_t)num_parts * 8, stream>>>(P, Q, (const i64*)starts.p, (const i64*)char_starts.p);
+    k_partition_scatter<<<grid, PART_BLOCK, Q.counters_in_global ? 0 : (size_t)num_parts * 8, stream>>>(
+      P, Q, (const i64*)starts.p, (const i64*)char_starts.p, (u64*)cursors.p);
     CUDA_TRY(cudaGetLastError());
     CUDA_TRY(cudaStreamSynchronize(stream));
     g_stats.kernel_launches += 2;

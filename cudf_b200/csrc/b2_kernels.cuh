@@ -1550,7 +1550,7 @@ struct DPartPlan {
   int str_col;        // index in cols[], -1 = none
   int str_offs64;     // input offsets are INT64
   int out_offs64;     // output offsets are INT64
-  int pad;
+  int counters_in_global;  // per-CTA partition counters live in global memory (many partitions)
   const void* str_offsets;
   void* out_offsets;
   DPartCol cols[MAX_PART_COLS];
@@ -1570,10 +1570,14 @@ __global__ void __launch_bounds__(PART_BLOCK)
 k_partition_count(const __grid_constant__ DPlan P, const __grid_constant__ DPartPlan Q,
                   u32* __restrict__ cta_counts /* [grid][nparts] */, u64* __restrict__ cta_chars /* [grid][nparts] or null */)
 {
+  // per-CTA counters: in shared memory, or — more partitions than shared memory holds
+  // (cpp/tests/partitioning/hash_partition_test.cpp:172-187) — directly in this CTA's zeroed slice
+  // of the global arrays
   extern __shared__ u64 s_part[];  // [nparts] string bytes, then [nparts] u32 row counts
-  u64* s_chars = s_part;
-  u32* s_hist  = (u32*)(s_part + Q.nparts);
-  for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) { s_hist[p] = 0; s_chars[p] = 0; }
+  const bool in_global = Q.counters_in_global != 0;
+  u64* s_chars = in_global ? (cta_chars ? cta_chars + (size_t)blockIdx.x * Q.nparts : nullptr) : s_part;
+  u32* s_hist  = in_global ? cta_counts + (size_t)blockIdx.x * Q.nparts : (u32*)(s_part + Q.nparts);
+  if (!in_global) for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) { s_hist[p] = 0; s_chars[p] = 0; }
   __syncthreads();
   const i64 lo = (i64)blockIdx.x * Q.rows_per_cta;
   const i64 hi = min(P.nrows, lo + Q.rows_per_cta);
@@ -1590,6 +1594,7 @@ k_partition_count(const __grid_constant__ DPlan P, const __grid_constant__ DPart
     }
   }
   __syncthreads();
+  if (in_global) return;
   for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) {
     cta_counts[(size_t)blockIdx.x * Q.nparts + p] = s_hist[p];
     if (cta_chars) cta_chars[(size_t)blockIdx.x * Q.nparts + p] = s_chars[p];
@@ -1599,13 +1604,15 @@ k_partition_count(const __grid_constant__ DPlan P, const __grid_constant__ DPart
 __global__ void __launch_bounds__(PART_BLOCK)
 k_partition_scatter(const __grid_constant__ DPlan P, const __grid_constant__ DPartPlan Q,
                     const i64* __restrict__ cta_starts /* [grid][nparts] */,
-                    const i64* __restrict__ cta_char_starts /* [grid][nparts] or null */)
+                    const i64* __restrict__ cta_char_starts /* [grid][nparts] or null */,
+                    u64* __restrict__ cta_cursors /* [grid][nparts], zeroed; only with counters_in_global */)
 {
   // cursor inside this CTA's share of each partition: rows in the high 24 bits, string bytes in the
   // low 40 bits, advanced by ONE atomic per row so that rows and bytes keep the same order
   extern __shared__ u64 s_part[];
-  u64* s_cur = s_part;
-  for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) s_cur[p] = 0;
+  const bool in_global = Q.counters_in_global != 0;
+  u64* s_cur = in_global ? cta_cursors + (size_t)blockIdx.x * Q.nparts : s_part;
+  if (!in_global) for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) s_cur[p] = 0;
   __syncthreads();
   const i64 lo = (i64)blockIdx.x * Q.rows_per_cta;
   const i64 hi = min(P.nrows, lo + Q.rows_per_cta);

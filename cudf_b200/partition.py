@@ -15,33 +15,44 @@ from .groupby import _check
 from .types import TypeId
 
 
-def hash_partition(table: Table, num_key_columns: int, num_partitions: int) -> Tuple[Table, List[int]]:
-    """Reorders the rows so that partition p occupies rows [offsets[p], offsets[p+1]); the first
-    ``num_key_columns`` columns are hashed.  Returns (partitioned table, offsets of num_partitions+1 entries)."""
+def hash_partition(table: Table, columns_to_hash, num_partitions: int) -> Tuple[Table, List[int]]:
+    """Reorders the rows so that partition p occupies rows [offsets[p], offsets[p+1]).
+    ``columns_to_hash`` is the list of column indices whose values decide the partition, like the
+    reference's argument (cpp/include/cudf/partitioning.hpp), or an int k meaning the first k columns.
+    Returns (partitioned table with the input's column order, offsets of num_partitions+1 entries).
+    No columns to hash, no partitions or no columns give an empty table of the same column types
+    (cpp/tests/partitioning/hash_partition_test.cpp:72-142)."""
     lib = _lib.load()
     cols = table.columns()
+    if isinstance(columns_to_hash, int):
+        hashed = list(range(columns_to_hash))
+    else:
+        hashed = [int(i) for i in columns_to_hash]
+    if any(i < 0 or i >= len(cols) for i in hashed):
+        raise IndexError("columns_to_hash names a column the table does not have")
+    order = hashed + [i for i in range(len(cols)) if i not in hashed]  # the C entry point hashes the leading columns
     keep: list = []
-    views = (_lib.ColumnView * len(cols))()
-    for i, c in enumerate(cols):
-        views[i] = c.c_view(keep)
-    device = cols[0].data.device if cols[0].data is not None else torch.device("cuda")
+    views = (_lib.ColumnView * max(1, len(cols)))()
+    for j, i in enumerate(order):
+        views[j] = cols[i].c_view(keep)
+    device = next((c.data.device for c in cols if c.data is not None), torch.device("cuda"))
     alloc = allocator_for(device)
-    out = (_lib.OwnedColumn * len(cols))()
+    out = (_lib.OwnedColumn * max(1, len(cols)))()
     offsets = (C.c_int64 * (num_partitions + 1))()
     stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
-    _check(lib.b2_hash_partition(views, len(cols), num_key_columns, num_partitions, stream, C.byref(alloc.struct),
+    _check(lib.b2_hash_partition(views, len(cols), len(hashed), num_partitions, stream, C.byref(alloc.struct),
                                  out, offsets))
-    res = []
-    for i in range(len(cols)):
-        oc = out[i]
+    res: List[Column] = [None] * len(cols)  # type: ignore[list-item]
+    for j, i in enumerate(order):
+        oc = out[j]
         offs, offs_t = None, TypeId.INT32
         if oc.num_children:
             child = oc.children[0]
             offs = alloc.adopt(child.data)
             offs_t = TypeId(child.type_id)
             child.data = None
-        res.append(Column(oc.type_id, oc.size, alloc.adopt(oc.data), alloc.adopt(oc.null_mask), 0, oc.null_count,
-                          offs, offs_t))
+        res[i] = Column(oc.type_id, oc.size, alloc.adopt(oc.data), alloc.adopt(oc.null_mask), 0, oc.null_count,
+                        offs, offs_t, oc.scale)
         oc.data = None
         oc.null_mask = None
         lib.b2_column_free(C.byref(oc), C.byref(alloc.struct), stream)  # host arrays of the descriptor

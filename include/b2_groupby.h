@@ -258,7 +258,11 @@ void b2_state_destroy(b2_groupby_state* st);
  * not; the first `num_key_columns` are hashed)
  * so that partition p occupies rows [offsets[p], offsets[p+1]).  Output columns come from the
  * allocator; `offsets` is a host array of num_parts+1 entries.  The partition of a key equals
- * the owner used by b2_state_pack.  Synchronises `stream`. */
+ * the owner used by b2_state_pack.  Up to 2^20 partitions (beyond 4096 the per-CTA counters move
+ * from shared to global memory).  num_key_columns == 0, num_parts == 0 or num_columns == 0 give
+ * empty columns of the input types and all-zero offsets, like the reference
+ * (cpp/tests/partitioning/hash_partition_test.cpp:72-142).  The order of rows inside a partition is
+ * unspecified.  Synchronises `stream`. */
 b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns,
                             int32_t num_key_columns, int32_t num_parts, void* stream,
                             const b2_allocator* allocator, b2_owned_column* out_columns,
