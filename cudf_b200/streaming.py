@@ -73,7 +73,10 @@ class StreamingGroupBy:
 
     def finalize(self):
         """streaming_groupby::finalize (groupby.hpp:566-568): (keys table, one results table per request)."""
-        if self._state is None or self.distinct_keys() == 0:
+        # before any aggregate() the reference throws; after batches that left no group (all keys
+        # null under EXCLUDE, empty batches) it returns empty columns
+        # (cpp/tests/groupby/streaming_groupby_test.cpp:514-538,876-882)
+        if self._state is None:
             raise LogicError("no data has been accumulated")
         return self._state.finalize()
 
