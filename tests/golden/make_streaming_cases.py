@@ -86,6 +86,23 @@ case("MultiColumnKeys", 1248, [[[1, 1, 2], [10, 20, 10], [100, 200, 300]], [[1, 
      [(2, "SUM", 1)], key_types=["INT32", "INT32"])
 case("CumulativeRowsCanExceedMaxDistinctKeys", 1293, [[[0, 1, 2], [10, 20, 30]]] * 5, SUM1, max_keys=3)
 
+# string keys (kept as a table of partial aggregates that is reduced batch by batch)
+STR = ["STRING"]
+case("StringKeySumTwoBatches", 1043, [[["a", "b", "c", "a"], [10, 20, 30, 40]], [["b", "c", "a", "d"], [5, 15, 25, 35]]],
+     SUM1, key_types=STR)
+case("StringKeyNonAsciiUtf8", 1066, [[["αλφα", "βητα", "γαμμα", "αλφα"], [10, 20, 30, 40]],
+                                     [["βητα", "δελτα", "αλφα", "🙂"], [5, 15, 25, 35]]], SUM1, key_types=STR)
+case("StringKeyMinMaxTwoBatches", 1089, [[["cat", "dog", "cat"], [5.0, 2.0, 8.0]], [["cat", "dog", "bird"], [3.0, 9.0, 1.0]]],
+     [(1, "MIN", 1), (1, "MAX", 1)], ["FLOAT64"], key_types=STR)
+UNIVERSE = ["alpha", "beta", "gamma", "delta"]
+case("StringKeyManySmallBatches", 1112, [[[UNIVERSE[b % 4], UNIVERSE[(b + 1) % 4]], [b * 10, b * 10 + 1]] for b in range(8)],
+     SUM1, key_types=STR)
+case("StringKeyDisjointBatches", 1141, [[["x", "y"], [10, 20]], [["z", "w"], [30, 40]], [["x", "w"], [50, 60]]], SUM1,
+     key_types=STR)
+case("StringKeyNullKeysExcluded", 1169, [[nulls(["a", "b", "c"], [1, 0, 1]), [10, 20, 30]], [nulls(["a", "b"], [1, 0]), [40, 50]]],
+     SUM1, key_types=STR)
+case("StringKeyMerge", 1196, [[["a", "b"], [10, 20]], [["b", "c"], [30, 40]]], SUM1, key_types=STR, workers=[0, 1])
+
 out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_streaming_cases.json")
 with open(out, "w", encoding="utf-8") as f:
     json.dump(dict(source="NVIDIA/cudf " + F, cases=cases), f, indent=1)
