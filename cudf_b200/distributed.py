@@ -83,6 +83,11 @@ class DistributedGroupBy:
         if world == 1:
             return self._gb.aggregate(requests)
         if self._strategy == "partials":
+            from .partials import keys_are_row_keyed
+            if keys_are_row_keyed(self._keys.columns(), self._null_handling):
+                # string / float / wide keys: their table slots reference local rows and cannot travel;
+                # the partial aggregates travel as a table instead
+                return self._aggregate_partial_table(requests, world)
             return self._aggregate_partials(requests, world)
         return self._aggregate_rows(requests, world)
 
@@ -134,6 +139,32 @@ class DistributedGroupBy:
         out = st.finalize()
         self._owned_groups_hint = out[0].num_rows()
         return out
+
+    def _aggregate_partial_table(self, requests, world):
+        """Partials strategy for keys that do not pack into 64 bits: local aggregate into a TABLE of partial
+        aggregates (keys, n, Σx, Σx², min, max ... per value column), hash partition of that table by key,
+        all-to-all of its columns, reduction groupby on the owner, finalisers — the reference's
+        multi-partition plan (python/cudf_polars/cudf_polars/streaming/actor_graph/groupby.py:339-456).
+        Wire bytes ∝ local groups, as for packed keys."""
+        from .column import Table
+        from .partials import PartialTable
+        from .partition import hash_partition
+        specs, sources = [], {}
+        for r in requests:
+            sources[id(r._values)] = r._values
+            specs += [(id(r._values), a.kind, a.ddof) for a in r._aggregations]
+        nkeys = self._keys.num_columns()
+        local = PartialTable(specs, self._null_handling, batch_options=self._options)
+        local.add_batch(self._keys.columns(), sources)
+        parts, offsets = hash_partition(Table(local.keys + local.columns()), nkeys, world)
+        recv = exchange_rows(parts, offsets, world, self._group)
+        local.reduce_rows(recv[:nkeys], recv[nkeys:])
+        okeys, flat = local.finalize(detect_nulls=True)
+        results, i = [], 0
+        for r in requests:
+            results.append(Table(flat[i:i + len(r._aggregations)]))
+            i += len(r._aggregations)
+        return Table(okeys), results
 
     def _aggregate_rows(self, requests, world):
         from .column import Table
@@ -192,5 +223,5 @@ def exchange_rows(parts, offsets, world, group=None):
             out.append(Column(TypeId.STRING, nrecv, chars, mask, 0, nulls, new_offs.view(torch.uint8), TypeId.INT64))
         else:
             buf = exchange_buffer(c.data, send_counts, recv_counts, type_width(c.type_id), group)
-            out.append(Column(c.type_id, nrecv, buf, mask, 0, nulls))
+            out.append(Column(c.type_id, nrecv, buf, mask, 0, nulls, None, TypeId.INT32, c.scale))
     return out

@@ -22,7 +22,8 @@ from tests import helpers as H
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
 dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
-for config, strategy, n in ((2, "partials", 200_000), (4, "partials", 200_000), (3, "rows", 150_000), (5, "rows", 40_000)):
+for config, strategy, n in ((2, "partials", 200_000), (4, "partials", 200_000), (3, "rows", 150_000), (5, "rows", 40_000),
+                            (5, "partials", 40_000)):  # string keys: the partial aggregates travel as a table
     shards = [workloads.make(config, n, rank=r, scale_domain=(config in (3, 4))) for r in range(world)]
     w = shards[rank]
     keys = cb.Table([cb.Column.from_host(k) for k in w.keys])

@@ -309,3 +309,65 @@ def test_row_exchange_with_strings_and_nulls_single_rank_group():
             dist.destroy_process_group()
     exp = oracle.groupby(w.keys, w.requests)
     H.assert_same_result(got, exp, w.requests, scales=H.result_scales(w.keys, w.requests, w.null_policy))
+
+
+@pytest.mark.parametrize("ranks", [2, 3])
+def test_partial_table_shuffle_for_string_keys_equals_one_shot(ranks):
+    """Keys that do not pack into 64 bits travel as a TABLE of partial aggregates: local aggregate, hash
+    partition of the partial table by key, (emulated) exchange, reduction groupby, finalisers — the steps of
+    DistributedGroupBy's partials strategy for string keys, with the all-to-all replaced by host slicing."""
+    import cudf_b200 as cb
+    from cudf_b200.partials import PartialTable
+    from cudf_b200.partition import hash_partition
+    n = 60_000
+    w = workloads.make(5, n)
+    kinds = [Kind.SUM, Kind.COUNT_VALID, Kind.COUNT_ALL, Kind.MEAN, Kind.MIN, Kind.MAX, Kind.VARIANCE, Kind.STD, Kind.M2]
+    reqs = [(v, kinds) for v, _ in w.requests]
+    nkeys = len(w.keys)
+
+    def cut(c, lo, hi):
+        if c.type_id == TypeId.STRING:
+            return HostColumn.from_strings(c.to_pylist()[lo:hi])
+        return HostColumn.from_numpy(c.values()[lo:hi], c.valid()[lo:hi] if c.mask is not None else None, type_id=c.type_id)
+
+    specs = [(q, k, 1) for q in range(len(reqs)) for k in kinds]
+    outgoing = []  # per rank: (host columns of the partitioned partial table, offsets)
+    tables = []
+    for r in range(ranks):
+        lo, hi = r * n // ranks, (r + 1) * n // ranks
+        pt = PartialTable(specs, w.null_policy)
+        pt.add_batch([cb.Column.from_host(cut(k, lo, hi)) for k in w.keys],
+                     {q: cb.Column.from_host(cut(v, lo, hi)) for q, (v, _) in enumerate(reqs)})
+        parts, offsets = hash_partition(cb.Table(pt.keys + pt.columns()), nkeys, ranks)
+        outgoing.append(([c.to_host() for c in parts.columns()], offsets))
+        tables.append(pt)
+    got_parts = []
+    for dst in range(ranks):
+        recv = []
+        for ci in range(len(outgoing[0][0])):
+            pieces = [cut(cols[ci], offs[dst], offs[dst + 1]) for cols, offs in outgoing]
+            if pieces[0].type_id == TypeId.STRING:
+                merged = HostColumn.from_strings([x for p in pieces for x in p.to_pylist()])
+            else:
+                valid = np.concatenate([p.valid() for p in pieces]) if any(p.mask is not None for p in pieces) else None
+                merged = HostColumn.from_numpy(np.concatenate([p.values() for p in pieces]), valid, type_id=pieces[0].type_id)
+            recv.append(cb.Column.from_host(merged))
+        pt = tables[dst]
+        pt.reduce_rows(recv[:nkeys], recv[nkeys:])
+        keys, flat = pt.finalize(detect_nulls=True)
+        res, i = [], 0
+        for _ in reqs:
+            res.append([c.to_host() for c in flat[i:i + len(kinds)]])
+            i += len(kinds)
+        got_parts.append(([k.to_host() for k in keys], res))
+
+    def cat(cols):
+        if cols[0].type_id == TypeId.STRING:
+            return HostColumn.from_strings([x for c in cols for x in c.to_pylist()])
+        valid = np.concatenate([c.valid() for c in cols]) if any(c.mask is not None for c in cols) else None
+        return HostColumn.from_numpy(np.concatenate([c.values() for c in cols]), valid, type_id=cols[0].type_id)
+    got = ([cat([p[0][k] for p in got_parts]) for k in range(nkeys)],
+           [[cat([p[1][q][a] for p in got_parts]) for a in range(len(kinds))] for q in range(len(reqs))])
+    exp = oracle.groupby(w.keys, reqs, w.null_policy)
+    H.assert_same_result(got, exp, reqs, check_nullable=False, scales=H.result_scales(w.keys, reqs, w.null_policy))
+    assert got[0][0].size == exp[0][0].size  # ownership is disjoint
