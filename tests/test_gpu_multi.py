@@ -73,4 +73,4 @@ def test_two_rank_distributed_groupby_matches_oracle(tmp_path):
                           "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
                          capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
-    assert out.stdout.count("OK") == 4
+    assert out.stdout.count("OK") == 5
