@@ -5,7 +5,8 @@
 //   validate → plan (key packing, accumulator cells, outputs) → size the global table →
 //   k_table_init → k_aggregate → read the control block (ONE stream sync: group count and the
 //   overflow flag) → allocate outputs from the caller's allocator → k_finalize → null counts.
-// If the first table is too small the pass is repeated with a table sized for the row count.
+// Without a hint the first table is small and speculative; if it overflows, a HyperLogLog pass over the
+// keys sizes the table for the repeated pass (B2_TRACE=1 prints the phases of a call to stderr).
 #include "../../include/b2_groupby.h"
 #include "b2_kernels.cuh"
 

@@ -1,19 +1,27 @@
 // b2_kernels.cuh — the CUDA kernels of the groupby engine (sm_100a).
 //
-//   k_table_init     identity-fills a table (replaces the per-column thrust::fill of
-//                    cpp/src/aggregation/aggregation.cu:87-97 and the cuco slot memset)
-//   k_aggregate      ONE fused pass over keys + values + bitmasks: per-CTA shared-memory
-//                    open-addressing table in front of the global-memory table
+//   k_table_init     identity-fills a table with linear 16-byte stores (replaces the per-column
+//                    thrust::fill of cpp/src/aggregation/aggregation.cu:87-97 and the cuco slot memset)
+//   k_aggregate      ONE fused pass over keys + values + bitmasks: a per-CTA shared-memory table
+//                    (direct-indexed key box sampled in the kernel, or a 2-probe hashed cache) in
+//                    front of the global-memory table
 //                    (replaces mapping_indices_kernel + single_pass_shmem_aggs_kernel +
 //                    the global-memory functors: cpp/src/groupby/hash/compute_mapping_indices.cuh:92-151,
 //                    compute_shared_memory_aggs.cu:260-353, single_pass_functors.cuh:86-157)
+//   k_hll            HyperLogLog pass over the key columns: sizes the table after the small
+//                    speculative one overflowed (the reference sizes by rows: compute_groupby.cu:93-102)
 //   k_finalize       compaction of occupied slots + key decode + compound finalisers + result
 //                    null masks in one pass (replaces retrieve_all, key gather, binary DIV,
 //                    m2/var/std tabulate and null-count kernels: output_utils.cu:139-224,
 //                    hash_compound_agg_finalizer.cu:93-186, common/m2_var_std.cu:49-59,160-187)
-//   k_gather_*       key gather for row-keyed tables (fixed width and strings)
-//   k_pack_* / k_merge   hash partition of partial records by owner and merge of partial records
+//   k_gather_fixed, k_string_lengths, k_scan_*, k_string_copy
+//                    key gather for row-keyed tables (fixed width and strings)
+//   k_pack_* / k_merge / k_merge_chunks
+//                    hash partition of partial records by owner and merge of partial records
 //                    (cpp/src/partitioning/partitioning.cu:120-337, streaming_groupby/merge.cu:91-142)
+//   k_partition_count / k_partition_scatter, k_mask_to_bytes / k_bytes_to_mask
+//                    row-level hash partition of a table (cudf::hash_partition) and the validity
+//                    conversions a row exchange needs
 #pragma once
 #include "b2_device.cuh"
 #include <type_traits>
