@@ -621,10 +621,13 @@ void launch_aggregate(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, int S,
                       cudaStream_t stream, u32 cap_dense = 0, u32 region_slots = 0)
 {
   auto kern = k_aggregate<KM, LAYOUT, NKF, K8>;
-  static thread_local size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
+  // the opt-in is an attribute of the function on ONE device: remembered per device
+  static thread_local size_t configured[64] = {};
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (smem > 48 * 1024 && smem > configured[dev & 63]) {
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
+    configured[dev & 63] = smem;
   }
   const int block = NKF > 0 ? LEAN_BLOCK : AGG_BLOCK;
   const int64_t tile = (int64_t)block * AGG_ROWS;
@@ -641,8 +644,12 @@ struct EventPair {  // times the fused kernel on the caller's stream; read after
 };
 EventPair& kernel_events()
 {
-  static thread_local EventPair ev;
-  return ev;
+  // events belong to the device that was current when they were created: one pair per device
+  static thread_local std::unique_ptr<EventPair> ev[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!ev[dev & 63]) ev[dev & 63] = std::make_unique<EventPair>();
+  return *ev[dev & 63];
 }
 
 // one pass of the fused kernel over the bound inputs into st.table
