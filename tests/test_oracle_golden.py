@@ -60,3 +60,20 @@ def test_oracle_threads_agree():
     H.assert_keys_equal(a[0], b[0], oa, ob)
     for x, y in zip(a[1][0], b[1][0]):
         H.assert_column_equal(x, y, oa, ob, 1e-15, "threads")
+
+
+def test_oracle_decimal_sum_keeps_type_and_wraps_like_the_representation():
+    """Fixed point SUM accumulates in the column's own representation type
+    (cpp/include/cudf/detail/aggregation/aggregation.hpp:956-963): a DECIMAL32 sum wraps at 32 bits,
+    and the scale of keys and results is the source's."""
+    k = HostColumn.from_numpy(np.array([7, 7, 7, 9], dtype=np.int64), type_id=TypeId.DECIMAL64, scale=-3)
+    v = HostColumn.from_numpy(np.array([2**31 - 1, 5, 10, -4], dtype=np.int32), type_id=TypeId.DECIMAL32, scale=2)
+    okeys, ores = oracle.groupby([k], [(v, [Kind.SUM, Kind.MIN, Kind.MAX, Kind.COUNT_VALID])])
+    assert okeys[0].type_id == TypeId.DECIMAL64 and okeys[0].scale == -3
+    got = {int(key): [c.values()[i].item() for c in ores[0]] for i, key in enumerate(okeys[0].values())}
+    wrapped = int(np.array([2**31 - 1 + 15], dtype=np.int64).astype(np.int32)[0])
+    assert got == {7: [wrapped, 5, 2**31 - 1, 3], 9: [-4, -4, -4, 1]}
+    assert [c.type_id for c in ores[0]] == [TypeId.DECIMAL32, TypeId.DECIMAL32, TypeId.DECIMAL32, TypeId.INT32]
+    assert [c.scale for c in ores[0]] == [2, 2, 2, 0]
+    with pytest.raises(oracle.OracleError, match="Invalid type/aggregation combination."):
+        oracle.groupby([k], [(v, [Kind.PRODUCT])])
