@@ -33,8 +33,22 @@ for config, strategy, n in ((2, "partials", 200_000), (4, "partials", 200_000), 
         cache.setdefault(id(v), cb.Column.from_host(v))
         reqs.append(cb.GroupByRequest(cache[id(v)], [Aggregation(Kind(a)) for a in aggs]))
     filt = [cache[id(f)] for f in w.row_filters]
-    okeys, ores = DistributedGroupBy(keys, w.null_policy, strategy=strategy, row_filters=filt).aggregate(reqs)
+    dgb = DistributedGroupBy(keys, w.null_policy, strategy=strategy, row_filters=filt)
+    okeys, ores = dgb.aggregate(reqs)
     mine = ([c.to_host() for c in okeys.columns()], [[c.to_host() for c in t.columns()] for t in ores])
+    # a second call on the same object sizes its tables from the first and must give the same groups
+    okeys2, ores2 = dgb.aggregate(reqs)
+    again = ([c.to_host() for c in okeys2.columns()], [[c.to_host() for c in t.columns()] for t in ores2])
+    o1, o2 = H.sort_order(mine[0]), H.sort_order(again[0])
+    H.assert_keys_equal(again[0], mine[0], o2, o1)
+    for t1, t2 in zip(mine[1], again[1]):
+        for c1, c2 in zip(t1, t2):
+            assert np.array_equal(c1.valid()[o1], c2.valid()[o2])
+            a, b = c1.values()[o1][c1.valid()[o1]], c2.values()[o2][c2.valid()[o2]]
+            if a.dtype.kind == "f":   # the order of the atomic additions differs between two runs
+                assert np.allclose(a, b, rtol=1e-9, atol=1e-9 * (np.abs(a).max() if a.size else 1.0), equal_nan=True)
+            else:
+                assert np.array_equal(a, b)
     gathered = [None] * world
     dist.all_gather_object(gathered, mine)
     if rank == 0:
