@@ -74,14 +74,26 @@ const DeviceInfo& device_info()
   if (dev != cached_dev) {
     CUDA_TRY(cudaDeviceGetAttribute(&info.sms, cudaDevAttrMultiProcessorCount, dev));
     CUDA_TRY(cudaDeviceGetAttribute(&info.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    cudaMemPool_t pool;
-    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
-      unsigned long long keep = ~0ull;  // keep scratch memory cached between calls
-      cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
-    }
     cached_dev = dev;
   }
   return info;
+}
+
+// The library's own temporaries come from the device's default stream-ordered pool.  The first
+// allocation a thread makes on a device tells that pool to keep freed memory cached between calls
+// (the default threshold returns it to the driver at every synchronisation).  Entry points that
+// allocate nothing never get here.
+void keep_pool_cached()
+{
+  static thread_local int tuned_dev = -1;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev == tuned_dev) return;
+  cudaMemPool_t pool;
+  if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+    unsigned long long keep = ~0ull;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+  }
+  tuned_dev = dev;
 }
 
 // ------------------------------------------------------------------------------ memory
@@ -89,6 +101,7 @@ void* default_alloc(size_t bytes, void* stream, void*)
 {
   void* p = nullptr;
   if (bytes == 0) bytes = 8;
+  keep_pool_cached();
   if (cudaMallocAsync(&p, bytes, (cudaStream_t)stream) != cudaSuccess) { cudaGetLastError(); return nullptr; }
   return p;
 }
@@ -794,7 +807,10 @@ void pack_table(b2_groupby_state& st, int nparts, cudaStream_t stream, Scratch& 
   if ((int64_t)run != G) B2_FAIL(B2_INTERNAL_ERROR, "pack: group count mismatch");
   CUDA_TRY(cudaMemcpyAsync(d_cursor, starts.data(), (size_t)nparts * sizeof(u64), cudaMemcpyHostToDevice, stream));
   out = Scratch(std::max<size_t>(8, (size_t)G * st.plan.stride * 8), stream);
-  k_pack_scatter<<<grid, 256, (size_t)nparts * 2 * sizeof(u64), stream>>>(st.table, st.cap, st.plan.stride, nparts, st.ctrl, d_cursor,
+  const size_t scatter_smem = (size_t)nparts * 2 * sizeof(u64);
+  if (scatter_smem > 48 * 1024)  // up to 4096 destinations x 16 bytes: beyond the default limit
+    CUDA_TRY(cudaFuncSetAttribute(k_pack_scatter, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)scatter_smem));
+  k_pack_scatter<<<grid, 256, scatter_smem, stream>>>(st.table, st.cap, st.plan.stride, nparts, st.ctrl, d_cursor,
                                                                           (u64*)out.p);
   CUDA_TRY(cudaGetLastError());
   CUDA_TRY(cudaStreamSynchronize(stream));  // `starts` is read by the copy above
@@ -1155,13 +1171,12 @@ extern "C" b2_status b2_groupby_aggregate_noalloc(b2_groupby* gb, const b2_aggre
         B2_FAIL(B2_INVALID_ARGUMENT, "a nullable result column needs a result_masks entry");
     }
 
-    // everything the kernels read is written first: the previous call's contents are irrelevant
+    // everything the kernels read is written first: the previous call's contents are irrelevant.
+    // The control block is reset on the device (claim limit = max_groups: one more claim than that
+    // sets the overflow flag), so nothing is copied from the host before the kernels run.
     DCtrl h{};
-    h.claim_limit = (u64)max_groups;  // one more claim than this sets the overflow flag
-    CUDA_TRY(cudaMemcpyAsync(ctrl, &h, sizeof(DCtrl), cudaMemcpyHostToDevice, stream));
     CUDA_TRY(cudaMemsetAsync(null_counts, 0, nulls_bytes, stream));
-    CUDA_TRY(cudaStreamSynchronize(stream));  // `h` is a stack object
-    k_table_init<<<grid_for((cap + 1) * P.stride / 2 + 1, 256, 16), 256, 0, stream>>>(table, cap + 1, P, nullptr, 0);
+    k_table_init<<<grid_for((cap + 1) * P.stride / 2 + 1, 256, 16), 256, 0, stream>>>(table, cap + 1, P, ctrl, (u64)max_groups);
     CUDA_TRY(cudaGetLastError());
     int64_t G = 0;
     if (P.nrows > 0) {
@@ -1198,7 +1213,7 @@ extern "C" b2_status b2_groupby_aggregate_noalloc(b2_groupby* gb, const b2_aggre
       launch_finalize(P, *plan, table, cap, cap + 1, ctrl, stream);
       CUDA_TRY(cudaGetLastError());
       g_stats.kernel_launches += 1;
-      CUDA_TRY(cudaMemcpyAsync(h_nulls, null_counts, sizeof(h_nulls), cudaMemcpyDeviceToHost, stream));
+      if (null_counts_out) CUDA_TRY(cudaMemcpyAsync(h_nulls, null_counts, sizeof(h_nulls), cudaMemcpyDeviceToHost, stream));
     }
     CUDA_TRY(cudaStreamSynchronize(stream));
     *num_groups_out = (int32_t)G;

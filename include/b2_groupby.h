@@ -308,10 +308,12 @@ void b2_column_free(b2_owned_column* col, const b2_allocator* allocator, void* s
  *
  * The first call on each device looks up the scratch array's device address
  * (cudaGetSymbolAddress, with that device current); make that first call before any stream
- * capture begins.  The call uses no cudaMalloc / cudaFree / cudaMallocAsync and no memory pool.
+ * capture begins.  The call uses no cudaMalloc / cudaFree / cudaMallocAsync, and neither reads nor
+ * configures any memory pool.
  * Every call reuses the same scratch array and re-initialises the parts it reads, so the previous
  * call's contents never leak into a result — but two calls that overlap in time on one GPU (other
- * streams, other host threads) race on it: serialise them.  Synchronises `stream` twice. */
+ * streams, other host threads) race on it: serialise them.  Synchronises `stream` twice when the
+ * input has rows (once for the group count, once after the results are written), once otherwise. */
 #define B2_NOALLOC_SCRATCH_BYTES (8u << 20)
 b2_status b2_groupby_aggregate_noalloc(b2_groupby* gb, const b2_aggregation_request* requests,
                                        int32_t num_requests, void* stream, int32_t max_groups,

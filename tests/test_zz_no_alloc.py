@@ -20,9 +20,30 @@ from tests import helpers as H
 pytestmark = pytest.mark.gpu
 
 
-def run_noalloc(keys, requests, policy, max_groups):
+def device_memory_in_use():
+    """(bytes in use, bytes reserved) of the device's default stream-ordered pool — where every
+    temporary of this library comes from — and the driver's count of free device bytes.  torch's own
+    counters would not do: they only see torch's caching allocator, which the library never uses."""
+    from cuda.bindings import runtime as rt
+    err, dev = rt.cudaGetDevice()
+    assert err == rt.cudaError_t.cudaSuccess
+    err, pool = rt.cudaDeviceGetDefaultMemPool(dev)
+    assert err == rt.cudaError_t.cudaSuccess
+    vals = []
+    for attr in (rt.cudaMemPoolAttr.cudaMemPoolAttrUsedMemCurrent, rt.cudaMemPoolAttr.cudaMemPoolAttrReservedMemCurrent):
+        err, v = rt.cudaMemPoolGetAttribute(pool, attr)
+        assert err == rt.cudaError_t.cudaSuccess
+        vals.append(int(v))
+    err, free, _total = rt.cudaMemGetInfo()
+    assert err == rt.cudaError_t.cudaSuccess
+    return vals[0], vals[1], int(free)
+
+
+def run_noalloc(keys, requests, policy, max_groups, warmed_up=False):
     """Calls b2_groupby_aggregate_noalloc through the C ABI; output buffers are plain torch tensors
-    allocated by the test (the caller's job), returned as host columns."""
+    allocated by the test (the caller's job), returned as host columns.  Checks that the call left
+    the device's memory accounting untouched: the default pool always, the driver's free-byte count
+    once a first call has loaded the kernels (``warmed_up``)."""
     import torch
     import cudf_b200 as cb
     from cudf_b200 import _lib
@@ -62,9 +83,14 @@ def run_noalloc(keys, requests, policy, max_groups):
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    used0, reserved0, free0 = device_memory_in_use()
     _check(lib.b2_groupby_aggregate_noalloc(gb._handle, creqs, len(reqs), stream, max_groups, c_key_data, c_key_masks,
                                             c_res_data, c_res_masks, C.byref(ngroups), nulls))
+    used1, reserved1, free1 = device_memory_in_use()
     assert torch.cuda.memory_allocated() == before
+    assert (used1, reserved1) == (used0, reserved0), "the call touched the default memory pool"
+    if warmed_up:
+        assert free1 == free0, "device memory was allocated or released during the call"
     G = ngroups.value
 
     def column(t, data, mask, null_count, nullable):
@@ -104,17 +130,20 @@ def make_inputs(seed, n, groups):
 
 def test_noalloc_matches_the_allocating_entry_point_twice_in_a_row():
     # two different inputs back to back: the second call must not see anything of the first
-    for seed, n, groups, policy in ((1, 300_000, 4000, NullPolicy.EXCLUDE), (2, 120_000, 600, NullPolicy.INCLUDE),
-                                    (1, 300_000, 4000, NullPolicy.EXCLUDE)):
+    from oracle import oracle
+    for call, (seed, n, groups, policy) in enumerate(((1, 300_000, 4000, NullPolicy.EXCLUDE),
+                                                      (2, 120_000, 600, NullPolicy.INCLUDE),
+                                                      (1, 300_000, 4000, NullPolicy.EXCLUDE))):
         keys, reqs = make_inputs(seed, n, groups)
-        got = run_noalloc(keys, reqs, policy, max_groups=8192)
+        got = run_noalloc(keys, reqs, policy, max_groups=8192, warmed_up=call > 0)
         exp = H.gpu_groupby(keys, reqs, policy)
         # the tolerance is relative to each group's Σ|x| / Σx² (see helpers.result_scales): both sides are
         # GPU sums with different summation orders
-        from oracle import oracle
-        orc_keys, _ = oracle.groupby(keys, reqs, policy)
-        scales = H.reorder_scales(H.result_scales(keys, reqs, policy), orc_keys, exp[0])
+        orc = oracle.groupby(keys, reqs, policy)
+        scales = H.reorder_scales(H.result_scales(keys, reqs, policy), orc[0], exp[0])
         H.assert_same_result(got, exp, reqs, scales=scales)
+        # and against the CPU oracle directly, not only against the other GPU entry point
+        H.assert_same_result(got, orc, reqs, scales=H.result_scales(keys, reqs, policy))
 
 
 def test_noalloc_rejects_sizes_beyond_the_scratch_array():
