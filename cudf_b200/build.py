@@ -12,7 +12,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "csrc", "b2_groupby.cu")
-DEPS = [SRC, os.path.join(HERE, "csrc", "b2_kernels.cuh"), os.path.join(HERE, "csrc", "b2_device.cuh"),
+DEPS = [SRC, os.path.join(HERE, "csrc", "b2_kernels.cuh"), os.path.join(HERE, "csrc", "b2_lean.cuh"), os.path.join(HERE, "csrc", "b2_partition.cuh"), os.path.join(HERE, "csrc", "b2_device.cuh"),
         os.path.join(os.path.dirname(HERE), "include", "b2_groupby.h")]
 LIB = os.path.join(HERE, "libb2groupby.so")
 

@@ -93,8 +93,10 @@ struct DPlan {
 enum PlanFlags : int {
   PF_VEC_KEYS = 1,  // every key column may be read 4 rows at a time with one 16-byte load
   PF_VEC_VAL0 = 2,  // value column 0 likewise (compact FLOAT32 layout)
-  PF_FAST     = 4   // every key column is 4 or 8 bytes wide and every mask / filter offset is a
+  PF_FAST     = 4,  // every key column is 4 or 8 bytes wide and every mask / filter offset is a
                     // multiple of 4, so the validity bits of 4 consecutive rows never straddle a mask word
+  PF_BULK     = 8   // value column 0's validity can be tiled with 16-byte-aligned bulk copies: mask
+                    // pointer 16-byte aligned and offset a multiple of 128 bits (or no mask at all)
 };
 
 // Dense key mapping of one aggregate pass, derived on the device by sample_dense_box: when the keys
@@ -121,9 +123,11 @@ struct DCtrl {
   u64 out_cursor;    // finalize: next dense output index
   u64 stat_smem_rows;
   u64 stat_gmem_rows;
-  u64 reserved;
+  u64 done_ctas;     // CTAs of the lean fused kernel that finished their merge (the last one counts the groups)
   u64 chunk_overflow;  // a sender of merged chunks had more records than a chunk holds
   u64 dense_slots;     // slots after the special slot that are addressed directly by dense-box position
+  u32 error;           // a bounded wait inside a kernel ran out (1: staged-tile ring of the lean kernel)
+  u32 pad0;
   u64 t_phase[5];      // CTA 0 of the fused kernel: %globaltimer at start, after sampling, after the
                        // shared-table init, after the row loop, after the merge (diagnostics)
   DDense dense;

@@ -9,6 +9,8 @@
 // keys sizes the table for the repeated pass (B2_TRACE=1 prints the phases of a call to stderr).
 #include "../../include/b2_groupby.h"
 #include "b2_kernels.cuh"
+#include "b2_lean.cuh"
+#include "b2_partition.cuh"
 
 #include <algorithm>
 #include <cmath>
@@ -302,6 +304,11 @@ struct b2_groupby_state {
   std::vector<ColView> row_keys;  // key views of that update (row-key mode output gather)
   int64_t expected_groups = 0;
   cudaStream_t last_stream = nullptr;
+  // a state filled by the partitioned path holds its finished groups as a compact list instead of a
+  // table: structure-of-arrays, word w of group g at groups[w * groups_cap + g], word 0 = key cell
+  Scratch groups;
+  int64_t groups_cap = 0;
+  int64_t groups_n = -1;  // -1 = no list
 };
 
 namespace {
@@ -544,9 +551,17 @@ void bind_plan_inputs(DPlan& P, const Schema& sc, const b2_groupby& gb, const b2
     fast = fast && (P.keys[k].width == 4 || P.keys[k].width == 8) && (!P.keys[k].mask || P.keys[k].offset % 4 == 0);
   for (int v = 0; v < sc.nvals; ++v) fast = fast && (!P.vals[v].mask || P.vals[v].offset % 4 == 0);
   if (fast) P.flags |= PF_FAST;
+  if (sc.f32mean) {
+    const DValCol& vc = P.vals[sc.cells[0].col];
+    if (!vc.mask || ((uintptr_t)vc.mask % 16 == 0 && vc.offset % 128 == 0)) P.flags |= PF_BULK;
+  }
 }
 
 // ------------------------------------------------------------------------------ table management
+constexpr int64_t DENSE_REGION_SLOTS = 32768;  // >= the largest dense box the shared memory can hold
+// whether table_variant 0 (auto) runs the lean kernel with the cp.async.bulk tile ring (variant 5)
+// or with register tiles (variant 4)
+constexpr bool LEAN_STAGED_BY_DEFAULT = true;
 // B2_TRACE=1 in the environment prints phase times to stderr (each mark synchronises the stream, so
 // the traced call itself is slower)
 struct Trace {
@@ -589,9 +604,8 @@ void free_table(b2_groupby_state& st, cudaStream_t stream)
   st.cap = 0;
 }
 
-constexpr int64_t DENSE_REGION_SLOTS = 32768;  // >= the largest dense box the shared memory can hold
-
-void alloc_table(b2_groupby_state& st, int64_t cap, double max_load, cudaStream_t stream, bool dense_region = false)
+void alloc_table(b2_groupby_state& st, int64_t cap, double max_load, cudaStream_t stream, bool dense_region = false,
+                 u32 cap_dense = 0)
 {
   free_table(st, stream);
   if (cap > 0x7FFFFFF0ll) B2_FAIL(B2_UNSUPPORTED, "hash table would need more than 2^31 slots");
@@ -611,8 +625,10 @@ void alloc_table(b2_groupby_state& st, int64_t cap, double max_load, cudaStream_
   static_assert(sizeof(DCtrl) / 4 <= 256, "the control block is initialised by one CTA of k_table_init");
   h.dense_slots = (u64)st.dense_slots;
   st.host_ctrl = h;
-  k_table_init<<<grid_for((cap + 1 + st.dense_slots) * st.plan.stride / 2 + 1, 256, 16), 256, 0, stream>>>(st.table, cap + 1 + st.dense_slots, st.plan, st.ctrl,
-                                                                                  h.claim_limit, h.dense_slots);
+  // the key box of the fused pass is sampled here too (needs a dense region, packed keys and enough rows)
+  if (st.dense_slots == 0 || st.plan.nrows < SAMPLE_ROWS) cap_dense = 0;
+  k_table_init<<<grid_for((cap + 1 + st.dense_slots) * st.plan.stride / 2 + 1, TABLE_INIT_BLOCK, 16), TABLE_INIT_BLOCK, 0, stream>>>(
+    st.table, cap + 1 + st.dense_slots, st.plan, st.ctrl, h.claim_limit, h.dense_slots, cap_dense);
   CUDA_TRY(cudaGetLastError());
   g_stats.kernel_launches++;
   g_stats.table_capacity = cap;
@@ -629,23 +645,39 @@ void read_ctrl(b2_groupby_state& st, cudaStream_t stream)
 
 int64_t num_groups(const b2_groupby_state& st) { return (int64_t)st.host_ctrl.nclaimed + (st.host_ctrl.special_used ? 1 : 0); }
 
-template <int KM, int LAYOUT, int NKF = 0, bool K8 = true>
-void launch_aggregate(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, int S, int fill_limit, size_t smem,
-                      cudaStream_t stream, u32 cap_dense = 0, u32 region_slots = 0)
+// the opt-in to more than 48 KB of dynamic shared memory is an attribute of a function on ONE device
+template <typename Kernel>
+void allow_shared(Kernel kern, size_t smem, size_t (&configured)[64])
 {
-  auto kern = k_aggregate<KM, LAYOUT, NKF, K8>;
-  // the opt-in is an attribute of the function on ONE device: remembered per device
-  static thread_local size_t configured[64] = {};
   int dev = 0;
   CUDA_TRY(cudaGetDevice(&dev));
   if (smem > 48 * 1024 && smem > configured[dev & 63]) {
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured[dev & 63] = smem;
   }
-  const int block = NKF > 0 ? LEAN_BLOCK : AGG_BLOCK;
-  const int64_t tile = (int64_t)block * AGG_ROWS;
+}
+
+template <int KM, int LAYOUT>
+void launch_aggregate(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, int S, int fill_limit, size_t smem,
+                      cudaStream_t stream, u32 cap_dense = 0, u32 region_slots = 0, int lean_first = 0)
+{
+  auto kern = k_aggregate<KM, LAYOUT>;
+  static thread_local size_t configured[64] = {};
+  allow_shared(kern, smem, configured);
+  const int64_t tile = (int64_t)AGG_BLOCK * AGG_ROWS;
   const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((P.nrows + tile - 1) / tile, device_info().sms));
-  kern<<<grid, block, smem, stream>>>(P, tbl, cap, ctrl, S, fill_limit, cap_dense, region_slots);
+  kern<<<grid, AGG_BLOCK, smem, stream>>>(P, tbl, cap, ctrl, S, fill_limit, cap_dense, region_slots, lean_first);
+  CUDA_TRY(cudaGetLastError());
+  g_stats.kernel_launches++;
+}
+
+template <int NK, bool K8, bool STAGED>
+void launch_lean(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, size_t smem, cudaStream_t stream, u32 region_slots)
+{
+  auto kern = k_aggregate_lean<NK, K8, STAGED>;
+  static thread_local size_t configured[64] = {};
+  allow_shared(kern, smem, configured);
+  kern<<<device_info().sms, 1024, smem, stream>>>(P, tbl, cap, ctrl, region_slots);
   CUDA_TRY(cudaGetLastError());
   g_stats.kernel_launches++;
 }
@@ -665,54 +697,96 @@ EventPair& kernel_events()
   return *ev[dev & 63];
 }
 
-// one pass of the fused kernel over the bound inputs into st.table
-void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stream)
+// How the fused pass uses shared memory for one (schema, inputs, options) combination: decided on the
+// host before the table is initialised, because the key-box sampler inside k_table_init needs the slot budget.
+struct SharedPlan {
+  int layout = SL_NONE;
+  int S = 0, fill_limit = 0;  // hashed mode
+  size_t smem = 0;            // dynamic shared memory of the kernels
+  u32 cap_dense = 0;          // slots a dense key box may use (0 = no box)
+  bool lean = false;          // k_aggregate_lean runs in front of k_aggregate
+  bool staged = false;        // ... with the cp.async.bulk tile ring
+};
+
+SharedPlan plan_shared(const b2_groupby_state& st, const b2_groupby& gb)
 {
   const Schema& sc = st.sc;
-  int layout = SL_NONE;
-  int S = 0, fill_limit = 0;
-  size_t smem = 0;
-  u32 cap_dense = 0;
-  if (gb.table_variant != 1) {
-    const int budget = gb.shared_table_bytes > 0 ? std::min(gb.shared_table_bytes, device_info().smem_optin - 1024)
-                                                 : device_info().smem_optin - 1024;
-    const int cell_bytes = sc.f32mean ? 8 : 8 * sc.ncells;  // accumulators of one slot
-    S = budget / (8 + cell_bytes) - 1;                      // hashed mode: key cell + accumulators
-    if (S >= 256) {
-      layout = sc.f32mean ? SL_F32MEAN : SL_GENERIC;
-      fill_limit = (int)(S * SMEM_FILL);
-      smem = (size_t)budget;
-      // dense mode: accumulators + one occupancy bit per slot
-      if (sc.key_mode == KM_PACKED && gb.table_variant != 3)
-        cap_dense = (u32)std::min<int64_t>(st.dense_slots, ((int64_t)budget - 64) * 8 / ((int64_t)cell_bytes * 8 + 1));
+  const DPlan& P = st.plan;
+  SharedPlan sp;
+  if (gb.table_variant == 1) return sp;
+  const int budget = gb.shared_table_bytes > 0 ? std::min(gb.shared_table_bytes, device_info().smem_optin - 1024)
+                                               : device_info().smem_optin - 1024;
+  const int cell_bytes = sc.f32mean ? 8 : 8 * sc.ncells;  // accumulators of one slot
+  sp.S = budget / (8 + cell_bytes) - 1;                   // hashed mode: key cell + accumulators
+  if (sp.S < 256) { sp.S = 0; return sp; }
+  sp.layout = sc.f32mean ? SL_F32MEAN : SL_GENERIC;
+  sp.fill_limit = (int)(sp.S * SMEM_FILL);
+  sp.smem = (size_t)budget;
+  if (sc.key_mode != KM_PACKED || gb.table_variant == 3) return sp;
+  // dense mode: accumulators + one occupancy bit per slot
+  sp.cap_dense = (u32)std::min<int64_t>(DENSE_REGION_SLOTS, ((int64_t)budget - 64) * 8 / ((int64_t)cell_bytes * 8 + 1));
+  // the lean kernel: Σ and n of one FLOAT32 column, 1..3 key columns of 4 or 8 bytes, aligned vector loads
+  const int need = PF_FAST | PF_VEC_KEYS | PF_VEC_VAL0;
+  if (sc.f32mean && sc.nkeys <= 3 && (P.flags & need) == need && P.nrows >= SAMPLE_ROWS && P.nrows < 0xFFFF0000ll) {
+    sp.lean = true;
+    sp.cap_dense = (u32)std::min<int64_t>(DENSE_REGION_SLOTS, ((int64_t)budget - 256) * 8 / 65);
+    // the staged variant needs room for its tile ring, flat 16-byte-aligned tiles, and validity that is
+    // either absent or the value column's own mask (also when used as the row filter)
+    const DValCol& vc = P.vals[sc.cells[0].col];
+    bool bulk_ok = (P.flags & PF_BULK) != 0;
+    for (int k = 0; k < sc.nkeys; ++k) bulk_ok = bulk_ok && P.keys[k].mask == nullptr;
+    bulk_ok = bulk_ok && (P.nfilters == 0 || (P.nfilters == 1 && P.filters[0] == vc.mask && P.filter_offsets[0] == vc.offset));
+    int64_t row_bytes = 4;
+    for (int k = 0; k < sc.nkeys; ++k) row_bytes += sc.key_width[k];
+    const int64_t ring = (int64_t)LEAN_STAGES * ((int64_t)LEAN_STAGED_CONSUMERS * LEAN_ROWS * row_bytes + LEAN_MASK_BYTES);
+    const int64_t staged_cap = ((int64_t)budget - ring - 512) * 8 / 65;
+    const bool want_staged = gb.table_variant == 5 || (gb.table_variant == 0 && LEAN_STAGED_BY_DEFAULT);
+    if (want_staged && bulk_ok && staged_cap >= 1024) {
+      sp.staged = true;
+      sp.cap_dense = (u32)std::min<int64_t>(DENSE_REGION_SLOTS, staged_cap);
     }
   }
-  g_stats.used_shared_table = layout != SL_NONE;
+  return sp;
+}
+
+// one pass of the fused kernel(s) over the bound inputs into st.table
+void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stream, const SharedPlan& sp)
+{
+  const Schema& sc = st.sc;
+  g_stats.used_shared_table = sp.layout != SL_NONE;
   const DPlan& P = st.plan;
+  const u32 cap_dense = st.dense_slots > 0 && P.nrows >= SAMPLE_ROWS ? sp.cap_dense : 0;
   EventPair& ev = kernel_events();
   cudaEventRecord(ev.a, stream);
-  if (sc.key_mode == KM_PACKED) {
-    if (layout == SL_F32MEAN) {
-      // the number of key columns is a template parameter of the lean path (1..3), 0 = generic loops
-      bool k8 = false;  // any 8-byte key column?
-      for (int k = 0; k < sc.nkeys; ++k) k8 = k8 || sc.key_width[k] == 8;
-#define B2_LEAN(N, W) launch_aggregate<KM_PACKED, SL_F32MEAN, N, W>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream, cap_dense, (u32)st.dense_slots)
-      switch ((P.flags & PF_FAST) ? sc.nkeys : 0) {
-        case 1: if (k8) B2_LEAN(1, true); else B2_LEAN(1, false); break;
-        case 2: if (k8) B2_LEAN(2, true); else B2_LEAN(2, false); break;
-        case 3: if (k8) B2_LEAN(3, true); else B2_LEAN(3, false); break;
-        default: B2_LEAN(0, true); break;
-      }
+  const bool lean = sp.lean && cap_dense > 0;
+  if (lean) {
+    bool k8 = false;  // any 8-byte key column?
+    for (int k = 0; k < sc.nkeys; ++k) k8 = k8 || sc.key_width[k] == 8;
+#define B2_LEAN(N, W)                                                                                         \
+    do {                                                                                                      \
+      if (sp.staged) launch_lean<N, W, true>(P, st.table, st.cap, st.ctrl, sp.smem, stream, (u32)st.dense_slots);  \
+      else launch_lean<N, W, false>(P, st.table, st.cap, st.ctrl, sp.smem, stream, (u32)st.dense_slots);      \
+    } while (0)
+    switch (sc.nkeys) {
+      case 1: if (k8) B2_LEAN(1, true); else B2_LEAN(1, false); break;
+      case 2: if (k8) B2_LEAN(2, true); else B2_LEAN(2, false); break;
+      default: if (k8) B2_LEAN(3, true); else B2_LEAN(3, false); break;
+    }
 #undef B2_LEAN
-    } else if (layout == SL_GENERIC) launch_aggregate<KM_PACKED, SL_GENERIC>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream, cap_dense, (u32)st.dense_slots);
+  }
+  if (sc.key_mode == KM_PACKED) {
+    if (sp.layout == SL_F32MEAN) launch_aggregate<KM_PACKED, SL_F32MEAN>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream, cap_dense, (u32)st.dense_slots, lean);
+    else if (sp.layout == SL_GENERIC) launch_aggregate<KM_PACKED, SL_GENERIC>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream, cap_dense, (u32)st.dense_slots);
     else launch_aggregate<KM_PACKED, SL_NONE>(P, st.table, st.cap, st.ctrl, 0, 0, 0, stream);
   } else {
-    if (layout == SL_GENERIC) launch_aggregate<KM_ROWS, SL_GENERIC>(P, st.table, st.cap, st.ctrl, S, fill_limit, smem, stream);
+    if (sp.layout == SL_GENERIC) launch_aggregate<KM_ROWS, SL_GENERIC>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream);
     else launch_aggregate<KM_ROWS, SL_NONE>(P, st.table, st.cap, st.ctrl, 0, 0, 0, stream);
   }
   cudaEventRecord(ev.b, stream);
   st.ctrl_fresh = false;
 }
+
+int64_t hll_estimate(const u32* regs);
 
 // distinct keys among the participating rows, from a HyperLogLog pass (k_hll); synchronises the stream
 int64_t estimate_groups(const b2_groupby_state& st, cudaStream_t stream)
@@ -726,36 +800,226 @@ int64_t estimate_groups(const b2_groupby_state& st, cudaStream_t stream)
   std::vector<u32> h(HLL_REGS);
   CUDA_TRY(cudaMemcpyAsync(h.data(), regs.p, regs.bytes, cudaMemcpyDeviceToHost, stream));
   CUDA_TRY(cudaStreamSynchronize(stream));
+  return hll_estimate(h.data());
+}
+
+int64_t hll_estimate(const u32* regs)
+{
   const double m = (double)HLL_REGS;
   double sum = 0.0;
   int zeros = 0;
-  for (u32 r : h) { sum += std::ldexp(1.0, -(int)r); zeros += r == 0; }
+  for (int i = 0; i < HLL_REGS; ++i) { sum += std::ldexp(1.0, -(int)regs[i]); zeros += regs[i] == 0; }
   const double alpha = 0.7213 / (1.0 + 1.079 / m);
   double e = alpha * m * m / sum;
   if (e <= 2.5 * m && zeros > 0) e = m * std::log(m / (double)zeros);  // small-range correction
   return (int64_t)e;
 }
 
+// out[0..n] = exclusive scan of in[0..n-1] (out[n] = the total), three launches
+void device_exclusive_scan(const i64* in, int64_t n, i64* out, cudaStream_t stream)
+{
+  const int64_t per = (int64_t)SCAN_BLOCK * SCAN_ITEMS;
+  const int nblocks = (int)std::max<int64_t>(1, (n + per - 1) / per);
+  Scratch totals((size_t)(nblocks + 1) * sizeof(i64), stream), bases((size_t)(nblocks + 1) * sizeof(i64), stream);
+  k_scan_block_totals<<<nblocks, SCAN_BLOCK, 0, stream>>>(in, n, (i64*)totals.p);
+  k_exclusive_scan<<<1, 1024, 0, stream>>>((const i64*)totals.p, (i64*)bases.p, nblocks);
+  k_scan_apply<<<nblocks, SCAN_BLOCK, 0, stream>>>(in, n, (const i64*)bases.p, out);
+  CUDA_TRY(cudaGetLastError());
+  g_stats.kernel_launches += 3;
+}
+
+// ------------------------------------------------------------------------------ partitioned path
+// Below this many groups the global table (a few tens of MB) lives in L2 and the fused pass wins.
+constexpr int64_t RP_MIN_GROUPS = 1 << 19;
+constexpr int64_t RP_MIN_ROWS   = 1 << 22;
+
+// Aggregates the bound inputs by radix partition + per-bucket shared-memory tables (b2_partition.cuh).
+// `hint` > 0: the expected number of groups (no HyperLogLog registers are kept).  Returns false, leaving
+// the state empty, when this path does not apply or gave up (too few groups, a bucket overflowed its
+// table, the group list overflowed): the caller then uses the global table, sized from *estimate.
+bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stream, int64_t hint, int64_t* estimate)
+{
+  const Schema& sc = st.sc;
+  const DPlan& P = st.plan;
+  const bool forced = gb.table_variant == 6;
+  if (sc.key_mode != KM_PACKED || sc.ncells < 1) return false;
+  Trace trace(stream);
+  const int sms = device_info().sms;
+  EventPair& ev = kernel_events();
+  cudaEventRecord(ev.a, stream);
+
+  // 1. rows per top-level digit, and the number of groups
+  constexpr int TOP = 1 << RP_BITS_TOP;
+  Scratch counters((size_t)TOP * 8 + (size_t)HLL_REGS * 4, stream);
+  CUDA_TRY(cudaMemsetAsync(counters.p, 0, counters.bytes, stream));
+  u64* d_hist = (u64*)counters.p;
+  u32* d_hll  = (u32*)(d_hist + TOP);
+  const int cgrid = (int)std::max<int64_t>(1, std::min<int64_t>((P.nrows + 4 * RP_BLOCK - 1) / (4 * RP_BLOCK), (int64_t)sms * 2));
+  if (hint > 0) k_rp_count<false><<<cgrid, RP_BLOCK, 0, stream>>>(P, d_hist, d_hll);
+  else k_rp_count<true><<<cgrid, RP_BLOCK, 0, stream>>>(P, d_hist, d_hll);
+  CUDA_TRY(cudaGetLastError());
+  g_stats.kernel_launches++;
+  std::vector<u64> h_hist(TOP);
+  std::vector<u32> h_hll(HLL_REGS);
+  CUDA_TRY(cudaMemcpyAsync(h_hist.data(), d_hist, (size_t)TOP * 8, cudaMemcpyDeviceToHost, stream));
+  if (hint <= 0) CUDA_TRY(cudaMemcpyAsync(h_hll.data(), d_hll, (size_t)HLL_REGS * 4, cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  int64_t active = 0;
+  for (u64 c : h_hist) active += (int64_t)c;
+  int64_t est = hint > 0 ? hint : hll_estimate(h_hll.data());
+  est = std::max<int64_t>(1, std::min(est, active));
+  if (estimate) *estimate = est;
+  trace.mark("partition: histogram + estimate");
+  if (active == 0) return false;
+  if (!forced && est < RP_MIN_GROUPS) return false;
+
+  // 2. digits: buckets of about half a shared-memory table each (two CTAs of the aggregate kernel per SM)
+  const int slot_bytes = 8 * (1 + sc.ncells);
+  const int budget = std::min((device_info().smem_optin - 2048), 110 * 1024);
+  int slots = 256;
+  while ((int64_t)(2 * slots + 1) * slot_bytes <= budget) slots *= 2;
+  if ((int64_t)(slots + 1) * slot_bytes > budget) return false;  // too many accumulators for a useful table
+  int T = 0;
+  while (((double)est * 1.05) / (double)(1ll << T) > 0.5 * slots) ++T;
+  T = std::max(T, 1);
+  if (T > 2 * RP_MAX_BITS) return false;
+  const int b1 = T <= RP_MAX_BITS ? T : (T + 1) / 2, b2 = T - b1;
+  const int F1 = 1 << b1, F2 = 1 << b2;
+  const int64_t nbuckets = (int64_t)F1 * F2;
+
+  try {
+    // 3. level 1
+    int words = 1 + sc.nvals, valid_word = -1;
+    for (int v = 0; v < sc.nvals; ++v) if (P.vals[v].mask) valid_word = 1 + sc.nvals;
+    if (valid_word >= 0) ++words;
+    std::vector<u64> h_start((size_t)F1 + 1);
+    {
+      u64 run = 0;
+      const int fold = TOP / F1;
+      for (int d = 0; d < F1; ++d) {
+        h_start[(size_t)d] = run;
+        for (int j = 0; j < fold; ++j) run += h_hist[(size_t)d * fold + j];
+      }
+      h_start[(size_t)F1] = run;
+    }
+    Scratch bounds1((size_t)(2 * F1 + 2) * 8, stream);  // [F1 + 1] starts, [F1] cursors
+    u64* d_start1 = (u64*)bounds1.p;
+    u64* d_cur1   = d_start1 + F1 + 1;
+    CUDA_TRY(cudaMemcpyAsync(d_start1, h_start.data(), (size_t)(F1 + 1) * 8, cudaMemcpyHostToDevice, stream));
+    CUDA_TRY(cudaMemcpyAsync(d_cur1, h_start.data(), (size_t)F1 * 8, cudaMemcpyHostToDevice, stream));
+    Scratch recA((size_t)words * (size_t)active * 8, stream);
+    DScatter D1{DRecords{(u64*)recA.p, active, words, valid_word}, d_cur1, 64 - b1, F1};
+    const int sgrid = (int)std::max<int64_t>(1, std::min<int64_t>((P.nrows + RP_TILE - 1) / RP_TILE, sms));
+    k_rp_scatter<<<sgrid, RP_BLOCK, 0, stream>>>(P, D1);
+    CUDA_TRY(cudaGetLastError());
+    g_stats.kernel_launches++;
+    trace.mark("partition: level-1 scatter");
+
+    // 4. level 2
+    Scratch recB, bounds2, tiles;
+    DRecords src{(u64*)recA.p, active, words, valid_word};
+    const u64* b_start = d_start1;
+    const u64* b_end   = d_cur1;
+    if (b2 > 0) {
+      tiles = Scratch((size_t)(F1 + 1) * 4, stream);
+      k_rp_tiles<<<1, 1024, 0, stream>>>(d_start1, d_cur1, F1, (u32*)tiles.p);
+      bounds2 = Scratch((size_t)(3 * nbuckets + 2) * 8, stream);  // [nb] counts, [nb + 1] starts, [nb] cursors
+      u64* d_hist2  = (u64*)bounds2.p;
+      u64* d_start2 = d_hist2 + nbuckets;
+      u64* d_cur2   = d_start2 + nbuckets + 1;
+      CUDA_TRY(cudaMemsetAsync(d_hist2, 0, (size_t)nbuckets * 8, stream));
+      DLevel2 L{src, d_start1, d_cur1, (const u32*)tiles.p, F1};
+      const int shift2 = 64 - b1 - b2;
+      const int64_t max_tiles = active / RP_TILE + F1;
+      const int g2 = (int)std::max<int64_t>(1, std::min<int64_t>(max_tiles, (int64_t)sms * 2));
+      k_rp_count2<<<g2, RP_BLOCK, 0, stream>>>(L, shift2, F2, d_hist2);
+      CUDA_TRY(cudaGetLastError());
+      device_exclusive_scan((const i64*)d_hist2, nbuckets, (i64*)d_start2, stream);
+      CUDA_TRY(cudaMemcpyAsync(d_cur2, d_start2, (size_t)nbuckets * 8, cudaMemcpyDeviceToDevice, stream));
+      recB = Scratch((size_t)words * (size_t)active * 8, stream);
+      DScatter D2{DRecords{(u64*)recB.p, active, words, valid_word}, d_cur2, shift2, F2};
+      k_rp_scatter2<<<std::min(g2, sms), RP_BLOCK, 0, stream>>>(L, D2);
+      CUDA_TRY(cudaGetLastError());
+      g_stats.kernel_launches += 3;
+      src.rec = (u64*)recB.p;
+      b_start = d_start2;
+      b_end   = d_cur2;
+      trace.mark("partition: level-2 count + scatter");
+    }
+
+    // 5. one shared-memory aggregate per bucket
+    const int64_t gcap = std::min<int64_t>(active, (int64_t)((double)est * (hint > 0 ? 1.25 : 1.08)) + 65536);
+    Scratch groups((size_t)(1 + sc.ncells) * (size_t)gcap * 8, stream);
+    if (!st.ctrl) {
+      st.ctrl = (DCtrl*)default_alloc(sizeof(DCtrl), stream, nullptr);
+      if (!st.ctrl) B2_FAIL(B2_OUT_OF_MEMORY, "out of device memory");
+    }
+    CUDA_TRY(cudaMemsetAsync(st.ctrl, 0, sizeof(DCtrl), stream));
+    Scratch work(8, stream);
+    CUDA_TRY(cudaMemsetAsync(work.p, 0, 8, stream));
+    DBuckets B{src, b_start, b_end, nbuckets, slots, (u64*)groups.p, gcap, (u64*)work.p};
+    const size_t smem = (size_t)(slots + 1) * slot_bytes;
+    static thread_local size_t configured[64] = {};
+    allow_shared(k_rp_aggregate, smem, configured);
+    k_rp_aggregate<<<(int)std::min<int64_t>(nbuckets, (int64_t)sms * 2), RPA_BLOCK, smem, stream>>>(P, B, st.ctrl);
+    CUDA_TRY(cudaGetLastError());
+    g_stats.kernel_launches++;
+    cudaEventRecord(ev.b, stream);
+    st.ctrl_fresh = false;
+    read_ctrl(st, stream);
+    trace.mark("partition: bucket aggregate");
+    {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, ev.a, ev.b) == cudaSuccess) g_stats.aggregate_kernel_ms += ms;
+      else cudaGetLastError();
+    }
+    if (getenv("B2_TRACE"))
+      fprintf(stderr, "[b2] partitioned: %lld active rows, estimate %lld groups, digits %d + %d, %d slots per bucket, %lld groups, overflow %d\n",
+              (long long)active, (long long)est, b1, b2, slots, (long long)st.host_ctrl.out_cursor, (int)st.host_ctrl.overflow);
+    if (st.host_ctrl.overflow) return false;
+    st.groups = std::move(groups);
+    st.groups_cap = gcap;
+    st.groups_n = (int64_t)st.host_ctrl.out_cursor;
+    g_stats.table_capacity = nbuckets * slots;
+    return true;
+  } catch (const Err& e) {
+    if (e.code != B2_OUT_OF_MEMORY) throw;
+    return false;  // not enough memory for the record buffers: the table path needs less
+  }
+}
+
 constexpr int64_t SPECULATIVE_CAP = 1 << 17;  // first table when nothing is known about the cardinality
 constexpr double MAX_LOAD = 0.70;
 
 // aggregates the bound inputs into an EMPTY state, growing the table until it fits
-void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stream)
+void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stream, bool may_partition = false)
 {
   const int64_t n = st.plan.nrows;
   const int64_t hint = st.expected_groups > 0 ? st.expected_groups : gb.expected_groups;
   const int64_t full = std::max<int64_t>(1024, (int64_t)((double)n / 0.6) + 64);  // groups <= rows
+  // the partitioned path serves one-shot aggregates over packed keys with very many groups
+  may_partition = may_partition && st.sc.key_mode == KM_PACKED && gb.table_variant != 1 && gb.table_variant != 7 &&
+                  (gb.table_variant == 6 || n >= RP_MIN_ROWS);
+  int64_t known = 0;  // groups estimated by a partitioned attempt that gave up
+  if (may_partition && (gb.table_variant == 6 || hint >= RP_MIN_GROUPS)) {
+    g_stats.table_attempts = 1;
+    if (aggregate_partitioned(st, gb, stream, hint, &known)) return;
+    may_partition = false;
+  }
   int64_t cap;
   if (hint > 0) cap = std::min(full, std::max<int64_t>(1024, (int64_t)((double)hint / 0.5) + 64));
+  else if (known > 0) cap = std::min(full, (int64_t)((double)known * 1.10 / 0.6) + 1024);
   else if (n <= SPECULATIVE_CAP / 2) cap = std::max<int64_t>(1024, 2 * n + 64);
   else cap = SPECULATIVE_CAP;
   for (int attempt = 1;; ++attempt) {
     g_stats.table_attempts = attempt;
     Trace trace(stream);
-    alloc_table(st, cap, cap >= full ? 1.0 : MAX_LOAD, stream, gb.table_variant != 1 && gb.table_variant != 3);
+    const SharedPlan sp = plan_shared(st, gb);
+    alloc_table(st, cap, cap >= full ? 1.0 : MAX_LOAD, stream, gb.table_variant != 1 && gb.table_variant != 3, sp.cap_dense);
     trace.mark("table allocation + init");
-    run_aggregate(st, gb, stream);
+    run_aggregate(st, gb, stream, sp);
     read_ctrl(st, stream);
+    if (st.host_ctrl.error) B2_FAIL(B2_INTERNAL_ERROR, "a bounded wait inside the fused aggregate kernel ran out");
     {
       float ms = 0.f;
       if (cudaEventElapsedTime(&ms, kernel_events().a, kernel_events().b) == cudaSuccess) g_stats.aggregate_kernel_ms += ms;
@@ -772,8 +1036,15 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
     if (cap >= full) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow at full capacity");
     if (attempt == 1) {
       // the speculative table was too small: count the distinct keys (HyperLogLog, one pass over the
-      // key columns) and size the table for them
-      const int64_t est = estimate_groups(st, stream);
+      // key columns) and size the table for them — or, with very many groups, leave the table for the
+      // partitioned path (its first pass keeps the HyperLogLog registers too)
+      int64_t est = 0;
+      if (may_partition) {
+        free_table(st, stream);
+        if (aggregate_partitioned(st, gb, stream, 0, &est)) return;
+        may_partition = false;
+      }
+      if (est <= 0) est = estimate_groups(st, stream);
       trace.mark("HyperLogLog estimate");
       cap = std::min(full, std::max<int64_t>(cap * 16, (int64_t)((double)est * 1.10 / 0.6) + 1024));
     } else {
@@ -911,9 +1182,10 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
 
   Trace trace(stream);
   read_ctrl(st, stream);
+  const bool listed = st.groups_n >= 0;  // the partitioned path left a compact group list, not a table
   if (st.table && st.host_ctrl.chunk_overflow) B2_FAIL(B2_LOGIC_ERROR, "partial-record chunk overflow");
   if (st.table && st.host_ctrl.overflow) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow while merging partial records");
-  const int64_t G = st.table ? num_groups(st) : 0;
+  const int64_t G = listed ? st.groups_n : st.table ? num_groups(st) : 0;
   if (G > 0x7FFFFFFFll) B2_FAIL(B2_UNSUPPORTED, "more than 2^31-1 groups");
   out->num_groups = (int32_t)G;
   out->num_keys = sc.nkeys;
@@ -973,8 +1245,12 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
   std::vector<u32> h_nulls(MAX_OUTS + MAX_KEYS, 0);
   trace.mark("finalize: output allocation");
   if (G > 0) {
-    CUDA_TRY(cudaMemsetAsync(&st.ctrl->out_cursor, 0, sizeof(u64), stream));
-    launch_finalize(st.plan, *plan, st.table, st.cap, st.cap + 1 + st.dense_slots, st.ctrl, stream);
+    if (listed) {
+      k_finalize_records<<<grid_for(G, 256, 16), 256, 0, stream>>>(st.plan, *plan, (const u64*)st.groups.p, st.groups_cap, G);
+    } else {
+      CUDA_TRY(cudaMemsetAsync(&st.ctrl->out_cursor, 0, sizeof(u64), stream));
+      launch_finalize(st.plan, *plan, st.table, st.cap, st.cap + 1 + st.dense_slots, st.ctrl, stream);
+    }
     CUDA_TRY(cudaGetLastError());
     g_stats.kernel_launches++;
     trace.mark("finalize: k_finalize");
@@ -1061,15 +1337,16 @@ b2_groupby_state* make_state(const b2_groupby& gb, const b2_aggregation_request*
 }
 
 void update_state(b2_groupby_state& st, const b2_groupby& gb, const b2_aggregation_request* reqs, int nreqs,
-                  cudaStream_t stream)
+                  cudaStream_t stream, bool may_partition = false)
 {
   validate_requests(gb, reqs, nreqs);
   if ((int)st.sc.req_val.size() != nreqs) B2_FAIL(B2_LOGIC_ERROR, "request list differs from the state's");
   st.last_stream = stream;
   if (gb.keys[0].v.size == 0) return;
+  if (st.groups_n >= 0) B2_FAIL(B2_INTERNAL_ERROR, "a finished group list takes no further updates");
   if (!st.table) {
     bind_plan_inputs(st.plan, st.sc, gb, reqs, nreqs);
-    aggregate_fresh(st, gb, stream);
+    aggregate_fresh(st, gb, stream, may_partition);
     if (st.sc.key_mode == KM_ROWS) { st.has_rows = true; st.row_keys = gb.keys; }
     return;
   }
@@ -1269,7 +1546,7 @@ b2_status b2_groupby_aggregate(b2_groupby* gb, const b2_aggregation_request* req
     device_info();
     std::unique_ptr<b2_groupby_state, void (*)(b2_groupby_state*)> st(make_state(*gb, requests, num_requests),
                                                                       b2_state_destroy);
-    update_state(*st, *gb, requests, num_requests, (cudaStream_t)stream);
+    update_state(*st, *gb, requests, num_requests, (cudaStream_t)stream, /*may_partition=*/true);
     finalize_state(*st, (cudaStream_t)stream, allocator, out);
   });
 }

@@ -29,9 +29,8 @@
 namespace b2 {
 
 constexpr int AGG_BLOCK      = 1024;  // threads per CTA of the fused kernel (one CTA per SM)
-constexpr int LEAN_BLOCK     = 1024;  // threads per CTA of the lean instantiations (512 measured 1.6x slower:
-                                      // too few warps to cover the shared-memory atomics' latency)
-constexpr int LEAN_ROWS      = 4;     // rows per thread per tile in the lean loop
+constexpr int LEAN_ROWS      = 4;     // rows per thread per tile of k_aggregate_lean (1024 threads; 512 measured
+                                      // 1.6x slower: too few warps to cover the shared-memory atomics' latency)
 constexpr int AGG_ROWS       = 4;     // rows per thread per tile
 // The shared-memory table is a cache: a key that finds neither itself nor a free slot within
 // SMEM_PROBES slots of its home goes to the global table, and the CTA's merge adds both parts up.
@@ -46,17 +45,28 @@ constexpr int SLOT_NONE      = -1;
 enum SmemLayout : int { SL_NONE = 0, SL_GENERIC = 1, SL_F32MEAN = 2 };
 
 // ------------------------------------------------------------------------------ table init
-__global__ void k_table_init(u64* __restrict__ tbl, i64 nslots, const __grid_constant__ DPlan P, DCtrl* ctrl,
-                             u64 claim_limit, u64 dense_slots = 0)
+__device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, DDense* out);
+
+// Must be launched with TABLE_INIT_BLOCK threads per CTA.  With `cap_dense` > 0 the last CTA also
+// samples the key box of the fused kernels that follow on the stream (sample_dense_box) into the
+// control block: one CTA's 1024 reads here instead of the same 1024 reads by every CTA of the fused
+// kernel (148 CTAs queueing on the same sectors cost 6.5 us of that kernel).
+constexpr int TABLE_INIT_BLOCK = 256;
+__global__ void __launch_bounds__(TABLE_INIT_BLOCK)
+k_table_init(u64* __restrict__ tbl, i64 nslots, const __grid_constant__ DPlan P, DCtrl* ctrl, u64 claim_limit,
+             u64 dense_slots = 0, u32 cap_dense = 0)
 {
+  const bool sampling = ctrl && cap_dense > 0;
   if (ctrl && blockIdx.x == 0 && threadIdx.x < sizeof(DCtrl) / 4) {
-    // a fresh control block: all zero except the claim limit
+    // a fresh control block: all zero except the claim limit (and the key box, which the sampling CTA writes)
     u32 v = 0;
     if (threadIdx.x == offsetof(DCtrl, claim_limit) / 4) v = (u32)claim_limit;
     if (threadIdx.x == offsetof(DCtrl, claim_limit) / 4 + 1) v = (u32)(claim_limit >> 32);
     if (threadIdx.x == offsetof(DCtrl, dense_slots) / 4) v = (u32)dense_slots;
-    ((u32*)ctrl)[threadIdx.x] = v;
+    const bool in_box = threadIdx.x >= offsetof(DCtrl, dense) / 4 && threadIdx.x < (offsetof(DCtrl, dense) + sizeof(DDense)) / 4;
+    if (!(sampling && in_box)) ((u32*)ctrl)[threadIdx.x] = v;
   }
+  if (sampling && blockIdx.x == gridDim.x - 1) sample_dense_box(P, cap_dense, &ctrl->dense);
   // the table is written as one linear run of 8-byte words, two per thread and step (16-byte stores):
   // word w belongs to cell (w mod stride) of slot (w div stride); cell 0 is the key
   __shared__ u64 s_init[MAX_CELLS + 1];
@@ -257,15 +267,13 @@ __device__ __forceinline__ void prefetch_l2(const void* p)
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
-// Every CTA of the fused kernel looks at the same 1024 evenly spaced rows (one per thread; after the
-// first CTA they come from L2) and derives the dense key box, or disables it when the box would not
-// fit `cap_slots` shared-memory slots.  All CTAs compute the same box (min / max are order
-// independent), so there is no extra launch and no host round trip.  Keys outside the box are still
-// aggregated correctly, through the global table.  Must be called by all 1024 threads of the CTA.
-// One sample per thread because every CTA reads the same rows and 148 CTAs' reads of the same
-// sectors queue up in L2 (4 per thread: 17.8 us per launch, 2: 10.9 us, 1: 6.5 us).
-constexpr int SAMPLE_PER_THREAD = 1;
-constexpr int SAMPLE_ROWS = 1024 * SAMPLE_PER_THREAD;
+// One CTA (the last one of k_table_init) looks at 1024 evenly spaced rows and derives the dense key
+// box, or disables it when the box would not fit `cap_slots` shared-memory slots.  The fused kernels
+// read the box from the control block, so there is no host round trip.  Keys outside the box are
+// still aggregated correctly, through the global table.  Must be called by all TABLE_INIT_BLOCK
+// threads of the CTA.
+constexpr int SAMPLE_ROWS = 1024;
+constexpr int SAMPLE_PER_THREAD = SAMPLE_ROWS / 256;
 __device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, DDense* out)
 {
   __shared__ i64 s_min[MAX_KEYS], s_max[MAX_KEYS];
@@ -328,6 +336,7 @@ __device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, 
   __syncthreads();
   if (threadIdx.x == 0) {
     DDense& D = *out;
+    for (int k = 0; k < MAX_KEYS; ++k) { D.min[k] = 0; D.range[k] = 0; D.mult[k] = 0; }
     D.enabled = 0;
     D.total   = 0;
     D.copies  = 1;
@@ -395,12 +404,12 @@ __device__ __forceinline__ u64 global_timer_ns()
   return t;
 }
 
-template <int KM, int LAYOUT, int NKF, bool K8 = true>
-__global__ void __launch_bounds__(NKF > 0 ? LEAN_BLOCK : AGG_BLOCK, 1)
+template <int KM, int LAYOUT>
+__global__ void __launch_bounds__(AGG_BLOCK, 1)
 k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* ctrl, int S_hash, int fill_limit,
-            u32 cap_dense, u32 region_slots)
+            u32 cap_dense, u32 region_slots, int lean_first)
 {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ int s_fill, s_new, s_cache_on, s_abort, s_hit, s_miss;
   __shared__ DDense s_dense;
 
@@ -408,15 +417,18 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
   const int tid    = threadIdx.x;
   const i64 dense_slots = (i64)region_slots;  // structure-of-arrays slots behind the special slot
   const bool timekeeper = blockIdx.x == 0 && tid == 0;
-  if (timekeeper) ctrl->t_phase[0] = global_timer_ns();
-  if (LAYOUT != SL_NONE && KM == KM_PACKED && cap_dense > 0 && P.nrows >= SAMPLE_ROWS && blockDim.x == 1024) {
-    sample_dense_box(P, cap_dense, &s_dense);
-    if (timekeeper) { ctrl->dense = s_dense; ctrl->t_phase[1] = global_timer_ns(); }  // for the host's statistics
+  const u64 t_start = timekeeper ? global_timer_ns() : 0;
+  if (LAYOUT != SL_NONE && KM == KM_PACKED && cap_dense > 0) {
+    // the key box sampled by k_table_init, which precedes this kernel on the stream
+    for (int i = tid; i < (int)(sizeof(DDense) / 4); i += blockDim.x) ((u32*)&s_dense)[i] = ((const u32*)&ctrl->dense)[i];
   } else if (tid == 0) {
     s_dense.enabled = 0;
   }
   if (tid == 0) { s_fill = 0; s_new = 0; s_cache_on = (LAYOUT != SL_NONE); s_abort = 0; s_hit = 0; s_miss = 0; }
   __syncthreads();
+  // k_aggregate_lean ran in front of this kernel and, having found a key box, took the whole input
+  if (lean_first && s_dense.enabled) return;
+  if (timekeeper) { ctrl->t_phase[0] = t_start; ctrl->t_phase[1] = global_timer_ns(); }
   const bool dense = (LAYOUT != SL_NONE) && KM == KM_PACKED && s_dense.enabled;
   const int S      = dense ? (int)s_dense.total : S_hash;  // slots (hashed mode: + the special slot at S)
   const int NS     = dense ? S * (int)s_dense.copies : S + 1;  // allocated slots per array
@@ -449,172 +461,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
   if (timekeeper) ctrl->t_phase[2] = global_timer_ns();
 
   u32 my_hit = 0, my_miss = 0, tot_hit = 0, tot_miss = 0;
-  const bool fast_ok = NKF > 0 && dense && (P.flags & PF_VEC_KEYS) && (P.flags & PF_VEC_VAL0) && (P.flags & PF_FAST);
-
-  // ---- lean loop: dense key box + compact FLOAT32 layout.  4 consecutive rows per thread per tile,
-  // 16-byte vector loads all issued before the first use, 32-bit arithmetic, two native
-  // shared-memory atomics per row.  It consumes all full tiles; the generic loop below takes the
-  // remaining rows.
-  i64 rows_done = 0;
-  if (LAYOUT == SL_F32MEAN && NKF > 0 && fast_ok) {
-    constexpr int NK = NKF > 0 ? NKF : 1;
-    const u32 lean_tile = (u32)blockDim.x * LEAN_ROWS;
-    const u32 nfull     = (u32)(P.nrows / lean_tile);
-    rows_done           = (i64)nfull * lean_tile;
-    const DValCol& vc   = P.vals[P.cells[0].col];
-    const u32 ssum_a = (u32)__cvta_generic_to_shared(ssum), scnt_a = (u32)__cvta_generic_to_shared(scnt);
-    const bool filt_is_val = P.nfilters == 1 && P.filters[0] == vc.mask && P.filter_offsets[0] == vc.offset;
-
-    // the loads of one tile: value vector + validity, activity nibble, key vectors + validity
-    auto load_tile = [&](u32 tile, float4& q, u32& vn, u32& act, uint4 (&ka)[NK], uint4 (&kb)[NK], u32 (&kn)[NK]) {
-      const u32 r0 = tile * lean_tile + (u32)tid * LEAN_ROWS;
-      const u32 ve = (u32)vc.offset + r0;
-      q  = __ldg((const float4*)((const float*)vc.data + ve));
-      vn = vc.mask ? nibble_aligned(vc.mask, ve) : 0xFu;
-      act = 0xFu;
-      if (filt_is_val) act = vn;
-      else for (int f = 0; f < P.nfilters; ++f) act &= nibble_aligned(P.filters[f], (u32)P.filter_offsets[f] + r0);
-#pragma unroll
-      for (int k = 0; k < NK; ++k) {
-        const DKeyCol& c = P.keys[k];
-        const u32 e = (u32)c.offset + r0;
-        kn[k] = c.mask ? nibble_aligned(c.mask, e) : 0xFu;
-        const uint4* kp = (const uint4*)(c.data + (u64)e * (u32)c.width);
-        ka[k] = __ldg(kp);
-        if (K8 && c.width == 8) kb[k] = __ldg(kp + 1);  // K8 = false: every key column is 4 bytes wide
-      }
-    };
-    // the key box in registers: the shared-memory atomics below clobber memory for the compiler, so
-    // anything left in s_dense would be re-read from shared memory in every tile
-    using box_t = typename std::conditional<K8, u64, u32>::type;  // 32 bits when every key column is 4 bytes wide
-    box_t bmin[NK], blim[NK];
-    u32 bmul[NK];
-    bool bnull[NK], bexcl[NK], bw4[NK];
-#pragma unroll
-    for (int k = 0; k < NK; ++k) {
-      const DKeyCol& c = P.keys[k];
-      bnull[k] = c.nullbit >= 0;
-      bexcl[k] = c.mask && !P.include_nulls;
-      bw4[k]   = !K8 || c.width == 4;
-      bmin[k]  = (box_t)s_dense.min[k];
-      blim[k]  = (box_t)(s_dense.range[k] - (bnull[k] ? 1ull : 0ull));
-      bmul[k]  = s_dense.mult[k];
-    }
-    float4 q, nq;
-    u32 vn = 0, act = 0, nvn = 0, nact = 0;
-    uint4 ka[NK], kb[NK], nka[NK], nkb[NK];
-    u32 kn[NK], nkn[NK];
-    // Register prefetch of the next tile pays off with 4-byte keys; with 8-byte key columns the second
-    // set of vector registers costs more than it hides (1 x int64 key: 0.361 ms with, 0.331 ms without).
-    constexpr bool PREFETCH = !K8;
-    if (PREFETCH && blockIdx.x < nfull) load_tile(blockIdx.x, q, vn, act, ka, kb, kn);
-    for (u32 tile = blockIdx.x; tile < nfull; tile += gridDim.x) {
-      const u32 r0 = tile * lean_tile + (u32)tid * LEAN_ROWS;
-      // software pipelining: the next tile's loads are in flight while this tile is folded
-      const u32 next = tile + gridDim.x;
-      if (!PREFETCH) load_tile(tile, q, vn, act, ka, kb, kn);
-      {
-        // the tile after (8-byte keys) is requested into L2 while this one is folded
-        constexpr u32 DIST = K8 ? 1 : 0;  // (distances 2 and 3, and 1-2 for 4-byte keys, measured the same)
-        const u32 far = tile + DIST * gridDim.x;
-        if (DIST > 0 && far < nfull) {
-          const u32 fr0 = far * lean_tile + (u32)tid * LEAN_ROWS;
-          prefetch_l2((const float*)vc.data + (u32)vc.offset + fr0);
-#pragma unroll
-          for (int k = 0; k < NK; ++k) prefetch_l2(P.keys[k].data + (u64)((u32)P.keys[k].offset + fr0) * (u32)P.keys[k].width);
-        }
-      }
-      if (PREFETCH && next < nfull) load_tile(next, nq, nvn, nact, nka, nkb, nkn);
-      // dense slots
-      u32 d0 = copy_off, d1 = copy_off, d2 = copy_off, d3 = copy_off, bad = 0;
-#pragma unroll
-      for (int k = 0; k < NK; ++k) {
-        if (bexcl[k]) act &= kn[k];
-        const u32 mult = bmul[k];
-        u32 x0, x1, x2, x3, o;
-        if (bw4[k]) {
-          const u32 mn = (u32)bmin[k];
-          const u32 lim = (u32)blim[k];
-          x0 = ka[k].x - mn; x1 = ka[k].y - mn; x2 = ka[k].z - mn; x3 = ka[k].w - mn;
-          // (straight-line bits; a single max-then-branch test of the rare case measured 4 % slower)
-          o = (x0 >= lim ? 1u : 0u) | (x1 >= lim ? 2u : 0u) | (x2 >= lim ? 4u : 0u) | (x3 >= lim ? 8u : 0u);
-          if (bnull[k]) {
-            if (!(kn[k] & 1u)) x0 = lim; if (!(kn[k] & 2u)) x1 = lim; if (!(kn[k] & 4u)) x2 = lim; if (!(kn[k] & 8u)) x3 = lim;
-            o &= kn[k];
-          }
-        } else {
-          const u64 mn = (u64)bmin[k];
-          const u64 lim = (u64)blim[k];
-          const u64 y0 = (((u64)ka[k].y << 32) | ka[k].x) - mn, y1 = (((u64)ka[k].w << 32) | ka[k].z) - mn;
-          const u64 y2 = (((u64)kb[k].y << 32) | kb[k].x) - mn, y3 = (((u64)kb[k].w << 32) | kb[k].z) - mn;
-          o = (y0 >= lim ? 1u : 0u) | (y1 >= lim ? 2u : 0u) | (y2 >= lim ? 4u : 0u) | (y3 >= lim ? 8u : 0u);
-          x0 = (u32)y0; x1 = (u32)y1; x2 = (u32)y2; x3 = (u32)y3;
-          if (bnull[k]) {
-            if (!(kn[k] & 1u)) x0 = (u32)lim; if (!(kn[k] & 2u)) x1 = (u32)lim; if (!(kn[k] & 4u)) x2 = (u32)lim; if (!(kn[k] & 8u)) x3 = (u32)lim;
-            o &= kn[k];
-          }
-        }
-        bad |= o;
-        d0 += x0 * mult; d1 += x1 * mult; d2 += x2 * mult; d3 += x3 * mult;
-      }
-      const u32 take = act & ~bad & vn;  // rows folded in shared memory
-      // the four rows' shared-memory atomics are issued back to back; the counts they return are
-      // looked at afterwards, so that the warp waits for one round trip, not four
-      u32 o0 = 0, o1 = 0, o2 = 0, o3 = 0;
-#define B2_LEAN_FOLD(J, D, X, O)                                                                    \
-      if (take & (1u << J)) {                                                                       \
-        sred_add_f32(ssum_a + 4u * (D), (X));                                                       \
-        O = satom_add_u32(scnt_a + 4u * (D), 1u);                                                   \
-      }
-      B2_LEAN_FOLD(0, d0, q.x, o0) B2_LEAN_FOLD(1, d1, q.y, o1) B2_LEAN_FOLD(2, d2, q.z, o2) B2_LEAN_FOLD(3, d3, q.w, o3)
-#undef B2_LEAN_FOLD
-      // every F32_SPILL_AT-th addend moves the fp32 partial of this key to the fp64 global cell, so
-      // that no fp32 sum ever holds many more addends than that (rows not taken keep O = 0)
-#define B2_LEAN_SPILL(D, O)                                                                         \
-      if (((O + 1u) & (F32_SPILL_AT - 1u)) == 0u) {                                                 \
-        const float part = atomicExch(ssum + (D), 0.f);                                             \
-        atomicAdd((double*)slot_ref(tbl, cap, stride, dense_slots, dense_gslot((D) - copy_off)).cells, (double)part);         \
-      }
-      if ((((o0 + 1u) & (F32_SPILL_AT - 1u)) == 0u) | (((o1 + 1u) & (F32_SPILL_AT - 1u)) == 0u) |
-          (((o2 + 1u) & (F32_SPILL_AT - 1u)) == 0u) | (((o3 + 1u) & (F32_SPILL_AT - 1u)) == 0u)) {
-        B2_LEAN_SPILL(d0, o0) B2_LEAN_SPILL(d1, o1) B2_LEAN_SPILL(d2, o2) B2_LEAN_SPILL(d3, o3)
-      }
-#undef B2_LEAN_SPILL
-      // rare rows: active but (a) null value -> only mark the group as present, (b) key outside the box
-      const u32 rare = act & (bad | ~vn);
-      if (rare) {
-        const u32 ds[LEAN_ROWS]  = {d0, d1, d2, d3};
-        const float xs[LEAN_ROWS] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-        for (int j = 0; j < LEAN_ROWS; ++j) {  // unrolled: no dynamic indexing
-          if (!((rare >> j) & 1u)) continue;
-          if (!((bad >> j) & 1u)) {
-            const u32 s = ds[j];
-            if (!((socc[s >> 5] >> (s & 31u)) & 1u)) atomicOr(&socc[s >> 5], 1u << (s & 31u));
-          } else {
-            const u64 key = pack_key(P, (i64)r0 + j);
-            const i64 g   = gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, &s_new);
-            ++my_miss;
-            if (g >= 0 && ((vn >> j) & 1u)) {
-              atomicAdd((double*)(tbl + g * stride + 1), (double)xs[j]);
-              atomicAdd(tbl + g * stride + 2, 1ull);
-            }
-          }
-        }
-      }
-      my_hit += __popc(act & ~bad);
-      if (tid == 0 && *(volatile int*)&s_new != 0) {
-        const int c = atomicExch(&s_new, 0);
-        const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)c) + (u64)c;
-        if (tot > ctrl->claim_limit) ctrl->overflow = 1;
-      }
-      if (PREFETCH) {
-        q = nq; vn = nvn; act = nact;
-#pragma unroll
-        for (int k = 0; k < NK; ++k) { ka[k] = nka[k]; if (K8) kb[k] = nkb[k]; kn[k] = nkn[k]; }
-      }
-    }
-  }
+  const i64 rows_done = 0;
 
   const i64 tile_rows = (i64)blockDim.x * AGG_ROWS;
   const i64 ntiles    = (P.nrows - rows_done + tile_rows - 1) / tile_rows;
@@ -955,7 +802,6 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
       const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)s_new) + (u64)s_new;
       if (tot > ctrl->claim_limit) ctrl->overflow = 1;
     }
-    if (dense) atomicAdd(&ctrl->reserved, 1ull);  // CTAs that ran with the dense key box
     if (timekeeper) ctrl->t_phase[4] = global_timer_ns();
   }
 }
@@ -1087,6 +933,65 @@ __device__ __forceinline__ void clear_bit(u32* mask, i64 g, u32* counter)
   atomicAdd(counter, 1u);
 }
 
+// One finished group -> output row g: key columns decoded from the key cell (packed keys) or the
+// representative row noted (row keys), then every requested aggregation from the accumulator cells
+// (cell c at cells[c * cstep]): COUNT as INT32, MEAN = Σx / n, M2 = Σx² − (Σx)²/n, VAR = M2 / (n − ddof),
+// STD = sqrt(VAR); results without a valid input are nulled and counted.
+__device__ __forceinline__ void write_group(const DPlan& P, const DOutPlan& O, u64 key, const u64* cells, i64 cstep, i64 g)
+{
+  if (P.key_mode == KM_PACKED) {
+    for (int k = 0; k < P.nkeys; ++k) {
+      const DKeyCol& c = P.keys[k];
+      if (c.nullbit >= 0 && ((key >> c.nullbit) & 1ull)) {
+        clear_bit(O.kmask[k], g, O.null_counts + MAX_OUTS + k);
+        store_int(O.kdata[k], g, c.width == 1 ? VC_U8 : c.width == 2 ? VC_U16 : c.width == 4 ? VC_U32 : VC_U64, 0);
+      } else {
+        const u64 v = (c.width == 8) ? (key >> c.shift) : ((key >> c.shift) & ((1ull << (8 * c.width)) - 1ull));
+        store_int(O.kdata[k], g, c.width == 1 ? VC_U8 : c.width == 2 ? VC_U16 : c.width == 4 ? VC_U32 : VC_U64, v);
+      }
+    }
+  } else {
+    O.rep_rows[g] = (int)(u32)key;
+  }
+  for (int o = 0; o < O.nouts; ++o) {
+    const DOutCol& oc = O.outs[o];
+    const i64 n = oc.c_cnt >= 0 ? (i64)cells[(i64)(oc.c_cnt) * cstep] : 1;
+    bool valid  = n > 0;
+    switch (oc.kind) {
+      case OK_COUNT: ((int*)oc.data)[g] = (int)cells[(i64)(oc.c_a) * cstep]; valid = true; break;
+      case OK_INT: store_int(oc.data, g, oc.rclass, valid ? cells[(i64)(oc.c_a) * cstep] : 0); break;
+      case OK_FLT: store_flt(oc.data, g, oc.rclass, valid ? __longlong_as_double((i64)cells[(i64)(oc.c_a) * cstep]) : 0.0); break;
+      case OK_MINMAX_F:
+        store_flt(oc.data, g, oc.rclass, valid ? __longlong_as_double((i64)f64_unordered(cells[(i64)(oc.c_a) * cstep])) : 0.0);
+        break;
+      case OK_MEAN: {
+        if (oc.rclass != VC_F64) {  // durations: integer division in the source type
+          store_int(oc.data, g, oc.rclass, valid ? (u64)((i64)cells[(i64)(oc.c_a) * cstep] / n) : 0);
+          break;
+        }
+        const double s = oc.src_float ? __longlong_as_double((i64)cells[(i64)(oc.c_a) * cstep]) : (double)(i64)cells[(i64)(oc.c_a) * cstep];
+        ((double*)oc.data)[g] = valid ? s / (double)n : 0.0;
+        break;
+      }
+      default: {  // M2, VAR, STD
+        double m2 = 0.0;
+        if (n > 0) {
+          const double s  = oc.src_float ? __longlong_as_double((i64)cells[(i64)(oc.c_a) * cstep]) : (double)(i64)cells[(i64)(oc.c_a) * cstep];
+          const double ss = oc.src_float ? __longlong_as_double((i64)cells[(i64)(oc.c_b) * cstep]) : (double)(i64)cells[(i64)(oc.c_b) * cstep];
+          m2 = ss - s * s / (double)n;
+        }
+        if (oc.kind == OK_M2) { ((double*)oc.data)[g] = m2; valid = true; break; }
+        const i64 df = n - oc.ddof;
+        valid        = n > 0 && df > 0;
+        const double var = valid ? m2 / (double)df : 0.0;
+        ((double*)oc.data)[g] = (oc.kind == OK_VAR) ? var : sqrt(var);
+        break;
+      }
+    }
+    if (!valid && oc.mask) clear_bit(oc.mask, g, O.null_counts + oc.null_slot);
+  }
+}
+
 constexpr int FIN_BLOCK = 256;
 constexpr int FIN_ITEMS = 8;  // slots per thread per chunk (1 for small tables, which otherwise fill few SMs)
 
@@ -1136,64 +1041,7 @@ __global__ void __launch_bounds__(FIN_BLOCK) k_finalize(const __grid_constant__ 
       if (!((m >> lane) & 1u)) continue;
       const i64 s = ch * chunk + (i64)j * FIN_BLOCK + threadIdx.x;
       const SlotRef ref = slot_ref(const_cast<u64*>(tbl), cap, stride, dense, s);
-      const u64 key = s == cap ? EMPTY : *ref.key;
-    const u64* cells = ref.cells;
-    const i64 cstep  = ref.step;
-
-    // keys
-    if (P.key_mode == KM_PACKED) {
-      for (int k = 0; k < P.nkeys; ++k) {
-        const DKeyCol& c = P.keys[k];
-        if (c.nullbit >= 0 && ((key >> c.nullbit) & 1ull)) {
-          clear_bit(O.kmask[k], g, O.null_counts + MAX_OUTS + k);
-          store_int(O.kdata[k], g, c.width == 1 ? VC_U8 : c.width == 2 ? VC_U16 : c.width == 4 ? VC_U32 : VC_U64, 0);
-        } else {
-          const u64 v = (c.width == 8) ? (key >> c.shift) : ((key >> c.shift) & ((1ull << (8 * c.width)) - 1ull));
-          store_int(O.kdata[k], g, c.width == 1 ? VC_U8 : c.width == 2 ? VC_U16 : c.width == 4 ? VC_U32 : VC_U64, v);
-        }
-      }
-    } else {
-      O.rep_rows[g] = (int)(u32)key;
-    }
-
-    // results
-    for (int o = 0; o < O.nouts; ++o) {
-      const DOutCol& oc = O.outs[o];
-      const i64 n = oc.c_cnt >= 0 ? (i64)cells[(i64)(oc.c_cnt) * cstep] : 1;
-      bool valid  = n > 0;
-      switch (oc.kind) {
-        case OK_COUNT: ((int*)oc.data)[g] = (int)cells[(i64)(oc.c_a) * cstep]; valid = true; break;
-        case OK_INT: store_int(oc.data, g, oc.rclass, valid ? cells[(i64)(oc.c_a) * cstep] : 0); break;
-        case OK_FLT: store_flt(oc.data, g, oc.rclass, valid ? __longlong_as_double((i64)cells[(i64)(oc.c_a) * cstep]) : 0.0); break;
-        case OK_MINMAX_F:
-          store_flt(oc.data, g, oc.rclass, valid ? __longlong_as_double((i64)f64_unordered(cells[(i64)(oc.c_a) * cstep])) : 0.0);
-          break;
-        case OK_MEAN: {
-          if (oc.rclass != VC_F64) {  // durations: integer division in the source type
-            store_int(oc.data, g, oc.rclass, valid ? (u64)((i64)cells[(i64)(oc.c_a) * cstep] / n) : 0);
-            break;
-          }
-          const double s = oc.src_float ? __longlong_as_double((i64)cells[(i64)(oc.c_a) * cstep]) : (double)(i64)cells[(i64)(oc.c_a) * cstep];
-          ((double*)oc.data)[g] = valid ? s / (double)n : 0.0;
-          break;
-        }
-        default: {  // M2, VAR, STD
-          double m2 = 0.0;
-          if (n > 0) {
-            const double s  = oc.src_float ? __longlong_as_double((i64)cells[(i64)(oc.c_a) * cstep]) : (double)(i64)cells[(i64)(oc.c_a) * cstep];
-            const double ss = oc.src_float ? __longlong_as_double((i64)cells[(i64)(oc.c_b) * cstep]) : (double)(i64)cells[(i64)(oc.c_b) * cstep];
-            m2 = ss - s * s / (double)n;
-          }
-          if (oc.kind == OK_M2) { ((double*)oc.data)[g] = m2; valid = true; break; }
-          const i64 df = n - oc.ddof;
-          valid        = n > 0 && df > 0;
-          const double var = valid ? m2 / (double)df : 0.0;
-          ((double*)oc.data)[g] = (oc.kind == OK_VAR) ? var : sqrt(var);
-          break;
-        }
-      }
-      if (!valid && oc.mask) clear_bit(oc.mask, g, O.null_counts + oc.null_slot);
-    }
+      write_group(P, O, s == cap ? EMPTY : *ref.key, ref.cells, ref.step, g);
     }
     __syncthreads();  // the shared arrays are rewritten by the next chunk
   }

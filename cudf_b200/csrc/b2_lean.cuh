@@ -1,0 +1,451 @@
+// b2_lean.cuh — the lean instantiation of the fused aggregate pass: "Σ and n of one FLOAT32 column"
+// (a mean) over 1..3 fixed-width key columns whose sampled key box fits shared memory.
+//
+//   k_aggregate_lean<NK, K8, STAGED>
+//     replaces mapping_indices_kernel + single_pass_shmem_aggs_kernel for this shape
+//     (cpp/src/groupby/hash/compute_mapping_indices.cuh:92-151, compute_shared_memory_aggs.cu:260-353).
+//
+// It is a kernel of its own, not a branch of k_aggregate, so that its register allocation is decided
+// by its row loop alone: everything rare (keys outside the sampled box, rows whose value is null,
+// the fp32 -> fp64 spill of a long partial sum, the ragged end of the input) lives in __noinline__
+// functions.  One CTA per SM, 4 consecutive rows per thread per tile, two native shared-memory
+// atomics per row into the CTA's direct-indexed table {fp32 partial sum, u32 count}.
+//
+//   STAGED = false : tiles go global -> registers with 16-byte ld.global.nc, the next tile's vectors
+//                    are loaded into a second register set while the current tile is folded;
+//   STAGED = true  : one producer warp streams key / value / validity tiles into a shared-memory
+//                    ring with cp.async.bulk (no multicast, no tensor map: the columns are flat)
+//                    completing on an mbarrier per stage; 31 consumer warps read the tiles from
+//                    shared memory.  Every wait is bounded; a wait that runs out sets ctrl->error.
+//
+// The key box comes from the control block: the sampler runs in k_table_init, which precedes this
+// kernel on the stream.  If the box did not fit, the kernel returns at once and the generic
+// k_aggregate (always launched behind it) takes the whole input.
+#pragma once
+#include "b2_kernels.cuh"
+
+namespace b2 {
+
+constexpr int LEAN_STAGED_CONSUMERS = 992;  // 31 consumer warps; warp 31 is the producer
+constexpr int LEAN_STAGES           = 2;
+constexpr int LEAN_MASK_BYTES       = 512;  // validity bytes of one staged tile, padded
+constexpr int LEAN_WAIT_TRIES       = 1 << 20;
+
+// ------------------------------------------------------------------------------ mbarrier / bulk copy
+__device__ __forceinline__ void mbar_init(u32 bar, u32 count)
+{
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(u32 bar, u32 bytes)
+{
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(u32 bar)
+{
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(u32 bar, u32 parity)
+{
+  u32 ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// bounded: false when the phase did not complete within LEAN_WAIT_TRIES attempts
+__device__ __forceinline__ bool mbar_wait(u32 bar, u32 parity)
+{
+  for (int i = 0; i < LEAN_WAIT_TRIES; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// flat global -> shared copy of `bytes` (a multiple of 16; both addresses 16-byte aligned) that
+// reports its bytes to `bar`
+__device__ __forceinline__ void bulk_g2s(u32 dst, const void* src, u32 bytes, u32 bar)
+{
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// ------------------------------------------------------------------------------ rare paths
+struct LeanRare {  // what the rare paths need: this CTA's table and the global one
+  float* ssum; u32* socc; int* s_new;
+  u64* tbl; i64 cap; i64 region; int stride; int special_pos;
+  DCtrl* ctrl; const DDense* box;
+};
+
+// reports this CTA's unreported slot claims of the hashed region
+__device__ __forceinline__ void lean_report_claims(const LeanRare& L)
+{
+  const int c = atomicExch(L.s_new, 0);
+  if (c) {
+    const u64 tot = atomicAdd(&L.ctrl->nclaimed, (u64)c) + (u64)c;
+    if (tot > L.ctrl->claim_limit) L.ctrl->overflow = 1;
+  }
+}
+
+// global slot of box position `pos`
+__device__ __forceinline__ SlotRef lean_box_slot(const LeanRare& L, u32 pos)
+{
+  const i64 g = (int)pos == L.special_pos ? L.cap : L.cap + 1 + (i64)pos;
+  return slot_ref(L.tbl, L.cap, L.stride, L.region, g);
+}
+
+// a row that cannot be folded in shared memory: its key lies outside the sampled box (global hashed
+// region), or it belongs to the ragged end of the input (in-box keys go to the dense region directly)
+__device__ __noinline__ void lean_slow_row(const DPlan& P, const LeanRare& L, i64 row, bool check_active)
+{
+  if (check_active && !row_active(P, row)) return;
+  if (*(volatile u32*)&L.ctrl->overflow) return;  // this attempt will be discarded
+  const u64 key = pack_key(P, row);
+  const int di  = key != EMPTY ? dense_index(P, *L.box, key) : -1;
+  SlotRef ref;
+  if (di >= 0) {
+    ref = lean_box_slot(L, (u32)di);
+    if ((int)di != L.special_pos && *(volatile u64*)ref.key == EMPTY) *(volatile u64*)ref.key = key;
+  } else {
+    const i64 g = gmem_find_insert_packed(L.tbl, L.cap, L.stride, key, mix64(key), L.ctrl, L.s_new);
+    lean_report_claims(L);
+    if (g < 0) return;
+    ref = slot_ref(L.tbl, L.cap, L.stride, L.region, g);
+  }
+  const DValCol& vc = P.vals[P.cells[0].col];
+  if (value_valid(vc, row)) {
+    atomicAdd((double*)ref.cells, (double)__ldg((const float*)vc.data + vc.offset + row));
+    atomicAdd(ref.cells + ref.step, 1ull);
+  }
+}
+
+// the rare rows of one 4-row group: active rows whose value is null (the group exists, nothing is
+// added) and active rows whose key lies outside the box
+__device__ __noinline__ void lean_rare_rows(const DPlan& P, const LeanRare& L, u32 rare, u32 bad, i64 r0, u32 d0, u32 d1,
+                                            u32 d2, u32 d3)
+{
+  const u32 ds[4] = {d0, d1, d2, d3};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (!((rare >> j) & 1u)) continue;
+    if (!((bad >> j) & 1u)) {
+      const u32 s = ds[j];
+      if (!((L.socc[s >> 5] >> (s & 31u)) & 1u)) atomicOr(&L.socc[s >> 5], 1u << (s & 31u));
+    } else {
+      lean_slow_row(P, L, r0 + j, false);
+    }
+  }
+}
+
+// every F32_SPILL_AT-th addend of a shared-memory slot moves its fp32 partial sum to the fp64 global
+// cell, so that no fp32 sum ever holds many more addends than that
+__device__ __noinline__ void lean_spill(const LeanRare& L, u32 slot, u32 copy_off)
+{
+  const float part = atomicExch(L.ssum + slot, 0.f);
+  atomicAdd((double*)lean_box_slot(L, slot - copy_off).cells, (double)part);
+}
+
+// ------------------------------------------------------------------------------ the kernel
+template <int NK, bool K8, bool STAGED>
+__global__ void __launch_bounds__(1024, 1)
+k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* ctrl, u32 region_slots)
+{
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ DDense s_dense;
+  __shared__ int s_new, s_last;
+  __shared__ __align__(8) u64 s_bars[2 * LEAN_STAGES];
+
+  const int tid = threadIdx.x;
+  const bool timekeeper = blockIdx.x == 0 && tid == 0;
+  if (timekeeper) ctrl->t_phase[0] = global_timer_ns();
+  // the key box sampled by k_table_init
+  for (int i = tid; i < (int)(sizeof(DDense) / 4); i += blockDim.x) ((u32*)&s_dense)[i] = ((const u32*)&ctrl->dense)[i];
+  if (tid == 0) { s_new = 0; s_last = 0; }
+  __syncthreads();
+  if (!s_dense.enabled) return;  // no box: the generic kernel behind this one takes the input
+  if (timekeeper) ctrl->t_phase[1] = global_timer_ns();
+
+  const int stride  = P.stride;
+  const int S       = (int)s_dense.total;
+  const int copies  = (int)s_dense.copies;
+  const int NS      = S * copies;
+  const int NSP     = (NS + 3) & ~3;  // arrays padded to 16 bytes
+  const u32 copy_off = (u32)((tid >> 5) % copies) * (u32)S;
+
+  float* ssum = (float*)smem_raw;       // [NSP] fp32 partial sums
+  u32* scnt   = (u32*)(ssum + NSP);     // [NSP] counts
+  u32* socc   = scnt + NSP;             // [(NS + 31) / 32] groups seen through a null value only
+  const int nocc = (NS + 31) / 32;
+  unsigned char* stage0 = smem_raw + (((size_t)(2 * NSP + nocc) * 4 + 127) & ~(size_t)127);
+
+  for (int i = tid; i < 2 * NSP + nocc; i += blockDim.x) ((u32*)smem_raw)[i] = 0;
+
+  const DValCol& vc = P.vals[P.cells[0].col];
+  const u32 ssum_a = (u32)__cvta_generic_to_shared(ssum), scnt_a = (u32)__cvta_generic_to_shared(scnt);
+  const bool filt_is_val = P.nfilters == 1 && P.filters[0] == vc.mask && P.filter_offsets[0] == vc.offset;
+
+  // position of the key whose bits equal EMPTY inside the box (it lives in the special slot), or -1
+  int special_pos = -1;
+  {
+    int bits = 0;
+    for (int k = 0; k < P.nkeys; ++k) bits += 8 * P.keys[k].width + (P.keys[k].nullbit >= 0 ? 1 : 0);
+    if (bits == 64) special_pos = dense_index(P, s_dense, EMPTY);
+  }
+  LeanRare L{ssum, socc, &s_new, tbl, cap, (i64)region_slots, stride, special_pos, ctrl, &s_dense};
+
+  // the key box in registers: the shared-memory atomics below clobber memory for the compiler, so
+  // anything left in s_dense would be re-read from shared memory in every tile
+  using box_t = typename std::conditional<K8, u64, u32>::type;  // 32 bits when every key column is 4 bytes wide
+  box_t bmin[NK], blim[NK];
+  u32 bmul[NK];
+  bool bnull[NK], bexcl[NK], bw4[NK];
+#pragma unroll
+  for (int k = 0; k < NK; ++k) {
+    const DKeyCol& c = P.keys[k];
+    bnull[k] = c.nullbit >= 0;
+    bexcl[k] = c.mask && !P.include_nulls;
+    bw4[k]   = !K8 || c.width == 4;
+    bmin[k]  = (box_t)s_dense.min[k];
+    blim[k]  = (box_t)(s_dense.range[k] - (bnull[k] ? 1ull : 0ull));
+    bmul[k]  = s_dense.mult[k];
+  }
+
+  if (STAGED && tid == 0) {
+    const u32 bar0 = (u32)__cvta_generic_to_shared(s_bars);
+    for (int s = 0; s < LEAN_STAGES; ++s) {
+      mbar_init(bar0 + 8u * s, 1);                                              // "full": the producer's expect_tx
+      mbar_init(bar0 + 8u * (LEAN_STAGES + s), LEAN_STAGED_CONSUMERS / 32);     // "empty": one arrival per consumer warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (timekeeper) ctrl->t_phase[2] = global_timer_ns();
+
+  // folds one group of 4 consecutive rows starting at row r0
+  auto fold = [&](i64 r0, const uint4 (&ka)[NK], const uint4 (&kb)[NK], const u32 (&kn)[NK], const float4& q, u32 vn, u32 act) {
+    u32 d0 = copy_off, d1 = copy_off, d2 = copy_off, d3 = copy_off, bad = 0;
+#pragma unroll
+    for (int k = 0; k < NK; ++k) {
+      if (bexcl[k]) act &= kn[k];
+      const u32 mult = bmul[k];
+      u32 x0, x1, x2, x3, o;
+      if (bw4[k]) {
+        const u32 mn = (u32)bmin[k];
+        const u32 lim = (u32)blim[k];
+        x0 = ka[k].x - mn; x1 = ka[k].y - mn; x2 = ka[k].z - mn; x3 = ka[k].w - mn;
+        o = (x0 >= lim ? 1u : 0u) | (x1 >= lim ? 2u : 0u) | (x2 >= lim ? 4u : 0u) | (x3 >= lim ? 8u : 0u);
+        if (bnull[k]) {
+          if (!(kn[k] & 1u)) x0 = lim; if (!(kn[k] & 2u)) x1 = lim; if (!(kn[k] & 4u)) x2 = lim; if (!(kn[k] & 8u)) x3 = lim;
+          o &= kn[k];
+        }
+      } else {
+        const u64 mn = (u64)bmin[k];
+        const u64 lim = (u64)blim[k];
+        const u64 y0 = (((u64)ka[k].y << 32) | ka[k].x) - mn, y1 = (((u64)ka[k].w << 32) | ka[k].z) - mn;
+        const u64 y2 = (((u64)kb[k].y << 32) | kb[k].x) - mn, y3 = (((u64)kb[k].w << 32) | kb[k].z) - mn;
+        o = (y0 >= lim ? 1u : 0u) | (y1 >= lim ? 2u : 0u) | (y2 >= lim ? 4u : 0u) | (y3 >= lim ? 8u : 0u);
+        x0 = (u32)y0; x1 = (u32)y1; x2 = (u32)y2; x3 = (u32)y3;
+        if (bnull[k]) {
+          if (!(kn[k] & 1u)) x0 = (u32)lim; if (!(kn[k] & 2u)) x1 = (u32)lim; if (!(kn[k] & 4u)) x2 = (u32)lim; if (!(kn[k] & 8u)) x3 = (u32)lim;
+          o &= kn[k];
+        }
+      }
+      bad |= o;
+      d0 += x0 * mult; d1 += x1 * mult; d2 += x2 * mult; d3 += x3 * mult;
+    }
+    const u32 take = act & ~bad & vn;  // rows folded in shared memory
+    // the four rows' shared-memory atomics are issued back to back; the counts they return are
+    // looked at afterwards, so that the warp waits for one round trip, not four
+    u32 o0 = 0, o1 = 0, o2 = 0, o3 = 0;
+    if (take & 1u) { sred_add_f32(ssum_a + 4u * d0, q.x); o0 = satom_add_u32(scnt_a + 4u * d0, 1u); }
+    if (take & 2u) { sred_add_f32(ssum_a + 4u * d1, q.y); o1 = satom_add_u32(scnt_a + 4u * d1, 1u); }
+    if (take & 4u) { sred_add_f32(ssum_a + 4u * d2, q.z); o2 = satom_add_u32(scnt_a + 4u * d2, 1u); }
+    if (take & 8u) { sred_add_f32(ssum_a + 4u * d3, q.w); o3 = satom_add_u32(scnt_a + 4u * d3, 1u); }
+    if ((((o0 + 1u) & (F32_SPILL_AT - 1u)) == 0u) | (((o1 + 1u) & (F32_SPILL_AT - 1u)) == 0u) |
+        (((o2 + 1u) & (F32_SPILL_AT - 1u)) == 0u) | (((o3 + 1u) & (F32_SPILL_AT - 1u)) == 0u)) {
+      // (rows not taken keep o = 0)
+      if (((o0 + 1u) & (F32_SPILL_AT - 1u)) == 0u) lean_spill(L, d0, copy_off);
+      if (((o1 + 1u) & (F32_SPILL_AT - 1u)) == 0u) lean_spill(L, d1, copy_off);
+      if (((o2 + 1u) & (F32_SPILL_AT - 1u)) == 0u) lean_spill(L, d2, copy_off);
+      if (((o3 + 1u) & (F32_SPILL_AT - 1u)) == 0u) lean_spill(L, d3, copy_off);
+    }
+    const u32 rare = act & (bad | ~vn);
+    if (rare) lean_rare_rows(P, L, rare, bad, r0, d0, d1, d2, d3);
+  };
+
+  i64 rows_done = 0;
+  if (!STAGED) {
+    // ---- tiles from global memory into registers
+    const u32 tile_rows = 1024u * LEAN_ROWS;
+    const u32 nfull     = (u32)(P.nrows / tile_rows);
+    rows_done           = (i64)nfull * tile_rows;
+    auto load_tile = [&](u32 tile, float4& q, u32& vn, u32& act, uint4 (&ka)[NK], uint4 (&kb)[NK], u32 (&kn)[NK]) {
+      const u32 r0 = tile * tile_rows + (u32)tid * LEAN_ROWS;
+      const u32 ve = (u32)vc.offset + r0;
+      q  = __ldg((const float4*)((const float*)vc.data + ve));
+      vn = vc.mask ? nibble_aligned(vc.mask, ve) : 0xFu;
+      act = 0xFu;
+      if (filt_is_val) act = vn;
+      else for (int f = 0; f < P.nfilters; ++f) act &= nibble_aligned(P.filters[f], (u32)P.filter_offsets[f] + r0);
+#pragma unroll
+      for (int k = 0; k < NK; ++k) {
+        const DKeyCol& c = P.keys[k];
+        const u32 e = (u32)c.offset + r0;
+        kn[k] = c.mask ? nibble_aligned(c.mask, e) : 0xFu;
+        const uint4* kp = (const uint4*)(c.data + (u64)e * (u32)c.width);
+        ka[k] = __ldg(kp);
+        if (K8 && c.width == 8) kb[k] = __ldg(kp + 1);
+        else kb[k] = make_uint4(0, 0, 0, 0);
+      }
+    };
+    float4 q, nq;
+    u32 vn = 0, act = 0, nvn = 0, nact = 0;
+    uint4 ka[NK], kb[NK], nka[NK], nkb[NK];
+    u32 kn[NK], nkn[NK];
+    // Register prefetch of the next tile pays off with 4-byte keys; with 8-byte key columns the second
+    // set of vector registers costs more than it hides, and the tile after is requested into L2 instead
+    constexpr bool PREFETCH = !K8;
+    if (PREFETCH && blockIdx.x < nfull) load_tile(blockIdx.x, q, vn, act, ka, kb, kn);
+    for (u32 tile = blockIdx.x; tile < nfull; tile += gridDim.x) {
+      const u32 next = tile + gridDim.x;
+      if (!PREFETCH) {
+        load_tile(tile, q, vn, act, ka, kb, kn);
+        if (next < nfull) {
+          const u32 fr0 = next * tile_rows + (u32)tid * LEAN_ROWS;
+          prefetch_l2((const float*)vc.data + (u32)vc.offset + fr0);
+#pragma unroll
+          for (int k = 0; k < NK; ++k) prefetch_l2(P.keys[k].data + (u64)((u32)P.keys[k].offset + fr0) * (u32)P.keys[k].width);
+        }
+      }
+      if (PREFETCH && next < nfull) load_tile(next, nq, nvn, nact, nka, nkb, nkn);
+      fold((i64)tile * tile_rows + (i64)tid * LEAN_ROWS, ka, kb, kn, q, vn, act);
+      if (PREFETCH) {
+        q = nq; vn = nvn; act = nact;
+#pragma unroll
+        for (int k = 0; k < NK; ++k) { ka[k] = nka[k]; kb[k] = nkb[k]; kn[k] = nkn[k]; }
+      }
+    }
+  } else {
+    // ---- tiles through the shared-memory ring.  Stage layout: [key column 0 | .. | key column NK-1 |
+    // value column | validity bytes of the value column].  The host only selects this variant when
+    // there are no key masks and the only row filter (if any) is the value column's own mask.
+    constexpr u32 TR = LEAN_STAGED_CONSUMERS * LEAN_ROWS;
+    const u32 nfull  = (u32)(P.nrows / TR);
+    rows_done        = (i64)nfull * TR;
+    u32 col_off[NK + 1];
+    u32 off = 0;
+#pragma unroll
+    for (int k = 0; k < NK; ++k) { col_off[k] = off; off += TR * (u32)P.keys[k].width; }
+    col_off[NK] = off;
+    const u32 mask_off = off + TR * 4u;
+    const u32 stage_bytes = mask_off + LEAN_MASK_BYTES;
+    const u32 bar0 = (u32)__cvta_generic_to_shared(s_bars);
+    const u32 stage_a = (u32)__cvta_generic_to_shared(stage0);
+    bool failed = false;
+    if (tid >= LEAN_STAGED_CONSUMERS) {
+      if (tid == LEAN_STAGED_CONSUMERS) {  // one lane issues every copy
+        u32 it = 0;
+        for (u32 tile = blockIdx.x; tile < nfull; tile += gridDim.x, ++it) {
+          const u32 s = it % LEAN_STAGES, round = it / LEAN_STAGES;
+          if (round > 0 && !mbar_wait(bar0 + 8u * (LEAN_STAGES + s), (round - 1) & 1u)) { failed = true; break; }
+          const u32 dst = stage_a + s * stage_bytes;
+          const u64 r0  = (u64)tile * TR;
+          const u32 full = bar0 + 8u * s;
+          mbar_expect_tx(full, mask_off + (vc.mask ? TR / 8u : 0u));
+#pragma unroll
+          for (int k = 0; k < NK; ++k)
+            bulk_g2s(dst + col_off[k], P.keys[k].data + ((u64)P.keys[k].offset + r0) * (u32)P.keys[k].width,
+                     TR * (u32)P.keys[k].width, full);
+          bulk_g2s(dst + col_off[NK], (const float*)vc.data + vc.offset + r0, TR * 4u, full);
+          if (vc.mask) bulk_g2s(dst + mask_off, (const unsigned char*)vc.mask + (((u64)vc.offset + r0) >> 3), TR / 8u, full);
+        }
+        // the copies still in flight must land before this CTA's shared memory is reused or released
+        if (failed) {
+          for (u32 s = 0; s < LEAN_STAGES && s < it; ++s) {
+            const u32 last = it - 1 - ((it - 1 - s) % LEAN_STAGES);  // last iteration that used stage s
+            mbar_wait(bar0 + 8u * s, (last / LEAN_STAGES) & 1u);
+          }
+        }
+      }
+    } else {
+      u32 it = 0;
+      for (u32 tile = blockIdx.x; tile < nfull; tile += gridDim.x, ++it) {
+        const u32 s = it % LEAN_STAGES, round = it / LEAN_STAGES;
+        if (!mbar_wait(bar0 + 8u * s, round & 1u)) { failed = true; break; }
+        const unsigned char* st = stage0 + (size_t)s * stage_bytes;
+        const u32 e = (u32)tid * LEAN_ROWS;  // element inside the tile
+        uint4 ka[NK], kb[NK];
+        u32 kn[NK];
+#pragma unroll
+        for (int k = 0; k < NK; ++k) {
+          kn[k] = 0xFu;
+          const uint4* kp = (const uint4*)(st + col_off[k] + (size_t)e * (u32)P.keys[k].width);
+          ka[k] = kp[0];
+          if (K8 && P.keys[k].width == 8) kb[k] = kp[1];
+          else kb[k] = make_uint4(0, 0, 0, 0);
+        }
+        const float4 q = *(const float4*)(st + col_off[NK] + (size_t)e * 4u);
+        const u32 vn = vc.mask ? ((*(const u32*)(st + mask_off + (e >> 5) * 4u)) >> (e & 31u)) & 0xFu : 0xFu;
+        const u32 act = filt_is_val ? vn : 0xFu;
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(bar0 + 8u * (LEAN_STAGES + s));  // the stage's data is in registers
+        fold((i64)tile * TR + e, ka, kb, kn, q, vn, act);
+      }
+    }
+    if (failed) ctrl->error = 1;
+  }
+
+  // ---- the ragged end of the input, row by row
+  for (i64 r = rows_done + (i64)blockIdx.x * blockDim.x + tid; r < P.nrows; r += (i64)gridDim.x * blockDim.x)
+    lean_slow_row(P, L, r, true);
+
+  // ---- merge this CTA's table into the dense region of the global table: the replicas of a box
+  // position are reduced in registers, then Σ and n are added with reductions that return nothing
+  // (no round trip), and the key cell is written with a plain store — every CTA writes the same key.
+  __syncthreads();
+  if (timekeeper) ctrl->t_phase[3] = global_timer_ns();
+  {
+    const int rot = (int)(((u64)blockIdx.x * 2654435761ull) % (u64)S);
+    for (int i0 = tid; i0 < S; i0 += blockDim.x) {
+      const int i = i0 + rot < S ? i0 + rot : i0 + rot - S;
+      double sum = 0.0;
+      u64 n = 0;
+      bool present = false;
+      for (int r = 0; r < copies; ++r) {
+        const int q = r * S + i;
+        const u32 c = scnt[q];
+        present = present || c != 0u || ((socc[q >> 5] >> (q & 31)) & 1u);
+        sum += (double)ssum[q];
+        n += c;
+      }
+      if (!present) continue;
+      const SlotRef ref = lean_box_slot(L, (u32)i);
+      if (i == special_pos) { if (ctrl->special_used == 0) ctrl->special_used = 1; }
+      else if (*(volatile u64*)ref.key == EMPTY) *(volatile u64*)ref.key = dense_key(P, s_dense, (u32)i);
+      if (n) { atomicAdd((double*)ref.cells, sum); atomicAdd(ref.cells + ref.step, n); }
+    }
+  }
+  lean_report_claims(L);
+
+  // ---- the last CTA to finish counts the groups of the dense region (their key cells were written
+  // with plain stores, so nobody counted them on the way)
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(&ctrl->done_ctas, 1ull) == (u64)gridDim.x - 1;
+  __syncthreads();
+  if (s_last) {
+    __threadfence();
+    int mine = 0;
+    for (int i = tid; i < S; i += blockDim.x) {
+      if (i == special_pos) continue;
+      const u64* kp = slot_ref(tbl, cap, stride, (i64)region_slots, cap + 1 + (i64)i).key;
+      mine += __ldcg(kp) != EMPTY ? 1 : 0;
+    }
+    mine = __reduce_add_sync(0xFFFFFFFFu, mine);
+    if ((tid & 31) == 0 && mine) atomicAdd(&s_new, mine);
+    __syncthreads();
+    if (tid == 0 && s_new) {
+      const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)s_new) + (u64)s_new;
+      if (tot > ctrl->claim_limit + (u64)S) ctrl->overflow = 1;
+    }
+  }
+  if (timekeeper) ctrl->t_phase[4] = global_timer_ns();
+}
+
+}  // namespace b2

@@ -1,0 +1,398 @@
+// b2_partition.cuh — the high-cardinality path: radix partition of the rows by key hash into
+// buckets whose groups fit a shared-memory table, then one shared-memory aggregate per bucket.
+//
+// Replaces the global-memory branch of the reference (compute_global_memory_aggs.cuh:74-187: one
+// probe of a global cuco set + one global atomic per row and aggregation) for inputs with millions of
+// groups.  There every row costs a random read-modify-write of a 32-byte sector per accumulator; here
+// the rows are moved twice at most, sequentially, and every atomic is a shared-memory atomic:
+//
+//   k_rp_count      one pass over the key columns: rows per level-1 digit (the top 10 bits of the key
+//                   hash) and, when the number of groups is not known, the HyperLogLog registers
+//   k_rp_scatter    rows -> records {key, value words, validity word}, written to the region of their
+//                   level-1 digit (structure-of-arrays record buffer; CTA-local counting per tile,
+//                   one global cursor reservation per digit and tile)
+//   k_rp_count2 /   second level inside every level-1 partition (only when one level leaves more
+//   k_rp_scatter2   groups per bucket than a shared-memory table holds)
+//   k_rp_aggregate  one CTA per bucket at a time: open-addressing table in shared memory, the
+//                   bucket's records folded with shared-memory atomics, the finished groups appended
+//                   to a compact record list (structure-of-arrays)
+//   k_finalize_records  record list -> output columns (the finishers of k_finalize)
+//
+// Packed keys only (all key columns fixed-width non-float, at most 64 bits together).
+#pragma once
+#include "b2_kernels.cuh"
+
+namespace b2 {
+
+constexpr int RP_BLOCK    = 1024;
+constexpr int RP_ROWS     = 8;                   // rows per thread per tile: two groups of 4 consecutive rows
+constexpr int RP_TILE     = RP_BLOCK * RP_ROWS;  // 8192 rows
+constexpr int RP_BITS_TOP = 10;                  // resolution of the first histogram
+constexpr int RP_MAX_BITS = 10;                  // widest digit of one level
+constexpr u64 RP_SALT     = 0x9FB21C651E98DF25ull;
+constexpr int RPA_BLOCK   = 512;                 // threads per CTA of the bucket aggregate (2 CTAs per SM)
+
+__device__ __forceinline__ u64 rp_hash(u64 key) { return mix64(key ^ RP_SALT); }
+
+// packed keys + activity of 4 consecutive rows starting at row0 (`nv` of them exist)
+__device__ __forceinline__ void rp_keys4(const DPlan& P, i64 row0, int nv, u64 (&kk)[4], u32& act)
+{
+  act = nv >= 4 ? 0xFu : (nv > 0 ? (1u << nv) - 1u : 0u);
+  if (nv == 4 && (P.flags & PF_VEC_KEYS)) {
+    packed_keys4(P, row0, kk, act);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      kk[j] = 0;
+      if (!((act >> j) & 1u)) continue;
+      if (!row_active(P, row0 + j)) { act &= ~(1u << j); continue; }
+      kk[j] = pack_key(P, row0 + j);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ level-1 histogram (+ HyperLogLog)
+template <bool WITH_HLL>
+__global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant__ DPlan P, u64* __restrict__ hist,
+                                                       u32* __restrict__ hll)
+{
+  __shared__ u32 s_hist[1 << RP_BITS_TOP];
+  __shared__ u32 s_regs[WITH_HLL ? HLL_REGS : 1];
+  for (int i = threadIdx.x; i < (1 << RP_BITS_TOP); i += blockDim.x) s_hist[i] = 0;
+  if (WITH_HLL) for (int i = threadIdx.x; i < HLL_REGS; i += blockDim.x) s_regs[i] = 0;
+  __syncthreads();
+  const i64 nquads = (P.nrows + 3) / 4;
+  for (i64 q = (i64)blockIdx.x * blockDim.x + threadIdx.x; q < nquads; q += (i64)gridDim.x * blockDim.x) {
+    u64 kk[4];
+    u32 act;
+    rp_keys4(P, q * 4, (int)min((i64)4, P.nrows - q * 4), kk, act);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (!((act >> j) & 1u)) continue;
+      atomicAdd(&s_hist[rp_hash(kk[j]) >> (64 - RP_BITS_TOP)], 1u);
+      if (WITH_HLL) {
+        const u64 h = mix64(kk[j] ^ 0x5bd1e9955bd1e995ull);  // same registers as k_hll
+        const u32 idx  = (u32)(h >> (64 - HLL_BITS));
+        const u32 rank = (u32)__clzll((i64)((h << HLL_BITS) | (1ull << (HLL_BITS - 1)))) + 1u;
+        if (s_regs[idx] < rank) atomicMax(&s_regs[idx], rank);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < (1 << RP_BITS_TOP); i += blockDim.x)
+    if (s_hist[i]) atomicAdd(&hist[i], (u64)s_hist[i]);
+  if (WITH_HLL)
+    for (int i = threadIdx.x; i < HLL_REGS; i += blockDim.x)
+      if (s_regs[i]) atomicMax(&hll[i], s_regs[i]);
+}
+
+// ------------------------------------------------------------------------------ records
+// A record buffer holds `cap` records, structure-of-arrays: word w of record i at rec[w * cap + i].
+// Word 0 is the packed key, words 1..nvals the value columns in their 64-bit carried form
+// (load_value), the last word (if any value column is nullable) the validity bits of the values.
+struct DRecords {
+  u64* rec;
+  i64 cap;
+  int words;       // words per record
+  int valid_word;  // index of the validity word, -1 = every value is valid
+};
+
+struct DScatter {
+  DRecords dst;
+  u64* cursors;  // [partitions] next free record of every destination (start offsets, advanced)
+  int shift;     // digit = (hash >> shift) & (fan - 1)
+  int fan;       // destinations per source partition (a power of two, <= 1 << RP_MAX_BITS)
+};
+
+// CTA-local counting of one tile, shared by both scatter levels.  Phase A gave every record its rank
+// among the tile's records of the same digit (s_hist); here the digits' runs are reserved with one
+// global atomic each and the counters are cleared for the next tile.
+__device__ __forceinline__ void rp_reserve(u32* s_hist, u64* s_base, u64* cursors, int fan)
+{
+  for (int d = threadIdx.x; d < fan; d += blockDim.x) {
+    const u32 c = s_hist[d];
+    s_hist[d] = 0;
+    if (c) s_base[d] = atomicAdd(&cursors[d], (u64)c);
+  }
+}
+
+// level 1: input rows -> records in the region of their digit
+__global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_scatter(const __grid_constant__ DPlan P, const DScatter D)
+{
+  __shared__ u32 s_hist[1 << RP_MAX_BITS];
+  __shared__ u64 s_base[1 << RP_MAX_BITS];
+  for (int i = threadIdx.x; i < D.fan; i += blockDim.x) s_hist[i] = 0;
+  __syncthreads();
+  const i64 ntiles = (P.nrows + RP_TILE - 1) / RP_TILE;
+  const u32 dmask = (u32)D.fan - 1u;
+  for (i64 tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    u64 kk[RP_ROWS];
+    u32 rank[RP_ROWS];
+    u32 act = 0;
+    // phase A: keys, digits, ranks inside the tile
+#pragma unroll
+    for (int g = 0; g < RP_ROWS / 4; ++g) {
+      const i64 row0 = tile * RP_TILE + (i64)g * (RP_TILE / 2) + (i64)threadIdx.x * 4;
+      u64 k4[4];
+      u32 a4;
+      rp_keys4(P, row0, (int)max((i64)0, min((i64)4, P.nrows - row0)), k4, a4);
+      act |= a4 << (4 * g);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        kk[4 * g + j] = k4[j];
+        rank[4 * g + j] = 0;
+        if ((a4 >> j) & 1u) {
+          const u32 d = (u32)(rp_hash(k4[j]) >> D.shift) & dmask;
+          rank[4 * g + j] = (d << 16) | atomicAdd(&s_hist[d], 1u);  // a tile holds 8192 rows: the rank fits 16 bits
+        }
+      }
+    }
+    __syncthreads();
+    rp_reserve(s_hist, s_base, D.cursors, D.fan);
+    __syncthreads();
+    // phase C: the records, word by word
+#pragma unroll
+    for (int g = 0; g < RP_ROWS / 4; ++g) {
+      const i64 row0 = tile * RP_TILE + (i64)g * (RP_TILE / 2) + (i64)threadIdx.x * 4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (!((act >> (4 * g + j)) & 1u)) continue;
+        const u32 r = rank[4 * g + j];
+        const i64 at = (i64)s_base[r >> 16] + (i64)(r & 0xFFFFu);
+        D.dst.rec[at] = kk[4 * g + j];
+        u64 vbits = 0;
+        for (int v = 0; v < P.nvals; ++v) {
+          const DValCol& vc = P.vals[v];
+          const bool ok = value_valid(vc, row0 + j);
+          vbits |= (u64)ok << v;
+          D.dst.rec[(i64)(1 + v) * D.dst.cap + at] = ok ? load_value(vc, row0 + j) : 0ull;
+        }
+        if (D.dst.valid_word >= 0) D.dst.rec[(i64)D.dst.valid_word * D.dst.cap + at] = vbits;
+      }
+    }
+    // (the next tile's phase A only touches s_hist, cleared above; s_base is rewritten after its barrier)
+  }
+}
+
+// Level 2 works on the tiles of the level-1 partitions: tile t belongs to the partition p with
+// tile_start[p] <= t < tile_start[p + 1] and covers records [start[p] + j * RP_TILE, ...) of it.
+struct DLevel2 {
+  DRecords src;
+  const u64* src_start;   // [parts + 1] first record of every source partition
+  const u64* src_end;     // [parts] one past its last record (the advanced level-1 cursors)
+  const u32* tile_start;  // [parts + 1] first tile of every source partition
+  int parts;
+};
+
+__device__ __forceinline__ int rp_partition_of_tile(const u32* tile_start, int parts, u32 tile)
+{
+  int lo = 0, hi = parts;  // tile_start[lo] <= tile < tile_start[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(tile_start + mid) <= tile) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// rows per (source partition, level-2 digit)
+__global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count2(const DLevel2 L, int shift, int fan, u64* __restrict__ hist2)
+{
+  __shared__ u32 s_hist[1 << RP_MAX_BITS];
+  for (int i = threadIdx.x; i < fan; i += blockDim.x) s_hist[i] = 0;
+  __syncthreads();
+  const u32 ntiles = __ldg(L.tile_start + L.parts);
+  const u32 dmask = (u32)fan - 1u;
+  for (u32 tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int p = rp_partition_of_tile(L.tile_start, L.parts, tile);
+    const i64 lo = (i64)L.src_start[p] + (i64)(tile - __ldg(L.tile_start + p)) * RP_TILE;
+    const i64 hi = min((i64)L.src_end[p], lo + RP_TILE);
+    for (i64 i = lo + threadIdx.x; i < hi; i += blockDim.x)
+      atomicAdd(&s_hist[(u32)(rp_hash(__ldg(L.src.rec + i)) >> shift) & dmask], 1u);
+    __syncthreads();
+    for (int d = threadIdx.x; d < fan; d += blockDim.x) {
+      const u32 c = s_hist[d];
+      s_hist[d] = 0;
+      if (c) atomicAdd(&hist2[(i64)p * fan + d], (u64)c);
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_scatter2(const DLevel2 L, const DScatter D)
+{
+  __shared__ u32 s_hist[1 << RP_MAX_BITS];
+  __shared__ u64 s_base[1 << RP_MAX_BITS];
+  for (int i = threadIdx.x; i < D.fan; i += blockDim.x) s_hist[i] = 0;
+  __syncthreads();
+  const u32 ntiles = __ldg(L.tile_start + L.parts);
+  const u32 dmask = (u32)D.fan - 1u;
+  for (u32 tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int p = rp_partition_of_tile(L.tile_start, L.parts, tile);
+    const i64 lo = (i64)L.src_start[p] + (i64)(tile - __ldg(L.tile_start + p)) * RP_TILE;
+    const i64 hi = min((i64)L.src_end[p], lo + RP_TILE);
+    u64 kk[RP_ROWS];
+    u32 rank[RP_ROWS];
+#pragma unroll
+    for (int j = 0; j < RP_ROWS; ++j) {
+      const i64 i = lo + (i64)j * RP_BLOCK + threadIdx.x;
+      rank[j] = 0xFFFFFFFFu;
+      if (i < hi) {
+        kk[j] = __ldg(L.src.rec + i);
+        const u32 d = (u32)(rp_hash(kk[j]) >> D.shift) & dmask;
+        rank[j] = (d << 16) | atomicAdd(&s_hist[d], 1u);
+      }
+    }
+    __syncthreads();
+    rp_reserve(s_hist, s_base, D.cursors + (i64)p * D.fan, D.fan);
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < RP_ROWS; ++j) {
+      if (rank[j] == 0xFFFFFFFFu) continue;
+      const i64 i  = lo + (i64)j * RP_BLOCK + threadIdx.x;
+      const i64 at = (i64)s_base[rank[j] >> 16] + (i64)(rank[j] & 0xFFFFu);
+      D.dst.rec[at] = kk[j];
+      for (int w = 1; w < L.src.words; ++w) D.dst.rec[(i64)w * D.dst.cap + at] = __ldg(L.src.rec + (i64)w * L.src.cap + i);
+    }
+  }
+}
+
+// tiles per source partition from its record count (one thread per partition), then scanned on the device
+__global__ void k_rp_tiles(const u64* __restrict__ start, const u64* __restrict__ end, int parts, u32* __restrict__ tile_start)
+{
+  // single CTA: exclusive scan of ceil(count / RP_TILE)
+  __shared__ u32 s_sum[1024];
+  u32 mine = 0;
+  const int per = (parts + (int)blockDim.x - 1) / (int)blockDim.x;
+  const int lo = threadIdx.x * per, hi = min(parts, lo + per);
+  for (int p = lo; p < hi; ++p) mine += (u32)((end[p] - start[p] + RP_TILE - 1) / RP_TILE);
+  s_sum[threadIdx.x] = mine;
+  __syncthreads();
+  for (int d = 1; d < (int)blockDim.x; d <<= 1) {
+    const u32 t = threadIdx.x >= (u32)d ? s_sum[threadIdx.x - d] : 0u;
+    __syncthreads();
+    s_sum[threadIdx.x] += t;
+    __syncthreads();
+  }
+  u32 run = s_sum[threadIdx.x] - mine;
+  for (int p = lo; p < hi; ++p) {
+    tile_start[p] = run;
+    run += (u32)((end[p] - start[p] + RP_TILE - 1) / RP_TILE);
+  }
+  if (threadIdx.x == blockDim.x - 1) tile_start[parts] = s_sum[threadIdx.x];
+}
+
+// ------------------------------------------------------------------------------ bucket aggregate
+struct DBuckets {
+  DRecords src;
+  const u64* start;  // [buckets] first record of every bucket
+  const u64* end;    // [buckets] one past its last record
+  i64 nbuckets;
+  int slots;         // shared-memory table slots (a power of two); slot `slots` holds the key whose bits equal EMPTY
+  u64* out;          // finished groups, structure-of-arrays: word w of group g at out[w * out_cap + g]; word 0 = key
+  i64 out_cap;
+  u64* next_bucket;  // work counter
+};
+
+__global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_constant__ DPlan P, const DBuckets B, DCtrl* ctrl)
+{
+  extern __shared__ __align__(16) unsigned char rp_smem[];
+  __shared__ i64 s_bucket;
+  __shared__ u32 s_count, s_fail, s_special;
+  __shared__ u64 s_outbase;
+  __shared__ u32 s_warp[RPA_BLOCK / 32];
+  const int S  = B.slots;
+  const int NS = S + 1;
+  u64* skeys  = (u64*)rp_smem;   // [NS]
+  u64* scells = skeys + NS;      // [ncells][NS]
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const u32 smask = (u32)S - 1u;
+  // a bucket whose groups fill the table beyond this gives up (the caller falls back to the global table)
+  const u32 fill_limit = (u32)S - (u32)(S >> 3);
+
+  for (;;) {
+    __syncthreads();
+    if (threadIdx.x == 0) { s_bucket = (i64)atomicAdd(B.next_bucket, 1ull); s_count = 0; s_fail = 0; s_special = 0; }
+    __syncthreads();
+    const i64 b = s_bucket;
+    if (b >= B.nbuckets) break;
+    const i64 lo = (i64)B.start[b], hi = (i64)B.end[b];
+    if (hi <= lo) continue;
+    // clear the table
+    for (int i = threadIdx.x; i < NS; i += blockDim.x) skeys[i] = EMPTY;
+    for (int c = 0; c < P.ncells; ++c) {
+      const u64 id = cell_identity(P.cells[c].op);
+      for (int i = threadIdx.x; i < NS; i += blockDim.x) scells[(size_t)c * NS + i] = id;
+    }
+    __syncthreads();
+    // fold the records
+    for (i64 i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const u64 key = __ldg(B.src.rec + i);
+      int slot = -1;
+      if (key == EMPTY) {
+        slot = S;
+        s_special = 1;
+      } else {
+        u32 idx = (u32)rp_hash(key) & smask;
+        for (int p = 0; p < S; ++p) {
+          u64 k = *(volatile u64*)(skeys + idx);
+          if (k == EMPTY) {
+            if (*(volatile u32*)&s_count >= fill_limit) break;
+            k = atomicCAS(skeys + idx, EMPTY, key);
+            if (k == EMPTY) { atomicAdd(&s_count, 1u); k = key; }
+          }
+          if (k == key) { slot = (int)idx; break; }
+          idx = (idx + 1u) & smask;
+        }
+      }
+      if (slot < 0) { s_fail = 1; continue; }
+      const u64 vbits = B.src.valid_word >= 0 ? __ldg(B.src.rec + (i64)B.src.valid_word * B.src.cap + i) : ~0ull;
+      int cur = -1;
+      u64 v = 0;
+      for (int c = 0; c < P.ncells; ++c) {
+        const int op = P.cells[c].op, col = P.cells[c].col;
+        if (op != OP_CNT_A) {
+          if (!((vbits >> col) & 1ull)) continue;
+          if (col != cur) { cur = col; v = __ldg(B.src.rec + (i64)(1 + col) * B.src.cap + i); }
+        }
+        cell_update(scells + (size_t)c * NS + slot, op, v);
+      }
+    }
+    __syncthreads();
+    if (s_fail) { if (threadIdx.x == 0) ctrl->overflow = 1; continue; }
+    // compact the occupied slots into the group list
+    const u32 ngroups = s_count + s_special;
+    if (threadIdx.x == 0) {
+      s_outbase = atomicAdd(&ctrl->out_cursor, (u64)ngroups);
+      if (s_outbase + ngroups > (u64)B.out_cap) ctrl->overflow = 1;
+    }
+    __syncthreads();
+    if (s_outbase + ngroups > (u64)B.out_cap) continue;
+    u32 run = 0;  // groups written by earlier rounds of this loop
+    for (int base = 0; base < NS; base += blockDim.x) {
+      const int i = base + threadIdx.x;
+      const bool occ = i < S ? skeys[i] != EMPTY : (i == S && s_special != 0);
+      const u32 m = __ballot_sync(0xFFFFFFFFu, occ);
+      if (lane == 0) s_warp[wid] = __popc(m);
+      __syncthreads();
+      u32 before = 0, total = 0;
+      for (int w = 0; w < RPA_BLOCK / 32; ++w) { const u32 c = s_warp[w]; if (w < wid) before += c; total += c; }
+      if (occ) {
+        const i64 g = (i64)s_outbase + run + before + __popc(m & ((1u << lane) - 1u));
+        B.out[g] = i < S ? skeys[i] : EMPTY;
+        for (int c = 0; c < P.ncells; ++c) B.out[(i64)(1 + c) * B.out_cap + g] = scells[(size_t)c * NS + i];
+      }
+      run += total;
+      __syncthreads();
+    }
+  }
+}
+
+// group list -> output columns
+__global__ void __launch_bounds__(256) k_finalize_records(const __grid_constant__ DPlan P, const __grid_constant__ DOutPlan O,
+                                                          const u64* __restrict__ groups, i64 cap, i64 ngroups)
+{
+  for (i64 g = (i64)blockIdx.x * blockDim.x + threadIdx.x; g < ngroups; g += (i64)gridDim.x * blockDim.x)
+    write_group(P, O, groups[g], groups + cap + g, cap, g);
+}
+
+}  // namespace b2

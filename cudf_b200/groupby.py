@@ -124,7 +124,8 @@ class GroupBy:
     table of key columns, ``null_handling`` decides whether rows with a null key are dropped
     (EXCLUDE, default) or grouped (INCLUDE).  Extras of this engine: ``expected_groups`` (sizing
     hint), ``row_filters`` (validity masks a row must pass: a fused ``drop_nulls``),
-    ``table_variant`` (0 auto, 1 global-memory table only, 2 shared-memory cache in front of it).
+    ``table_variant`` (0 auto, 1 global-memory table only, 3 shared-memory table with hashing only,
+    4 / 5 the lean FLOAT32-mean kernel with register tiles / with the bulk-copy tile ring).
     """
 
     def __init__(self, keys: Table, null_handling: NullPolicy = NullPolicy.EXCLUDE, *,

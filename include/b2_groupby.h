@@ -149,7 +149,9 @@ typedef struct b2_groupby_result {
 typedef struct b2_groupby_options {
   int64_t expected_groups;  /* hint; <= 0 = unknown (engine speculates, then estimates)        */
   int32_t table_variant;    /* 0 auto; 1 global-memory table only; 3 shared-memory table with
-                               hashing only (no dense key box)                               */
+                               hashing only (no dense key box); 4 / 5 = auto, but the lean
+                               FLOAT32-mean kernel reads its tiles through registers (4) or
+                               through the cp.async.bulk shared-memory ring (5)               */
   int32_t shared_table_bytes; /* <= 0 = auto                                                   */
   /* Fused drop_nulls pre-filter (cpp/src/stream_compaction/drop_nulls.cu:56-96): a row takes
    * part only if it is valid in every one of these masks (bit i = row i, same bit layout and

@@ -15,6 +15,33 @@ GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref
 # north_star tolerances: float sum/mean/var within 1e-12 (fp64 sources) or 1e-5 (fp32 sources)
 RTOL_F64 = 1e-12
 RTOL_F32 = 1e-5
+# A float result is held to the STRICT relative tolerance |got - exp| <= rtol * |exp| whenever
+# |exp| >= STRICT_FROM * (error scale of its group: Σ|x| for sums and means, Σx²/(n - ddof) for
+# variances; for a standard deviation the ratio of the variances decides); only results that
+# cancellation drove below that are compared relative to the scale.
+STRICT_FROM = 1e-3
+# one record per compared float column: what, values compared, values held to the strict tolerance,
+# the largest strict relative error among those, values that only pass through the scaled bound, the
+# largest error relative to the scale among them (printed by the parity tests, written to PARITY_STATS_FILE)
+PARITY_STATS: list = []
+PARITY_STATS_FILE = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out", "parity_stats.jsonl")
+
+
+def record_parity_stats(label: str):
+    """Tags the records collected since the last call with ``label``, prints and appends them to the stats file."""
+    recs = [dict(r, config=label) for r in PARITY_STATS]
+    PARITY_STATS.clear()
+    for r in recs:
+        print(f"[parity] {label}: {r['what']}: {r['n']} values, strict {r['strict_n']} (max rel err {r['strict_max']:.3e}, "
+              f"rtol {r['rtol']:g}), scaled-only {r['scaled_n']} (max err/scale {r['scaled_max']:.3e})")
+    try:
+        os.makedirs(os.path.dirname(PARITY_STATS_FILE), exist_ok=True)
+        with open(PARITY_STATS_FILE, "a", encoding="utf-8") as f:
+            for r in recs:
+                f.write(json.dumps(r) + "\n")
+    except OSError:
+        pass
+    return recs
 
 
 def load_golden() -> list:
@@ -74,7 +101,7 @@ def take(col: HostColumn, order: np.ndarray) -> list:
 
 
 def assert_column_equal(got: HostColumn, exp: HostColumn, order_got, order_exp, rtol: float, what: str,
-                        check_nullable: bool = False, scale=None):
+                        check_nullable: bool = False, scale=None, strict_power: int = 1):
     assert TypeId(got.type_id) == TypeId(exp.type_id), f"{what}: type {got.type_id!r} != {exp.type_id!r}"
     assert got.size == exp.size, f"{what}: size {got.size} != {exp.size}"
     assert getattr(got, "scale", 0) == getattr(exp, "scale", 0), f"{what}: decimal scale differs"
@@ -95,12 +122,25 @@ def assert_column_equal(got: HostColumn, exp: HostColumn, order_got, order_exp, 
         fin = ~(nan_a | inf)
         err = np.abs(a[fin] - b[fin])
         mag = np.maximum(np.abs(a[fin]), np.abs(b[fin]))
-        if scale is not None:
-            mag = np.maximum(mag, np.asarray(scale, dtype=np.float64)[order_exp][ve][fin])
-        tol = rtol * mag + 1e-300
+        if scale is None:
+            strict = np.ones(err.size, dtype=bool)
+            sc = mag
+        else:
+            sc = np.asarray(scale, dtype=np.float64)[order_exp][ve][fin]
+            # (a standard deviation is the root of a difference: its conditioning is that of the variance)
+            strict = mag ** strict_power >= STRICT_FROM * sc ** strict_power
+        # strict: relative to the result itself; the rest: relative to the group's error scale
+        tol = rtol * np.where(strict, mag, np.maximum(mag, sc)) + 1e-300
         bad = np.flatnonzero(err > tol)
+        with np.errstate(divide="ignore", invalid="ignore"):
+            rel = np.where(mag > 0, err / mag, 0.0)
+            rel_sc = np.where(sc > 0, err / np.maximum(mag, sc), 0.0)
+        PARITY_STATS.append({"what": what, "n": int(err.size), "strict_n": int(strict.sum()),
+                             "strict_max": float(rel[strict].max()) if strict.any() else 0.0,
+                             "scaled_n": int((~strict).sum()),
+                             "scaled_max": float(rel_sc[~strict].max()) if (~strict).any() else 0.0, "rtol": rtol})
         assert bad.size == 0, (f"{what}: {bad.size} values beyond rtol {rtol}; first {a[fin][bad[:4]]} vs "
-                               f"{b[fin][bad[:4]]}")
+                               f"{b[fin][bad[:4]]} (strict: {strict[bad[:4]]})")
     else:
         bad = np.flatnonzero(a != b)
         assert bad.size == 0, f"{what}: {bad.size} values differ; first {a[bad[:8]]} vs {b[bad[:8]]}"
@@ -248,4 +288,4 @@ def assert_same_result(got, exp, requests, check_nullable=True, scales=None):
             if scales is not None and is_floating(er[q][a].type_id):
                 scale = _scale_for(kind, ddof, *scales[q])
             assert_column_equal(gr[q][a], er[q][a], og, oe, rtol_for(vals.type_id), f"request {q} agg {aggs[a]}",
-                                check_nullable=check_nullable, scale=scale)
+                                check_nullable=check_nullable, scale=scale, strict_power=2 if Kind(kind) == Kind.STD else 1)

@@ -1,33 +1,24 @@
 """The benchmark configurations at their FULL benchmark sizes on one B200, inputs generated on the
-device (seeded torch generators), checked against an independent sort-based computation in torch
-(exact for integers) and through size-independent properties (group count, Σ counts, Σ sums,
-min <= mean <= max, idempotence of re-aggregating the result)."""
-import numpy as np
+device (workloads.make_device: seeded torch generators), every group checked against an
+independent computation in torch (index_add / bincount / scatter_reduce over the generating
+tensors: exact for integers, fp64 for floats) plus size-independent properties (group count,
+Σ counts, Σ sums, min <= mean <= max)."""
 import pytest
+
+import workloads
+from cudf_b200.types import Kind
 
 pytestmark = pytest.mark.gpu
 
 
-def _mask_words(valid):
-    """bool tensor -> cudf bitmask words (int32 tensor), LSB first."""
-    import torch
-    n = valid.numel()
-    pad = (-n) % 32
-    v = torch.cat([valid, torch.zeros(pad, dtype=torch.bool, device=valid.device)]) if pad else valid
-    w = (v.view(-1, 32).to(torch.int64) << torch.arange(32, device=valid.device, dtype=torch.int64)).sum(1)
-    w = torch.where(w >= 2**31, w - 2**32, w).to(torch.int32)
-    return torch.cat([w, torch.zeros(16, dtype=torch.int32, device=valid.device)])
-
-
-def _agg(keys, reqs, **opts):
+def _agg(w, extra=None, **opts):
     import cudf_b200 as cb
-    gb = cb.GroupBy(cb.Table(keys), **opts)
+    from cudf_b200.aggregation import Aggregation
+    reqs = [cb.GroupByRequest(v, [Aggregation(Kind(a)) for a in (extra[i] if extra else aggs)])
+            for i, (v, aggs) in enumerate(w.requests)]
+    gb = cb.GroupBy(cb.Table(w.keys), row_filters=w.row_filters, **opts)
     out_keys, out = gb.aggregate(reqs)
     return out_keys, out, cb.last_call_stats()
-
-
-def _typed(col, dtype):
-    return col.data[: col.size * dtype.itemsize].view(dtype) if hasattr(dtype, "itemsize") else None
 
 
 def _tensor(col, torch_dtype):
@@ -36,20 +27,13 @@ def _tensor(col, torch_dtype):
     return col.data[:nbytes].view(torch_dtype)
 
 
-def test_c2_full_size_100m_rows():
+@pytest.mark.parametrize("variant", [0, 5])
+def test_c2_full_size_100m_rows(variant):
+    """variant 0: tiles through registers; 5: through the bulk-copy shared-memory ring."""
     import torch
-    import cudf_b200 as cb
-    from cudf_b200 import aggregation as agg
-    g = torch.Generator(device="cuda").manual_seed(44)
-    n = 100_000_000
-    a = torch.randint(0, 100, (n,), device="cuda", dtype=torch.int32, generator=g)
-    b = torch.randint(0, 100, (n,), device="cuda", dtype=torch.int32, generator=g)
-    v = torch.rand(n, device="cuda", generator=g) * 1000
-    valid = torch.rand(n, device="cuda", generator=g) >= 0.02
-    mask = _mask_words(valid)
-    vc = cb.Column.from_tensor(v, mask)
-    keys, out, st = _agg([cb.Column.from_tensor(a), cb.Column.from_tensor(b)],
-                         [cb.GroupByRequest(vc, [agg.mean(), agg.count(), agg.sum()])], row_filters=[vc])
+    w = workloads.make_device(2)
+    a, b, v, valid = (w.raw[k] for k in ("a", "b", "v", "valid"))
+    keys, out, st = _agg(w, extra=[[Kind.MEAN, Kind.COUNT_VALID, Kind.SUM]], table_variant=variant)
     assert st.used_shared_table and st.table_attempts == 1
     G = keys.num_rows()
     assert G == 10_000
@@ -71,14 +55,9 @@ def test_c2_full_size_100m_rows():
 
 def test_c3_full_size_500m_rows_bit_exact():
     import torch
-    import cudf_b200 as cb
-    from cudf_b200 import aggregation as agg
-    g = torch.Generator(device="cuda").manual_seed(45)
-    n = 500_000_000
-    k = torch.randint(0, 100_000_000, (n,), device="cuda", dtype=torch.int64, generator=g)
-    v = torch.randint(-1_000_000_000, 1_000_000_001, (n,), device="cuda", dtype=torch.int64, generator=g)
-    keys, out, st = _agg([cb.Column.from_tensor(k)],
-                         [cb.GroupByRequest(cb.Column.from_tensor(v), [agg.sum(), agg.min(), agg.max(), agg.count()])])
+    w = workloads.make_device(3)
+    n, k, v = w.rows, w.raw["k"], w.raw["v"]
+    keys, out, st = _agg(w)
     G = keys.num_rows()
     ok = _tensor(keys.columns()[0], torch.int64)
     s, mn, mx = (_tensor(out[0].columns()[i], torch.int64) for i in range(3))
@@ -87,55 +66,34 @@ def test_c3_full_size_500m_rows_bit_exact():
     assert int(cnt.sum()) == n
     assert int(s.sum()) == int(v.sum())
     assert bool((mn <= mx).all())
-    # exact check against a sort-based computation on a slice of the key space (bounded memory)
-    sel = k < 5_000_000
-    ks, vs = k[sel], v[sel]
-    uk, inv = torch.unique(ks, return_inverse=True)
-    ref_sum = torch.zeros(uk.numel(), dtype=torch.int64, device="cuda").index_add_(0, inv, vs)
-    ref_cnt = torch.bincount(inv, minlength=uk.numel())
-    ref_min = torch.full((uk.numel(),), 2**62, dtype=torch.int64, device="cuda").scatter_reduce_(0, inv, vs, "amin")
-    ref_max = torch.full((uk.numel(),), -2**62, dtype=torch.int64, device="cuda").scatter_reduce_(0, inv, vs, "amax")
-    osel = ok < 5_000_000
-    order = torch.argsort(ok[osel])
-    assert torch.equal(ok[osel][order], uk)
-    assert torch.equal(s[osel][order], ref_sum)
-    assert torch.equal(cnt[osel][order].to(torch.int64), ref_cnt)
-    assert torch.equal(mn[osel][order], ref_min) and torch.equal(mx[osel][order], ref_max)
-    assert G == int(torch.unique(k).numel())
+    # every group, exactly, against dense references over the key domain [0, 100M)
+    dom = 100_000_000
+    ref_cnt = torch.bincount(k, minlength=dom)
+    assert G == int((ref_cnt > 0).sum())
+    assert torch.equal(cnt.to(torch.int64), ref_cnt[ok])
+    del ref_cnt
+    ref = torch.zeros(dom, dtype=torch.int64, device="cuda").index_add_(0, k, v)
+    assert torch.equal(s, ref[ok])
+    ref.fill_(2**62).scatter_reduce_(0, k, v, "amin")
+    assert torch.equal(mn, ref[ok])
+    ref.fill_(-2**62).scatter_reduce_(0, k, v, "amax")
+    assert torch.equal(mx, ref[ok])
+    assert torch.unique(ok).numel() == G
 
 
 def test_c4_full_size_1b_rows_zipf():
     import torch
-    import cudf_b200 as cb
-    from cudf_b200 import aggregation as agg
-    g = torch.Generator(device="cuda").manual_seed(46)
-    n, distinct = 1_000_000_000, 10_000_000
-    w = torch.arange(1, distinct + 1, device="cuda", dtype=torch.float64) ** (-1.1)
-    cdf = torch.cumsum(w, 0)
-    cdf /= cdf[-1].clone()
-    perm = torch.randperm(distinct, device="cuda", generator=g)
-    k = torch.empty(n, dtype=torch.int64, device="cuda")
-    chunk = 100_000_000
-    for lo in range(0, n, chunk):
-        u = torch.rand(chunk, device="cuda", dtype=torch.float64, generator=g)
-        r = torch.searchsorted(cdf, u).clamp_(max=distinct - 1)
-        k[lo:lo + chunk] = perm[r]
-        del u, r
-    v = torch.empty(n, dtype=torch.float64, device="cuda")
-    v.log_normal_(0.0, 1.0, generator=g)
-    valid = torch.rand(n, device="cuda", generator=g) >= 0.01
-    mask = _mask_words(valid)
-    keys, out, st = _agg([cb.Column.from_tensor(k)],
-                         [cb.GroupByRequest(cb.Column.from_tensor(v, mask), [agg.sum(), agg.mean(), agg.variance(), agg.count()])])
+    w = workloads.make_device(4)
+    k, v, valid, distinct = (w.raw[x] for x in ("k", "v", "valid", "distinct"))
+    keys, out, st = _agg(w, extra=[[Kind.SUM, Kind.MEAN, Kind.VARIANCE, Kind.COUNT_VALID]])
     G = keys.num_rows()
     ok = _tensor(keys.columns()[0], torch.int64)
     s, mean, var = (_tensor(out[0].columns()[i], torch.float64) for i in range(3))
     cnt = _tensor(out[0].columns()[3], torch.int32)
     assert torch.unique(ok).numel() == G
+    assert G == int(torch.bincount(k, minlength=distinct).clamp_(max=1).sum())
     assert int(cnt.sum()) == int(valid.sum())
     total = float(torch.where(valid, v, torch.zeros_like(v)).sum())
-    smask = ~torch.isnan(s)
-    nullmask_s = out[0].columns()[0].mask
     got_total = float(s[cnt > 0].sum())
     assert abs(got_total - total) <= 1e-9 * total
     # independent per-group computation (dense by id, fp64 atomics in torch)
@@ -144,7 +102,7 @@ def test_c4_full_size_1b_rows_zipf():
     ref_cnt = torch.bincount(k[valid], minlength=distinct)
     has = cnt > 0
     kk = ok[has]
-    assert torch.equal(cnt[has].to(torch.int64), ref_cnt[kk])
+    assert torch.equal(cnt.to(torch.int64), ref_cnt[ok])
     rel = ((s[has] - ref_sum[kk]).abs() / ref_sum[kk]).max()
     assert float(rel) < 1e-11
     many = has & (cnt > 1)
@@ -157,54 +115,94 @@ def test_c4_full_size_1b_rows_zipf():
 
 
 def test_c5_full_size_200m_rows_string_keys():
+    """Every group: the output string equals the pool string of its id, and Σ, n, min, max of both value
+    columns (int32 exact, float64 to 1e-12 of the group's Σ|x| scale — all values are positive here, so that is
+    the strict relative error) against scatter references keyed on (pool id, k2)."""
     import torch
-    import cudf_b200 as cb
-    from cudf_b200 import aggregation as agg
     from cudf_b200.types import TypeId
-    g = torch.Generator(device="cuda").manual_seed(47)
-    n, pool = 200_000_000, 1_000_000
-    plen = torch.randint(8, 33, (pool,), device="cuda", generator=g)
-    poff = torch.zeros(pool + 1, dtype=torch.int64, device="cuda")
-    poff[1:] = torch.cumsum(plen, 0)
-    alphabet = torch.tensor(list(b"abcdefghijklmnopqrstuvwxyz0123456789"), dtype=torch.uint8, device="cuda")
-    pchars = alphabet[torch.randint(0, 36, (int(poff[-1]),), device="cuda", generator=g)]
-    idx = torch.randint(0, pool, (n,), device="cuda", generator=g)
-    lens = plen[idx]
-    offs = torch.zeros(n + 1, dtype=torch.int64, device="cuda")
-    offs[1:] = torch.cumsum(lens, 0)
-    total = int(offs[-1])
-    assert total > 2**31  # forces INT64 offsets, like the reference's large-strings mode
-    chars = torch.empty(total, dtype=torch.uint8, device="cuda")
-    chunk = 20_000_000
-    for lo in range(0, n, chunk):
-        hi = min(n, lo + chunk)
-        b0, b1 = int(offs[lo]), int(offs[hi])
-        src = torch.repeat_interleave(poff[idx[lo:hi]] - offs[lo:hi], lens[lo:hi]) + torch.arange(b0, b1, device="cuda")
-        chars[b0:b1] = pchars[src]
-        del src
-    k2 = torch.randint(0, 16, (n,), device="cuda", dtype=torch.int32, generator=g)
-    v1 = 100.0 + 15.0 * torch.randn(n, device="cuda", dtype=torch.float64, generator=g)
-    v2 = torch.randint(0, 1_000_000, (n,), device="cuda", dtype=torch.int32, generator=g)
-    val1 = torch.rand(n, device="cuda", generator=g) >= 0.03
-    val2 = torch.rand(n, device="cuda", generator=g) >= 0.03
-    scol = cb.Column(TypeId.STRING, n, chars, None, 0, 0, offs.view(torch.uint8), TypeId.INT64)
-    aggs = [agg.sum(), agg.count(), agg.mean(), agg.min(), agg.max()]
-    keys, out, st = _agg([scol, cb.Column.from_tensor(k2)],
-                         [cb.GroupByRequest(cb.Column.from_tensor(v1, _mask_words(val1)), aggs),
-                          cb.GroupByRequest(cb.Column.from_tensor(v2, _mask_words(val2)), aggs)])
+    w = workloads.make_device(5)
+    n = w.rows
+    idx, k2, v1, v2, val1, val2 = (w.raw[x] for x in ("idx", "k2", "v1", "v2", "val1", "val2"))
+    pchars, poff = w.raw["pool_chars"], w.raw["pool_offsets"]
+    assert w.keys[0].offsets_type == TypeId.INT64   # > 2 GiB of chars: the reference's large-strings mode
+    keys, out, st = _agg(w)
     G = keys.num_rows()
-    gid = idx * 16 + k2.to(torch.int64)
-    assert G == int(torch.unique(gid).numel())
-    c1 = _tensor(out[0].columns()[1], torch.int32)
-    c2 = _tensor(out[1].columns()[1], torch.int32)
-    assert int(c1.sum()) == int(val1.sum()) and int(c2.sum()) == int(val2.sum())
-    s2 = _tensor(out[1].columns()[0], torch.int64)
-    assert int(s2[c2 > 0].sum()) == int(v2[val2].to(torch.int64).sum())
-    mn1, mx1, mean1 = (_tensor(out[0].columns()[i], torch.float64) for i in (3, 4, 2))
-    h = c1 > 0
-    assert bool((mn1[h] <= mean1[h] + 1e-9).all()) and bool((mean1[h] <= mx1[h] + 1e-9).all())
-    # output strings: offsets child is INT32 (16M keys x ~20 B < 2 GiB) and every key has length 8..32
+    gid_in = idx * 16 + k2.to(torch.int64)
+    dom = 16_000_000
+    present = torch.bincount(gid_in, minlength=dom)
+    assert G == int((present > 0).sum())
+    del present
+    # ---- identify every output group: the pool id of its string by (length, 64-bit polynomial hash), then verify bytes
     kcol = keys.columns()[0]
-    ooffs = _tensor(type("C", (), {"data": kcol.offsets, "size": G + 1})(), torch.int32 if kcol.offsets_type == TypeId.INT32 else torch.int64)
-    ol = ooffs[1:] - ooffs[:-1]
-    assert int(ol.min()) >= 8 and int(ol.max()) <= 32
+    odt = torch.int32 if kcol.offsets_type == TypeId.INT32 else torch.int64
+    ooffs = kcol.offsets[: (G + 1) * (4 if odt == torch.int32 else 8)].view(odt).to(torch.int64)
+    olen = ooffs[1:] - ooffs[:-1]
+    assert int(olen.min()) >= 8 and int(olen.max()) <= 32
+
+    def poly_hash(chars, offs):
+        lens = offs[1:] - offs[:-1]
+        h = torch.zeros(lens.numel(), dtype=torch.int64, device="cuda")
+        for j in range(32):
+            take = lens > j
+            c = chars[(offs[:-1] + j).clamp_(max=chars.numel() - 1)].to(torch.int64)
+            h = torch.where(take, h * 1000003 + c + 1, h)
+        return h * 64 + lens
+    ph = poly_hash(pchars, poff)
+    sorted_ph, pid_of = torch.sort(ph)
+    oh = poly_hash(kcol.data, ooffs)
+    pos = torch.searchsorted(sorted_ph, oh).clamp_(max=sorted_ph.numel() - 1)
+    assert torch.equal(sorted_ph[pos], oh)          # every output string's hash is a pool string's hash
+    pid = pid_of[pos]
+    # bytes equal (guards against hash collisions and against a wrong pool id among equal hashes of equal strings)
+    plen = poff[1:] - poff[:-1]
+    assert torch.equal(plen[pid], olen)
+    for j in range(32):
+        take = olen > j
+        a = kcol.data[(ooffs[:-1] + j)[take]]
+        b = pchars[(poff[:-1][pid] + j)[take]]
+        assert torch.equal(a, b)
+    ok2 = _tensor(keys.columns()[1], torch.int32).to(torch.int64)
+    # pool strings may repeat (random 8-char strings collide with negligible probability, but be exact):
+    # map every input pool id to the FIRST pool id holding the same string
+    first_of = torch.empty_like(pid_of)
+    uniq_h, inv = torch.unique(ph, return_inverse=True)
+    first = torch.full((uniq_h.numel(),), ph.numel(), dtype=torch.int64, device="cuda").scatter_reduce_(
+        0, inv, torch.arange(ph.numel(), device="cuda"), "amin")
+    first_of = first[inv]
+    gid_out = first_of[pid] * 16 + ok2
+    gid_in = first_of[idx] * 16 + k2.to(torch.int64)
+    assert torch.unique(gid_out).numel() == G
+    # ---- value columns
+    s1, c1, m1, mn1, mx1 = (_tensor(out[0].columns()[i], t) for i, t in
+                            enumerate((torch.float64, torch.int32, torch.float64, torch.float64, torch.float64)))
+    s2, c2, m2, mn2, mx2 = (_tensor(out[1].columns()[i], t) for i, t in
+                            enumerate((torch.int64, torch.int32, torch.float64, torch.int32, torch.int32)))
+    assert int(c1.sum()) == int(val1.sum()) and int(c2.sum()) == int(val2.sum())
+    # int32 column: exact
+    g2, x2 = gid_in[val2], v2[val2].to(torch.int64)
+    ref = torch.bincount(g2, minlength=dom)
+    assert torch.equal(c2.to(torch.int64), ref[gid_out])
+    h2 = c2 > 0
+    ref = torch.zeros(dom, dtype=torch.int64, device="cuda").index_add_(0, g2, x2)
+    assert torch.equal(s2[h2], ref[gid_out][h2])
+    ref_sum2 = ref[gid_out][h2].double()
+    ref.fill_(2**40).scatter_reduce_(0, g2, x2, "amin")
+    assert torch.equal(mn2[h2].to(torch.int64), ref[gid_out][h2])
+    ref.fill_(-1).scatter_reduce_(0, g2, x2, "amax")
+    assert torch.equal(mx2[h2].to(torch.int64), ref[gid_out][h2])
+    assert float(((m2[h2] - ref_sum2 / c2[h2]).abs() / m2[h2].abs().clamp_(min=1e-300)).max()) < 1e-12
+    del ref, g2, x2
+    # float64 column: 1e-12 (values ~N(100, 15): sums do not cancel)
+    g1, x1 = gid_in[val1], v1[val1]
+    refc = torch.bincount(g1, minlength=dom)
+    assert torch.equal(c1.to(torch.int64), refc[gid_out])
+    h1 = c1 > 0
+    reff = torch.zeros(dom, dtype=torch.float64, device="cuda").index_add_(0, g1, x1)
+    rs = reff[gid_out][h1]
+    assert float(((s1[h1] - rs).abs() / rs.abs()).max()) < 1e-12
+    assert float(((m1[h1] - rs / c1[h1]).abs() / m1[h1].abs()).max()) < 1e-12
+    reff.fill_(float("inf")).scatter_reduce_(0, g1, x1, "amin")
+    assert torch.equal(mn1[h1], reff[gid_out][h1])
+    reff.fill_(float("-inf")).scatter_reduce_(0, g1, x1, "amax")
+    assert torch.equal(mx1[h1], reff[gid_out][h1])
+    assert bool((mn1[h1] <= m1[h1] + 1e-9).all()) and bool((m1[h1] <= mx1[h1] + 1e-9).all())

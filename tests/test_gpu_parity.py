@@ -25,10 +25,54 @@ def check(keys, requests, policy=NullPolicy.EXCLUDE, row_filters=(), **opts):
 
 
 @pytest.mark.parametrize("config,n", [(1, 400_000), (2, 600_000), (3, 300_000), (4, 500_000), (5, 120_000)])
-@pytest.mark.parametrize("variant", [0, 1, 3])
+@pytest.mark.parametrize("variant", [0, 1, 3, 5])
 def test_benchmark_configs_match_oracle(config, n, variant):
+    """Variants: 0 auto, 1 global table only, 3 hashed shared table, 5 the bulk-copy tile ring (C2)."""
     w = workloads.make(config, n, scale_domain=(config in (3, 4)))
     check(w.keys, w.requests, w.null_policy, w.row_filters, table_variant=variant)
+    H.record_parity_stats(f"C{config} {n} rows, table_variant {variant}")
+
+
+def test_config1_full_size_10m_rows_against_the_oracle():
+    """C1 at its full 10M rows: every group against the CPU oracle, strict 1e-12 wherever the sum is
+    not cancelled below 1e-3 of Σ|x|."""
+    w = workloads.make(1)
+    assert w.rows == 10_000_000
+    got = check(w.keys, w.requests, w.null_policy, w.row_filters)
+    assert got[0][0].size == 1000
+    H.record_parity_stats("C1 full size (10M rows)")
+
+
+def test_five_key_columns():
+    """More than 4 key columns (the reference switches to cached row hashes there,
+    cpp/src/groupby/hash/compute_groupby.cu:68-91): packed when the widths allow, row keys otherwise."""
+    rng = np.random.default_rng(5)
+    n = 60_000
+    narrow = [HostColumn.from_numpy(rng.integers(0, 4, n).astype(dt)) for dt in (np.int8, np.int16, np.uint8, np.int8, np.int16)]
+    v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.1)
+    w = HostColumn.from_numpy(rng.integers(-50, 50, n).astype(np.int32))
+    got = check(narrow, [(v, ALL_AGGS), (w, [Kind.SUM, Kind.MIN, Kind.MAX])])
+    assert got[0][0].size == 4 ** 5
+    wide = [HostColumn.from_numpy(rng.integers(0, 3, n).astype(np.int64), valid=rng.random(n) > 0.05) for _ in range(5)]
+    check(wide, [(v, ALL_AGGS)])                       # 5 x 8 bytes: row keys
+    check(wide, [(v, ALL_AGGS)], NullPolicy.INCLUDE)
+    six = wide + [HostColumn.from_numpy(rng.random(n).round(1))]   # a float column among six
+    check(six, [(w, [Kind.SUM, Kind.COUNT_ALL])], NullPolicy.INCLUDE)
+
+
+def test_two_string_key_columns():
+    """Two STRING key columns, UTF-8 content, nulls under both policies
+    (cpp/tests/groupby/keys_tests.cpp:306-321 has one; the row comparator is column-wise)."""
+    rng = np.random.default_rng(6)
+    n = 40_000
+    words = ["", "a", "año", "aa", "añejo", "b", "日本", "日本語", "z" * 40, "ab"]
+    s1 = HostColumn.from_strings([None if rng.random() < 0.05 else words[i] for i in rng.integers(0, len(words), n)])
+    s2 = HostColumn.from_strings([words[i] for i in rng.integers(0, 4, n)])
+    k3 = HostColumn.from_numpy(rng.integers(0, 3, n).astype(np.int16))
+    v = HostColumn.from_numpy(rng.standard_normal(n).astype(np.float32), valid=rng.random(n) > 0.2)
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        got = check([s1, s2, k3], [(v, ALL_AGGS)], policy)
+        assert got[0][0].size == (len(words) + (policy == NullPolicy.INCLUDE)) * 4 * 3
 
 
 def test_config2_full_domain_uses_compact_shared_table():
