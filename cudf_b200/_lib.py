@@ -104,6 +104,12 @@ PROTOTYPES = {
                                                C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                                C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int32),
                                                C.POINTER(C.c_int32)]),
+    "b2_comm_unique_id": (C.c_int, [C.c_void_p]),
+    "b2_comm_create": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
+    "b2_comm_adopt": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
+    "b2_comm_destroy": (None, [C.c_void_p]),
+    "b2_groupby_aggregate_multi": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(AggregationRequest), C.c_int32, C.c_void_p,
+                                             C.POINTER(Allocator), C.POINTER(GroupbyResult)]),
     "b2_last_error": (C.c_char_p, []),
     "b2_version": (C.c_char_p, []),
     "b2_get_last_stats": (None, [C.POINTER(CallStats)]),

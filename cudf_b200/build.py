@@ -17,7 +17,7 @@ DEPS = [SRC, os.path.join(HERE, "csrc", "b2_kernels.cuh"), os.path.join(HERE, "c
 LIB = os.path.join(HERE, "libb2groupby.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared"]
+              "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared", "-ldl"]
 
 
 def find_nvcc() -> str:

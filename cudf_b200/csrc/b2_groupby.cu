@@ -12,6 +12,9 @@
 #include "b2_lean.cuh"
 #include "b2_partition.cuh"
 
+#include <dlfcn.h>
+#include <nccl.h>
+
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
@@ -875,7 +878,8 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
 
   // 2. digits: buckets of about half a shared-memory table each (two CTAs of the aggregate kernel per SM)
   const int slot_bytes = 8 * (1 + sc.ncells);
-  const int budget = std::min((device_info().smem_optin - 2048), 110 * 1024);
+  int budget = std::min((device_info().smem_optin - 2048), 110 * 1024);
+  if (gb.shared_table_bytes > 0) budget = std::min(budget, std::max(gb.shared_table_bytes, 257 * slot_bytes));
   int slots = 256;
   while ((int64_t)(2 * slots + 1) * slot_bytes <= budget) slots *= 2;
   if ((int64_t)(slots + 1) * slot_bytes > budget) return false;  // too many accumulators for a useful table
@@ -1183,6 +1187,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
   Trace trace(stream);
   read_ctrl(st, stream);
   const bool listed = st.groups_n >= 0;  // the partitioned path left a compact group list, not a table
+  if (st.table && st.host_ctrl.chunk_overflow >= 2) B2_FAIL(B2_INTERNAL_ERROR, "the local aggregate failed on another rank");
   if (st.table && st.host_ctrl.chunk_overflow) B2_FAIL(B2_LOGIC_ERROR, "partial-record chunk overflow");
   if (st.table && st.host_ctrl.overflow) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow while merging partial records");
   const int64_t G = listed ? st.groups_n : st.table ? num_groups(st) : 0;
@@ -1915,6 +1920,262 @@ void b2_column_free(b2_owned_column* c, const b2_allocator* allocator, void* str
   for (int i = 0; i < c->num_children; ++i) b2_column_free(&c->children[i], allocator, stream);
   std::free(c->children);
   std::memset(c, 0, sizeof(*c));
+}
+
+// ------------------------------------------------------------------------------ multi-GPU (NCCL)
+}  // extern "C" (reopened below)
+
+namespace {
+
+// the NCCL entry points this library uses, resolved at run time
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
+  ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+const NcclApi& nccl_api()
+{
+  static NcclApi api;
+  static std::once_flag once;
+  static std::string failure;
+  std::call_once(once, [] {
+    const char* override_path = getenv("B2_NCCL_LIB");
+    void* h = nullptr;
+    if (override_path && *override_path) h = dlopen(override_path, RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);  // the copy the host process already uses
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) { failure = std::string("cannot load libnccl.so.2: ") + dlerror(); return; }
+    api.handle = h;
+    auto sym = [&](const char* name) {
+      void* p = dlsym(h, name);
+      if (!p && failure.empty()) failure = std::string("libnccl.so.2 lacks ") + name;
+      return p;
+    };
+    api.GetUniqueId    = (decltype(api.GetUniqueId))sym("ncclGetUniqueId");
+    api.CommInitRank   = (decltype(api.CommInitRank))sym("ncclCommInitRank");
+    api.CommDestroy    = (decltype(api.CommDestroy))sym("ncclCommDestroy");
+    api.GroupStart     = (decltype(api.GroupStart))sym("ncclGroupStart");
+    api.GroupEnd       = (decltype(api.GroupEnd))sym("ncclGroupEnd");
+    api.Send           = (decltype(api.Send))sym("ncclSend");
+    api.Recv           = (decltype(api.Recv))sym("ncclRecv");
+    api.AllGather      = (decltype(api.AllGather))sym("ncclAllGather");
+    api.GetErrorString = (decltype(api.GetErrorString))sym("ncclGetErrorString");
+  });
+  if (!failure.empty()) B2_FAIL(B2_UNSUPPORTED, failure);
+  return api;
+}
+
+#define NCCL_TRY(expr)                                                                            \
+  do {                                                                                            \
+    ncclResult_t r_ = (expr);                                                                     \
+    if (r_ != ncclSuccess)                                                                        \
+      B2_FAIL(B2_CUDA_ERROR, std::string("NCCL error at " #expr ": ") + nccl_api().GetErrorString(r_)); \
+  } while (0)
+
+void rethrow(b2_status s)
+{
+  if (s != B2_SUCCESS) throw Err{s, g_last_error};
+}
+
+constexpr int64_t MULTI_CHUNK_RECORDS = 16384;  // records per destination of the fixed-size exchange
+constexpr int64_t MULTI_CHUNK_LIMIT   = 64ll << 20;  // bytes all chunks of one rank may take
+
+}  // namespace
+
+struct b2_comm {
+  ncclComm_t comm = nullptr;
+  int rank = 0, nranks = 1;
+  bool owned = false;
+  bool chunks_overflowed = false;  // the fixed-size exchange overflowed before (every rank saw the same flag)
+};
+
+namespace {
+
+// all-to-all of equal-sized pieces
+void exchange_equal(const b2_comm& c, const unsigned char* send, unsigned char* recv, size_t piece, cudaStream_t stream)
+{
+  const NcclApi& n = nccl_api();
+  NCCL_TRY(n.GroupStart());
+  for (int r = 0; r < c.nranks; ++r) {
+    NCCL_TRY(n.Send(send + (size_t)r * piece, piece, ncclUint8, r, c.comm, stream));
+    NCCL_TRY(n.Recv(recv + (size_t)r * piece, piece, ncclUint8, r, c.comm, stream));
+  }
+  NCCL_TRY(n.GroupEnd());
+}
+
+// A rank whose local pass failed still takes part in the exchange — with chunks (or a count row) that
+// carry a failure mark — so that every rank leaves the call with an error instead of one rank
+// leaving while its peers wait in the collective.
+constexpr u64 CHUNK_MARK_OVERFLOW = 1, CHUNK_MARK_FAILED = 2;
+
+void aggregate_multi(b2_comm& c, b2_groupby& gb, const b2_aggregation_request* reqs, int nreqs, cudaStream_t stream,
+                     const b2_allocator* allocator, b2_groupby_result* out)
+{
+  const NcclApi& n = nccl_api();
+  // what can fail before any communication fails on every rank alike (same schema everywhere)
+  std::unique_ptr<b2_groupby_state, void (*)(b2_groupby_state*)> local(make_state(gb, reqs, nreqs), b2_state_destroy);
+  if (local->sc.key_mode != KM_PACKED)
+    B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys are not transferable; partition the rows instead");
+  const int W = c.nranks;
+  const int64_t chunk_bytes = b2_state_chunk_bytes(local.get(), MULTI_CHUNK_RECORDS);
+  const int64_t chunk_words = chunk_bytes / 8;
+  bool failed = false;
+  Err failure{B2_SUCCESS, ""};
+  try {
+    update_state(*local, gb, reqs, nreqs, stream);
+  } catch (const Err& e) {
+    failed = true;
+    failure = e;
+    cudaGetLastError();
+  }
+
+  // ---- small states: fixed-size chunks, no host round trip before the exchange
+  if (!c.chunks_overflowed && chunk_bytes * W <= MULTI_CHUNK_LIMIT) {
+    Scratch send((size_t)chunk_bytes * W, stream), recv((size_t)chunk_bytes * W, stream);
+    if (failed) {
+      const u64 head[2] = {0, CHUNK_MARK_FAILED};
+      for (int r = 0; r < W; ++r)
+        CUDA_TRY(cudaMemcpyAsync((u64*)send.p + (size_t)r * chunk_words, head, 16, cudaMemcpyHostToDevice, stream));
+      CUDA_TRY(cudaStreamSynchronize(stream));  // `head` is a stack object
+    } else {
+      rethrow(b2_state_pack_chunks(local.get(), W, MULTI_CHUNK_RECORDS, stream, send.p));
+    }
+    exchange_equal(c, (const unsigned char*)send.p, (unsigned char*)recv.p, (size_t)chunk_bytes, stream);
+    if (failed) {
+      CUDA_TRY(cudaStreamSynchronize(stream));
+      throw failure;
+    }
+    std::unique_ptr<b2_groupby_state, void (*)(b2_groupby_state*)> merged(make_state(gb, reqs, nreqs), b2_state_destroy);
+    rethrow(b2_state_merge_chunks(merged.get(), recv.p, W, MULTI_CHUNK_RECORDS, stream));
+    read_ctrl(*merged, stream);
+    if (merged->host_ctrl.chunk_overflow >= CHUNK_MARK_FAILED) B2_FAIL(B2_INTERNAL_ERROR, "the local aggregate failed on another rank");
+    if (!merged->host_ctrl.chunk_overflow) {
+      finalize_state(*merged, stream, allocator, out);
+      return;
+    }
+    c.chunks_overflowed = true;  // every rank read a marked chunk: all of them come here
+  }
+
+  // ---- exact sizes: count matrix (with a status word per rank) by all-gather, then variable send / recv
+  Scratch records;
+  std::vector<int64_t> counts((size_t)W + 1, 0);
+  if (!failed) {
+    try {
+      std::vector<int64_t> cnt;
+      pack_table(*local, W, stream, records, cnt);
+      std::copy(cnt.begin(), cnt.end(), counts.begin());
+    } catch (const Err& e) {
+      failed = true;
+      failure = e;
+      cudaGetLastError();
+      std::fill(counts.begin(), counts.end(), 0);
+    }
+  }
+  counts[(size_t)W] = failed ? 1 : 0;
+  const int row = W + 1;
+  Scratch dcounts((size_t)row * 8, stream), dmatrix((size_t)W * row * 8, stream);
+  CUDA_TRY(cudaMemcpyAsync(dcounts.p, counts.data(), (size_t)row * 8, cudaMemcpyHostToDevice, stream));
+  NCCL_TRY(n.AllGather(dcounts.p, dmatrix.p, (size_t)row, ncclInt64, c.comm, stream));
+  std::vector<int64_t> matrix((size_t)W * row);
+  CUDA_TRY(cudaMemcpyAsync(matrix.data(), dmatrix.p, (size_t)W * row * 8, cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  if (failed) throw failure;
+  for (int r = 0; r < W; ++r)
+    if (matrix[(size_t)r * row + W] != 0) B2_FAIL(B2_INTERNAL_ERROR, "the local aggregate failed on another rank");
+  const size_t rb = (size_t)local->plan.stride * 8;
+  int64_t nrecv = 0;
+  std::vector<int64_t> recv_counts((size_t)W);
+  for (int r = 0; r < W; ++r) { recv_counts[(size_t)r] = matrix[(size_t)r * row + c.rank]; nrecv += recv_counts[(size_t)r]; }
+  Scratch recv(std::max<size_t>(8, (size_t)nrecv * rb), stream);
+  NCCL_TRY(n.GroupStart());
+  {
+    size_t soff = 0, roff = 0;
+    for (int r = 0; r < W; ++r) {
+      if (counts[(size_t)r] > 0) NCCL_TRY(n.Send((const unsigned char*)records.p + soff, (size_t)counts[(size_t)r] * rb, ncclUint8, r, c.comm, stream));
+      if (recv_counts[(size_t)r] > 0) NCCL_TRY(n.Recv((unsigned char*)recv.p + roff, (size_t)recv_counts[(size_t)r] * rb, ncclUint8, r, c.comm, stream));
+      soff += (size_t)counts[(size_t)r] * rb;
+      roff += (size_t)recv_counts[(size_t)r] * rb;
+    }
+  }
+  NCCL_TRY(n.GroupEnd());
+  // the local table is no longer needed; the merged one is sized for the records received
+  rethrow(b2_state_reset(local.get(), std::max<int64_t>(nrecv, 1), stream));
+  merge_records(*local, (const u64*)recv.p, nrecv, stream);
+  finalize_state(*local, stream, allocator, out);
+}
+
+}  // namespace
+
+extern "C" {
+
+b2_status b2_comm_unique_id(uint8_t id[B2_COMM_ID_BYTES])
+{
+  return guarded([&] {
+    if (!id) B2_FAIL(B2_INVALID_ARGUMENT, "id is null");
+    static_assert(sizeof(ncclUniqueId) == B2_COMM_ID_BYTES, "NCCL unique id size");
+    ncclUniqueId u;
+    NCCL_TRY(nccl_api().GetUniqueId(&u));
+    std::memcpy(id, &u, sizeof(u));
+  });
+}
+
+b2_status b2_comm_create(const uint8_t id[B2_COMM_ID_BYTES], int32_t rank, int32_t num_ranks, b2_comm** out)
+{
+  return guarded([&] {
+    if (!out) B2_FAIL(B2_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    if (!id || num_ranks < 1 || rank < 0 || rank >= num_ranks) B2_FAIL(B2_INVALID_ARGUMENT, "bad rank / num_ranks / id");
+    ncclUniqueId u;
+    std::memcpy(&u, id, sizeof(u));
+    auto c = std::make_unique<b2_comm>();
+    NCCL_TRY(nccl_api().CommInitRank(&c->comm, num_ranks, u, rank));
+    c->rank = rank; c->nranks = num_ranks; c->owned = true;
+    *out = c.release();
+  });
+}
+
+b2_status b2_comm_adopt(void* nccl_comm, int32_t rank, int32_t num_ranks, b2_comm** out)
+{
+  return guarded([&] {
+    if (!out) B2_FAIL(B2_INVALID_ARGUMENT, "out is null");
+    *out = nullptr;
+    if (!nccl_comm || num_ranks < 1 || rank < 0 || rank >= num_ranks) B2_FAIL(B2_INVALID_ARGUMENT, "bad communicator / rank / num_ranks");
+    nccl_api();
+    auto c = std::make_unique<b2_comm>();
+    c->comm = (ncclComm_t)nccl_comm; c->rank = rank; c->nranks = num_ranks; c->owned = false;
+    *out = c.release();
+  });
+}
+
+void b2_comm_destroy(b2_comm* comm)
+{
+  if (!comm) return;
+  if (comm->owned && comm->comm) {
+    try { nccl_api().CommDestroy(comm->comm); } catch (...) {}
+  }
+  delete comm;
+}
+
+b2_status b2_groupby_aggregate_multi(b2_comm* comm, b2_groupby* gb, const b2_aggregation_request* requests,
+                                     int32_t num_requests, void* stream, const b2_allocator* allocator,
+                                     b2_groupby_result* out)
+{
+  return guarded([&] {
+    if (!comm || !gb || !out) B2_FAIL(B2_INVALID_ARGUMENT, "null argument");
+    g_stats = b2_call_stats{};
+    std::memset(out, 0, sizeof(*out));
+    if (gb->keys.empty()) B2_FAIL(B2_LOGIC_ERROR, "groupby needs at least one key column");
+    device_info();
+    aggregate_multi(*comm, *gb, requests, num_requests, (cudaStream_t)stream, allocator, out);
+  });
 }
 
 const char* b2_last_error(void) { return g_last_error.c_str(); }

@@ -1338,7 +1338,7 @@ k_merge_chunks(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, 
   for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (i64)gridDim.x * blockDim.x) {
     const i64 c = i / chunk_records, r = i - c * chunk_records;
     const u64* chunk = chunks + c * chunk_words;
-    if (r == 0 && chunk[1] != 0) ctrl->chunk_overflow = 1;
+    if (r == 0 && chunk[1] != 0) atomicMax(&ctrl->chunk_overflow, chunk[1]);  // 1 = too many records, 2 = the sender failed
     if ((u64)r >= chunk[0] || chunk[1] != 0) continue;
     const u64* rec = chunk + 2 + r * stride;
     const u64 key  = rec[0];

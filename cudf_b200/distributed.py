@@ -4,8 +4,13 @@ The reference has no NCCL path; its multi-GPU groupby is the cudf-polars streami
 local aggregation, hash shuffle of the PARTIAL aggregates keyed on the group keys, then a reduction
 groupby on each owner (python/cudf_polars/cudf_polars/streaming/actor_graph/groupby.py:339-456),
 with the shuffle built on cudf::hash_partition (cpp/libcudf_streaming/src/partition_utils.cpp:72-100).
-Here the exchange is ``torch.distributed.all_to_all_single`` (NCCL over NVLink/NVSwitch on GPUs,
-gloo on CPU for tests); everything else is the CUDA library.
+For keys that pack into 64 bits the whole plan is ONE call into the CUDA library per rank
+(``b2_groupby_aggregate_multi``: local aggregate, partition of the partial records by owner, NCCL
+send / recv on the caller's stream, merge, finalise) over a communicator the library creates from
+an id that ``torch.distributed`` broadcasts once per process group (``Communicator``).  For the
+other shapes (string / float / wide keys, the rows strategy) the exchange is
+``torch.distributed.all_to_all_single`` (NCCL over NVLink/NVSwitch on GPUs, gloo on CPU for tests)
+between calls into the library.
 
 Two strategies:
   * ``partials``: aggregate locally, partition the partial records {key, n, Σx, Σx², min, max …} by
@@ -52,6 +57,14 @@ def exchange_buffer(buf: torch.Tensor, send_counts: Sequence[int], recv_counts: 
     return out
 
 
+def agree_on_status(ok: bool, device, group=None) -> bool:
+    """True iff every rank reports ``ok``.  A rank whose local step failed must still reach the next
+    collective, or its peers wait there for ever: it reports the failure here and all ranks raise."""
+    t = torch.tensor([0 if ok else 1], dtype=torch.int32, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return int(t.item()) == 0
+
+
 def exchange_records(records: torch.Tensor, counts: Sequence[int], record_bytes: int, group=None
                      ) -> Tuple[torch.Tensor, int]:
     """Exchange of packed partial records: returns (received records, number received)."""
@@ -60,12 +73,56 @@ def exchange_records(records: torch.Tensor, counts: Sequence[int], record_bytes:
     return out, sum(recv_counts)
 
 
+class Communicator:
+    """``b2_comm``: the NCCL communicator ``b2_groupby_aggregate_multi`` exchanges over, one per
+    (process group, device).  Rank 0 draws the NCCL unique id, ``torch.distributed`` broadcasts it."""
+
+    _cache = {}
+
+    def __init__(self, device, group=None):
+        import ctypes as C
+        from . import _lib
+        from .groupby import _check
+        lib = _lib.load()
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            buf = (C.c_uint8 * 128)()
+            _check(lib.b2_comm_unique_id(buf))
+            ident = torch.tensor(list(buf), dtype=torch.uint8)
+        ident = ident.to(device)
+        dist.broadcast(ident, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        raw = (C.c_uint8 * 128)(*ident.cpu().tolist())
+        handle = C.c_void_p()
+        with torch.cuda.device(device):
+            _check(lib.b2_comm_create(raw, rank, world, C.byref(handle)))
+        self._handle = handle
+        self.rank, self.world = rank, world
+
+    @classmethod
+    def for_group(cls, device, group=None) -> "Communicator":
+        key = (id(group), str(device))
+        if key not in cls._cache:
+            cls._cache[key] = cls(device, group)
+        return cls._cache[key]
+
+    def close(self):
+        from . import _lib
+        if self._handle:
+            _lib.load().b2_comm_destroy(self._handle)
+            self._handle = None
+
+
 class DistributedGroupBy:
     """``GroupBy`` over row-sharded inputs: every rank passes its own rows; every rank receives the
     finished groups it owns."""
 
-    def __init__(self, keys, null_handling=0, *, strategy: str = "partials", group=None, **options):
+    def __init__(self, keys, null_handling=0, *, strategy: str = "partials", group=None, python_exchange: bool = False,
+                 **options):
+        """``python_exchange`` keeps the partials strategy on ``torch.distributed`` collectives between
+        library calls (the only form on CPU/gloo) instead of the single native call."""
         from .groupby import GroupBy
+        self._python_exchange = bool(python_exchange)
         if strategy not in ("partials", "rows"):
             raise ValueError("strategy must be 'partials' or 'rows'")
         self._keys = keys
@@ -88,8 +145,28 @@ class DistributedGroupBy:
                 # string / float / wide keys: their table slots reference local rows and cannot travel;
                 # the partial aggregates travel as a table instead
                 return self._aggregate_partial_table(requests, world)
+            if self._keys.columns()[0].data is not None and self._keys.columns()[0].data.is_cuda and not self._python_exchange:
+                return self._aggregate_partials_native(requests)
             return self._aggregate_partials(requests, world)
         return self._aggregate_rows(requests, world)
+
+    def _aggregate_partials_native(self, requests):
+        """Packed keys on GPUs: the whole plan inside the library (``b2_groupby_aggregate_multi``)."""
+        import ctypes as C
+        from . import _lib
+        from .column import allocator_for
+        from .groupby import _adopt_result, _check, _requests_to_c
+        lib = _lib.load()
+        device = self._gb._device
+        comm = Communicator.for_group(device, self._group)
+        keep: list = []
+        creqs = _requests_to_c(requests, keep)
+        alloc = allocator_for(device)
+        res = _lib.GroupbyResult()
+        stream = torch.cuda.current_stream(device).cuda_stream
+        _check(lib.b2_groupby_aggregate_multi(comm._handle, self._gb._handle, creqs, len(requests), C.c_void_p(stream),
+                                              C.byref(alloc.struct), C.byref(res)))
+        return _adopt_result(res, alloc)
 
     # records per destination of the fixed-size exchange (one all-to-all, no host round trip)
     CHUNK_RECORDS = 16384
@@ -101,7 +178,14 @@ class DistributedGroupBy:
         # speculative table and the cardinality estimate; a wrong hint only costs a regrowth
         if self._local_groups_hint > 0 and "expected_groups" not in self._options:
             st.reset(expected_groups=self._local_groups_hint + self._local_groups_hint // 8)
-        st.update()
+        device = self._keys.columns()[0].data.device
+        error = None
+        try:
+            st.update()
+        except Exception as e:   # reported to every rank before anyone enters the exchange
+            error = e
+        if not agree_on_status(error is None, device, self._group):
+            raise error if error is not None else RuntimeError("the local aggregate failed on another rank")
         if not self._chunks_overflowed and st.chunk_bytes(self.CHUNK_RECORDS) * world <= (64 << 20):
             # small states: equal-split all-to-all of fixed chunks; a sender with too many records
             # marks every chunk it sends, so all ranks take the fallback below together — and, having

@@ -151,7 +151,9 @@ typedef struct b2_groupby_options {
   int32_t table_variant;    /* 0 auto; 1 global-memory table only; 3 shared-memory table with
                                hashing only (no dense key box); 4 / 5 = auto, but the lean
                                FLOAT32-mean kernel reads its tiles through registers (4) or
-                               through the cp.async.bulk shared-memory ring (5)               */
+                               through the cp.async.bulk shared-memory ring (5); 6 = always
+                               take the radix-partitioned path when the keys allow it (auto
+                               takes it from about half a million groups), 7 = never          */
   int32_t shared_table_bytes; /* <= 0 = auto                                                   */
   /* Fused drop_nulls pre-filter (cpp/src/stream_compaction/drop_nulls.cu:56-96): a row takes
    * part only if it is valid in every one of these masks (bit i = row i, same bit layout and
@@ -281,6 +283,37 @@ b2_status b2_bytes_to_mask(const uint8_t* bytes, int64_t size, void* stream, uin
 
 /* Releases the buffers of one owned column obtained from b2_hash_partition. */
 void b2_column_free(b2_owned_column* col, const b2_allocator* allocator, void* stream);
+
+/* ---- multi-GPU: one process per GPU, NCCL over NVLink / NVSwitch ----------
+ * The reference's distributed groupby aggregates locally, hash-partitions the PARTIAL aggregates by
+ * key, shuffles them and reduces on the owner (python/cudf_polars/cudf_polars/streaming/actor_graph/
+ * groupby.py:339-456 over partition_and_pack / unpack_and_concat,
+ * cpp/libcudf_streaming/src/partition_utils.cpp:72-185).  b2_groupby_aggregate_multi is that plan as
+ * one call per rank: local fused aggregate -> partial records partitioned by owner = hash(key) mod
+ * ranks -> ONE exchange (ncclSend / ncclRecv pairs inside an ncclGroup, on `stream`) -> merge ->
+ * finalize.  Every rank receives the finished groups it owns; the key sets of the ranks are disjoint.
+ *
+ * A b2_comm wraps an NCCL communicator.  The NCCL library is resolved at run time (the copy
+ * already loaded into the process, else libnccl.so.2 from the loader path; B2_NCCL_LIB overrides),
+ * so the library has no link-time dependency on it.  b2_comm_unique_id (rank 0) + b2_comm_create
+ * (every rank, with its GPU current) follow ncclGetUniqueId / ncclCommInitRank; b2_comm_adopt wraps a
+ * communicator the caller already owns (it is not destroyed by b2_comm_destroy).
+ *
+ * Small states travel as fixed-size chunks (no host round trip: b2_state_pack_chunks); a rank with
+ * more records than a chunk holds marks every chunk it sends, and all ranks repeat the exchange with
+ * exact sizes (one all-gather of the count matrix, then variable send / recv).  Keys that do not
+ * pack into 64 bits (strings, floats, wide composites) return B2_UNSUPPORTED on EVERY rank before
+ * any communication (the key types are the same everywhere): partition the rows with
+ * b2_hash_partition instead.  All ranks must make the same sequence of calls. */
+typedef struct b2_comm b2_comm;
+#define B2_COMM_ID_BYTES 128
+b2_status b2_comm_unique_id(uint8_t id[B2_COMM_ID_BYTES]);
+b2_status b2_comm_create(const uint8_t id[B2_COMM_ID_BYTES], int32_t rank, int32_t num_ranks, b2_comm** out);
+b2_status b2_comm_adopt(void* nccl_comm, int32_t rank, int32_t num_ranks, b2_comm** out);
+void b2_comm_destroy(b2_comm* comm);
+b2_status b2_groupby_aggregate_multi(b2_comm* comm, b2_groupby* gb, const b2_aggregation_request* requests,
+                                     int32_t num_requests, void* stream, const b2_allocator* allocator,
+                                     b2_groupby_result* out);
 
 /* ---- aggregate without any device allocation -----------------------------
  * No counterpart in the reference (libcudf always allocates through an rmm resource).

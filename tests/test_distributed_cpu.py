@@ -74,3 +74,32 @@ def test_plan_exchange_offsets():
 def test_single_process_falls_back_to_local_groupby_path():
     # with no process group a DistributedGroupBy is a plain GroupBy: nothing to exchange
     assert not dist.is_initialized()
+
+
+def _status_worker(rank, world, port, failing_rank, result_queue):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ok = D.agree_on_status(rank != failing_rank, torch.device("cpu"))
+        # whatever happened, every rank is still in step: a following collective completes
+        t = torch.tensor([rank + 1])
+        dist.all_reduce(t)
+        result_queue.put((rank, ok, int(t.item())))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("failing_rank", [-1, 0, 1])
+def test_a_failing_rank_is_seen_by_every_rank(failing_rank):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_status_worker, args=(r, 2, port, failing_rank, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert [g[1] for g in got] == [failing_rank < 0] * 2
+    assert [g[2] for g in got] == [3, 3]

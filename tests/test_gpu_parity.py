@@ -346,3 +346,57 @@ def test_results_are_deterministic_for_integers():
     oa, ob = H.sort_order(a[0]), H.sort_order(b[0])
     for x, y in zip(a[1][0], b[1][0]):
         assert H.take(x, oa) == H.take(y, ob)
+
+
+# ------------------------------------------------------------------------------------ partitioned path
+def _partition_inputs(seed, n, domain, nullable_keys=False):
+    rng = np.random.default_rng(seed)
+    kv = rng.integers(-1, domain, n).astype(np.int64)          # -1 = the key whose bits equal the empty-slot marker
+    k = HostColumn.from_numpy(kv, valid=(rng.random(n) > 0.02) if nullable_keys else None)
+    v1 = HostColumn.from_numpy(rng.integers(-10**9, 10**9, n).astype(np.int64))
+    v2 = HostColumn.from_numpy(rng.lognormal(0, 1, n), valid=rng.random(n) > 0.05)
+    v3 = HostColumn.from_numpy(rng.integers(-100, 100, n).astype(np.int16), valid=rng.random(n) > 0.3)
+    return k, v1, v2, v3
+
+
+@pytest.mark.parametrize("table_bytes", [0, 16384])
+@pytest.mark.parametrize("policy", [NullPolicy.EXCLUDE, NullPolicy.INCLUDE])
+def test_partitioned_path_matches_oracle(table_bytes, policy):
+    """table_variant 6 forces the radix-partitioned path; 16 KB tables force its second level
+    (300K groups / 128 per bucket = 12 digit bits)."""
+    import cudf_b200 as cb
+    k, v1, v2, v3 = _partition_inputs(21, 700_000, 400_000, nullable_keys=True)
+    reqs = [(v1, [Kind.SUM, Kind.MIN, Kind.MAX, Kind.COUNT_VALID]), (v2, [Kind.SUM, Kind.MEAN, Kind.VARIANCE, Kind.COUNT_ALL]),
+            (v3, [Kind.SUM, Kind.MIN, Kind.MAX, Kind.MEAN, (Kind.STD, 0), Kind.SUM_OF_SQUARES])]
+    got = check([k], reqs, policy, table_variant=6, shared_table_bytes=table_bytes)
+    st = cb.last_call_stats()
+    assert st.table_attempts == 1 and not st.used_shared_table      # one partitioned pass, no table fallback
+    assert got[0][0].size > 300_000
+
+
+def test_partitioned_path_composite_keys_and_row_filters():
+    rng = np.random.default_rng(22)
+    n = 500_000
+    a = HostColumn.from_numpy(rng.integers(0, 3000, n).astype(np.int32))
+    b = HostColumn.from_numpy(rng.integers(-50, 50, n).astype(np.int16), valid=rng.random(n) > 0.1)
+    v = HostColumn.from_numpy(rng.standard_normal(n).astype(np.float32), valid=rng.random(n) > 0.2)
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        check([a, b], [(v, ALL_AGGS)], policy, row_filters=[v], table_variant=6)
+    check([a, b], [(v, ALL_AGGS)], table_variant=6, shared_table_bytes=20000)
+
+
+def test_partitioned_path_falls_back_when_the_hint_is_far_too_low():
+    """A hint of 1000 groups for 300K: buckets overflow their shared-memory tables, the attempt is
+    discarded and the global table takes over — same result."""
+    import cudf_b200 as cb
+    k, v1, v2, _ = _partition_inputs(23, 600_000, 400_000)
+    got = check([k], [(v1, [Kind.SUM, Kind.MAX]), (v2, [Kind.MEAN])], table_variant=6, expected_groups=1000)
+    assert got[0][0].size > 250_000
+
+
+def test_partitioned_path_few_rows_and_skew():
+    rng = np.random.default_rng(24)
+    for n in (1, 5, 4097, 70_000):
+        k = HostColumn.from_numpy(np.where(rng.random(n) < 0.5, 7, rng.integers(0, 50_000, n)).astype(np.int64))
+        v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.1)
+        check([k], [(v, ALL_AGGS)], table_variant=6)

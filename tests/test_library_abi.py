@@ -62,3 +62,16 @@ def test_missing_library_fails_loudly(tmp_path, monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(_lib.LibraryMissing, match="no CPU fallback"):
         _lib.load()
+
+
+def test_comm_entry_points_reject_bad_arguments():
+    """The multi-GPU entry points (no GPU needed for the argument checks)."""
+    lib = _lib.load()
+    handle = ctypes.c_void_p()
+    ident = (ctypes.c_uint8 * 128)()
+    assert lib.b2_comm_create(ident, 2, 2, ctypes.byref(handle)) == _lib.Status.INVALID_ARGUMENT
+    assert lib.b2_comm_create(None, 0, 1, ctypes.byref(handle)) == _lib.Status.INVALID_ARGUMENT
+    assert lib.b2_comm_adopt(None, 0, 1, ctypes.byref(handle)) == _lib.Status.INVALID_ARGUMENT
+    assert handle.value is None
+    assert lib.b2_groupby_aggregate_multi(None, None, None, 0, None, None, None) == _lib.Status.INVALID_ARGUMENT
+    lib.b2_comm_destroy(None)
