@@ -95,8 +95,8 @@ PROTOTYPES = {
     "b2_state_num_groups": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]),
     "b2_state_finalize": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(Allocator), C.POINTER(GroupbyResult)]),
     "b2_state_destroy": (None, [C.c_void_p]),
-    "b2_hash_partition": (C.c_int, [C.POINTER(ColumnView), C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
-                                    C.POINTER(Allocator), C.POINTER(OwnedColumn), C.POINTER(C.c_int64)]),
+    "b2_hash_partition": (C.c_int, [C.POINTER(ColumnView), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_uint32,
+                                    C.c_void_p, C.POINTER(Allocator), C.POINTER(OwnedColumn), C.POINTER(C.c_int64)]),
     "b2_mask_to_bytes": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "b2_bytes_to_mask": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b2_column_free": (None, [C.POINTER(OwnedColumn), C.POINTER(Allocator), C.c_void_p]),

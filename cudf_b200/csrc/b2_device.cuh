@@ -325,6 +325,79 @@ __device__ inline bool rows_equal(const DPlan& P, i64 a, i64 b)
   return true;
 }
 
+// ---------------------------------------------------------------------------------- the reference's row hash
+// cudf::hash_partition assigns row -> hash(row) % partitions with MurmurHash3_x86_32 per element
+// (cpp/include/cudf/hashing/detail/murmurhash3_x86_32.cuh:22-76: the published algorithm of Austin
+// Appleby over the element's bytes, seeded), a null element hashing to UINT32_MAX
+// (cpp/include/cudf/detail/row_operator/hashing.cuh:52-75), the first column's hash folded with the
+// others by boost's hash_combine (cpp/include/cudf/hashing/detail/hashing.hpp:83-86); floats hash
+// with -0 -> +0 and one NaN, BOOL8 as the byte 0 / 1.  HASH_IDENTITY casts the numeric element to
+// uint32 instead (cpp/src/partitioning/partitioning.cu:856-874).
+__host__ __device__ __forceinline__ u32 rotl32(u32 x, int r) { return (x << r) | (x >> (32 - r)); }
+
+__host__ __device__ inline u32 murmur3_x86_32(const unsigned char* data, i64 len, u32 seed)
+{
+  const u32 c1 = 0xcc9e2d51u, c2 = 0x1b873593u;
+  u32 h = seed;
+  const i64 nblocks = len / 4;
+  for (i64 i = 0; i < nblocks; ++i) {
+    u32 k = (u32)data[4 * i] | ((u32)data[4 * i + 1] << 8) | ((u32)data[4 * i + 2] << 16) | ((u32)data[4 * i + 3] << 24);
+    k *= c1; k = rotl32(k, 15); k *= c2;
+    h ^= k; h = rotl32(h, 13); h = h * 5u + 0xe6546b64u;
+  }
+  const unsigned char* tail = data + 4 * nblocks;
+  u32 k = 0;
+  switch (len & 3) {
+    case 3: k ^= (u32)tail[2] << 16;
+    case 2: k ^= (u32)tail[1] << 8;
+    case 1: k ^= (u32)tail[0];
+            k *= c1; k = rotl32(k, 15); k *= c2; h ^= k;
+  }
+  h ^= (u32)len;
+  h ^= h >> 16; h *= 0x85ebca6bu; h ^= h >> 13; h *= 0xc2b2ae35u; h ^= h >> 16;
+  return h;
+}
+// the same over a value held in a register (little endian, `nbytes` = 1, 2, 4 or 8)
+__host__ __device__ __forceinline__ u32 murmur3_x86_32_value(u64 v, int nbytes, u32 seed)
+{
+  unsigned char b[8];
+  for (int i = 0; i < 8; ++i) b[i] = (unsigned char)(v >> (8 * i));
+  return murmur3_x86_32(b, nbytes, seed);
+}
+__host__ __device__ __forceinline__ u32 hash_combine32(u32 lhs, u32 rhs)
+{
+  return lhs ^ (rhs + 0x9e3779b9u + (lhs << 6) + (lhs >> 2));
+}
+
+enum RefHash : int { RH_IDENTITY = 0, RH_MURMUR3 = 1, RH_ENGINE = 2 /* this engine's own 64-bit mix */ };
+
+__device__ inline u32 ref_element_hash(const DKeyCol& c, i64 row, int kind, u32 seed)
+{
+  const i64 idx = c.offset + row;
+  if (c.mask && !bit_valid(c.mask, idx)) return 0xFFFFFFFFu;
+  if (c.vclass == VC_STRING) {
+    const i64 b = str_offset(c, idx), e = str_offset(c, idx + 1);
+    return murmur3_x86_32(c.data + b, e - b, seed);
+  }
+  u64 bits = canonical_bits(c, idx);  // -0 -> +0, one NaN
+  if (c.vclass == VC_BOOL) bits = bits != 0;
+  if (kind == RH_IDENTITY) {
+    switch (c.vclass) {
+      case VC_F32: return (u32)__uint_as_float((u32)bits);
+      case VC_F64: return (u32)__longlong_as_double((i64)bits);
+      default: return (u32)bits;  // integers: the low 32 bits, as static_cast<uint32_t> gives
+    }
+  }
+  return murmur3_x86_32_value(bits, c.width, seed);
+}
+
+__device__ inline u32 ref_row_hash(const DPlan& P, i64 row, int kind, u32 seed)
+{
+  u32 h = ref_element_hash(P.keys[0], row, kind, seed);
+  for (int k = 1; k < P.nkeys; ++k) h = hash_combine32(h, ref_element_hash(P.keys[k], row, kind, seed));
+  return h;
+}
+
 // ---------------------------------------------------------------------------------- values
 // A value is carried as 64 bits: integers sign/zero-extended to int64, floats widened to double.
 __device__ __forceinline__ u64 load_value(const DValCol& c, i64 row)

@@ -565,6 +565,7 @@ constexpr int64_t DENSE_REGION_SLOTS = 32768;  // >= the largest dense box the s
 // whether table_variant 0 (auto) runs the lean kernel with the cp.async.bulk tile ring (variant 5)
 // or with register tiles (variant 4)
 constexpr bool LEAN_STAGED_BY_DEFAULT = true;
+constexpr int64_t LEAN_DIRECT_SMEM = 136 * 1024;  // table of the register-tile variant: 17K slots
 // B2_TRACE=1 in the environment prints phase times to stderr (each mark synchronises the stream, so
 // the traced call itself is slower)
 struct Trace {
@@ -674,10 +675,10 @@ void launch_aggregate(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, int S,
   g_stats.kernel_launches++;
 }
 
-template <int NK, bool K8, bool STAGED>
+template <int NK, bool K8, bool STAGED, bool KEY_MASKS>
 void launch_lean(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, size_t smem, cudaStream_t stream, u32 region_slots)
 {
-  auto kern = k_aggregate_lean<NK, K8, STAGED>;
+  auto kern = k_aggregate_lean<NK, K8, STAGED, KEY_MASKS>;
   static thread_local size_t configured[64] = {};
   allow_shared(kern, smem, configured);
   kern<<<device_info().sms, 1024, smem, stream>>>(P, tbl, cap, ctrl, region_slots);
@@ -709,6 +710,7 @@ struct SharedPlan {
   u32 cap_dense = 0;          // slots a dense key box may use (0 = no box)
   bool lean = false;          // k_aggregate_lean runs in front of k_aggregate
   bool staged = false;        // ... with the cp.async.bulk tile ring
+  size_t lean_smem = 0;       // dynamic shared memory of k_aggregate_lean
 };
 
 SharedPlan plan_shared(const b2_groupby_state& st, const b2_groupby& gb)
@@ -732,7 +734,13 @@ SharedPlan plan_shared(const b2_groupby_state& st, const b2_groupby& gb)
   const int need = PF_FAST | PF_VEC_KEYS | PF_VEC_VAL0;
   if (sc.f32mean && sc.nkeys <= 3 && (P.flags & need) == need && P.nrows >= SAMPLE_ROWS && P.nrows < 0xFFFF0000ll) {
     sp.lean = true;
-    sp.cap_dense = (u32)std::min<int64_t>(DENSE_REGION_SLOTS, ((int64_t)budget - 256) * 8 / 65);
+    // Register tiles arrive through L1, which is what the shared-memory carve-out leaves of the SM's
+    // 256 KB: with the whole opt-in taken, ~24 KB of L1 cannot hold the lines of the loads in flight
+    // (32 warps x 3 vector loads x 2 tiles) and the row loop slows down by a third.  So this variant
+    // takes a table of at most LEAN_DIRECT_SMEM and leaves the rest to L1; wider key boxes go to the
+    // generic kernel.
+    sp.lean_smem = (size_t)std::min<int64_t>(budget, gb.shared_table_bytes > 0 ? budget : LEAN_DIRECT_SMEM);
+    sp.cap_dense = (u32)std::min<int64_t>(DENSE_REGION_SLOTS, ((int64_t)sp.lean_smem - 256) * 8 / 65);
     // the staged variant needs room for its tile ring, flat 16-byte-aligned tiles, and validity that is
     // either absent or the value column's own mask (also when used as the row filter)
     const DValCol& vc = P.vals[sc.cells[0].col];
@@ -746,6 +754,7 @@ SharedPlan plan_shared(const b2_groupby_state& st, const b2_groupby& gb)
     const bool want_staged = gb.table_variant == 5 || (gb.table_variant == 0 && LEAN_STAGED_BY_DEFAULT);
     if (want_staged && bulk_ok && staged_cap >= 1024) {
       sp.staged = true;
+      sp.lean_smem = (size_t)budget;  // bulk copies land in shared memory directly: L1 is not in their way
       sp.cap_dense = (u32)std::min<int64_t>(DENSE_REGION_SLOTS, staged_cap);
     }
   }
@@ -765,10 +774,14 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
   if (lean) {
     bool k8 = false;  // any 8-byte key column?
     for (int k = 0; k < sc.nkeys; ++k) k8 = k8 || sc.key_width[k] == 8;
-#define B2_LEAN(N, W)                                                                                         \
-    do {                                                                                                      \
-      if (sp.staged) launch_lean<N, W, true>(P, st.table, st.cap, st.ctrl, sp.smem, stream, (u32)st.dense_slots);  \
-      else launch_lean<N, W, false>(P, st.table, st.cap, st.ctrl, sp.smem, stream, (u32)st.dense_slots);      \
+    bool key_masks = false;
+    for (int k = 0; k < sc.nkeys; ++k) key_masks = key_masks || P.keys[k].mask != nullptr;
+    // (the staged variant is only planned when no key column carries a mask)
+#define B2_LEAN(N, W)                                                                                              \
+    do {                                                                                                           \
+      if (sp.staged) launch_lean<N, W, true, false>(P, st.table, st.cap, st.ctrl, sp.lean_smem, stream, (u32)st.dense_slots);  \
+      else if (key_masks) launch_lean<N, W, false, true>(P, st.table, st.cap, st.ctrl, sp.lean_smem, stream, (u32)st.dense_slots); \
+      else launch_lean<N, W, false, false>(P, st.table, st.cap, st.ctrl, sp.lean_smem, stream, (u32)st.dense_slots);    \
     } while (0)
     switch (sc.nkeys) {
       case 1: if (k8) B2_LEAN(1, true); else B2_LEAN(1, false); break;
@@ -875,6 +888,13 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
   trace.mark("partition: histogram + estimate");
   if (active == 0) return false;
   if (!forced && est < RP_MIN_GROUPS) return false;
+  // Heavy skew (one key holding several per cent of the rows) would put that key's rows into one bucket
+  // and serialise them on one shared-memory slot: the fused pass with its hot-key cache serves such inputs.
+  {
+    u64 top = 0;
+    for (u64 c : h_hist) top = std::max(top, c);
+    if (!forced && (double)top > 8.0 * (double)active / TOP + 4096.0) return false;
+  }
 
   // 2. digits: buckets of about half a shared-memory table each (two CTAs of the aggregate kernel per SM)
   const int slot_bytes = 8 * (1 + sc.ncells);
@@ -887,7 +907,11 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
   while (((double)est * 1.05) / (double)(1ll << T) > 0.5 * slots) ++T;
   T = std::max(T, 1);
   if (T > 2 * RP_MAX_BITS) return false;
-  const int b1 = T <= RP_MAX_BITS ? T : (T + 1) / 2, b2 = T - b1;
+  int b1 = T <= RP_MAX_BITS ? T : (T + 1) / 2, b2 = T - b1;
+  if (const char* e = getenv("B2_RP_BITS")) {  // tuning aid: "b1,b2"
+    int x = 0, y = 0;
+    if (sscanf(e, "%d,%d", &x, &y) == 2 && x >= 1 && x <= RP_MAX_BITS && y >= 0 && y <= RP_MAX_BITS) { b1 = x; b2 = y; }
+  }
   const int F1 = 1 << b1, F2 = 1 << b2;
   const int64_t nbuckets = (int64_t)F1 * F2;
 
@@ -913,8 +937,12 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
     CUDA_TRY(cudaMemcpyAsync(d_cur1, h_start.data(), (size_t)F1 * 8, cudaMemcpyHostToDevice, stream));
     Scratch recA((size_t)words * (size_t)active * 8, stream);
     DScatter D1{DRecords{(u64*)recA.p, active, words, valid_word}, d_cur1, 64 - b1, F1};
-    const int sgrid = (int)std::max<int64_t>(1, std::min<int64_t>((P.nrows + RP_TILE - 1) / RP_TILE, sms));
-    k_rp_scatter<<<sgrid, RP_BLOCK, 0, stream>>>(P, D1);
+    const int sgrid = (int)std::max<int64_t>(1, std::min<int64_t>((P.nrows + RP_TILE - 1) / RP_TILE, (int64_t)sms * 2));
+    {
+      static thread_local size_t configured[64] = {};
+      allow_shared(k_rp_scatter, rp_tile_smem(F1), configured);
+    }
+    k_rp_scatter<<<sgrid, RPS_BLOCK, rp_tile_smem(F1), stream>>>(P, D1);
     CUDA_TRY(cudaGetLastError());
     g_stats.kernel_launches++;
     trace.mark("partition: level-1 scatter");
@@ -942,7 +970,11 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
       CUDA_TRY(cudaMemcpyAsync(d_cur2, d_start2, (size_t)nbuckets * 8, cudaMemcpyDeviceToDevice, stream));
       recB = Scratch((size_t)words * (size_t)active * 8, stream);
       DScatter D2{DRecords{(u64*)recB.p, active, words, valid_word}, d_cur2, shift2, F2};
-      k_rp_scatter2<<<std::min(g2, sms), RP_BLOCK, 0, stream>>>(L, D2);
+      {
+        static thread_local size_t configured[64] = {};
+        allow_shared(k_rp_scatter2, rp_tile_smem(F2), configured);
+      }
+      k_rp_scatter2<<<(int)std::max<int64_t>(1, std::min<int64_t>(max_tiles, (int64_t)sms * 2)), RPS_BLOCK, rp_tile_smem(F2), stream>>>(L, D2);
       CUDA_TRY(cudaGetLastError());
       g_stats.kernel_launches += 3;
       src.rec = (u64*)recB.p;
@@ -1731,137 +1763,150 @@ void b2_state_destroy(b2_groupby_state* st)
 }
 
 b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, int32_t num_key_columns,
-                            int32_t num_parts, void* stream_, const b2_allocator* allocator,
-                            b2_owned_column* out_columns, int64_t* offsets)
+                            int32_t num_parts, int32_t hash_function, uint32_t seed, void* stream_,
+                            const b2_allocator* allocator, b2_owned_column* out_columns, int64_t* offsets)
 {
   return guarded([&] {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (!offsets || num_columns < 0 || (num_columns > 0 && (!columns || !out_columns)) || num_key_columns < 0 ||
         num_key_columns > num_columns || num_parts < 0 || num_parts > (1 << 20))
       B2_FAIL(B2_INVALID_ARGUMENT, "bad argument");
+    // cpp/src/partitioning/partitioning.cu:938-945
+    if (hash_function != B2_HASH_IDENTITY && hash_function != B2_HASH_MURMUR3)
+      B2_FAIL(B2_LOGIC_ERROR, "Unsupported hash function in hash_partition");
     if (num_columns > MAX_PART_COLS) B2_FAIL(B2_UNSUPPORTED, "more than 32 columns");
+    if (num_key_columns > MAX_KEYS) B2_FAIL(B2_UNSUPPORTED, "more than 16 columns to hash");
     device_info();
     const b2_allocator al = resolve(allocator);
     // nothing to hash, or nowhere to put the rows: an empty table of the same column types and
-    // num_parts + 1 zero offsets (cpp/tests/partitioning/hash_partition_test.cpp:72-142)
-    const bool empty_result = num_key_columns == 0 || num_parts == 0 || num_columns == 0;
-    const int64_t n = (empty_result || num_columns == 0) ? 0 : columns[0].size;
-    int str_col = -1;
+    // num_parts + 1 zero offsets (cpp/src/partitioning/partitioning.cu:885-888,
+    // cpp/tests/partitioning/hash_partition_test.cpp:72-142)
+    const bool empty_result = num_key_columns == 0 || num_parts == 0 || num_columns == 0 || columns[0].size == 0;
+    const int64_t n = empty_result ? 0 : columns[0].size;
     for (int c = 0; c < num_columns; ++c) {
-      if (!empty_result && columns[c].size != n) B2_FAIL(B2_LOGIC_ERROR, "columns differ in size");
+      // cpp/src/partitioning/partitioning.cu:934-937 (std::invalid_argument there)
+      if (!empty_result && columns[c].size != n)
+        B2_FAIL(B2_INVALID_ARGUMENT, "Input table and key table must have same number of rows, or key table should have no columns.");
       if (columns[c].type_id == B2_STRING) {
-        if (str_col >= 0) B2_FAIL(B2_UNSUPPORTED, "hash_partition serves at most one STRING column");
         if (n > 0 && (columns[c].num_children < 1 || !columns[c].children))
           B2_FAIL(B2_INVALID_ARGUMENT, "STRING column needs an offsets child");
-        str_col = c;
       } else if (width_of(columns[c].type_id) == 0) {
         B2_FAIL(B2_UNSUPPORTED, "hash_partition serves fixed-width and STRING columns");
       }
+      // cpp/src/partitioning/partitioning.cu:890-894
+      if (c < num_key_columns && num_parts > 0 && hash_function == B2_HASH_IDENTITY && !is_numeric_t(columns[c].type_id))
+        B2_FAIL(B2_LOGIC_ERROR, "IdentityHash does not support this data type");
     }
-    // hashing plan over the key columns: nulls hash as nulls (they are rows like any other here)
-    b2_groupby gb;
-    for (int k = 0; k < num_key_columns; ++k) gb.keys.emplace_back(columns[k]);
-    gb.null_policy = B2_NULL_INCLUDE;
-    DPlan P{};
-    if (!empty_result) {
-      Schema sc = make_schema(gb, nullptr, 0);
-      fill_plan_schema(P, sc);
-      bind_plan_inputs(P, sc, gb, nullptr, 0);
-    }
-
-    auto Qp = std::make_unique<DPartPlan>();
-    DPartPlan& Q = *Qp;
-    std::memset(&Q, 0, sizeof(Q));
-    Q.ncols = num_columns;
-    Q.nparts = num_parts;
-    Q.str_col = str_col;
-    const int64_t want = std::max<int64_t>(1, (n + 8191) / 8192);
-    int grid = (int)std::min<int64_t>(want, (int64_t)device_info().sms * 4);
-    // per-CTA counters fit shared memory up to 4096 partitions; beyond that they live in global
-    // memory, with fewer CTAs so that grid x partitions stays bounded
-    Q.counters_in_global = num_parts > 4096;
-    if (Q.counters_in_global) grid = (int)std::max<int64_t>(1, std::min<int64_t>(grid, (int64_t)(1 << 22) / num_parts));
-    Q.rows_per_cta = ((n + grid - 1) / grid + PART_BLOCK - 1) / PART_BLOCK * PART_BLOCK;
     for (int c = 0; c < num_columns; ++c) std::memset(&out_columns[c], 0, sizeof(b2_owned_column));
+    for (int p = 0; p <= num_parts; ++p) offsets[p] = 0;
     struct Guard {
       b2_owned_column* cols; int n; const b2_allocator* al; cudaStream_t s; bool armed = true;
       ~Guard() { if (armed) for (int i = 0; i < n; ++i) b2_column_free(&cols[i], al, s); }
     } guard{out_columns, num_columns, &al, stream};
-    for (int c = 0; c < num_columns; ++c) {
-      const bool nullable = columns[c].null_mask != nullptr && !empty_result;
-      DPartCol& d = Q.cols[c];
-      if (c == str_col) {
-        b2_owned_column& oc = out_columns[c];
-        oc.type_id = B2_STRING;
-        oc.size = (int32_t)n;
-        if (nullable) {
-          oc.null_mask_bytes = (size_t)std::max<int64_t>(1, (n + 511) / 512) * 64;
-          oc.null_mask = (uint32_t*)out_alloc(al, oc.null_mask_bytes, stream);
-        }
-        if (n > 0) {
-          const b2_column_view& o = columns[c].children[0];
-          Q.str_offsets = (const unsigned char*)o.data + (size_t)o.offset * (o.type_id == B2_INT64 ? 8 : 4);
-          Q.str_offs64 = o.type_id == B2_INT64;
-        }
-        d.width = 0;
-      } else {
-        init_owned(out_columns[c], columns[c].type_id, n, nullable, al, stream);
-        out_columns[c].scale = columns[c].scale;
-        d.width = width_of(columns[c].type_id);
-      }
-      out_columns[c].scale = columns[c].scale;
-      out_columns[c].null_count = (nullable && n > 0) ? columns[c].null_count : 0;
-      if (nullable) CUDA_TRY(cudaMemsetAsync(out_columns[c].null_mask, 0, out_columns[c].null_mask_bytes, stream));
-      d.src = (const unsigned char*)columns[c].data; d.mask = columns[c].null_mask; d.offset = columns[c].offset;
-      d.dst = (unsigned char*)out_columns[c].data;
-      d.dst_mask = out_columns[c].null_mask;
-    }
-    for (int p = 0; p <= num_parts; ++p) offsets[p] = 0;
 
-    const size_t cells = (size_t)grid * num_parts;
-    Scratch counts(std::max<size_t>(8, cells * sizeof(u32)), stream), starts(std::max<size_t>(8, cells * sizeof(i64)), stream);
-    Scratch chars, char_starts;
-    if (str_col >= 0) {
-      chars = Scratch(std::max<size_t>(8, cells * sizeof(u64)), stream);
-      char_starts = Scratch(std::max<size_t>(8, cells * sizeof(i64)), stream);
-    }
-    const size_t smem = Q.counters_in_global ? 0 : (size_t)num_parts * 12;
-    Scratch cursors;
-    if (Q.counters_in_global) {
-      cursors = Scratch(std::max<size_t>(8, cells * sizeof(u64)), stream);
-      CUDA_TRY(cudaMemsetAsync(counts.p, 0, counts.bytes, stream));
-      CUDA_TRY(cudaMemsetAsync(cursors.p, 0, cursors.bytes, stream));
-      if (str_col >= 0) CUDA_TRY(cudaMemsetAsync(chars.p, 0, chars.bytes, stream));
-    }
-    int64_t total_chars = 0;
-    std::vector<i64> h_starts(cells), h_cstarts(cells);
-    if (n > 0) {
-      k_partition_count<<<grid, PART_BLOCK, smem, stream>>>(P, Q, (u32*)counts.p, (u64*)chars.p);
-      CUDA_TRY(cudaGetLastError());
-      std::vector<u32> h_counts(cells);
-      std::vector<u64> h_chars(cells, 0);
-      CUDA_TRY(cudaMemcpyAsync(h_counts.data(), counts.p, cells * sizeof(u32), cudaMemcpyDeviceToHost, stream));
-      if (str_col >= 0) CUDA_TRY(cudaMemcpyAsync(h_chars.data(), chars.p, cells * sizeof(u64), cudaMemcpyDeviceToHost, stream));
-      CUDA_TRY(cudaStreamSynchronize(stream));
-      int64_t run = 0;
-      for (int p = 0; p < num_parts; ++p) {
-        offsets[p] = run;
-        for (int b = 0; b < grid; ++b) {
-          h_starts[(size_t)b * num_parts + p] = run;
-          run += h_counts[(size_t)b * num_parts + p];
-          h_cstarts[(size_t)b * num_parts + p] = total_chars;
-          total_chars += (int64_t)h_chars[(size_t)b * num_parts + p];
+    if (empty_result) {
+      for (int c = 0; c < num_columns; ++c) {
+        b2_owned_column& oc = out_columns[c];
+        if (columns[c].type_id == B2_STRING) {
+          oc.type_id = B2_STRING;
+        } else {
+          init_owned(oc, columns[c].type_id, 0, false, al, stream);
         }
+        oc.scale = columns[c].scale;
       }
-      offsets[num_parts] = run;
-      if (run != n) B2_FAIL(B2_INTERNAL_ERROR, "hash_partition: row count mismatch");
+      guard.armed = false;
+      return;
     }
-    if (str_col >= 0) {
-      // chars + offsets of the partitioned STRING column; INT64 offsets beyond the reference's
-      // large-strings threshold (cpp/src/strings/utilities.cu:150-157)
-      b2_owned_column& oc = out_columns[str_col];
-      const bool big = total_chars > 0x7FFFFFFFll;
-      oc.data_bytes = (size_t)std::max<int64_t>(total_chars, 1);
+
+    // hashing plan over the key columns (their descriptors; nulls hash as nulls)
+    b2_groupby gb;
+    for (int k = 0; k < num_key_columns; ++k) gb.keys.emplace_back(columns[k]);
+    gb.null_policy = B2_NULL_INCLUDE;
+    DPlan P{};
+    {
+      Schema sc = make_schema(gb, nullptr, 0);
+      fill_plan_schema(P, sc);
+      bind_plan_inputs(P, sc, gb, nullptr, 0);
+    }
+    DPartPlan Q{};
+    Q.nparts = num_parts;
+    Q.hash_kind = hash_function == B2_HASH_IDENTITY ? RH_IDENTITY : RH_MURMUR3;
+    Q.seed = seed;
+    const int64_t want = std::max<int64_t>(1, (n + 8191) / 8192);
+    int grid = (int)std::min<int64_t>(want, (int64_t)device_info().sms * 4);
+    // per-CTA counters fit shared memory up to 4096 partitions; beyond that they live in global memory,
+    // with fewer CTAs so that grid x partitions stays bounded (hash_partition_test.cpp:172-187)
+    Q.counters_in_global = num_parts > 4096;
+    if (Q.counters_in_global) grid = (int)std::max<int64_t>(1, std::min<int64_t>(grid, (int64_t)(1 << 22) / num_parts));
+    Q.rows_per_cta = ((n + grid - 1) / grid + PART_BLOCK - 1) / PART_BLOCK * PART_BLOCK;
+    const size_t cells = (size_t)grid * num_parts;
+    const size_t smem = Q.counters_in_global ? 0 : (size_t)num_parts * 4;
+
+    // 1. rows per (partition, CTA), 2. their starts by one exclusive scan, 3. the permutation
+    Scratch counts(cells * 8, stream), starts((cells + 1) * 8, stream), d_offsets((size_t)(num_parts + 1) * 8, stream);
+    Scratch cta_scratch, perm((size_t)n * 4, stream);
+    if (Q.counters_in_global) {
+      cta_scratch = Scratch(cells * 4, stream);
+      CUDA_TRY(cudaMemsetAsync(cta_scratch.p, 0, cta_scratch.bytes, stream));
+    }
+    k_partition_count<<<grid, PART_BLOCK, smem, stream>>>(P, Q, (i64*)counts.p, (u32*)cta_scratch.p);
+    CUDA_TRY(cudaGetLastError());
+    device_exclusive_scan((const i64*)counts.p, (int64_t)cells, (i64*)starts.p, stream);
+    k_partition_offsets<<<grid_for(num_parts + 1, 256, 4), 256, 0, stream>>>((const i64*)starts.p, num_parts, grid, (i64*)d_offsets.p);
+    CUDA_TRY(cudaMemcpyAsync(offsets, d_offsets.p, (size_t)(num_parts + 1) * 8, cudaMemcpyDeviceToHost, stream));
+    if (Q.counters_in_global) CUDA_TRY(cudaMemsetAsync(cta_scratch.p, 0, cta_scratch.bytes, stream));
+    k_partition_perm<<<grid, PART_BLOCK, smem, stream>>>(P, Q, (const i64*)starts.p, (u32*)cta_scratch.p, (int*)perm.p);
+    CUDA_TRY(cudaGetLastError());
+    g_stats.kernel_launches += 3;
+
+    // 4. every column gathered by the permutation
+    Scratch null_scratch(8, stream);
+    for (int c = 0; c < num_columns; ++c) {
+      const b2_column_view& in = columns[c];
+      b2_owned_column& oc = out_columns[c];
+      const bool nullable = in.null_mask != nullptr;
+      if (in.type_id != B2_STRING) {
+        init_owned(oc, in.type_id, n, nullable, al, stream);
+        oc.scale = in.scale;
+        oc.null_count = nullable ? in.null_count : 0;
+        const int g = grid_for(n, 256, 16);
+        switch (width_of(in.type_id)) {
+          case 1: k_gather_column<unsigned char><<<g, 256, 0, stream>>>((const unsigned char*)in.data, in.null_mask, in.offset, (const int*)perm.p, n, (unsigned char*)oc.data, oc.null_mask); break;
+          case 2: k_gather_column<unsigned short><<<g, 256, 0, stream>>>((const unsigned short*)in.data, in.null_mask, in.offset, (const int*)perm.p, n, (unsigned short*)oc.data, oc.null_mask); break;
+          case 4: k_gather_column<u32><<<g, 256, 0, stream>>>((const u32*)in.data, in.null_mask, in.offset, (const int*)perm.p, n, (u32*)oc.data, oc.null_mask); break;
+          default: k_gather_column<u64><<<g, 256, 0, stream>>>((const u64*)in.data, in.null_mask, in.offset, (const int*)perm.p, n, (u64*)oc.data, oc.null_mask); break;
+        }
+        CUDA_TRY(cudaGetLastError());
+        g_stats.kernel_launches++;
+        continue;
+      }
+      // STRING: lengths -> offsets by scan -> bytes (any number of STRING columns)
+      oc.type_id = B2_STRING;
+      oc.size = (int32_t)n;
+      oc.null_count = nullable ? in.null_count : 0;
+      if (nullable) {
+        oc.null_mask_bytes = (size_t)std::max<int64_t>(1, (n + 511) / 512) * 64;
+        oc.null_mask = (uint32_t*)out_alloc(al, oc.null_mask_bytes, stream);
+        CUDA_TRY(cudaMemsetAsync(oc.null_mask, 0xFF, oc.null_mask_bytes, stream));
+      }
+      DKeyCol kc{};
+      kc.data = (const unsigned char*)in.data;
+      kc.mask = in.null_mask;
+      kc.offset = in.offset;
+      kc.vclass = VC_STRING;
+      const b2_column_view& o = in.children[0];
+      kc.offsets = (const unsigned char*)o.data + (size_t)o.offset * (o.type_id == B2_INT64 ? 8 : 4);
+      kc.offs64 = o.type_id == B2_INT64;
+      Scratch lens((size_t)(n + 1) * 8, stream), offs((size_t)(n + 1) * 8, stream);
+      CUDA_TRY(cudaMemsetAsync(null_scratch.p, 0, 8, stream));
+      k_string_lengths<<<grid_for(n, 256, 8), 256, 0, stream>>>(kc, (const int*)perm.p, n, (i64*)lens.p, oc.null_mask, (u32*)null_scratch.p);
+      CUDA_TRY(cudaGetLastError());
+      device_exclusive_scan((const i64*)lens.p, n, (i64*)offs.p, stream);
+      i64 total = 0;
+      CUDA_TRY(cudaMemcpyAsync(&total, (i64*)offs.p + n, 8, cudaMemcpyDeviceToHost, stream));
+      CUDA_TRY(cudaStreamSynchronize(stream));
+      const bool big = total > 0x7FFFFFFFll;  // cpp/src/strings/utilities.cu:150-157
+      oc.data_bytes = (size_t)std::max<i64>(total, 1);
       oc.data = out_alloc(al, oc.data_bytes, stream);
       oc.num_children = 1;
       oc.children = (b2_owned_column*)std::calloc(1, sizeof(b2_owned_column));
@@ -1869,21 +1914,13 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
       oc.children[0].size = (int32_t)(n + 1);
       oc.children[0].data_bytes = (size_t)(n + 1) * (big ? 8 : 4);
       oc.children[0].data = out_alloc(al, oc.children[0].data_bytes, stream);
-      Q.cols[str_col].dst = (unsigned char*)oc.data;
-      Q.out_offsets = oc.children[0].data;
-      Q.out_offs64 = big;
-      // the closing offset
-      if (big) { const i64 t = total_chars; CUDA_TRY(cudaMemcpyAsync((i64*)oc.children[0].data + n, &t, 8, cudaMemcpyHostToDevice, stream)); CUDA_TRY(cudaStreamSynchronize(stream)); }
-      else { const int t = (int)total_chars; CUDA_TRY(cudaMemcpyAsync((int*)oc.children[0].data + n, &t, 4, cudaMemcpyHostToDevice, stream)); CUDA_TRY(cudaStreamSynchronize(stream)); }
+      if (big) k_string_copy<i64><<<grid_for(n * 32, 256, 8), 256, 0, stream>>>(kc, (const int*)perm.p, n, (const i64*)offs.p, (i64*)oc.children[0].data, (unsigned char*)oc.data);
+      else k_string_copy<int><<<grid_for(n * 32, 256, 8), 256, 0, stream>>>(kc, (const int*)perm.p, n, (const i64*)offs.p, (int*)oc.children[0].data, (unsigned char*)oc.data);
+      CUDA_TRY(cudaGetLastError());
+      g_stats.kernel_launches += 5;
     }
-    if (n == 0) { guard.armed = false; return; }
-    CUDA_TRY(cudaMemcpyAsync(starts.p, h_starts.data(), cells * sizeof(i64), cudaMemcpyHostToDevice, stream));
-    if (str_col >= 0) CUDA_TRY(cudaMemcpyAsync(char_starts.p, h_cstarts.data(), cells * sizeof(i64), cudaMemcpyHostToDevice, stream));
-    k_partition_scatter<<<grid, PART_BLOCK, Q.counters_in_global ? 0 : (size_t)num_parts * 8, stream>>>(
-      P, Q, (const i64*)starts.p, (const i64*)char_starts.p, (u64*)cursors.p);
-    CUDA_TRY(cudaGetLastError());
     CUDA_TRY(cudaStreamSynchronize(stream));
-    g_stats.kernel_launches += 2;
+    if (offsets[num_parts] != n) B2_FAIL(B2_INTERNAL_ERROR, "hash_partition: row count mismatch");
     guard.armed = false;
   });
 }

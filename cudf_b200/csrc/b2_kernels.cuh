@@ -1388,119 +1388,105 @@ k_merge(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* 
 
 
 // ------------------------------------------------------------------------------ row hash partition
-// cudf::hash_partition for fixed-width tables (cpp/src/partitioning/partitioning.cu:120-337):
-// pass 1 counts rows per (CTA, partition); the host turns the counts into CTA-major start offsets
-// inside each partition; pass 2 recomputes the partition of each row and scatters every column.
+// cudf::hash_partition (cpp/src/partitioning/partitioning.cu:120-337,569-750): partition of a row =
+// row hash % partitions, the hash being the reference's (ref_row_hash: MurmurHash3_x86_32 + hash_combine,
+// or the identity hash).  Three steps: rows per (partition, CTA) -> exclusive scan on the device ->
+// permutation "output position -> input row" -> gather of every column by that permutation (the
+// reference's general path gathers too, :750; its shared-memory fast path is limited to fixed-width
+// tables and 1024 partitions, :253-337).  Rows keep their input order inside a (partition, CTA) run
+// only up to the order of the shared-memory atomics: the order inside a partition is unspecified.
 constexpr int PART_BLOCK    = 512;
 constexpr int MAX_PART_COLS = 32;
 
-struct DPartCol {
-  const unsigned char* src; const u32* mask; i64 offset; int width; int pad;
-  unsigned char* dst; u32* dst_mask;
-};
 struct DPartPlan {
-  int ncols; int nparts;
+  int nparts;
+  int hash_kind;   // RefHash
+  u32 seed;
+  int counters_in_global;  // per-CTA partition counters live in global memory (more partitions than shared memory holds)
   i64 rows_per_cta;
-  // at most one STRING column: chars + offsets in, chars + offsets out (rows and bytes of a partition
-  // keep the same order, so the output offsets are monotone)
-  int str_col;        // index in cols[], -1 = none
-  int str_offs64;     // input offsets are INT64
-  int out_offs64;     // output offsets are INT64
-  int counters_in_global;  // per-CTA partition counters live in global memory (many partitions)
-  const void* str_offsets;
-  void* out_offsets;
-  DPartCol cols[MAX_PART_COLS];
 };
 
-__device__ __forceinline__ u32 row_partition(const DPlan& P, i64 row, u32 nparts)
+__device__ __forceinline__ u32 row_partition(const DPlan& P, const DPartPlan& Q, i64 row)
 {
-  const u64 h = (P.key_mode == KM_PACKED) ? mix64(pack_key(P, row)) : hash_row(P, row);
-  return owner_of(h, nparts);
-}
-__device__ __forceinline__ i64 part_str_offset(const DPartPlan& Q, i64 idx)
-{
-  return Q.str_offs64 ? (i64)__ldg((const i64*)Q.str_offsets + idx) : (i64)__ldg((const int*)Q.str_offsets + idx);
+  const u32 h = ref_row_hash(P, row, Q.hash_kind, Q.seed);
+  return (Q.nparts & (Q.nparts - 1)) == 0 ? (h & (u32)(Q.nparts - 1)) : h % (u32)Q.nparts;
 }
 
+// counts[p * gridDim.x + cta] = rows of this CTA's slice that go to partition p (partition-major, so that
+// one exclusive scan over the array gives every (partition, CTA) run its start)
 __global__ void __launch_bounds__(PART_BLOCK)
-k_partition_count(const __grid_constant__ DPlan P, const __grid_constant__ DPartPlan Q,
-                  u32* __restrict__ cta_counts /* [grid][nparts] */, u64* __restrict__ cta_chars /* [grid][nparts] or null */)
+k_partition_count(const __grid_constant__ DPlan P, const DPartPlan Q, i64* __restrict__ counts, u32* __restrict__ cta_scratch)
 {
-  // per-CTA counters: in shared memory, or — more partitions than shared memory holds
-  // (cpp/tests/partitioning/hash_partition_test.cpp:172-187) — directly in this CTA's zeroed slice
-  // of the global arrays
-  extern __shared__ u64 s_part[];  // [nparts] string bytes, then [nparts] u32 row counts
+  extern __shared__ u32 s_hist[];
   const bool in_global = Q.counters_in_global != 0;
-  u64* s_chars = in_global ? (cta_chars ? cta_chars + (size_t)blockIdx.x * Q.nparts : nullptr) : s_part;
-  u32* s_hist  = in_global ? cta_counts + (size_t)blockIdx.x * Q.nparts : (u32*)(s_part + Q.nparts);
-  if (!in_global) for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) { s_hist[p] = 0; s_chars[p] = 0; }
+  u32* hist = in_global ? cta_scratch + (size_t)blockIdx.x * Q.nparts : s_hist;  // (global slices arrive zeroed)
+  if (!in_global) for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) hist[p] = 0;
   __syncthreads();
   const i64 lo = (i64)blockIdx.x * Q.rows_per_cta;
   const i64 hi = min(P.nrows, lo + Q.rows_per_cta);
-  for (i64 r = lo + threadIdx.x; r < hi; r += blockDim.x) {
-    const u32 p = row_partition(P, r, (u32)Q.nparts);
-    atomicAdd(&s_hist[p], 1u);
-    if (Q.str_col >= 0) {
-      const DPartCol& col = Q.cols[Q.str_col];
-      const i64 idx = col.offset + r;
-      if (!col.mask || bit_valid(col.mask, idx)) {
-        const i64 len = part_str_offset(Q, idx + 1) - part_str_offset(Q, idx);
-        if (len > 0) atomicAdd(&s_chars[p], (u64)len);
-      }
-    }
+  const u32 lane = threadIdx.x & 31u;
+  for (i64 r0 = lo + (threadIdx.x - lane); r0 < hi; r0 += blockDim.x) {
+    const i64 r = r0 + lane;
+    const u32 p = r < hi ? row_partition(P, Q, r) : NO_DEST;
+    // lanes headed for the same partition add once (with few partitions every lane would hit the same words)
+    const u32 peers = __match_any_sync(0xFFFFFFFFu, p);
+    if (p != NO_DEST && (int)lane == __ffs(peers) - 1) atomicAdd(&hist[p], (u32)__popc(peers));
   }
   __syncthreads();
-  if (in_global) return;
-  for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) {
-    cta_counts[(size_t)blockIdx.x * Q.nparts + p] = s_hist[p];
-    if (cta_chars) cta_chars[(size_t)blockIdx.x * Q.nparts + p] = s_chars[p];
-  }
+  for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) counts[(size_t)p * gridDim.x + blockIdx.x] = (i64)hist[p];
 }
 
-__global__ void __launch_bounds__(PART_BLOCK)
-k_partition_scatter(const __grid_constant__ DPlan P, const __grid_constant__ DPartPlan Q,
-                    const i64* __restrict__ cta_starts /* [grid][nparts] */,
-                    const i64* __restrict__ cta_char_starts /* [grid][nparts] or null */,
-                    u64* __restrict__ cta_cursors /* [grid][nparts], zeroed; only with counters_in_global */)
+// offsets[p] = start of partition p (its first (partition, CTA) run), offsets[nparts] = the row count
+__global__ void k_partition_offsets(const i64* __restrict__ starts, int nparts, int grid, i64* __restrict__ offsets)
 {
-  // cursor inside this CTA's share of each partition: rows in the high 24 bits, string bytes in the
-  // low 40 bits, advanced by ONE atomic per row so that rows and bytes keep the same order
-  extern __shared__ u64 s_part[];
+  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p <= nparts; p += gridDim.x * blockDim.x)
+    offsets[p] = starts[(size_t)p * grid];  // (p == nparts reads the scan's closing total)
+}
+
+// perm[output position] = input row
+__global__ void __launch_bounds__(PART_BLOCK)
+k_partition_perm(const __grid_constant__ DPlan P, const DPartPlan Q, const i64* __restrict__ starts, u32* __restrict__ cta_scratch,
+                 int* __restrict__ perm)
+{
+  extern __shared__ u32 s_cur[];
   const bool in_global = Q.counters_in_global != 0;
-  u64* s_cur = in_global ? cta_cursors + (size_t)blockIdx.x * Q.nparts : s_part;
-  if (!in_global) for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) s_cur[p] = 0;
+  u32* cur = in_global ? cta_scratch + (size_t)blockIdx.x * Q.nparts : s_cur;  // (global slices arrive zeroed)
+  if (!in_global) for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) cur[p] = 0;
   __syncthreads();
   const i64 lo = (i64)blockIdx.x * Q.rows_per_cta;
   const i64 hi = min(P.nrows, lo + Q.rows_per_cta);
-  for (i64 r = lo + threadIdx.x; r < hi; r += blockDim.x) {
-    const u32 p = row_partition(P, r, (u32)Q.nparts);
-    i64 len = 0, sbeg = 0;
-    if (Q.str_col >= 0) {
-      const DPartCol& col = Q.cols[Q.str_col];
-      const i64 idx = col.offset + r;
-      if (!col.mask || bit_valid(col.mask, idx)) {
-        sbeg = part_str_offset(Q, idx);
-        len  = part_str_offset(Q, idx + 1) - sbeg;
-      }
+  const u32 lane = threadIdx.x & 31u;
+  for (i64 r0 = lo + (threadIdx.x - lane); r0 < hi; r0 += blockDim.x) {
+    const i64 r = r0 + lane;
+    const u32 p = r < hi ? row_partition(P, Q, r) : NO_DEST;
+    const u32 peers = __match_any_sync(0xFFFFFFFFu, p);
+    const int lead  = __ffs(peers) - 1;
+    u32 base = 0;
+    if (p != NO_DEST && (int)lane == lead) base = atomicAdd(&cur[p], (u32)__popc(peers));
+    base = __shfl_sync(0xFFFFFFFFu, base, lead);
+    if (p != NO_DEST)
+      perm[starts[(size_t)p * gridDim.x + blockIdx.x] + (i64)base + __popc(peers & ((1u << lane) - 1u))] = (int)r;
+  }
+}
+
+// out[i] = src[offset + perm[i]] for a fixed-width column (W bytes per element), validity gathered into whole
+// mask words by ballot
+template <typename T>
+__global__ void k_gather_column(const T* __restrict__ src, const u32* __restrict__ src_mask, i64 src_offset,
+                                const int* __restrict__ perm, i64 n, T* __restrict__ dst, u32* __restrict__ dst_mask)
+{
+  const u32 lane = threadIdx.x & 31u;
+  const i64 nround = (n + 31) / 32 * 32;
+  for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < nround; i += (i64)gridDim.x * blockDim.x) {
+    bool valid = false;
+    if (i < n) {
+      const i64 idx = src_offset + perm[i];
+      dst[i] = src[idx];
+      valid = !src_mask || bit_valid(src_mask, idx);
     }
-    const u64 cur = atomicAdd(&s_cur[p], (1ull << 40) | (u64)len);
-    const i64 dst = cta_starts[(size_t)blockIdx.x * Q.nparts + p] + (i64)(cur >> 40);
-    for (int c = 0; c < Q.ncols; ++c) {
-      const DPartCol& col = Q.cols[c];
-      const i64 idx = col.offset + r;
-      if (c == Q.str_col) {
-        const i64 cdst = cta_char_starts[(size_t)blockIdx.x * Q.nparts + p] + (i64)(cur & ((1ull << 40) - 1));
-        if (Q.out_offs64) ((i64*)Q.out_offsets)[dst] = cdst; else ((int*)Q.out_offsets)[dst] = (int)cdst;
-        for (i64 b = 0; b < len; ++b) col.dst[cdst + b] = col.src[sbeg + b];
-      } else {
-        switch (col.width) {
-          case 1: col.dst[dst] = col.src[idx]; break;
-          case 2: ((unsigned short*)col.dst)[dst] = ((const unsigned short*)col.src)[idx]; break;
-          case 4: ((u32*)col.dst)[dst] = ((const u32*)col.src)[idx]; break;
-          default: ((u64*)col.dst)[dst] = ((const u64*)col.src)[idx]; break;
-        }
-      }
-      if (col.dst_mask && bit_valid(col.mask, idx)) atomicOr(col.dst_mask + (dst >> 5), 1u << (dst & 31));
+    if (dst_mask) {
+      const u32 word = __ballot_sync(0xFFFFFFFFu, valid);
+      if (lane == 0) dst_mask[i >> 5] = word;
     }
   }
 }

@@ -1,7 +1,7 @@
 """``hash_partition``: mirror of ``pylibcudf.partitioning.hash_partition`` /
-``cudf::hash_partition`` (cpp/include/cudf/partitioning.hpp, cpp/src/partitioning/partitioning.cu:950-975)
-for tables of fixed-width columns and at most one STRING column, through the C ABI
-(b2_hash_partition), plus the validity bitmask <-> byte helpers a row exchange needs."""
+``cudf::hash_partition`` (cpp/include/cudf/partitioning.hpp:97-108, cpp/src/partitioning/partitioning.cu:876-975)
+for tables of fixed-width and STRING columns, through the C ABI (b2_hash_partition), plus the
+validity bitmask <-> byte helpers a row exchange needs."""
 from __future__ import annotations
 
 import ctypes as C
@@ -14,14 +14,21 @@ from .column import Column, Table, allocator_for
 from .groupby import _check
 from .types import TypeId
 
+HASH_IDENTITY, HASH_MURMUR3 = 0, 1   # cudf::hash_id (cpp/include/cudf/partitioning.hpp:32-35)
+DEFAULT_HASH_SEED = 0                # cpp/include/cudf/hashing.hpp:29
 
-def hash_partition(table: Table, columns_to_hash, num_partitions: int) -> Tuple[Table, List[int]]:
+
+def hash_partition(table: Table, columns_to_hash, num_partitions: int, hash_function: int = HASH_MURMUR3,
+                   seed: int = DEFAULT_HASH_SEED) -> Tuple[Table, List[int]]:
     """Reorders the rows so that partition p occupies rows [offsets[p], offsets[p+1]).
     ``columns_to_hash`` is the list of column indices whose values decide the partition, like the
-    reference's argument (cpp/include/cudf/partitioning.hpp), or an int k meaning the first k columns.
+    reference's argument (cpp/include/cudf/partitioning.hpp), or an int k meaning the first k columns;
+    ``hash_function`` / ``seed`` as in the reference (MurmurHash3_x86_32 with seed 0 by default), and
+    the partition of every row is the reference's.
     Returns (partitioned table with the input's column order, offsets of num_partitions+1 entries).
-    No columns to hash, no partitions or no columns give an empty table of the same column types
-    (cpp/tests/partitioning/hash_partition_test.cpp:72-142)."""
+    No columns to hash, no partitions, no rows or no columns give an empty table of the same column
+    types (cpp/tests/partitioning/hash_partition_test.cpp:72-142); a column index outside the table
+    raises IndexError (std::out_of_range there, :48-58)."""
     lib = _lib.load()
     cols = table.columns()
     if isinstance(columns_to_hash, int):
@@ -40,8 +47,8 @@ def hash_partition(table: Table, columns_to_hash, num_partitions: int) -> Tuple[
     out = (_lib.OwnedColumn * max(1, len(cols)))()
     offsets = (C.c_int64 * (num_partitions + 1))()
     stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
-    _check(lib.b2_hash_partition(views, len(cols), len(hashed), num_partitions, stream, C.byref(alloc.struct),
-                                 out, offsets))
+    _check(lib.b2_hash_partition(views, len(cols), len(hashed), num_partitions, int(hash_function), int(seed) & 0xFFFFFFFF,
+                                 stream, C.byref(alloc.struct), out, offsets))
     res: List[Column] = [None] * len(cols)  # type: ignore[list-item]
     for j, i in enumerate(order):
         oc = out[j]

@@ -256,21 +256,29 @@ b2_status b2_state_finalize(b2_groupby_state* st, void* stream, const b2_allocat
 void b2_state_destroy(b2_groupby_state* st);
 
 /* ---- row-level hash partition: the multi-GPU pre-step for high-cardinality inputs ---
- * cudf::hash_partition(table, columns_to_hash, num_partitions)
- * (cpp/include/cudf/partitioning.hpp; cpp/src/partitioning/partitioning.cu:950-975):
- * reorders the rows of `columns` (fixed-width columns and at most one STRING column, nullable or
- * not; the first `num_key_columns` are hashed)
- * so that partition p occupies rows [offsets[p], offsets[p+1]).  Output columns come from the
- * allocator; `offsets` is a host array of num_parts+1 entries.  The partition of a key equals
- * the owner used by b2_state_pack.  Up to 2^20 partitions (beyond 4096 the per-CTA counters move
- * from shared to global memory).  num_key_columns == 0, num_parts == 0 or num_columns == 0 give
- * empty columns of the input types and all-zero offsets, like the reference
- * (cpp/tests/partitioning/hash_partition_test.cpp:72-142).  The order of rows inside a partition is
- * unspecified.  Synchronises `stream`. */
+ * cudf::hash_partition(input, columns_to_hash, num_partitions, hash_function, seed)
+ * (cpp/include/cudf/partitioning.hpp:97-108; cpp/src/partitioning/partitioning.cu:876-975):
+ * reorders the rows of `columns` (fixed-width and STRING columns, nullable or not; the first
+ * `num_key_columns` are hashed) so that partition p occupies rows [offsets[p], offsets[p+1]).
+ * The partition of a row is the reference's: row hash % num_parts with
+ *   B2_HASH_MURMUR3  MurmurHash3_x86_32(element bytes, seed) per column, a null element hashing to
+ *                    UINT32_MAX, columns folded left to right with hash_combine
+ *                    (hashing/detail/murmurhash3_x86_32.cuh:22-76, row_operator/hashing.cuh:52-134,
+ *                    hashing/detail/hashing.hpp:83-86; floats: -0 as +0, one NaN);
+ *   B2_HASH_IDENTITY the numeric element cast to uint32 (partitioning.cu:856-874); hashing a
+ *                    non-numeric column is B2_LOGIC_ERROR "IdentityHash does not support this data type".
+ * Output columns come from the allocator; `offsets` is a host array of num_parts+1 entries.  Up to
+ * 2^20 partitions (beyond 4096 the per-CTA counters move from shared to global memory).
+ * num_key_columns == 0, num_parts == 0, num_columns == 0 or zero rows give empty columns of the
+ * input types and all-zero offsets (partitioning.cu:885-888,
+ * cpp/tests/partitioning/hash_partition_test.cpp:72-142); columns of different sizes are
+ * B2_INVALID_ARGUMENT (std::invalid_argument in the reference, :934-937).  The order of rows inside a
+ * partition is unspecified.  Synchronises `stream`. */
+enum { B2_HASH_IDENTITY = 0, B2_HASH_MURMUR3 = 1 };  /* cudf::hash_id, partitioning.hpp:32-35 */
 b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns,
-                            int32_t num_key_columns, int32_t num_parts, void* stream,
-                            const b2_allocator* allocator, b2_owned_column* out_columns,
-                            int64_t* offsets);
+                            int32_t num_key_columns, int32_t num_parts, int32_t hash_function,
+                            uint32_t seed, void* stream, const b2_allocator* allocator,
+                            b2_owned_column* out_columns, int64_t* offsets);
 
 /* Validity bitmask <-> one byte per row (1 = valid).  A row exchange between ranks moves validity
  * as bytes because a partition starts at an arbitrary bit of its mask

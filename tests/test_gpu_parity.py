@@ -351,7 +351,9 @@ def test_results_are_deterministic_for_integers():
 # ------------------------------------------------------------------------------------ partitioned path
 def _partition_inputs(seed, n, domain, nullable_keys=False):
     rng = np.random.default_rng(seed)
-    kv = rng.integers(-1, domain, n).astype(np.int64)          # -1 = the key whose bits equal the empty-slot marker
+    # int64 keys include -1, whose bits equal the empty-slot marker; nullable keys are int32 so that key +
+    # null flag still pack into 64 bits under INCLUDE
+    kv = rng.integers(-1, domain, n).astype(np.int32 if nullable_keys else np.int64)
     k = HostColumn.from_numpy(kv, valid=(rng.random(n) > 0.02) if nullable_keys else None)
     v1 = HostColumn.from_numpy(rng.integers(-10**9, 10**9, n).astype(np.int64))
     v2 = HostColumn.from_numpy(rng.lognormal(0, 1, n), valid=rng.random(n) > 0.05)
@@ -372,6 +374,17 @@ def test_partitioned_path_matches_oracle(table_bytes, policy):
     st = cb.last_call_stats()
     assert st.table_attempts == 1 and not st.used_shared_table      # one partitioned pass, no table fallback
     assert got[0][0].size > 300_000
+
+
+@pytest.mark.parametrize("table_bytes", [0, 16384])
+def test_partitioned_path_int64_keys_with_the_empty_marker_key(table_bytes):
+    import cudf_b200 as cb
+    k, v1, v2, v3 = _partition_inputs(25, 600_000, 400_000)
+    assert (k.values() == -1).any()
+    check([k], [(v1, [Kind.SUM, Kind.MIN, Kind.MAX, Kind.COUNT_VALID]), (v2, [Kind.MEAN, Kind.M2]), (v3, [Kind.SUM, Kind.COUNT_ALL])],
+          table_variant=6, shared_table_bytes=table_bytes)
+    st = cb.last_call_stats()
+    assert st.table_attempts == 1 and not st.used_shared_table
 
 
 def test_partitioned_path_composite_keys_and_row_filters():

@@ -121,3 +121,114 @@ def test_only_the_hashed_columns_decide():  # hash_partition_test.cpp:300-324
     a, b = out1.columns()[0].to_host().values(), out2.columns()[1].to_host().values()
     for p in range(3):  # same keys in every partition (the order inside a partition is unspecified)
         assert sorted(a[off1[p]:off1[p + 1]].tolist()) == sorted(b[off2[p]:off2[p + 1]].tolist())
+
+
+# ------------------------------------------------------------------------------------ against the oracle
+def _comparable(x):
+    """NaN compares unequal to itself: rows are compared through a stand-in."""
+    return "nan" if isinstance(x, float) and x != x else x
+
+
+def _rows_of(cols, lo, hi):
+    """The rows [lo, hi) of host columns as a sorted list of tuples (None = null)."""
+    lists = [[_comparable(x) for x in c.to_pylist()[lo:hi]] for c in cols]
+    return sorted(zip(*lists), key=repr)
+
+
+def _check_against_oracle(cols, hashed, nparts, **kw):
+    """Every partition holds exactly the rows the reference's rule assigns to it (as a multiset: the order
+    inside a partition is unspecified), validity and null counts included."""
+    from cudf_b200.partition import hash_partition
+    from oracle import partition_oracle as PO
+    out, offsets = hash_partition(_table(cols), hashed, nparts, **kw)
+    got = [c.to_host() for c in out.columns()]
+    n = cols[0].size
+    assert len(offsets) == nparts + 1 and offsets[0] == 0 and offsets[-1] == n and offsets == sorted(offsets)
+    part = PO.partition_of_rows([cols[i] for i in hashed], nparts, kw.get("hash_function", PO.HASH_MURMUR3), kw.get("seed", 0))
+    assert np.array_equal(np.diff(offsets), np.bincount(part, minlength=nparts))
+    src = [[_comparable(x) for x in c.to_pylist()] for c in cols]
+    for p in range(nparts):
+        rows = np.flatnonzero(part == p)
+        exp = sorted(zip(*[[l[i] for i in rows] for l in src]), key=repr)
+        assert _rows_of(got, offsets[p], offsets[p + 1]) == exp, f"partition {p}"
+    for g, c in zip(got, cols):
+        assert g.null_count == c.null_count and TypeId(g.type_id) == TypeId(c.type_id)
+    return offsets
+
+
+def _mixed_table(seed, n):
+    rng = np.random.default_rng(seed)
+    words = ["", "a", "año", "日本語", "z" * 37, "ab", "abc", "abcd", "abcde"]
+    return [HostColumn.from_numpy(rng.integers(-500, 500, n).astype(np.int32), valid=rng.random(n) > 0.1),
+            HostColumn.from_strings([None if rng.random() < 0.07 else words[i] + str(i) for i in rng.integers(0, len(words), n)]),
+            HostColumn.from_numpy(rng.choice([0.0, -0.0, np.nan, 1.5, -2.25, np.inf], n)),
+            HostColumn.from_strings([words[i] for i in rng.integers(0, len(words), n)]),
+            HostColumn.from_numpy(rng.integers(0, 3, n).astype(np.uint8), type_id=TypeId.BOOL8),
+            HostColumn.from_numpy(rng.integers(-2**60, 2**60, n).astype(np.int64)),
+            HostColumn.from_numpy(rng.integers(0, 2**16, n).astype(np.uint16)),
+            HostColumn.from_numpy(rng.standard_normal(n).astype(np.float32), valid=rng.random(n) > 0.5)]
+
+
+@pytest.mark.parametrize("nparts", [1, 2, 3, 8, 13, 1000])
+def test_partition_assignment_is_the_references_murmur3(nparts):
+    cols = _mixed_table(1, 3000)
+    _check_against_oracle(cols, [0], nparts)
+    _check_against_oracle(cols, [1, 2], nparts)                       # a nullable STRING and a float column
+    _check_against_oracle(cols, [3, 1, 4, 5, 6, 7, 0, 2], nparts)     # two STRING columns among eight
+
+
+def test_custom_seed_changes_the_assignment_deterministically():  # hash_partition_test.cpp:341-364
+    cols = _mixed_table(2, 2000)
+    a = _check_against_oracle(cols, [2, 3], 7, seed=12345)
+    b = _check_against_oracle(cols, [2, 3], 7, seed=12345)
+    c = _check_against_oracle(cols, [2, 3], 7, seed=0)
+    assert a == b and a != c
+
+
+def test_identity_hash():  # cpp/src/partitioning/partitioning.cu:856-874, hash_partition_test.cpp:326-339
+    import cudf_b200 as cb
+    from cudf_b200.partition import HASH_IDENTITY, hash_partition
+    rng = np.random.default_rng(3)
+    n = 5000
+    cols = [HostColumn.from_numpy(rng.integers(0, 10_000, n).astype(np.int32)),
+            HostColumn.from_numpy(rng.integers(-5, 5, n).astype(np.int64), valid=rng.random(n) > 0.2),
+            HostColumn.from_strings([str(i) for i in range(n)])]
+    off = _check_against_oracle(cols, [0], 10, hash_function=HASH_IDENTITY)
+    out, _ = hash_partition(_table(cols), [0], 10, hash_function=HASH_IDENTITY)
+    v = out.columns()[0].to_host().values()
+    for p in range(10):   # identity: the key itself decides, value % partitions
+        assert (v[off[p]:off[p + 1]] % 10 == p).all()
+    _check_against_oracle(cols, [0, 1], 6, hash_function=HASH_IDENTITY)
+    with pytest.raises(cb.LogicError, match="IdentityHash does not support this data type"):
+        hash_partition(_table(cols), [2], 3, hash_function=HASH_IDENTITY)
+    with pytest.raises(cb.LogicError, match="Unsupported hash function"):
+        hash_partition(_table(cols), [0], 3, hash_function=9)
+
+
+def test_argument_errors():  # hash_partition_test.cpp:48-70
+    import cudf_b200 as cb
+    from cudf_b200.partition import hash_partition
+    cols = _three_columns()
+    with pytest.raises(IndexError):                    # std::out_of_range in the reference
+        hash_partition(_table(cols), [-1], 3)
+    with pytest.raises(IndexError):
+        hash_partition(_table(cols), [3], 3)
+    short = HostColumn.from_numpy(np.arange(1, 10, dtype=np.int16))
+    with pytest.raises(ValueError, match="same number of rows"):   # std::invalid_argument in the reference
+        hash_partition(cb.Table([cb.Column.from_host(cols[0]), cb.Column.from_host(short)]), [1], 3)
+
+
+def test_partition_of_many_rows_matches_the_oracle_counts():
+    """2M rows, 8 destinations (the shape of a row exchange between 8 ranks): counts per partition are the oracle's."""
+    from cudf_b200.partition import hash_partition
+    from oracle import partition_oracle as PO
+    rng = np.random.default_rng(4)
+    n = 2_000_000
+    k = HostColumn.from_numpy(rng.integers(0, 10**12, n).astype(np.int64))
+    v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.01)
+    out, offsets = hash_partition(_table([k, v]), [0], 8)
+    part = PO.partition_of_rows([k], 8)
+    assert np.array_equal(np.diff(offsets), np.bincount(part, minlength=8))
+    got_k = out.columns()[0].to_host().values()
+    for p in range(8):
+        assert np.array_equal(np.sort(got_k[offsets[p]:offsets[p + 1]]), np.sort(k.values()[part == p]))
