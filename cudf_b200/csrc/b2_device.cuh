@@ -131,6 +131,7 @@ struct DCtrl {
   u64 t_phase[5];      // CTA 0 of the fused kernel: %globaltimer at start, after sampling, after the
                        // shared-table init, after the row loop, after the merge (diagnostics)
   DDense dense;
+  u32 null_counts[80];  // finalize: nulls per result column [0, 64) and per key column [64, 80)
 };
 
 // ---------------------------------------------------------------------------------- table addressing

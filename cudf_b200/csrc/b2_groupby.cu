@@ -761,8 +761,11 @@ SharedPlan plan_shared(const b2_groupby_state& st, const b2_groupby& gb)
   return sp;
 }
 
-// one pass of the fused kernel(s) over the bound inputs into st.table
-void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stream, const SharedPlan& sp)
+// One pass of the fused kernel over the bound inputs into st.table.  With `try_lean` the lean kernel
+// runs alone and the function returns true: it declines on the device when the sampled key box did not
+// fit, which the caller sees in the control block it reads anyway (dense.enabled == 0) and answers
+// with a second call without `try_lean`.
+bool run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stream, const SharedPlan& sp, bool try_lean)
 {
   const Schema& sc = st.sc;
   g_stats.used_shared_table = sp.layout != SL_NONE;
@@ -770,7 +773,7 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
   const u32 cap_dense = st.dense_slots > 0 && P.nrows >= SAMPLE_ROWS ? sp.cap_dense : 0;
   EventPair& ev = kernel_events();
   cudaEventRecord(ev.a, stream);
-  const bool lean = sp.lean && cap_dense > 0;
+  const bool lean = try_lean && sp.lean && cap_dense > 0;
   if (lean) {
     bool k8 = false;  // any 8-byte key column?
     for (int k = 0; k < sc.nkeys; ++k) k8 = k8 || sc.key_width[k] == 8;
@@ -789,9 +792,12 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
       default: if (k8) B2_LEAN(3, true); else B2_LEAN(3, false); break;
     }
 #undef B2_LEAN
+    cudaEventRecord(ev.b, stream);
+    st.ctrl_fresh = false;
+    return true;
   }
   if (sc.key_mode == KM_PACKED) {
-    if (sp.layout == SL_F32MEAN) launch_aggregate<KM_PACKED, SL_F32MEAN>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream, cap_dense, (u32)st.dense_slots, lean);
+    if (sp.layout == SL_F32MEAN) launch_aggregate<KM_PACKED, SL_F32MEAN>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream, cap_dense, (u32)st.dense_slots, 0);
     else if (sp.layout == SL_GENERIC) launch_aggregate<KM_PACKED, SL_GENERIC>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream, cap_dense, (u32)st.dense_slots);
     else launch_aggregate<KM_PACKED, SL_NONE>(P, st.table, st.cap, st.ctrl, 0, 0, 0, stream);
   } else {
@@ -800,6 +806,7 @@ void run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
   }
   cudaEventRecord(ev.b, stream);
   st.ctrl_fresh = false;
+  return false;
 }
 
 int64_t hll_estimate(const u32* regs);
@@ -1053,9 +1060,17 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
     const SharedPlan sp = plan_shared(st, gb);
     alloc_table(st, cap, cap >= full ? 1.0 : MAX_LOAD, stream, gb.table_variant != 1 && gb.table_variant != 3, sp.cap_dense);
     trace.mark("table allocation + init");
-    run_aggregate(st, gb, stream, sp);
+    const bool lean_ran = run_aggregate(st, gb, stream, sp, true);
     read_ctrl(st, stream);
     if (st.host_ctrl.error) B2_FAIL(B2_INTERNAL_ERROR, "a bounded wait inside the fused aggregate kernel ran out");
+    if (lean_ran && !st.host_ctrl.dense.enabled) {
+      // the key box did not fit the lean kernel's table: it did nothing; the generic kernel takes the input
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, kernel_events().a, kernel_events().b) == cudaSuccess) g_stats.aggregate_kernel_ms += ms;
+      else cudaGetLastError();
+      run_aggregate(st, gb, stream, sp, false);
+      read_ctrl(st, stream);
+    }
     {
       float ms = 0.f;
       if (cudaEventElapsedTime(&ms, kernel_events().a, kernel_events().b) == cudaSuccess) g_stats.aggregate_kernel_ms += ms;
@@ -1271,9 +1286,13 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
     plan->kdata[k] = c.data;
     plan->kmask[k] = c.null_mask;
   }
-  Scratch null_counts((MAX_OUTS + MAX_KEYS) * sizeof(u32), stream);
-  CUDA_TRY(cudaMemsetAsync(null_counts.p, 0, null_counts.bytes, stream));
-  plan->null_counts = (u32*)null_counts.p;
+  // the null counters live in the control block (a state without a table or group list has no groups)
+  static_assert(sizeof(DCtrl::null_counts) == (MAX_OUTS + MAX_KEYS) * sizeof(u32), "null counters of the control block");
+  if (G > 0) {
+    if (!st.ctrl) B2_FAIL(B2_INTERNAL_ERROR, "groups without a control block");
+    CUDA_TRY(cudaMemsetAsync(st.ctrl->null_counts, 0, sizeof(DCtrl::null_counts), stream));
+    plan->null_counts = st.ctrl->null_counts;
+  }
   if (sc.key_mode == KM_ROWS) {
     rep_rows = Scratch(std::max<size_t>(8, (size_t)G * sizeof(int)), stream);
     plan->rep_rows = (int*)rep_rows.p;
@@ -1340,7 +1359,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
         g_stats.kernel_launches += 3;
       }
     }
-    CUDA_TRY(cudaMemcpyAsync(h_nulls.data(), null_counts.p, null_counts.bytes, cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaMemcpyAsync(h_nulls.data(), st.ctrl->null_counts, sizeof(DCtrl::null_counts), cudaMemcpyDeviceToHost, stream));
     CUDA_TRY(cudaStreamSynchronize(stream));
     trace.mark("finalize: key gather + nulls");
   } else {
@@ -2031,7 +2050,6 @@ struct b2_comm {
   ncclComm_t comm = nullptr;
   int rank = 0, nranks = 1;
   bool owned = false;
-  bool chunks_overflowed = false;  // the fixed-size exchange overflowed before (every rank saw the same flag)
 };
 
 namespace {
@@ -2074,11 +2092,14 @@ void aggregate_multi(b2_comm& c, b2_groupby& gb, const b2_aggregation_request* r
     cudaGetLastError();
   }
 
-  // ---- small states: fixed-size chunks, no host round trip before the exchange
-  if (!c.chunks_overflowed && chunk_bytes * W <= MULTI_CHUNK_LIMIT) {
+  // ---- small states: fixed-size chunks, no host round trip before the exchange.  Every rank takes
+  // this branch or none does (the condition depends on the schema and the rank count only); a rank
+  // whose groups cannot fit whatever their split sends marked chunks without packing anything.
+  if (chunk_bytes * W <= MULTI_CHUNK_LIMIT) {
     Scratch send((size_t)chunk_bytes * W, stream), recv((size_t)chunk_bytes * W, stream);
-    if (failed) {
-      const u64 head[2] = {0, CHUNK_MARK_FAILED};
+    const bool hopeless = !failed && local->table && local->ctrl_fresh && num_groups(*local) > (int64_t)W * MULTI_CHUNK_RECORDS;
+    if (failed || hopeless) {
+      const u64 head[2] = {0, failed ? CHUNK_MARK_FAILED : CHUNK_MARK_OVERFLOW};
       for (int r = 0; r < W; ++r)
         CUDA_TRY(cudaMemcpyAsync((u64*)send.p + (size_t)r * chunk_words, head, 16, cudaMemcpyHostToDevice, stream));
       CUDA_TRY(cudaStreamSynchronize(stream));  // `head` is a stack object
@@ -2094,11 +2115,11 @@ void aggregate_multi(b2_comm& c, b2_groupby& gb, const b2_aggregation_request* r
     rethrow(b2_state_merge_chunks(merged.get(), recv.p, W, MULTI_CHUNK_RECORDS, stream));
     read_ctrl(*merged, stream);
     if (merged->host_ctrl.chunk_overflow >= CHUNK_MARK_FAILED) B2_FAIL(B2_INTERNAL_ERROR, "the local aggregate failed on another rank");
-    if (!merged->host_ctrl.chunk_overflow) {
+    if (merged->host_ctrl.chunk_overflow < CHUNK_MARK_OVERFLOW) {
       finalize_state(*merged, stream, allocator, out);
       return;
     }
-    c.chunks_overflowed = true;  // every rank read a marked chunk: all of them come here
+    // every rank read a marked chunk: all of them go on to the exact-size exchange
   }
 
   // ---- exact sizes: count matrix (with a status word per rank) by all-gather, then variable send / recv

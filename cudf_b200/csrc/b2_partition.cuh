@@ -432,13 +432,14 @@ __global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_cons
           if (one_col) vals[j] = __ldg(B.src.rec + B.src.cap + i);
         }
       }
+      // slots of the batch's records
+      int slots[RPA_BATCH];
 #pragma unroll
       for (int j = 0; j < RPA_BATCH; ++j) {
         const i64 i = base + (i64)j * blockDim.x + threadIdx.x;
-        const bool live = i < hi;
         const u64 key = keys[j];
         int slot = -1;
-        if (live) {
+        if (i < hi) {
           if (key == EMPTY) {
             slot = S;
             s_special = 1;
@@ -457,24 +458,47 @@ __global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_cons
           }
           if (slot < 0) s_fail = 1;
         }
-        // the lanes left the probe loop at different iterations: bring them back together, then every
-        // accumulator is ONE predicated atomic for the whole warp (diverged, each lane's atomics were
-        // issued on their own: 11.5 of 32 lanes active on average, 2.8x the instructions)
-        __syncwarp();
-        int cur = one_col ? 0 : -1;
-        u64 v = vals[j];
-        for (int c = 0; c < P.ncells; ++c) {
-          const int op = P.cells[c].op, col = P.cells[c].col;
-          bool doit = slot >= 0;
-          if (op != OP_CNT_A) {
-            doit = doit && ((vbits[j] >> col) & 1ull);
-            if (col != cur) {  // (uniform: the cells of a value column are adjacent)
-              cur = col;
-              v = live ? __ldg(B.src.rec + (i64)(1 + col) * B.src.cap + i) : 0ull;
-            }
+        slots[j] = slot;
+      }
+      // The lanes left the probe loops at different iterations: bring them back together, then go
+      // through the accumulators cell by cell — the operator is decoded once per cell and batch (not
+      // once per record), and each update is ONE predicated atomic for the whole warp.  (Diverged,
+      // each lane's atomics were issued on their own: 11.5 of 32 lanes active on average.)
+      __syncwarp();
+      int cur = one_col ? 0 : -1;
+      for (int c = 0; c < P.ncells; ++c) {
+        const int op = P.cells[c].op, col = P.cells[c].col;
+        if (op != OP_CNT_A && col != cur) {  // (the cells of a value column are adjacent)
+          cur = col;
+#pragma unroll
+          for (int j = 0; j < RPA_BATCH; ++j) {
+            const i64 i = base + (i64)j * blockDim.x + threadIdx.x;
+            vals[j] = i < hi ? __ldg(B.src.rec + (i64)(1 + col) * B.src.cap + i) : 0ull;
           }
-          if (doit) cell_update(scells + (size_t)c * NS + slot, op, v);
         }
+        u64* cell = scells + (size_t)c * NS;
+        u32 ok = 0;  // records of the batch that update this cell
+#pragma unroll
+        for (int j = 0; j < RPA_BATCH; ++j)
+          if (slots[j] >= 0 && (op == OP_CNT_A || ((vbits[j] >> col) & 1ull))) ok |= 1u << j;
+#define B2_RPA_APPLY(EXPR)                                                        \
+        _Pragma("unroll") for (int j = 0; j < RPA_BATCH; ++j)                     \
+          if ((ok >> j) & 1u) { u64* p = cell + slots[j]; const u64 v = vals[j]; EXPR; }
+        switch (op) {
+          case OP_SUM_I: B2_RPA_APPLY(atomicAdd(p, v)) break;
+          case OP_CNT_V: case OP_CNT_A: B2_RPA_APPLY((void)v; atomicAdd(p, 1ull)) break;
+          case OP_SUM_F: B2_RPA_APPLY(atomicAdd((double*)p, __longlong_as_double((i64)v))) break;
+          case OP_SSQ_I: B2_RPA_APPLY(atomicAdd(p, v * v)) break;
+          case OP_SSQ_F: B2_RPA_APPLY(const double d = __longlong_as_double((i64)v); atomicAdd((double*)p, d * d)) break;
+          case OP_MIN_I: B2_RPA_APPLY(atomicMin((i64*)p, (i64)v)) break;
+          case OP_MAX_I: B2_RPA_APPLY(atomicMax((i64*)p, (i64)v)) break;
+          case OP_MIN_U: B2_RPA_APPLY(atomicMin(p, v)) break;
+          case OP_MAX_U: B2_RPA_APPLY(atomicMax(p, v)) break;
+          case OP_MIN_F: B2_RPA_APPLY(atomicMin(p, f64_ordered(v))) break;
+          case OP_MAX_F: B2_RPA_APPLY(atomicMax(p, f64_ordered(v))) break;
+          default: B2_RPA_APPLY(cell_update(p, op, v)) break;  // products: compare-and-swap loops
+        }
+#undef B2_RPA_APPLY
       }
     }
     __syncthreads();

@@ -68,12 +68,12 @@ def test_one_rank_native_plan_small_states_travel_as_chunks(comm):
 
 
 def test_one_rank_native_plan_falls_back_to_exact_sizes(comm):
-    # ~59K groups: more than the 16384 records a chunk holds; the comm remembers the overflow afterwards
+    # ~59K groups: more than the 16384 records a chunk holds
     w = workloads.make(3, 300_000, scale_domain=True)
     got = _check_against_oracle(comm, w)
     assert got[0][0].size > 16384
     _check_against_oracle(comm, workloads.make(4, 300_000, scale_domain=True))
-    _check_against_oracle(comm, workloads.make(2, 100_000))   # small again, now through the exact-size form
+    _check_against_oracle(comm, workloads.make(2, 100_000))   # small again: back to chunks
 
 
 def test_row_keyed_requests_are_refused_before_any_communication(comm):
