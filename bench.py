@@ -376,6 +376,26 @@ def run_other_configs(peak, which=(1, 5, 3, 4)):
                               "GBps_kernel": alg / (k / 1e3) / 1e9 if k > 0 else None,
                               "frac": alg / (k / 1e3) / 1e9 / peak if k > 0 else None,
                               "calls": 5, "data": "generated on the device, seeded"}
+            if cfg == 3:
+                # cudf::hash_partition of the same rows into 8 destinations (the pre-step of a row exchange
+                # between 8 ranks): reads the table twice (hash pass, gather), writes it once
+                try:
+                    from cudf_b200.partition import hash_partition
+                    table = cb.Table(w.keys + [v for v, _ in w.requests])
+                    pres = {}
+
+                    def part():
+                        pres["out"] = hash_partition(table, [0], 8)
+                    part()
+                    pms = statistics.median(time_calls(part, 5, torch.cuda.synchronize))
+                    tbytes = w.input_bytes
+                    out["hash_partition_C3_rows_8_parts"] = {
+                        "rows": w.rows, "partitions": 8, "ms_per_call": pms, "table_bytes": tbytes,
+                        "GBps_3x_table_bytes": 3 * tbytes / (pms / 1e3) / 1e9, "frac": 3 * tbytes / (pms / 1e3) / 1e9 / peak,
+                        "rows_per_partition_min_max": [int(min(np.diff(pres["out"][1]))), int(max(np.diff(pres["out"][1])))]}
+                    del pres, table
+                except Exception as e:
+                    out["hash_partition_C3_rows_8_parts"] = {"error": f"{type(e).__name__}: {e}"}
             del w, reqs, keys, res
         except Exception as e:  # one configuration must not take the headline line down
             out[f"C{cfg}"] = {"error": f"{type(e).__name__}: {e}"}
@@ -469,7 +489,7 @@ def run_b2(args):
 
     def step_resident():
         if world == 1:
-            gb = cb.GroupBy(keys, w.null_policy, row_filters=filt)
+            gb = cb.GroupBy(keys, w.null_policy, row_filters=filt, table_variant=args.table_variant)
         elif args.reuse_groupby and kept:
             gb = kept[0]
         else:
@@ -666,6 +686,8 @@ def main():
     ap.add_argument("--reuse-groupby", action="store_true",
                     help="N > 1: keep one DistributedGroupBy across the steps instead of a fresh one per step")
     ap.add_argument("--c4-reuse-too", action="store_true", help="N > 1: also report c4_strong with a reused object")
+    ap.add_argument("--table-variant", type=int, default=0,
+                    help="N = 1: the engine's table_variant option for the resident steps (0 = auto; see include/b2_groupby.h)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the full-size C1/C3/C4/C5 block (N = 1)")
     ap.add_argument("--no-c4", action="store_true", help="skip the c4_strong block")

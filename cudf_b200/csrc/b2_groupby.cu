@@ -1696,16 +1696,13 @@ b2_status b2_state_pack_chunks(b2_groupby_state* st, int32_t num_parts, int64_t 
         CUDA_TRY(cudaMemsetAsync((u64*)out + p * chunk_words, 0, 16, stream));
       return;
     }
-    Scratch dcounts((size_t)num_parts * 2 * sizeof(u64), stream);
-    CUDA_TRY(cudaMemsetAsync(dcounts.p, 0, dcounts.bytes, stream));
-    u64* d_counts = (u64*)dcounts.p;
+    Scratch cursors((size_t)(num_parts + 1) * sizeof(u64), stream);  // per destination + the ticket of the last CTA
+    CUDA_TRY(cudaMemsetAsync(cursors.p, 0, cursors.bytes, stream));
     const int grid = grid_for(st->cap + 1 + st->dense_slots, 256, 8);
-    k_pack_count<<<grid, 256, (size_t)num_parts * sizeof(u64), stream>>>(st->table, st->cap, st->plan.stride, num_parts,
-                                                                           st->ctrl, d_counts);
-    k_pack_chunks<<<grid, 256, 0, stream>>>(st->table, st->cap, st->plan.stride, num_parts, st->ctrl, d_counts,
-                                            d_counts + num_parts, (u64*)out, chunk_records);
+    k_pack_chunks<<<grid, 256, 0, stream>>>(st->table, st->cap, st->plan.stride, num_parts, st->ctrl, (u64*)cursors.p,
+                                            (u64*)out, chunk_records);
     CUDA_TRY(cudaGetLastError());
-    g_stats.kernel_launches += 2;
+    g_stats.kernel_launches += 1;
   });
 }
 

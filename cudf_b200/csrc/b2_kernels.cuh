@@ -1292,36 +1292,52 @@ __device__ __forceinline__ i64 table_slot_packed(const DPlan& P, u64* tbl, i64 c
   return gmem_find_insert_packed(tbl, cap, stride, key, mix64(key), ctrl, s_new);
 }
 
-// fixed-size chunks: chunk d = { count, overflow, records[chunk_records] }
-__global__ void k_pack_chunks(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, const DCtrl* ctrl,
-                              const u64* __restrict__ counts, u64* __restrict__ cursors /* zeroed */,
-                              u64* __restrict__ out, i64 chunk_records)
+// fixed-size chunks: chunk d = { count, overflow, records[chunk_records] }.  One launch: every occupied
+// slot takes the next position of its destination's chunk (records beyond the chunk's capacity are not
+// written); the last CTA to finish writes the headers — the counts, or, when any destination
+// overflowed, the overflow mark in EVERY chunk, so that every receiver learns of it.
+// `cursors` ([nparts] counters + one ticket word) must arrive zeroed.
+__global__ void __launch_bounds__(256)
+k_pack_chunks(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, const DCtrl* ctrl, u64* __restrict__ cursors,
+              u64* __restrict__ out, i64 chunk_records)
 {
+  __shared__ int s_last;
+  const i64 chunk_words = 2 + chunk_records * stride;
+  const i64 last = cap + (i64)ctrl->dense_slots;
+  const u32 lane = threadIdx.x & 31u;
+  for (i64 s0 = (i64)blockIdx.x * blockDim.x + (threadIdx.x - lane); s0 <= last; s0 += (i64)gridDim.x * blockDim.x) {
+    const i64 s = s0 + lane;
+    u32 dest = NO_DEST;
+    u64 key = 0;
+    SlotRef src{nullptr, nullptr, 0};
+    if (s <= last) {
+      src = slot_ref(const_cast<u64*>(tbl), cap, stride, last - cap, s);
+      key = s != cap ? *src.key : EMPTY;
+      const bool occ = s != cap ? key != EMPTY : ctrl->special_used != 0;
+      if (occ) dest = owner_of(mix64(key), (u32)nparts);
+    }
+    const u64 pos = warp_add_by_dest(cursors, dest);  // lanes of one destination reserve together
+    if (dest == NO_DEST || pos >= (u64)chunk_records) continue;
+    u64* dst = out + (i64)dest * chunk_words + 2 + (i64)pos * stride;
+    dst[0] = key;
+    for (int c = 1; c < stride; ++c) dst[c] = src.cells[(i64)(c - 1) * src.step];
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&cursors[nparts], 1ull) == (u64)gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
   __shared__ int s_over;
   if (threadIdx.x == 0) s_over = 0;
   __syncthreads();
   for (int p = threadIdx.x; p < nparts; p += blockDim.x)
-    if (counts[p] > (u64)chunk_records) s_over = 1;
+    if (__ldcg(&cursors[p]) > (u64)chunk_records) s_over = 1;
   __syncthreads();
   const bool over = s_over != 0;
-  const i64 chunk_words = 2 + chunk_records * stride;
-  if (blockIdx.x == 0)
-    for (int p = threadIdx.x; p < nparts; p += blockDim.x) {
-      out[p * chunk_words]     = over ? 0ull : counts[p];
-      out[p * chunk_words + 1] = over ? 1ull : 0ull;
-    }
-  if (over) return;
-  const i64 last = cap + (i64)ctrl->dense_slots;
-  for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s <= last; s += (i64)gridDim.x * blockDim.x) {
-    const SlotRef src = slot_ref(const_cast<u64*>(tbl), cap, stride, last - cap, s);
-    const u64 key = s != cap ? *src.key : EMPTY;
-    const bool occ = s != cap ? key != EMPTY : ctrl->special_used != 0;
-    if (!occ) continue;
-    const u32 p   = owner_of(mix64(key), (u32)nparts);
-    const u64 pos = atomicAdd(&cursors[p], 1ull);
-    u64* dst = out + p * chunk_words + 2 + pos * stride;
-    dst[0] = key;
-    for (int c = 1; c < stride; ++c) dst[c] = src.cells[(i64)(c - 1) * src.step];
+  for (int p = threadIdx.x; p < nparts; p += blockDim.x) {
+    out[(i64)p * chunk_words]     = over ? 0ull : __ldcg(&cursors[p]);
+    out[(i64)p * chunk_words + 1] = over ? 1ull : 0ull;
   }
 }
 

@@ -46,12 +46,15 @@ for config, strategy, n, python_exchange in ((2, "partials", 200_000, False), (2
     again = ([c.to_host() for c in okeys2.columns()], [[c.to_host() for c in t.columns()] for t in ores2])
     o1, o2 = H.sort_order(mine[0]), H.sort_order(again[0])
     H.assert_keys_equal(again[0], mine[0], o2, o1)
-    for t1, t2 in zip(mine[1], again[1]):
+    for (v, _), t1, t2 in zip(w.requests, mine[1], again[1]):
+        # the order of the atomic additions differs between two runs: fp32 sources are summed in short fp32
+        # partial sums (a few ulps of fp32 apart), everything else in fp64
+        rt = 1e-5 if v.type_id == TypeId.FLOAT32 else 1e-9
         for c1, c2 in zip(t1, t2):
             assert np.array_equal(c1.valid()[o1], c2.valid()[o2])
             a, b = c1.values()[o1][c1.valid()[o1]], c2.values()[o2][c2.valid()[o2]]
-            if a.dtype.kind == "f":   # the order of the atomic additions differs between two runs
-                assert np.allclose(a, b, rtol=1e-9, atol=1e-9 * (np.abs(a).max() if a.size else 1.0), equal_nan=True)
+            if a.dtype.kind == "f":
+                assert np.allclose(a, b, rtol=rt, atol=rt * (np.abs(a).max() if a.size else 1.0), equal_nan=True)
             else:
                 assert np.array_equal(a, b)
     gathered = [None] * world
@@ -94,3 +97,7 @@ def test_two_rank_distributed_groupby_matches_oracle(tmp_path):
                          capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert out.stdout.count("OK") == 8
+    log_dir = os.path.join(ROOT, "gpurun_out")   # keep rank 0's summary lines beside the other run logs
+    if os.path.isdir(log_dir):
+        with open(os.path.join(log_dir, "two_rank_worker.log"), "w", encoding="utf-8") as f:
+            f.write("".join(ln + "\n" for ln in out.stdout.splitlines() if ln.endswith("OK")))
