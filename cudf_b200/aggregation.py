@@ -54,6 +54,16 @@ def std(ddof: int = 1) -> Aggregation:
     return Aggregation(Kind.STD, ddof)
 
 
+def argmax() -> Aggregation:
+    """Row index of the largest valid value of every group (the first such row on ties)."""
+    return Aggregation(Kind.ARGMAX)
+
+
+def argmin() -> Aggregation:
+    """Row index of the smallest valid value of every group (the first such row on ties)."""
+    return Aggregation(Kind.ARGMIN)
+
+
 def median() -> Aggregation:
     """Served by the reference's sort path only; this engine reports it as unsupported."""
     return Aggregation(Kind.MEDIAN)

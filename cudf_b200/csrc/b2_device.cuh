@@ -47,8 +47,14 @@ enum ValClass : int {
 // cpp/src/groupby/hash/extract_single_pass_aggs.cpp:63-109
 enum CellOp : int {
   OP_SUM_I = 0, OP_SUM_F, OP_SSQ_I, OP_SSQ_F, OP_MIN_I, OP_MIN_U, OP_MIN_F, OP_MAX_I, OP_MAX_U,
-  OP_MAX_F, OP_CNT_V, OP_CNT_A, OP_PROD_I, OP_PROD_F
+  OP_MAX_F, OP_CNT_V, OP_CNT_A, OP_PROD_I, OP_PROD_F,
+  // the cell holds the ROW of the smallest / largest value seen so far (all-ones = none yet): ARGMIN /
+  // ARGMAX themselves, and MIN / MAX of STRING values, which the reference computes as ARGMIN / ARGMAX
+  // followed by a gather (cpp/src/groupby/hash/extract_single_pass_aggs.cpp:39-60)
+  OP_ARGMIN, OP_ARGMAX
 };
+__host__ __device__ __forceinline__ bool is_arg_op(int op) { return op == OP_ARGMIN || op == OP_ARGMAX; }
+constexpr unsigned long long ARG_NONE = 0xFFFFFFFFFFFFFFFFull;
 
 struct DKeyCol {
   const unsigned char* data;
@@ -66,9 +72,10 @@ struct DKeyCol {
 struct DValCol {
   const unsigned char* data;
   const u32* mask;
+  const void* offsets;  // STRING values (MIN / MAX / ARGMIN / ARGMAX of strings): the offsets child
   i64 offset;
   int vclass;
-  int pad;
+  int offs64;           // ... typed INT64
 };
 
 struct DCell {
@@ -445,6 +452,7 @@ __host__ __device__ __forceinline__ u64 cell_identity(int op)
     case OP_MAX_I: return 0x8000000000000000ull;
     case OP_PROD_I: return 1ull;
     case OP_PROD_F: return 0x3FF0000000000000ull;  // 1.0
+    case OP_ARGMIN: case OP_ARGMAX: return ARG_NONE;
     default: return 0ull;                          // sums, counts, MAX_U, MAX_F
   }
 }
@@ -480,6 +488,56 @@ __device__ __forceinline__ void cell_update(u64* cell, int op, u64 v)
       break;
     }
     default: break;
+  }
+}
+
+// ---- ARGMIN / ARGMAX cells: row of the extreme value -------------------------------------------------
+// value at row a <, ==, > value at row b of one value column: -1, 0, +1; 2 when a NaN makes them
+// unordered.  Strings compare byte-wise, the shorter one first when one is a prefix of the other
+// (cpp/include/cudf/strings/string_view.cuh:306-321: UTF-8 byte order is code point order).
+__device__ inline int value_compare(const DValCol& c, i64 a, i64 b)
+{
+  const i64 ia = c.offset + a, ib = c.offset + b;
+  if (c.vclass == VC_STRING) {
+    const i64 ba = c.offs64 ? __ldg((const i64*)c.offsets + ia) : (i64)__ldg((const int*)c.offsets + ia);
+    const i64 ea = c.offs64 ? __ldg((const i64*)c.offsets + ia + 1) : (i64)__ldg((const int*)c.offsets + ia + 1);
+    const i64 bb = c.offs64 ? __ldg((const i64*)c.offsets + ib) : (i64)__ldg((const int*)c.offsets + ib);
+    const i64 eb = c.offs64 ? __ldg((const i64*)c.offsets + ib + 1) : (i64)__ldg((const int*)c.offsets + ib + 1);
+    const i64 la = ea - ba, lb = eb - bb, n = la < lb ? la : lb;
+    for (i64 i = 0; i < n; ++i) {
+      const unsigned char x = c.data[ba + i], y = c.data[bb + i];
+      if (x != y) return x < y ? -1 : 1;
+    }
+    return la < lb ? -1 : (la > lb ? 1 : 0);
+  }
+  const u64 x = load_value(c, a), y = load_value(c, b);
+  if (c.vclass == VC_F32 || c.vclass == VC_F64) {
+    const double dx = __longlong_as_double((i64)x), dy = __longlong_as_double((i64)y);
+    if (dx != dx || dy != dy) return 2;
+    return dx < dy ? -1 : (dx > dy ? 1 : 0);
+  }
+  if (c.vclass == VC_U64) return x < y ? -1 : (x > y ? 1 : 0);
+  return (i64)x < (i64)y ? -1 : ((i64)x > (i64)y ? 1 : 0);
+}
+
+// Folds row `row` into an ARGMIN / ARGMAX cell: the row replaces the cell's row when its value is
+// strictly better, or equal with a smaller row index — so the result is the FIRST row holding the
+// extreme value whatever the order of arrival (the reference keeps whichever equal value arrived first,
+// cpp/include/cudf/detail/aggregation/device_aggregators.cuh:222-263; its tests use distinct values).
+// A NaN never replaces anything and is never replaced by a smaller / larger number that arrives later
+// only if it arrived first — the comparisons with NaN are false, as in the reference.
+__device__ inline void arg_update(u64* cell, int op, const DValCol& c, i64 row)
+{
+  u64 old = *(volatile u64*)cell;
+  for (;;) {
+    if (old != ARG_NONE) {
+      const int cmp = value_compare(c, row, (i64)old);
+      const bool better = op == OP_ARGMIN ? cmp == -1 : cmp == 1;
+      if (!(better || (cmp == 0 && (u64)row < old))) return;
+    }
+    const u64 prev = atomicCAS(cell, old, (u64)row);
+    if (prev == old) return;
+    old = prev;
   }
 }
 

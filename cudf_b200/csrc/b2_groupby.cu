@@ -188,7 +188,7 @@ int vclass_of(int t)
 int result_type(int src, int kind)
 {
   switch (kind) {
-    case B2_AGG_COUNT_VALID: case B2_AGG_COUNT_ALL: return B2_INT32;
+    case B2_AGG_COUNT_VALID: case B2_AGG_COUNT_ALL: case B2_AGG_ARGMAX: case B2_AGG_ARGMIN: return B2_INT32;
     case B2_AGG_MIN: case B2_AGG_MAX: return src;
     case B2_AGG_SUM: return (is_float_t(src) || is_duration_t(src) || is_decimal_t(src)) ? src : B2_INT64;  // decimals keep type and scale
     case B2_AGG_SUM_OF_SQUARES: case B2_AGG_PRODUCT: return is_float_t(src) ? src : B2_INT64;
@@ -203,10 +203,11 @@ int classify_request(int src, int kind)
 {
   switch (kind) {
     case B2_AGG_COUNT_VALID: case B2_AGG_COUNT_ALL: return 0;
-    case B2_AGG_MIN: case B2_AGG_MAX:
-      if (is_numeric_t(src) || is_timestamp_t(src) || is_duration_t(src) || is_decimal_t(src)) return 0;
-      if (src == B2_STRING || src == B2_DECIMAL128 || src == B2_DICTIONARY32 || src == B2_STRUCT || src == B2_LIST)
-        return 2;
+    case B2_AGG_MIN: case B2_AGG_MAX: case B2_AGG_ARGMAX: case B2_AGG_ARGMIN:
+      // MIN / MAX of strings run as ARGMIN / ARGMAX + gather, like the reference's
+      // (cpp/src/groupby/hash/extract_single_pass_aggs.cpp:39-60, hash_compound_agg_finalizer.cu:39-76)
+      if (is_numeric_t(src) || is_timestamp_t(src) || is_duration_t(src) || is_decimal_t(src) || src == B2_STRING) return 0;
+      if (src == B2_DECIMAL128 || src == B2_DICTIONARY32 || src == B2_STRUCT || src == B2_LIST) return 2;
       return 1;
     case B2_AGG_SUM:
       // decimal SUM / MIN / MAX run on the hash path of the reference too
@@ -290,6 +291,9 @@ struct Schema {  // everything that is fixed by (key types, requests): cells and
   std::vector<int> req_nouts;
   std::vector<int> req_val;  // request → value column slot
   bool f32mean = false;      // cells == {Σ of a FLOAT32 column, n of it}: compact shared-memory layout
+  bool has_arg = false;      // some cell holds a row index (ARGMIN / ARGMAX, MIN / MAX of strings): such cells
+                             // live in the global table of ONE aggregate call only (no shared-memory copies,
+                             // no partial records: a row index means nothing outside its batch)
 };
 
 }  // namespace
@@ -379,7 +383,8 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
   // value columns: identical views share one slot
   struct VKey { const void* d; const void* m; int off, type; };
   std::vector<VKey> seen;
-  struct Need { bool sum = false, cnt = false, ssq = false, mn = false, mx = false, prod = false, nulls = false; };
+  struct Need { bool sum = false, cnt = false, ssq = false, mn = false, mx = false, prod = false, nulls = false,
+                amin = false, amax = false; };
   std::vector<Need> need;
   sc.req_val.resize((size_t)nreqs);
   bool need_cnt_all = false;
@@ -405,8 +410,10 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
         case B2_AGG_SUM: nd.sum = true; break;
         case B2_AGG_COUNT_VALID: nd.cnt = true; break;
         case B2_AGG_COUNT_ALL: need_cnt_all = true; break;
-        case B2_AGG_MIN: nd.mn = true; break;
-        case B2_AGG_MAX: nd.mx = true; break;
+        case B2_AGG_MIN: if (v.type_id == B2_STRING) nd.amin = true; else nd.mn = true; break;
+        case B2_AGG_MAX: if (v.type_id == B2_STRING) nd.amax = true; else nd.mx = true; break;
+        case B2_AGG_ARGMIN: nd.amin = true; break;
+        case B2_AGG_ARGMAX: nd.amax = true; break;
         case B2_AGG_PRODUCT: nd.prod = true; break;
         case B2_AGG_SUM_OF_SQUARES: nd.ssq = true; break;
         case B2_AGG_MEAN: nd.sum = nd.cnt = true; break;
@@ -417,7 +424,7 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
   sc.nvals = (int)seen.size();
 
   // cells, per value column in the order Σ, n, Σx², min, max, Π; the row count last
-  struct CellIdx { int sum = -1, cnt = -1, ssq = -1, mn = -1, mx = -1, prod = -1; };
+  struct CellIdx { int sum = -1, cnt = -1, ssq = -1, mn = -1, mx = -1, prod = -1, amin = -1, amax = -1; };
   std::vector<CellIdx> idx((size_t)sc.nvals);
   auto add_cell = [&](int op, int col) {
     if (sc.ncells >= MAX_CELLS) B2_FAIL(B2_UNSUPPORTED, "too many accumulators in one aggregate call");
@@ -430,6 +437,8 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
     const bool f = is_float_t(t);
     const bool uns = t == B2_UINT64;
     if (nd.nulls && (nd.sum || nd.ssq || nd.mn || nd.mx || nd.prod)) nd.cnt = true;  // decides validity
+    if (nd.amin) { idx[(size_t)s].amin = add_cell(OP_ARGMIN, s); sc.has_arg = true; }
+    if (nd.amax) { idx[(size_t)s].amax = add_cell(OP_ARGMAX, s); sc.has_arg = true; }
     if (nd.sum) idx[(size_t)s].sum = add_cell(f ? OP_SUM_F : OP_SUM_I, s);
     if (nd.cnt) idx[(size_t)s].cnt = add_cell(OP_CNT_V, s);
     if (nd.ssq) idx[(size_t)s].ssq = add_cell(f ? OP_SSQ_F : OP_SSQ_I, s);
@@ -465,8 +474,16 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
         case B2_AGG_SUM: o.kind = f ? OK_FLT : OK_INT; o.c_a = ci.sum; break;
         case B2_AGG_SUM_OF_SQUARES: o.kind = f ? OK_FLT : OK_INT; o.c_a = ci.ssq; break;
         case B2_AGG_PRODUCT: o.kind = f ? OK_FLT : OK_INT; o.c_a = ci.prod; break;
-        case B2_AGG_MIN: o.kind = f ? OK_MINMAX_F : OK_INT; o.c_a = ci.mn; break;
-        case B2_AGG_MAX: o.kind = f ? OK_MINMAX_F : OK_INT; o.c_a = ci.mx; break;
+        case B2_AGG_MIN:
+          if (t == B2_STRING) { o.kind = OK_STRARG; o.c_a = ci.amin; o.c_cnt = -1; }
+          else { o.kind = f ? OK_MINMAX_F : OK_INT; o.c_a = ci.mn; }
+          break;
+        case B2_AGG_MAX:
+          if (t == B2_STRING) { o.kind = OK_STRARG; o.c_a = ci.amax; o.c_cnt = -1; }
+          else { o.kind = f ? OK_MINMAX_F : OK_INT; o.c_a = ci.mx; }
+          break;
+        case B2_AGG_ARGMIN: o.kind = OK_ARG; o.c_a = ci.amin; o.c_cnt = -1; break;
+        case B2_AGG_ARGMAX: o.kind = OK_ARG; o.c_a = ci.amax; o.c_cnt = -1; break;
         case B2_AGG_MEAN: o.kind = OK_MEAN; o.c_a = ci.sum; o.c_cnt = ci.cnt; break;
         case B2_AGG_M2: o.kind = OK_M2; o.c_a = ci.sum; o.c_b = ci.ssq; o.c_cnt = ci.cnt; o.nullable = false; break;
         case B2_AGG_VARIANCE: o.kind = OK_VAR; o.c_a = ci.sum; o.c_b = ci.ssq; o.c_cnt = ci.cnt; o.nullable = true; break;
@@ -530,6 +547,18 @@ void bind_plan_inputs(DPlan& P, const Schema& sc, const b2_groupby& gb, const b2
     P.vals[s].data = (const unsigned char*)v.data;
     P.vals[s].mask = (v.null_mask && v.null_count != 0) ? v.null_mask : nullptr;
     P.vals[s].offset = v.offset;
+    P.vals[s].offsets = nullptr;
+    P.vals[s].offs64 = 0;
+    if (v.type_id == B2_STRING) {
+      if (v.size > 0 && (v.num_children < 1 || !v.children ||
+                         (v.children[0].type_id != B2_INT32 && v.children[0].type_id != B2_INT64)))
+        B2_FAIL(B2_INVALID_ARGUMENT, "STRING values column needs an INT32 or INT64 offsets child");
+      if (v.num_children > 0 && v.children) {
+        const b2_column_view& o = v.children[0];
+        P.vals[s].offsets = (const unsigned char*)o.data + (size_t)o.offset * (o.type_id == B2_INT64 ? 8 : 4);
+        P.vals[s].offs64 = o.type_id == B2_INT64;
+      }
+    }
   }
   // 16-byte vector loads of 4 consecutive rows need aligned column starts
   auto aligned = [](const void* base, int64_t offset, int width) {
@@ -718,7 +747,7 @@ SharedPlan plan_shared(const b2_groupby_state& st, const b2_groupby& gb)
   const Schema& sc = st.sc;
   const DPlan& P = st.plan;
   SharedPlan sp;
-  if (gb.table_variant == 1) return sp;
+  if (gb.table_variant == 1 || sc.has_arg) return sp;
   const int budget = gb.shared_table_bytes > 0 ? std::min(gb.shared_table_bytes, device_info().smem_optin - 1024)
                                                : device_info().smem_optin - 1024;
   const int cell_bytes = sc.f32mean ? 8 : 8 * sc.ncells;  // accumulators of one slot
@@ -865,7 +894,7 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
   const Schema& sc = st.sc;
   const DPlan& P = st.plan;
   const bool forced = gb.table_variant == 6;
-  if (sc.key_mode != KM_PACKED || sc.ncells < 1) return false;
+  if (sc.key_mode != KM_PACKED || sc.ncells < 1 || sc.has_arg) return false;
   Trace trace(stream);
   const int sms = device_info().sms;
   EventPair& ev = kernel_events();
@@ -1107,6 +1136,8 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
 // all groups of a table as packed records, destination-major by owner; counts on the host
 void pack_table(b2_groupby_state& st, int nparts, cudaStream_t stream, Scratch& out, std::vector<int64_t>& counts)
 {
+  if (st.sc.has_arg)
+    B2_FAIL(B2_UNSUPPORTED, "ARGMIN / ARGMAX and MIN / MAX of strings hold row indices of one batch: no partial records");
   if (st.sc.key_mode != KM_PACKED)
     B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys are not transferable; partition the rows instead");
   counts.assign((size_t)nparts, 0);
@@ -1141,6 +1172,8 @@ void pack_table(b2_groupby_state& st, int nparts, cudaStream_t stream, Scratch& 
 
 void merge_records(b2_groupby_state& st, const u64* recs, int64_t nrecs, cudaStream_t stream)
 {
+  if (st.sc.has_arg)
+    B2_FAIL(B2_UNSUPPORTED, "ARGMIN / ARGMAX and MIN / MAX of strings hold row indices of one batch: no partial records");
   if (st.sc.key_mode != KM_PACKED)
     B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys are not transferable; partition the rows instead");
   if (nrecs <= 0) return;
@@ -1222,6 +1255,48 @@ void init_owned(b2_owned_column& c, int type_id, int64_t n, bool nullable, const
   }
 }
 
+// STRING column of the strings at rows `rows` (-1 = none) of `kc`: lengths -> offsets by scan -> bytes.
+// `c` has its type, size and (optional) null mask set; chars and the offsets child are allocated here.
+// Synchronises the stream once (the total size decides between INT32 and INT64 offsets).
+void gather_strings(const DKeyCol& kc, const int* rows, int64_t G, b2_owned_column& c, u32* null_counter,
+                    const b2_allocator& al, cudaStream_t stream)
+{
+  Scratch lens((size_t)(G + 1) * sizeof(i64), stream), offs((size_t)(G + 1) * sizeof(i64), stream);
+  k_string_lengths<<<grid_for(G, 256, 8), 256, 0, stream>>>(kc, rows, G, (i64*)lens.p, c.null_mask, null_counter);
+  CUDA_TRY(cudaGetLastError());
+  device_exclusive_scan((const i64*)lens.p, G, (i64*)offs.p, stream);
+  i64 total = 0;
+  CUDA_TRY(cudaMemcpyAsync(&total, (i64*)offs.p + G, sizeof(i64), cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  // INT64 offsets once the chars pass the reference's large-strings threshold (cpp/src/strings/utilities.cu:150-157)
+  const bool big = total > 0x7FFFFFFFll;
+  c.data_bytes = (size_t)std::max<i64>(total, 1);
+  c.data = out_alloc(al, c.data_bytes, stream);
+  c.num_children = 1;
+  c.children = (b2_owned_column*)std::calloc(1, sizeof(b2_owned_column));
+  b2_owned_column& oc = c.children[0];
+  oc.type_id = big ? B2_INT64 : B2_INT32;
+  oc.size = (int32_t)(G + 1);
+  oc.data_bytes = (size_t)(G + 1) * (big ? 8 : 4);
+  oc.data = out_alloc(al, oc.data_bytes, stream);
+  if (big) k_string_copy<i64><<<grid_for(G * 32, 256, 8), 256, 0, stream>>>(kc, rows, G, (const i64*)offs.p, (i64*)oc.data, (unsigned char*)c.data);
+  else k_string_copy<int><<<grid_for(G * 32, 256, 8), 256, 0, stream>>>(kc, rows, G, (const i64*)offs.p, (int*)oc.data, (unsigned char*)c.data);
+  CUDA_TRY(cudaGetLastError());
+  g_stats.kernel_launches += 5;
+}
+
+// a STRING column without rows: one zero offset
+void empty_strings(b2_owned_column& c, const b2_allocator& al, cudaStream_t stream)
+{
+  c.num_children = 1;
+  c.children = (b2_owned_column*)std::calloc(1, sizeof(b2_owned_column));
+  c.children[0].type_id = B2_INT32;
+  c.children[0].size = 1;
+  c.children[0].data_bytes = 4;
+  c.children[0].data = out_alloc(al, 4, stream);
+  CUDA_TRY(cudaMemsetAsync(c.children[0].data, 0, 4, stream));
+}
+
 void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocator* allocator, b2_groupby_result* out)
 {
   const Schema& sc = st.sc;
@@ -1255,13 +1330,27 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
   auto plan = std::make_unique<DOutPlan>();
   std::memset(plan.get(), 0, sizeof(DOutPlan));
   plan->nouts = (int)sc.outs.size();
+  std::vector<Scratch> arg_rows(sc.outs.size());  // MIN / MAX of strings: the winning row of every group
   for (size_t i = 0; i < sc.outs.size(); ++i) {
     const OutSpec& o = sc.outs[i];
     b2_owned_column& c = out->results[o.req][o.agg];
-    init_owned(c, o.rtype, G, o.nullable, al, stream);
+    if (o.kind == OK_STRARG) {
+      std::memset(&c, 0, sizeof(c));
+      c.type_id = B2_STRING;
+      c.size = (int32_t)G;
+      if (o.nullable) {
+        c.null_mask_bytes = (size_t)std::max<int64_t>(1, (G + 511) / 512) * 64;
+        c.null_mask = (uint32_t*)out_alloc(al, c.null_mask_bytes, stream);
+        CUDA_TRY(cudaMemsetAsync(c.null_mask, 0xFF, c.null_mask_bytes, stream));
+      }
+      arg_rows[i] = Scratch(std::max<size_t>(8, (size_t)G * sizeof(int)), stream);
+    } else {
+      init_owned(c, o.rtype, G, o.nullable, al, stream);
+    }
     c.scale = o.scale;
     DOutCol& d = plan->outs[i];
-    d.data = c.data; d.mask = c.null_mask; d.kind = o.kind; d.rclass = vclass_of(o.rtype);
+    d.data = o.kind == OK_STRARG ? arg_rows[i].p : c.data;
+    d.mask = c.null_mask; d.kind = o.kind; d.rclass = vclass_of(o.rtype);
     d.c_a = o.c_a; d.c_b = o.c_b; d.c_cnt = o.c_cnt; d.ddof = o.ddof; d.src_float = o.src_float;
     d.null_slot = (int)i;
   }
@@ -1324,57 +1413,28 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
           g_stats.kernel_launches++;
           continue;
         }
-        // strings: lengths → offsets → bytes
-        Scratch lens((size_t)(G + 1) * sizeof(i64), stream), offs((size_t)(G + 1) * sizeof(i64), stream);
-        k_string_lengths<<<grid_for(G, 256, 8), 256, 0, stream>>>(kc, plan->rep_rows, G, (i64*)lens.p, c.null_mask,
-                                                                  plan->null_counts + MAX_OUTS + k);
-        {
-          const int64_t per = (int64_t)SCAN_BLOCK * SCAN_ITEMS;
-          const int nblocks = (int)((G + per - 1) / per);
-          Scratch totals((size_t)(nblocks + 1) * sizeof(i64), stream), bases((size_t)(nblocks + 1) * sizeof(i64), stream);
-          k_scan_block_totals<<<nblocks, SCAN_BLOCK, 0, stream>>>((const i64*)lens.p, G, (i64*)totals.p);
-          k_exclusive_scan<<<1, 1024, 0, stream>>>((const i64*)totals.p, (i64*)bases.p, nblocks);
-          k_scan_apply<<<nblocks, SCAN_BLOCK, 0, stream>>>((const i64*)lens.p, G, (const i64*)bases.p, (i64*)offs.p);
-        }
-        CUDA_TRY(cudaGetLastError());
-        i64 total = 0;
-        CUDA_TRY(cudaMemcpyAsync(&total, (i64*)offs.p + G, sizeof(i64), cudaMemcpyDeviceToHost, stream));
-        CUDA_TRY(cudaStreamSynchronize(stream));
-        trace.mark("finalize: string lengths+scan");
-        // INT64 offsets once the chars pass the reference's large-strings threshold
-        // (cpp/src/strings/utilities.cu:150-157)
-        const bool big = total > 0x7FFFFFFFll;
-        c.data_bytes = (size_t)std::max<i64>(total, 1);
-        c.data = out_alloc(al, c.data_bytes, stream);
-        c.num_children = 1;
-        c.children = (b2_owned_column*)std::calloc(1, sizeof(b2_owned_column));
-        b2_owned_column& oc = c.children[0];
-        oc.type_id = big ? B2_INT64 : B2_INT32;
-        oc.size = (int32_t)(G + 1);
-        oc.data_bytes = (size_t)(G + 1) * (big ? 8 : 4);
-        oc.data = out_alloc(al, oc.data_bytes, stream);
-        if (big) k_string_copy<i64><<<grid_for(G * 32, 256, 8), 256, 0, stream>>>(kc, plan->rep_rows, G, (const i64*)offs.p, (i64*)oc.data, (unsigned char*)c.data);
-        else k_string_copy<int><<<grid_for(G * 32, 256, 8), 256, 0, stream>>>(kc, plan->rep_rows, G, (const i64*)offs.p, (int*)oc.data, (unsigned char*)c.data);
-        CUDA_TRY(cudaGetLastError());
-        g_stats.kernel_launches += 3;
+        gather_strings(kc, plan->rep_rows, G, c, plan->null_counts + MAX_OUTS + k, al, stream);
+        trace.mark("finalize: key strings");
       }
+    }
+    // MIN / MAX of strings: gather the winning rows' strings (cpp/src/groupby/hash/hash_compound_agg_finalizer.cu:39-76)
+    for (size_t i = 0; i < sc.outs.size(); ++i) {
+      const OutSpec& o = sc.outs[i];
+      if (o.kind != OK_STRARG) continue;
+      const DValCol& vc = st.plan.vals[sc.req_val[(size_t)o.req]];
+      DKeyCol kc{};
+      kc.data = vc.data; kc.mask = nullptr; kc.offsets = vc.offsets; kc.offset = vc.offset; kc.vclass = VC_STRING; kc.offs64 = vc.offs64;
+      gather_strings(kc, (const int*)arg_rows[i].p, G, out->results[o.req][o.agg], plan->null_counts + i, al, stream);
     }
     CUDA_TRY(cudaMemcpyAsync(h_nulls.data(), st.ctrl->null_counts, sizeof(DCtrl::null_counts), cudaMemcpyDeviceToHost, stream));
     CUDA_TRY(cudaStreamSynchronize(stream));
     trace.mark("finalize: key gather + nulls");
   } else {
-    // empty result: STRING keys still carry a one-entry offsets child
+    // empty result: STRING columns still carry a one-entry offsets child
     for (int k = 0; k < sc.nkeys; ++k)
-      if (sc.key_types[k] == B2_STRING) {
-        b2_owned_column& c = out->keys[k];
-        c.num_children = 1;
-        c.children = (b2_owned_column*)std::calloc(1, sizeof(b2_owned_column));
-        c.children[0].type_id = B2_INT32;
-        c.children[0].size = 1;
-        c.children[0].data_bytes = 4;
-        c.children[0].data = out_alloc(al, 4, stream);
-        CUDA_TRY(cudaMemsetAsync(c.children[0].data, 0, 4, stream));
-      }
+      if (sc.key_types[k] == B2_STRING) empty_strings(out->keys[k], al, stream);
+    for (const OutSpec& o : sc.outs)
+      if (o.kind == OK_STRARG) empty_strings(out->results[o.req][o.agg], al, stream);
     CUDA_TRY(cudaStreamSynchronize(stream));
   }
   for (size_t i = 0; i < sc.outs.size(); ++i) out->results[sc.outs[i].req][sc.outs[i].agg].null_count = (int32_t)h_nulls[i];
@@ -1408,6 +1468,8 @@ void update_state(b2_groupby_state& st, const b2_groupby& gb, const b2_aggregati
   }
   if (st.sc.key_mode != KM_PACKED)
     B2_FAIL(B2_UNSUPPORTED, "a state keyed on string / float / wide keys takes one update only");
+  if (st.sc.has_arg)
+    B2_FAIL(B2_UNSUPPORTED, "a state with ARGMIN / ARGMAX or MIN / MAX of strings takes one update only");
   // batch-local table, then merge (a failed pass must not leave half a batch in the state)
   b2_groupby_state tmp;
   tmp.sc = st.sc;
@@ -1474,6 +1536,8 @@ extern "C" b2_status b2_groupby_aggregate_noalloc(b2_groupby* gb, const b2_aggre
     Schema sc = make_schema(*gb, requests, num_requests);
     if (sc.key_mode != KM_PACKED)
       B2_FAIL(B2_UNSUPPORTED, "the no-allocation variant serves keys that pack into 64 bits (no string / float / wide keys)");
+    for (const OutSpec& o : sc.outs)
+      if (o.kind == OK_STRARG) B2_FAIL(B2_UNSUPPORTED, "the no-allocation variant does not serve MIN / MAX of strings (their size is not known in advance)");
     DPlan P;
     fill_plan_schema(P, sc);
     bind_plan_inputs(P, sc, *gb, requests, num_requests);
@@ -1687,8 +1751,8 @@ b2_status b2_state_pack_chunks(b2_groupby_state* st, int32_t num_parts, int64_t 
   return guarded([&] {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (!st || !out || num_parts < 1 || num_parts > 4096 || chunk_records < 1) B2_FAIL(B2_INVALID_ARGUMENT, "bad argument");
-    if (st->sc.key_mode != KM_PACKED)
-      B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys are not transferable; partition the rows instead");
+    if (st->sc.key_mode != KM_PACKED || st->sc.has_arg)
+      B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys (or of row-index accumulators) are not transferable; partition the rows instead");
     device_info();
     const int64_t chunk_words = 2 + chunk_records * st->plan.stride;
     if (!st->table) {  // no groups: empty chunks
@@ -1712,8 +1776,8 @@ b2_status b2_state_merge_chunks(b2_groupby_state* st, const void* chunks, int32_
   return guarded([&] {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (!st || !chunks || num_chunks < 1 || chunk_records < 1) B2_FAIL(B2_INVALID_ARGUMENT, "bad argument");
-    if (st->sc.key_mode != KM_PACKED)
-      B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys are not transferable; partition the rows instead");
+    if (st->sc.key_mode != KM_PACKED || st->sc.has_arg)
+      B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys (or of row-index accumulators) are not transferable; partition the rows instead");
     if (st->table) B2_FAIL(B2_LOGIC_ERROR, "b2_state_merge_chunks needs an empty state");
     device_info();
     st->last_stream = stream;
@@ -2074,8 +2138,8 @@ void aggregate_multi(b2_comm& c, b2_groupby& gb, const b2_aggregation_request* r
   const NcclApi& n = nccl_api();
   // what can fail before any communication fails on every rank alike (same schema everywhere)
   std::unique_ptr<b2_groupby_state, void (*)(b2_groupby_state*)> local(make_state(gb, reqs, nreqs), b2_state_destroy);
-  if (local->sc.key_mode != KM_PACKED)
-    B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys are not transferable; partition the rows instead");
+  if (local->sc.key_mode != KM_PACKED || local->sc.has_arg)
+    B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys (or of row-index accumulators) are not transferable; partition the rows instead");
   const int W = c.nranks;
   const int64_t chunk_bytes = b2_state_chunk_bytes(local.get(), MULTI_CHUNK_RECORDS);
   const int64_t chunk_words = chunk_bytes / 8;

@@ -672,7 +672,8 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
         for (int j = 0; j < AGG_ROWS; ++j) {
           if (sl[j] == SLOT_NONE || !((use >> j) & 1u)) continue;
           // two call sites so that each atomic knows its address space (shared vs global reduction)
-          if (LAYOUT == SL_GENERIC && sl[j] >= 0) cell_update(scells + (size_t)c * NS + sl[j], op, v[j]);
+          if (is_arg_op(op)) arg_update(tbl + (i64)(-2 - sl[j]) * stride + 1 + c, op, P.vals[col], row0 + j);  // (global table only)
+          else if (LAYOUT == SL_GENERIC && sl[j] >= 0) cell_update(scells + (size_t)c * NS + sl[j], op, v[j]);
           else cell_update(tbl + (i64)(-2 - sl[j]) * stride + 1 + c, op, v[j]);
         }
       }
@@ -885,7 +886,9 @@ enum OutKind : int {
   OK_INT,        // integer cell (Σ, Σx², Π, min, max of integers) stored in the result width
   OK_FLT,        // double cell (Σ, Σx², Π of floats) stored as FLOAT32/FLOAT64
   OK_MINMAX_F,   // ordered-encoded double cell
-  OK_MEAN, OK_M2, OK_VAR, OK_STD
+  OK_MEAN, OK_M2, OK_VAR, OK_STD,
+  OK_ARG,        // ARGMIN / ARGMAX: the row held by the cell as INT32, null when none
+  OK_STRARG      // MIN / MAX of strings: the row (or -1) into a scratch array the host gathers the strings by
 };
 
 struct DOutCol {
@@ -964,6 +967,12 @@ __device__ __forceinline__ void write_group(const DPlan& P, const DOutPlan& O, u
       case OK_MINMAX_F:
         store_flt(oc.data, g, oc.rclass, valid ? __longlong_as_double((i64)f64_unordered(cells[(i64)(oc.c_a) * cstep])) : 0.0);
         break;
+      case OK_ARG: case OK_STRARG: {
+        const u64 r = cells[(i64)(oc.c_a) * cstep];
+        valid = r != ARG_NONE;
+        ((int*)oc.data)[g] = valid ? (int)r : (oc.kind == OK_ARG ? 0 : -1);
+        break;
+      }
       case OK_MEAN: {
         if (oc.rclass != VC_F64) {  // durations: integer division in the source type
           store_int(oc.data, g, oc.rclass, valid ? (u64)((i64)cells[(i64)(oc.c_a) * cstep] / n) : 0);
@@ -1073,7 +1082,9 @@ __global__ void k_string_lengths(DKeyCol c, const int* __restrict__ rows, i64 ng
   for (i64 g = (i64)blockIdx.x * blockDim.x + threadIdx.x; g < ngroups; g += (i64)gridDim.x * blockDim.x) {
     const i64 idx = c.offset + rows[g];
     i64 len = 0;
-    if (c.mask && !bit_valid(c.mask, idx)) {
+    if (rows[g] < 0) {
+      // no row (a string MIN / MAX of a group without a valid value: nulled by the finisher already)
+    } else if (c.mask && !bit_valid(c.mask, idx)) {
       if (dst_mask) clear_bit(dst_mask, g, null_counter);
     } else {
       len = str_offset(c, idx + 1) - str_offset(c, idx);

@@ -60,6 +60,8 @@ class Kind(enum.IntEnum):
     # kinds the reference serves on its sort path only; accepted by the API so that the
     # "unsupported" status can be reported the way an adapter needs it
     MEDIAN = 14
+    ARGMAX = 16
+    ARGMIN = 17
     NUNIQUE = 18
     NTH_ELEMENT = 19
 
@@ -120,7 +122,7 @@ def result_type(source: int, kind: int) -> TypeId:
     """Result element type of aggregation ``kind`` over ``source``
     (cpp/include/cudf/detail/aggregation/aggregation.hpp:884-1013)."""
     source, kind = TypeId(source), Kind(kind)
-    if kind in (Kind.COUNT_VALID, Kind.COUNT_ALL):
+    if kind in (Kind.COUNT_VALID, Kind.COUNT_ALL, Kind.ARGMAX, Kind.ARGMIN):
         return TypeId.INT32
     if kind in (Kind.MIN, Kind.MAX):
         return source

@@ -58,7 +58,7 @@ enum TypeId : int32_t {
 };
 enum Kind : int32_t {
   K_SUM = 0, K_PRODUCT = 2, K_MIN = 3, K_MAX = 4, K_COUNT_VALID = 5, K_COUNT_ALL = 6,
-  K_SUMSQ = 9, K_MEAN = 10, K_M2 = 11, K_VAR = 12, K_STD = 13
+  K_SUMSQ = 9, K_MEAN = 10, K_M2 = 11, K_VAR = 12, K_STD = 13, K_ARGMAX = 16, K_ARGMIN = 17
 };
 
 struct Col {  // host-memory mirror of a column_view
@@ -157,6 +157,10 @@ struct Acc {  // per (group, request): every simple accumulator the supported ki
   long double fprod = 1;
   int64_t imin = 0, imax = 0;  // signed or unsigned compare depending on the source type
   double fmin = 0, fmax = 0;
+  // ARGMIN / ARGMAX (and MIN / MAX of strings, which the reference computes as ARGMIN / ARGMAX + gather,
+  // cpp/src/groupby/hash/extract_single_pass_aggs.cpp:39-60): row of the extreme valid value, the first
+  // such row on ties; -1 = no valid value (ARGMIN_SENTINEL, cpp/include/cudf/detail/aggregation/aggregation.hpp)
+  int64_t argmin = -1, argmax = -1;
 };
 
 struct Group {
@@ -196,7 +200,7 @@ void alloc(OutCol& c, int32_t type, int64_t n, int w, bool nullable)
 int32_t result_type(int32_t src, int32_t kind)
 {
   switch (kind) {
-    case K_COUNT_VALID: case K_COUNT_ALL: return T_INT32;
+    case K_COUNT_VALID: case K_COUNT_ALL: case K_ARGMAX: case K_ARGMIN: return T_INT32;
     case K_MIN: case K_MAX: return src;
     case K_SUM:
       // fixed point sums keep their type (aggregation.hpp:956-963): a DECIMAL32 sum wraps at 32 bits
@@ -214,12 +218,35 @@ int check_combo(int32_t src, int32_t kind)
   const bool numeric = (src >= T_INT8 && src <= T_BOOL8);
   switch (kind) {
     case K_COUNT_VALID: case K_COUNT_ALL: return 0;
-    case K_MIN: case K_MAX: return (numeric || is_timestamp(src) || is_duration(src) || is_decimal(src)) ? 0 : 1;
+    case K_MIN: case K_MAX: case K_ARGMIN: case K_ARGMAX:
+      return (numeric || is_timestamp(src) || is_duration(src) || is_decimal(src) || src == T_STRING) ? 0 : 1;
     case K_SUM: return (numeric || is_duration(src) || is_decimal(src)) ? 0 : 1;  // PRODUCT of decimals throws (sum_tests.cpp:245-246)
     case K_MEAN: return (numeric || is_duration(src)) ? 0 : 1;
     case K_SUMSQ: case K_PRODUCT: case K_M2: case K_VAR: case K_STD: return numeric ? 0 : 1;
     default: return 1;
   }
+}
+
+// value at row a vs value at row b of one column: -1, 0, +1, or 2 when a NaN makes them unordered
+// (strings: byte-wise, cpp/include/cudf/strings/string_view.cuh:306-321)
+int compare_rows(const Col& c, int64_t a, int64_t b)
+{
+  if (c.type_id == T_STRING) {
+    auto off = [&](int64_t i) {
+      return c.offsets_type == T_INT64 ? ((const int64_t*)c.offsets)[c.offset + i] : (int64_t)((const int32_t*)c.offsets)[c.offset + i];
+    };
+    const int64_t ba = off(a), la = off(a + 1) - ba, bb = off(b), lb = off(b + 1) - bb;
+    const int r = std::memcmp((const char*)c.data + ba, (const char*)c.data + bb, (size_t)std::min(la, lb));
+    if (r != 0) return r < 0 ? -1 : 1;
+    return la < lb ? -1 : (la > lb ? 1 : 0);
+  }
+  const Val x = load(c, a), y = load(c, b);
+  if (is_float(c.type_id)) {
+    if (x.f != x.f || y.f != y.f) return 2;
+    return x.f < y.f ? -1 : (x.f > y.f ? 1 : 0);
+  }
+  if (c.type_id == T_UINT64) return (uint64_t)x.i < (uint64_t)y.i ? -1 : ((uint64_t)x.i > (uint64_t)y.i ? 1 : 0);
+  return x.i < y.i ? -1 : (x.i > y.i ? 1 : 0);
 }
 
 struct Partial {  // one thread's table over a contiguous row range
@@ -258,6 +285,10 @@ void aggregate_range(Partial& P, int64_t lo, int64_t hi, const Col* keys, int nk
       const Col& vc = reqs[q].values;
       if (!bit(vc.mask, (int64_t)vc.offset + r)) continue;  // null value: skipped
       Acc& a = P.accs[(size_t)(g * nreqs + q)];
+      // rows arrive in ascending order: a strict comparison keeps the first row of equal values
+      if (a.argmin < 0 || compare_rows(vc, r, a.argmin) == -1) a.argmin = r;
+      if (a.argmax < 0 || compare_rows(vc, r, a.argmax) == 1) a.argmax = r;
+      if (vc.type_id == T_STRING) { a.count++; continue; }
       const Val v = load(vc, r);
       const bool first = a.count == 0;
       a.count++;
@@ -285,9 +316,13 @@ void aggregate_range(Partial& P, int64_t lo, int64_t hi, const Col* keys, int nk
   }
 }
 
-void merge_acc(Acc& d, const Acc& s, int32_t vtype)
+void merge_acc(Acc& d, const Acc& s, const Col& vc)
 {
+  const int32_t vtype = vc.type_id;
   if (s.count == 0) return;
+  // `s` covers later rows than `d`: strict comparisons keep the first row of equal values
+  if (s.argmin >= 0 && (d.argmin < 0 || compare_rows(vc, s.argmin, d.argmin) == -1)) d.argmin = s.argmin;
+  if (s.argmax >= 0 && (d.argmax < 0 || compare_rows(vc, s.argmax, d.argmax) == 1)) d.argmax = s.argmax;
   const bool first = d.count == 0;
   d.count += s.count;
   d.isum = (int64_t)((uint64_t)d.isum + (uint64_t)s.isum);
@@ -370,8 +405,7 @@ Result* run(const Col* keys, int nkeys, int null_policy, const Req* reqs, int nr
         } else g = it->second;
         D.groups[(size_t)g].rows += S.groups[(size_t)kv.second].rows;
         for (int q = 0; q < nreqs; ++q)
-          merge_acc(D.accs[(size_t)(g * nreqs + q)], S.accs[(size_t)(kv.second * nreqs + q)],
-                    reqs[q].values.type_id);
+          merge_acc(D.accs[(size_t)(g * nreqs + q)], S.accs[(size_t)(kv.second * nreqs + q)], reqs[q].values);
       }
       S = Partial{};
     }
@@ -429,6 +463,29 @@ Result* run(const Col* keys, int nkeys, int null_policy, const Req* reqs, int nr
       bool nullable = src_has_nulls;
       if (kind == K_COUNT_VALID || kind == K_COUNT_ALL || kind == K_M2) nullable = false;
       if (kind == K_VAR || kind == K_STD) nullable = true;  // n - ddof <= 0 can always occur
+      if (rt == T_STRING) {
+        // MIN / MAX of strings: gather of the ARGMIN / ARGMAX rows, null where there is none
+        // (cpp/src/groupby/hash/hash_compound_agg_finalizer.cu:39-76)
+        const Col& c = reqs[q].values;
+        o.type_id = T_STRING;
+        o.size = G;
+        o.offsets.assign((size_t)G + 1, 0);
+        if (nullable) o.mask.assign((size_t)((G + 31) / 32), 0xFFFFFFFFu);
+        for (int64_t g = 0; g < G; ++g) {
+          const Acc& A = P.accs[(size_t)(g * nreqs + q)];
+          const int64_t r = kind == K_MIN ? A.argmin : A.argmax;
+          if (r < 0) {
+            if (nullable) set_null(o, g);
+          } else {
+            int64_t b, e;
+            if (c.offsets_type == T_INT64) { b = ((const int64_t*)c.offsets)[c.offset + r]; e = ((const int64_t*)c.offsets)[c.offset + r + 1]; }
+            else { b = ((const int32_t*)c.offsets)[c.offset + r]; e = ((const int32_t*)c.offsets)[c.offset + r + 1]; }
+            o.data.insert(o.data.end(), (const uint8_t*)c.data + b, (const uint8_t*)c.data + e);
+          }
+          o.offsets[(size_t)g + 1] = (int64_t)o.data.size();
+        }
+        continue;
+      }
       alloc(o, rt, G, width_of(rt), nullable);
       for (int64_t g = 0; g < G; ++g) {
         const Acc& A = P.accs[(size_t)(g * nreqs + q)];
@@ -451,6 +508,12 @@ Result* run(const Col* keys, int nkeys, int null_policy, const Req* reqs, int nr
           case K_MAX:
             if (cnt == 0) { if (nullable) set_null(o, g); break; }
             write_typed(o, g, rt, A.imax, A.fmax); break;
+          case K_ARGMIN: case K_ARGMAX: {
+            const int64_t r = kind == K_ARGMIN ? A.argmin : A.argmax;
+            if (r < 0) { if (nullable) set_null(o, g); break; }
+            put<int32_t>(o, g, (int32_t)r);
+            break;
+          }
           case K_MEAN: {
             if (cnt == 0) { if (nullable) set_null(o, g); break; }
             if (is_duration(st)) { write_typed(o, g, rt, A.isum / cnt, 0); break; }

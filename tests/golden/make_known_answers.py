@@ -65,6 +65,35 @@ case("COUNT_ALL.zero_valid_values", "cpp/tests/groupby/count_tests.cpp:98", [1, 
      "COUNT_ALL", [1], [3], ALL_FIXED)
 case("COUNT_ALL.null_keys_and_values", "cpp/tests/groupby/count_tests.cpp:128", K11N, V11_A, "COUNT_ALL",
      [1, 2, 3, 4], [3, 4, 2, 1], ALL_FIXED)
+# ARGMIN / ARGMAX: the row index of the extreme value (values are distinct in the reference's vectors)
+V10_DESC = [9, 8, 7, 6, 5, 4, 3, 2, 1, 0]
+ARG_TYPES = ["INT8", "INT16", "INT32", "INT64", "FLOAT32", "FLOAT64", "UINT8", "UINT16", "UINT32", "UINT64"]
+case("ARGMIN.basic", "cpp/tests/groupby/argmin_tests.cpp:23", K10, V10_DESC, "ARGMIN", [1, 2, 3], [6, 9, 8], ARG_TYPES)
+case("ARGMIN.zero_valid_keys", "cpp/tests/groupby/argmin_tests.cpp:43", [None, None, None], [3, 4, 5], "ARGMIN", [], [], ARG_TYPES)
+case("ARGMIN.zero_valid_values", "cpp/tests/groupby/argmin_tests.cpp:63", [1, 1, 1], [None, None, None], "ARGMIN", [1], [None], ARG_TYPES)
+case("ARGMIN.null_keys_and_values", "cpp/tests/groupby/argmin_tests.cpp:83", K11N,
+     nulls([9, 8, 7, 6, 5, 4, 3, 2, 1, 0, 4], [1, 1, 1, 1, 1, 0, 0, 1, 1, 1, 0]), "ARGMIN", [1, 2, 3, 4], [3, 9, 8, None], ARG_TYPES)
+case("ARGMAX.basic", "cpp/tests/groupby/argmax_tests.cpp:22", K10, V10_DESC, "ARGMAX", [1, 2, 3], [0, 1, 2], ARG_TYPES)
+case("ARGMAX.zero_valid_keys", "cpp/tests/groupby/argmax_tests.cpp:42", [None, None, None], [3, 4, 5], "ARGMAX", [], [], ARG_TYPES)
+case("ARGMAX.zero_valid_values", "cpp/tests/groupby/argmax_tests.cpp:62", [1, 1, 1], [None, None, None], "ARGMAX", [1], [None], ARG_TYPES)
+case("ARGMAX.null_keys_and_values", "cpp/tests/groupby/argmax_tests.cpp:82",
+     [1, 2, None, 1, 2, 2, 1, 3, 3, 2, 4], nulls([9, 8, 7, 6, 5, 4, 3, 2, 1, 0, 4], [0, 0, 1, 1, 1, 1, 1, 1, 1, 1, 0]),
+     "ARGMAX", [1, 2, 3, 4], [3, 4, 7, None], ARG_TYPES)
+STR10 = ["año", "bit", "₹1", "aaa", "zit", "bat", "aab", "$1", "€1", "wut"]
+case("ARGMIN.string_basic", "cpp/tests/groupby/argmin_tests.cpp:111", K10, STR10, "ARGMIN", [1, 2, 3], [3, 5, 7], value_type="STRING")
+case("ARGMIN.string_zero_valid_values", "cpp/tests/groupby/argmin_tests.cpp:129", [1, 1, 1], [None, None, None], "ARGMIN",
+     [1], [None], value_type="STRING")
+case("ARGMAX.string_basic", "cpp/tests/groupby/argmax_tests.cpp:110", K10, STR10, "ARGMAX", [1, 2, 3], [0, 4, 2], value_type="STRING")
+case("ARGMAX.string_zero_valid_values", "cpp/tests/groupby/argmax_tests.cpp:128", [1, 1, 1], [None, None, None], "ARGMAX",
+     [1], [None], value_type="STRING")
+# MIN / MAX of strings (ARGMIN / ARGMAX + gather in the hash path)
+STR10B = ["año", "bit", "₹1", "aaa", "zit", "bat", "aaa", "$1", "₹1", "wut"]
+case("MIN.string_basic", "cpp/tests/groupby/min_tests.cpp:123", K10, STR10B, "MIN", [1, 2, 3], ["aaa", "bat", "$1"], value_type="STRING")
+case("MIN.string_zero_valid_values", "cpp/tests/groupby/min_tests.cpp:139", [1, 1, 1], [None, None, None], "MIN", [1], [None],
+     value_type="STRING")
+case("MAX.string_basic", "cpp/tests/groupby/max_tests.cpp:127", K10, STR10B, "MAX", [1, 2, 3], ["año", "zit", "₹1"], value_type="STRING")
+case("MAX.string_zero_valid_values", "cpp/tests/groupby/max_tests.cpp:143", [1, 1, 1], [None, None, None], "MAX", [1], [None],
+     value_type="STRING")
 family("MEAN", "cpp/tests/groupby/mean_tests.cpp", [37, 57, 72, 87, 102], [3.0, 19.0 / 4, 17.0 / 3],
        [4.5, 14.0 / 3, 5.0, None], V11_A, NUMERIC)
 family("VARIANCE", "cpp/tests/groupby/var_tests.cpp", [24, 44, 60, 76, 92], [9.0, 131.0 / 12, 31.0 / 3],

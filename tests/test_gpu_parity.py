@@ -28,6 +28,7 @@ def check(keys, requests, policy=NullPolicy.EXCLUDE, row_filters=(), **opts):
 @pytest.mark.parametrize("variant", [0, 1, 3, 5])
 def test_benchmark_configs_match_oracle(config, n, variant):
     """Variants: 0 auto, 1 global table only, 3 hashed shared table, 5 the bulk-copy tile ring (C2)."""
+    H.PARITY_STATS.clear()
     w = workloads.make(config, n, scale_domain=(config in (3, 4)))
     check(w.keys, w.requests, w.null_policy, w.row_filters, table_variant=variant)
     H.record_parity_stats(f"C{config} {n} rows, table_variant {variant}")
@@ -36,6 +37,7 @@ def test_benchmark_configs_match_oracle(config, n, variant):
 def test_config1_full_size_10m_rows_against_the_oracle():
     """C1 at its full 10M rows: every group against the CPU oracle, strict 1e-12 wherever the sum is
     not cancelled below 1e-3 of Σ|x|."""
+    H.PARITY_STATS.clear()
     w = workloads.make(1)
     assert w.rows == 10_000_000
     got = check(w.keys, w.requests, w.null_policy, w.row_filters)
@@ -336,7 +338,9 @@ def test_error_statuses_mirror_the_reference():
     with pytest.raises(cb.UnsupportedError):
         gb.aggregate([cb.GroupByRequest(k, [agg.median()])])
     with pytest.raises(cb.UnsupportedError):
-        gb.aggregate([cb.GroupByRequest(s, [agg.min()])])
+        gb.aggregate([cb.GroupByRequest(s, [agg.nth_element(0)])])
+    # MIN / MAX of strings are served by the hash path (cpp/src/groupby/hash/hash_compound_agg_finalizer.cu:39-91)
+    assert gb.aggregate([cb.GroupByRequest(s, [agg.min()])])[1][0].columns()[0].size == 4
 
 
 def test_results_are_deterministic_for_integers():
@@ -413,3 +417,48 @@ def test_partitioned_path_few_rows_and_skew():
         k = HostColumn.from_numpy(np.where(rng.random(n) < 0.5, 7, rng.integers(0, 50_000, n)).astype(np.int64))
         v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.1)
         check([k], [(v, ALL_AGGS)], table_variant=6)
+
+
+# ------------------------------------------------------------------------------------ ARGMIN / ARGMAX, MIN / MAX of strings
+def test_argmin_argmax_and_string_min_max():
+    """Row-index accumulators (cpp/src/groupby/hash/extract_single_pass_aggs.cpp:39-60): the first row of the
+    extreme value wins on ties, so the result is the oracle's whatever the arrival order on the GPU."""
+    rng = np.random.default_rng(31)
+    n = 80_000
+    words = ["", "a", "aa", "año", "b", "日本", "日本語", "z" * 40, "ab", "abc", "abd", "Ab", "$1", "€1", "₹1"]
+    k = HostColumn.from_numpy(rng.integers(0, 700, n).astype(np.int32), valid=rng.random(n) > 0.05)
+    vi = HostColumn.from_numpy(rng.integers(-20, 20, n).astype(np.int16), valid=rng.random(n) > 0.3)      # many ties
+    vf = HostColumn.from_numpy(rng.integers(-50, 50, n).astype(np.float64) / 4)
+    vu = HostColumn.from_numpy(rng.integers(0, 2**63, n).astype(np.uint64) * np.uint64(2))
+    vs = HostColumn.from_strings([None if rng.random() < 0.2 else words[i] + words[j]
+                                  for i, j in zip(rng.integers(0, len(words), n), rng.integers(0, len(words), n))])
+    reqs = [(vi, [Kind.ARGMIN, Kind.ARGMAX, Kind.MIN, Kind.SUM, Kind.COUNT_VALID]), (vf, [Kind.ARGMAX, Kind.ARGMIN, Kind.MEAN]),
+            (vu, [Kind.ARGMIN, Kind.ARGMAX]), (vs, [Kind.MIN, Kind.MAX, Kind.ARGMIN, Kind.ARGMAX, Kind.COUNT_VALID])]
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        got = check([k], reqs, policy)
+        assert TypeId(got[1][3][0].type_id) == TypeId.STRING and TypeId(got[1][3][2].type_id) == TypeId.INT32
+    # string keys with string values, and an empty input
+    ks = HostColumn.from_strings([words[i] for i in rng.integers(0, len(words), n)])
+    check([ks, k], [(vs, [Kind.MAX, Kind.MIN]), (vi, [Kind.ARGMIN])], NullPolicy.INCLUDE)
+    empty = HostColumn.from_numpy(np.zeros(0, np.int32))
+    got = check([empty], [(HostColumn.from_strings([]), [Kind.MIN, Kind.ARGMAX])])
+    assert got[1][0][0].size == 0 and TypeId(got[1][0][0].type_id) == TypeId.STRING
+
+
+def test_row_index_accumulators_stay_inside_one_batch():
+    """A row index means nothing in another batch or on another rank: states refuse them."""
+    import cudf_b200 as cb
+    from cudf_b200 import aggregation as agg
+    from cudf_b200.groupby import GroupByState
+    rng = np.random.default_rng(32)
+    k = cb.Column.from_host(HostColumn.from_numpy(rng.integers(0, 10, 1000).astype(np.int32)))
+    v = cb.Column.from_host(HostColumn.from_numpy(rng.integers(0, 100, 1000).astype(np.int32)))
+    gb = cb.GroupBy(cb.Table([k]))
+    st = GroupByState(gb, [cb.GroupByRequest(v, [agg.argmin()])])
+    st.update()
+    with pytest.raises(cb.UnsupportedError):
+        st.update()
+    with pytest.raises(cb.UnsupportedError):
+        st.pack(2)
+    keys, res = st.finalize()
+    assert keys.num_rows() == 10
