@@ -1490,6 +1490,143 @@ void update_state(b2_groupby_state& st, const b2_groupby& gb, const b2_aggregati
   if (tmp.ctrl) cudaFreeAsync(tmp.ctrl, stream);
 }
 
+// ------------------------------------------------------------------------------ string keys through a dictionary
+// One-shot aggregates of many rows keyed on STRING columns (plus fixed-width ones): every string column is
+// first replaced by the slot index of its string in a dictionary table (k_dict_encode), so that the keys
+// pack into one 64-bit cell and the packed-key paths (fused shared-memory tables, the partitioned path)
+// serve the call; the finished id column of the result is turned back into strings by gathering the
+// representative rows.  Worth it while a column's distinct strings are few enough for its dictionary (and
+// the representatives' bytes) to stay cached: the table is tried at 2^22 slots, then once larger, then the
+// call goes the row-key way as before.  The groups and every result are the same either way.
+constexpr int64_t DICT_MIN_ROWS   = 1 << 21;
+constexpr int64_t DICT_FIRST_CAP  = 1 << 22;
+constexpr int64_t DICT_SECOND_CAP = 1 << 26;
+constexpr double DICT_MAX_LOAD    = 0.7;
+
+struct EncodedKeys {
+  bool active = false;
+  b2_groupby gb;                  // the caller's groupby with id columns in place of the string columns
+  std::vector<int> cols;          // key indices that were strings
+  std::vector<Scratch> tables;    // per such column: the dictionary {tag | representative row}
+  std::vector<Scratch> ids;       // per such column: UINT32 ids, element offset as the string column's
+};
+
+bool encode_string_keys(const b2_groupby& gb, cudaStream_t stream, EncodedKeys& ek)
+{
+  if (gb.table_variant != 0 && gb.table_variant != 8) return false;
+  const int64_t n = gb.keys[0].v.size;
+  if (n == 0 || (gb.table_variant == 0 && n < DICT_MIN_ROWS)) return false;
+  int bits = 0, nstr = 0;
+  for (const ColView& k : gb.keys) {
+    const b2_column_view& c = k.v;
+    if (c.type_id == B2_STRING) {
+      if (c.num_children < 1 || !c.children) return false;
+      bits += 32; ++nstr;
+    } else {
+      const int w = width_of(c.type_id);
+      if (w == 0 || is_float_t(c.type_id)) return false;
+      bits += 8 * w;
+    }
+    if (gb.null_policy == B2_NULL_INCLUDE && c.null_mask) ++bits;
+  }
+  if (nstr == 0 || bits > 64) return false;
+
+  Trace trace(stream);
+  Scratch ctrl(sizeof(DCtrl), stream);
+  ek.gb = gb;
+  for (size_t k = 0; k < gb.keys.size(); ++k) {
+    const b2_column_view& c = gb.keys[k].v;
+    if (c.type_id != B2_STRING) continue;
+    auto plan = std::make_unique<DPlan>();
+    std::memset(plan.get(), 0, sizeof(DPlan));
+    plan->nrows = n; plan->nkeys = 1; plan->key_mode = KM_ROWS; plan->stride = 1;
+    DKeyCol& kc = plan->keys[0];
+    kc.data = (const unsigned char*)c.data; kc.mask = c.null_mask; kc.offset = c.offset; kc.vclass = VC_STRING; kc.nullbit = -1;
+    const b2_column_view& o = c.children[0];
+    kc.offsets = (const unsigned char*)o.data + (size_t)o.offset * (o.type_id == B2_INT64 ? 8 : 4);
+    kc.offs64 = o.type_id == B2_INT64;
+
+    Scratch ids((size_t)(c.offset + n) * sizeof(u32), stream);
+    Scratch table;
+    int64_t cap = 1024;
+    while (cap < std::min<int64_t>(DICT_FIRST_CAP, std::max<int64_t>(n / 8, 1024))) cap *= 2;
+    bool done = false;
+    for (int attempt = 0; attempt < 2 && !done; ++attempt) {
+      if (attempt == 1) {
+        int64_t cap2 = cap;
+        while (cap2 < std::min<int64_t>(DICT_SECOND_CAP, 2 * n)) cap2 *= 2;
+        if (cap2 == cap) break;
+        cap = cap2;
+      }
+      table = Scratch((size_t)cap * sizeof(u64), stream);
+      CUDA_TRY(cudaMemsetAsync(table.p, 0xFF, (size_t)cap * sizeof(u64), stream));
+      DCtrl h{};
+      h.claim_limit = (u64)((double)cap * DICT_MAX_LOAD);
+      CUDA_TRY(cudaMemcpyAsync(ctrl.p, &h, sizeof(DCtrl), cudaMemcpyHostToDevice, stream));
+      const int grid = grid_for((n + DICT_ROWS - 1) / DICT_ROWS, DICT_BLOCK, 8);
+      k_dict_encode<<<grid, DICT_BLOCK, 0, stream>>>(*plan, (u64*)table.p, cap, (DCtrl*)ctrl.p, (u32*)ids.p);
+      CUDA_TRY(cudaGetLastError());
+      g_stats.kernel_launches++;
+      CUDA_TRY(cudaMemcpyAsync(&h, ctrl.p, sizeof(DCtrl), cudaMemcpyDeviceToHost, stream));
+      CUDA_TRY(cudaStreamSynchronize(stream));
+      done = h.overflow == 0;
+    }
+    if (!done) return false;
+    trace.mark("string key -> dictionary ids");
+
+    ColView& dst = ek.gb.keys[k];
+    b2_column_view v{};
+    v.type_id = B2_UINT32; v.size = c.size; v.data = ids.p; v.null_mask = c.null_mask; v.null_count = c.null_count; v.offset = c.offset;
+    dst = ColView(v);
+    ek.cols.push_back((int)k);
+    ek.tables.push_back(std::move(table));
+    ek.ids.push_back(std::move(ids));
+  }
+  ek.gb.table_variant = 0;
+  ek.active = true;
+  return true;
+}
+
+// The id key columns of a finished result become the STRING columns the caller asked for.
+void restore_string_keys(const EncodedKeys& ek, const b2_groupby& gb, cudaStream_t stream, b2_groupby_result* out)
+{
+  const b2_allocator al = resolve(&out->allocator);
+  const int64_t G = out->num_groups;
+  OwnedGuard guard{out};
+  for (size_t i = 0; i < ek.cols.size(); ++i) {
+    const int k = ek.cols[i];
+    b2_owned_column idc = out->keys[k];  // UINT32 ids (+ the null mask of the key under INCLUDE)
+    b2_owned_column& c = out->keys[k];
+    std::memset(&c, 0, sizeof(c));
+    c.type_id = B2_STRING;
+    c.size = (int32_t)G;
+    c.null_mask = idc.null_mask; c.null_mask_bytes = idc.null_mask_bytes; c.null_count = idc.null_count;
+    idc.null_mask = nullptr;
+    struct IdFree {
+      b2_owned_column& c; const b2_allocator& al; cudaStream_t s;
+      ~IdFree() { if (c.data) al.deallocate(c.data, c.data_bytes, s, al.ctx); }
+    } id_free{idc, al, stream};
+    if (G == 0) { empty_strings(c, al, stream); continue; }
+    const b2_column_view& src = gb.keys[(size_t)k].v;
+    DKeyCol kc{};
+    kc.data = (const unsigned char*)src.data; kc.mask = nullptr; kc.offset = src.offset; kc.vclass = VC_STRING; kc.nullbit = -1;
+    const b2_column_view& o = src.children[0];
+    kc.offsets = (const unsigned char*)o.data + (size_t)o.offset * (o.type_id == B2_INT64 ? 8 : 4);
+    kc.offs64 = o.type_id == B2_INT64;
+    Scratch rows((size_t)G * sizeof(int), stream);
+    k_dict_rows<<<grid_for(G, 256, 8), 256, 0, stream>>>((const u32*)idc.data, c.null_mask, (const u64*)ek.tables[i].p, G, (int*)rows.p);
+    CUDA_TRY(cudaGetLastError());
+    g_stats.kernel_launches++;
+    // the mask travels as it is: gather_strings must neither clear bits nor count (rows of null keys are -1)
+    u32* mask = c.null_mask;
+    c.null_mask = nullptr;
+    gather_strings(kc, (const int*)rows.p, G, c, nullptr, al, stream);
+    c.null_mask = mask;
+  }
+  CUDA_TRY(cudaStreamSynchronize(stream));  // the id columns and dictionaries are released behind this call
+  guard.armed = false;
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------------------ no-allocation variant
@@ -1664,10 +1801,14 @@ b2_status b2_groupby_aggregate(b2_groupby* gb, const b2_aggregation_request* req
     std::memset(out, 0, sizeof(*out));
     if (gb->keys.empty()) B2_FAIL(B2_LOGIC_ERROR, "groupby needs at least one key column");
     device_info();
-    std::unique_ptr<b2_groupby_state, void (*)(b2_groupby_state*)> st(make_state(*gb, requests, num_requests),
+    validate_requests(*gb, requests, num_requests);
+    EncodedKeys ek;
+    const b2_groupby& use = encode_string_keys(*gb, (cudaStream_t)stream, ek) ? ek.gb : *gb;
+    std::unique_ptr<b2_groupby_state, void (*)(b2_groupby_state*)> st(make_state(use, requests, num_requests),
                                                                       b2_state_destroy);
-    update_state(*st, *gb, requests, num_requests, (cudaStream_t)stream, /*may_partition=*/true);
+    update_state(*st, use, requests, num_requests, (cudaStream_t)stream, /*may_partition=*/true);
     finalize_state(*st, (cudaStream_t)stream, allocator, out);
+    if (ek.active) restore_string_keys(ek, *gb, (cudaStream_t)stream, out);
   });
 }
 

@@ -880,6 +880,73 @@ __global__ void __launch_bounds__(1024) k_hll(const __grid_constant__ DPlan P, u
     if (s_regs[i]) atomicMax(&regs[i], s_regs[i]);
 }
 
+// ------------------------------------------------------------------------------ string keys -> dictionary ids
+// A STRING key column is replaced by the slot index of its string in a dictionary table {tag | first row
+// seen}, so that (id, other keys) packs into one 64-bit key cell and the packed-key paths serve the
+// aggregate.  The table of a column with few distinct strings stays in L2, and so do the representatives'
+// bytes the probes compare against; the row's own string is read once, in row order.  `P` holds the one
+// string column as its only key.  ids[P.keys[0].offset + row] = slot (0 for a null row: its null bit or its
+// exclusion decides, not the payload).  CTAs stop at their next tile once the table is over its claim limit.
+constexpr int DICT_BLOCK = 256;
+constexpr int DICT_ROWS  = 4;  // rows per thread and tile, strided by the block so that loads coalesce
+
+__global__ void __launch_bounds__(DICT_BLOCK) k_dict_encode(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap,
+                                                            DCtrl* ctrl, u32* __restrict__ ids)
+{
+  __shared__ int s_new;
+  __shared__ u32 s_stop;
+  if (threadIdx.x == 0) { s_new = 0; s_stop = 0; }
+  __syncthreads();
+  const DKeyCol& c = P.keys[0];
+  constexpr i64 TILE = (i64)DICT_BLOCK * DICT_ROWS;
+  for (i64 base = (i64)blockIdx.x * TILE; base < P.nrows; base += (i64)gridDim.x * TILE) {
+    // offsets of the tile's rows first (one coalesced pass), then hash and probe row by row
+    i64 b[DICT_ROWS], e[DICT_ROWS];
+    bool live[DICT_ROWS];
+#pragma unroll
+    for (int j = 0; j < DICT_ROWS; ++j) {
+      const i64 row = base + (i64)j * DICT_BLOCK + threadIdx.x;
+      live[j] = row < P.nrows && !(c.mask && !bit_valid(c.mask, c.offset + row));
+      b[j] = e[j] = 0;
+      if (live[j]) { b[j] = str_offset(c, c.offset + row); e[j] = str_offset(c, c.offset + row + 1); }
+    }
+    u64 h[DICT_ROWS];
+#pragma unroll
+    for (int j = 0; j < DICT_ROWS; ++j) h[j] = live[j] ? mix64(hash_bytes(c.data + b[j], e[j] - b[j], 0x243F6A8885A308D3ull)) : 0;
+#pragma unroll
+    for (int j = 0; j < DICT_ROWS; ++j) {
+      const i64 row = base + (i64)j * DICT_BLOCK + threadIdx.x;
+      if (row >= P.nrows) continue;
+      u32 id = 0;
+      if (live[j]) {
+        const i64 s = gmem_find_insert_rows(P, tbl, cap, 1, row, h[j], ctrl, &s_new);
+        if (s >= 0) id = (u32)s;
+      }
+      ids[c.offset + row] = id;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int n = s_new;
+      s_new = 0;
+      if (n) {
+        const u64 tot = atomicAdd(&ctrl->nclaimed, (u64)n) + (u64)n;
+        if (tot > ctrl->claim_limit) ctrl->overflow = 1;
+      }
+      s_stop = *(volatile u32*)&ctrl->overflow;
+    }
+    __syncthreads();
+    if (s_stop) return;
+  }
+}
+
+// ids of the finished groups -> the representative rows of their strings (-1 for a null key)
+__global__ void k_dict_rows(const u32* __restrict__ ids, const u32* __restrict__ id_mask, const u64* __restrict__ tbl,
+                            i64 ngroups, int* __restrict__ rows)
+{
+  for (i64 g = (i64)blockIdx.x * blockDim.x + threadIdx.x; g < ngroups; g += (i64)gridDim.x * blockDim.x)
+    rows[g] = (id_mask && !bit_valid(id_mask, g)) ? -1 : (int)(u32)tbl[ids[g]];
+}
+
 // ------------------------------------------------------------------------------ finalize
 enum OutKind : int {
   OK_COUNT = 0,  // int32 from a count cell

@@ -154,7 +154,9 @@ typedef struct b2_groupby_options {
                                FLOAT32-mean kernel reads its tiles through registers (4) or
                                through the cp.async.bulk shared-memory ring (5); 6 = always
                                take the radix-partitioned path when the keys allow it (auto
-                               takes it from about half a million groups), 7 = never          */
+                               takes it from about half a million groups), 7 = never; 8 =
+                               auto, and STRING key columns are replaced by dictionary ids
+                               first whatever the row count (auto does so from 2M rows)       */
   int32_t shared_table_bytes; /* <= 0 = auto                                                   */
   /* Fused drop_nulls pre-filter (cpp/src/stream_compaction/drop_nulls.cu:56-96): a row takes
    * part only if it is valid in every one of these masks (bit i = row i, same bit layout and

@@ -25,9 +25,10 @@ def check(keys, requests, policy=NullPolicy.EXCLUDE, row_filters=(), **opts):
 
 
 @pytest.mark.parametrize("config,n", [(1, 400_000), (2, 600_000), (3, 300_000), (4, 500_000), (5, 120_000)])
-@pytest.mark.parametrize("variant", [0, 1, 3, 5])
+@pytest.mark.parametrize("variant", [0, 1, 3, 5, 8])
 def test_benchmark_configs_match_oracle(config, n, variant):
-    """Variants: 0 auto, 1 global table only, 3 hashed shared table, 5 the bulk-copy tile ring (C2)."""
+    """Variants: 0 auto, 1 global table only, 3 hashed shared table, 5 the bulk-copy tile ring (C2),
+    8 STRING keys through dictionary ids (C5)."""
     H.PARITY_STATS.clear()
     w = workloads.make(config, n, scale_domain=(config in (3, 4)))
     check(w.keys, w.requests, w.null_policy, w.row_filters, table_variant=variant)
@@ -73,8 +74,42 @@ def test_two_string_key_columns():
     k3 = HostColumn.from_numpy(rng.integers(0, 3, n).astype(np.int16))
     v = HostColumn.from_numpy(rng.standard_normal(n).astype(np.float32), valid=rng.random(n) > 0.2)
     for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
-        got = check([s1, s2, k3], [(v, ALL_AGGS)], policy)
-        assert got[0][0].size == (len(words) + (policy == NullPolicy.INCLUDE)) * 4 * 3
+        for variant in (0, 8):
+            got = check([s1, s2, k3], [(v, ALL_AGGS)], policy, table_variant=variant)
+            assert got[0][0].size == (len(words) + (policy == NullPolicy.INCLUDE)) * 4 * 3
+
+
+def test_string_keys_through_dictionary_ids():
+    """table_variant 8: every STRING key column is replaced by dictionary ids before the packed-key
+    aggregate and gathered back afterwards.  A dictionary that outgrows its first table (60K distinct strings
+    in 200K rows), a sliced nullable column under both policies, INT64 offsets, an all-null column."""
+    import cudf_b200 as cb
+    rng = np.random.default_rng(61)
+    n = 200_000
+    pool = [("k%05d" % i) * (1 + i % 4) for i in range(60_000)]
+    s = HostColumn.from_strings([pool[i] for i in rng.integers(0, len(pool), n)])
+    k2 = HostColumn.from_numpy(rng.integers(0, 3, n).astype(np.int8))
+    v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.1)
+    w = HostColumn.from_numpy(rng.integers(-9, 9, n).astype(np.int64))
+    reqs = [(v, ALL_AGGS), (w, [Kind.SUM, Kind.MIN, Kind.MAX, Kind.COUNT_ALL])]
+    got = check([s, k2], reqs, table_variant=8)
+    assert cb.last_call_stats().kernel_launches >= 4     # two dictionary attempts + the aggregate
+    assert got[0][0].size > 100_000
+    # a slice (element offset 5) of a nullable column with INT64 offsets
+    m = 50_000
+    words = ["", "x", "xy", "año", "日本語", "q" * 70]
+    full = HostColumn.from_strings([None if rng.random() < 0.1 else words[i] for i in rng.integers(0, len(words), m + 9)],
+                                   large_offsets=True)
+    sl = HostColumn(TypeId.STRING, m, full.data, full.mask, 5, full.offsets)
+    kk = HostColumn.from_numpy(rng.integers(0, 4, m).astype(np.int32), valid=rng.random(m) > 0.05)
+    vv = HostColumn.from_numpy(rng.integers(-1000, 1000, m).astype(np.int32), valid=rng.random(m) > 0.2)
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        got = check([kk, sl], [(vv, [Kind.SUM, Kind.MEAN, Kind.MIN, Kind.MAX, Kind.COUNT_VALID])], policy, table_variant=8)
+        assert got[0][0].size == (len(words) + (policy == NullPolicy.INCLUDE)) * (4 + (policy == NullPolicy.INCLUDE))
+    nothing = HostColumn.from_strings([None] * 1000)
+    one = HostColumn.from_numpy(np.ones(1000, np.int32))
+    assert check([nothing], [(one, [Kind.SUM])], NullPolicy.EXCLUDE, table_variant=8)[0][0].size == 0
+    assert check([nothing], [(one, [Kind.SUM])], NullPolicy.INCLUDE, table_variant=8)[0][0].size == 1
 
 
 def test_config2_full_domain_uses_compact_shared_table():
