@@ -291,6 +291,7 @@ struct Schema {  // everything that is fixed by (key types, requests): cells and
   std::vector<int> req_nouts;
   std::vector<int> req_val;  // request → value column slot
   bool f32mean = false;      // cells == {Σ of a FLOAT32 column, n of it}: compact shared-memory layout
+  bool fixed = false;        // cells ⊆ {Σx, n, Σx²} of ONE float column: fixed-point shared-memory layout
   bool has_arg = false;      // some cell holds a row index (ARGMIN / ARGMAX, MIN / MAX of strings): such cells
                              // live in the global table of ONE aggregate call only (no shared-memory copies,
                              // no partial records: a row index means nothing outside its batch)
@@ -495,6 +496,13 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
   if ((int)sc.outs.size() > MAX_OUTS) B2_FAIL(B2_UNSUPPORTED, "more than 64 aggregations in one aggregate call");
   sc.f32mean = sc.key_mode == KM_PACKED && sc.ncells == 2 && sc.cells[0].op == OP_SUM_F && sc.cells[1].op == OP_CNT_V &&
                sc.cells[0].col == sc.cells[1].col && sc.val_types[sc.cells[0].col] == B2_FLOAT32;
+  if (sc.key_mode == KM_PACKED && !sc.f32mean && sc.nvals == 1 && is_float_t(sc.val_types[0]) && sc.ncells >= 1) {
+    sc.fixed = true;
+    for (int c = 0; c < sc.ncells; ++c) {
+      const int op = sc.cells[c].op;
+      sc.fixed = sc.fixed && (op == OP_SUM_F || op == OP_CNT_V || op == OP_SSQ_F);
+    }
+  }
   return sc;
 }
 
@@ -587,6 +595,7 @@ void bind_plan_inputs(DPlan& P, const Schema& sc, const b2_groupby& gb, const b2
     const DValCol& vc = P.vals[sc.cells[0].col];
     if (!vc.mask || ((uintptr_t)vc.mask % 16 == 0 && vc.offset % 128 == 0)) P.flags |= PF_BULK;
   }
+  if (sc.fixed) P.flags |= PF_FIXED;
 }
 
 // ------------------------------------------------------------------------------ table management
@@ -750,10 +759,16 @@ SharedPlan plan_shared(const b2_groupby_state& st, const b2_groupby& gb)
   if (gb.table_variant == 1 || sc.has_arg) return sp;
   const int budget = gb.shared_table_bytes > 0 ? std::min(gb.shared_table_bytes, device_info().smem_optin - 1024)
                                                : device_info().smem_optin - 1024;
-  const int cell_bytes = sc.f32mean ? 8 : 8 * sc.ncells;  // accumulators of one slot
+  // the fixed-point layout needs the sampled magnitude of the values, which only tables with a dense
+  // region get (variants 1 and 3 have none); variant 2 keeps the generic 8-byte cells for comparison
+  const bool fixed = sc.fixed && gb.table_variant != 2 && gb.table_variant != 3 && P.nrows >= SAMPLE_ROWS;
+  int fixed_arrays = 0;
+  for (int c = 0; c < sc.ncells; ++c) fixed_arrays += sc.cells[c].op == OP_SUM_F || sc.cells[c].op == OP_SSQ_F;
+  // accumulators of one slot
+  const int cell_bytes = sc.f32mean ? 8 : fixed ? 4 + 4 * FX_LIMBS * fixed_arrays : 8 * sc.ncells;
   sp.S = budget / (8 + cell_bytes) - 1;                   // hashed mode: key cell + accumulators
   if (sp.S < 256) { sp.S = 0; return sp; }
-  sp.layout = sc.f32mean ? SL_F32MEAN : SL_GENERIC;
+  sp.layout = sc.f32mean ? SL_F32MEAN : fixed ? SL_FIXED : SL_GENERIC;
   sp.fill_limit = (int)(sp.S * SMEM_FILL);
   sp.smem = (size_t)budget;
   if (sc.key_mode != KM_PACKED || gb.table_variant == 3) return sp;
@@ -828,6 +843,7 @@ bool run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
   if (sc.key_mode == KM_PACKED) {
     if (sp.layout == SL_F32MEAN) launch_aggregate<KM_PACKED, SL_F32MEAN>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream, cap_dense, (u32)st.dense_slots, 0);
     else if (sp.layout == SL_GENERIC) launch_aggregate<KM_PACKED, SL_GENERIC>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream, cap_dense, (u32)st.dense_slots);
+    else if (sp.layout == SL_FIXED) launch_aggregate<KM_PACKED, SL_FIXED>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream, cap_dense, (u32)st.dense_slots);
     else launch_aggregate<KM_PACKED, SL_NONE>(P, st.table, st.cap, st.ctrl, 0, 0, 0, stream);
   } else {
     if (sp.layout == SL_GENERIC) launch_aggregate<KM_ROWS, SL_GENERIC>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream);
@@ -907,22 +923,54 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
   u64* d_hist = (u64*)counters.p;
   u32* d_hll  = (u32*)(d_hist + TOP);
   const int cgrid = (int)std::max<int64_t>(1, std::min<int64_t>((P.nrows + 4 * RP_BLOCK - 1) / (4 * RP_BLOCK), (int64_t)sms * 2));
-  if (hint > 0) k_rp_count<false><<<cgrid, RP_BLOCK, 0, stream>>>(P, d_hist, d_hll);
-  else k_rp_count<true><<<cgrid, RP_BLOCK, 0, stream>>>(P, d_hist, d_hll);
+  // skewed inputs: the hottest keys of a Σx / n / Σx² aggregate are folded by the counting pass itself
+  const bool with_hot = sc.fixed && gb.table_variant != 2;
+  Scratch hot_mem;
+  DHot hot{};
+  if (with_hot) {
+    const size_t b_ckeys = (size_t)HOT_COUNT_SLOTS * 8, b_ccnt = (size_t)HOT_COUNT_SLOTS * 4, b_keys = (size_t)HOT_SLOTS * 8,
+                 b_ids = (size_t)HOT_SLOTS * 2, b_info = 16, b_acc = (size_t)HOT_MAX * HOT_ACC_WORDS * 8;
+    hot_mem = Scratch(b_ckeys + b_keys + b_ccnt + b_ids + b_info + b_acc, stream);
+    unsigned char* m = (unsigned char*)hot_mem.p;
+    u64* ckeys = (u64*)m;
+    hot.keys = (u64*)(m + b_ckeys);
+    u32* ccnt = (u32*)(m + b_ckeys + b_keys);
+    hot.ids = (unsigned short*)(m + b_ckeys + b_keys + b_ccnt);
+    hot.info = (u32*)(m + b_ckeys + b_keys + b_ccnt + b_ids);
+    hot.acc = (u64*)(m + b_ckeys + b_keys + b_ccnt + b_ids + b_info);
+    CUDA_TRY(cudaMemsetAsync(m, 0xFF, b_ckeys + b_keys, stream));
+    CUDA_TRY(cudaMemsetAsync(ccnt, 0, b_ccnt + b_ids + b_info + b_acc, stream));
+    k_hot_sample<<<sms, 256, 0, stream>>>(P, ckeys, ccnt, hot.info);
+    k_hot_select<<<1, 1024, 0, stream>>>(ckeys, ccnt, hot);
+    CUDA_TRY(cudaGetLastError());
+    g_stats.kernel_launches += 2;
+    static thread_local size_t configured[2][64] = {};
+    allow_shared(k_rp_count<false, true>, rp_count_hot_smem(), configured[0]);
+    allow_shared(k_rp_count<true, true>, rp_count_hot_smem(), configured[1]);
+    if (hint > 0) k_rp_count<false, true><<<std::min(cgrid, sms), RP_BLOCK, rp_count_hot_smem(), stream>>>(P, d_hist, d_hll, hot);
+    else k_rp_count<true, true><<<std::min(cgrid, sms), RP_BLOCK, rp_count_hot_smem(), stream>>>(P, d_hist, d_hll, hot);
+  } else if (hint > 0) {
+    k_rp_count<false, false><<<cgrid, RP_BLOCK, 0, stream>>>(P, d_hist, d_hll, hot);
+  } else {
+    k_rp_count<true, false><<<cgrid, RP_BLOCK, 0, stream>>>(P, d_hist, d_hll, hot);
+  }
   CUDA_TRY(cudaGetLastError());
   g_stats.kernel_launches++;
   std::vector<u64> h_hist(TOP);
   std::vector<u32> h_hll(HLL_REGS);
   CUDA_TRY(cudaMemcpyAsync(h_hist.data(), d_hist, (size_t)TOP * 8, cudaMemcpyDeviceToHost, stream));
   if (hint <= 0) CUDA_TRY(cudaMemcpyAsync(h_hll.data(), d_hll, (size_t)HLL_REGS * 4, cudaMemcpyDeviceToHost, stream));
+  u32 h_hot[2] = {0, 0};  // number of hot keys, exponent info
+  if (with_hot) CUDA_TRY(cudaMemcpyAsync(h_hot, hot.info, sizeof(h_hot), cudaMemcpyDeviceToHost, stream));
   CUDA_TRY(cudaStreamSynchronize(stream));
-  int64_t active = 0;
+  const int nhot = (int)h_hot[0];
+  int64_t active = 0;  // rows that go through the partitions (the rows of hot keys are folded already)
   for (u64 c : h_hist) active += (int64_t)c;
   int64_t est = hint > 0 ? hint : hll_estimate(h_hll.data());
   est = std::max<int64_t>(1, std::min(est, active));
   if (estimate) *estimate = est;
   trace.mark("partition: histogram + estimate");
-  if (active == 0) return false;
+  if (active == 0 && nhot == 0) return false;
   if (!forced && est < RP_MIN_GROUPS) return false;
   // Heavy skew (one key holding several per cent of the rows) would put that key's rows into one bucket
   // and serialise them on one shared-memory slot: the fused pass with its hot-key cache serves such inputs.
@@ -933,7 +981,7 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
   }
 
   // 2. digits: buckets of about half a shared-memory table each (two CTAs of the aggregate kernel per SM)
-  const int slot_bytes = 8 * (1 + sc.ncells);
+  const int slot_bytes = with_hot ? RPA_FIXED_SLOT_BYTES : 8 * (1 + sc.ncells);
   int budget = std::min((device_info().smem_optin - 2048), 110 * 1024);
   if (gb.shared_table_bytes > 0) budget = std::min(budget, std::max(gb.shared_table_bytes, 257 * slot_bytes));
   int slots = 256;
@@ -971,14 +1019,16 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
     u64* d_cur1   = d_start1 + F1 + 1;
     CUDA_TRY(cudaMemcpyAsync(d_start1, h_start.data(), (size_t)(F1 + 1) * 8, cudaMemcpyHostToDevice, stream));
     CUDA_TRY(cudaMemcpyAsync(d_cur1, h_start.data(), (size_t)F1 * 8, cudaMemcpyHostToDevice, stream));
-    Scratch recA((size_t)words * (size_t)active * 8, stream);
+    Scratch recA((size_t)words * (size_t)std::max<int64_t>(active, 1) * 8, stream);
     DScatter D1{DRecords{(u64*)recA.p, active, words, valid_word}, d_cur1, 64 - b1, F1};
     const int sgrid = (int)std::max<int64_t>(1, std::min<int64_t>((P.nrows + RP_TILE - 1) / RP_TILE, (int64_t)sms * 2));
+    const bool simple = sc.nvals == 1 && valid_word < 0;
+    const size_t scatter_smem = (nhot > 0 && simple) ? rp_scatter_hot_offset(F1) + (size_t)HOT_SLOTS * 8 : rp_tile_smem(F1);
     {
       static thread_local size_t configured[64] = {};
-      allow_shared(k_rp_scatter, rp_tile_smem(F1), configured);
+      allow_shared(k_rp_scatter, scatter_smem, configured);
     }
-    k_rp_scatter<<<sgrid, RPS_BLOCK, rp_tile_smem(F1), stream>>>(P, D1);
+    k_rp_scatter<<<sgrid, RPS_BLOCK, scatter_smem, stream>>>(P, D1, nhot > 0 ? hot.keys : nullptr);
     CUDA_TRY(cudaGetLastError());
     g_stats.kernel_launches++;
     trace.mark("partition: level-1 scatter");
@@ -1004,7 +1054,7 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
       CUDA_TRY(cudaGetLastError());
       device_exclusive_scan((const i64*)d_hist2, nbuckets, (i64*)d_start2, stream);
       CUDA_TRY(cudaMemcpyAsync(d_cur2, d_start2, (size_t)nbuckets * 8, cudaMemcpyDeviceToDevice, stream));
-      recB = Scratch((size_t)words * (size_t)active * 8, stream);
+      recB = Scratch((size_t)words * (size_t)std::max<int64_t>(active, 1) * 8, stream);
       DScatter D2{DRecords{(u64*)recB.p, active, words, valid_word}, d_cur2, shift2, F2};
       {
         static thread_local size_t configured[64] = {};
@@ -1020,7 +1070,7 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
     }
 
     // 5. one shared-memory aggregate per bucket
-    const int64_t gcap = std::min<int64_t>(active, (int64_t)((double)est * (hint > 0 ? 1.25 : 1.08)) + 65536);
+    const int64_t gcap = std::min<int64_t>(active, (int64_t)((double)est * (hint > 0 ? 1.25 : 1.08)) + 65536) + HOT_MAX;
     Scratch groups((size_t)(1 + sc.ncells) * (size_t)gcap * 8, stream);
     if (!st.ctrl) {
       st.ctrl = (DCtrl*)default_alloc(sizeof(DCtrl), stream, nullptr);
@@ -1031,11 +1081,22 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
     CUDA_TRY(cudaMemsetAsync(work.p, 0, 8, stream));
     DBuckets B{src, b_start, b_end, nbuckets, slots, (u64*)groups.p, gcap, (u64*)work.p};
     const size_t smem = (size_t)(slots + 1) * slot_bytes;
-    static thread_local size_t configured[64] = {};
-    allow_shared(k_rp_aggregate, smem, configured);
-    k_rp_aggregate<<<(int)std::min<int64_t>(nbuckets, (int64_t)sms * 2), RPA_BLOCK, smem, stream>>>(P, B, st.ctrl);
+    static thread_local size_t configured[2][64] = {};
+    const int agrid = (int)std::min<int64_t>(nbuckets, (int64_t)sms * 2);
+    if (with_hot) {
+      allow_shared(k_rp_aggregate<true>, smem, configured[1]);
+      k_rp_aggregate<true><<<agrid, RPA_BLOCK, smem, stream>>>(P, B, st.ctrl, hot.info + 1);
+    } else {
+      allow_shared(k_rp_aggregate<false>, smem, configured[0]);
+      k_rp_aggregate<false><<<agrid, RPA_BLOCK, smem, stream>>>(P, B, st.ctrl, nullptr);
+    }
     CUDA_TRY(cudaGetLastError());
     g_stats.kernel_launches++;
+    if (nhot > 0) {
+      k_rp_append_hot<<<HOT_SLOTS / 256, 256, 0, stream>>>(P, hot, (u64*)groups.p, gcap, st.ctrl);
+      CUDA_TRY(cudaGetLastError());
+      g_stats.kernel_launches++;
+    }
     cudaEventRecord(ev.b, stream);
     st.ctrl_fresh = false;
     read_ctrl(st, stream);
@@ -1046,8 +1107,8 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
       else cudaGetLastError();
     }
     if (getenv("B2_TRACE"))
-      fprintf(stderr, "[b2] partitioned: %lld active rows, estimate %lld groups, digits %d + %d, %d slots per bucket, %lld groups, overflow %d\n",
-              (long long)active, (long long)est, b1, b2, slots, (long long)st.host_ctrl.out_cursor, (int)st.host_ctrl.overflow);
+      fprintf(stderr, "[b2] partitioned: %lld rows through the partitions, %d hot keys, estimate %lld groups, digits %d + %d, %d slots per bucket, %lld groups, overflow %d\n",
+              (long long)active, nhot, (long long)est, b1, b2, slots, (long long)st.host_ctrl.out_cursor, (int)st.host_ctrl.overflow);
     if (st.host_ctrl.overflow) return false;
     st.groups = std::move(groups);
     st.groups_cap = gcap;
@@ -1110,7 +1171,7 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
                 (t[1] > t[0] ? t[1] - t[0] : 0) * 1e-3, ((t[1] > t[0] ? t[2] - t[1] : t[2] - t[0])) * 1e-3, (t[3] - t[2]) * 1e-3,
                 (t[4] - t[3]) * 1e-3);
       }
-      if (getenv("B2_TRACE")) fprintf(stderr, "[b2] attempt %d cap %lld kernel %.3f ms overflow %d claimed %llu\n", attempt, (long long)cap, ms, (int)st.host_ctrl.overflow, (unsigned long long)st.host_ctrl.nclaimed);
+      if (getenv("B2_TRACE")) fprintf(stderr, "[b2] attempt %d cap %lld kernel %.3f ms overflow %d claimed %llu, rows folded in shared memory %llu, in the global table %llu\n", attempt, (long long)cap, ms, (int)st.host_ctrl.overflow, (unsigned long long)st.host_ctrl.nclaimed, (unsigned long long)st.host_ctrl.stat_smem_rows, (unsigned long long)st.host_ctrl.stat_gmem_rows);
     }
     if (!st.host_ctrl.overflow) break;
     if (cap >= full) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow at full capacity");

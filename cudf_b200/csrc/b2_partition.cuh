@@ -55,25 +55,211 @@ __device__ __forceinline__ void rp_keys4(const DPlan& P, i64 row0, int nv, u64 (
   }
 }
 
-// ------------------------------------------------------------------------------ level-1 histogram (+ HyperLogLog)
-template <bool WITH_HLL>
-__global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant__ DPlan P, u64* __restrict__ hist,
-                                                       u32* __restrict__ hll)
+
+// ------------------------------------------------------------------------------ hot keys (skewed inputs)
+// A key that holds a visible share of the rows would put all its records into one bucket and serialise them
+// on one shared-memory slot.  For aggregates whose cells are Σx / n / Σx² of one float column the hottest
+// keys are therefore taken out before the rows are partitioned:
+//   k_hot_sample   256K evenly spaced rows -> occurrences per key (a global counting table), and the
+//                  largest magnitude among the sampled values (places the fixed-point windows)
+//   k_hot_select   the keys seen most often (at most HOT_MAX, at least 3 times each) -> the hot set: an
+//                  open-addressing table of HOT_SLOTS key cells and a dense id per key
+//   k_rp_count<..., HOT>  folds the rows of hot keys into per-CTA fixed-point accumulators (fx_split /
+//                  fx_add: native 32-bit shared-memory atomics, which keep their rate on hot addresses) and
+//                  counts only the other rows into the digit histogram; k_rp_scatter skips hot rows
+//   k_rp_append_hot  the hot keys' finished cells -> the group list
+// Hot and cold keys are disjoint, so the list is the union of both parts.
+constexpr int HOT_SAMPLES    = 1 << 18;
+constexpr int HOT_COUNT_SLOTS = 1 << 19;  // counting table of the sampler
+constexpr int HOT_MAX        = 2048;      // keys in the hot set
+constexpr int HOT_SLOTS      = 4096;      // its table (load <= 1/2)
+constexpr u32 HOT_MIN_COUNT  = 3;         // occurrences among the samples that make a key hot
+constexpr int HOT_ACC_WORDS  = 4;         // global accumulators per hot key: n, Σx, Σx², seen
+
+struct DHot {
+  u64* keys;        // [HOT_SLOTS] hot-set table, EMPTY = free
+  unsigned short* ids;  // [HOT_SLOTS] dense id of the key in the same slot
+  u32* info;        // [0] number of hot keys, [1] 1 + largest biased exponent among the sampled values
+  u64* acc;         // [HOT_MAX][HOT_ACC_WORDS] finished accumulators (filled by k_rp_count)
+};
+
+__device__ __forceinline__ int hot_find(const u64* hk, u64 key, u64 h)
 {
+  u32 idx = (u32)h & (HOT_SLOTS - 1);
+  for (int p = 0; p < HOT_SLOTS; ++p) {
+    const u64 k = hk[idx];
+    if (k == key) return (int)idx;
+    if (k == EMPTY) return -1;
+    idx = (idx + 1u) & (HOT_SLOTS - 1);
+  }
+  return -1;
+}
+
+__global__ void __launch_bounds__(256) k_hot_sample(const __grid_constant__ DPlan P, u64* __restrict__ ckeys,
+                                                    u32* __restrict__ ccnt, u32* __restrict__ info)
+{
+  const i64 nsamp  = P.nrows < HOT_SAMPLES ? P.nrows : HOT_SAMPLES;
+  const i64 stride = P.nrows / (nsamp > 0 ? nsamp : 1);
+  u32 emax = 0;
+  for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < nsamp; i += (i64)gridDim.x * blockDim.x) {
+    const i64 row = i * stride + (stride > 1 ? (i64)(((u64)i * 7919ull) % (u64)stride) : 0);
+    if (!row_active(P, row)) continue;
+    const u64 key = pack_key(P, row);
+    if (key != EMPTY) {
+      u32 idx = (u32)(rp_hash(key) >> 20) & (HOT_COUNT_SLOTS - 1);
+      for (int p = 0; p < 64; ++p) {  // (a sample that finds no slot in 64 probes is dropped: it is only a sample)
+        u64 k = ckeys[idx];
+        if (k == EMPTY) {
+          k = atomicCAS(ckeys + idx, EMPTY, key);
+          if (k == EMPTY) k = key;
+        }
+        if (k == key) { atomicAdd(ccnt + idx, 1u); break; }
+        idx = (idx + 1u) & (HOT_COUNT_SLOTS - 1);
+      }
+    }
+    if (value_valid(P.vals[0], row)) {
+      const u32 e = (u32)((load_value(P.vals[0], row) >> 52) & 0x7FFu);
+      if (e != 0x7FFu && e + 1u > emax) emax = e + 1u;
+    }
+  }
+  emax = __reduce_max_sync(0xFFFFFFFFu, emax);
+  if ((threadIdx.x & 31) == 0 && emax) atomicMax(info + 1, emax);
+}
+
+// single CTA of 1024 threads; `hot.keys` arrives filled with EMPTY, `hot.info[0]` zero
+__global__ void __launch_bounds__(1024) k_hot_select(const u64* __restrict__ ckeys, const u32* __restrict__ ccnt, DHot hot)
+{
+  __shared__ u32 s_hist[256];   // keys per (clamped) count
+  __shared__ u32 s_min, s_n;
+  if (threadIdx.x < 256) s_hist[threadIdx.x] = 0;
+  if (threadIdx.x == 0) s_n = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < HOT_COUNT_SLOTS; i += blockDim.x) {
+    const u32 c = ccnt[i];
+    if (c >= HOT_MIN_COUNT) atomicAdd(&s_hist[c < 255u ? c : 255u], 1u);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    // the smallest count from which on at most HOT_MAX keys qualify
+    u32 total = 0, t = 256;
+    while (t > HOT_MIN_COUNT && total + s_hist[t - 1] <= (u32)HOT_MAX) { --t; total += s_hist[t]; }
+    s_min = t;
+  }
+  __syncthreads();
+  const u32 tmin = s_min;
+  for (int i = threadIdx.x; i < HOT_COUNT_SLOTS; i += blockDim.x) {
+    const u32 c = ccnt[i];
+    if (c < tmin || (c < 255u ? c : 255u) < tmin) continue;
+    const u64 key = ckeys[i];
+    const u32 id = atomicAdd(&s_n, 1u);
+    if (id >= (u32)HOT_MAX) continue;  // (cannot happen: tmin bounds the number of qualifying keys)
+    u32 idx = (u32)rp_hash(key) & (HOT_SLOTS - 1);
+    for (;;) {
+      const u64 old = atomicCAS(hot.keys + idx, EMPTY, key);
+      if (old == EMPTY) { hot.ids[idx] = (unsigned short)id; break; }
+      idx = (idx + 1u) & (HOT_SLOTS - 1);  // terminates: at most HOT_MAX keys in HOT_SLOTS slots
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) hot.info[0] = s_n < (u32)HOT_MAX ? s_n : (u32)HOT_MAX;
+}
+
+// ------------------------------------------------------------------------------ level-1 histogram (+ HyperLogLog)
+// With HOT the kernel also carries the hot set (dynamic shared memory: keys, ids, then per hot key an
+// addend count, the limbs of Σx and of Σx², and a "seen" bit): rows of hot keys are folded here and left out
+// of the histogram.  P.cells are Σx / n / Σx² of value column 0 in that case.
+constexpr size_t rp_count_hot_smem() { return (size_t)HOT_SLOTS * 10 + (size_t)HOT_MAX * (4 + 8 * FX_LIMBS) + HOT_MAX / 8; }
+
+template <bool WITH_HLL, bool HOT>
+__global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant__ DPlan P, u64* __restrict__ hist,
+                                                       u32* __restrict__ hll, const DHot hot)
+{
+  extern __shared__ __align__(16) unsigned char rp_hot_smem[];
   __shared__ u32 s_hist[1 << RP_BITS_TOP];
   __shared__ u32 s_regs[WITH_HLL ? HLL_REGS : 1];
+  u64* hk = (u64*)rp_hot_smem;                              // [HOT_SLOTS]
+  unsigned short* hid = (unsigned short*)(hk + HOT_SLOTS);  // [HOT_SLOTS]
+  u32* hcnt = (u32*)(hid + HOT_SLOTS);                      // [HOT_MAX]
+  int* hlx  = (int*)(hcnt + HOT_MAX);                       // [FX_LIMBS][HOT_MAX]
+  int* hlq  = hlx + FX_LIMBS * HOT_MAX;                     // [FX_LIMBS][HOT_MAX]
+  u32* hseen = (u32*)(hlq + FX_LIMBS * HOT_MAX);            // [HOT_MAX / 32]
+  int nh = 0, bx = FX_NEVER, bq = FX_NEVER;
   for (int i = threadIdx.x; i < (1 << RP_BITS_TOP); i += blockDim.x) s_hist[i] = 0;
   if (WITH_HLL) for (int i = threadIdx.x; i < HLL_REGS; i += blockDim.x) s_regs[i] = 0;
+  if (HOT) {
+    nh = (int)hot.info[0];
+    if (hot.info[1]) {
+      const int emax = (int)hot.info[1] - 1;
+      bx = emax + FX_HEADROOM - FX_MAX_SHIFT;
+      bq = 2 * emax - 1023 + 1 + 2 * FX_HEADROOM - FX_MAX_SHIFT;
+    }
+    if (nh > 0) {
+      for (int i = threadIdx.x; i < HOT_SLOTS; i += blockDim.x) { hk[i] = hot.keys[i]; hid[i] = hot.ids[i]; }
+      for (int i = threadIdx.x; i < HOT_MAX * (1 + 2 * FX_LIMBS) + HOT_MAX / 32; i += blockDim.x) hcnt[i] = 0;
+    }
+  }
   __syncthreads();
+  int c_sum = -1, c_cnt = -1, c_ssq = -1;
+  if (HOT)
+    for (int c = 0; c < P.ncells; ++c) {
+      if (P.cells[c].op == OP_SUM_F) c_sum = c;
+      if (P.cells[c].op == OP_CNT_V) c_cnt = c;
+      if (P.cells[c].op == OP_SSQ_F) c_ssq = c;
+    }
   const i64 nquads = (P.nrows + 3) / 4;
   for (i64 q = (i64)blockIdx.x * blockDim.x + threadIdx.x; q < nquads; q += (i64)gridDim.x * blockDim.x) {
     u64 kk[4];
     u32 act;
-    rp_keys4(P, q * 4, (int)min((i64)4, P.nrows - q * 4), kk, act);
+    const int nv = (int)min((i64)4, P.nrows - q * 4);
+    rp_keys4(P, q * 4, nv, kk, act);
+    u64 hh[4];
+    int hs[4];
+    u32 hotm = 0;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      if (!((act >> j) & 1u)) continue;
-      atomicAdd(&s_hist[rp_hash(kk[j]) >> (64 - RP_BITS_TOP)], 1u);
+      hh[j] = rp_hash(kk[j]);
+      hs[j] = -1;
+      if (HOT && nh > 0 && ((act >> j) & 1u) && kk[j] != EMPTY) {
+        hs[j] = hot_find(hk, kk[j], hh[j]);
+        if (hs[j] >= 0) hotm |= 1u << j;
+      }
+    }
+    if (HOT && hotm) {
+      const DValCol& vc = P.vals[0];
+      u32 vn = hotm;
+      if (vc.mask) vn &= valid_nibble(vc.mask, vc.offset + q * 4, nv);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (!((hotm >> j) & 1u)) continue;
+        const int id = (int)hid[hs[j]];
+        if (!((hseen[id >> 5] >> (id & 31)) & 1u)) atomicOr(&hseen[id >> 5], 1u << (id & 31));
+        if (!((vn >> j) & 1u)) continue;
+        const u64 xb = load_value(vc, q * 4 + j);
+        const double d = __longlong_as_double((i64)xb);
+        int qx = 0, qq = 0;
+        u32 lx[4], lq[4];
+        bool fits = c_sum < 0 || fx_split(xb, bx, qx, lx);
+        if (fits && c_ssq >= 0) fits = fx_split((u64)__double_as_longlong(d * d), bq, qq, lq);
+        u64* acc = hot.acc + (size_t)id * HOT_ACC_WORDS;
+        if (!fits) {  // outside the fixed-point window: straight to the fp64 accumulators
+          atomicAdd(acc, 1ull);
+          if (c_sum >= 0) atomicAdd((double*)(acc + 1), d);
+          if (c_ssq >= 0) atomicAdd((double*)(acc + 2), d * d);
+          continue;
+        }
+        if (c_sum >= 0) fx_add(hlx, HOT_MAX, id, (xb >> 63) != 0, qx, lx);
+        if (c_ssq >= 0) fx_add(hlq, HOT_MAX, id, false, qq, lq);
+        const u32 old = atomicAdd(hcnt + id, 1u);
+        if (((old + 1u) & (FX_FLUSH - 1u)) == 0u) {
+          if (c_sum >= 0) atomicAdd((double*)(acc + 1), fx_take(hlx, HOT_MAX, id, bx));
+          if (c_ssq >= 0) atomicAdd((double*)(acc + 2), fx_take(hlq, HOT_MAX, id, bq));
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (!((act >> j) & 1u) || ((hotm >> j) & 1u)) continue;
+      atomicAdd(&s_hist[hh[j] >> (64 - RP_BITS_TOP)], 1u);
       if (WITH_HLL) {
         const u64 h = mix64(kk[j] ^ 0x5bd1e9955bd1e995ull);  // same registers as k_hll
         const u32 idx  = (u32)(h >> (64 - HLL_BITS));
@@ -88,6 +274,39 @@ __global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant_
   if (WITH_HLL)
     for (int i = threadIdx.x; i < HLL_REGS; i += blockDim.x)
       if (s_regs[i]) atomicMax(&hll[i], s_regs[i]);
+  if (HOT && nh > 0) {
+    // CTAs start at different ids so that they do not all hit the same accumulators at once
+    const int rot = (int)(((u64)blockIdx.x * 2654435761ull) % (u64)nh);
+    for (int i0 = threadIdx.x; i0 < nh; i0 += blockDim.x) {
+      const int id = i0 + rot < nh ? i0 + rot : i0 + rot - nh;
+      u64* acc = hot.acc + (size_t)id * HOT_ACC_WORDS;
+      const u32 n = hcnt[id];
+      if (n) {
+        atomicAdd(acc, (u64)n);
+        if (c_sum >= 0) atomicAdd((double*)(acc + 1), fx_take(hlx, HOT_MAX, id, bx));
+        if (c_ssq >= 0) atomicAdd((double*)(acc + 2), fx_take(hlq, HOT_MAX, id, bq));
+      }
+      if (((hseen[id >> 5] >> (id & 31)) & 1u) && acc[3] == 0) acc[3] = 1;
+    }
+  }
+}
+
+// the hot keys' finished cells join the group list (one thread per hot-set slot)
+__global__ void k_rp_append_hot(const __grid_constant__ DPlan P, const DHot hot, u64* __restrict__ out, i64 out_cap, DCtrl* ctrl)
+{
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= HOT_SLOTS) return;
+  const u64 key = hot.keys[i];
+  if (key == EMPTY) return;
+  const u64* acc = hot.acc + (size_t)hot.ids[i] * HOT_ACC_WORDS;
+  if (acc[3] == 0) return;  // sampled, but no participating row (cannot happen with samples taken from the rows)
+  const u64 g = atomicAdd(&ctrl->out_cursor, 1ull);
+  if (g >= (u64)out_cap) { ctrl->overflow = 1; return; }
+  out[g] = key;
+  for (int c = 0; c < P.ncells; ++c) {
+    const int op = P.cells[c].op;
+    out[(i64)(1 + c) * out_cap + g] = op == OP_CNT_V ? acc[0] : op == OP_SUM_F ? acc[1] : acc[2];
+  }
 }
 
 // ------------------------------------------------------------------------------ records
@@ -123,7 +342,7 @@ struct RpTile {
   unsigned short* dig;  // [RP_TILE] digit of every staged record
   unsigned short* src;  // [RP_TILE] position of the record inside the source tile (records of other shapes)
 };
-constexpr size_t rp_tile_smem(int fan) { return (size_t)fan * 4 + (size_t)(fan + 1) * 4 + (size_t)fan * 8 + (size_t)RP_TILE * (8 + 8 + 2 + 2) + 64; }
+__host__ __device__ constexpr size_t rp_tile_smem(int fan) { return (size_t)fan * 4 + (size_t)(fan + 1) * 4 + (size_t)fan * 8 + (size_t)RP_TILE * (8 + 8 + 2 + 2) + 64; }
 
 __device__ __forceinline__ RpTile rp_tile_carve(unsigned char* smem, int fan)
 {
@@ -166,17 +385,27 @@ __device__ __forceinline__ void rp_tile_plan(const RpTile& t, u64* cursors, int 
 }
 
 // level 1: input rows -> records in the region of their digit
-__global__ void __launch_bounds__(RPS_BLOCK, 2) k_rp_scatter(const __grid_constant__ DPlan P, const DScatter D)
+// (`hot_keys`: the hot-set table whose keys k_rp_count folded already — their rows are left out here.  The
+// table is copied into the staging array of the values when that is unused (records of other shapes than
+// "one value column without nulls"), else behind the staging arrays: HOT_SLOTS * 8 more bytes of dynamic
+// shared memory.)
+__host__ __device__ constexpr size_t rp_scatter_hot_offset(int fan) { return (rp_tile_smem(fan) + 15) & ~(size_t)15; }
+
+__global__ void __launch_bounds__(RPS_BLOCK, 2) k_rp_scatter(const __grid_constant__ DPlan P, const DScatter D,
+                                                          const u64* __restrict__ hot_keys)
 {
   extern __shared__ __align__(16) unsigned char rp_stage[];
   const RpTile t = rp_tile_carve(rp_stage, D.fan);
-  for (int i = threadIdx.x; i < D.fan; i += blockDim.x) t.hist[i] = 0;
-  __syncthreads();
-  const i64 ntiles = (P.nrows + RP_TILE - 1) / RP_TILE;
-  const u32 dmask = (u32)D.fan - 1u;
   // one value column without nulls is the common case: its values are loaded together with the keys and
   // staged with them; other shapes stage the key and the row, and gather the value words at copy-out
   const bool simple = P.nvals == 1 && D.dst.valid_word < 0;
+  static_assert(HOT_SLOTS <= RP_TILE, "the hot-set table fits the staging array of the values");
+  u64* hk = simple ? (u64*)(rp_stage + rp_scatter_hot_offset(D.fan)) : t.vals;
+  for (int i = threadIdx.x; i < D.fan; i += blockDim.x) t.hist[i] = 0;
+  if (hot_keys) for (int i = threadIdx.x; i < HOT_SLOTS; i += blockDim.x) hk[i] = hot_keys[i];
+  __syncthreads();
+  const i64 ntiles = (P.nrows + RP_TILE - 1) / RP_TILE;
+  const u32 dmask = (u32)D.fan - 1u;
   for (i64 tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
     const i64 tile0 = tile * RP_TILE;
     u64 kk[RP_ROWS], vv[RP_ROWS];
@@ -201,7 +430,9 @@ __global__ void __launch_bounds__(RPS_BLOCK, 2) k_rp_scatter(const __grid_consta
     for (int j = 0; j < RP_ROWS; ++j) {
       rank[j] = 0;
       if ((act >> j) & 1u) {
-        const u32 d = (u32)(rp_hash(kk[j]) >> D.shift) & dmask;
+        const u64 h = rp_hash(kk[j]);
+        if (hot_keys && kk[j] != EMPTY && hot_find(hk, kk[j], h) >= 0) { act &= ~(1u << j); continue; }
+        const u32 d = (u32)(h >> D.shift) & dmask;
         rank[j] = (d << 16) | atomicAdd(&t.hist[d], 1u);  // a tile holds 4096 rows: the rank fits 16 bits
       }
     }
@@ -386,7 +617,15 @@ struct DBuckets {
   u64* next_bucket;  // work counter
 };
 
-__global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_constant__ DPlan P, const DBuckets B, DCtrl* ctrl)
+// FIXED (the cells are Σx / n / Σx² of one float column): a slot keeps its sums as fixed-point limbs plus one
+// fp64 cell each for what does not fit the limbs' window (and for the limbs' periodic flushes), and its count
+// as 32 bits — nine native 32-bit atomics per record instead of three 64-bit ones, which shared memory only
+// does as compare-and-swap loops.  `vexp` = 1 + the largest biased exponent among the sampled values.
+constexpr int RPA_FIXED_SLOT_BYTES = 8 + 8 + 8 + 4 + 8 * FX_LIMBS;
+
+template <bool FIXED>
+__global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_constant__ DPlan P, const DBuckets B, DCtrl* ctrl,
+                                                            const u32* __restrict__ vexp)
 {
   extern __shared__ __align__(16) unsigned char rp_smem[];
   __shared__ i64 s_bucket;
@@ -397,6 +636,26 @@ __global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_cons
   const int NS = S + 1;
   u64* skeys  = (u64*)rp_smem;   // [NS]
   u64* scells = skeys + NS;      // [ncells][NS]
+  // FIXED: [NS] fp64 Σx beside the limbs, [NS] the same for Σx², [NS] counts, limbs of Σx, limbs of Σx²
+  double* fex = (double*)scells;
+  double* feq = fex + NS;
+  u32* fcnt   = (u32*)(feq + NS);
+  int* flx    = (int*)(fcnt + NS);
+  int* flq    = flx + FX_LIMBS * NS;
+  int fx_bx = FX_NEVER, fx_bq = FX_NEVER, c_sum = -1, c_cnt = -1, c_ssq = -1;
+  if (FIXED) {
+    const u32 ve = __ldg(vexp);
+    if (ve) {
+      const int emax = (int)ve - 1;
+      fx_bx = emax + FX_HEADROOM - FX_MAX_SHIFT;
+      fx_bq = 2 * emax - 1023 + 1 + 2 * FX_HEADROOM - FX_MAX_SHIFT;
+    }
+    for (int c = 0; c < P.ncells; ++c) {
+      if (P.cells[c].op == OP_SUM_F) c_sum = c;
+      if (P.cells[c].op == OP_CNT_V) c_cnt = c;
+      if (P.cells[c].op == OP_SSQ_F) c_ssq = c;
+    }
+  }
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const u32 smask = (u32)S - 1u;
   // a bucket whose groups fill the table beyond this gives up (the caller falls back to the global table)
@@ -412,9 +671,14 @@ __global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_cons
     if (hi <= lo) continue;
     // clear the table
     for (int i = threadIdx.x; i < NS; i += blockDim.x) skeys[i] = EMPTY;
-    for (int c = 0; c < P.ncells; ++c) {
-      const u64 id = cell_identity(P.cells[c].op);
-      for (int i = threadIdx.x; i < NS; i += blockDim.x) scells[(size_t)c * NS + i] = id;
+    if (FIXED) {
+      for (int i = threadIdx.x; i < 2 * NS; i += blockDim.x) scells[i] = 0;                       // fex, feq
+      for (int i = threadIdx.x; i < (1 + 2 * FX_LIMBS) * NS; i += blockDim.x) fcnt[i] = 0;        // fcnt, flx, flq
+    } else {
+      for (int c = 0; c < P.ncells; ++c) {
+        const u64 id = cell_identity(P.cells[c].op);
+        for (int i = threadIdx.x; i < NS; i += blockDim.x) scells[(size_t)c * NS + i] = id;
+      }
     }
     __syncthreads();
     // fold the records, RPA_BATCH per thread at a time: all loads of a batch are issued before the first
@@ -465,8 +729,34 @@ __global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_cons
       // once per record), and each update is ONE predicated atomic for the whole warp.  (Diverged,
       // each lane's atomics were issued on their own: 11.5 of 32 lanes active on average.)
       __syncwarp();
+      if (FIXED) {
+#pragma unroll
+        for (int j = 0; j < RPA_BATCH; ++j) {
+          if (slots[j] < 0 || !(vbits[j] & 1ull)) continue;
+          const int s = slots[j];
+          const u64 xb = vals[j];
+          const double d = __longlong_as_double((i64)xb);
+          int qx = 0, qq = 0;
+          u32 lx[4], lq[4];
+          bool fits = c_sum < 0 || fx_split(xb, fx_bx, qx, lx);
+          if (fits && c_ssq >= 0) fits = fx_split((u64)__double_as_longlong(d * d), fx_bq, qq, lq);
+          if (!fits) {
+            if (c_sum >= 0) atomicAdd(fex + s, d);
+            if (c_ssq >= 0) atomicAdd(feq + s, d * d);
+            atomicAdd(fcnt + s, 1u);
+            continue;
+          }
+          if (c_sum >= 0) fx_add(flx, NS, s, (xb >> 63) != 0, qx, lx);
+          if (c_ssq >= 0) fx_add(flq, NS, s, false, qq, lq);
+          const u32 old = atomicAdd(fcnt + s, 1u);
+          if (((old + 1u) & (FX_FLUSH - 1u)) == 0u) {
+            if (c_sum >= 0) atomicAdd(fex + s, fx_take(flx, NS, s, fx_bx));
+            if (c_ssq >= 0) atomicAdd(feq + s, fx_take(flq, NS, s, fx_bq));
+          }
+        }
+      }
       int cur = one_col ? 0 : -1;
-      for (int c = 0; c < P.ncells; ++c) {
+      for (int c = 0; !FIXED && c < P.ncells; ++c) {
         const int op = P.cells[c].op, col = P.cells[c].col;
         if (op != OP_CNT_A && col != cur) {  // (the cells of a value column are adjacent)
           cur = col;
@@ -523,7 +813,13 @@ __global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_cons
       if (occ) {
         const i64 g = (i64)s_outbase + run + before + __popc(m & ((1u << lane) - 1u));
         B.out[g] = i < S ? skeys[i] : EMPTY;
-        for (int c = 0; c < P.ncells; ++c) B.out[(i64)(1 + c) * B.out_cap + g] = scells[(size_t)c * NS + i];
+        if (FIXED) {
+          if (c_cnt >= 0) B.out[(i64)(1 + c_cnt) * B.out_cap + g] = (u64)fcnt[i];
+          if (c_sum >= 0) B.out[(i64)(1 + c_sum) * B.out_cap + g] = (u64)__double_as_longlong(fex[i] + fx_take(flx, NS, i, fx_bx));
+          if (c_ssq >= 0) B.out[(i64)(1 + c_ssq) * B.out_cap + g] = (u64)__double_as_longlong(feq[i] + fx_take(flq, NS, i, fx_bq));
+        } else {
+          for (int c = 0; c < P.ncells; ++c) B.out[(i64)(1 + c) * B.out_cap + g] = scells[(size_t)c * NS + i];
+        }
       }
       run += total;
       __syncthreads();

@@ -25,9 +25,11 @@ def check(keys, requests, policy=NullPolicy.EXCLUDE, row_filters=(), **opts):
 
 
 @pytest.mark.parametrize("config,n", [(1, 400_000), (2, 600_000), (3, 300_000), (4, 500_000), (5, 120_000)])
-@pytest.mark.parametrize("variant", [0, 1, 3, 5, 8])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 5, 6, 8])
 def test_benchmark_configs_match_oracle(config, n, variant):
-    """Variants: 0 auto, 1 global table only, 3 hashed shared table, 5 the bulk-copy tile ring (C2),
+    """Variants: 0 auto (C1 / C4: float sums as fixed-point limbs in shared memory), 1 global table only,
+    2 auto with 8-byte shared-memory cells, 3 hashed shared table, 5 the bulk-copy tile ring (C2),
+    6 the partitioned path whatever the size (C4: with its hot keys folded by the counting pass),
     8 STRING keys through dictionary ids (C5)."""
     H.PARITY_STATS.clear()
     w = workloads.make(config, n, scale_domain=(config in (3, 4)))
@@ -77,6 +79,32 @@ def test_two_string_key_columns():
         for variant in (0, 8):
             got = check([s1, s2, k3], [(v, ALL_AGGS)], policy, table_variant=variant)
             assert got[0][0].size == (len(words) + (policy == NullPolicy.INCLUDE)) * 4 * 3
+
+
+@pytest.mark.parametrize("variant", [0, 2, 6])
+@pytest.mark.parametrize("vtype", ["f64", "f32"])
+def test_float_sums_as_fixed_point_limbs(variant, vtype):
+    """Σx / n / Σx² of one float column: shared-memory sums are kept as fixed-point limbs (variant 0: the fused
+    kernel; variant 6: the hot keys of the partitioned path; variant 2: 8-byte cells for comparison).  Skewed keys,
+    values of both signs, zeros, denormals, and magnitudes far outside the window the sampled maximum places —
+    those take the fp64 cells of the global table, and the result must not care."""
+    rng = np.random.default_rng(77)
+    n = 300_000
+    ranks = np.minimum((rng.pareto(1.1, n) * 3).astype(np.int64), 200_000)
+    k = HostColumn.from_numpy(ranks * 7919 % 1_000_003)
+    x = rng.standard_normal(n) * np.exp(rng.standard_normal(n) * 2)
+    x[rng.random(n) < 0.01] = 0.0
+    x[rng.random(n) < 0.002] *= 1e-30      # far below the window
+    x[rng.random(n) < 0.002] *= 1e25       # far above it
+    x[rng.random(n) < 0.0005] = 5e-324     # denormal
+    if vtype == "f32":
+        x = x.astype(np.float32)
+    v = HostColumn.from_numpy(x, valid=rng.random(n) > 0.05)
+    aggs = [Kind.SUM, Kind.COUNT_VALID, Kind.MEAN, Kind.SUM_OF_SQUARES, Kind.VARIANCE]
+    check([k], [(v, aggs)], table_variant=variant)
+    check([k], [(v, [Kind.SUM])], table_variant=variant)                       # Σx alone, no count cell
+    k_few = HostColumn.from_numpy(rng.integers(0, 50, n).astype(np.int32))     # a dense key box
+    check([k_few], [(v, aggs)], table_variant=variant)
 
 
 def test_string_keys_through_dictionary_ids():
