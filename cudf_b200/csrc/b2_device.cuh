@@ -102,10 +102,8 @@ enum PlanFlags : int {
   PF_VEC_VAL0 = 2,  // value column 0 likewise (compact FLOAT32 layout)
   PF_FAST     = 4,  // every key column is 4 or 8 bytes wide and every mask / filter offset is a
                     // multiple of 4, so the validity bits of 4 consecutive rows never straddle a mask word
-  PF_BULK     = 8,  // value column 0's validity can be tiled with 16-byte-aligned bulk copies: mask
+  PF_BULK     = 8   // value column 0's validity can be tiled with 16-byte-aligned bulk copies: mask
                     // pointer 16-byte aligned and offset a multiple of 128 bits (or no mask at all)
-  PF_FIXED    = 16  // the cells are Σx / n / Σx² of one float column: the key-box sampler also looks at the
-                    // magnitude of the values (fixed-point shared-memory layout)
 };
 
 // Dense key mapping of one aggregate pass, derived on the device by sample_dense_box: when the keys
@@ -117,7 +115,7 @@ struct DDense {
   u32 total;               // slots of one copy = product of ranges
   u32 copies;              // replicas of the table in shared memory (warp w uses copy w % copies):
                            // few groups mean many rows per slot, and same-address atomics serialise
-  u32 vexp;                // SL_FIXED: 1 + the largest biased exponent among the sampled values (0 = none)
+  u32 pad;
   i64 min[MAX_KEYS];
   u64 range[MAX_KEYS];     // includes one extra value for "null" on nullable INCLUDE columns
   u32 mult[MAX_KEYS];

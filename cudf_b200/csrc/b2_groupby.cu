@@ -291,7 +291,7 @@ struct Schema {  // everything that is fixed by (key types, requests): cells and
   std::vector<int> req_nouts;
   std::vector<int> req_val;  // request → value column slot
   bool f32mean = false;      // cells == {Σ of a FLOAT32 column, n of it}: compact shared-memory layout
-  bool fixed = false;        // cells ⊆ {Σx, n, Σx²} of ONE float column: fixed-point shared-memory layout
+  bool fixed = false;        // cells ⊆ {Σx, n, Σx²} of ONE float column: the partitioned path folds hot keys and keeps fixed-point cells
   bool has_arg = false;      // some cell holds a row index (ARGMIN / ARGMAX, MIN / MAX of strings): such cells
                              // live in the global table of ONE aggregate call only (no shared-memory copies,
                              // no partial records: a row index means nothing outside its batch)
@@ -595,7 +595,6 @@ void bind_plan_inputs(DPlan& P, const Schema& sc, const b2_groupby& gb, const b2
     const DValCol& vc = P.vals[sc.cells[0].col];
     if (!vc.mask || ((uintptr_t)vc.mask % 16 == 0 && vc.offset % 128 == 0)) P.flags |= PF_BULK;
   }
-  if (sc.fixed) P.flags |= PF_FIXED;
 }
 
 // ------------------------------------------------------------------------------ table management
@@ -759,16 +758,10 @@ SharedPlan plan_shared(const b2_groupby_state& st, const b2_groupby& gb)
   if (gb.table_variant == 1 || sc.has_arg) return sp;
   const int budget = gb.shared_table_bytes > 0 ? std::min(gb.shared_table_bytes, device_info().smem_optin - 1024)
                                                : device_info().smem_optin - 1024;
-  // the fixed-point layout needs the sampled magnitude of the values, which only tables with a dense
-  // region get (variants 1 and 3 have none); variant 2 keeps the generic 8-byte cells for comparison
-  const bool fixed = sc.fixed && gb.table_variant != 2 && gb.table_variant != 3 && P.nrows >= SAMPLE_ROWS;
-  int fixed_arrays = 0;
-  for (int c = 0; c < sc.ncells; ++c) fixed_arrays += sc.cells[c].op == OP_SUM_F || sc.cells[c].op == OP_SSQ_F;
-  // accumulators of one slot
-  const int cell_bytes = sc.f32mean ? 8 : fixed ? 4 + 4 * FX_LIMBS * fixed_arrays : 8 * sc.ncells;
+  const int cell_bytes = sc.f32mean ? 8 : 8 * sc.ncells;  // accumulators of one slot
   sp.S = budget / (8 + cell_bytes) - 1;                   // hashed mode: key cell + accumulators
   if (sp.S < 256) { sp.S = 0; return sp; }
-  sp.layout = sc.f32mean ? SL_F32MEAN : fixed ? SL_FIXED : SL_GENERIC;
+  sp.layout = sc.f32mean ? SL_F32MEAN : SL_GENERIC;
   sp.fill_limit = (int)(sp.S * SMEM_FILL);
   sp.smem = (size_t)budget;
   if (sc.key_mode != KM_PACKED || gb.table_variant == 3) return sp;
@@ -843,7 +836,6 @@ bool run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
   if (sc.key_mode == KM_PACKED) {
     if (sp.layout == SL_F32MEAN) launch_aggregate<KM_PACKED, SL_F32MEAN>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream, cap_dense, (u32)st.dense_slots, 0);
     else if (sp.layout == SL_GENERIC) launch_aggregate<KM_PACKED, SL_GENERIC>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream, cap_dense, (u32)st.dense_slots);
-    else if (sp.layout == SL_FIXED) launch_aggregate<KM_PACKED, SL_FIXED>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream, cap_dense, (u32)st.dense_slots);
     else launch_aggregate<KM_PACKED, SL_NONE>(P, st.table, st.cap, st.ctrl, 0, 0, 0, stream);
   } else {
     if (sp.layout == SL_GENERIC) launch_aggregate<KM_ROWS, SL_GENERIC>(P, st.table, st.cap, st.ctrl, sp.S, sp.fill_limit, sp.smem, stream);

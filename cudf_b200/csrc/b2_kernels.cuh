@@ -42,21 +42,20 @@ constexpr int GMEM_PROBES    = 2048;  // probe limit of the global table before 
 constexpr u32 F32_SPILL_AT   = 1024;  // packed {f32 sum, u32 n} cells spill to fp64 at this count
 constexpr int SLOT_NONE      = -1;
 
-enum SmemLayout : int { SL_NONE = 0, SL_GENERIC = 1, SL_F32MEAN = 2, SL_FIXED = 3 };
+enum SmemLayout : int { SL_NONE = 0, SL_GENERIC = 1, SL_F32MEAN = 2 };
 
-// SL_FIXED: Σx (and Σx²) of one FLOAT32 / FLOAT64 column held in shared memory as fixed-point limbs.
-// 64-bit shared-memory atomics (the fp64 adds of SL_GENERIC among them) are compare-and-swap loops in
-// hardware terms: 420 G adds/s per GPU on spread-out addresses, 33 G/s when an eighth of them hit one
-// slot (hot keys), against 2.2 T/s and 1.2 T/s for native 32-bit adds.  So a sum is kept as FX_LIMBS
-// signed 32-bit words, word i counting units of 2^(B + 18 i): a value's 53-bit mantissa, shifted to its
-// place, is cut into at most four 18-bit pieces and each piece added to its word with one native atomic.
-// The pieces add up exactly — no rounding happens until a slot is flushed, which converts its words to
-// one double (one rounding for up to FX_FLUSH addends) and adds that to the fp64 cell of the global
-// table.  Every FX_FLUSH-th addend of a slot flushes it, so that no word overflows.  B comes from the
-// largest magnitude among the sampled rows (k_table_init): a value whose bits do not fit the 108-bit
-// window (zero fits; denormals, infinities, NaN and values more than 2^FX_HEADROOM above or about 2^47
-// below the sampled maximum do not) takes the global table's fp64 cells instead, so the result does not
-// depend on the sample — only the speed does.
+// ------------------------------------------------------------------------------ float sums as fixed-point limbs
+// 64-bit shared-memory atomics (fp64 adds among them) run as compare-and-swap loops: measured 420 G adds/s
+// per GPU on spread-out addresses and 33 G/s when an eighth of them hit one slot (hot keys), against 2.2 T/s
+// and 1.2 T/s for native 32-bit adds.  The partitioned path therefore keeps Σx and Σx² of a float column as
+// FX_LIMBS signed 32-bit words per slot, word i counting units of 2^(B - 1075 + 18 i): a value's 53-bit
+// mantissa, shifted to its place, is cut into at most four 18-bit pieces and each piece is added to its word
+// with one native atomic.  The pieces add up exactly; nothing is rounded until a slot is emptied (fx_take),
+// which turns its words into one double.  Every FX_FLUSH-th addend of a slot empties it, so that no word
+// overflows.  B comes from the largest magnitude among sampled rows: a value whose bits do not fit the
+// 108-bit window (zero fits; denormals, infinities, NaN and values more than 2^FX_HEADROOM above or about
+// 2^47 below the sampled maximum do not) is added to an fp64 cell instead, so the result does not depend
+// on the sample — only the speed does.
 constexpr int FX_LIMB_BITS = 18;
 constexpr int FX_LIMBS     = 6;
 constexpr int FX_MAX_SHIFT = FX_LIMB_BITS * (FX_LIMBS - 4) + FX_LIMB_BITS - 1;  // 53: four pieces end in the last word
@@ -64,25 +63,27 @@ constexpr int FX_HEADROOM  = 6;     // the window reaches 2^6 above the sampled 
 constexpr u32 FX_FLUSH     = 2048;  // addends of a slot between flushes: (2048 + rows in flight) * 2^18 < 2^31
 constexpr int FX_NEVER     = 1 << 20;  // window base with which no value fits (nothing was sampled)
 
-// pieces of |x| in units of 2^(B - 1075); false when x does not fit the window that starts at B
+// pieces of |x| in units of 2^(B - 1075), piece i for word q + i; false when x does not fit the window that
+// starts at B.  32-bit arithmetic throughout: the mantissa as chunks of 18 + 18 + 17 bits, shifted by r < 18.
 __device__ __forceinline__ bool fx_split(u64 bits, int B, int& q, u32 (&l)[4])
 {
-  const int e = (int)((bits >> 52) & 0x7FFu);
+  const u32 lo = (u32)bits, hi = (u32)(bits >> 32);
+  const int e = (int)((hi >> 20) & 0x7FFu);
   if (e == 0) {  // zero adds nothing; denormals go the slow way
     q = 0; l[0] = l[1] = l[2] = l[3] = 0;
     return (bits << 1) == 0;
   }
   const int shift = e - B;
   if (e == 0x7FF || shift < 0 || shift > FX_MAX_SHIFT) return false;
-  const u64 M  = (bits & 0xFFFFFFFFFFFFFull) | (1ull << 52);
-  q            = (shift * 57) >> 10;  // shift / 18 for 0 <= shift < 64
-  const int r  = shift - FX_LIMB_BITS * q;
-  const u64 lo = M << r;
-  const u32 hi = r > 11 ? (u32)(M >> (64 - r)) : 0u;
-  l[0] = (u32)lo & 0x3FFFFu;
-  l[1] = (u32)(lo >> 18) & 0x3FFFFu;
-  l[2] = (u32)(lo >> 36) & 0x3FFFFu;
-  l[3] = (u32)(lo >> 54) | (hi << 10);
+  q = (shift * 57) >> 10;  // shift / 18 for 0 <= shift < 64
+  const int r = shift - FX_LIMB_BITS * q, rr = FX_LIMB_BITS - r;  // 1 <= rr <= 18
+  const u32 m0 = lo & 0x3FFFFu;
+  const u32 m1 = __funnelshift_r(lo, hi, 18) & 0x3FFFFu;
+  const u32 m2 = ((hi & 0xFFFFFu) | 0x100000u) >> 4;
+  l[0] = (m0 << r) & 0x3FFFFu;
+  l[1] = ((m1 << r) | (m0 >> rr)) & 0x3FFFFu;
+  l[2] = ((m2 << r) | (m1 >> rr)) & 0x3FFFFu;
+  l[3] = m2 >> rr;
   return true;
 }
 __device__ __forceinline__ void fx_add(int* limbs, int ns, int slot, bool neg, int q, const u32 (&l)[4])
@@ -333,9 +334,7 @@ constexpr int SAMPLE_PER_THREAD = SAMPLE_ROWS / 256;
 __device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, DDense* out)
 {
   __shared__ i64 s_min[MAX_KEYS], s_max[MAX_KEYS];
-  __shared__ u32 s_vexp;
   if (threadIdx.x < MAX_KEYS) { s_min[threadIdx.x] = 0x7FFFFFFFFFFFFFFFll; s_max[threadIdx.x] = (i64)0x8000000000000000ull; }
-  if (threadIdx.x == 0) s_vexp = 0;
   __syncthreads();
   const i64 nsamp  = P.nrows < SAMPLE_ROWS ? P.nrows : SAMPLE_ROWS;
   const i64 stride = P.nrows / (nsamp > 0 ? nsamp : 1);
@@ -390,19 +389,6 @@ __device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, 
       }
       if ((threadIdx.x & 31) == 0 && lo <= hi) { atomicMin(&s_min[k], lo); atomicMax(&s_max[k], hi); }
     }
-    if (P.flags & PF_FIXED) {
-      // the largest finite magnitude among the samples of value column 0 places the fixed-point windows
-      const DValCol& vc = P.vals[0];
-      u32 emax = 0;
-#pragma unroll
-      for (int j = 0; j < SAMPLE_PER_THREAD; ++j) {
-        if (!((ok >> j) & 1u) || !value_valid(vc, rows[j])) continue;
-        const u32 e = (u32)((load_value(vc, rows[j]) >> 52) & 0x7FFu);
-        if (e != 0x7FFu && e + 1u > emax) emax = e + 1u;
-      }
-      emax = __reduce_max_sync(0xFFFFFFFFu, emax);
-      if ((threadIdx.x & 31) == 0 && emax) atomicMax(&s_vexp, emax);
-    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -411,7 +397,7 @@ __device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, 
     D.enabled = 0;
     D.total   = 0;
     D.copies  = 1;
-    D.vexp    = s_vexp;
+    D.pad     = 0;
     bool ok   = P.key_mode == KM_PACKED && nsamp >= SAMPLE_ROWS && cap_slots > 0;
     for (int pass = 0; pass < 2 && ok && !D.enabled; ++pass) {  // pass 0: padded box, pass 1: tight box
       u64 total = 1;
@@ -494,7 +480,6 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
     for (int i = tid; i < (int)(sizeof(DDense) / 4); i += blockDim.x) ((u32*)&s_dense)[i] = ((const u32*)&ctrl->dense)[i];
   } else if (tid == 0) {
     s_dense.enabled = 0;
-    s_dense.vexp = 0;
   }
   if (tid == 0) { s_fill = 0; s_new = 0; s_cache_on = (LAYOUT != SL_NONE); s_abort = 0; s_hit = 0; s_miss = 0; }
   __syncthreads();
@@ -516,31 +501,9 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
   float* ssum = (float*)scells;                            // SL_F32MEAN: [NS] fp32 partial sums
   u32* scnt   = (u32*)(ssum + NS);                         // SL_F32MEAN: [NS] counts
   u32* socc   = (u32*)(scells + (size_t)(LAYOUT == SL_F32MEAN ? 1 : P.ncells) * NS);  // dense mode: occupancy bits
-  // SL_FIXED: [NS] addend counts, then FX_LIMBS words of Σx per slot (limb-major), then the same for Σx²
-  int fx_sum = -1, fx_cnt = -1, fx_ssq = -1;  // cells of the plan
-  if (LAYOUT == SL_FIXED)
-    for (int c = 0; c < P.ncells; ++c) {
-      if (P.cells[c].op == OP_SUM_F) fx_sum = c;
-      if (P.cells[c].op == OP_CNT_V) fx_cnt = c;
-      if (P.cells[c].op == OP_SSQ_F) fx_ssq = c;
-    }
-  const int fx_arrays = (fx_sum >= 0 ? 1 : 0) + (fx_ssq >= 0 ? 1 : 0);
-  u32* fcnt  = (u32*)scells;
-  int* flx   = (int*)(fcnt + NS);                                  // Σx limbs (when fx_sum >= 0)
-  int* flq   = flx + (fx_sum >= 0 ? (size_t)FX_LIMBS * NS : 0);    // Σx² limbs (when fx_ssq >= 0)
-  if (LAYOUT == SL_FIXED) socc = (u32*)(flx + (size_t)fx_arrays * FX_LIMBS * NS);
-  int fx_bx = FX_NEVER, fx_bq = FX_NEVER;  // window bases of x and x² (biased exponents of limb 0's unit)
-  if (LAYOUT == SL_FIXED && s_dense.vexp) {
-    const int emax = (int)s_dense.vexp - 1;
-    fx_bx = emax + FX_HEADROOM - FX_MAX_SHIFT;
-    fx_bq = 2 * emax - 1023 + 1 + 2 * FX_HEADROOM - FX_MAX_SHIFT;
-  }
-
   if (LAYOUT != SL_NONE) {
     if (!dense) for (int i = tid; i < NS; i += blockDim.x) skeys[i] = EMPTY;
-    if (LAYOUT == SL_FIXED) {
-      for (int i = tid; i < (1 + fx_arrays * FX_LIMBS) * NS; i += blockDim.x) fcnt[i] = 0;
-    } else if (LAYOUT == SL_GENERIC) {
+    if (LAYOUT == SL_GENERIC) {
       for (int c = 0; c < P.ncells; ++c) {
         const u64 id = cell_identity(P.cells[c].op);
         for (int i = tid; i < NS; i += blockDim.x) scells[(size_t)c * NS + i] = id;
@@ -746,48 +709,6 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
         }
       }
     } else {
-      if (LAYOUT == SL_FIXED && act) {
-        // rows with a shared-memory slot: the value's pieces into the slot's limbs; a value that does not
-        // fit the window sends its row to the global table instead (below, with the rows that missed)
-        const DValCol& vc = P.vals[0];
-        u32 vn = act;
-        if (vc.mask) vn &= valid_nibble(vc.mask, vc.offset + row0, nv);
-        u64 xb[AGG_ROWS];
-#pragma unroll
-        for (int j = 0; j < AGG_ROWS; ++j) xb[j] = ((vn >> j) & 1u) && sl[j] >= 0 ? load_value(vc, row0 + j) : 0;
-#pragma unroll
-        for (int j = 0; j < AGG_ROWS; ++j) {
-          if (sl[j] < 0 || !((vn >> j) & 1u)) continue;
-          int qx = 0, qq = 0;
-          u32 lx[4], lq[4];
-          bool fits = fx_sum < 0 || fx_split(xb[j], fx_bx, qx, lx);
-          if (fits && fx_ssq >= 0) {
-            const double d = __longlong_as_double((i64)xb[j]);
-            fits = fx_split((u64)__double_as_longlong(d * d), fx_bq, qq, lq);
-          }
-          const int s = sl[j];
-          if (!fits) {
-            i64 g;
-            if (dense) g = dense_gslot((u32)s - copy_off);
-            else g = gmem_find_insert_packed(tbl, cap, stride, s == S ? EMPTY : skeys[s], mix64(kk[j]), ctrl, &s_new);
-            sl[j] = g >= 0 ? -2 - (int)g : SLOT_NONE;
-            continue;
-          }
-          if (fx_sum >= 0) fx_add(flx, NS, s, (xb[j] >> 63) != 0, qx, lx);
-          if (fx_ssq >= 0) fx_add(flq, NS, s, false, qq, lq);
-          const u32 old = atomicAdd(fcnt + s, 1u);
-          if (((old + 1u) & (FX_FLUSH - 1u)) == 0u) {
-            i64 g;
-            if (dense) g = dense_gslot((u32)s - copy_off);
-            else g = gmem_find_insert_packed(tbl, cap, stride, s == S ? EMPTY : skeys[s], mix64(kk[j]), ctrl, &s_new);
-            if (g >= 0) {
-              const SlotRef slot = slot_ref(tbl, cap, stride, dense_slots, g);
-              if (fx_sum >= 0) atomicAdd((double*)(slot.cells + (i64)fx_sum * slot.step), fx_take(flx, NS, s, fx_bx));
-              if (fx_ssq >= 0) atomicAdd((double*)(slot.cells + (i64)fx_ssq * slot.step), fx_take(flq, NS, s, fx_bq));
-            }
-          }
-        }
-      }
       int cur_col = -1;
       u64 v[AGG_ROWS];
       u32 vn = 0;
@@ -806,7 +727,6 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
 #pragma unroll
         for (int j = 0; j < AGG_ROWS; ++j) {
           if (sl[j] == SLOT_NONE || !((use >> j) & 1u)) continue;
-          if (LAYOUT == SL_FIXED && sl[j] >= 0) continue;  // folded into the limbs above
           // two call sites so that each atomic knows its address space (shared vs global reduction)
           if (is_arg_op(op)) arg_update(tbl + (i64)(-2 - sl[j]) * stride + 1 + c, op, P.vals[col], row0 + j);  // (global table only)
           else if (LAYOUT == SL_GENERIC && sl[j] >= 0) cell_update(scells + (size_t)c * NS + sl[j], op, v[j]);
@@ -875,8 +795,7 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
           bool present = false;
           for (int r = 0; r < copies; ++r) {
             const int q = r * S + i;
-            present = present || ((socc[q >> 5] >> (q & 31)) & 1u) || (LAYOUT == SL_F32MEAN && scnt[q] != 0u) ||
-                      (LAYOUT == SL_FIXED && fcnt[q] != 0u);
+            present = present || ((socc[q >> 5] >> (q & 31)) & 1u) || (LAYOUT == SL_F32MEAN && scnt[q] != 0u);
           }
           if (!present) continue;
           const u64 key = dense_key(P, s_dense, (u32)i);
@@ -894,21 +813,6 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
             u64 n = 0;
             for (int r = 0; r < copies; ++r) { sum += (double)ssum[r * S + i]; n += scnt[r * S + i]; }
             if (n) { atomicAdd((double*)slot.cells, sum); atomicAdd(slot.cells + slot.step, n); }
-          } else if (LAYOUT == SL_FIXED) {
-            u64 n = 0;
-            double sx = 0.0, sq = 0.0;
-            for (int r = 0; r < copies; ++r) {
-              const u32 nr = fcnt[r * S + i];
-              if (nr == 0u) continue;
-              n += nr;
-              if (fx_sum >= 0) sx += fx_take(flx, NS, r * S + i, fx_bx);
-              if (fx_ssq >= 0) sq += fx_take(flq, NS, r * S + i, fx_bq);
-            }
-            if (n) {
-              if (fx_sum >= 0) atomicAdd((double*)(slot.cells + (i64)fx_sum * slot.step), sx);
-              if (fx_ssq >= 0) atomicAdd((double*)(slot.cells + (i64)fx_ssq * slot.step), sq);
-              if (fx_cnt >= 0) atomicAdd(slot.cells + (i64)fx_cnt * slot.step, n);
-            }
           } else {
             for (int c = 0; c < P.ncells; ++c) {
               const int op = P.cells[c].op;
@@ -941,13 +845,6 @@ k_aggregate(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCt
         if (n) {
           atomicAdd((double*)(slot + 1), (double)ssum[i]);
           atomicAdd(slot + 2, (u64)n);
-        }
-      } else if (LAYOUT == SL_FIXED) {
-        const u32 n = fcnt[i];
-        if (n) {
-          if (fx_sum >= 0) atomicAdd((double*)(slot + 1 + fx_sum), fx_take(flx, NS, i, fx_bx));
-          if (fx_ssq >= 0) atomicAdd((double*)(slot + 1 + fx_ssq), fx_take(flq, NS, i, fx_bq));
-          if (fx_cnt >= 0) atomicAdd(slot + 1 + fx_cnt, (u64)n);
         }
       } else {
         for (int c = 0; c < P.ncells; ++c) {

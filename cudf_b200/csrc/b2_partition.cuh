@@ -168,7 +168,8 @@ __global__ void __launch_bounds__(1024) k_hot_select(const u64* __restrict__ cke
 // With HOT the kernel also carries the hot set (dynamic shared memory: keys, ids, then per hot key an
 // addend count, the limbs of Σx and of Σx², and a "seen" bit): rows of hot keys are folded here and left out
 // of the histogram.  P.cells are Σx / n / Σx² of value column 0 in that case.
-constexpr size_t rp_count_hot_smem() { return (size_t)HOT_SLOTS * 10 + (size_t)HOT_MAX * (4 + 8 * FX_LIMBS) + HOT_MAX / 8; }
+constexpr int HOT_STRIDE = HOT_MAX + 1;  // words between the limbs of one key: odd, so that they lie in different banks
+constexpr size_t rp_count_hot_smem() { return (size_t)HOT_SLOTS * 10 + (size_t)HOT_MAX * 4 + (size_t)HOT_STRIDE * 8 * FX_LIMBS + HOT_MAX / 8; }
 
 template <bool WITH_HLL, bool HOT>
 __global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant__ DPlan P, u64* __restrict__ hist,
@@ -180,9 +181,9 @@ __global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant_
   u64* hk = (u64*)rp_hot_smem;                              // [HOT_SLOTS]
   unsigned short* hid = (unsigned short*)(hk + HOT_SLOTS);  // [HOT_SLOTS]
   u32* hcnt = (u32*)(hid + HOT_SLOTS);                      // [HOT_MAX]
-  int* hlx  = (int*)(hcnt + HOT_MAX);                       // [FX_LIMBS][HOT_MAX]
-  int* hlq  = hlx + FX_LIMBS * HOT_MAX;                     // [FX_LIMBS][HOT_MAX]
-  u32* hseen = (u32*)(hlq + FX_LIMBS * HOT_MAX);            // [HOT_MAX / 32]
+  int* hlx  = (int*)(hcnt + HOT_MAX);                       // [FX_LIMBS][HOT_STRIDE]
+  int* hlq  = hlx + FX_LIMBS * HOT_STRIDE;                  // [FX_LIMBS][HOT_STRIDE]
+  u32* hseen = (u32*)(hlq + FX_LIMBS * HOT_STRIDE);         // [HOT_MAX / 32]
   int nh = 0, bx = FX_NEVER, bq = FX_NEVER;
   for (int i = threadIdx.x; i < (1 << RP_BITS_TOP); i += blockDim.x) s_hist[i] = 0;
   if (WITH_HLL) for (int i = threadIdx.x; i < HLL_REGS; i += blockDim.x) s_regs[i] = 0;
@@ -195,7 +196,7 @@ __global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant_
     }
     if (nh > 0) {
       for (int i = threadIdx.x; i < HOT_SLOTS; i += blockDim.x) { hk[i] = hot.keys[i]; hid[i] = hot.ids[i]; }
-      for (int i = threadIdx.x; i < HOT_MAX * (1 + 2 * FX_LIMBS) + HOT_MAX / 32; i += blockDim.x) hcnt[i] = 0;
+      for (int i = threadIdx.x; i < HOT_MAX + 2 * FX_LIMBS * HOT_STRIDE + HOT_MAX / 32; i += blockDim.x) hcnt[i] = 0;
     }
   }
   __syncthreads();
@@ -247,12 +248,12 @@ __global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant_
           if (c_ssq >= 0) atomicAdd((double*)(acc + 2), d * d);
           continue;
         }
-        if (c_sum >= 0) fx_add(hlx, HOT_MAX, id, (xb >> 63) != 0, qx, lx);
-        if (c_ssq >= 0) fx_add(hlq, HOT_MAX, id, false, qq, lq);
+        if (c_sum >= 0) fx_add(hlx, HOT_STRIDE, id, (xb >> 63) != 0, qx, lx);
+        if (c_ssq >= 0) fx_add(hlq, HOT_STRIDE, id, false, qq, lq);
         const u32 old = atomicAdd(hcnt + id, 1u);
         if (((old + 1u) & (FX_FLUSH - 1u)) == 0u) {
-          if (c_sum >= 0) atomicAdd((double*)(acc + 1), fx_take(hlx, HOT_MAX, id, bx));
-          if (c_ssq >= 0) atomicAdd((double*)(acc + 2), fx_take(hlq, HOT_MAX, id, bq));
+          if (c_sum >= 0) atomicAdd((double*)(acc + 1), fx_take(hlx, HOT_STRIDE, id, bx));
+          if (c_ssq >= 0) atomicAdd((double*)(acc + 2), fx_take(hlq, HOT_STRIDE, id, bq));
         }
       }
     }
@@ -283,8 +284,8 @@ __global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant_
       const u32 n = hcnt[id];
       if (n) {
         atomicAdd(acc, (u64)n);
-        if (c_sum >= 0) atomicAdd((double*)(acc + 1), fx_take(hlx, HOT_MAX, id, bx));
-        if (c_ssq >= 0) atomicAdd((double*)(acc + 2), fx_take(hlq, HOT_MAX, id, bq));
+        if (c_sum >= 0) atomicAdd((double*)(acc + 1), fx_take(hlx, HOT_STRIDE, id, bx));
+        if (c_ssq >= 0) atomicAdd((double*)(acc + 2), fx_take(hlq, HOT_STRIDE, id, bq));
       }
       if (((hseen[id >> 5] >> (id & 31)) & 1u) && acc[3] == 0) acc[3] = 1;
     }

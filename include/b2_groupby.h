@@ -149,8 +149,8 @@ typedef struct b2_groupby_result {
  *      cpp/src/groupby/hash/helpers.cuh:19-40, cpp/include/cudf/detail/cuco_helpers.hpp:16) */
 typedef struct b2_groupby_options {
   int64_t expected_groups;  /* hint; <= 0 = unknown (engine speculates, then estimates)        */
-  int32_t table_variant;    /* 0 auto; 1 global-memory table only; 2 = auto, but float sums keep
-                               8-byte shared-memory cells (no fixed-point limbs); 3 shared-memory table with
+  int32_t table_variant;    /* 0 auto; 1 global-memory table only; 2 = auto, but the partitioned
+                               path folds no hot keys and keeps fp64 cells (no fixed-point limbs); 3 shared-memory table with
                                hashing only (no dense key box); 4 / 5 = auto, but the lean
                                FLOAT32-mean kernel reads its tiles through registers (4) or
                                through the cp.async.bulk shared-memory ring (5); 6 = always

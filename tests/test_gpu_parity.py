@@ -27,10 +27,9 @@ def check(keys, requests, policy=NullPolicy.EXCLUDE, row_filters=(), **opts):
 @pytest.mark.parametrize("config,n", [(1, 400_000), (2, 600_000), (3, 300_000), (4, 500_000), (5, 120_000)])
 @pytest.mark.parametrize("variant", [0, 1, 2, 3, 5, 6, 8])
 def test_benchmark_configs_match_oracle(config, n, variant):
-    """Variants: 0 auto (C1 / C4: float sums as fixed-point limbs in shared memory), 1 global table only,
-    2 auto with 8-byte shared-memory cells, 3 hashed shared table, 5 the bulk-copy tile ring (C2),
-    6 the partitioned path whatever the size (C4: with its hot keys folded by the counting pass),
-    8 STRING keys through dictionary ids (C5)."""
+    """Variants: 0 auto, 1 global table only, 2 auto without fixed-point float sums, 3 hashed shared table,
+    5 the bulk-copy tile ring (C2), 6 the partitioned path whatever the size (C1 / C4: hot keys folded by the
+    counting pass, float sums as fixed-point limbs), 8 STRING keys through dictionary ids (C5)."""
     H.PARITY_STATS.clear()
     w = workloads.make(config, n, scale_domain=(config in (3, 4)))
     check(w.keys, w.requests, w.null_policy, w.row_filters, table_variant=variant)
@@ -84,10 +83,10 @@ def test_two_string_key_columns():
 @pytest.mark.parametrize("variant", [0, 2, 6])
 @pytest.mark.parametrize("vtype", ["f64", "f32"])
 def test_float_sums_as_fixed_point_limbs(variant, vtype):
-    """Σx / n / Σx² of one float column: shared-memory sums are kept as fixed-point limbs (variant 0: the fused
-    kernel; variant 6: the hot keys of the partitioned path; variant 2: 8-byte cells for comparison).  Skewed keys,
-    values of both signs, zeros, denormals, and magnitudes far outside the window the sampled maximum places —
-    those take the fp64 cells of the global table, and the result must not care."""
+    """Σx / n / Σx² of one float column: the partitioned path (variant 6) folds the hot keys in its counting
+    pass and keeps every shared-memory sum as fixed-point limbs; variants 0 and 2 are the table path on the same
+    input.  Skewed keys, values of both signs, zeros, denormals, and magnitudes far outside the window the sampled
+    maximum places — those are added to fp64 cells instead, and the result must not care."""
     rng = np.random.default_rng(77)
     n = 300_000
     ranks = np.minimum((rng.pareto(1.1, n) * 3).astype(np.int64), 200_000)
