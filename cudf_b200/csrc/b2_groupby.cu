@@ -20,6 +20,7 @@
 #include <cstdio>
 #include <chrono>
 #include <cstring>
+#include <functional>
 #include <memory>
 #include <mutex>
 #include <string>
@@ -317,6 +318,13 @@ struct b2_groupby_state {
   Scratch groups;
   int64_t groups_cap = 0;
   int64_t groups_n = -1;  // -1 = no list
+  // One-shot calls: the first table attempt may leave its control block unread, so that the result columns
+  // are allocated (for `deferred_bound` groups) and k_finalize is enqueued while the fused kernel still runs,
+  // and ONE synchronisation reads group count, overflow flags and null counts together.
+  bool deferred = false;
+  bool deferred_lean = false;    // the lean kernel ran alone in that attempt
+  int64_t deferred_cap = 0;      // capacity of that attempt's table
+  int64_t deferred_bound = 0;    // most groups that attempt can leave in the table without raising its overflow flag
 };
 
 namespace {
@@ -1117,7 +1125,19 @@ constexpr int64_t SPECULATIVE_CAP = 1 << 17;  // first table when nothing is kno
 constexpr double MAX_LOAD = 0.70;
 
 // aggregates the bound inputs into an EMPTY state, growing the table until it fits
-void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stream, bool may_partition = false)
+constexpr int64_t DEFER_MAX_GROUPS = 1 << 20;  // over-allocation a deferred first attempt may cost per result column
+
+void add_kernel_ms()
+{
+  float ms = 0.f;
+  if (cudaEventElapsedTime(&ms, kernel_events().a, kernel_events().b) == cudaSuccess) g_stats.aggregate_kernel_ms += ms;
+  else cudaGetLastError();
+}
+
+// `defer`: the first table attempt may return with its control block unread (st.deferred; see the state);
+// `resume`: continue such an attempt after finalize_state read the control block and found it wanting.
+void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stream, bool may_partition = false,
+                     bool defer = false, bool resume = false)
 {
   const int64_t n = st.plan.nrows;
   const int64_t hint = st.expected_groups > 0 ? st.expected_groups : gb.expected_groups;
@@ -1126,7 +1146,7 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
   may_partition = may_partition && st.sc.key_mode == KM_PACKED && gb.table_variant != 1 && gb.table_variant != 7 &&
                   (gb.table_variant == 6 || n >= RP_MIN_ROWS);
   int64_t known = 0;  // groups estimated by a partitioned attempt that gave up
-  if (may_partition && (gb.table_variant == 6 || hint >= RP_MIN_GROUPS)) {
+  if (!resume && may_partition && (gb.table_variant == 6 || hint >= RP_MIN_GROUPS)) {
     g_stats.table_attempts = 1;
     if (aggregate_partitioned(st, gb, stream, hint, &known)) return;
     may_partition = false;
@@ -1136,13 +1156,28 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
   else if (known > 0) cap = std::min(full, (int64_t)((double)known * 1.10 / 0.6) + 1024);
   else if (n <= SPECULATIVE_CAP / 2) cap = std::max<int64_t>(1024, 2 * n + 64);
   else cap = SPECULATIVE_CAP;
+  defer = defer && !resume && st.sc.key_mode == KM_PACKED && !st.sc.has_arg && !getenv("B2_TRACE");
   for (int attempt = 1;; ++attempt) {
     g_stats.table_attempts = attempt;
     Trace trace(stream);
     const SharedPlan sp = plan_shared(st, gb);
-    alloc_table(st, cap, cap >= full ? 1.0 : MAX_LOAD, stream, gb.table_variant != 1 && gb.table_variant != 3, sp.cap_dense);
-    trace.mark("table allocation + init");
-    const bool lean_ran = run_aggregate(st, gb, stream, sp, true);
+    bool lean_ran;
+    if (resume && attempt == 1) {
+      cap = st.deferred_cap;
+      lean_ran = st.deferred_lean;
+    } else {
+      alloc_table(st, cap, cap >= full ? 1.0 : MAX_LOAD, stream, gb.table_variant != 1 && gb.table_variant != 3, sp.cap_dense);
+      trace.mark("table allocation + init");
+      lean_ran = run_aggregate(st, gb, stream, sp, true);
+      const int64_t bound = std::min<int64_t>(n, (int64_t)st.host_ctrl.claim_limit + 1 + st.dense_slots);
+      if (defer && attempt == 1 && bound <= DEFER_MAX_GROUPS) {
+        st.deferred = true;
+        st.deferred_lean = lean_ran;
+        st.deferred_cap = cap;
+        st.deferred_bound = bound;
+        return;
+      }
+    }
     read_ctrl(st, stream);
     if (st.host_ctrl.error) B2_FAIL(B2_INTERNAL_ERROR, "a bounded wait inside the fused aggregate kernel ran out");
     if (lean_ran && !st.host_ctrl.dense.enabled) {
@@ -1194,6 +1229,33 @@ void pack_table(b2_groupby_state& st, int nparts, cudaStream_t stream, Scratch& 
   if (st.sc.key_mode != KM_PACKED)
     B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys are not transferable; partition the rows instead");
   counts.assign((size_t)nparts, 0);
+  if (st.groups_n >= 0) {
+    // a finished group list (the partitioned path): counts, then the records, with the same kernel
+    const int64_t G = st.groups_n;
+    Scratch dcounts((size_t)nparts * 2 * sizeof(u64), stream);
+    CUDA_TRY(cudaMemsetAsync(dcounts.p, 0, dcounts.bytes, stream));
+    u64* d_counts = (u64*)dcounts.p;
+    u64* d_cursor = d_counts + nparts;
+    const int grid = grid_for(std::max<int64_t>(G, 1), 256, 8);
+    const size_t smem = (size_t)nparts * 2 * sizeof(u64);
+    if (smem > 48 * 1024) CUDA_TRY(cudaFuncSetAttribute(k_pack_list, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    k_pack_list<<<grid, 256, smem, stream>>>((const u64*)st.groups.p, st.groups_cap, G, st.plan.stride, nparts, d_counts, nullptr);
+    CUDA_TRY(cudaGetLastError());
+    std::vector<u64> h((size_t)nparts);
+    CUDA_TRY(cudaMemcpyAsync(h.data(), d_counts, (size_t)nparts * sizeof(u64), cudaMemcpyDeviceToHost, stream));
+    CUDA_TRY(cudaStreamSynchronize(stream));
+    std::vector<u64> starts((size_t)nparts);
+    u64 run = 0;
+    for (int p = 0; p < nparts; ++p) { starts[(size_t)p] = run; run += h[(size_t)p]; counts[(size_t)p] = (int64_t)h[(size_t)p]; }
+    if ((int64_t)run != G) B2_FAIL(B2_INTERNAL_ERROR, "pack: group count mismatch");
+    CUDA_TRY(cudaMemcpyAsync(d_cursor, starts.data(), (size_t)nparts * sizeof(u64), cudaMemcpyHostToDevice, stream));
+    out = Scratch(std::max<size_t>(8, (size_t)G * st.plan.stride * 8), stream);
+    k_pack_list<<<grid, 256, smem, stream>>>((const u64*)st.groups.p, st.groups_cap, G, st.plan.stride, nparts, d_cursor, (u64*)out.p);
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaStreamSynchronize(stream));  // `starts` is read by the copy above
+    g_stats.kernel_launches += 2;
+    return;
+  }
   if (!st.table) { out = Scratch(8, stream); return; }
   read_ctrl(st, stream);
   const int64_t G = num_groups(st);
@@ -1350,7 +1412,9 @@ void empty_strings(b2_owned_column& c, const b2_allocator& al, cudaStream_t stre
   CUDA_TRY(cudaMemsetAsync(c.children[0].data, 0, 4, stream));
 }
 
-void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocator* allocator, b2_groupby_result* out)
+// `resume` (one-shot calls): continues the aggregate when a deferred first attempt turns out to have failed.
+void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocator* allocator, b2_groupby_result* out,
+                    const std::function<void()>* resume = nullptr)
 {
   const Schema& sc = st.sc;
   const b2_allocator al = resolve(allocator);
@@ -1360,12 +1424,19 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
   OwnedGuard guard{out};
 
   Trace trace(stream);
-  read_ctrl(st, stream);
+  // A deferred first attempt: nothing has been read back yet.  The columns are allocated for the most groups
+  // that attempt can hold, k_finalize is enqueued behind the fused kernel, and one synchronisation tells
+  // whether the attempt stood (then the columns are cut to the group count) or has to be continued.
+  const bool speculative = st.deferred && st.table != nullptr && st.groups_n < 0;
+  if (!speculative) read_ctrl(st, stream);
   const bool listed = st.groups_n >= 0;  // the partitioned path left a compact group list, not a table
-  if (st.table && st.host_ctrl.chunk_overflow >= 2) B2_FAIL(B2_INTERNAL_ERROR, "the local aggregate failed on another rank");
-  if (st.table && st.host_ctrl.chunk_overflow) B2_FAIL(B2_LOGIC_ERROR, "partial-record chunk overflow");
-  if (st.table && st.host_ctrl.overflow) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow while merging partial records");
-  const int64_t G = listed ? st.groups_n : st.table ? num_groups(st) : 0;
+  if (!speculative) {
+    if (st.table && st.host_ctrl.chunk_overflow >= 2) B2_FAIL(B2_INTERNAL_ERROR, "the local aggregate failed on another rank");
+    if (st.table && st.host_ctrl.chunk_overflow) B2_FAIL(B2_LOGIC_ERROR, "partial-record chunk overflow");
+    if (st.table && st.host_ctrl.overflow) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow while merging partial records");
+  }
+  // (speculative: G is the number of rows the columns are allocated for until the control block is read)
+  int64_t G = speculative ? st.deferred_bound : listed ? st.groups_n : st.table ? num_groups(st) : 0;
   if (G > 0x7FFFFFFFll) B2_FAIL(B2_UNSUPPORTED, "more than 2^31-1 groups");
   out->num_groups = (int32_t)G;
   out->num_keys = sc.nkeys;
@@ -1383,6 +1454,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
   auto plan = std::make_unique<DOutPlan>();
   std::memset(plan.get(), 0, sizeof(DOutPlan));
   plan->nouts = (int)sc.outs.size();
+  plan->max_groups = speculative ? G : 0;
   std::vector<Scratch> arg_rows(sc.outs.size());  // MIN / MAX of strings: the winning row of every group
   for (size_t i = 0; i < sc.outs.size(); ++i) {
     const OutSpec& o = sc.outs[i];
@@ -1453,6 +1525,36 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
     g_stats.kernel_launches++;
     trace.mark("finalize: k_finalize");
 
+    if (speculative) {
+      CUDA_TRY(cudaMemcpyAsync(&st.host_ctrl, st.ctrl, sizeof(DCtrl), cudaMemcpyDeviceToHost, stream));
+      CUDA_TRY(cudaStreamSynchronize(stream));
+      st.ctrl_fresh = true;
+      st.deferred = false;
+      const DCtrl& h = st.host_ctrl;
+      const bool stood = !h.overflow && !h.error && !(st.deferred_lean && !h.dense.enabled);
+      if (stood) add_kernel_ms();  // (a continued attempt adds its kernel times itself)
+      if (!stood || num_groups(st) > G) {
+        b2_result_free(out);  // (the guard then finds nothing left to free)
+        guard.armed = false;
+        if (!stood) {
+          if (!resume) B2_FAIL(B2_INTERNAL_ERROR, "a deferred table attempt failed and cannot be continued");
+          (*resume)();
+        }
+        finalize_state(st, stream, allocator, out);
+        return;
+      }
+      G = num_groups(st);
+      out->num_groups = (int32_t)G;
+      for (int k = 0; k < sc.nkeys; ++k) { out->keys[k].size = (int32_t)G; out->keys[k].null_count = (int32_t)h.null_counts[MAX_OUTS + k]; }
+      for (size_t i = 0; i < sc.outs.size(); ++i) {
+        b2_owned_column& c = out->results[sc.outs[i].req][sc.outs[i].agg];
+        c.size = (int32_t)G;
+        c.null_count = (int32_t)h.null_counts[i];
+      }
+      guard.armed = false;
+      return;
+    }
+
     if (sc.key_mode == KM_ROWS) {
       if ((int)st.row_keys.size() != sc.nkeys) B2_FAIL(B2_INTERNAL_ERROR, "row-keyed state without bound key views");
       for (int k = 0; k < sc.nkeys; ++k) {
@@ -1506,7 +1608,7 @@ b2_groupby_state* make_state(const b2_groupby& gb, const b2_aggregation_request*
 }
 
 void update_state(b2_groupby_state& st, const b2_groupby& gb, const b2_aggregation_request* reqs, int nreqs,
-                  cudaStream_t stream, bool may_partition = false)
+                  cudaStream_t stream, bool may_partition = false, bool defer = false)
 {
   validate_requests(gb, reqs, nreqs);
   if ((int)st.sc.req_val.size() != nreqs) B2_FAIL(B2_LOGIC_ERROR, "request list differs from the state's");
@@ -1515,7 +1617,7 @@ void update_state(b2_groupby_state& st, const b2_groupby& gb, const b2_aggregati
   if (st.groups_n >= 0) B2_FAIL(B2_INTERNAL_ERROR, "a finished group list takes no further updates");
   if (!st.table) {
     bind_plan_inputs(st.plan, st.sc, gb, reqs, nreqs);
-    aggregate_fresh(st, gb, stream, may_partition);
+    aggregate_fresh(st, gb, stream, may_partition, defer);
     if (st.sc.key_mode == KM_ROWS) { st.has_rows = true; st.row_keys = gb.keys; }
     return;
   }
@@ -1859,8 +1961,9 @@ b2_status b2_groupby_aggregate(b2_groupby* gb, const b2_aggregation_request* req
     const b2_groupby& use = encode_string_keys(*gb, (cudaStream_t)stream, ek) ? ek.gb : *gb;
     std::unique_ptr<b2_groupby_state, void (*)(b2_groupby_state*)> st(make_state(use, requests, num_requests),
                                                                       b2_state_destroy);
-    update_state(*st, use, requests, num_requests, (cudaStream_t)stream, /*may_partition=*/true);
-    finalize_state(*st, (cudaStream_t)stream, allocator, out);
+    update_state(*st, use, requests, num_requests, (cudaStream_t)stream, /*may_partition=*/true, /*defer=*/true);
+    const std::function<void()> resume = [&] { aggregate_fresh(*st, use, (cudaStream_t)stream, true, false, /*resume=*/true); };
+    finalize_state(*st, (cudaStream_t)stream, allocator, out, &resume);
     if (ek.active) restore_string_keys(ek, *gb, (cudaStream_t)stream, out);
   });
 }
@@ -1999,6 +2102,10 @@ b2_status b2_state_reset(b2_groupby_state* st, int64_t expected_groups, void* st
   return guarded([&] {
     if (!st) B2_FAIL(B2_INVALID_ARGUMENT, "null argument");
     free_table(*st, (cudaStream_t)stream);
+    st->groups.release();
+    st->groups_n = -1;
+    st->groups_cap = 0;
+    st->deferred = false;
     st->host_ctrl = DCtrl{};
     st->ctrl_fresh = true;
     st->has_rows = false;
@@ -2340,7 +2447,7 @@ void aggregate_multi(b2_comm& c, b2_groupby& gb, const b2_aggregation_request* r
   bool failed = false;
   Err failure{B2_SUCCESS, ""};
   try {
-    update_state(*local, gb, reqs, nreqs, stream);
+    update_state(*local, gb, reqs, nreqs, stream, /*may_partition=*/true);
   } catch (const Err& e) {
     failed = true;
     failure = e;
@@ -2352,7 +2459,9 @@ void aggregate_multi(b2_comm& c, b2_groupby& gb, const b2_aggregation_request* r
   // whose groups cannot fit whatever their split sends marked chunks without packing anything.
   if (chunk_bytes * W <= MULTI_CHUNK_LIMIT) {
     Scratch send((size_t)chunk_bytes * W, stream), recv((size_t)chunk_bytes * W, stream);
-    const bool hopeless = !failed && local->table && local->ctrl_fresh && num_groups(*local) > (int64_t)W * MULTI_CHUNK_RECORDS;
+    // (a group list is what the partitioned path leaves: half a million groups at least, never chunk-sized)
+    const bool hopeless = !failed && (local->groups_n >= 0 ||
+                                      (local->table && local->ctrl_fresh && num_groups(*local) > (int64_t)W * MULTI_CHUNK_RECORDS));
     if (failed || hopeless) {
       const u64 head[2] = {0, failed ? CHUNK_MARK_FAILED : CHUNK_MARK_OVERFLOW};
       for (int r = 0; r < W; ++r)

@@ -1040,6 +1040,8 @@ struct DOutPlan {
   u32* kmask[MAX_KEYS];
   int* rep_rows;           // row-key mode: representative row per group
   u32* null_counts;        // [MAX_OUTS + MAX_KEYS]
+  i64 max_groups;          // > 0: the output columns hold this many rows; groups beyond them are not written
+                           // (the host compares the cursor with it afterwards)
 };
 
 __device__ __forceinline__ void store_int(void* data, i64 g, int rclass, u64 v)
@@ -1174,6 +1176,7 @@ __global__ void __launch_bounds__(FIN_BLOCK) k_finalize(const __grid_constant__ 
       const i64 g = (i64)next + __popc(m & ((1u << lane) - 1u));
       next += __popc(m);
       if (!((m >> lane) & 1u)) continue;
+      if (O.max_groups > 0 && g >= O.max_groups) continue;
       const i64 s = ch * chunk + (i64)j * FIN_BLOCK + threadIdx.x;
       const SlotRef ref = slot_ref(const_cast<u64*>(tbl), cap, stride, dense, s);
       write_group(P, O, s == cap ? EMPTY : *ref.key, ref.cells, ref.step, g);
@@ -1408,6 +1411,45 @@ k_pack_scatter(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, con
     const SlotRef src = slot_ref(const_cast<u64*>(tbl), cap, stride, last - cap, s);
     dst[0] = key;
     for (int c = 1; c < stride; ++c) dst[c] = src.cells[(i64)(c - 1) * src.step];
+  }
+}
+
+// The same for a state that holds its groups as a list (structure-of-arrays: word w of group g at
+// groups[w * gcap + g]) — what the partitioned path leaves: CTA-contiguous ranges of the list, one global
+// reservation per destination and CTA, records written in destination-major order.
+__global__ void __launch_bounds__(256)
+k_pack_list(const u64* __restrict__ groups, i64 gcap, i64 ngroups, int stride, int nparts, u64* __restrict__ cursors,
+            u64* __restrict__ out /* nullptr: only count into `cursors` */)
+{
+  extern __shared__ u64 s_pack[];  // [nparts] counts, then [nparts] bases
+  u64* s_cnt  = s_pack;
+  u64* s_base = s_pack + nparts;
+  const i64 per  = (ngroups + gridDim.x - 1) / gridDim.x;
+  const i64 lo   = (i64)blockIdx.x * per;
+  const i64 hi   = min(ngroups, lo + per);
+  const u32 lane = threadIdx.x & 31u;
+  for (int p = threadIdx.x; p < nparts; p += blockDim.x) s_cnt[p] = 0;
+  __syncthreads();
+  for (i64 g0 = lo + (threadIdx.x - lane); g0 < hi; g0 += blockDim.x) {
+    const i64 g = g0 + lane;
+    warp_add_by_dest(s_cnt, g < hi ? owner_of(mix64(groups[g]), (u32)nparts) : NO_DEST);
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < nparts; p += blockDim.x) {
+    s_base[p] = s_cnt[p] ? atomicAdd(&cursors[p], s_cnt[p]) : 0;
+    s_cnt[p]  = 0;
+  }
+  if (!out) return;
+  __syncthreads();
+  for (i64 g0 = lo + (threadIdx.x - lane); g0 < hi; g0 += blockDim.x) {
+    const i64 g = g0 + lane;
+    const u64 key = g < hi ? groups[g] : 0;
+    const u32 p = g < hi ? owner_of(mix64(key), (u32)nparts) : NO_DEST;
+    const u64 r = warp_add_by_dest(s_cnt, p);
+    if (p == NO_DEST) continue;
+    u64* dst = out + (s_base[p] + r) * stride;
+    dst[0] = key;
+    for (int c = 1; c < stride; ++c) dst[c] = groups[(i64)c * gcap + g];
   }
 }
 

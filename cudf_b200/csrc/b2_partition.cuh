@@ -775,18 +775,26 @@ __global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_cons
 #define B2_RPA_APPLY(EXPR)                                                        \
         _Pragma("unroll") for (int j = 0; j < RPA_BATCH; ++j)                     \
           if ((ok >> j) & 1u) { u64* p = cell + slots[j]; const u64 v = vals[j]; EXPR; }
+        // 64-bit shared-memory atomics run as compare-and-swap loops; what can be said in 32 bits is:
+        // a count stays below 2^32 inside a bucket; an integer sum is its low word (the add that wraps it
+        // carries into the high word) — both exact; a minimum or maximum is only attempted by a value that
+        // improves on what the cell holds at that moment (the cell moves one way only).
         switch (op) {
-          case OP_SUM_I: B2_RPA_APPLY(atomicAdd(p, v)) break;
-          case OP_CNT_V: case OP_CNT_A: B2_RPA_APPLY((void)v; atomicAdd(p, 1ull)) break;
+          case OP_SUM_I:
+            B2_RPA_APPLY(const u32 lo = (u32)v; const u32 old = atomicAdd((u32*)p, lo);
+                         const u32 hi = (u32)(v >> 32) + ((u32)(old + lo) < old ? 1u : 0u);
+                         if (hi) atomicAdd((u32*)p + 1, hi))
+            break;
+          case OP_CNT_V: case OP_CNT_A: B2_RPA_APPLY((void)v; atomicAdd((u32*)p, 1u)) break;
           case OP_SUM_F: B2_RPA_APPLY(atomicAdd((double*)p, __longlong_as_double((i64)v))) break;
           case OP_SSQ_I: B2_RPA_APPLY(atomicAdd(p, v * v)) break;
           case OP_SSQ_F: B2_RPA_APPLY(const double d = __longlong_as_double((i64)v); atomicAdd((double*)p, d * d)) break;
-          case OP_MIN_I: B2_RPA_APPLY(atomicMin((i64*)p, (i64)v)) break;
-          case OP_MAX_I: B2_RPA_APPLY(atomicMax((i64*)p, (i64)v)) break;
-          case OP_MIN_U: B2_RPA_APPLY(atomicMin(p, v)) break;
-          case OP_MAX_U: B2_RPA_APPLY(atomicMax(p, v)) break;
-          case OP_MIN_F: B2_RPA_APPLY(atomicMin(p, f64_ordered(v))) break;
-          case OP_MAX_F: B2_RPA_APPLY(atomicMax(p, f64_ordered(v))) break;
+          case OP_MIN_I: B2_RPA_APPLY(if ((i64)v < *(volatile i64*)p) atomicMin((i64*)p, (i64)v)) break;
+          case OP_MAX_I: B2_RPA_APPLY(if ((i64)v > *(volatile i64*)p) atomicMax((i64*)p, (i64)v)) break;
+          case OP_MIN_U: B2_RPA_APPLY(if (v < *(volatile u64*)p) atomicMin(p, v)) break;
+          case OP_MAX_U: B2_RPA_APPLY(if (v > *(volatile u64*)p) atomicMax(p, v)) break;
+          case OP_MIN_F: B2_RPA_APPLY(const u64 o = f64_ordered(v); if (o < *(volatile u64*)p) atomicMin(p, o)) break;
+          case OP_MAX_F: B2_RPA_APPLY(const u64 o = f64_ordered(v); if (o > *(volatile u64*)p) atomicMax(p, o)) break;
           default: B2_RPA_APPLY(cell_update(p, op, v)) break;  // products: compare-and-swap loops
         }
 #undef B2_RPA_APPLY

@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from .aggregation import Aggregation
 from .column import Column, Table, TorchAllocator, allocator_for
-from .types import Kind, NullPolicy, TypeId
+from .types import type_width, Kind, NullPolicy, TypeId
 
 
 class LogicError(RuntimeError):
@@ -73,6 +73,17 @@ def _requests_to_c(requests: Sequence[GroupByRequest], keep: list):
 def _adopt_column(oc: _lib.OwnedColumn, alloc: TorchAllocator) -> Column:
     data = alloc.adopt(oc.data)
     mask = alloc.adopt(oc.null_mask)
+    # a call that allocated its result before it knew the group count hands over buffers larger than the
+    # column: the column's tensors are views of the part that belongs to it
+    width = type_width(oc.type_id)
+    if data is not None and width:
+        used = (oc.size * width + 3) // 4 * 4
+        if data.numel() > max(used, 8):
+            data = data[:max(used, 8)]
+    if mask is not None:
+        used = max(1, (oc.size + 511) // 512) * 64
+        if mask.numel() > used:
+            mask = mask[:used]
     offsets, offs_t = None, TypeId.INT32
     if oc.num_children:
         child = oc.children[0]

@@ -25,10 +25,13 @@ dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
 # native = the whole plan inside the library (b2_groupby_aggregate_multi); python = torch.distributed collectives
 # between library calls; C3 with 300K rows holds ~30K groups per destination: more than a 16384-record chunk,
 # so both forms take their exact-size fallback over NCCL; string keys (C5): the partial aggregates travel as a table
-for config, strategy, n, python_exchange in ((2, "partials", 200_000, False), (2, "partials", 200_000, True),
-                                            (4, "partials", 200_000, False), (3, "partials", 300_000, False),
-                                            (3, "partials", 300_000, True), (3, "rows", 150_000, False),
-                                            (5, "rows", 40_000, False), (5, "partials", 40_000, False)):
+# table_variant 6: the local pass takes the partitioned path (as it does by itself from half a million groups), whose
+# group list is packed by owner instead of a table
+for config, strategy, n, python_exchange, variant in (
+        (2, "partials", 200_000, False, 0), (2, "partials", 200_000, True, 0), (4, "partials", 200_000, False, 0),
+        (3, "partials", 300_000, False, 0), (3, "partials", 300_000, True, 0), (3, "rows", 150_000, False, 0),
+        (5, "rows", 40_000, False, 0), (5, "partials", 40_000, False, 0),
+        (4, "partials", 200_000, False, 6), (3, "partials", 300_000, False, 6)):
     shards = [workloads.make(config, n, rank=r, scale_domain=(config in (3, 4))) for r in range(world)]
     w = shards[rank]
     keys = cb.Table([cb.Column.from_host(k) for k in w.keys])
@@ -38,7 +41,8 @@ for config, strategy, n, python_exchange in ((2, "partials", 200_000, False), (2
         cache.setdefault(id(v), cb.Column.from_host(v))
         reqs.append(cb.GroupByRequest(cache[id(v)], [Aggregation(Kind(a)) for a in aggs]))
     filt = [cache[id(f)] for f in w.row_filters]
-    dgb = DistributedGroupBy(keys, w.null_policy, strategy=strategy, row_filters=filt, python_exchange=python_exchange)
+    dgb = DistributedGroupBy(keys, w.null_policy, strategy=strategy, row_filters=filt, python_exchange=python_exchange,
+                             table_variant=variant)
     okeys, ores = dgb.aggregate(reqs)
     mine = ([c.to_host() for c in okeys.columns()], [[c.to_host() for c in t.columns()] for t in ores])
     # a second call on the same object sizes its tables from the first and must give the same groups
@@ -78,8 +82,8 @@ for config, strategy, n, python_exchange in ((2, "partials", 200_000, False), (2
         exp = oracle.groupby(full_keys, full_reqs, w.null_policy, row_filters=fm)
         H.assert_same_result((got_keys, got_res), exp, full_reqs, check_nullable=False,
                              scales=H.result_scales(full_keys, full_reqs, w.null_policy, fm))
-        print(f"config {config} strategy {strategy} {'python' if python_exchange else 'native'} exchange: "
-              f"{got_keys[0].size} groups OK", flush=True)
+        print(f"config {config} strategy {strategy} {'python' if python_exchange else 'native'} exchange"
+              f"{', partitioned local pass' if variant == 6 else ''}: {got_keys[0].size} groups OK", flush=True)
 dist.barrier()
 dist.destroy_process_group()
 '''
@@ -96,7 +100,7 @@ def test_two_rank_distributed_groupby_matches_oracle(tmp_path):
                           "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
                          capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
-    assert out.stdout.count("OK") == 8
+    assert out.stdout.count("OK") == 10
     log_dir = os.path.join(ROOT, "gpurun_out")   # keep rank 0's summary lines beside the other run logs
     if os.path.isdir(log_dir):
         with open(os.path.join(log_dir, "two_rank_worker.log"), "w", encoding="utf-8") as f:
