@@ -1531,7 +1531,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
       st.ctrl_fresh = true;
       st.deferred = false;
       const DCtrl& h = st.host_ctrl;
-      const bool stood = !h.overflow && !h.error && !(st.deferred_lean && !h.dense.enabled);
+      const bool stood = !h.overflow && !h.error && !h.chunk_overflow && !(st.deferred_lean && !h.dense.enabled);
       if (stood) add_kernel_ms();  // (a continued attempt adds its kernel times itself)
       if (!stood || num_groups(st) > G) {
         b2_result_free(out);  // (the guard then finds nothing left to free)
@@ -2047,6 +2047,8 @@ b2_status b2_state_pack_chunks(b2_groupby_state* st, int32_t num_parts, int64_t 
 {
   return guarded([&] {
     cudaStream_t stream = (cudaStream_t)stream_;
+    // a table whose first attempt has not been read back: the kernel itself marks the chunks if it failed
+    const int check = (st && st->deferred) ? (st->deferred_lean ? 3 : 1) : 0;
     if (!st || !out || num_parts < 1 || num_parts > 4096 || chunk_records < 1) B2_FAIL(B2_INVALID_ARGUMENT, "bad argument");
     if (st->sc.key_mode != KM_PACKED || st->sc.has_arg)
       B2_FAIL(B2_UNSUPPORTED, "partial records of string / float / wide keys (or of row-index accumulators) are not transferable; partition the rows instead");
@@ -2061,7 +2063,7 @@ b2_status b2_state_pack_chunks(b2_groupby_state* st, int32_t num_parts, int64_t 
     CUDA_TRY(cudaMemsetAsync(cursors.p, 0, cursors.bytes, stream));
     const int grid = grid_for(st->cap + 1 + st->dense_slots, 256, 8);
     k_pack_chunks<<<grid, 256, 0, stream>>>(st->table, st->cap, st->plan.stride, num_parts, st->ctrl, (u64*)cursors.p,
-                                            (u64*)out, chunk_records);
+                                            (u64*)out, chunk_records, check);
     CUDA_TRY(cudaGetLastError());
     g_stats.kernel_launches += 1;
   });
@@ -2433,6 +2435,20 @@ void exchange_equal(const b2_comm& c, const unsigned char* send, unsigned char* 
 // leaving while its peers wait in the collective.
 constexpr u64 CHUNK_MARK_OVERFLOW = 1, CHUNK_MARK_FAILED = 2;
 
+struct RedoExact {};  // the fixed-size exchange did not hold: every rank repeats it with exact sizes
+
+// reads back a first table attempt that was left unread and, if it failed, continues the aggregate
+void resolve_deferred(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stream)
+{
+  if (!st.deferred) return;
+  st.deferred = false;
+  st.ctrl_fresh = false;
+  read_ctrl(st, stream);
+  const DCtrl& h = st.host_ctrl;
+  if (!h.overflow && !h.error && !(st.deferred_lean && !h.dense.enabled)) { add_kernel_ms(); return; }
+  aggregate_fresh(st, gb, stream, /*may_partition=*/true, /*defer=*/false, /*resume=*/true);
+}
+
 void aggregate_multi(b2_comm& c, b2_groupby& gb, const b2_aggregation_request* reqs, int nreqs, cudaStream_t stream,
                      const b2_allocator* allocator, b2_groupby_result* out)
 {
@@ -2446,8 +2462,12 @@ void aggregate_multi(b2_comm& c, b2_groupby& gb, const b2_aggregation_request* r
   const int64_t chunk_words = chunk_bytes / 8;
   bool failed = false;
   Err failure{B2_SUCCESS, ""};
+  // With chunk-sized states the local attempt is not read back before the exchange: k_pack_chunks marks its
+  // chunks if the attempt failed, and the one synchronisation of the call comes after the merged table's
+  // finalize kernel has been enqueued.
+  const bool chunked = chunk_bytes * W <= MULTI_CHUNK_LIMIT;
   try {
-    update_state(*local, gb, reqs, nreqs, stream, /*may_partition=*/true);
+    update_state(*local, gb, reqs, nreqs, stream, /*may_partition=*/true, /*defer=*/chunked);
   } catch (const Err& e) {
     failed = true;
     failure = e;
@@ -2457,7 +2477,7 @@ void aggregate_multi(b2_comm& c, b2_groupby& gb, const b2_aggregation_request* r
   // ---- small states: fixed-size chunks, no host round trip before the exchange.  Every rank takes
   // this branch or none does (the condition depends on the schema and the rank count only); a rank
   // whose groups cannot fit whatever their split sends marked chunks without packing anything.
-  if (chunk_bytes * W <= MULTI_CHUNK_LIMIT) {
+  if (chunked) {
     Scratch send((size_t)chunk_bytes * W, stream), recv((size_t)chunk_bytes * W, stream);
     // (a group list is what the partitioned path leaves: half a million groups at least, never chunk-sized)
     const bool hopeless = !failed && (local->groups_n >= 0 ||
@@ -2477,13 +2497,30 @@ void aggregate_multi(b2_comm& c, b2_groupby& gb, const b2_aggregation_request* r
     }
     std::unique_ptr<b2_groupby_state, void (*)(b2_groupby_state*)> merged(make_state(gb, reqs, nreqs), b2_state_destroy);
     rethrow(b2_state_merge_chunks(merged.get(), recv.p, W, MULTI_CHUNK_RECORDS, stream));
-    read_ctrl(*merged, stream);
-    if (merged->host_ctrl.chunk_overflow >= CHUNK_MARK_FAILED) B2_FAIL(B2_INTERNAL_ERROR, "the local aggregate failed on another rank");
-    if (merged->host_ctrl.chunk_overflow < CHUNK_MARK_OVERFLOW) {
-      finalize_state(*merged, stream, allocator, out);
+    // the merged table is finalized before anything is read back (at most W chunks of groups); a marked chunk
+    // shows in its control block, which that one synchronisation reads
+    merged->deferred = true;
+    merged->deferred_lean = false;
+    merged->deferred_cap = merged->cap;
+    merged->deferred_bound = std::min<int64_t>((int64_t)W * MULTI_CHUNK_RECORDS, (int64_t)merged->host_ctrl.claim_limit + 1);
+    const std::function<void()> redo = [] { throw RedoExact{}; };
+    try {
+      finalize_state(*merged, stream, allocator, out, &redo);
       return;
+    } catch (const RedoExact&) {
+      if (merged->host_ctrl.chunk_overflow >= CHUNK_MARK_FAILED) B2_FAIL(B2_INTERNAL_ERROR, "the local aggregate failed on another rank");
+      if (merged->host_ctrl.chunk_overflow < CHUNK_MARK_OVERFLOW) B2_FAIL(B2_INTERNAL_ERROR, "hash table overflow while merging partial-record chunks");
     }
     // every rank read a marked chunk: all of them go on to the exact-size exchange
+  }
+  if (!failed) {
+    try {
+      resolve_deferred(*local, gb, stream);
+    } catch (const Err& e) {
+      failed = true;
+      failure = e;
+      cudaGetLastError();
+    }
   }
 
   // ---- exact sizes: count matrix (with a status word per rank) by all-gather, then variable send / recv

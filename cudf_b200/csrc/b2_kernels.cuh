@@ -1476,9 +1476,13 @@ __device__ __forceinline__ i64 table_slot_packed(const DPlan& P, u64* tbl, i64 c
 // written); the last CTA to finish writes the headers — the counts, or, when any destination
 // overflowed, the overflow mark in EVERY chunk, so that every receiver learns of it.
 // `cursors` ([nparts] counters + one ticket word) must arrive zeroed.
+// `check`: the table comes from an aggregate attempt whose control block the host has not read — bit 0: an
+// attempt that overflowed or hit an error marks every chunk like an overflow (the receivers then make all
+// ranks repeat the exchange with exact sizes, and this rank continues its aggregate first); bit 1: so does
+// a lean fused kernel that declined its input (no key box).
 __global__ void __launch_bounds__(256)
 k_pack_chunks(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, const DCtrl* ctrl, u64* __restrict__ cursors,
-              u64* __restrict__ out, i64 chunk_records)
+              u64* __restrict__ out, i64 chunk_records, int check)
 {
   __shared__ int s_last;
   const i64 chunk_words = 2 + chunk_records * stride;
@@ -1513,7 +1517,9 @@ k_pack_chunks(const u64* __restrict__ tbl, i64 cap, int stride, int nparts, cons
   for (int p = threadIdx.x; p < nparts; p += blockDim.x)
     if (__ldcg(&cursors[p]) > (u64)chunk_records) s_over = 1;
   __syncthreads();
-  const bool over = s_over != 0;
+  bool over = s_over != 0;
+  if ((check & 1) && (ctrl->overflow != 0 || ctrl->error != 0)) over = true;
+  if ((check & 2) && ctrl->dense.enabled == 0) over = true;
   for (int p = threadIdx.x; p < nparts; p += blockDim.x) {
     out[(i64)p * chunk_words]     = over ? 0ull : __ldcg(&cursors[p]);
     out[(i64)p * chunk_words + 1] = over ? 1ull : 0ull;
