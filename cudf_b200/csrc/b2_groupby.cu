@@ -992,10 +992,6 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
   T = std::max(T, 1);
   if (T > 2 * RP_MAX_BITS) return false;
   int b1 = T <= RP_MAX_BITS ? T : (T + 1) / 2, b2 = T - b1;
-  if (const char* e = getenv("B2_RP_BITS")) {  // tuning aid: "b1,b2"
-    int x = 0, y = 0;
-    if (sscanf(e, "%d,%d", &x, &y) == 2 && x >= 1 && x <= RP_MAX_BITS && y >= 0 && y <= RP_MAX_BITS) { b1 = x; b2 = y; }
-  }
   const int F1 = 1 << b1, F2 = 1 << b2;
   const int64_t nbuckets = (int64_t)F1 * F2;
 
