@@ -929,8 +929,9 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
   DHot hot{};
   if (with_hot) {
     const size_t b_ckeys = (size_t)HOT_COUNT_SLOTS * 8, b_ccnt = (size_t)HOT_COUNT_SLOTS * 4, b_keys = (size_t)HOT_SLOTS * 8,
-                 b_ids = (size_t)HOT_SLOTS * 2, b_info = 16, b_acc = (size_t)HOT_MAX * HOT_ACC_WORDS * 8;
-    hot_mem = Scratch(b_ckeys + b_keys + b_ccnt + b_ids + b_info + b_acc, stream);
+                 b_ids = (size_t)HOT_SLOTS * 2, b_info = 16 + 256 * 4, b_acc = (size_t)HOT_MAX * HOT_ACC_WORDS * 8;
+    const size_t b_mask = ((size_t)(P.nrows + 31) / 32 + 2) * 4;  // (written for every quad before it is read)
+    hot_mem = Scratch(b_ckeys + b_keys + b_ccnt + b_ids + b_info + b_acc + b_mask, stream);
     unsigned char* m = (unsigned char*)hot_mem.p;
     u64* ckeys = (u64*)m;
     hot.keys = (u64*)(m + b_ckeys);
@@ -938,12 +939,14 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
     hot.ids = (unsigned short*)(m + b_ckeys + b_keys + b_ccnt);
     hot.info = (u32*)(m + b_ckeys + b_keys + b_ccnt + b_ids);
     hot.acc = (u64*)(m + b_ckeys + b_keys + b_ccnt + b_ids + b_info);
+    hot.row_mask = (u32*)(m + b_ckeys + b_keys + b_ccnt + b_ids + b_info + b_acc);
     CUDA_TRY(cudaMemsetAsync(m, 0xFF, b_ckeys + b_keys, stream));
     CUDA_TRY(cudaMemsetAsync(ccnt, 0, b_ccnt + b_ids + b_info + b_acc, stream));
     k_hot_sample<<<sms, 256, 0, stream>>>(P, ckeys, ccnt, hot.info);
-    k_hot_select<<<1, 1024, 0, stream>>>(ckeys, ccnt, hot);
+    k_hot_hist<<<sms, 256, 0, stream>>>(ccnt, hot.info + 4);
+    k_hot_select<<<sms, 256, 0, stream>>>(ckeys, ccnt, hot.info + 4, hot);
     CUDA_TRY(cudaGetLastError());
-    g_stats.kernel_launches += 2;
+    g_stats.kernel_launches += 3;
     static thread_local size_t configured[2][64] = {};
     allow_shared(k_rp_count<false, true>, rp_count_hot_smem(), configured[0]);
     allow_shared(k_rp_count<true, true>, rp_count_hot_smem(), configured[1]);
@@ -963,7 +966,7 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
   u32 h_hot[2] = {0, 0};  // number of hot keys, exponent info
   if (with_hot) CUDA_TRY(cudaMemcpyAsync(h_hot, hot.info, sizeof(h_hot), cudaMemcpyDeviceToHost, stream));
   CUDA_TRY(cudaStreamSynchronize(stream));
-  const int nhot = (int)h_hot[0];
+  const int nhot = (int)std::min<u32>(h_hot[0], (u32)HOT_MAX);
   int64_t active = 0;  // rows that go through the partitions (the rows of hot keys are folded already)
   for (u64 c : h_hist) active += (int64_t)c;
   int64_t est = hint > 0 ? hint : hll_estimate(h_hll.data());
@@ -1018,13 +1021,11 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
     Scratch recA((size_t)words * (size_t)std::max<int64_t>(active, 1) * 8, stream);
     DScatter D1{DRecords{(u64*)recA.p, active, words, valid_word}, d_cur1, 64 - b1, F1};
     const int sgrid = (int)std::max<int64_t>(1, std::min<int64_t>((P.nrows + RP_TILE - 1) / RP_TILE, (int64_t)sms * 2));
-    const bool simple = sc.nvals == 1 && valid_word < 0;
-    const size_t scatter_smem = (nhot > 0 && simple) ? rp_scatter_hot_offset(F1) + (size_t)HOT_SLOTS * 8 : rp_tile_smem(F1);
     {
       static thread_local size_t configured[64] = {};
-      allow_shared(k_rp_scatter, scatter_smem, configured);
+      allow_shared(k_rp_scatter, rp_tile_smem(F1), configured);
     }
-    k_rp_scatter<<<sgrid, RPS_BLOCK, scatter_smem, stream>>>(P, D1, nhot > 0 ? hot.keys : nullptr);
+    k_rp_scatter<<<sgrid, RPS_BLOCK, rp_tile_smem(F1), stream>>>(P, D1, nhot > 0 ? hot.row_mask : nullptr);
     CUDA_TRY(cudaGetLastError());
     g_stats.kernel_launches++;
     trace.mark("partition: level-1 scatter");
@@ -1390,8 +1391,8 @@ void gather_strings(const DKeyCol& kc, const int* rows, int64_t G, b2_owned_colu
   oc.size = (int32_t)(G + 1);
   oc.data_bytes = (size_t)(G + 1) * (big ? 8 : 4);
   oc.data = out_alloc(al, oc.data_bytes, stream);
-  if (big) k_string_copy<i64><<<grid_for(G * 32, 256, 8), 256, 0, stream>>>(kc, rows, G, (const i64*)offs.p, (i64*)oc.data, (unsigned char*)c.data);
-  else k_string_copy<int><<<grid_for(G * 32, 256, 8), 256, 0, stream>>>(kc, rows, G, (const i64*)offs.p, (int*)oc.data, (unsigned char*)c.data);
+  if (big) k_string_copy<i64><<<grid_for(G * 4, 256, 8), 256, 0, stream>>>(kc, rows, G, (const i64*)offs.p, (i64*)oc.data, (unsigned char*)c.data);
+  else k_string_copy<int><<<grid_for(G * 4, 256, 8), 256, 0, stream>>>(kc, rows, G, (const i64*)offs.p, (int*)oc.data, (unsigned char*)c.data);
   CUDA_TRY(cudaGetLastError());
   g_stats.kernel_launches += 5;
 }
@@ -2293,8 +2294,8 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
       oc.children[0].size = (int32_t)(n + 1);
       oc.children[0].data_bytes = (size_t)(n + 1) * (big ? 8 : 4);
       oc.children[0].data = out_alloc(al, oc.children[0].data_bytes, stream);
-      if (big) k_string_copy<i64><<<grid_for(n * 32, 256, 8), 256, 0, stream>>>(kc, (const int*)perm.p, n, (const i64*)offs.p, (i64*)oc.children[0].data, (unsigned char*)oc.data);
-      else k_string_copy<int><<<grid_for(n * 32, 256, 8), 256, 0, stream>>>(kc, (const int*)perm.p, n, (const i64*)offs.p, (int*)oc.children[0].data, (unsigned char*)oc.data);
+      if (big) k_string_copy<i64><<<grid_for(n * 4, 256, 8), 256, 0, stream>>>(kc, (const int*)perm.p, n, (const i64*)offs.p, (i64*)oc.children[0].data, (unsigned char*)oc.data);
+      else k_string_copy<int><<<grid_for(n * 4, 256, 8), 256, 0, stream>>>(kc, (const int*)perm.p, n, (const i64*)offs.p, (int*)oc.children[0].data, (unsigned char*)oc.data);
       CUDA_TRY(cudaGetLastError());
       g_stats.kernel_launches += 5;
     }

@@ -1309,19 +1309,24 @@ template <typename OffT>
 __global__ void k_string_copy(DKeyCol c, const int* __restrict__ rows, i64 ngroups, const i64* __restrict__ offs,
                               OffT* __restrict__ out_offs, unsigned char* __restrict__ chars)
 {
-  // one warp per string
-  const int lane = threadIdx.x & 31;
-  const i64 warp0 = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
-  for (i64 g = warp0; g <= ngroups; g += nwarps) {
-    if (lane == 0) out_offs[g] = (OffT)offs[g];
+  // four lanes per string, 8 bytes per lane and step (key strings are short: a warp per string left most of
+  // its lanes idle); the source is read as aligned words, the destination written byte by byte
+  const int sub = threadIdx.x & 3;
+  const i64 s0 = ((i64)blockIdx.x * blockDim.x + threadIdx.x) >> 2;
+  const i64 ns = ((i64)gridDim.x * blockDim.x) >> 2;
+  for (i64 g = s0; g <= ngroups; g += ns) {
+    if (sub == 0) out_offs[g] = (OffT)offs[g];
     if (g == ngroups) break;
     const i64 len = offs[g + 1] - offs[g];
     if (len == 0) continue;
     const i64 idx = c.offset + rows[g];
     const unsigned char* src = c.data + str_offset(c, idx);
     unsigned char* dst = chars + offs[g];
-    for (i64 b = lane; b < len; b += 32) dst[b] = src[b];
+    for (i64 b = (i64)sub * 8; b < len; b += 32) {
+      const int nb = (int)(len - b < 8 ? len - b : 8);
+      u64 v = load_bytes8(src + b, nb);
+      for (int i = 0; i < nb; ++i) { dst[b + i] = (unsigned char)v; v >>= 8; }
+    }
   }
 }
 

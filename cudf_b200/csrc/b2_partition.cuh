@@ -62,7 +62,8 @@ __device__ __forceinline__ void rp_keys4(const DPlan& P, i64 row0, int nv, u64 (
 // keys are therefore taken out before the rows are partitioned:
 //   k_hot_sample   256K evenly spaced rows -> occurrences per key (a global counting table), and the
 //                  largest magnitude among the sampled values (places the fixed-point windows)
-//   k_hot_select   the keys seen most often (at most HOT_MAX, at least 3 times each) -> the hot set: an
+//   k_hot_hist /   the keys seen most often (at most HOT_MAX, at least 3 times each) -> the hot set: an
+//   k_hot_select
 //                  open-addressing table of HOT_SLOTS key cells and a dense id per key
 //   k_rp_count<..., HOT>  folds the rows of hot keys into per-CTA fixed-point accumulators (fx_split /
 //                  fx_add: native 32-bit shared-memory atomics, which keep their rate on hot addresses) and
@@ -79,8 +80,10 @@ constexpr int HOT_ACC_WORDS  = 4;         // global accumulators per hot key: n,
 struct DHot {
   u64* keys;        // [HOT_SLOTS] hot-set table, EMPTY = free
   unsigned short* ids;  // [HOT_SLOTS] dense id of the key in the same slot
-  u32* info;        // [0] number of hot keys, [1] 1 + largest biased exponent among the sampled values
+  u32* info;        // [0] number of hot keys, [1] 1 + largest biased exponent among the sampled values,
+                    // [4, 260) keys per occurrence count (k_hot_hist)
   u64* acc;         // [HOT_MAX][HOT_ACC_WORDS] finished accumulators (filled by k_rp_count)
+  u32* row_mask;    // one bit per row: the row's key is hot (written by k_rp_count, read by k_rp_scatter)
 };
 
 __device__ __forceinline__ int hot_find(const u64* hk, u64 key, u64 h)
@@ -126,33 +129,40 @@ __global__ void __launch_bounds__(256) k_hot_sample(const __grid_constant__ DPla
   if ((threadIdx.x & 31) == 0 && emax) atomicMax(info + 1, emax);
 }
 
-// single CTA of 1024 threads; `hot.keys` arrives filled with EMPTY, `hot.info[0]` zero
-__global__ void __launch_bounds__(1024) k_hot_select(const u64* __restrict__ ckeys, const u32* __restrict__ ccnt, DHot hot)
+// keys per (clamped) occurrence count: `hist` = 256 zeroed words
+__global__ void __launch_bounds__(256) k_hot_hist(const u32* __restrict__ ccnt, u32* __restrict__ hist)
 {
-  __shared__ u32 s_hist[256];   // keys per (clamped) count
-  __shared__ u32 s_min, s_n;
-  if (threadIdx.x < 256) s_hist[threadIdx.x] = 0;
-  if (threadIdx.x == 0) s_n = 0;
+  __shared__ u32 s_hist[256];
+  s_hist[threadIdx.x] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < HOT_COUNT_SLOTS; i += blockDim.x) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < HOT_COUNT_SLOTS; i += gridDim.x * blockDim.x) {
     const u32 c = ccnt[i];
     if (c >= HOT_MIN_COUNT) atomicAdd(&s_hist[c < 255u ? c : 255u], 1u);
   }
   __syncthreads();
+  if (s_hist[threadIdx.x]) atomicAdd(&hist[threadIdx.x], s_hist[threadIdx.x]);
+}
+
+// `hot.keys` arrives filled with EMPTY, `hot.info[0]` (the id counter, then the number of hot keys) zero.
+// Every CTA derives the same threshold from the histogram: the smallest count from which on at most HOT_MAX
+// keys qualify.
+__global__ void __launch_bounds__(256) k_hot_select(const u64* __restrict__ ckeys, const u32* __restrict__ ccnt,
+                                                    const u32* __restrict__ hist, DHot hot)
+{
+  __shared__ u32 s_min;
   if (threadIdx.x == 0) {
-    // the smallest count from which on at most HOT_MAX keys qualify
     u32 total = 0, t = 256;
-    while (t > HOT_MIN_COUNT && total + s_hist[t - 1] <= (u32)HOT_MAX) { --t; total += s_hist[t]; }
+    while (t > HOT_MIN_COUNT && total + hist[t - 1] <= (u32)HOT_MAX) { --t; total += hist[t]; }
     s_min = t;
   }
   __syncthreads();
   const u32 tmin = s_min;
-  for (int i = threadIdx.x; i < HOT_COUNT_SLOTS; i += blockDim.x) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < HOT_COUNT_SLOTS; i += gridDim.x * blockDim.x) {
     const u32 c = ccnt[i];
-    if (c < tmin || (c < 255u ? c : 255u) < tmin) continue;
+    if ((c < 255u ? c : 255u) < tmin) continue;
     const u64 key = ckeys[i];
-    const u32 id = atomicAdd(&s_n, 1u);
-    if (id >= (u32)HOT_MAX) continue;  // (cannot happen: tmin bounds the number of qualifying keys)
+    const u32 id = atomicAdd(hot.info, 1u);  // (at most HOT_MAX keys qualify: tmin bounds them)
+    if (id >= (u32)HOT_MAX) continue;
     u32 idx = (u32)rp_hash(key) & (HOT_SLOTS - 1);
     for (;;) {
       const u64 old = atomicCAS(hot.keys + idx, EMPTY, key);
@@ -160,8 +170,6 @@ __global__ void __launch_bounds__(1024) k_hot_select(const u64* __restrict__ cke
       idx = (idx + 1u) & (HOT_SLOTS - 1);  // terminates: at most HOT_MAX keys in HOT_SLOTS slots
     }
   }
-  __syncthreads();
-  if (threadIdx.x == 0) hot.info[0] = s_n < (u32)HOT_MAX ? s_n : (u32)HOT_MAX;
 }
 
 // ------------------------------------------------------------------------------ level-1 histogram (+ HyperLogLog)
@@ -188,7 +196,7 @@ __global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant_
   for (int i = threadIdx.x; i < (1 << RP_BITS_TOP); i += blockDim.x) s_hist[i] = 0;
   if (WITH_HLL) for (int i = threadIdx.x; i < HLL_REGS; i += blockDim.x) s_regs[i] = 0;
   if (HOT) {
-    nh = (int)hot.info[0];
+    nh = (int)min(hot.info[0], (u32)HOT_MAX);
     if (hot.info[1]) {
       const int emax = (int)hot.info[1] - 1;
       bx = emax + FX_HEADROOM - FX_MAX_SHIFT;
@@ -208,10 +216,12 @@ __global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant_
       if (P.cells[c].op == OP_SSQ_F) c_ssq = c;
     }
   const i64 nquads = (P.nrows + 3) / 4;
-  for (i64 q = (i64)blockIdx.x * blockDim.x + threadIdx.x; q < nquads; q += (i64)gridDim.x * blockDim.x) {
+  // (whole warps stay in the loop — a lane beyond the last quad has no rows — because the hot-row mask of
+  // 8 consecutive quads is put together with shuffles)
+  for (i64 q = (i64)blockIdx.x * blockDim.x + threadIdx.x; q - (threadIdx.x & 31) < nquads; q += (i64)gridDim.x * blockDim.x) {
     u64 kk[4];
     u32 act;
-    const int nv = (int)min((i64)4, P.nrows - q * 4);
+    const int nv = (int)max((i64)0, min((i64)4, P.nrows - q * 4));
     rp_keys4(P, q * 4, nv, kk, act);
     u64 hh[4];
     int hs[4];
@@ -224,6 +234,14 @@ __global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant_
         hs[j] = hot_find(hk, kk[j], hh[j]);
         if (hs[j] >= 0) hotm |= 1u << j;
       }
+    }
+    if (HOT && nh > 0) {
+      // bit r of word w of the row mask = row 32 w + r: this quad's four bits sit at 4 (q mod 8) of word q / 8
+      u32 w = hotm << (4 * (threadIdx.x & 7));
+      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 1);
+      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 2);
+      w |= __shfl_xor_sync(0xFFFFFFFFu, w, 4);
+      if ((threadIdx.x & 7) == 0 && q < nquads) hot.row_mask[q >> 3] = w;
     }
     if (HOT && hotm) {
       const DValCol& vc = P.vals[0];
@@ -262,7 +280,7 @@ __global__ void __launch_bounds__(RP_BLOCK, 1) k_rp_count(const __grid_constant_
       if (!((act >> j) & 1u) || ((hotm >> j) & 1u)) continue;
       atomicAdd(&s_hist[hh[j] >> (64 - RP_BITS_TOP)], 1u);
       if (WITH_HLL) {
-        const u64 h = mix64(kk[j] ^ 0x5bd1e9955bd1e995ull);  // same registers as k_hll
+        const u64 h = hh[j] * 0x9E3779B97F4A7C15ull;  // (the partition hash, re-spread: these registers are only ever read alone)
         const u32 idx  = (u32)(h >> (64 - HLL_BITS));
         const u32 rank = (u32)__clzll((i64)((h << HLL_BITS) | (1ull << (HLL_BITS - 1)))) + 1u;
         if (s_regs[idx] < rank) atomicMax(&s_regs[idx], rank);
@@ -386,24 +404,16 @@ __device__ __forceinline__ void rp_tile_plan(const RpTile& t, u64* cursors, int 
 }
 
 // level 1: input rows -> records in the region of their digit
-// (`hot_keys`: the hot-set table whose keys k_rp_count folded already — their rows are left out here.  The
-// table is copied into the staging array of the values when that is unused (records of other shapes than
-// "one value column without nulls"), else behind the staging arrays: HOT_SLOTS * 8 more bytes of dynamic
-// shared memory.)
-__host__ __device__ constexpr size_t rp_scatter_hot_offset(int fan) { return (rp_tile_smem(fan) + 15) & ~(size_t)15; }
-
+// (`hot_rows`: one bit per row, set for the rows whose keys k_rp_count folded already — they are left out here)
 __global__ void __launch_bounds__(RPS_BLOCK, 2) k_rp_scatter(const __grid_constant__ DPlan P, const DScatter D,
-                                                          const u64* __restrict__ hot_keys)
+                                                          const u32* __restrict__ hot_rows)
 {
   extern __shared__ __align__(16) unsigned char rp_stage[];
   const RpTile t = rp_tile_carve(rp_stage, D.fan);
   // one value column without nulls is the common case: its values are loaded together with the keys and
   // staged with them; other shapes stage the key and the row, and gather the value words at copy-out
   const bool simple = P.nvals == 1 && D.dst.valid_word < 0;
-  static_assert(HOT_SLOTS <= RP_TILE, "the hot-set table fits the staging array of the values");
-  u64* hk = simple ? (u64*)(rp_stage + rp_scatter_hot_offset(D.fan)) : t.vals;
   for (int i = threadIdx.x; i < D.fan; i += blockDim.x) t.hist[i] = 0;
-  if (hot_keys) for (int i = threadIdx.x; i < HOT_SLOTS; i += blockDim.x) hk[i] = hot_keys[i];
   __syncthreads();
   const i64 ntiles = (P.nrows + RP_TILE - 1) / RP_TILE;
   const u32 dmask = (u32)D.fan - 1u;
@@ -420,6 +430,7 @@ __global__ void __launch_bounds__(RPS_BLOCK, 2) k_rp_scatter(const __grid_consta
       u64 k4[4];
       u32 a4;
       rp_keys4(P, row0, nv, k4, a4);
+      if (hot_rows && nv > 0) a4 &= ~(__ldg(hot_rows + (row0 >> 5)) >> (row0 & 31));  // (row0 is a multiple of 4)
       act |= a4 << (4 * g);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -431,9 +442,7 @@ __global__ void __launch_bounds__(RPS_BLOCK, 2) k_rp_scatter(const __grid_consta
     for (int j = 0; j < RP_ROWS; ++j) {
       rank[j] = 0;
       if ((act >> j) & 1u) {
-        const u64 h = rp_hash(kk[j]);
-        if (hot_keys && kk[j] != EMPTY && hot_find(hk, kk[j], h) >= 0) { act &= ~(1u << j); continue; }
-        const u32 d = (u32)(h >> D.shift) & dmask;
+        const u32 d = (u32)(rp_hash(kk[j]) >> D.shift) & dmask;
         rank[j] = (d << 16) | atomicAdd(&t.hist[d], 1u);  // a tile holds 4096 rows: the rank fits 16 bits
       }
     }

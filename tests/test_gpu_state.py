@@ -87,6 +87,25 @@ def test_emulated_ranks_partials_shuffle_equals_one_shot(config, ranks):
     assert got[0][0].size == exp[0][0].size
 
 
+def test_pack_into_the_largest_number_of_destinations():
+    """b2_state_pack accepts up to 4096 destinations; the scatter kernel then needs 64 KB of dynamic shared
+    memory (beyond the 48 KB default).  All records merged back into one state give the one-shot result."""
+    import cudf_b200 as cb
+    w = workloads.make(3, 20_000, scale_domain=True)
+    reqs = [(v, AGGS) for v, _ in w.requests]
+    gb, dreqs = _device_objects(w.keys, reqs, w.null_policy, 0, 20_000)
+    st = cb.GroupByState(gb, dreqs)
+    st.update()
+    records, counts = st.pack(4096)
+    assert len(counts) == 4096 and sum(counts) == st.num_groups() and max(counts) < 40
+    total = sum(counts)
+    st.reset()
+    st.merge(records[: total * st.record_bytes], total)
+    got = _to_host(st.finalize())
+    exp = oracle.groupby(w.keys, reqs, w.null_policy)
+    H.assert_same_result(got, exp, reqs, scales=H.result_scales(w.keys, reqs, w.null_policy))
+
+
 @pytest.mark.parametrize("estimate", [3, 4000, 6000, 10**7])
 def test_merge_into_a_table_sized_from_an_estimate(estimate):
     """An empty state sized from an estimate of the distinct keys: too small an estimate (3, 4000 for
