@@ -19,6 +19,8 @@ Prints ONE JSON line (rank 0):
   parity       checks of the LAST timed step's result computed after the timed region (every N);
   configs      N = 1: one entry per other configuration (C1, C3, C4, C5) at full size, inputs generated
                on the device: ms per call (median of 5), kernel ms, algorithmic bytes, fraction of the peak;
+  c3_strong    (N > 1) the 500M-row all-distinct configuration split over the N ranks, rows shuffled by key
+               before the local aggregate, every group checked exactly
   c4_strong    the 1B-row skewed configuration split by rows over the N ranks (1B/N rows each), a fresh
                distributed groupby per step: ms per step (max over ranks) and rows/s, with its own parity.
 ``--impl reference`` times the reference's CPU path (pandas, single-threaded by construction) on a
@@ -329,6 +331,34 @@ def parity_c4(raw, out):
             "max_err_var_over_scale": e_var, "rtol": 1e-11}
 
 
+def parity_c3(raw, out, total_rows):
+    """C3 (sum, min, max, count of an int64 column; int64 keys U[0,100M)): owned key sets disjoint, union =
+    input keys, and every owned group's sum / min / max / count equal — integers, exactly — to torch
+    references over all ranks' inputs (index_add / scatter_reduce / bincount on 100M-entry arrays, all-reduced)."""
+    import torch
+    k, v = raw["k"], raw["v"]
+    domain = 100_000_000
+    keys, res = out
+    ok_keys = _tensor(keys.columns()[0], torch.int64)
+    cols = res[0].columns()
+    s, mn, mx = (_tensor(cols[i], torch.int64) for i in range(3))
+    cnt = _tensor(cols[3], torch.int32).to(torch.int64)
+    ref_cnt = _all_reduce(torch.bincount(k, minlength=domain))
+    ref_sum = _all_reduce(torch.zeros(domain, dtype=torch.int64, device=k.device).index_add_(0, k, v))
+    ref_min = _all_reduce(torch.full((domain,), 2**62, dtype=torch.int64, device=k.device).scatter_reduce_(0, k, v, "amin"), "min")
+    ref_max = _all_reduce(torch.full((domain,), -2**62, dtype=torch.int64, device=k.device).scatter_reduce_(0, k, v, "amax"), "max")
+    owned = _all_reduce(torch.bincount(ok_keys, minlength=domain))
+    disjoint = int(owned.max()) <= 1
+    union_ok = bool(((owned > 0) == (ref_cnt > 0)).all())
+    bad = ((s != ref_sum[ok_keys]) | (mn != ref_min[ok_keys]) | (mx != ref_max[ok_keys]) | (cnt != ref_cnt[ok_keys])).sum()
+    bad = int(_all_reduce(bad.reshape(1).clone()).item())
+    rows = int(_all_reduce(cnt.sum().reshape(1).clone()).item())
+    ok = disjoint and union_ok and bad == 0 and rows == total_rows
+    return {"ok": bool(ok), "owned_key_sets_disjoint": disjoint, "union_equals_input_keys": union_ok,
+            "groups_total": int((owned > 0).sum()), "groups_expected": int((ref_cnt > 0).sum()),
+            "groups_with_a_wrong_sum_min_max_or_count": bad, "rows_counted": rows, "rows_expected": total_rows}
+
+
 def time_calls(fn, n, barrier):
     """n calls of fn, each bracketed by CUDA events on the current stream: list of ms."""
     import torch
@@ -454,6 +484,39 @@ def run_c4_strong(world, rank, device, steps, reuse):
         entry.update({"kernel_ms": k, "algorithmic_bytes": alg, "GBps_call": alg / (med / 1e3) / 1e9,
                       "frac_call": alg / (med / 1e3) / 1e9 / peak, "frac": alg / (k / 1e3) / 1e9 / peak if k > 0 else None})
     return entry
+
+
+def run_c3_strong(world, rank, device, steps):
+    """N > 1: the 500M-row all-distinct configuration split by rows over the ranks, the ROWS shuffled by key
+    (hash_partition + one all-to-all per column) before a local aggregate; a fresh object per step."""
+    import torch
+    import torch.distributed as dist
+    import cudf_b200 as cb
+    from cudf_b200.distributed import DistributedGroupBy
+    n = workloads.FULL_ROWS[3] // world
+    w = workloads.make_device(3, n, device=device, rank=rank)
+    keys = cb.Table(w.keys)
+    reqs = w.groupby_requests()
+    res = {}
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        res["out"] = DistributedGroupBy(keys, strategy="rows").aggregate(reqs)
+    for _ in range(2):
+        step()
+    ms = time_calls(step, steps, barrier)
+    t = torch.tensor(ms, device=device, dtype=torch.float64)
+    _all_reduce(t, "max")
+    ms = [float(x) for x in t.tolist()]
+    par = parity_c3(w.raw, res["out"], n * world)
+    med = statistics.median(ms)
+    return {"workload": WORKLOADS[3], "strategy": "rows shuffled by key, then a local aggregate", "rows_total": n * world,
+            "rows_per_gpu": n, "n_gpus": world, "steps": steps, "ms_per_step": med, "ms_per_step_min": min(ms),
+            "ms_per_step_max": max(ms), "rows_per_s": n * world / (med / 1e3), "groups": par["groups_total"],
+            "scaling": "strong", "parity": par}
 
 
 def run_b2(args):
@@ -616,6 +679,13 @@ def run_b2(args):
         except Exception as e:
             c4 = {"error": f"{type(e).__name__}: {e}"}
         torch.cuda.empty_cache()
+    c3 = None
+    if world > 1 and not args.no_c4:
+        try:
+            c3 = run_c3_strong(world, rank, device, 5)
+        except Exception as e:
+            c3 = {"error": f"{type(e).__name__}: {e}"}
+        torch.cuda.empty_cache()
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -646,6 +716,8 @@ def run_b2(args):
             "parity": parity,
             "c4_strong": c4,
         }
+        if c3 is not None:
+            line["c3_strong"] = c3
         if world == 1 and not args.no_configs:
             # C4 at full size on one GPU is the c4_strong entry above
             line["configs"] = run_other_configs(peak, (1, 5, 3) if c4 and "error" not in c4 else (1, 5, 3, 4))
