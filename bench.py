@@ -29,6 +29,7 @@ bounded sample of the same workload; libcudf itself cannot be built offline.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -575,6 +576,10 @@ def run_b2(args):
     barrier()
     with sampler:
         events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        # the interpreter's cyclic garbage collector is paused while steps are timed, as timeit does: a
+        # collection inside one rank's step stalls every rank of that step
+        gc.collect()
+        gc.disable()
         barrier()
         events[0].record()
         for i in range(args.steps):
@@ -584,6 +589,7 @@ def run_b2(args):
             kernel_ms.append(st.aggregate_kernel_ms)
             events[i + 1].record()
         barrier()
+        gc.enable()
         ms = events[0].elapsed_time(events[-1])
         per_step = torch.tensor([events[i].elapsed_time(events[i + 1]) for i in range(args.steps)], device=device,
                                 dtype=torch.float64)
