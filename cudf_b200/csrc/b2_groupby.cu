@@ -984,7 +984,7 @@ bool aggregate_partitioned(b2_groupby_state& st, const b2_groupby& gb, cudaStrea
   }
 
   // 2. digits: buckets of about half a shared-memory table each (two CTAs of the aggregate kernel per SM)
-  const int slot_bytes = with_hot ? RPA_FIXED_SLOT_BYTES : 8 * (1 + sc.ncells);
+  const int slot_bytes = (with_hot ? RPA_FIXED_SLOT_BYTES : 8 * (1 + sc.ncells)) + RPA_INDEX_BYTES;
   int budget = std::min((device_info().smem_optin - 2048), 110 * 1024);
   if (gb.shared_table_bytes > 0) budget = std::min(budget, std::max(gb.shared_table_bytes, 257 * slot_bytes));
   int slots = 256;

@@ -632,6 +632,7 @@ struct DBuckets {
 // as 32 bits — nine native 32-bit atomics per record instead of three 64-bit ones, which shared memory only
 // does as compare-and-swap loops.  `vexp` = 1 + the largest biased exponent among the sampled values.
 constexpr int RPA_FIXED_SLOT_BYTES = 8 + 8 + 8 + 4 + 8 * FX_LIMBS;
+constexpr int RPA_INDEX_BYTES = 2;  // per slot: the claim-order index
 
 template <bool FIXED>
 __global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_constant__ DPlan P, const DBuckets B, DCtrl* ctrl,
@@ -641,7 +642,6 @@ __global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_cons
   __shared__ i64 s_bucket;
   __shared__ u32 s_count, s_fail, s_special;
   __shared__ u64 s_outbase;
-  __shared__ u32 s_warp[RPA_BLOCK / 32];
   const int S  = B.slots;
   const int NS = S + 1;
   u64* skeys  = (u64*)rp_smem;   // [NS]
@@ -652,6 +652,9 @@ __global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_cons
   u32* fcnt   = (u32*)(feq + NS);
   int* flx    = (int*)(fcnt + NS);
   int* flq    = flx + FX_LIMBS * NS;
+  // slots in the order they were claimed: the finished groups are written in that order, consecutive
+  // threads to consecutive list entries, without scanning the table for occupied slots
+  unsigned short* sidx = FIXED ? (unsigned short*)(flq + FX_LIMBS * NS) : (unsigned short*)(scells + (size_t)P.ncells * NS);
   int fx_bx = FX_NEVER, fx_bq = FX_NEVER, c_sum = -1, c_cnt = -1, c_ssq = -1;
   if (FIXED) {
     const u32 ve = __ldg(vexp);
@@ -724,7 +727,7 @@ __global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_cons
               if (k == EMPTY) {
                 if (*(volatile u32*)&s_count >= fill_limit) break;
                 k = atomicCAS(skeys + idx, EMPTY, key);
-                if (k == EMPTY) { atomicAdd(&s_count, 1u); k = key; }
+                if (k == EMPTY) { sidx[atomicAdd(&s_count, 1u)] = (unsigned short)idx; k = key; }
               }
               if (k == key) { slot = (int)idx; break; }
               idx = (idx + 1u) & smask;
@@ -819,28 +822,17 @@ __global__ void __launch_bounds__(RPA_BLOCK, 2) k_rp_aggregate(const __grid_cons
     }
     __syncthreads();
     if (s_outbase + ngroups > (u64)B.out_cap) continue;
-    u32 run = 0;  // groups written by earlier rounds of this loop
-    for (int base = 0; base < NS; base += blockDim.x) {
-      const int i = base + threadIdx.x;
-      const bool occ = i < S ? skeys[i] != EMPTY : (i == S && s_special != 0);
-      const u32 m = __ballot_sync(0xFFFFFFFFu, occ);
-      if (lane == 0) s_warp[wid] = __popc(m);
-      __syncthreads();
-      u32 before = 0, total = 0;
-      for (int w = 0; w < RPA_BLOCK / 32; ++w) { const u32 c = s_warp[w]; if (w < wid) before += c; total += c; }
-      if (occ) {
-        const i64 g = (i64)s_outbase + run + before + __popc(m & ((1u << lane) - 1u));
-        B.out[g] = i < S ? skeys[i] : EMPTY;
-        if (FIXED) {
-          if (c_cnt >= 0) B.out[(i64)(1 + c_cnt) * B.out_cap + g] = (u64)fcnt[i];
-          if (c_sum >= 0) B.out[(i64)(1 + c_sum) * B.out_cap + g] = (u64)__double_as_longlong(fex[i] + fx_take(flx, NS, i, fx_bx));
-          if (c_ssq >= 0) B.out[(i64)(1 + c_ssq) * B.out_cap + g] = (u64)__double_as_longlong(feq[i] + fx_take(flq, NS, i, fx_bq));
-        } else {
-          for (int c = 0; c < P.ncells; ++c) B.out[(i64)(1 + c) * B.out_cap + g] = scells[(size_t)c * NS + i];
-        }
+    for (u32 pos = threadIdx.x; pos < ngroups; pos += blockDim.x) {
+      const int i = pos < s_count ? (int)sidx[pos] : S;  // (the special slot, if used, comes last)
+      const i64 g = (i64)s_outbase + pos;
+      B.out[g] = i < S ? skeys[i] : EMPTY;
+      if (FIXED) {
+        if (c_cnt >= 0) B.out[(i64)(1 + c_cnt) * B.out_cap + g] = (u64)fcnt[i];
+        if (c_sum >= 0) B.out[(i64)(1 + c_sum) * B.out_cap + g] = (u64)__double_as_longlong(fex[i] + fx_take(flx, NS, i, fx_bx));
+        if (c_ssq >= 0) B.out[(i64)(1 + c_ssq) * B.out_cap + g] = (u64)__double_as_longlong(feq[i] + fx_take(flq, NS, i, fx_bq));
+      } else {
+        for (int c = 0; c < P.ncells; ++c) B.out[(i64)(1 + c) * B.out_cap + g] = scells[(size_t)c * NS + i];
       }
-      run += total;
-      __syncthreads();
     }
   }
 }
