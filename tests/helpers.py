@@ -22,9 +22,9 @@ RTOL_F32 = 1e-5
 STRICT_FROM = 1e-3
 # one record per compared float column: what, values compared, values held to the strict tolerance,
 # the largest strict relative error among those, values that only pass through the scaled bound, the
-# largest error relative to the scale among them (printed by the parity tests, written to PARITY_STATS_FILE)
+# largest error relative to the scale among them (printed by the parity tests; also appended to
+# $B2_TEST_LOG_DIR/parity_stats.jsonl when that variable names a directory)
 PARITY_STATS: list = []
-PARITY_STATS_FILE = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out", "parity_stats.jsonl")
 
 
 def record_parity_stats(label: str):
@@ -34,13 +34,14 @@ def record_parity_stats(label: str):
     for r in recs:
         print(f"[parity] {label}: {r['what']}: {r['n']} values, strict {r['strict_n']} (max rel err {r['strict_max']:.3e}, "
               f"rtol {r['rtol']:g}), scaled-only {r['scaled_n']} (max err/scale {r['scaled_max']:.3e})")
-    try:
-        os.makedirs(os.path.dirname(PARITY_STATS_FILE), exist_ok=True)
-        with open(PARITY_STATS_FILE, "a", encoding="utf-8") as f:
-            for r in recs:
-                f.write(json.dumps(r) + "\n")
-    except OSError:
-        pass
+    log_dir = os.environ.get("B2_TEST_LOG_DIR")
+    if log_dir and os.path.isdir(log_dir):
+        try:
+            with open(os.path.join(log_dir, "parity_stats.jsonl"), "a", encoding="utf-8") as f:
+                for r in recs:
+                    f.write(json.dumps(r) + "\n")
+        except OSError:
+            pass
     return recs
 
 

@@ -101,7 +101,7 @@ def test_two_rank_distributed_groupby_matches_oracle(tmp_path):
                          capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert out.stdout.count("OK") == 10
-    log_dir = os.path.join(ROOT, "gpurun_out")   # keep rank 0's summary lines beside the other run logs
-    if os.path.isdir(log_dir):
+    log_dir = os.environ.get("B2_TEST_LOG_DIR")   # keep rank 0's summary lines where the caller collects its logs
+    if log_dir and os.path.isdir(log_dir):
         with open(os.path.join(log_dir, "two_rank_worker.log"), "w", encoding="utf-8") as f:
             f.write("".join(ln + "\n" for ln in out.stdout.splitlines() if ln.endswith("OK")))
