@@ -2224,7 +2224,29 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
 
     // 1. rows per (partition, CTA), 2. their starts by one exclusive scan, 3. the permutation
     Scratch counts(cells * 8, stream), starts((cells + 1) * 8, stream), d_offsets((size_t)(num_parts + 1) * 8, stream);
-    Scratch cta_scratch, perm((size_t)n * 4, stream);
+    // columns the placing kernel moves itself (fixed width, no null mask); the others go through the permutation
+    auto direct = std::make_unique<DDirectCols>();
+    std::memset(direct.get(), 0, sizeof(DDirectCols));
+    std::vector<bool> is_direct((size_t)num_columns, false);
+    bool need_perm = false;
+    for (int c = 0; c < num_columns; ++c) {
+      const b2_column_view& in = columns[c];
+      if (in.type_id != B2_STRING && in.null_mask == nullptr) {
+        b2_owned_column& oc = out_columns[c];
+        init_owned(oc, in.type_id, n, false, al, stream);
+        oc.scale = in.scale;
+        const int w = width_of(in.type_id);
+        const int i = direct->n++;
+        direct->width[i] = w;
+        direct->src[i] = (const unsigned char*)in.data + (size_t)in.offset * w;
+        direct->dst[i] = (unsigned char*)oc.data;
+        is_direct[(size_t)c] = true;
+      } else {
+        need_perm = true;
+      }
+    }
+    Scratch cta_scratch, perm;
+    if (need_perm) perm = Scratch((size_t)n * 4, stream);
     if (Q.counters_in_global) {
       cta_scratch = Scratch(cells * 4, stream);
       CUDA_TRY(cudaMemsetAsync(cta_scratch.p, 0, cta_scratch.bytes, stream));
@@ -2235,13 +2257,14 @@ b2_status b2_hash_partition(const b2_column_view* columns, int32_t num_columns, 
     k_partition_offsets<<<grid_for(num_parts + 1, 256, 4), 256, 0, stream>>>((const i64*)starts.p, num_parts, grid, (i64*)d_offsets.p);
     CUDA_TRY(cudaMemcpyAsync(offsets, d_offsets.p, (size_t)(num_parts + 1) * 8, cudaMemcpyDeviceToHost, stream));
     if (Q.counters_in_global) CUDA_TRY(cudaMemsetAsync(cta_scratch.p, 0, cta_scratch.bytes, stream));
-    k_partition_perm<<<grid, PART_BLOCK, smem, stream>>>(P, Q, (const i64*)starts.p, (u32*)cta_scratch.p, (int*)perm.p);
+    k_partition_perm<<<grid, PART_BLOCK, smem, stream>>>(P, Q, (const i64*)starts.p, (u32*)cta_scratch.p, (int*)perm.p, *direct);
     CUDA_TRY(cudaGetLastError());
     g_stats.kernel_launches += 3;
 
     // 4. every column gathered by the permutation
     Scratch null_scratch(8, stream);
     for (int c = 0; c < num_columns; ++c) {
+      if (is_direct[(size_t)c]) continue;
       const b2_column_view& in = columns[c];
       b2_owned_column& oc = out_columns[c];
       const bool nullable = in.null_mask != nullptr;

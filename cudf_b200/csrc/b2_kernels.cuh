@@ -1649,10 +1649,21 @@ __global__ void k_partition_offsets(const i64* __restrict__ starts, int nparts, 
     offsets[p] = starts[(size_t)p * grid];  // (p == nparts reads the scan's closing total)
 }
 
-// perm[output position] = input row
+// Fixed-width columns without a null mask are moved by the kernel that places the rows: it reads them in row
+// order (coalesced) and writes each row to its output position — the rows of one partition inside a warp go
+// to consecutive positions — instead of being gathered through the permutation afterwards, which reads every
+// sector of a source column once per partition that has a row in it.
+struct DDirectCols {
+  int n;
+  int width[MAX_PART_COLS];
+  const unsigned char* src[MAX_PART_COLS];  // first element of the view
+  unsigned char* dst[MAX_PART_COLS];
+};
+
+// perm[output position] = input row (when `perm` is given), and the direct columns moved
 __global__ void __launch_bounds__(PART_BLOCK)
 k_partition_perm(const __grid_constant__ DPlan P, const DPartPlan Q, const i64* __restrict__ starts, u32* __restrict__ cta_scratch,
-                 int* __restrict__ perm)
+                 int* __restrict__ perm, const __grid_constant__ DDirectCols D)
 {
   extern __shared__ u32 s_cur[];
   const bool in_global = Q.counters_in_global != 0;
@@ -1670,8 +1681,17 @@ k_partition_perm(const __grid_constant__ DPlan P, const DPartPlan Q, const i64* 
     u32 base = 0;
     if (p != NO_DEST && (int)lane == lead) base = atomicAdd(&cur[p], (u32)__popc(peers));
     base = __shfl_sync(0xFFFFFFFFu, base, lead);
-    if (p != NO_DEST)
-      perm[starts[(size_t)p * gridDim.x + blockIdx.x] + (i64)base + __popc(peers & ((1u << lane) - 1u))] = (int)r;
+    if (p == NO_DEST) continue;
+    const i64 d = starts[(size_t)p * gridDim.x + blockIdx.x] + (i64)base + __popc(peers & ((1u << lane) - 1u));
+    if (perm) perm[d] = (int)r;
+    for (int c = 0; c < D.n; ++c) {
+      switch (D.width[c]) {
+        case 8: ((u64*)D.dst[c])[d] = __ldg((const u64*)D.src[c] + r); break;
+        case 4: ((u32*)D.dst[c])[d] = __ldg((const u32*)D.src[c] + r); break;
+        case 2: ((unsigned short*)D.dst[c])[d] = __ldg((const unsigned short*)D.src[c] + r); break;
+        default: D.dst[c][d] = D.src[c][r]; break;
+      }
+    }
   }
 }
 
