@@ -365,12 +365,26 @@ __host__ __device__ inline u32 murmur3_x86_32(const unsigned char* data, i64 len
   h ^= h >> 16; h *= 0x85ebca6bu; h ^= h >> 13; h *= 0xc2b2ae35u; h ^= h >> 16;
   return h;
 }
-// the same over a value held in a register (little endian, `nbytes` = 1, 2, 4 or 8)
+// the same over a value held in a register (little endian, `nbytes` = 1, 2, 4 or 8): whole 4-byte blocks go
+// through the block round directly, 1 or 2 bytes are the tail
 __host__ __device__ __forceinline__ u32 murmur3_x86_32_value(u64 v, int nbytes, u32 seed)
 {
-  unsigned char b[8];
-  for (int i = 0; i < 8; ++i) b[i] = (unsigned char)(v >> (8 * i));
-  return murmur3_x86_32(b, nbytes, seed);
+  const u32 c1 = 0xcc9e2d51u, c2 = 0x1b873593u;
+  u32 h = seed;
+  auto block = [&](u32 k) {
+    k *= c1; k = rotl32(k, 15); k *= c2;
+    h ^= k; h = rotl32(h, 13); h = h * 5u + 0xe6546b64u;
+  };
+  if (nbytes >= 4) block((u32)v);
+  if (nbytes == 8) block((u32)(v >> 32));
+  if (nbytes < 4) {
+    u32 k = (u32)v & (nbytes == 1 ? 0xFFu : 0xFFFFu);
+    k *= c1; k = rotl32(k, 15); k *= c2;
+    h ^= k;
+  }
+  h ^= (u32)nbytes;
+  h ^= h >> 16; h *= 0x85ebca6bu; h ^= h >> 13; h *= 0xc2b2ae35u; h ^= h >> 16;
+  return h;
 }
 __host__ __device__ __forceinline__ u32 hash_combine32(u32 lhs, u32 rhs)
 {

@@ -1631,12 +1631,20 @@ k_partition_count(const __grid_constant__ DPlan P, const DPartPlan Q, i64* __res
   const i64 lo = (i64)blockIdx.x * Q.rows_per_cta;
   const i64 hi = min(P.nrows, lo + Q.rows_per_cta);
   const u32 lane = threadIdx.x & 31u;
-  for (i64 r0 = lo + (threadIdx.x - lane); r0 < hi; r0 += blockDim.x) {
-    const i64 r = r0 + lane;
-    const u32 p = r < hi ? row_partition(P, Q, r) : NO_DEST;
-    // lanes headed for the same partition add once (with few partitions every lane would hit the same words)
-    const u32 peers = __match_any_sync(0xFFFFFFFFu, p);
-    if (p != NO_DEST && (int)lane == __ffs(peers) - 1) atomicAdd(&hist[p], (u32)__popc(peers));
+  // four rows per thread and step, their loads in flight together
+  for (i64 r0 = lo + (threadIdx.x - lane); r0 < hi; r0 += 4 * (i64)blockDim.x) {
+    u32 p[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const i64 r = r0 + (i64)u * blockDim.x + lane;
+      p[u] = r < hi ? row_partition(P, Q, r) : NO_DEST;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      // lanes headed for the same partition add once (with few partitions every lane would hit the same words)
+      const u32 peers = __match_any_sync(0xFFFFFFFFu, p[u]);
+      if (p[u] != NO_DEST && (int)lane == __ffs(peers) - 1) atomicAdd(&hist[p[u]], (u32)__popc(peers));
+    }
   }
   __syncthreads();
   for (int p = threadIdx.x; p < Q.nparts; p += blockDim.x) counts[(size_t)p * gridDim.x + blockIdx.x] = (i64)hist[p];
