@@ -1644,7 +1644,7 @@ void update_state(b2_groupby_state& st, const b2_groupby& gb, const b2_aggregati
 
 // ------------------------------------------------------------------------------ string keys through a dictionary
 // One-shot aggregates of many rows keyed on STRING columns (plus fixed-width ones): every string column is
-// first replaced by the slot index of its string in a dictionary table (k_dict_encode), so that the keys
+// first replaced by the id of its string in a dictionary (k_dict_encode), so that the keys
 // pack into one 64-bit cell and the packed-key paths (fused shared-memory tables, the partitioned path)
 // serve the call; the finished id column of the result is turned back into strings by gathering the
 // representative rows.  Worth it while a column's distinct strings are few enough for its dictionary (and
@@ -1659,7 +1659,8 @@ struct EncodedKeys {
   bool active = false;
   b2_groupby gb;                  // the caller's groupby with id columns in place of the string columns
   std::vector<int> cols;          // key indices that were strings
-  std::vector<Scratch> tables;    // per such column: the dictionary {tag | representative row}
+  std::vector<Scratch> tables;    // per such column: the dictionary (cells, pool of string prefixes, first rows)
+  std::vector<const int*> first_rows;  // ... and where its first rows start
   std::vector<Scratch> ids;       // per such column: UINT32 ids, element offset as the string column's
 };
 
@@ -1700,6 +1701,7 @@ bool encode_string_keys(const b2_groupby& gb, cudaStream_t stream, EncodedKeys& 
 
     Scratch ids((size_t)(c.offset + n) * sizeof(u32), stream);
     Scratch table;
+    const int* first_rows = nullptr;
     int64_t cap = 1024;
     while (cap < std::min<int64_t>(DICT_FIRST_CAP, std::max<int64_t>(n / 8, 1024))) cap *= 2;
     bool done = false;
@@ -1710,13 +1712,18 @@ bool encode_string_keys(const b2_groupby& gb, cudaStream_t stream, EncodedKeys& 
         if (cap2 == cap) break;
         cap = cap2;
       }
-      table = Scratch((size_t)cap * sizeof(u64), stream);
+      // cells, then the pool of string prefixes (one entry per id; ids lost to races for a cell stay unused,
+      // so the pool holds as many entries as the table has cells), then the first rows
+      const int64_t pool_cap = std::min<int64_t>(cap, (int64_t)DICT_ID_MASK - 1);
+      table = Scratch((size_t)cap * 8 + (size_t)pool_cap * 32 + (size_t)pool_cap * 4, stream);
       CUDA_TRY(cudaMemsetAsync(table.p, 0xFF, (size_t)cap * sizeof(u64), stream));
+      DDict D{(u64*)table.p, cap, (u64*)table.p + cap, (int*)((u64*)table.p + cap + pool_cap * 4), pool_cap};
       DCtrl h{};
       h.claim_limit = (u64)((double)cap * DICT_MAX_LOAD);
       CUDA_TRY(cudaMemcpyAsync(ctrl.p, &h, sizeof(DCtrl), cudaMemcpyHostToDevice, stream));
       const int grid = grid_for((n + DICT_ROWS - 1) / DICT_ROWS, DICT_BLOCK, 8);
-      k_dict_encode<<<grid, DICT_BLOCK, 0, stream>>>(*plan, (u64*)table.p, cap, (DCtrl*)ctrl.p, (u32*)ids.p);
+      k_dict_encode<<<grid, DICT_BLOCK, 0, stream>>>(*plan, D, (DCtrl*)ctrl.p, (u32*)ids.p);
+      first_rows = D.first_row;
       CUDA_TRY(cudaGetLastError());
       g_stats.kernel_launches++;
       CUDA_TRY(cudaMemcpyAsync(&h, ctrl.p, sizeof(DCtrl), cudaMemcpyDeviceToHost, stream));
@@ -1732,6 +1739,7 @@ bool encode_string_keys(const b2_groupby& gb, cudaStream_t stream, EncodedKeys& 
     dst = ColView(v);
     ek.cols.push_back((int)k);
     ek.tables.push_back(std::move(table));
+    ek.first_rows.push_back(first_rows);
     ek.ids.push_back(std::move(ids));
   }
   ek.gb.table_variant = 0;
@@ -1766,7 +1774,7 @@ void restore_string_keys(const EncodedKeys& ek, const b2_groupby& gb, cudaStream
     kc.offsets = (const unsigned char*)o.data + (size_t)o.offset * (o.type_id == B2_INT64 ? 8 : 4);
     kc.offs64 = o.type_id == B2_INT64;
     Scratch rows((size_t)G * sizeof(int), stream);
-    k_dict_rows<<<grid_for(G, 256, 8), 256, 0, stream>>>((const u32*)idc.data, c.null_mask, (const u64*)ek.tables[i].p, G, (int*)rows.p);
+    k_dict_rows<<<grid_for(G, 256, 8), 256, 0, stream>>>((const u32*)idc.data, c.null_mask, ek.first_rows[i], G, (int*)rows.p);
     CUDA_TRY(cudaGetLastError());
     g_stats.kernel_launches++;
     // the mask travels as it is: gather_strings must neither clear bits nor count (rows of null keys are -1)

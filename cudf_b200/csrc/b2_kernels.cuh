@@ -940,17 +940,71 @@ __global__ void __launch_bounds__(1024) k_hll(const __grid_constant__ DPlan P, u
 }
 
 // ------------------------------------------------------------------------------ string keys -> dictionary ids
-// A STRING key column is replaced by the slot index of its string in a dictionary table {tag | first row
-// seen}, so that (id, other keys) packs into one 64-bit key cell and the packed-key paths serve the
-// aggregate.  The table of a column with few distinct strings stays in L2, and so do the representatives'
-// bytes the probes compare against; the row's own string is read once, in row order.  `P` holds the one
-// string column as its only key.  ids[P.keys[0].offset + row] = slot (0 for a null row: its null bit or its
-// exclusion decides, not the payload).  CTAs stop at their next tile once the table is over its claim limit.
-constexpr int DICT_BLOCK = 256;
-constexpr int DICT_ROWS  = 4;  // rows per thread and tile, strided by the block so that loads coalesce
+// A STRING key column is replaced by the id of its string in a dictionary, so that (id, other keys) packs into
+// one 64-bit key cell and the packed-key paths serve the aggregate.  The dictionary is an open-addressing
+// table of 8-byte cells {hash tag(30) | clamped length(8) | id(26)} plus, per id, the first 32 bytes of the
+// string in a dense pool (ids are handed out in order of arrival: the pool of a column with few distinct
+// strings is a few contiguous megabytes that stay in L2, where the first rows' own strings — scattered over
+// the column — do not) and the first row that held it (for the bytes beyond 32, and for the output).  A probe
+// that finds its tag and length compares against the pool entry.  `P` holds the one string column as its only
+// key.  ids[P.keys[0].offset + row] = id (0 for a null row: its null bit or its exclusion decides, not the
+// payload).  CTAs stop at their next tile once the table or the pool is over its limit.
+constexpr int DICT_BLOCK  = 256;
+constexpr int DICT_ROWS   = 4;   // rows per thread and tile, strided by the block so that loads coalesce
+constexpr int DICT_INLINE = 32;  // string bytes kept in the pool
+constexpr u64 DICT_ID_MASK = (1ull << 26) - 1ull;
 
-__global__ void __launch_bounds__(DICT_BLOCK) k_dict_encode(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap,
-                                                            DCtrl* ctrl, u32* __restrict__ ids)
+struct DDict {
+  u64* cells;      // [cap], EMPTY = free
+  i64 cap;
+  u64* pool;       // [pool_cap][4]
+  int* first_row;  // [pool_cap]
+  i64 pool_cap;    // <= 2^26 - 2
+};
+
+// id of the string [p, p + len) of row `row`, inserting it when new; -1 after an overflow
+__device__ __forceinline__ i64 dict_find_insert(const DPlan& P, const DDict& D, const unsigned char* p, i64 len, i64 row, u64 h,
+                                                DCtrl* ctrl, int* s_new)
+{
+  const u64 head = ((h >> 34) << 34) | ((u64)(len < 255 ? len : 255) << 26);
+  u64 w[4];  // my first DICT_INLINE bytes, zero padded
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const i64 left = len - 8 * i;
+    w[i] = left > 0 ? load_bytes8(p + 8 * i, (int)(left < 8 ? left : 8)) : 0ull;
+  }
+  i64 idx = (i64)reduce64(h, (u64)D.cap);
+  for (int probe = 0; probe < GMEM_PROBES; ++probe) {
+    u64 k = *(volatile u64*)(D.cells + idx);
+    if (k == EMPTY) {
+      // the entry is written before the cell that publishes it; a thread that loses the race for the cell
+      // leaves its id unused
+      const u64 id = atomicAdd(&ctrl->out_cursor, 1ull);
+      if (id >= (u64)D.pool_cap) { ctrl->overflow = 1; return -1; }
+      u64* e = D.pool + id * 4;
+      e[0] = w[0]; e[1] = w[1]; e[2] = w[2]; e[3] = w[3];
+      D.first_row[id] = (int)row;
+      __threadfence();
+      k = atomicCAS(D.cells + idx, EMPTY, head | id);
+      if (k == EMPTY) { atomicAdd(s_new, 1); return (i64)id; }
+    }
+    if (((k ^ head) & ~DICT_ID_MASK) == 0) {  // same tag and (clamped) length
+      const u64 id = k & DICT_ID_MASK;
+      const ulonglong2* e = (const ulonglong2*)(D.pool + id * 4);
+      const ulonglong2 e0 = __ldcg(e), e1 = __ldcg(e + 1);
+      bool same = e0.x == w[0] && e0.y == w[1] && e1.x == w[2] && e1.y == w[3];
+      if (same && len > DICT_INLINE) same = rows_equal(P, row, (i64)__ldcg(D.first_row + id));
+      if (same) return (i64)id;
+    }
+    if (probe_gave_up(probe, ctrl, s_new)) return -1;
+    if (++idx == D.cap) idx = 0;
+  }
+  ctrl->overflow = 1;
+  return -1;
+}
+
+__global__ void __launch_bounds__(DICT_BLOCK) k_dict_encode(const __grid_constant__ DPlan P, const DDict D, DCtrl* ctrl,
+                                                            u32* __restrict__ ids)
 {
   __shared__ int s_new;
   __shared__ u32 s_stop;
@@ -978,7 +1032,7 @@ __global__ void __launch_bounds__(DICT_BLOCK) k_dict_encode(const __grid_constan
       if (row >= P.nrows) continue;
       u32 id = 0;
       if (live[j]) {
-        const i64 s = gmem_find_insert_rows(P, tbl, cap, 1, row, h[j], ctrl, &s_new);
+        const i64 s = dict_find_insert(P, D, c.data + b[j], e[j] - b[j], row, h[j], ctrl, &s_new);
         if (s >= 0) id = (u32)s;
       }
       ids[c.offset + row] = id;
@@ -998,12 +1052,12 @@ __global__ void __launch_bounds__(DICT_BLOCK) k_dict_encode(const __grid_constan
   }
 }
 
-// ids of the finished groups -> the representative rows of their strings (-1 for a null key)
-__global__ void k_dict_rows(const u32* __restrict__ ids, const u32* __restrict__ id_mask, const u64* __restrict__ tbl,
+// ids of the finished groups -> the first rows that held their strings (-1 for a null key)
+__global__ void k_dict_rows(const u32* __restrict__ ids, const u32* __restrict__ id_mask, const int* __restrict__ first_row,
                             i64 ngroups, int* __restrict__ rows)
 {
   for (i64 g = (i64)blockIdx.x * blockDim.x + threadIdx.x; g < ngroups; g += (i64)gridDim.x * blockDim.x)
-    rows[g] = (id_mask && !bit_valid(id_mask, g)) ? -1 : (int)(u32)tbl[ids[g]];
+    rows[g] = (id_mask && !bit_valid(id_mask, g)) ? -1 : first_row[ids[g]];
 }
 
 // ------------------------------------------------------------------------------ finalize
