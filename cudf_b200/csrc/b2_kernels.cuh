@@ -963,16 +963,11 @@ struct DDict {
 };
 
 // id of the string [p, p + len) of row `row`, inserting it when new; -1 after an overflow
-__device__ __forceinline__ i64 dict_find_insert(const DPlan& P, const DDict& D, const unsigned char* p, i64 len, i64 row, u64 h,
+// (`w` = the string's first DICT_INLINE bytes, zero padded)
+__device__ __forceinline__ i64 dict_find_insert(const DPlan& P, const DDict& D, const u64 (&w)[4], i64 len, i64 row, u64 h,
                                                 DCtrl* ctrl, int* s_new)
 {
   const u64 head = ((h >> 34) << 34) | ((u64)(len < 255 ? len : 255) << 26);
-  u64 w[4];  // my first DICT_INLINE bytes, zero padded
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const i64 left = len - 8 * i;
-    w[i] = left > 0 ? load_bytes8(p + 8 * i, (int)(left < 8 ? left : 8)) : 0ull;
-  }
   i64 idx = (i64)reduce64(h, (u64)D.cap);
   for (int probe = 0; probe < GMEM_PROBES; ++probe) {
     u64 k = *(volatile u64*)(D.cells + idx);
@@ -1023,16 +1018,27 @@ __global__ void __launch_bounds__(DICT_BLOCK) k_dict_encode(const __grid_constan
       b[j] = e[j] = 0;
       if (live[j]) { b[j] = str_offset(c, c.offset + row); e[j] = str_offset(c, c.offset + row + 1); }
     }
-    u64 h[DICT_ROWS];
-#pragma unroll
-    for (int j = 0; j < DICT_ROWS; ++j) h[j] = live[j] ? mix64(hash_bytes(c.data + b[j], e[j] - b[j], 0x243F6A8885A308D3ull)) : 0;
 #pragma unroll
     for (int j = 0; j < DICT_ROWS; ++j) {
       const i64 row = base + (i64)j * DICT_BLOCK + threadIdx.x;
       if (row >= P.nrows) continue;
       u32 id = 0;
       if (live[j]) {
-        const i64 s = dict_find_insert(P, D, c.data + b[j], e[j] - b[j], row, h[j], ctrl, &s_new);
+        // the first 32 bytes once, as four zero-padded words: hashed from registers (every lane takes the same four
+        // steps whatever its string's length) and compared against the pool entry; longer strings hash their rest
+        const unsigned char* p = c.data + b[j];
+        const i64 len = e[j] - b[j];
+        u64 w[4];
+        u64 h = 0x243F6A8885A308D3ull;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const i64 left = len - 8 * i;
+          w[i] = left > 0 ? load_bytes8(p + 8 * i, (int)(left < 8 ? left : 8)) : 0ull;
+          h = mix64(h ^ w[i]) + 0x9E3779B97F4A7C15ull;
+        }
+        if (len > DICT_INLINE) h = hash_bytes(p + DICT_INLINE, len - DICT_INLINE, h);
+        h = mix64(mix64(h ^ ((u64)len << 56)));
+        const i64 s = dict_find_insert(P, D, w, len, row, h, ctrl, &s_new);
         if (s >= 0) id = (u32)s;
       }
       ids[c.offset + row] = id;
