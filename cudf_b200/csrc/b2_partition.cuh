@@ -410,9 +410,11 @@ __global__ void __launch_bounds__(RPS_BLOCK, 2) k_rp_scatter(const __grid_consta
 {
   extern __shared__ __align__(16) unsigned char rp_stage[];
   const RpTile t = rp_tile_carve(rp_stage, D.fan);
-  // one value column without nulls is the common case: its values are loaded together with the keys and
-  // staged with them; other shapes stage the key and the row, and gather the value words at copy-out
-  const bool simple = P.nvals == 1 && D.dst.valid_word < 0;
+  // one value column is the common case: its values are loaded together with the keys and staged with them
+  // (a null value as a flag beside the staged digit); other shapes stage the key and the row, and gather the
+  // value words at copy-out
+  const bool one = P.nvals == 1;
+  const bool nullable = one && D.dst.valid_word >= 0;
   for (int i = threadIdx.x; i < D.fan; i += blockDim.x) t.hist[i] = 0;
   __syncthreads();
   const i64 ntiles = (P.nrows + RP_TILE - 1) / RP_TILE;
@@ -421,7 +423,7 @@ __global__ void __launch_bounds__(RPS_BLOCK, 2) k_rp_scatter(const __grid_consta
     const i64 tile0 = tile * RP_TILE;
     u64 kk[RP_ROWS], vv[RP_ROWS];
     u32 rank[RP_ROWS];
-    u32 act = 0;
+    u32 act = 0, vok = 0xFFFFFFFFu;
     // phase A: keys (and values), digits, ranks inside the tile
 #pragma unroll
     for (int g = 0; g < RP_ROWS / 4; ++g) {
@@ -432,10 +434,11 @@ __global__ void __launch_bounds__(RPS_BLOCK, 2) k_rp_scatter(const __grid_consta
       rp_keys4(P, row0, nv, k4, a4);
       if (hot_rows && nv > 0) a4 &= ~(__ldg(hot_rows + (row0 >> 5)) >> (row0 & 31));  // (row0 is a multiple of 4)
       act |= a4 << (4 * g);
+      if (nullable && nv > 0) vok = (vok & ~(0xFu << (4 * g))) | (valid_nibble(P.vals[0].mask, P.vals[0].offset + row0, nv) << (4 * g));
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         kk[4 * g + j] = k4[j];
-        vv[4 * g + j] = (simple && j < nv) ? load_value(P.vals[0], row0 + j) : 0ull;
+        vv[4 * g + j] = (one && j < nv) ? load_value(P.vals[0], row0 + j) : 0ull;
       }
     }
 #pragma unroll
@@ -455,19 +458,20 @@ __global__ void __launch_bounds__(RPS_BLOCK, 2) k_rp_scatter(const __grid_consta
       const u32 d = rank[j] >> 16;
       const u32 pos = t.off[d] + (rank[j] & 0xFFFFu);
       t.keys[pos] = kk[j];
-      t.dig[pos]  = (unsigned short)d;
-      if (simple) t.vals[pos] = vv[j];
+      t.dig[pos]  = (unsigned short)(d | (((vok >> j) & 1u) ? 0u : 0x8000u));  // (digits stay below 2^RP_MAX_BITS)
+      if (one) t.vals[pos] = vv[j];
       else t.src[pos] = (unsigned short)((j >> 2) * (RP_TILE / (RP_ROWS / 4)) + (int)threadIdx.x * 4 + (j & 3));
     }
     __syncthreads();
     // phase D: copy out in staging order
     const u32 ntile = t.off[D.fan];
     for (u32 pos = threadIdx.x; pos < ntile; pos += blockDim.x) {
-      const u32 d = t.dig[pos];
+      const u32 dg = t.dig[pos], d = dg & 0x7FFFu;
       const i64 at = (i64)t.base[d] + (i64)(pos - t.off[d]);
       D.dst.rec[at] = t.keys[pos];
-      if (simple) {
+      if (one) {
         D.dst.rec[D.dst.cap + at] = t.vals[pos];
+        if (nullable) D.dst.rec[(i64)D.dst.valid_word * D.dst.cap + at] = (u64)((dg >> 15) ^ 1u);
       } else {
         const i64 row = tile0 + t.src[pos];
         u64 vbits = 0;
@@ -536,20 +540,25 @@ __global__ void __launch_bounds__(RPS_BLOCK, 2) k_rp_scatter2(const DLevel2 L, c
   __syncthreads();
   const u32 ntiles = __ldg(L.tile_start + L.parts);
   const u32 dmask = (u32)D.fan - 1u;
-  const bool two_words = L.src.words == 2;  // key + one value: the value is loaded and staged with the key
+  // key + one value (+ its validity word): the value is loaded and staged with the key, the validity as a
+  // flag beside the staged digit; records of other shapes are copied word by word from their source position
+  const bool nullable = L.src.words == 3 && L.src.valid_word == 2;
+  const bool staged = L.src.words == 2 || nullable;
   for (u32 tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
     const int p = rp_partition_of_tile(L.tile_start, L.parts, tile);
     const i64 lo = (i64)L.src_start[p] + (i64)(tile - __ldg(L.tile_start + p)) * RP_TILE;
     const i64 hi = min((i64)L.src_end[p], lo + RP_TILE);
     u64 kk[RP_ROWS], vv[RP_ROWS];
     u32 rank[RP_ROWS];
+    u32 vok = 0xFFFFFFFFu;
 #pragma unroll
     for (int j = 0; j < RP_ROWS; ++j) {
       const i64 i = lo + (i64)j * RPS_BLOCK + threadIdx.x;
       kk[j] = 0; vv[j] = 0;
       if (i < hi) {
         kk[j] = __ldg(L.src.rec + i);
-        if (two_words) vv[j] = __ldg(L.src.rec + L.src.cap + i);
+        if (staged) vv[j] = __ldg(L.src.rec + L.src.cap + i);
+        if (nullable && !(__ldg(L.src.rec + 2 * L.src.cap + i) & 1ull)) vok &= ~(1u << j);
       }
     }
 #pragma unroll
@@ -569,18 +578,19 @@ __global__ void __launch_bounds__(RPS_BLOCK, 2) k_rp_scatter2(const DLevel2 L, c
       const u32 d = rank[j] >> 16;
       const u32 pos = t.off[d] + (rank[j] & 0xFFFFu);
       t.keys[pos] = kk[j];
-      t.dig[pos]  = (unsigned short)d;
-      if (two_words) t.vals[pos] = vv[j];
+      t.dig[pos]  = (unsigned short)(d | (((vok >> j) & 1u) ? 0u : 0x8000u));
+      if (staged) t.vals[pos] = vv[j];
       else t.src[pos] = (unsigned short)(j * RPS_BLOCK + (int)threadIdx.x);
     }
     __syncthreads();
     const u32 ntile = t.off[D.fan];
     for (u32 pos = threadIdx.x; pos < ntile; pos += blockDim.x) {
-      const u32 d = t.dig[pos];
+      const u32 dg = t.dig[pos], d = dg & 0x7FFFu;
       const i64 at = (i64)t.base[d] + (i64)(pos - t.off[d]);
       D.dst.rec[at] = t.keys[pos];
-      if (two_words) {
+      if (staged) {
         D.dst.rec[D.dst.cap + at] = t.vals[pos];
+        if (nullable) D.dst.rec[2 * D.dst.cap + at] = (u64)((dg >> 15) ^ 1u);
       } else {
         const i64 i = lo + t.src[pos];
         for (int w = 1; w < L.src.words; ++w) D.dst.rec[(i64)w * D.dst.cap + at] = __ldg(L.src.rec + (i64)w * L.src.cap + i);
