@@ -86,12 +86,16 @@ __device__ __forceinline__ bool fx_split(u64 bits, int B, int& q, u32 (&l)[4])
   l[3] = m2 >> rr;
   return true;
 }
+// (the limb arrays live in shared memory: 32-bit shared addresses and reductions that return nothing)
 __device__ __forceinline__ void fx_add(int* limbs, int ns, int slot, bool neg, int q, const u32 (&l)[4])
 {
-  int* p = limbs + (size_t)q * ns + slot;
+  const u32 base = (u32)__cvta_generic_to_shared(limbs) + 4u * (u32)(q * ns + slot);
 #pragma unroll
   for (int i = 0; i < 4; ++i)
-    if (l[i]) atomicAdd(p + (size_t)i * ns, neg ? -(int)l[i] : (int)l[i]);
+    if (l[i]) {
+      const int v = neg ? -(int)l[i] : (int)l[i];
+      asm volatile("red.shared.add.s32 [%0], %1;" ::"r"(base + 4u * (u32)(i * ns)), "r"(v) : "memory");
+    }
 }
 // empties the limbs of one slot and returns their value
 __device__ __noinline__ double fx_take(int* limbs, int ns, int slot, int B)
