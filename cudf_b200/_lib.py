@@ -99,6 +99,9 @@ PROTOTYPES = {
                                     C.c_void_p, C.POINTER(Allocator), C.POINTER(OwnedColumn), C.POINTER(C.c_int64)]),
     "b2_mask_to_bytes": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
     "b2_bytes_to_mask": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b2_finish_partial": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(ColumnView), C.POINTER(ColumnView),
+                                    C.POINTER(ColumnView), C.c_int32, C.c_void_p, C.POINTER(Allocator),
+                                    C.POINTER(OwnedColumn)]),
     "b2_column_free": (None, [C.POINTER(OwnedColumn), C.POINTER(Allocator), C.c_void_p]),
     "b2_groupby_aggregate_noalloc": (C.c_int, [C.c_void_p, C.POINTER(AggregationRequest), C.c_int32, C.c_void_p,
                                                C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),

@@ -2359,6 +2359,76 @@ b2_status b2_bytes_to_mask(const uint8_t* bytes, int64_t size, void* stream, uin
   });
 }
 
+b2_status b2_finish_partial(int32_t kind, int32_t ddof, int32_t result_type_id, const b2_column_view* sum,
+                            const b2_column_view* count, const b2_column_view* sum_sq, int32_t nullable,
+                            void* stream_, const b2_allocator* allocator, b2_owned_column* out)
+{
+  return guarded([&] {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!count || !out) B2_FAIL(B2_INVALID_ARGUMENT, "null argument");
+    if (width_of(count->type_id) == 0 || is_float_t(count->type_id) || is_decimal_t(count->type_id))
+      B2_FAIL(B2_DATA_TYPE_ERROR, "count must be an integer column");
+    DFinish F{};
+    switch (kind) {
+      case B2_AGG_COUNT_VALID: F.kind = FK_COUNT; result_type_id = B2_INT32; nullable = 0; break;
+      case B2_AGG_MEAN: F.kind = FK_MEAN; break;
+      case B2_AGG_M2: F.kind = FK_M2; result_type_id = B2_FLOAT64; nullable = 0; break;
+      case B2_AGG_VARIANCE: F.kind = FK_VAR; result_type_id = B2_FLOAT64; nullable = 1; break;
+      case B2_AGG_STD: F.kind = FK_STD; result_type_id = B2_FLOAT64; nullable = 1; break;
+      case -1: F.kind = FK_VALID_ONLY; nullable = 1; break;
+      default: B2_FAIL(B2_INVALID_ARGUMENT, "kind is not a finisher over partial columns");
+    }
+    const bool needs_sum = F.kind == FK_MEAN || F.kind == FK_M2 || F.kind == FK_VAR || F.kind == FK_STD;
+    const bool needs_ssq = F.kind == FK_M2 || F.kind == FK_VAR || F.kind == FK_STD;
+    auto view = [&](const b2_column_view* c, const char* what) {
+      if (!c) B2_FAIL(B2_INVALID_ARGUMENT, std::string(what) + " column is missing");
+      if (c->size != count->size) B2_FAIL(B2_INVALID_ARGUMENT, std::string(what) + " and count differ in size");
+      if (width_of(c->type_id) == 0 || is_decimal_t(c->type_id)) B2_FAIL(B2_DATA_TYPE_ERROR, std::string(what) + " must be a numeric, timestamp or duration column");
+      DValCol v{};
+      v.data = (const unsigned char*)c->data; v.mask = nullptr; v.offset = c->offset; v.vclass = vclass_of(c->type_id);
+      return v;
+    };
+    F.cnt = view(count, "count");
+    if (needs_sum) F.sum = view(sum, "sum");
+    if (needs_ssq) F.ssq = view(sum_sq, "sum of squares");
+    F.ddof = ddof;
+    F.int_mean = F.kind == FK_MEAN && !is_float_t(result_type_id);
+    if (F.kind == FK_MEAN && !is_float_t(result_type_id) && !is_duration_t(result_type_id))
+      B2_FAIL(B2_DATA_TYPE_ERROR, "a mean is FLOAT64 or, for durations, the duration type");
+    device_info();
+    const b2_allocator al = resolve(allocator);
+    const int64_t n = count->size;
+    std::memset(out, 0, sizeof(*out));
+    if (F.kind == FK_VALID_ONLY) {
+      out->type_id = B2_INT8;  // (no values: a carrier for the mask)
+      out->size = (int32_t)n;
+      out->null_mask_bytes = (size_t)std::max<int64_t>(1, (n + 511) / 512) * 64;
+      out->null_mask = (uint32_t*)out_alloc(al, out->null_mask_bytes, stream);
+    } else {
+      init_owned(*out, result_type_id, n, nullable != 0, al, stream);
+    }
+    F.rclass = vclass_of(result_type_id);
+    F.out = out->data;
+    F.out_mask = out->null_mask;
+    Scratch nulls(8, stream);
+    CUDA_TRY(cudaMemsetAsync(nulls.p, 0, 8, stream));
+    F.null_count = (u32*)nulls.p;
+    try {
+      if (n > 0) {
+        k_finish_partial<<<grid_for(n, 256, 8), 256, 0, stream>>>(F, n);
+        CUDA_TRY(cudaGetLastError());
+      }
+      u32 h = 0;
+      CUDA_TRY(cudaMemcpyAsync(&h, nulls.p, 4, cudaMemcpyDeviceToHost, stream));
+      CUDA_TRY(cudaStreamSynchronize(stream));
+      out->null_count = (int32_t)h;
+    } catch (...) {
+      b2_column_free(out, &al, stream);
+      throw;
+    }
+  });
+}
+
 void b2_column_free(b2_owned_column* c, const b2_allocator* allocator, void* stream)
 {
   if (!c) return;

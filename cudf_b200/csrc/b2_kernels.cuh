@@ -1249,6 +1249,72 @@ __global__ void __launch_bounds__(FIN_BLOCK) k_finalize(const __grid_constant__ 
   }
 }
 
+// ------------------------------------------------------------------------------ finishers over partial columns
+// Partial aggregates that travel as columns (string / float / wide keys between ranks and batches: Σx, n, Σx²
+// per group) are finished here: mean, M2, variance, standard deviation, counts as INT32 — the formulas of
+// write_group (cpp/src/groupby/hash/hash_compound_agg_finalizer.cu:93-186, common/m2_var_std.cu:57) — and the
+// validity of a result from n.
+struct DFinish {
+  int kind;        // FK_* below
+  int ddof;
+  int rclass;      // ValClass of the result
+  int int_mean;    // mean by integer division in the source type (durations)
+  DValCol sum, cnt, ssq;
+  void* out;
+  u32* out_mask;   // nullptr = not nullable
+  u32* null_count;
+};
+enum FinishKind : int { FK_COUNT = 0, FK_MEAN, FK_M2, FK_VAR, FK_STD, FK_VALID_ONLY };
+
+__device__ __forceinline__ double carried_as_double(const DValCol& c, u64 v)
+{
+  if (c.vclass == VC_F32 || c.vclass == VC_F64) return __longlong_as_double((i64)v);
+  if (c.vclass == VC_U64) return (double)v;
+  return (double)(i64)v;
+}
+
+__global__ void k_finish_partial(const DFinish F, i64 n)
+{
+  const u32 lane = threadIdx.x & 31u;
+  const i64 nround = (n + 31) / 32 * 32;
+  for (i64 g = (i64)blockIdx.x * blockDim.x + threadIdx.x; g < nround; g += (i64)gridDim.x * blockDim.x) {
+    bool valid = false;
+    if (g < n) {
+      const i64 c = (i64)load_value(F.cnt, g);
+      valid = c > 0;
+      switch (F.kind) {
+        case FK_COUNT: store_int(F.out, g, F.rclass, (u64)c); valid = true; break;
+        case FK_MEAN: {
+          const u64 sv = load_value(F.sum, g);
+          if (F.int_mean) store_int(F.out, g, F.rclass, (u64)((i64)sv / (c > 0 ? c : 1)));
+          else store_flt(F.out, g, F.rclass, carried_as_double(F.sum, sv) / (double)(c > 0 ? c : 1));
+          break;
+        }
+        case FK_M2: case FK_VAR: case FK_STD: {
+          const double s = carried_as_double(F.sum, load_value(F.sum, g)), ss = carried_as_double(F.ssq, load_value(F.ssq, g));
+          const double m2 = c > 0 ? ss - s * s / (double)c : 0.0;
+          if (F.kind == FK_M2) { store_flt(F.out, g, F.rclass, m2); valid = true; break; }
+          const i64 df = c - F.ddof;
+          valid = c > 0 && df > 0;
+          const double var = valid ? m2 / (double)df : 0.0;
+          store_flt(F.out, g, F.rclass, F.kind == FK_VAR ? var : sqrt(var));
+          break;
+        }
+        default: break;  // FK_VALID_ONLY: the mask alone
+      }
+    }
+    if (F.out_mask) {
+      const u32 word = __ballot_sync(0xFFFFFFFFu, valid);
+      if (lane == 0) {
+        F.out_mask[g >> 5] = word;
+        const i64 here = n - g < 32 ? n - g : 32;  // rows of this word
+        const u32 nulls = (u32)here - (u32)__popc(word);
+        if (nulls && F.null_count) atomicAdd(F.null_count, nulls);
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------ key gather (row keys)
 struct DGather {
   const unsigned char* src; const u32* src_mask; i64 src_offset; int width;

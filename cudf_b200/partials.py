@@ -67,6 +67,31 @@ def _from_typed(values: torch.Tensor, type_id: TypeId, valid: Optional[torch.Ten
     return Column(type_id, values.numel(), raw, mask, 0, nulls, None, TypeId.INT32, scale)
 
 
+def _finish(kind, ddof: int, result_type_id: TypeId, sums: Optional[Column], counts: Column,
+            sum_sq: Optional[Column], nullable: bool) -> Column:
+    """One finished result column from partial columns: the library's finishers (b2_finish_partial) — mean, M2,
+    variance, standard deviation, counts as INT32, or (``kind`` None) only the validity a result takes from n."""
+    import ctypes as C
+    from . import _lib
+    from .column import allocator_for
+    from .groupby import _check
+    lib = _lib.load()
+    keep: list = []
+    device = counts.data.device if counts.data is not None else torch.device("cuda")
+    alloc = allocator_for(device)
+    views = [(_lib.ColumnView * 1)(c.c_view(keep)) if c is not None else None for c in (sums, counts, sum_sq)]
+    out = _lib.OwnedColumn()
+    stream = torch.cuda.current_stream(device).cuda_stream
+    _check(lib.b2_finish_partial(-1 if kind is None else int(kind), int(ddof), int(result_type_id), views[0], views[1],
+                                 views[2], 1 if nullable else 0, C.c_void_p(stream), C.byref(alloc.struct), C.byref(out)))
+    data = alloc.adopt(out.data)
+    mask = alloc.adopt(out.null_mask)
+    col = Column(out.type_id, out.size, data, mask, 0, out.null_count, None, TypeId.INT32, 0)
+    out.data = None
+    out.null_mask = None
+    return col
+
+
 def _concat(a: Column, b: Column) -> Column:
     """Rows of ``a`` followed by rows of ``b`` (same type)."""
     from .partition import bytes_to_mask
@@ -207,7 +232,6 @@ class PartialTable:
     def finalize(self, detect_nulls: bool = False) -> Tuple[List[Column], List[Column]]:
         """(key columns, one result column per spec).  ``detect_nulls``: also treat a source as having nulls
         when a group holds no valid value of it (partial rows that came from other ranks)."""
-        from .partition import bytes_to_mask
         n = self.size
         results = []
         for sid, kind, ddof in self.specs:
@@ -217,37 +241,22 @@ class PartialTable:
             has_nulls = self.src_nulls.get(sid, False)
             if detect_nulls and not has_nulls and n:
                 has_nulls = bool((cnt == 0).any())
-            some = (cnt > 0).to(torch.uint8)
+            count_col = self.cols[(sid, Kind.COUNT_VALID)]
             if kind in (Kind.COUNT_VALID, Kind.COUNT_ALL):
-                src = cnt if kind == Kind.COUNT_VALID else _typed(self.cols[(sid, Kind.COUNT_ALL)])
-                col = _from_typed(src.to(torch.int32), TypeId.INT32, None)
+                src = count_col if kind == Kind.COUNT_VALID else self.cols[(sid, Kind.COUNT_ALL)]
+                col = _finish(Kind.COUNT_VALID, 0, TypeId.INT32, None, src, None, False)
             elif kind in (Kind.SUM, Kind.PRODUCT, Kind.MIN, Kind.MAX, Kind.SUM_OF_SQUARES):
                 p = self.cols[(sid, kind)]
                 mask, nulls = None, 0
                 if has_nulls:  # nullable iff the source has nulls (cpp/src/groupby/hash/output_utils.cu:61-68)
-                    mask, nulls = bytes_to_mask(some)
+                    carrier = _finish(None, 0, TypeId.INT8, None, count_col, None, True)
+                    mask, nulls = carrier.mask, carrier.null_count
                 col = Column(p.type_id, p.size, p.data, mask, p.offset, nulls, None, TypeId.INT32, p.scale)
             elif kind == Kind.MEAN:
-                s = _typed(self.cols[(sid, Kind.SUM)])
-                safe = torch.clamp(cnt, min=1)
-                if is_duration(st):  # integer division in the source type
-                    val = torch.div(s.to(torch.int64), safe, rounding_mode="trunc").to(s.dtype)
-                else:
-                    val = s.to(torch.float64) / safe.to(torch.float64)
-                col = _from_typed(val, rt, some if has_nulls else None)
+                col = _finish(Kind.MEAN, 0, rt, self.cols[(sid, Kind.SUM)], count_col, None, has_nulls)
             else:  # M2, VARIANCE, STD
-                s = _typed(self.cols[(sid, Kind.SUM)]).to(torch.float64)
-                ss = _typed(self.cols[(sid, Kind.SUM_OF_SQUARES)]).to(torch.float64)
-                nf = torch.clamp(cnt, min=1).to(torch.float64)
-                m2 = torch.where(cnt > 0, ss - s * s / nf, torch.zeros_like(ss))
-                if kind == Kind.M2:
-                    col = _from_typed(m2, TypeId.FLOAT64, None)
-                else:
-                    df = cnt - int(ddof)
-                    ok = (cnt > 0) & (df > 0)
-                    var = torch.where(ok, m2 / torch.clamp(df, min=1).to(torch.float64), torch.zeros_like(m2))
-                    col = _from_typed(var if kind == Kind.VARIANCE else torch.sqrt(var), TypeId.FLOAT64,
-                                      ok.to(torch.uint8))
+                col = _finish(kind, int(ddof), TypeId.FLOAT64, self.cols[(sid, Kind.SUM)], count_col,
+                              self.cols[(sid, Kind.SUM_OF_SQUARES)], True)
             assert col.size == n
             results.append(col)
         return list(self.keys), results

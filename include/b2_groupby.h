@@ -293,6 +293,19 @@ b2_status b2_mask_to_bytes(const uint32_t* mask, int64_t offset, int64_t size, v
 b2_status b2_bytes_to_mask(const uint8_t* bytes, int64_t size, void* stream, uint32_t* mask,
                            int32_t* null_count_device);
 
+/* Finishes partial aggregates that travel as columns (what string / float / wide keys exchange between ranks
+ * and batches: Σx, n and Σx² per group): the finalizers of the hash path over such columns
+ * (cpp/src/groupby/hash/hash_compound_agg_finalizer.cu:93-186, cpp/src/groupby/common/m2_var_std.cu:57).
+ * `kind` is B2_AGG_COUNT_VALID (n as INT32), B2_AGG_MEAN (Σx / n as `result_type_id`: FLOAT64, or a duration type
+ * by integer division), B2_AGG_M2, B2_AGG_VARIANCE, B2_AGG_STD (FLOAT64), or -1: no values, only the validity of
+ * a result from n.  `sum` / `sum_sq` are fixed-width numeric columns (NULL where the kind does not need them),
+ * `count` is an integer column (INT32 from one aggregate, INT64 once counts were summed).  `nullable` != 0 gives the result a validity mask (valid where n > 0; variance and standard
+ * deviation: where n - ddof > 0) and its null count; variance and standard deviation always carry one.
+ * Synchronises `stream` once. */
+b2_status b2_finish_partial(int32_t kind, int32_t ddof, int32_t result_type_id, const b2_column_view* sum,
+                            const b2_column_view* count, const b2_column_view* sum_sq, int32_t nullable,
+                            void* stream, const b2_allocator* allocator, b2_owned_column* out);
+
 /* Releases the buffers of one owned column obtained from b2_hash_partition. */
 void b2_column_free(b2_owned_column* col, const b2_allocator* allocator, void* stream);
 

@@ -87,6 +87,43 @@ def test_emulated_ranks_partials_shuffle_equals_one_shot(config, ranks):
     assert got[0][0].size == exp[0][0].size
 
 
+def test_finishers_over_partial_columns():
+    """b2_finish_partial against the same formulas in numpy: mean (FLOAT64, and a duration by integer division),
+    M2, variance and standard deviation with their validity (n - ddof > 0), counts as INT32, the validity alone."""
+    import cudf_b200 as cb
+    from cudf_b200.partials import _finish
+    rng = np.random.default_rng(12)
+    n = 5000
+    cnt = rng.integers(0, 6, n).astype(np.int64)
+    x = [rng.standard_normal(c) * 10 for c in cnt]
+    s = np.array([v.sum() for v in x])
+    ss = np.array([(v * v).sum() for v in x])
+    dev = lambda a, t=None: cb.Column.from_host(HostColumn.from_numpy(a, type_id=t))
+    c_col, s_col, ss_col = dev(cnt), dev(s), dev(ss)
+    mean = _finish(Kind.MEAN, 0, TypeId.FLOAT64, s_col, c_col, None, True).to_host()
+    ok = cnt > 0
+    assert np.array_equal(mean.valid(), ok) and mean.null_count == int((~ok).sum())
+    assert np.allclose(mean.values()[ok], s[ok] / cnt[ok], rtol=1e-15, atol=0)
+    for kind, ddof in ((Kind.M2, 0), (Kind.VARIANCE, 1), (Kind.VARIANCE, 0), (Kind.STD, 2)):
+        got = _finish(kind, ddof, TypeId.FLOAT64, s_col, c_col, ss_col, True).to_host()
+        m2 = np.where(ok, ss - s * s / np.maximum(cnt, 1), 0.0)
+        if kind == Kind.M2:
+            assert got.mask is None and np.allclose(got.values(), m2, rtol=1e-14, atol=1e-12)
+            continue
+        good = ok & (cnt - ddof > 0)
+        var = m2[good] / (cnt[good] - ddof)
+        assert np.array_equal(got.valid(), good) and got.null_count == int((~good).sum())
+        assert np.allclose(got.values()[good], var if kind == Kind.VARIANCE else np.sqrt(var), rtol=1e-14, atol=1e-12)
+    counts32 = _finish(Kind.COUNT_VALID, 0, TypeId.INT32, None, dev(cnt.astype(np.int32)), None, False).to_host()
+    assert counts32.type_id == TypeId.INT32 and np.array_equal(counts32.values(), cnt.astype(np.int32))
+    carrier = _finish(None, 0, TypeId.INT8, None, c_col, None, True)
+    assert carrier.null_count == int((~ok).sum())
+    total = rng.integers(-10**6, 10**6, n).astype(np.int64)
+    dur = _finish(Kind.MEAN, 0, TypeId.DURATION_SECONDS, dev(total, TypeId.DURATION_SECONDS), c_col, None, False).to_host()
+    q = np.trunc(total[ok] / cnt[ok]).astype(np.int64)   # C++ integer division truncates towards zero
+    assert dur.type_id == TypeId.DURATION_SECONDS and np.array_equal(dur.values()[ok], q)
+
+
 def test_pack_into_the_largest_number_of_destinations():
     """b2_state_pack accepts up to 4096 destinations; the scatter kernel then needs 64 KB of dynamic shared
     memory (beyond the 48 KB default).  All records merged back into one state give the one-shot result."""

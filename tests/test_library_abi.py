@@ -55,6 +55,16 @@ def test_argument_errors_need_no_gpu():
     v = (_lib.ColumnView * 1)()
     v[0].type_id, v[0].size = 3, 0
     assert lib.b2_groupby_create(v, 1, 7, None, ctypes.byref(out)) == _lib.Status.INVALID_ARGUMENT
+    # finishers over partial columns: what is wrong with the arguments is said before anything touches a GPU
+    oc = _lib.OwnedColumn()
+    assert lib.b2_finish_partial(10, 1, 10, None, None, None, 0, None, None, ctypes.byref(oc)) == _lib.Status.INVALID_ARGUMENT
+    cnt = (_lib.ColumnView * 1)()
+    cnt[0].type_id, cnt[0].size = 4, 5        # INT64 counts
+    assert lib.b2_finish_partial(99, 1, 10, None, cnt, None, 0, None, None, ctypes.byref(oc)) == _lib.Status.INVALID_ARGUMENT
+    assert lib.b2_finish_partial(10, 1, 10, None, cnt, None, 0, None, None, ctypes.byref(oc)) == _lib.Status.INVALID_ARGUMENT   # MEAN
+    assert b"sum column is missing" in lib.b2_last_error()
+    cnt[0].type_id = 10                       # FLOAT64 is not a count
+    assert lib.b2_finish_partial(5, 1, 3, None, cnt, None, 0, None, None, ctypes.byref(oc)) == _lib.Status.DATA_TYPE_ERROR      # COUNT_VALID
 
 
 def test_missing_library_fails_loudly(tmp_path, monkeypatch):
