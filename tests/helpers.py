@@ -18,8 +18,13 @@ RTOL_F32 = 1e-5
 # A float result is held to the STRICT relative tolerance |got - exp| <= rtol * |exp| whenever
 # |exp| >= STRICT_FROM * (error scale of its group: Σ|x| for sums and means, Σx²/(n - ddof) for
 # variances; for a standard deviation the ratio of the variances decides); only results that
-# cancellation drove below that are compared relative to the scale.
+# cancellation drove below that are compared relative to the scale.  The threshold is the point
+# where the strict tolerance, rtol * |exp|, is 9 unit roundoffs of the SOURCE type times the scale:
+# 1e-3 for fp64 sources (1e-15 * scale against 2^-53), 5.4e-2 for fp32 sources (5.4e-7 * scale
+# against 2^-24).  Below it a sum accumulated in the source's own precision, in any order (the
+# reference adds fp32 values with fp32 atomics), cannot be told from a wrong one by the result alone.
 STRICT_FROM = 1e-3
+STRICT_FROM_F32 = STRICT_FROM * (2.0 ** -24 / RTOL_F32) / (2.0 ** -53 / RTOL_F64)
 # one record per compared float column: what, values compared, values held to the strict tolerance,
 # the largest strict relative error among those, values that only pass through the scaled bound, the
 # largest error relative to the scale among them (printed by the parity tests; also appended to
@@ -102,7 +107,8 @@ def take(col: HostColumn, order: np.ndarray) -> list:
 
 
 def assert_column_equal(got: HostColumn, exp: HostColumn, order_got, order_exp, rtol: float, what: str,
-                        check_nullable: bool = False, scale=None, strict_power: int = 1):
+                        check_nullable: bool = False, scale=None, strict_power: int = 1,
+                        strict_from: float = STRICT_FROM):
     assert TypeId(got.type_id) == TypeId(exp.type_id), f"{what}: type {got.type_id!r} != {exp.type_id!r}"
     assert got.size == exp.size, f"{what}: size {got.size} != {exp.size}"
     assert getattr(got, "scale", 0) == getattr(exp, "scale", 0), f"{what}: decimal scale differs"
@@ -133,7 +139,7 @@ def assert_column_equal(got: HostColumn, exp: HostColumn, order_got, order_exp, 
         else:
             sc = np.asarray(scale, dtype=np.float64)[order_exp][ve][fin]
             # (a standard deviation is the root of a difference: its conditioning is that of the variance)
-            strict = mag ** strict_power >= STRICT_FROM * sc ** strict_power
+            strict = mag ** strict_power >= strict_from * sc ** strict_power
         # strict: relative to the result itself; the rest: relative to the group's error scale
         tol = rtol * np.where(strict, mag, np.maximum(mag, sc)) + 1e-300
         bad = np.flatnonzero(err > tol)
@@ -177,6 +183,10 @@ def assert_keys_equal(got: List[HostColumn], exp: List[HostColumn], order_got, o
 
 def rtol_for(source_type: int) -> float:
     return RTOL_F32 if TypeId(source_type) == TypeId.FLOAT32 else RTOL_F64
+
+
+def strict_from_for(source_type: int) -> float:
+    return STRICT_FROM_F32 if TypeId(source_type) == TypeId.FLOAT32 else STRICT_FROM
 
 
 def golden_instances(case: dict):
@@ -279,7 +289,7 @@ def _scale_for(kind, ddof, sa, ss, n):
 def assert_same_result(got, exp, requests, check_nullable=True, scales=None):
     """Compares two (keys, results) pairs after sorting both by key: keys, counts, integer results
     bit-exact; float results within the north-star tolerance of their SOURCE type (1e-12 for
-    fp64 sources, 1e-5 for fp32), relative to max(|result|, error scale of the group) when
+    fp64 sources, 1e-5 for fp32), relative to max(|result|, error scale of the group) below the strict threshold when
     ``scales`` (from result_scales, in ``exp``'s group order) is given."""
     gk, gr = got
     ek, er = exp
@@ -293,4 +303,5 @@ def assert_same_result(got, exp, requests, check_nullable=True, scales=None):
             if scales is not None and is_floating(er[q][a].type_id):
                 scale = _scale_for(kind, ddof, *scales[q])
             assert_column_equal(gr[q][a], er[q][a], og, oe, rtol_for(vals.type_id), f"request {q} agg {aggs[a]}",
-                                check_nullable=check_nullable, scale=scale, strict_power=2 if Kind(kind) == Kind.STD else 1)
+                                check_nullable=check_nullable, scale=scale, strict_power=2 if Kind(kind) == Kind.STD else 1,
+                                strict_from=strict_from_for(vals.type_id))
