@@ -99,11 +99,13 @@ struct DPlan {
 
 enum PlanFlags : int {
   PF_VEC_KEYS = 1,  // every key column may be read 4 rows at a time with one 16-byte load
-  PF_VEC_VAL0 = 2,  // value column 0 likewise (compact FLOAT32 layout)
+  PF_VEC_VAL0 = 2,  // value column 0 likewise (the compact "Σ and n of one float column" layouts)
   PF_FAST     = 4,  // every key column is 4 or 8 bytes wide and every mask / filter offset is a
                     // multiple of 4, so the validity bits of 4 consecutive rows never straddle a mask word
-  PF_BULK     = 8   // value column 0's validity can be tiled with 16-byte-aligned bulk copies: mask
+  PF_BULK     = 8,  // value column 0's validity can be tiled with 16-byte-aligned bulk copies: mask
                     // pointer 16-byte aligned and offset a multiple of 128 bits (or no mask at all)
+  PF_F64MEAN  = 16  // the cells are Σ and n of one FLOAT64 column: the key-box sampler also records the
+                    // largest exponent among the sampled values (the window of the fixed-point limbs)
 };
 
 // Dense key mapping of one aggregate pass, derived on the device by sample_dense_box: when the keys
@@ -115,7 +117,7 @@ struct DDense {
   u32 total;               // slots of one copy = product of ranges
   u32 copies;              // replicas of the table in shared memory (warp w uses copy w % copies):
                            // few groups mean many rows per slot, and same-address atomics serialise
-  u32 pad;
+  u32 vexp;                // PF_F64MEAN: 1 + the largest biased exponent among the sampled values, 0 = none seen
   i64 min[MAX_KEYS];
   u64 range[MAX_KEYS];     // includes one extra value for "null" on nullable INCLUDE columns
   u32 mult[MAX_KEYS];

@@ -292,6 +292,7 @@ struct Schema {  // everything that is fixed by (key types, requests): cells and
   std::vector<int> req_nouts;
   std::vector<int> req_val;  // request → value column slot
   bool f32mean = false;      // cells == {Σ of a FLOAT32 column, n of it}: compact shared-memory layout
+  bool f64mean = false;      // cells == {Σ of a FLOAT64 column, n of it}: the lean kernel keeps Σ as fixed-point limbs
   bool fixed = false;        // cells ⊆ {Σx, n, Σx²} of ONE float column: the partitioned path folds hot keys and keeps fixed-point cells
   bool has_arg = false;      // some cell holds a row index (ARGMIN / ARGMAX, MIN / MAX of strings): such cells
                              // live in the global table of ONE aggregate call only (no shared-memory copies,
@@ -504,6 +505,8 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
   if ((int)sc.outs.size() > MAX_OUTS) B2_FAIL(B2_UNSUPPORTED, "more than 64 aggregations in one aggregate call");
   sc.f32mean = sc.key_mode == KM_PACKED && sc.ncells == 2 && sc.cells[0].op == OP_SUM_F && sc.cells[1].op == OP_CNT_V &&
                sc.cells[0].col == sc.cells[1].col && sc.val_types[sc.cells[0].col] == B2_FLOAT32;
+  sc.f64mean = sc.key_mode == KM_PACKED && sc.ncells == 2 && sc.cells[0].op == OP_SUM_F && sc.cells[1].op == OP_CNT_V &&
+               sc.cells[0].col == sc.cells[1].col && sc.val_types[sc.cells[0].col] == B2_FLOAT64;
   if (sc.key_mode == KM_PACKED && !sc.f32mean && sc.nvals == 1 && is_float_t(sc.val_types[0]) && sc.ncells >= 1) {
     sc.fixed = true;
     for (int c = 0; c < sc.ncells; ++c) {
@@ -588,6 +591,8 @@ void bind_plan_inputs(DPlan& P, const Schema& sc, const b2_groupby& gb, const b2
     if (ok) P.flags |= PF_VEC_KEYS;
   }
   if (sc.f32mean && aligned(P.vals[sc.cells[0].col].data, P.vals[sc.cells[0].col].offset, 4)) P.flags |= PF_VEC_VAL0;
+  if (sc.f64mean && aligned(P.vals[sc.cells[0].col].data, P.vals[sc.cells[0].col].offset, 8)) P.flags |= PF_VEC_VAL0;
+  if (sc.f64mean) P.flags |= PF_F64MEAN;
   P.nfilters = (int)gb.filters.size();
   bool fast = true;
   for (int f = 0; f < P.nfilters; ++f) {
@@ -599,7 +604,7 @@ void bind_plan_inputs(DPlan& P, const Schema& sc, const b2_groupby& gb, const b2
     fast = fast && (P.keys[k].width == 4 || P.keys[k].width == 8) && (!P.keys[k].mask || P.keys[k].offset % 4 == 0);
   for (int v = 0; v < sc.nvals; ++v) fast = fast && (!P.vals[v].mask || P.vals[v].offset % 4 == 0);
   if (fast) P.flags |= PF_FAST;
-  if (sc.f32mean) {
+  if (sc.f32mean || sc.f64mean) {
     const DValCol& vc = P.vals[sc.cells[0].col];
     if (!vc.mask || ((uintptr_t)vc.mask % 16 == 0 && vc.offset % 128 == 0)) P.flags |= PF_BULK;
   }
@@ -654,7 +659,7 @@ void free_table(b2_groupby_state& st, cudaStream_t stream)
 }
 
 void alloc_table(b2_groupby_state& st, int64_t cap, double max_load, cudaStream_t stream, bool dense_region = false,
-                 u32 cap_dense = 0)
+                 u32 cap_dense = 0, u32 cap_lean = 0)
 {
   free_table(st, stream);
   if (cap > 0x7FFFFFF0ll) B2_FAIL(B2_UNSUPPORTED, "hash table would need more than 2^31 slots");
@@ -677,7 +682,7 @@ void alloc_table(b2_groupby_state& st, int64_t cap, double max_load, cudaStream_
   // the key box of the fused pass is sampled here too (needs a dense region, packed keys and enough rows)
   if (st.dense_slots == 0 || st.plan.nrows < SAMPLE_ROWS) cap_dense = 0;
   k_table_init<<<grid_for((cap + 1 + st.dense_slots) * st.plan.stride / 2 + 1, TABLE_INIT_BLOCK, 16), TABLE_INIT_BLOCK, 0, stream>>>(
-    st.table, cap + 1 + st.dense_slots, st.plan, st.ctrl, h.claim_limit, h.dense_slots, cap_dense);
+    st.table, cap + 1 + st.dense_slots, st.plan, st.ctrl, h.claim_limit, h.dense_slots, cap_dense, cap_lean);
   CUDA_TRY(cudaGetLastError());
   g_stats.kernel_launches++;
   g_stats.table_capacity = cap;
@@ -720,10 +725,10 @@ void launch_aggregate(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, int S,
   g_stats.kernel_launches++;
 }
 
-template <int NK, bool K8, bool STAGED, bool KEY_MASKS>
+template <int NK, bool K8, bool STAGED, bool KEY_MASKS, bool V8>
 void launch_lean(const DPlan& P, u64* tbl, int64_t cap, DCtrl* ctrl, size_t smem, cudaStream_t stream, u32 region_slots)
 {
-  auto kern = k_aggregate_lean<NK, K8, STAGED, KEY_MASKS>;
+  auto kern = k_aggregate_lean<NK, K8, STAGED, KEY_MASKS, V8>;
   static thread_local size_t configured[64] = {};
   allow_shared(kern, smem, configured);
   kern<<<device_info().sms, 1024, smem, stream>>>(P, tbl, cap, ctrl, region_slots);
@@ -753,6 +758,7 @@ struct SharedPlan {
   int S = 0, fill_limit = 0;  // hashed mode
   size_t smem = 0;            // dynamic shared memory of the kernels
   u32 cap_dense = 0;          // slots a dense key box may use (0 = no box)
+  u32 cap_lean = 0;           // slots of the lean kernel's table when that is fewer than cap_dense (0 = the same)
   bool lean = false;          // k_aggregate_lean runs in front of k_aggregate
   bool staged = false;        // ... with the cp.async.bulk tile ring
   size_t lean_smem = 0;       // dynamic shared memory of k_aggregate_lean
@@ -775,33 +781,39 @@ SharedPlan plan_shared(const b2_groupby_state& st, const b2_groupby& gb)
   if (sc.key_mode != KM_PACKED || gb.table_variant == 3) return sp;
   // dense mode: accumulators + one occupancy bit per slot
   sp.cap_dense = (u32)std::min<int64_t>(DENSE_REGION_SLOTS, ((int64_t)budget - 64) * 8 / ((int64_t)cell_bytes * 8 + 1));
-  // the lean kernel: Σ and n of one FLOAT32 column, 1..3 key columns of 4 or 8 bytes, aligned vector loads
+  // the lean kernel: Σ and n of one FLOAT32 / FLOAT64 column, 1..3 key columns of 4 or 8 bytes, aligned vector loads
   const int need = PF_FAST | PF_VEC_KEYS | PF_VEC_VAL0;
-  if (sc.f32mean && sc.nkeys <= 3 && (P.flags & need) == need && P.nrows >= SAMPLE_ROWS && P.nrows < 0xFFFF0000ll) {
+  if ((sc.f32mean || sc.f64mean) && sc.nkeys <= 3 && (P.flags & need) == need && P.nrows >= SAMPLE_ROWS && P.nrows < 0xFFFF0000ll) {
     sp.lean = true;
+    // bits of one slot: fp32 sum + count + occupancy bit, or the limbs of a FLOAT64 sum + count + occupancy bit
+    const int64_t slot_bits = sc.f64mean ? (4 * FX_LIMBS + 4) * 8 + 1 : 65;
+    const u32 cap_generic = sp.cap_dense;
     // Register tiles arrive through L1, which is what the shared-memory carve-out leaves of the SM's
     // 256 KB: with the whole opt-in taken, ~24 KB of L1 cannot hold the lines of the loads in flight
     // (32 warps x 3 vector loads x 2 tiles) and the row loop slows down by a third.  So this variant
     // takes a table of at most LEAN_DIRECT_SMEM and leaves the rest to L1; wider key boxes go to the
     // generic kernel.
     sp.lean_smem = (size_t)std::min<int64_t>(budget, gb.shared_table_bytes > 0 ? budget : LEAN_DIRECT_SMEM);
-    sp.cap_dense = (u32)std::min<int64_t>(DENSE_REGION_SLOTS, ((int64_t)sp.lean_smem - 256) * 8 / 65);
+    sp.cap_dense = (u32)std::min<int64_t>(DENSE_REGION_SLOTS, ((int64_t)sp.lean_smem - 256) * 8 / slot_bits);
     // the staged variant needs room for its tile ring, flat 16-byte-aligned tiles, and validity that is
     // either absent or the value column's own mask (also when used as the row filter)
     const DValCol& vc = P.vals[sc.cells[0].col];
     bool bulk_ok = (P.flags & PF_BULK) != 0;
     for (int k = 0; k < sc.nkeys; ++k) bulk_ok = bulk_ok && P.keys[k].mask == nullptr;
     bulk_ok = bulk_ok && (P.nfilters == 0 || (P.nfilters == 1 && P.filters[0] == vc.mask && P.filter_offsets[0] == vc.offset));
-    int64_t row_bytes = 4;
+    int64_t row_bytes = sc.f64mean ? 8 : 4;
     for (int k = 0; k < sc.nkeys; ++k) row_bytes += sc.key_width[k];
     const int64_t ring = (int64_t)LEAN_STAGES * ((int64_t)LEAN_STAGED_CONSUMERS * LEAN_ROWS * row_bytes + LEAN_MASK_BYTES);
-    const int64_t staged_cap = ((int64_t)budget - ring - 512) * 8 / 65;
+    const int64_t staged_cap = ((int64_t)budget - ring - 512) * 8 / slot_bits;
     const bool want_staged = gb.table_variant == 5 || (gb.table_variant == 0 && LEAN_STAGED_BY_DEFAULT);
     if (want_staged && bulk_ok && staged_cap >= 1024) {
       sp.staged = true;
       sp.lean_smem = (size_t)budget;  // bulk copies land in shared memory directly: L1 is not in their way
       sp.cap_dense = (u32)std::min<int64_t>(DENSE_REGION_SLOTS, staged_cap);
     }
+    // FLOAT64: the generic kernel's 16-byte slots hold a wider key box than the limbs do; such a box is left
+    // to it (the lean kernel declines).  FLOAT32: both tables have 8-byte slots, the lean capacity serves both.
+    if (sc.f64mean && cap_generic > sp.cap_dense) { sp.cap_lean = sp.cap_dense; sp.cap_dense = cap_generic; }
   }
   return sp;
 }
@@ -825,18 +837,20 @@ bool run_aggregate(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t stre
     bool key_masks = false;
     for (int k = 0; k < sc.nkeys; ++k) key_masks = key_masks || P.keys[k].mask != nullptr;
     // (the staged variant is only planned when no key column carries a mask)
-#define B2_LEAN(N, W)                                                                                              \
+#define B2_LEAN_V(N, W, V)                                                                                         \
     do {                                                                                                           \
-      if (sp.staged) launch_lean<N, W, true, false>(P, st.table, st.cap, st.ctrl, sp.lean_smem, stream, (u32)st.dense_slots);  \
-      else if (key_masks) launch_lean<N, W, false, true>(P, st.table, st.cap, st.ctrl, sp.lean_smem, stream, (u32)st.dense_slots); \
-      else launch_lean<N, W, false, false>(P, st.table, st.cap, st.ctrl, sp.lean_smem, stream, (u32)st.dense_slots);    \
+      if (sp.staged) launch_lean<N, W, true, false, V>(P, st.table, st.cap, st.ctrl, sp.lean_smem, stream, (u32)st.dense_slots);  \
+      else if (key_masks) launch_lean<N, W, false, true, V>(P, st.table, st.cap, st.ctrl, sp.lean_smem, stream, (u32)st.dense_slots); \
+      else launch_lean<N, W, false, false, V>(P, st.table, st.cap, st.ctrl, sp.lean_smem, stream, (u32)st.dense_slots);    \
     } while (0)
+#define B2_LEAN(N, W) do { if (sc.f64mean) B2_LEAN_V(N, W, true); else B2_LEAN_V(N, W, false); } while (0)
     switch (sc.nkeys) {
       case 1: if (k8) B2_LEAN(1, true); else B2_LEAN(1, false); break;
       case 2: if (k8) B2_LEAN(2, true); else B2_LEAN(2, false); break;
       default: if (k8) B2_LEAN(3, true); else B2_LEAN(3, false); break;
     }
 #undef B2_LEAN
+#undef B2_LEAN_V
     cudaEventRecord(ev.b, stream);
     st.ctrl_fresh = false;
     return true;
@@ -1163,7 +1177,8 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
       cap = st.deferred_cap;
       lean_ran = st.deferred_lean;
     } else {
-      alloc_table(st, cap, cap >= full ? 1.0 : MAX_LOAD, stream, gb.table_variant != 1 && gb.table_variant != 3, sp.cap_dense);
+      alloc_table(st, cap, cap >= full ? 1.0 : MAX_LOAD, stream, gb.table_variant != 1 && gb.table_variant != 3, sp.cap_dense,
+                  sp.cap_lean);
       trace.mark("table allocation + init");
       lean_ran = run_aggregate(st, gb, stream, sp, true);
       const int64_t bound = std::min<int64_t>(n, (int64_t)st.host_ctrl.claim_limit + 1 + st.dense_slots);
@@ -1182,6 +1197,11 @@ void aggregate_fresh(b2_groupby_state& st, const b2_groupby& gb, cudaStream_t st
       float ms = 0.f;
       if (cudaEventElapsedTime(&ms, kernel_events().a, kernel_events().b) == cudaSuccess) g_stats.aggregate_kernel_ms += ms;
       else cudaGetLastError();
+      if (st.host_ctrl.dense.total != 0) {
+        // ... but it fits the generic kernel's (the sampler kept it, switched off): switch it on
+        static const int one = 1;
+        CUDA_TRY(cudaMemcpyAsync(&st.ctrl->dense.enabled, &one, sizeof(int), cudaMemcpyHostToDevice, stream));
+      }
       run_aggregate(st, gb, stream, sp, false);
       read_ctrl(st, stream);
     }

@@ -87,15 +87,20 @@ __device__ __forceinline__ bool fx_split(u64 bits, int B, int& q, u32 (&l)[4])
   return true;
 }
 // (the limb arrays live in shared memory: 32-bit shared addresses and reductions that return nothing)
-__device__ __forceinline__ void fx_add(int* limbs, int ns, int slot, bool neg, int q, const u32 (&l)[4])
+// (`limbs_saddr`: the shared-memory address of word 0 of slot 0)
+__device__ __forceinline__ void fx_add_s(u32 limbs_saddr, int ns, int slot, bool neg, int q, const u32 (&l)[4])
 {
-  const u32 base = (u32)__cvta_generic_to_shared(limbs) + 4u * (u32)(q * ns + slot);
+  const u32 base = limbs_saddr + 4u * (u32)(q * ns + slot);
 #pragma unroll
   for (int i = 0; i < 4; ++i)
     if (l[i]) {
       const int v = neg ? -(int)l[i] : (int)l[i];
       asm volatile("red.shared.add.s32 [%0], %1;" ::"r"(base + 4u * (u32)(i * ns)), "r"(v) : "memory");
     }
+}
+__device__ __forceinline__ void fx_add(int* limbs, int ns, int slot, bool neg, int q, const u32 (&l)[4])
+{
+  fx_add_s((u32)__cvta_generic_to_shared(limbs), ns, slot, neg, q, l);
 }
 // empties the limbs of one slot and returns their value
 __device__ __noinline__ double fx_take(int* limbs, int ns, int slot, int B)
@@ -106,16 +111,17 @@ __device__ __noinline__ double fx_take(int* limbs, int ns, int slot, int B)
 }
 
 // ------------------------------------------------------------------------------ table init
-__device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, DDense* out);
+__device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, u32 cap_lean, DDense* out);
 
 // Must be launched with TABLE_INIT_BLOCK threads per CTA.  With `cap_dense` > 0 the last CTA also
 // samples the key box of the fused kernels that follow on the stream (sample_dense_box) into the
 // control block: one CTA's 1024 reads here instead of the same 1024 reads by every CTA of the fused
-// kernel (148 CTAs queueing on the same sectors cost 6.5 us of that kernel).
+// kernel (148 CTAs queueing on the same sectors cost 6.5 us of that kernel).  `cap_lean` > 0: a lean kernel
+// follows whose table holds fewer slots than the generic kernel's `cap_dense`.
 constexpr int TABLE_INIT_BLOCK = 256;
 __global__ void __launch_bounds__(TABLE_INIT_BLOCK)
 k_table_init(u64* __restrict__ tbl, i64 nslots, const __grid_constant__ DPlan P, DCtrl* ctrl, u64 claim_limit,
-             u64 dense_slots = 0, u32 cap_dense = 0)
+             u64 dense_slots = 0, u32 cap_dense = 0, u32 cap_lean = 0)
 {
   const bool sampling = ctrl && cap_dense > 0;
   if (ctrl && blockIdx.x == 0 && threadIdx.x < sizeof(DCtrl) / 4) {
@@ -127,7 +133,7 @@ k_table_init(u64* __restrict__ tbl, i64 nslots, const __grid_constant__ DPlan P,
     const bool in_box = threadIdx.x >= offsetof(DCtrl, dense) / 4 && threadIdx.x < (offsetof(DCtrl, dense) + sizeof(DDense)) / 4;
     if (!(sampling && in_box)) ((u32*)ctrl)[threadIdx.x] = v;
   }
-  if (sampling && blockIdx.x == gridDim.x - 1) sample_dense_box(P, cap_dense, &ctrl->dense);
+  if (sampling && blockIdx.x == gridDim.x - 1) sample_dense_box(P, cap_dense, cap_lean, &ctrl->dense);
   // the table is written as one linear run of 8-byte words, two per thread and step (16-byte stores):
   // word w belongs to cell (w mod stride) of slot (w div stride); cell 0 is the key
   __shared__ u64 s_init[MAX_CELLS + 1];
@@ -331,14 +337,18 @@ __device__ __forceinline__ void prefetch_l2(const void* p)
 // One CTA (the last one of k_table_init) looks at 1024 evenly spaced rows and derives the dense key
 // box, or disables it when the box would not fit `cap_slots` shared-memory slots.  The fused kernels
 // read the box from the control block, so there is no host round trip.  Keys outside the box are
-// still aggregated correctly, through the global table.  Must be called by all TABLE_INIT_BLOCK
-// threads of the CTA.
+// still aggregated correctly, through the global table.  With `cap_lean` > 0 a box of more than
+// `cap_lean` slots that still fits `cap_slots` is written with enabled = 0 and its total kept: the lean
+// kernel declines it, and the host enables it for the generic kernel it launches instead.  Must be called
+// by all TABLE_INIT_BLOCK threads of the CTA.
 constexpr int SAMPLE_ROWS = 1024;
 constexpr int SAMPLE_PER_THREAD = SAMPLE_ROWS / 256;
-__device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, DDense* out)
+__device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, u32 cap_lean, DDense* out)
 {
   __shared__ i64 s_min[MAX_KEYS], s_max[MAX_KEYS];
+  __shared__ u32 s_vexp;
   if (threadIdx.x < MAX_KEYS) { s_min[threadIdx.x] = 0x7FFFFFFFFFFFFFFFll; s_max[threadIdx.x] = (i64)0x8000000000000000ull; }
+  if (threadIdx.x == 0) s_vexp = 0;
   __syncthreads();
   const i64 nsamp  = P.nrows < SAMPLE_ROWS ? P.nrows : SAMPLE_ROWS;
   const i64 stride = P.nrows / (nsamp > 0 ? nsamp : 1);
@@ -393,6 +403,26 @@ __device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, 
       }
       if ((threadIdx.x & 31) == 0 && lo <= hi) { atomicMin(&s_min[k], lo); atomicMax(&s_max[k], hi); }
     }
+    if (P.flags & PF_F64MEAN) {
+      // the largest exponent among the sampled FLOAT64 values places the window of the fixed-point limbs
+      // (zeros, denormals, infinities and NaN say nothing about it; a null's payload is not looked at)
+      const DValCol& vc = P.vals[P.cells[0].col];
+      u64 bits[SAMPLE_PER_THREAD];
+      u32 w[SAMPLE_PER_THREAD];
+#pragma unroll
+      for (int j = 0; j < SAMPLE_PER_THREAD; ++j) {
+        bits[j] = __ldg((const u64*)vc.data + vc.offset + rows[j]);
+        w[j]    = vc.mask ? __ldg(vc.mask + ((vc.offset + rows[j]) >> 5)) >> ((vc.offset + rows[j]) & 31) : 1u;
+      }
+      u32 emax = 0;
+#pragma unroll
+      for (int j = 0; j < SAMPLE_PER_THREAD; ++j) {
+        const u32 e = (u32)(bits[j] >> 52) & 0x7FFu;
+        if (((ok >> j) & 1u) && (w[j] & 1u) && e != 0u && e != 0x7FFu && e + 1u > emax) emax = e + 1u;
+      }
+      emax = __reduce_max_sync(0xFFFFFFFFu, emax);
+      if ((threadIdx.x & 31) == 0 && emax) atomicMax(&s_vexp, emax);
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -401,7 +431,7 @@ __device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, 
     D.enabled = 0;
     D.total   = 0;
     D.copies  = 1;
-    D.pad     = 0;
+    D.vexp    = s_vexp;
     bool ok   = P.key_mode == KM_PACKED && nsamp >= SAMPLE_ROWS && cap_slots > 0;
     for (int pass = 0; pass < 2 && ok && !D.enabled; ++pass) {  // pass 0: padded box, pass 1: tight box
       u64 total = 1;
@@ -420,10 +450,12 @@ __device__ __forceinline__ void sample_dense_box(const DPlan& P, u32 cap_slots, 
         if (total > (u64)cap_slots) fits = false;
       }
       if (fits) {
-        D.enabled = 1;
+        const bool lean_too = cap_lean == 0 || total <= (u64)cap_lean;
+        D.enabled = lean_too ? 1 : 0;
         D.total   = (u32)total;
-        const u32 r = cap_slots / (u32)total;
+        const u32 r = (cap_lean != 0 && lean_too ? cap_lean : cap_slots) / (u32)total;
         D.copies  = r < 1 ? 1u : (r > 32u ? 32u : r);
+        // (a padded box that only the generic table holds: the tight one may still fit the lean table)
       }
     }
   }

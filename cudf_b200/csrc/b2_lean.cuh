@@ -1,7 +1,7 @@
-// b2_lean.cuh — the lean instantiation of the fused aggregate pass: "Σ and n of one FLOAT32 column"
-// (a mean) over 1..3 fixed-width key columns whose sampled key box fits shared memory.
+// b2_lean.cuh — the lean instantiation of the fused aggregate pass: "Σ and n of one FLOAT32 or FLOAT64
+// column" (a mean) over 1..3 fixed-width key columns whose sampled key box fits shared memory.
 //
-//   k_aggregate_lean<NK, K8, STAGED>
+//   k_aggregate_lean<NK, K8, STAGED, KEY_MASKS, V8>
 //     replaces mapping_indices_kernel + single_pass_shmem_aggs_kernel for this shape
 //     (cpp/src/groupby/hash/compute_mapping_indices.cuh:92-151, compute_shared_memory_aggs.cu:260-353).
 //
@@ -10,6 +10,13 @@
 // the fp32 -> fp64 spill of a long partial sum, the ragged end of the input) lives in __noinline__
 // functions.  One CTA per SM, 4 consecutive rows per thread per tile, two native shared-memory
 // atomics per row into the CTA's direct-indexed table {fp32 partial sum, u32 count}.
+//
+//   V8 = true : the value column is FLOAT64.  A 64-bit floating-point add in shared memory is a
+//               compare-and-swap loop, so the partial sum of a slot is kept as FX_LIMBS signed 32-bit words
+//               of fixed point instead (fx_split / fx_add_s): a row costs up to four native 32-bit adds and
+//               its count, and the partial sums are exact.  The window of the limbs comes from the largest
+//               exponent the key-box sampler saw; a value outside it (or a denormal, an infinity, NaN) is
+//               added to the fp64 cell of the global table directly, as a rare row.
 //
 //   STAGED = false : tiles go global -> registers with 16-byte ld.global.nc, the next tile's vectors
 //                    are loaded into a second register set while the current tile is folded;
@@ -68,7 +75,9 @@ __device__ __forceinline__ void bulk_g2s(u32 dst, const void* src, u32 bytes, u3
 
 // ------------------------------------------------------------------------------ rare paths
 struct LeanRare {  // what the rare paths need: this CTA's table and the global one
-  float* ssum; u32* socc; int* s_new;
+  float* ssum;  // fp32 partial sums, or (V8) the limbs: word i of slot s at ((int*)ssum)[i * nsp + s]
+  int nsp, fx_base;
+  u32* socc; int* s_new;
   u64* tbl; i64 cap; i64 region; int stride; int special_pos;
   DCtrl* ctrl; const DDense* box;
 };
@@ -91,7 +100,8 @@ __device__ __forceinline__ SlotRef lean_box_slot(const LeanRare& L, u32 pos)
 }
 
 // a row that cannot be folded in shared memory: its key lies outside the sampled box (global hashed
-// region), or it belongs to the ragged end of the input (in-box keys go to the dense region directly)
+// region), its FLOAT64 value does not fit the window of the limbs, or it belongs to the ragged end of
+// the input (in-box keys go to the dense region directly)
 __device__ __noinline__ void lean_slow_row(const DPlan& P, const LeanRare& L, i64 row, bool check_active)
 {
   if (check_active && !row_active(P, row)) return;
@@ -110,13 +120,15 @@ __device__ __noinline__ void lean_slow_row(const DPlan& P, const LeanRare& L, i6
   }
   const DValCol& vc = P.vals[P.cells[0].col];
   if (value_valid(vc, row)) {
-    atomicAdd((double*)ref.cells, (double)__ldg((const float*)vc.data + vc.offset + row));
+    const double x = vc.vclass == VC_F64 ? __ldg((const double*)vc.data + vc.offset + row)
+                                         : (double)__ldg((const float*)vc.data + vc.offset + row);
+    atomicAdd((double*)ref.cells, x);
     atomicAdd(ref.cells + ref.step, 1ull);
   }
 }
 
 // the rare rows of one 4-row group: active rows whose value is null (the group exists, nothing is
-// added) and active rows whose key lies outside the box
+// added) and active rows whose key lies outside the box or whose value lies outside the limbs' window (`bad`)
 __device__ __noinline__ void lean_rare_rows(const DPlan& P, const LeanRare& L, u32 rare, u32 bad, i64 r0, u32 d0, u32 d1,
                                             u32 d2, u32 d3)
 {
@@ -140,9 +152,14 @@ __device__ __noinline__ void lean_spill(const LeanRare& L, u32 slot, u32 copy_of
   const float part = atomicExch(L.ssum + slot, 0.f);
   atomicAdd((double*)lean_box_slot(L, slot - copy_off).cells, (double)part);
 }
+// V8: every FX_FLUSH-th addend of a slot empties its limbs into the fp64 global cell, so that no word overflows
+__device__ __noinline__ void lean_flush(const LeanRare& L, u32 slot, u32 copy_off)
+{
+  atomicAdd((double*)lean_box_slot(L, slot - copy_off).cells, fx_take((int*)L.ssum, L.nsp, (int)slot, L.fx_base));
+}
 
 // ------------------------------------------------------------------------------ the kernel
-template <int NK, bool K8, bool STAGED, bool KEY_MASKS>
+template <int NK, bool K8, bool STAGED, bool KEY_MASKS, bool V8>
 __global__ void __launch_bounds__(1024, 1)
 k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap, DCtrl* ctrl, u32 region_slots)
 {
@@ -168,14 +185,18 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
   const int NSP     = (NS + 3) & ~3;  // arrays padded to 16 bytes
   const u32 copy_off = (u32)((tid >> 5) % copies) * (u32)S;
 
-  float* ssum = (float*)smem_raw;       // [NSP] fp32 partial sums
-  u32* scnt   = (u32*)(ssum + NSP);     // [NSP] counts
-  u32* socc   = scnt + NSP;             // [(NS + 31) / 32] groups seen through a null value only
+  constexpr int SUM_WORDS = V8 ? FX_LIMBS : 1;  // 32-bit words of one slot's partial sum
+  constexpr u32 VB = V8 ? 8u : 4u;              // bytes of one value
+  float* ssum = (float*)smem_raw;               // [NSP] fp32 partial sums; V8: [FX_LIMBS][NSP] limbs
+  u32* scnt   = (u32*)(ssum + SUM_WORDS * NSP); // [NSP] counts
+  u32* socc   = scnt + NSP;                     // [(NS + 31) / 32] groups seen through a null value only
   const int nocc = (NS + 31) / 32;
-  unsigned char* stage0 = smem_raw + (((size_t)(2 * NSP + nocc) * 4 + 127) & ~(size_t)127);
+  unsigned char* stage0 = smem_raw + (((size_t)((SUM_WORDS + 1) * NSP + nocc) * 4 + 127) & ~(size_t)127);
+  // V8: the window of the limbs, from the largest exponent the sampler saw
+  const int fx_base = V8 && s_dense.vexp ? (int)s_dense.vexp - 1 + FX_HEADROOM - FX_MAX_SHIFT : FX_NEVER;
 
   {
-    const int nwords = 2 * NSP + nocc, nquads = nwords / 4;  // the arrays start 16-byte aligned
+    const int nwords = (SUM_WORDS + 1) * NSP + nocc, nquads = nwords / 4;  // the arrays start 16-byte aligned
     for (int i = tid; i < nquads; i += blockDim.x) ((uint4*)smem_raw)[i] = make_uint4(0, 0, 0, 0);
     for (int i = 4 * nquads + tid; i < nwords; i += blockDim.x) ((u32*)smem_raw)[i] = 0;
   }
@@ -191,7 +212,7 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
     for (int k = 0; k < P.nkeys; ++k) bits += 8 * P.keys[k].width + (P.keys[k].nullbit >= 0 ? 1 : 0);
     if (bits == 64) special_pos = dense_index(P, s_dense, EMPTY);
   }
-  LeanRare L{ssum, socc, &s_new, tbl, cap, (i64)region_slots, stride, special_pos, ctrl, &s_dense};
+  LeanRare L{ssum, NSP, fx_base, socc, &s_new, tbl, cap, (i64)region_slots, stride, special_pos, ctrl, &s_dense};
 
   // the key box in registers: the shared-memory atomics below clobber memory for the compiler, so
   // anything left in s_dense would be re-read from shared memory in every tile
@@ -223,7 +244,9 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
   if (timekeeper) ctrl->t_phase[2] = global_timer_ns();
 
   // folds one group of 4 consecutive rows starting at row r0
-  auto fold = [&](i64 r0, const uint4 (&ka)[NK], const uint4 (&kb)[NK], const u32 (&kn)[NK], const float4& q, u32 vn, u32 act) {
+  // (the values: four floats in qa, or — V8 — four doubles in qa and qb)
+  auto fold = [&](i64 r0, const uint4 (&ka)[NK], const uint4 (&kb)[NK], const u32 (&kn)[NK], const uint4& qa, const uint4& qb,
+                  u32 vn, u32 act) {
     u32 d0 = copy_off, d1 = copy_off, d2 = copy_off, d3 = copy_off, bad = 0;
 #pragma unroll
     for (int k = 0; k < NK; ++k) {
@@ -258,17 +281,37 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
     // the four rows' shared-memory atomics are issued back to back; the counts they return are
     // looked at afterwards, so that the warp waits for one round trip, not four
     u32 o0 = 0, o1 = 0, o2 = 0, o3 = 0;
-    if (take & 1u) { sred_add_f32(ssum_a + 4u * d0, q.x); o0 = satom_add_u32(scnt_a + 4u * d0, 1u); }
-    if (take & 2u) { sred_add_f32(ssum_a + 4u * d1, q.y); o1 = satom_add_u32(scnt_a + 4u * d1, 1u); }
-    if (take & 4u) { sred_add_f32(ssum_a + 4u * d2, q.z); o2 = satom_add_u32(scnt_a + 4u * d2, 1u); }
-    if (take & 8u) { sred_add_f32(ssum_a + 4u * d3, q.w); o3 = satom_add_u32(scnt_a + 4u * d3, 1u); }
-    if ((((o0 + 1u) & (F32_SPILL_AT - 1u)) == 0u) | (((o1 + 1u) & (F32_SPILL_AT - 1u)) == 0u) |
-        (((o2 + 1u) & (F32_SPILL_AT - 1u)) == 0u) | (((o3 + 1u) & (F32_SPILL_AT - 1u)) == 0u)) {
+    if (!V8) {
+      if (take & 1u) { sred_add_f32(ssum_a + 4u * d0, __uint_as_float(qa.x)); o0 = satom_add_u32(scnt_a + 4u * d0, 1u); }
+      if (take & 2u) { sred_add_f32(ssum_a + 4u * d1, __uint_as_float(qa.y)); o1 = satom_add_u32(scnt_a + 4u * d1, 1u); }
+      if (take & 4u) { sred_add_f32(ssum_a + 4u * d2, __uint_as_float(qa.z)); o2 = satom_add_u32(scnt_a + 4u * d2, 1u); }
+      if (take & 8u) { sred_add_f32(ssum_a + 4u * d3, __uint_as_float(qa.w)); o3 = satom_add_u32(scnt_a + 4u * d3, 1u); }
+    } else {
+      // a value that does not fit the window joins the rare rows (its bit moves from `take` to `bad`)
+      auto add8 = [&](u32 bit, u32 d, u32 lo, u32 hi, u32& o) {
+        if (!(take & bit)) return;
+        int q;
+        u32 l[4];
+        if (fx_split(((u64)hi << 32) | lo, fx_base, q, l)) {
+          fx_add_s(ssum_a, NSP, (int)d, (hi >> 31) != 0u, q, l);
+          o = satom_add_u32(scnt_a + 4u * d, 1u);
+        } else {
+          bad |= bit;
+        }
+      };
+      add8(1u, d0, qa.x, qa.y, o0);
+      add8(2u, d1, qa.z, qa.w, o1);
+      add8(4u, d2, qb.x, qb.y, o2);
+      add8(8u, d3, qb.z, qb.w, o3);
+    }
+    constexpr u32 EVERY = V8 ? FX_FLUSH : F32_SPILL_AT;
+    if ((((o0 + 1u) & (EVERY - 1u)) == 0u) | (((o1 + 1u) & (EVERY - 1u)) == 0u) |
+        (((o2 + 1u) & (EVERY - 1u)) == 0u) | (((o3 + 1u) & (EVERY - 1u)) == 0u)) {
       // (rows not taken keep o = 0)
-      if (((o0 + 1u) & (F32_SPILL_AT - 1u)) == 0u) lean_spill(L, d0, copy_off);
-      if (((o1 + 1u) & (F32_SPILL_AT - 1u)) == 0u) lean_spill(L, d1, copy_off);
-      if (((o2 + 1u) & (F32_SPILL_AT - 1u)) == 0u) lean_spill(L, d2, copy_off);
-      if (((o3 + 1u) & (F32_SPILL_AT - 1u)) == 0u) lean_spill(L, d3, copy_off);
+      if (((o0 + 1u) & (EVERY - 1u)) == 0u) { if (V8) lean_flush(L, d0, copy_off); else lean_spill(L, d0, copy_off); }
+      if (((o1 + 1u) & (EVERY - 1u)) == 0u) { if (V8) lean_flush(L, d1, copy_off); else lean_spill(L, d1, copy_off); }
+      if (((o2 + 1u) & (EVERY - 1u)) == 0u) { if (V8) lean_flush(L, d2, copy_off); else lean_spill(L, d2, copy_off); }
+      if (((o3 + 1u) & (EVERY - 1u)) == 0u) { if (V8) lean_flush(L, d3, copy_off); else lean_spill(L, d3, copy_off); }
     }
     const u32 rare = act & (bad | ~vn);
     if (rare) lean_rare_rows(P, L, rare, bad, r0, d0, d1, d2, d3);
@@ -280,10 +323,13 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
     const u32 tile_rows = 1024u * LEAN_ROWS;
     const u32 nfull     = (u32)(P.nrows / tile_rows);
     rows_done           = (i64)nfull * tile_rows;
-    auto load_tile = [&](u32 tile, float4& q, u32& vn, u32& act, uint4 (&ka)[NK], uint4 (&kb)[NK], u32 (&kn)[NK]) {
+    auto load_tile = [&](u32 tile, uint4& qa, uint4& qb, u32& vn, u32& act, uint4 (&ka)[NK], uint4 (&kb)[NK], u32 (&kn)[NK]) {
       const u32 r0 = tile * tile_rows + (u32)tid * LEAN_ROWS;
       const u32 ve = (u32)vc.offset + r0;
-      q  = __ldg((const float4*)((const float*)vc.data + ve));
+      const uint4* vp = (const uint4*)(vc.data + (u64)ve * VB);
+      qa = __ldg(vp);
+      if (V8) qb = __ldg(vp + 1);
+      else qb = make_uint4(0, 0, 0, 0);
       vn = vc.mask ? nibble_aligned(vc.mask, ve) : 0xFu;
       act = 0xFu;
       if (filt_is_val) act = vn;
@@ -299,29 +345,29 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
         else kb[k] = make_uint4(0, 0, 0, 0);
       }
     };
-    float4 q, nq;
+    uint4 qa, qb, nqa, nqb;
     u32 vn = 0, act = 0, nvn = 0, nact = 0;
     uint4 ka[NK], kb[NK], nka[NK], nkb[NK];
     u32 kn[NK], nkn[NK];
     // Register prefetch of the next tile pays off with 4-byte keys; with 8-byte key columns the second
     // set of vector registers costs more than it hides, and the tile after is requested into L2 instead
-    constexpr bool PREFETCH = !K8;
-    if (PREFETCH && blockIdx.x < nfull) load_tile(blockIdx.x, q, vn, act, ka, kb, kn);
+    constexpr bool PREFETCH = !K8 && !V8;
+    if (PREFETCH && blockIdx.x < nfull) load_tile(blockIdx.x, qa, qb, vn, act, ka, kb, kn);
     for (u32 tile = blockIdx.x; tile < nfull; tile += gridDim.x) {
       const u32 next = tile + gridDim.x;
       if (!PREFETCH) {
-        load_tile(tile, q, vn, act, ka, kb, kn);
+        load_tile(tile, qa, qb, vn, act, ka, kb, kn);
         if (next < nfull) {
           const u32 fr0 = next * tile_rows + (u32)tid * LEAN_ROWS;
-          prefetch_l2((const float*)vc.data + (u32)vc.offset + fr0);
+          prefetch_l2(vc.data + (u64)((u32)vc.offset + fr0) * VB);
 #pragma unroll
           for (int k = 0; k < NK; ++k) prefetch_l2(P.keys[k].data + (u64)((u32)P.keys[k].offset + fr0) * (u32)P.keys[k].width);
         }
       }
-      if (PREFETCH && next < nfull) load_tile(next, nq, nvn, nact, nka, nkb, nkn);
-      fold((i64)tile * tile_rows + (i64)tid * LEAN_ROWS, ka, kb, kn, q, vn, act);
+      if (PREFETCH && next < nfull) load_tile(next, nqa, nqb, nvn, nact, nka, nkb, nkn);
+      fold((i64)tile * tile_rows + (i64)tid * LEAN_ROWS, ka, kb, kn, qa, qb, vn, act);
       if (PREFETCH) {
-        q = nq; vn = nvn; act = nact;
+        qa = nqa; qb = nqb; vn = nvn; act = nact;
 #pragma unroll
         for (int k = 0; k < NK; ++k) { ka[k] = nka[k]; kb[k] = nkb[k]; kn[k] = nkn[k]; }
       }
@@ -338,7 +384,7 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
 #pragma unroll
     for (int k = 0; k < NK; ++k) { col_off[k] = off; off += TR * (u32)P.keys[k].width; }
     col_off[NK] = off;
-    const u32 mask_off = off + TR * 4u;
+    const u32 mask_off = off + TR * VB;
     const u32 stage_bytes = mask_off + LEAN_MASK_BYTES;
     const u32 bar0 = (u32)__cvta_generic_to_shared(s_bars);
     const u32 stage_a = (u32)__cvta_generic_to_shared(stage0);
@@ -357,7 +403,7 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
           for (int k = 0; k < NK; ++k)
             bulk_g2s(dst + col_off[k], P.keys[k].data + ((u64)P.keys[k].offset + r0) * (u32)P.keys[k].width,
                      TR * (u32)P.keys[k].width, full);
-          bulk_g2s(dst + col_off[NK], (const float*)vc.data + vc.offset + r0, TR * 4u, full);
+          bulk_g2s(dst + col_off[NK], vc.data + ((u64)vc.offset + r0) * VB, TR * VB, full);
           if (vc.mask) bulk_g2s(dst + mask_off, (const unsigned char*)vc.mask + (((u64)vc.offset + r0) >> 3), TR / 8u, full);
         }
         // the copies still in flight must land before this CTA's shared memory is reused or released
@@ -385,12 +431,14 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
           if (K8 && P.keys[k].width == 8) kb[k] = kp[1];
           else kb[k] = make_uint4(0, 0, 0, 0);
         }
-        const float4 q = *(const float4*)(st + col_off[NK] + (size_t)e * 4u);
+        const uint4* vp = (const uint4*)(st + col_off[NK] + (size_t)e * VB);
+        const uint4 qa = vp[0];
+        const uint4 qb = V8 ? vp[1] : make_uint4(0, 0, 0, 0);
         const u32 vn = vc.mask ? ((*(const u32*)(st + mask_off + (e >> 5) * 4u)) >> (e & 31u)) & 0xFu : 0xFu;
         const u32 act = filt_is_val ? vn : 0xFu;
         __syncwarp();
         if ((tid & 31) == 0) mbar_arrive(bar0 + 8u * (LEAN_STAGES + s));  // the stage's data is in registers
-        fold((i64)tile * TR + e, ka, kb, kn, q, vn, act);
+        fold((i64)tile * TR + e, ka, kb, kn, qa, qb, vn, act);
       }
     }
     if (failed) ctrl->error = 1;
@@ -439,14 +487,26 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
       double sum = 0.0;
       u64 n = 0;
       bool present = false;
+      i64 words[SUM_WORDS] = {};  // V8: the replicas' limbs, added word by word (exact)
       for (int r = 0; r < copies; ++r) {
         const int q = r * S + i;
         const u32 c = scnt[q];
         present = present || c != 0u || ((socc[q >> 5] >> (q & 31)) & 1u);
-        sum += (double)ssum[q];
+        if (V8) {
+#pragma unroll
+          for (int w = 0; w < SUM_WORDS; ++w) words[w] += (i64)((const int*)ssum)[w * NSP + q];
+        } else {
+          sum += (double)ssum[q];
+        }
         n += c;
       }
       if (!present) continue;
+      if (V8) {
+        double acc = 0.0;
+#pragma unroll
+        for (int w = SUM_WORDS - 1; w >= 0; --w) acc = acc * 262144.0 + (double)words[w];
+        sum = acc == 0.0 ? 0.0 : ldexp(acc, fx_base - 1075);
+      }
       const SlotRef ref = lean_box_slot(L, (u32)i);
       // (an unconditional store: reading the cell first would put an L2 round trip into every iteration)
       if (i == special_pos) { if (ctrl->special_used == 0) ctrl->special_used = 1; }

@@ -319,6 +319,51 @@ def test_float32_sum_spills_to_fp64():
     check([k, k2], [(v, [Kind.SUM, Kind.COUNT_VALID])])
 
 
+def test_float64_mean_keeps_its_sum_as_fixed_point_limbs():
+    """Σ and n of one FLOAT64 column over a sampled key box: the lean kernel keeps each partial sum as
+    fixed-point limbs whose window comes from the sampled values.  Register tiles (4), the bulk-copy ring (5)
+    and auto (0); values far outside the window, zeros, denormals, infinities and NaN (added to the fp64
+    cells directly); a group with many thousand addends per CTA (the limbs are emptied every 2048); nullable
+    keys under both policies and keys the sample missed; a box that only the generic kernel's table holds
+    (8000 keys), and one that neither holds (40000 keys)."""
+    rng = np.random.default_rng(83)
+    n = 1_500_000
+    x = rng.standard_normal(n) * np.exp(rng.standard_normal(n))
+    x[rng.random(n) < 0.01] = 0.0
+    x[rng.random(n) < 0.001] *= 1e-30
+    x[rng.random(n) < 0.001] *= 1e25
+    x[rng.random(n) < 0.0005] = 5e-324
+    k = rng.integers(0, 1000, n).astype(np.int64)
+    x[(k == 5) & (rng.random(n) < 0.01)] = np.inf
+    x[(k == 6) & (rng.random(n) < 0.01)] = -np.inf
+    x[(k == 7) & (rng.random(n) < 0.01)] = np.nan
+    v = HostColumn.from_numpy(x, valid=rng.random(n) > 0.05)
+    aggs = [Kind.SUM, Kind.COUNT_VALID, Kind.MEAN]
+    for variant in (0, 4, 5):
+        got = check([HostColumn.from_numpy(k)], [(v, aggs)], table_variant=variant)
+        assert got[0][0].size == 1000
+        check([HostColumn.from_numpy(k)], [(v, [Kind.MEAN])], row_filters=[v], table_variant=variant)
+    # one group takes 99.9 % of the rows
+    hot = HostColumn.from_numpy((rng.random(n) < 0.001).astype(np.int32))
+    zero = HostColumn.from_numpy(np.zeros(n, dtype=np.int64))
+    check([zero, hot], [(v, aggs)])
+    tame = HostColumn.from_numpy(rng.standard_normal(n) * 1e-3 + 1.0)        # every value inside the window
+    check([zero, hot], [(tame, aggs)])
+    # nullable keys, keys far outside the sampled box
+    a = rng.integers(-40, 40, n).astype(np.int32)
+    b = rng.integers(1000, 1012, n).astype(np.int64)
+    odd = rng.choice(n, 30, replace=False)
+    a[odd] = rng.integers(-2**31, 2**31 - 1, 30)
+    b[odd[:10]] = rng.integers(-2**62, 2**62, 10)
+    ka = HostColumn.from_numpy(a, valid=rng.random(n) > 0.01)
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        check([ka, HostColumn.from_numpy(b)], [(v, aggs)], policy)
+    # key boxes wider than the limbs' table
+    for distinct in (8000, 40_000):
+        wide = HostColumn.from_numpy(rng.integers(0, distinct, n).astype(np.int32))
+        assert check([wide], [(v, aggs)])[0][0].size == distinct
+
+
 def test_min_max_with_nan_and_infinity_terminate():
     # cpp/tests/groupby/min_tests.cpp:518-541, max_tests.cpp:526-549: all-NaN groups must not hang
     keys = HostColumn.from_numpy(np.array([1, 1, 2, 2, 2], dtype=np.int32))
