@@ -212,6 +212,8 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
     for (int k = 0; k < P.nkeys; ++k) bits += 8 * P.keys[k].width + (P.keys[k].nullbit >= 0 ? 1 : 0);
     if (bits == 64) special_pos = dense_index(P, s_dense, EMPTY);
   }
+  // bytes of key column k: a constant when no column is 8 bytes wide, so the offsets below fold away
+  auto kwidth = [&](int k) -> u32 { return K8 ? (u32)P.keys[k].width : 4u; };
   LeanRare L{ssum, NSP, fx_base, socc, &s_new, tbl, cap, (i64)region_slots, stride, special_pos, ctrl, &s_dense};
 
   // the key box in registers: the shared-memory atomics below clobber memory for the compiler, so
@@ -317,12 +319,10 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
     if (rare) lean_rare_rows(P, L, rare, bad, r0, d0, d1, d2, d3);
   };
 
-  i64 rows_done = 0;
   if (!STAGED) {
     // ---- tiles from global memory into registers
     const u32 tile_rows = 1024u * LEAN_ROWS;
     const u32 nfull     = (u32)(P.nrows / tile_rows);
-    rows_done           = (i64)nfull * tile_rows;
     auto load_tile = [&](u32 tile, uint4& qa, uint4& qb, u32& vn, u32& act, uint4 (&ka)[NK], uint4 (&kb)[NK], u32 (&kn)[NK]) {
       const u32 r0 = tile * tile_rows + (u32)tid * LEAN_ROWS;
       const u32 ve = (u32)vc.offset + r0;
@@ -339,7 +339,7 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
         const DKeyCol& c = P.keys[k];
         const u32 e = (u32)c.offset + r0;
         kn[k] = (KEY_MASKS && c.mask) ? nibble_aligned(c.mask, e) : 0xFu;
-        const uint4* kp = (const uint4*)(c.data + (u64)e * (u32)c.width);
+        const uint4* kp = (const uint4*)(c.data + (u64)e * kwidth(k));
         ka[k] = __ldg(kp);
         if (K8 && c.width == 8) kb[k] = __ldg(kp + 1);
         else kb[k] = make_uint4(0, 0, 0, 0);
@@ -361,7 +361,7 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
           const u32 fr0 = next * tile_rows + (u32)tid * LEAN_ROWS;
           prefetch_l2(vc.data + (u64)((u32)vc.offset + fr0) * VB);
 #pragma unroll
-          for (int k = 0; k < NK; ++k) prefetch_l2(P.keys[k].data + (u64)((u32)P.keys[k].offset + fr0) * (u32)P.keys[k].width);
+          for (int k = 0; k < NK; ++k) prefetch_l2(P.keys[k].data + (u64)((u32)P.keys[k].offset + fr0) * kwidth(k));
         }
       }
       if (PREFETCH && next < nfull) load_tile(next, nqa, nqb, nvn, nact, nka, nkb, nkn);
@@ -378,11 +378,10 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
     // there are no key masks and the only row filter (if any) is the value column's own mask.
     constexpr u32 TR = LEAN_STAGED_CONSUMERS * LEAN_ROWS;
     const u32 nfull  = (u32)(P.nrows / TR);
-    rows_done        = (i64)nfull * TR;
     u32 col_off[NK + 1];
     u32 off = 0;
 #pragma unroll
-    for (int k = 0; k < NK; ++k) { col_off[k] = off; off += TR * (u32)P.keys[k].width; }
+    for (int k = 0; k < NK; ++k) { col_off[k] = off; off += TR * kwidth(k); }
     col_off[NK] = off;
     const u32 mask_off = off + TR * VB;
     const u32 stage_bytes = mask_off + LEAN_MASK_BYTES;
@@ -401,8 +400,7 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
           mbar_expect_tx(full, mask_off + (vc.mask ? TR / 8u : 0u));
 #pragma unroll
           for (int k = 0; k < NK; ++k)
-            bulk_g2s(dst + col_off[k], P.keys[k].data + ((u64)P.keys[k].offset + r0) * (u32)P.keys[k].width,
-                     TR * (u32)P.keys[k].width, full);
+            bulk_g2s(dst + col_off[k], P.keys[k].data + ((u64)P.keys[k].offset + r0) * kwidth(k), TR * kwidth(k), full);
           bulk_g2s(dst + col_off[NK], vc.data + ((u64)vc.offset + r0) * VB, TR * VB, full);
           if (vc.mask) bulk_g2s(dst + mask_off, (const unsigned char*)vc.mask + (((u64)vc.offset + r0) >> 3), TR / 8u, full);
         }
@@ -426,7 +424,7 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
 #pragma unroll
         for (int k = 0; k < NK; ++k) {
           kn[k] = 0xFu;
-          const uint4* kp = (const uint4*)(st + col_off[k] + (size_t)e * (u32)P.keys[k].width);
+          const uint4* kp = (const uint4*)(st + col_off[k] + (size_t)e * kwidth(k));
           ka[k] = kp[0];
           if (K8 && P.keys[k].width == 8) kb[k] = kp[1];
           else kb[k] = make_uint4(0, 0, 0, 0);
@@ -444,7 +442,10 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
     if (failed) ctrl->error = 1;
   }
 
-  // ---- the ragged end of the input, row by row
+  // ---- the ragged end of the input, row by row (the row count of the full tiles is worked out again here
+  // rather than kept in registers through the row loop; the same goes for the table's shape in the merge)
+  constexpr i64 TILE_ROWS = (STAGED ? LEAN_STAGED_CONSUMERS : 1024) * LEAN_ROWS;
+  const i64 rows_done = P.nrows / TILE_ROWS * TILE_ROWS;
   for (i64 r = rows_done + (i64)blockIdx.x * blockDim.x + tid; r < P.nrows; r += (i64)gridDim.x * blockDim.x)
     lean_slow_row(P, L, r, true);
 
@@ -457,6 +458,11 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
     // position -> key without divisions (dense_key divides twice per key column: 13 us of this merge for
     // 16 positions per thread): mixed-radix decode with one reciprocal per column, exact because
     // positions and ranges stay below 2^15
+    const int S = (int)s_dense.total, copies = (int)s_dense.copies, NSP = (S * copies + 3) & ~3;
+    const int special_pos = L.special_pos;
+    const float* ssum = (const float*)smem_raw;
+    const u32* scnt   = (const u32*)(ssum + SUM_WORDS * NSP);
+    const u32* socc   = scnt + NSP;
     u32 rng[NK], magic[NK];
 #pragma unroll
     for (int k = 0; k < NK; ++k) {
@@ -524,6 +530,7 @@ k_aggregate_lean(const __grid_constant__ DPlan P, u64* __restrict__ tbl, i64 cap
   __syncthreads();
   if (s_last) {
     __threadfence();
+    const int S = (int)s_dense.total, special_pos = L.special_pos;
     int mine = 0;
     for (int i = tid; i < S; i += blockDim.x) {
       if (i == special_pos) continue;

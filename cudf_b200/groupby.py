@@ -136,7 +136,7 @@ class GroupBy:
     (EXCLUDE, default) or grouped (INCLUDE).  Extras of this engine: ``expected_groups`` (sizing
     hint), ``row_filters`` (validity masks a row must pass: a fused ``drop_nulls``),
     ``table_variant`` (0 auto, 1 global-memory table only, 3 shared-memory table with hashing only,
-    4 / 5 the lean FLOAT32-mean kernel with register tiles / with the bulk-copy tile ring, 6 / 7 always /
+    4 / 5 the lean float-mean kernel with register tiles / with the bulk-copy tile ring, 6 / 7 always /
     never the radix-partitioned path for very many groups, 8 STRING keys through dictionary ids whatever the
     row count).
     """

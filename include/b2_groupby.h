@@ -152,7 +152,7 @@ typedef struct b2_groupby_options {
   int32_t table_variant;    /* 0 auto; 1 global-memory table only; 2 = auto, but the partitioned
                                path folds no hot keys and keeps fp64 cells (no fixed-point limbs); 3 shared-memory table with
                                hashing only (no dense key box); 4 / 5 = auto, but the lean
-                               FLOAT32-mean kernel reads its tiles through registers (4) or
+                               float-mean kernel reads its tiles through registers (4) or
                                through the cp.async.bulk shared-memory ring (5); 6 = always
                                take the radix-partitioned path when the keys allow it (auto
                                takes it from about half a million groups), 7 = never; 8 =
