@@ -17,6 +17,12 @@ def sum() -> Aggregation:  # noqa: A001 - mirrors the reference's name
     return Aggregation(Kind.SUM)
 
 
+def sum_overflow() -> Aggregation:
+    """cudf::make_sum_overflow_aggregation (cpp/include/cudf/aggregation.hpp:214-217): a struct
+    {sum in the source type, overflow flag} per group; signed integers and decimals only."""
+    return Aggregation(Kind.SUM_OVERFLOW)
+
+
 def product() -> Aggregation:
     return Aggregation(Kind.PRODUCT)
 

@@ -30,7 +30,7 @@ class Column:
 
     def __init__(self, type_id: int, size: int, data: Optional[torch.Tensor], mask: Optional[torch.Tensor] = None,
                  offset: int = 0, null_count: int = -1, offsets: Optional[torch.Tensor] = None,
-                 offsets_type: TypeId = TypeId.INT32, scale: int = 0):
+                 offsets_type: TypeId = TypeId.INT32, scale: int = 0, children: Optional[list] = None):
         self.type_id = TypeId(type_id)
         self.scale = int(scale)  # DECIMAL32/64 only
         self.size = int(size)
@@ -40,6 +40,7 @@ class Column:
         self.null_count = int(null_count) if mask is not None else 0
         self.offsets = offsets
         self.offsets_type = TypeId(offsets_type)
+        self.children = children  # STRUCT results (SUM_OVERFLOW): the child columns
 
     # -- construction ---------------------------------------------------------------------
     @staticmethod
@@ -71,6 +72,9 @@ class Column:
         def np_of(t, dtype):
             return None if t is None else t.cpu().numpy().view(dtype).copy()
         mask = np_of(self.mask, np.uint32)
+        if self.type_id == TypeId.STRUCT:
+            return HostColumn(self.type_id, self.size, None, mask, self.offset, None, 0,
+                              [c.to_host() for c in (self.children or [])])
         if self.type_id == TypeId.STRING:
             od = np.int64 if self.offsets_type == TypeId.INT64 else np.int32
             chars = np.zeros(0, np.uint8) if self.data is None else self.data.cpu().numpy().copy()

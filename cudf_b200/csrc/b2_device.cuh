@@ -51,7 +51,10 @@ enum CellOp : int {
   // the cell holds the ROW of the smallest / largest value seen so far (all-ones = none yet): ARGMIN /
   // ARGMAX themselves, and MIN / MAX of STRING values, which the reference computes as ARGMIN / ARGMAX
   // followed by a gather (cpp/src/groupby/hash/extract_single_pass_aggs.cpp:39-60)
-  OP_ARGMIN, OP_ARGMAX
+  OP_ARGMIN, OP_ARGMAX,
+  // SUM_OVERFLOW of a 64-bit source: Σ(v >> 32) and Σ(v & 0xFFFFFFFF), each exact in 64 bits for fewer than 2^31
+  // rows, so that the finisher knows the exact sum and whether it fits the source type
+  OP_SUM_HI, OP_SUM_LO
 };
 __host__ __device__ __forceinline__ bool is_arg_op(int op) { return op == OP_ARGMIN || op == OP_ARGMAX; }
 constexpr unsigned long long ARG_NONE = 0xFFFFFFFFFFFFFFFFull;
@@ -479,6 +482,8 @@ __device__ __forceinline__ void cell_update(u64* cell, int op, u64 v)
 {
   switch (op) {
     case OP_SUM_I: atomicAdd(cell, v); break;
+    case OP_SUM_HI: atomicAdd(cell, (u64)((i64)v >> 32)); break;
+    case OP_SUM_LO: atomicAdd(cell, v & 0xFFFFFFFFull); break;
     case OP_SUM_F: atomicAdd((double*)cell, __longlong_as_double((i64)v)); break;
     case OP_SSQ_I: atomicAdd(cell, v * v); break;
     case OP_SSQ_F: { const double d = __longlong_as_double((i64)v); atomicAdd((double*)cell, d * d); break; }
@@ -561,7 +566,7 @@ __device__ inline void arg_update(u64* cell, int op, const DValCol& c, i64 row)
 __device__ __forceinline__ u64 cell_combine(int op, u64 a, u64 b)
 {
   switch (op) {
-    case OP_SUM_I: case OP_SSQ_I: case OP_CNT_V: case OP_CNT_A: return a + b;
+    case OP_SUM_I: case OP_SSQ_I: case OP_CNT_V: case OP_CNT_A: case OP_SUM_HI: case OP_SUM_LO: return a + b;
     case OP_SUM_F: case OP_SSQ_F:
       return (u64)__double_as_longlong(__longlong_as_double((i64)a) + __longlong_as_double((i64)b));
     case OP_MIN_I: return (i64)a < (i64)b ? a : b;
@@ -580,7 +585,7 @@ __device__ __forceinline__ u64 cell_combine(int op, u64 a, u64 b)
 __device__ __forceinline__ void cell_merge(u64* cell, int op, u64 part)
 {
   switch (op) {
-    case OP_SUM_I: case OP_SSQ_I: case OP_CNT_V: case OP_CNT_A: atomicAdd(cell, part); break;
+    case OP_SUM_I: case OP_SSQ_I: case OP_CNT_V: case OP_CNT_A: case OP_SUM_HI: case OP_SUM_LO: atomicAdd(cell, part); break;
     case OP_SUM_F: case OP_SSQ_F: atomicAdd((double*)cell, __longlong_as_double((i64)part)); break;
     case OP_MIN_I: atomicMin((i64*)cell, (i64)part); break;
     case OP_MIN_U: case OP_MIN_F: atomicMin(cell, part); break;

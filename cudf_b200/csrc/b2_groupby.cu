@@ -192,6 +192,7 @@ int result_type(int src, int kind)
     case B2_AGG_COUNT_VALID: case B2_AGG_COUNT_ALL: case B2_AGG_ARGMAX: case B2_AGG_ARGMIN: return B2_INT32;
     case B2_AGG_MIN: case B2_AGG_MAX: return src;
     case B2_AGG_SUM: return (is_float_t(src) || is_duration_t(src) || is_decimal_t(src)) ? src : B2_INT64;  // decimals keep type and scale
+    case B2_AGG_SUM_OVERFLOW: return B2_STRUCT;  // {sum: the source type, overflow: BOOL8} (aggregation.hpp:990-995)
     case B2_AGG_SUM_OF_SQUARES: case B2_AGG_PRODUCT: return is_float_t(src) ? src : B2_INT64;
     case B2_AGG_MEAN: return is_duration_t(src) ? src : B2_FLOAT64;
     default: return B2_FLOAT64;
@@ -215,6 +216,12 @@ int classify_request(int src, int kind)
       // (cpp/tests/groupby/sum_tests.cpp:220-248, min_tests.cpp:271-292, max_tests.cpp:279-300)
       if (is_numeric_t(src) || is_duration_t(src) || is_decimal_t(src)) return 0;
       if (src == B2_DECIMAL128 || src == B2_DICTIONARY32) return 2;
+      return 1;
+    case B2_AGG_SUM_OVERFLOW:
+      // signed integers and decimals (cpp/include/cudf/detail/aggregation/aggregation.hpp:980-995,
+      // cpp/tests/groupby/sum_overflow_tests.cpp:495-561: BOOL8 and the unsigned types throw)
+      if (src == B2_INT8 || src == B2_INT16 || src == B2_INT32 || src == B2_INT64 || is_decimal_t(src)) return 0;
+      if (src == B2_DECIMAL128) return 2;
       return 1;
     case B2_AGG_MEAN:
       if (is_numeric_t(src) || is_duration_t(src)) return 0;
@@ -267,6 +274,7 @@ struct OutSpec {  // one requested aggregation → one result column
   int req, agg;
   int kind;      // OutKind
   int rtype;     // b2_type_id of the result
+  int ctype = 0; // OK_SUMOVF: type of the struct's sum child (the source type)
   int scale = 0; // decimal results: the source column's scale
   int c_a = -1, c_b = -1, c_cnt = -1;
   int ddof = 1;
@@ -394,7 +402,7 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
   struct VKey { const void* d; const void* m; int off, type; };
   std::vector<VKey> seen;
   struct Need { bool sum = false, cnt = false, ssq = false, mn = false, mx = false, prod = false, nulls = false,
-                amin = false, amax = false; };
+                amin = false, amax = false, ovf8 = false; };
   std::vector<Need> need;
   sc.req_val.resize((size_t)nreqs);
   bool need_cnt_all = false;
@@ -418,6 +426,9 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
     for (int a = 0; a < reqs[r].num_aggregations; ++a) {
       switch (reqs[r].aggregations[a].kind) {
         case B2_AGG_SUM: nd.sum = true; break;
+        // SUM_OVERFLOW: sources of up to 32 bits share the int64 Σ cell of SUM (it cannot wrap below 2^31 rows);
+        // a 64-bit source gets two cells that hold its exact sum
+        case B2_AGG_SUM_OVERFLOW: if (width_of(v.type_id) == 8) nd.ovf8 = true; else nd.sum = true; break;
         case B2_AGG_COUNT_VALID: nd.cnt = true; break;
         case B2_AGG_COUNT_ALL: need_cnt_all = true; break;
         case B2_AGG_MIN: if (v.type_id == B2_STRING) nd.amin = true; else nd.mn = true; break;
@@ -434,7 +445,7 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
   sc.nvals = (int)seen.size();
 
   // cells, per value column in the order Σ, n, Σx², min, max, Π; the row count last
-  struct CellIdx { int sum = -1, cnt = -1, ssq = -1, mn = -1, mx = -1, prod = -1, amin = -1, amax = -1; };
+  struct CellIdx { int sum = -1, cnt = -1, ssq = -1, mn = -1, mx = -1, prod = -1, amin = -1, amax = -1, hi = -1, lo = -1; };
   std::vector<CellIdx> idx((size_t)sc.nvals);
   auto add_cell = [&](int op, int col) {
     if (sc.ncells >= MAX_CELLS) B2_FAIL(B2_UNSUPPORTED, "too many accumulators in one aggregate call");
@@ -446,7 +457,7 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
     const int t = sc.val_types[s];
     const bool f = is_float_t(t);
     const bool uns = t == B2_UINT64;
-    if (nd.nulls && (nd.sum || nd.ssq || nd.mn || nd.mx || nd.prod)) nd.cnt = true;  // decides validity
+    if (nd.nulls && (nd.sum || nd.ssq || nd.mn || nd.mx || nd.prod || nd.ovf8)) nd.cnt = true;  // decides validity
     if (nd.amin) { idx[(size_t)s].amin = add_cell(OP_ARGMIN, s); sc.has_arg = true; }
     if (nd.amax) { idx[(size_t)s].amax = add_cell(OP_ARGMAX, s); sc.has_arg = true; }
     if (nd.sum) idx[(size_t)s].sum = add_cell(f ? OP_SUM_F : OP_SUM_I, s);
@@ -455,6 +466,7 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
     if (nd.mn) idx[(size_t)s].mn = add_cell(f ? OP_MIN_F : uns ? OP_MIN_U : OP_MIN_I, s);
     if (nd.mx) idx[(size_t)s].mx = add_cell(f ? OP_MAX_F : uns ? OP_MAX_U : OP_MAX_I, s);
     if (nd.prod) idx[(size_t)s].prod = add_cell(f ? OP_PROD_F : OP_PROD_I, s);
+    if (nd.ovf8) { idx[(size_t)s].hi = add_cell(OP_SUM_HI, s); idx[(size_t)s].lo = add_cell(OP_SUM_LO, s); }
   }
   int cnt_all = -1;
   if (need_cnt_all) cnt_all = add_cell(OP_CNT_A, 0);
@@ -481,6 +493,10 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
       switch (kind) {
         case B2_AGG_COUNT_VALID: o.kind = OK_COUNT; o.c_a = ci.cnt; o.c_cnt = -1; o.nullable = false; break;
         case B2_AGG_COUNT_ALL: o.kind = OK_COUNT; o.c_a = cnt_all; o.c_cnt = -1; o.nullable = false; break;
+        case B2_AGG_SUM_OVERFLOW:
+          o.kind = OK_SUMOVF; o.ctype = t; o.scale = is_decimal_t(t) ? reqs[r].values.scale : 0;
+          if (width_of(t) == 8) { o.c_a = ci.hi; o.c_b = ci.lo; } else { o.c_a = ci.sum; }
+          break;
         case B2_AGG_SUM: o.kind = f ? OK_FLT : OK_INT; o.c_a = ci.sum; break;
         case B2_AGG_SUM_OF_SQUARES: o.kind = f ? OK_FLT : OK_INT; o.c_a = ci.ssq; break;
         case B2_AGG_PRODUCT: o.kind = f ? OK_FLT : OK_INT; o.c_a = ci.prod; break;
@@ -1486,13 +1502,23 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
         CUDA_TRY(cudaMemsetAsync(c.null_mask, 0xFF, c.null_mask_bytes, stream));
       }
       arg_rows[i] = Scratch(std::max<size_t>(8, (size_t)G * sizeof(int)), stream);
+    } else if (o.kind == OK_SUMOVF) {
+      // a STRUCT column: no data of its own, the struct-level mask, children {sum, overflow} without masks
+      // (cpp/tests/groupby/sum_overflow_tests.cpp:200-211)
+      init_owned(c, B2_STRUCT, G, o.nullable, al, stream);
+      c.num_children = 2;
+      c.children = (b2_owned_column*)std::calloc(2, sizeof(b2_owned_column));
+      init_owned(c.children[0], o.ctype, G, false, al, stream);
+      c.children[0].scale = o.scale;
+      init_owned(c.children[1], B2_BOOL8, G, false, al, stream);
     } else {
       init_owned(c, o.rtype, G, o.nullable, al, stream);
     }
-    c.scale = o.scale;
+    c.scale = o.kind == OK_SUMOVF ? 0 : o.scale;
     DOutCol& d = plan->outs[i];
-    d.data = o.kind == OK_STRARG ? arg_rows[i].p : c.data;
-    d.mask = c.null_mask; d.kind = o.kind; d.rclass = vclass_of(o.rtype);
+    d.data = o.kind == OK_STRARG ? arg_rows[i].p : o.kind == OK_SUMOVF ? c.children[0].data : c.data;
+    d.data2 = o.kind == OK_SUMOVF ? c.children[1].data : nullptr;
+    d.mask = c.null_mask; d.kind = o.kind; d.rclass = vclass_of(o.kind == OK_SUMOVF ? o.ctype : o.rtype);
     d.c_a = o.c_a; d.c_b = o.c_b; d.c_cnt = o.c_cnt; d.ddof = o.ddof; d.src_float = o.src_float;
     d.null_slot = (int)i;
   }
@@ -1567,6 +1593,7 @@ void finalize_state(b2_groupby_state& st, cudaStream_t stream, const b2_allocato
         b2_owned_column& c = out->results[sc.outs[i].req][sc.outs[i].agg];
         c.size = (int32_t)G;
         c.null_count = (int32_t)h.null_counts[i];
+        for (int ch = 0; ch < c.num_children && sc.outs[i].kind == OK_SUMOVF; ++ch) c.children[ch].size = (int32_t)G;
       }
       guard.armed = false;
       return;
@@ -1853,8 +1880,10 @@ extern "C" b2_status b2_groupby_aggregate_noalloc(b2_groupby* gb, const b2_aggre
     Schema sc = make_schema(*gb, requests, num_requests);
     if (sc.key_mode != KM_PACKED)
       B2_FAIL(B2_UNSUPPORTED, "the no-allocation variant serves keys that pack into 64 bits (no string / float / wide keys)");
-    for (const OutSpec& o : sc.outs)
+    for (const OutSpec& o : sc.outs) {
       if (o.kind == OK_STRARG) B2_FAIL(B2_UNSUPPORTED, "the no-allocation variant does not serve MIN / MAX of strings (their size is not known in advance)");
+      if (o.kind == OK_SUMOVF) B2_FAIL(B2_UNSUPPORTED, "the no-allocation variant does not serve SUM_OVERFLOW (a struct result)");
+    }
     DPlan P;
     fill_plan_schema(P, sc);
     bind_plan_inputs(P, sc, *gb, requests, num_requests);

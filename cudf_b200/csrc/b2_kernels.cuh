@@ -1110,11 +1110,13 @@ enum OutKind : int {
   OK_MINMAX_F,   // ordered-encoded double cell
   OK_MEAN, OK_M2, OK_VAR, OK_STD,
   OK_ARG,        // ARGMIN / ARGMAX: the row held by the cell as INT32, null when none
-  OK_STRARG      // MIN / MAX of strings: the row (or -1) into a scratch array the host gathers the strings by
+  OK_STRARG,     // MIN / MAX of strings: the row (or -1) into a scratch array the host gathers the strings by
+  OK_SUMOVF      // SUM_OVERFLOW: the sum in the source type into `data`, "the exact sum does not fit it" into `data2`
 };
 
 struct DOutCol {
   void* data;
+  void* data2;    // OK_SUMOVF: the BOOL8 overflow child
   u32* mask;      // nullptr = result not nullable
   int kind;       // OutKind
   int rclass;     // ValClass of the result element type
@@ -1195,6 +1197,31 @@ __device__ __forceinline__ void write_group(const DPlan& P, const DOutPlan& O, u
         const u64 r = cells[(i64)(oc.c_a) * cstep];
         valid = r != ARG_NONE;
         ((int*)oc.data)[g] = valid ? (int)r : (oc.kind == OK_ARG ? 0 : -1);
+        break;
+      }
+      case OK_SUMOVF: {
+        // The exact sum is Σ(v >> 32) · 2^32 + Σ(v & 0xFFFFFFFF) for a 64-bit source (cells c_a, c_b), the one
+        // int64 cell otherwise.  The reference raises the flag when an add wraps in the source type
+        // (cpp/include/cudf/detail/aggregation/device_aggregators.cuh:136-160), which depends on the order the
+        // rows arrive in; "the exact sum does not fit" is what every order gives when a group's values share a
+        // sign, and what the order that alternates signs gives otherwise.
+        bool ovf = false;
+        u64 sum  = 0;
+        if (valid) {
+          if (oc.c_b >= 0) {
+            const u64 lo = cells[(i64)(oc.c_b) * cstep];
+            const i64 t  = (i64)cells[(i64)(oc.c_a) * cstep] + (i64)(lo >> 32);
+            ovf = t < -2147483648ll || t > 2147483647ll;
+            sum = ((u64)t << 32) | (lo & 0xFFFFFFFFull);
+          } else {
+            const i64 v    = (i64)cells[(i64)(oc.c_a) * cstep];
+            const int bits = oc.rclass == VC_I8 ? 8 : oc.rclass == VC_I16 ? 16 : 32;
+            ovf = v < -(1ll << (bits - 1)) || v > (1ll << (bits - 1)) - 1;
+            sum = (u64)v;
+          }
+        }
+        store_int(oc.data, g, oc.rclass, sum);
+        ((unsigned char*)oc.data2)[g] = ovf ? 1 : 0;
         break;
       }
       case OK_MEAN: {

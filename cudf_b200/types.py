@@ -47,6 +47,7 @@ class TypeId(enum.IntEnum):
 
 class Kind(enum.IntEnum):
     SUM = 0
+    SUM_OVERFLOW = 1   # struct {sum: the source type, overflow: BOOL8}
     PRODUCT = 2
     MIN = 3
     MAX = 4
@@ -126,6 +127,8 @@ def result_type(source: int, kind: int) -> TypeId:
         return TypeId.INT32
     if kind in (Kind.MIN, Kind.MAX):
         return source
+    if kind == Kind.SUM_OVERFLOW:
+        return TypeId.STRUCT  # children {sum: source, overflow: BOOL8} (aggregation.hpp:990-995)
     if kind == Kind.SUM:
         # decimals keep their type and scale (aggregation.hpp:956-963)
         return source if (is_floating(source) or is_duration(source) or is_decimal(source)) else TypeId.INT64
@@ -171,6 +174,7 @@ class HostColumn:
     offset: int = 0
     offsets: Optional[np.ndarray] = None  # STRING: int32 or int64, offset+size+1 entries
     scale: int = 0                        # DECIMAL32/64: value = data * 10**scale (cpp/include/cudf/types.hpp data_type)
+    children: Optional[list] = None       # STRUCT: the child columns (``data`` is None)
 
     @property
     def null_count(self) -> int:

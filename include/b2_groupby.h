@@ -63,7 +63,7 @@ typedef enum b2_type_id {
  *      (cpp/include/cudf/aggregation.hpp:78-121).  Only the kinds the reference's
  *      hash path serves are listed (cpp/src/groupby/hash/groupby.cu:63-131). */
 typedef enum b2_agg_kind {
-  B2_AGG_SUM = 0, B2_AGG_PRODUCT = 2, B2_AGG_MIN = 3, B2_AGG_MAX = 4,
+  B2_AGG_SUM = 0, B2_AGG_SUM_OVERFLOW = 1, B2_AGG_PRODUCT = 2, B2_AGG_MIN = 3, B2_AGG_MAX = 4,
   B2_AGG_COUNT_VALID = 5, B2_AGG_COUNT_ALL = 6, B2_AGG_SUM_OF_SQUARES = 9,
   B2_AGG_MEAN = 10, B2_AGG_M2 = 11, B2_AGG_VARIANCE = 12, B2_AGG_STD = 13,
   B2_AGG_ARGMAX = 16, B2_AGG_ARGMIN = 17

@@ -54,11 +54,13 @@ enum TypeId : int32_t {
   T_EMPTY = 0, T_INT8, T_INT16, T_INT32, T_INT64, T_UINT8, T_UINT16, T_UINT32, T_UINT64,
   T_FLOAT32, T_FLOAT64, T_BOOL8, T_TS_DAYS, T_TS_S, T_TS_MS, T_TS_US, T_TS_NS,
   T_DUR_DAYS, T_DUR_S, T_DUR_MS, T_DUR_US, T_DUR_NS, T_DICT32, T_STRING, T_LIST,
-  T_DEC32, T_DEC64  // fixed point: the integer representation; the scale is metadata the caller keeps
+  T_DEC32, T_DEC64,  // fixed point: the integer representation; the scale is metadata the caller keeps
+  T_DEC128, T_STRUCT // (DECIMAL128 is not served; STRUCT is the result type of SUM_OVERFLOW)
 };
 enum Kind : int32_t {
   K_SUM = 0, K_PRODUCT = 2, K_MIN = 3, K_MAX = 4, K_COUNT_VALID = 5, K_COUNT_ALL = 6,
-  K_SUMSQ = 9, K_MEAN = 10, K_M2 = 11, K_VAR = 12, K_STD = 13, K_ARGMAX = 16, K_ARGMIN = 17
+  K_SUMSQ = 9, K_MEAN = 10, K_M2 = 11, K_VAR = 12, K_STD = 13, K_ARGMAX = 16, K_ARGMIN = 17,
+  K_SUM_OVERFLOW = 1
 };
 
 struct Col {  // host-memory mirror of a column_view
@@ -161,6 +163,12 @@ struct Acc {  // per (group, request): every simple accumulator the supported ki
   // cpp/src/groupby/hash/extract_single_pass_aggs.cpp:39-60): row of the extreme valid value, the first
   // such row on ties; -1 = no valid value (ARGMIN_SENTINEL, cpp/include/cudf/detail/aggregation/aggregation.hpp)
   int64_t argmin = -1, argmax = -1;
+  // SUM_OVERFLOW: the exact sum.  The reference adds in the source type and raises the flag when an add wraps
+  // (cpp/include/cudf/detail/aggregation/device_aggregators.cuh:136-160); which adds wrap depends on the order
+  // the rows arrive in.  "The exact sum does not fit the source type" is the flag every arrival order gives when
+  // the values of a group share a sign (the reference's tests, cpp/tests/groupby/sum_overflow_tests.cpp:260-378),
+  // and the flag of the order that alternates signs otherwise; the sum of a flagged group is not specified there.
+  __int128 xsum = 0;
 };
 
 struct Group {
@@ -175,6 +183,9 @@ struct OutCol {
   std::vector<uint32_t> mask;  // empty => not nullable
   int64_t null_count = 0;
   std::vector<int64_t> offsets;  // STRING keys (always int64 here)
+  // STRUCT results (SUM_OVERFLOW): `data` is child 0 (the sum, typed child_type), `data2` child 1 (BOOL8)
+  int32_t child_type = 0;
+  std::vector<uint8_t> data2;
 };
 
 struct Result {
@@ -208,6 +219,7 @@ int32_t result_type(int32_t src, int32_t kind)
       return T_INT64;
     case K_SUMSQ: case K_PRODUCT: return is_float(src) ? src : T_INT64;
     case K_MEAN: return is_duration(src) ? src : T_FLOAT64;
+    case K_SUM_OVERFLOW: return T_STRUCT;  // {sum: src, overflow: BOOL8} (aggregation.hpp:990-995)
     default: return T_FLOAT64;  // M2, VAR, STD
   }
 }
@@ -222,6 +234,8 @@ int check_combo(int32_t src, int32_t kind)
       return (numeric || is_timestamp(src) || is_duration(src) || is_decimal(src) || src == T_STRING) ? 0 : 1;
     case K_SUM: return (numeric || is_duration(src) || is_decimal(src)) ? 0 : 1;  // PRODUCT of decimals throws (sum_tests.cpp:245-246)
     case K_MEAN: return (numeric || is_duration(src)) ? 0 : 1;
+    case K_SUM_OVERFLOW:  // signed integers and decimals (aggregation.hpp:980-988)
+      return (src == T_INT8 || src == T_INT16 || src == T_INT32 || src == T_INT64 || is_decimal(src)) ? 0 : 1;
     case K_SUMSQ: case K_PRODUCT: case K_M2: case K_VAR: case K_STD: return numeric ? 0 : 1;
     default: return 1;
   }
@@ -301,6 +315,7 @@ void aggregate_range(Partial& P, int64_t lo, int64_t hi, const Col* keys, int nk
         else { a.fmin = (v.f < a.fmin) ? v.f : a.fmin; a.fmax = (v.f > a.fmax) ? v.f : a.fmax; }
       } else {
         a.isum = (int64_t)((uint64_t)a.isum + (uint64_t)v.i);
+        a.xsum += (__int128)v.i;
         a.isumsq = (int64_t)((uint64_t)a.isumsq + (uint64_t)v.i * (uint64_t)v.i);
         a.iprod = (int64_t)((uint64_t)a.iprod * (uint64_t)v.i);
         if (first) { a.imin = v.i; a.imax = v.i; }
@@ -326,6 +341,7 @@ void merge_acc(Acc& d, const Acc& s, const Col& vc)
   const bool first = d.count == 0;
   d.count += s.count;
   d.isum = (int64_t)((uint64_t)d.isum + (uint64_t)s.isum);
+  d.xsum += s.xsum;
   d.isumsq = (int64_t)((uint64_t)d.isumsq + (uint64_t)s.isumsq);
   d.iprod = (int64_t)((uint64_t)d.iprod * (uint64_t)s.iprod);
   d.fsum += s.fsum; d.fsumsq += s.fsumsq; d.fprod *= s.fprod;
@@ -486,6 +502,22 @@ Result* run(const Col* keys, int nkeys, int null_policy, const Req* reqs, int nr
         }
         continue;
       }
+      if (kind == K_SUM_OVERFLOW) {
+        // children without masks, values of a null struct 0 / false (sum_overflow_tests.cpp:200-211)
+        const int w = width_of(st);
+        alloc(o, T_STRUCT, G, w, nullable);
+        o.child_type = st;
+        o.data2.assign((size_t)G, 0);
+        for (int64_t g = 0; g < G; ++g) {
+          const Acc& A = P.accs[(size_t)(g * nreqs + q)];
+          if (A.count == 0) { if (nullable) set_null(o, g); continue; }
+          const __int128 lo = -((__int128)1 << (8 * w - 1)), hi = ((__int128)1 << (8 * w - 1)) - 1;
+          const int64_t wrapped = (int64_t)(uint64_t)A.xsum;  // low bits; write_typed narrows
+          write_typed(o, g, st, wrapped, 0);
+          o.data2[(size_t)g] = (A.xsum < lo || A.xsum > hi) ? 1 : 0;
+        }
+        continue;
+      }
       alloc(o, rt, G, width_of(rt), nullable);
       for (int64_t g = 0; g < G; ++g) {
         const Acc& A = P.accs[(size_t)(g * nreqs + q)];
@@ -581,6 +613,10 @@ const uint32_t* orc_col_mask(void* h, int32_t req, int32_t idx)
   auto* c = pick(h, req, idx); return c->mask.empty() ? nullptr : c->mask.data();
 }
 int64_t orc_col_null_count(void* h, int32_t req, int32_t idx) { return pick(h, req, idx)->null_count; }
+// STRUCT results: the type of child 0 (whose bytes orc_col_data returns) and the BOOL8 bytes of child 1
+int32_t orc_col_child_type(void* h, int32_t req, int32_t idx) { return pick(h, req, idx)->child_type; }
+const void* orc_col_data2(void* h, int32_t req, int32_t idx) { return pick(h, req, idx)->data2.data(); }
+int64_t orc_col_bytes2(void* h, int32_t req, int32_t idx) { return (int64_t)pick(h, req, idx)->data2.size(); }
 const int64_t* orc_col_offsets(void* h, int32_t req, int32_t idx)
 {
   auto* c = pick(h, req, idx); return c->offsets.empty() ? nullptr : c->offsets.data();

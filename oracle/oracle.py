@@ -56,7 +56,9 @@ def _lib():
         lib.orc_num_groups.argtypes = [C.c_void_p]
         for name, rt in (("orc_col_type", C.c_int32), ("orc_col_bytes", C.c_int64),
                          ("orc_col_data", C.c_void_p), ("orc_col_mask", C.c_void_p),
-                         ("orc_col_null_count", C.c_int64), ("orc_col_offsets", C.c_void_p)):
+                         ("orc_col_null_count", C.c_int64), ("orc_col_offsets", C.c_void_p),
+                         ("orc_col_child_type", C.c_int32), ("orc_col_data2", C.c_void_p),
+                         ("orc_col_bytes2", C.c_int64)):
             f = getattr(lib, name)
             f.restype = rt
             f.argtypes = [C.c_void_p, C.c_int32, C.c_int32]
@@ -128,6 +130,16 @@ def groupby(keys: Sequence[HostColumn], requests: Sequence[Tuple[HostColumn, Seq
             if mp:
                 nw = (ngroups + 31) // 32
                 mask = np.ctypeslib.as_array((C.c_uint32 * nw).from_address(mp)).copy()
+            if t == TypeId.STRUCT:
+                # SUM_OVERFLOW: children {sum in the source type, overflow flag}, the mask on the struct
+                ct = TypeId(lib.orc_col_child_type(h, req, idx))
+                nb2 = lib.orc_col_bytes2(h, req, idx)
+                flags = np.ctypeslib.as_array((C.c_uint8 * nb2).from_address(lib.orc_col_data2(h, req, idx))).copy() \
+                    if nb2 else np.zeros(0, np.uint8)
+                dec = ct in (TypeId.DECIMAL32, TypeId.DECIMAL64)
+                kids = [HostColumn(ct, int(ngroups), raw.view(STORAGE_DTYPE[ct]), None, 0, None, scale if dec else 0),
+                        HostColumn(TypeId.BOOL8, int(ngroups), flags, None, 0, None, 0)]
+                return HostColumn(t, int(ngroups), None, mask, 0, None, 0, kids)
             if t == TypeId.STRING:
                 op = lib.orc_col_offsets(h, req, idx)
                 offs = np.ctypeslib.as_array((C.c_int64 * (ngroups + 1)).from_address(op)).copy()

@@ -39,10 +39,15 @@ cases = []
 
 
 def case(name, ref, keys, vals, agg, expect_keys, expect_vals, value_types=None, key_type="INT32",
-         null_policy="EXCLUDE", ddof=1, value_type=None, scale=0):
-    cases.append(dict(name=name, ref=ref, key_type=key_type, keys=keys, vals=vals, agg=agg, ddof=ddof,
-                      null_policy=null_policy, expect_keys=expect_keys, expect_vals=expect_vals,
-                      value_types=value_types or [value_type or "INT32"], scale=scale))
+         null_policy="EXCLUDE", ddof=1, value_type=None, scale=0, expect_overflow=None):
+    c = dict(name=name, ref=ref, key_type=key_type, keys=keys, vals=vals, agg=agg, ddof=ddof,
+             null_policy=null_policy, expect_keys=expect_keys, expect_vals=expect_vals,
+             value_types=value_types or [value_type or "INT32"], scale=scale)
+    if expect_overflow is not None:
+        # SUM_OVERFLOW: the struct's children are expect_vals (None = null struct, "?" = a sum the test does
+        # not look at) and these flags
+        c["expect_overflow"] = expect_overflow
+    cases.append(c)
 
 
 def family(agg, file, lines, basic, nullcase, nullvals, value_types, zero_valid_values=None):
@@ -161,6 +166,27 @@ case("KEYS.string_basic", "cpp/tests/groupby/keys_tests.cpp:306",
      ["aaa", "año", "₹1"], [9, 19, 17], key_type="STRING")
 case("COUNT_VALID.string_values", "cpp/tests/groupby/count_tests.cpp:134", [1, 3, 3, 5, 5, 0],
      ["1", "1", "1", "1", "1", "1"], "COUNT_VALID", [0, 1, 3, 5], [1, 1, 2, 2], value_type="STRING")
+
+# SUM_OVERFLOW: a struct {sum in the source type, overflow flag} per group (the DECIMAL128 instances of the
+# typed tests are left out: that type is not served)
+SOVF = "cpp/tests/groupby/sum_overflow_tests.cpp"
+SOVF_TYPES = ["INT8", "INT16", "INT32", "INT64", "DECIMAL32", "DECIMAL64"]
+case("SUM_OVERFLOW.basic", f"{SOVF}:42", K10, V10, "SUM_OVERFLOW", [1, 2, 3], [9, 19, 17], SOVF_TYPES,
+     expect_overflow=[False, False, False])
+case("SUM_OVERFLOW.empty_cols", f"{SOVF}:145", [], [], "SUM_OVERFLOW", [], [], SOVF_TYPES, expect_overflow=[])
+case("SUM_OVERFLOW.zero_valid_keys", f"{SOVF}:167", [None, None, None], [3, 4, 5], "SUM_OVERFLOW", [], [], SOVF_TYPES,
+     expect_overflow=[])
+case("SUM_OVERFLOW.zero_valid_values", f"{SOVF}:190", [1, 1, 1], [None, None, None], "SUM_OVERFLOW", [1], [None],
+     SOVF_TYPES, expect_overflow=[False])
+case("SUM_OVERFLOW.null_keys_and_values", f"{SOVF}:222", K11N, V11_A, "SUM_OVERFLOW", [1, 2, 3, 4], [9, 14, 10, None],
+     SOVF_TYPES, expect_overflow=[False, False, False, False])
+for vt, bits in (("INT8", 8), ("INT16", 16), ("INT32", 32), ("INT64", 64), ("DECIMAL32", 32), ("DECIMAL64", 64)):
+    # type_max - 5, + 10 (group 1); type_max - 5 twice (group 3); type_min + 5, - 10 (group 4): only the flags
+    # are compared there
+    mx, mn = 2 ** (bits - 1) - 1, -(2 ** (bits - 1))
+    case(f"SUM_OVERFLOW.overflow_detection[{vt}]", f"{SOVF}:260", [1, 2, 3, 4, 1, 2, 2, 1, 3, 3, 2, 4, 4],
+         [mx - 5, 10, 20, mn + 5, 10, 20, 30, mx - 5, mx - 5, 1, 40, -10, mn + 5], "SUM_OVERFLOW", [1, 2, 3, 4],
+         ["?", 100, "?", "?"], value_type=vt, expect_overflow=[True, False, True, True])
 
 out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_known_answers.json")
 with open(out, "w", encoding="utf-8") as f:

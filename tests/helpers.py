@@ -8,7 +8,7 @@ from typing import List, Sequence
 
 import numpy as np
 
-from cudf_b200.types import HostColumn, Kind, NullPolicy, STORAGE_DTYPE, TypeId, is_floating, result_type
+from cudf_b200.types import HostColumn, Kind, NullPolicy, STORAGE_DTYPE, TypeId, is_floating, pack_mask, result_type
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_known_answers.json")
 
@@ -119,6 +119,21 @@ def assert_column_equal(got: HostColumn, exp: HostColumn, order_got, order_exp, 
     vg, ve = got.valid()[order_got], exp.valid()[order_exp]
     assert np.array_equal(vg, ve), f"{what}: validity differs at {np.flatnonzero(vg != ve)[:8]}"
     assert got.null_count == exp.null_count, f"{what}: null_count {got.null_count} != {exp.null_count}"
+    if got.type_id == TypeId.STRUCT:   # SUM_OVERFLOW: {sum in the source type, overflow flag}, the mask on the struct
+        assert len(got.children) == 2 and len(exp.children) == 2, f"{what}: a struct of two children"
+        (gs, gf), (es, ef) = got.children, exp.children
+        assert gs.mask is None and gf.mask is None, f"{what}: the children carry no masks"
+        assert TypeId(gs.type_id) == TypeId(es.type_id) and TypeId(gf.type_id) == TypeId.BOOL8, f"{what}: child types"
+        assert gs.scale == es.scale, f"{what}: decimal scale of the sum child differs"
+        assert gs.size == got.size and gf.size == got.size, f"{what}: child sizes"
+        fa, fb = gf.values()[order_got] != 0, ef.values()[order_exp] != 0
+        assert np.array_equal(fa, fb), f"{what}: overflow flags differ at {np.flatnonzero(fa != fb)[:8]}"
+        # the sum of a group that overflowed is not specified by the reference; a null struct holds 0 / false
+        sa, sb = gs.values()[order_got], es.values()[order_exp]
+        cmp = ~fa
+        bad = np.flatnonzero(sa[cmp] != sb[cmp])
+        assert bad.size == 0, f"{what}: {bad.size} sums differ; first {sa[cmp][bad[:8]]} vs {sb[cmp][bad[:8]]}"
+        return
     if got.type_id == TypeId.STRING:   # MIN / MAX of strings
         ga, gb = take(got, order_got), take(exp, order_exp)
         assert ga == gb, f"{what}: {[x for x, y in zip(ga, gb) if x != y][:4]} vs {[y for x, y in zip(ga, gb) if x != y][:4]}"
@@ -203,6 +218,17 @@ def golden_instances(case: dict):
         vals = make_column(case["vals"], vt, scale=scale)
         rt = result_type(TypeId[vt], kind)   # (COUNT and ARGMIN / ARGMAX of strings are INT32, their MIN / MAX strings)
         ekeys = make_column(case["expect_keys"], case["key_type"])
+        if kind == Kind.SUM_OVERFLOW:
+            # a struct: children without masks (0 / false where the struct is null; "?" = a sum the reference's
+            # test does not look at), the validity on the struct
+            ev = case["expect_vals"]
+            sums = make_column([0 if v is None or v == "?" else v for v in ev], vt, scale=scale)
+            flags = HostColumn.from_numpy(np.array(case["expect_overflow"], dtype=np.uint8), type_id=TypeId.BOOL8)
+            valid = np.array([v is not None for v in ev], dtype=bool)
+            evals = HostColumn(TypeId.STRUCT, len(ev), None, None if valid.all() else pack_mask(valid), 0, None, 0,
+                               [sums, flags])
+            yield f'{case["name"]}[{vt}]', keys, vals, kind, case["ddof"], policy, ekeys, evals
+            continue
         evals = make_column(case["expect_vals"], rt.name, scale=scale if rt.name.startswith("DECIMAL") else 0)
         yield f'{case["name"]}[{vt}]', keys, vals, kind, case["ddof"], policy, ekeys, evals
 

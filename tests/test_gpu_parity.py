@@ -364,6 +364,53 @@ def test_float64_mean_keeps_its_sum_as_fixed_point_limbs():
         assert check([wide], [(v, aggs)])[0][0].size == distinct
 
 
+@pytest.mark.parametrize("vtype", ["INT8", "INT16", "INT32", "INT64", "DECIMAL32", "DECIMAL64"])
+def test_sum_overflow_struct_results(vtype):
+    """SUM_OVERFLOW (cpp/tests/groupby/sum_overflow_tests.cpp): a struct {sum in the source type, overflow flag}
+    per group.  Values large enough that some groups leave the source type's range and others do not, null
+    values (groups without a valid value give a null struct), both null policies, beside SUM / MEAN of the same
+    column, on the table paths and the partitioned path; then 5000 groups of ten ones (MultiBlock, :440)."""
+    t = TypeId[vtype]
+    rng = np.random.default_rng(91)
+    n = 300_000
+    dt = np.dtype(H.STORAGE_DTYPE[t])
+    info = np.iinfo(dt)
+    k = HostColumn.from_numpy(rng.integers(0, 3000, n).astype(np.int32), valid=rng.random(n) > 0.02)
+    # ~100 rows per group: magnitudes up to max / 40 overflow in some groups only; one sign per group,
+    # so that every arrival order of the reference gives the same flag
+    sign = np.where((k.values() % 3) == 0, -1, 1)
+    mag = rng.integers(0, int(info.max) // 40, n, dtype=np.int64)
+    x = (sign * mag).astype(dt)
+    valid = rng.random(n) > 0.1
+    valid[k.values() == 17] = False          # a group without a valid value
+    scale = -2 if vtype.startswith("DECIMAL") else 0
+    v = HostColumn.from_numpy(x, valid=valid, type_id=t, scale=scale)
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        for variant in (0, 1, 3, 6):
+            got = check([k], [(v, [Kind.SUM_OVERFLOW, Kind.SUM, Kind.COUNT_VALID])], policy, table_variant=variant)
+            st = got[1][0][0]
+            assert st.type_id == TypeId.STRUCT and st.null_count == 1 and st.children[0].scale == scale
+            flags = st.children[1].values()
+            assert 0 < int(flags.sum()) < flags.size
+    ones = HostColumn.from_numpy(np.ones(50_000, dtype=dt), type_id=t, scale=scale)
+    k5 = HostColumn.from_numpy((np.arange(50_000) % 5000).astype(np.int32))
+    got = check([k5], [(ones, [Kind.SUM_OVERFLOW])])
+    assert (got[1][0][0].children[0].values() == 10).all() and not got[1][0][0].children[1].values().any()
+
+
+def test_sum_overflow_rejects_bool_and_unsigned_values():
+    # cpp/tests/groupby/sum_overflow_tests.cpp:495-561: cudf::logic_error for BOOL8, UINT32, UINT64
+    import cudf_b200 as cb
+    from cudf_b200 import aggregation as agg
+    k = cb.Column.from_host(HostColumn.from_numpy(np.array([1, 1, 1], dtype=np.int32)))
+    gb = cb.GroupBy(cb.Table([k]))
+    for vals in (np.array([True, False, True]), np.array([1, 2, 3], dtype=np.uint32), np.array([1, 2, 3], dtype=np.uint64),
+                 np.array([1.0, 2.0, 3.0])):
+        v = cb.Column.from_host(HostColumn.from_numpy(vals))
+        with pytest.raises(cb.LogicError, match="Invalid type/aggregation combination."):
+            gb.aggregate([cb.GroupByRequest(v, [agg.sum_overflow()])])
+
+
 def test_min_max_with_nan_and_infinity_terminate():
     # cpp/tests/groupby/min_tests.cpp:518-541, max_tests.cpp:526-549: all-NaN groups must not hang
     keys = HostColumn.from_numpy(np.array([1, 1, 2, 2, 2], dtype=np.int32))
