@@ -128,7 +128,9 @@ typedef struct b2_owned_column {
   uint32_t* null_mask; /* NULL when the column is not nullable */
   size_t null_mask_bytes;
   int32_t num_children;
-  struct b2_owned_column* children; /* host array (STRING: children[0] = offsets) */
+  struct b2_owned_column* children; /* host array (STRING: children[0] = offsets; STRUCT, the result of
+                                       SUM_OVERFLOW: children[0] = the sum in the source type, children[1] =
+                                       the BOOL8 overflow flag, the null mask on the struct) */
 } b2_owned_column;
 
 /* Return value of aggregate: std::pair<std::unique_ptr<table>, std::vector<aggregation_result>>
