@@ -50,6 +50,10 @@ class Column:
         offs_t = TypeId.INT32
         if hc.offsets is not None and hc.offsets.dtype == np.int64:
             offs_t = TypeId.INT64
+        if hc.children:  # DICTIONARY32 values: {indices, keys}
+            kids = [Column.from_host(c, device, pinned) for c in hc.children]
+            return Column(hc.type_id, hc.size, None, _to_device(hc.mask, device, pinned), hc.offset,
+                          hc.null_count if hc.mask is not None else 0, children=kids)
         return Column(hc.type_id, hc.size, _to_device(hc.data, device, pinned), _to_device(hc.mask, device, pinned),
                       hc.offset, hc.null_count if hc.mask is not None else 0, _to_device(hc.offsets, device, pinned),
                       offs_t, getattr(hc, "scale", 0))
@@ -105,6 +109,11 @@ class Column:
             keep.append(child)
             v.num_children = 1
             v.children = child
+        elif self.children:
+            kids = (_lib.ColumnView * len(self.children))(*[c.c_view(keep) for c in self.children])
+            keep.append(kids)
+            v.num_children = len(self.children)
+            v.children = kids
         keep.append(self)
         return v
 

@@ -2001,6 +2001,60 @@ b2_status b2_groupby_create(const b2_column_view* keys, int32_t num_keys, int32_
 
 void b2_groupby_destroy(b2_groupby* gb) { delete gb; }
 
+// DICTIONARY32 value columns with fixed-width keys, decoded once into plain columns of the keys' type (the
+// reference resolves the key at every update and produces results of the keys' type:
+// cpp/src/groupby/hash/output_utils.cu:65-66, cpp/tests/groupby/mean_tests.cpp:128-147, max_tests.cpp:226-246).
+// Dictionaries of strings are left as they are (their MIN / MAX are dictionary columns: not served).
+struct DecodedValues {
+  std::vector<b2_aggregation_request> reqs;
+  std::vector<Scratch> bufs;
+};
+const b2_aggregation_request* decode_dictionary_values(const b2_aggregation_request* reqs, int nreqs, cudaStream_t stream,
+                                                       DecodedValues& dv)
+{
+  bool any = false;
+  for (int r = 0; reqs && r < nreqs; ++r) any = any || reqs[r].values.type_id == B2_DICTIONARY32;
+  if (!any) return reqs;
+  dv.reqs.assign(reqs, reqs + nreqs);
+  struct Seen { const void* idx; const void* keys; int off; void* buf; };
+  std::vector<Seen> seen;
+  for (int r = 0; r < nreqs; ++r) {
+    b2_column_view& v = dv.reqs[(size_t)r].values;
+    if (v.type_id != B2_DICTIONARY32) continue;
+    // children {indices, keys} (cpp/include/cudf/dictionary/dictionary_column_view.hpp:56-57)
+    if (v.num_children != 2 || !v.children) B2_FAIL(B2_INVALID_ARGUMENT, "a DICTIONARY32 column needs its indices and keys children");
+    const b2_column_view& ix = v.children[0];
+    const b2_column_view& ky = v.children[1];
+    const int iw = width_of(ix.type_id), w = width_of(ky.type_id);
+    const bool int_index = ix.type_id >= B2_INT8 && ix.type_id <= B2_UINT64;
+    if (!int_index || iw == 0) B2_FAIL(B2_INVALID_ARGUMENT, "dictionary indices must be an integer column");
+    if (w == 0 || ky.type_id == B2_DICTIONARY32) continue;  // string keys: validate_requests reports them
+    void* buf = nullptr;
+    for (const Seen& sn : seen)
+      if (sn.idx == ix.data && sn.keys == ky.data && sn.off == v.offset) buf = sn.buf;
+    if (!buf) {
+      dv.bufs.emplace_back(std::max<size_t>(8, (size_t)((int64_t)v.offset + v.size) * (size_t)w), stream);
+      buf = dv.bufs.back().p;
+      seen.push_back(Seen{ix.data, ky.data, v.offset, buf});
+      if (v.size > 0) {
+        DDictDecode D{};
+        D.indices = (const unsigned char*)ix.data; D.index_width = iw;
+        D.index_signed = ix.type_id >= B2_INT8 && ix.type_id <= B2_INT64;
+        D.index_offset = (i64)v.offset + ix.offset;
+        D.keys = (const unsigned char*)ky.data; D.keys_offset = ky.offset; D.nkeys = ky.size; D.width = w;
+        D.mask = v.null_mask; D.mask_offset = v.offset;
+        D.dst = (unsigned char*)buf + (size_t)v.offset * (size_t)w;
+        k_dict_decode<<<grid_for(v.size, 256, 8), 256, 0, stream>>>(D, (i64)v.size);
+        CUDA_TRY(cudaGetLastError());
+        g_stats.kernel_launches++;
+      }
+    }
+    // the decoded column keeps the dictionary column's mask and element offset
+    v.type_id = ky.type_id; v.scale = ky.scale; v.data = buf; v.num_children = 0; v.children = nullptr;
+  }
+  return dv.reqs.data();
+}
+
 b2_status b2_groupby_aggregate(b2_groupby* gb, const b2_aggregation_request* requests, int32_t num_requests,
                                void* stream, const b2_allocator* allocator, b2_groupby_result* out)
 {
@@ -2010,6 +2064,9 @@ b2_status b2_groupby_aggregate(b2_groupby* gb, const b2_aggregation_request* req
     std::memset(out, 0, sizeof(*out));
     if (gb->keys.empty()) B2_FAIL(B2_LOGIC_ERROR, "groupby needs at least one key column");
     device_info();
+    if (num_requests < 0 || (num_requests > 0 && !requests)) B2_FAIL(B2_INVALID_ARGUMENT, "requests is null");
+    DecodedValues dv;  // (lives until the results are finished)
+    requests = decode_dictionary_values(requests, num_requests, (cudaStream_t)stream, dv);
     validate_requests(*gb, requests, num_requests);
     EncodedKeys ek;
     const b2_groupby& use = encode_string_keys(*gb, (cudaStream_t)stream, ek) ? ek.gb : *gb;

@@ -1102,6 +1102,35 @@ __global__ void k_dict_rows(const u32* __restrict__ ids, const u32* __restrict__
     rows[g] = (id_mask && !bit_valid(id_mask, g)) ? -1 : first_row[ids[g]];
 }
 
+// ------------------------------------------------------------------------------ dictionary values
+// DICTIONARY32 value columns (cpp/include/cudf/detail/aggregation/device_aggregators.cuh:189-220: the reference
+// looks the key up at every update): values[i] = keys[indices[i]] written out once, so that the aggregate passes
+// see a plain column of the keys' type.  Null rows (their index may be anything) are written as zero.
+struct DDictDecode {
+  const unsigned char* indices; int index_width; int index_signed; i64 index_offset;  // element offset of row 0
+  const unsigned char* keys; i64 keys_offset; i64 nkeys; int width;
+  const u32* mask; i64 mask_offset;  // the dictionary column's validity (nullptr = all valid)
+  unsigned char* dst;                // element 0 of the decoded rows
+};
+__global__ void __launch_bounds__(256) k_dict_decode(const DDictDecode D, i64 n)
+{
+  for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (i64)gridDim.x * blockDim.x) {
+    u64 v = 0;
+    if (!D.mask || bit_valid(D.mask, D.mask_offset + i)) {
+      const u64 raw = load_fixed_bits(D.indices, D.index_offset + i, D.index_width);
+      const int sh  = 64 - 8 * D.index_width;
+      const i64 idx = D.index_signed ? ((i64)(raw << sh) >> sh) : (i64)raw;
+      if (idx >= 0 && idx < D.nkeys) v = load_fixed_bits(D.keys, D.keys_offset + idx, D.width);
+    }
+    switch (D.width) {
+      case 1: D.dst[i] = (unsigned char)v; break;
+      case 2: ((unsigned short*)D.dst)[i] = (unsigned short)v; break;
+      case 4: ((u32*)D.dst)[i] = (u32)v; break;
+      default: ((u64*)D.dst)[i] = v; break;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------ finalize
 enum OutKind : int {
   OK_COUNT = 0,  // int32 from a count cell

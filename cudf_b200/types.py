@@ -202,6 +202,23 @@ class HostColumn:
         return HostColumn(type_id, n, values, mask, offset, None, int(scale))
 
     @staticmethod
+    def from_dictionary(values, valid=None, index_type: int = TypeId.INT32, offset: int = 0) -> "HostColumn":
+        """DICTIONARY32 column of fixed-width values: children {indices, sorted unique keys}
+        (cpp/include/cudf/dictionary/dictionary_column_view.hpp:29-57).  The index of a null row is arbitrary."""
+        values = np.ascontiguousarray(values)
+        ok = np.ones(values.size, dtype=bool) if valid is None else np.asarray(valid, dtype=bool)
+        keys = np.unique(values[ok])
+        idx = np.searchsorted(keys, values) if keys.size else np.zeros(values.size, dtype=np.int64)
+        idx = np.where(ok, np.minimum(idx, max(keys.size - 1, 0)), 0)
+        indices = HostColumn.from_numpy(idx.astype(STORAGE_DTYPE[TypeId(index_type)]), type_id=index_type, offset=offset)
+        indices.offset = 0  # the parent's offset applies to the indices (their prefix is padding)
+        indices.size = values.size + offset
+        parent = HostColumn(TypeId.DICTIONARY32, values.size, None,
+                            None if valid is None else pack_mask(ok, offset), offset, None, 0,
+                            [indices, HostColumn.from_numpy(keys)])
+        return parent
+
+    @staticmethod
     def from_strings(strings: Sequence[Optional[str]], large_offsets: bool = False) -> "HostColumn":
         """STRING column from Python strings (None = null), UTF-8 bytes, INT32 or INT64 offsets
         (cpp/include/cudf/strings/strings_column_view.hpp:53)."""

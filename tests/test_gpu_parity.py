@@ -411,6 +411,57 @@ def test_sum_overflow_rejects_bool_and_unsigned_values():
             gb.aggregate([cb.GroupByRequest(v, [agg.sum_overflow()])])
 
 
+def test_dictionary_values_are_looked_up_by_key():
+    """DICTIONARY32 value columns with fixed-width keys: the results are those of the column of looked-up keys, in
+    the keys' type (cpp/include/cudf/detail/aggregation/device_aggregators.cuh:189-220,
+    cpp/src/groupby/hash/output_utils.cu:65-66).  The reference's own vectors (mean_tests.cpp:128-147,
+    max_tests.cpp:226-246, count_tests.cpp:185-207), then nullable and sliced dictionaries with INT8 / INT32 /
+    UINT32 / INT64 indices against the oracle on the decoded column; a dictionary of strings is not served."""
+    import cudf_b200 as cb
+    from cudf_b200 import aggregation as agg
+    k = HostColumn.from_numpy(np.array([1, 2, 3, 1, 2, 2, 1, 3, 3, 2], dtype=np.int32))
+    gk, gr = H.gpu_groupby([k], [(HostColumn.from_dictionary(np.arange(10, dtype=np.int16)), [Kind.MEAN])])
+    order = H.sort_order(gk)
+    assert H.take(gk[0], order) == [1, 2, 3] and H.take(gr[0][0], order) == [9.0 / 3, 19.0 / 4, 17.0 / 3]
+    big = np.array([0xABC, 0xBBB, 0xF1, 0xAAA, 0xFFF, 0xBAA, 0xAAA, 0x01, 0xF1, 0xEEE], dtype=np.int64)
+    gk, gr = H.gpu_groupby([k], [(HostColumn.from_dictionary(big), [Kind.MAX, Kind.MIN])])
+    order = H.sort_order(gk)
+    assert gr[0][0].type_id == TypeId.INT64 and H.take(gr[0][0], order) == [0xABC, 0xFFF, 0xF1]
+    assert H.take(gr[0][1], order) == [0xAAA, 0xBAA, 0x01]
+    sk = HostColumn.from_strings(["1", "3", "3", "5", "5", "0"])
+    gk, gr = H.gpu_groupby([sk], [(HostColumn.from_dictionary(np.ones(6, dtype=np.int32)), [Kind.COUNT_VALID])])
+    order = H.sort_order(gk)
+    assert H.take(gk[0], order) == [b"0", b"1", b"3", b"5"] and H.take(gr[0][0], order) == [1, 1, 2, 2]
+
+    rng = np.random.default_rng(97)
+    n = 200_000
+    keys = HostColumn.from_numpy(rng.integers(0, 500, n).astype(np.int32))
+    pool = rng.standard_normal(120)
+    x = pool[rng.integers(0, pool.size, n)]
+    valid = rng.random(n) > 0.1
+    for index_type, offset in ((TypeId.INT8, 0), (TypeId.INT32, 3), (TypeId.UINT32, 0), (TypeId.INT64, 64)):
+        d = HostColumn.from_dictionary(x, valid=valid, index_type=index_type, offset=offset)
+        plain = HostColumn.from_numpy(x, valid=valid)
+        reqs_d = [(d, ALL_AGGS), (d, [Kind.SUM])]
+        reqs_p = [(plain, ALL_AGGS), (plain, [Kind.SUM])]
+        got = H.gpu_groupby([keys], reqs_d)
+        exp = oracle.groupby([keys], reqs_p)
+        H.assert_same_result(got, exp, reqs_p, scales=H.result_scales([keys], reqs_p, NullPolicy.EXCLUDE))
+    ints = rng.integers(-50, 50, n).astype(np.int32)
+    di = HostColumn.from_dictionary(ints, valid=valid)
+    pi = HostColumn.from_numpy(ints, valid=valid)
+    got = H.gpu_groupby([keys], [(di, [Kind.SUM, Kind.SUM_OVERFLOW, Kind.PRODUCT, Kind.ARGMIN])], table_variant=6)
+    exp = oracle.groupby([keys], [(pi, [Kind.SUM, Kind.SUM_OVERFLOW, Kind.PRODUCT, Kind.ARGMIN])])
+    H.assert_same_result(got, exp, [(pi, [Kind.SUM, Kind.SUM_OVERFLOW, Kind.PRODUCT, Kind.ARGMIN])])
+    # a dictionary of strings: MIN / MAX would be dictionary columns (max_tests.cpp:198-224)
+    words = HostColumn.from_strings(["a", "b"])
+    sd = HostColumn(TypeId.DICTIONARY32, 2, None, None, 0, None, 0,
+                    [HostColumn.from_numpy(np.array([0, 1], dtype=np.int32)), words])
+    kk = cb.Column.from_host(HostColumn.from_numpy(np.array([1, 1], dtype=np.int32)))
+    with pytest.raises(cb.UnsupportedError):
+        cb.GroupBy(cb.Table([kk])).aggregate([cb.GroupByRequest(cb.Column.from_host(sd), [agg.max()])])
+
+
 def test_min_max_with_nan_and_infinity_terminate():
     # cpp/tests/groupby/min_tests.cpp:518-541, max_tests.cpp:526-549: all-NaN groups must not hang
     keys = HostColumn.from_numpy(np.array([1, 1, 2, 2, 2], dtype=np.int32))
