@@ -179,7 +179,11 @@ def test_batchwise_updates_equal_one_shot():
     # (an int64 key with nulls under INCLUDE needs 65 bits: such states are row-keyed and take one update)
     k = HostColumn.from_numpy(rng.integers(0, 5000, n).astype(np.int32), valid=rng.random(n) > 0.02)
     v = HostColumn.from_numpy(rng.standard_normal(n), valid=rng.random(n) > 0.1)
-    reqs = [(v, AGGS)]
+    # SUM_OVERFLOW of a 64-bit column through batches: its two exact-sum cells add up like any other
+    # (some groups of ~60 values of up to 2^58 leave the int64 range, others do not)
+    w = HostColumn.from_numpy(rng.integers(0, 2 ** 58, n, dtype=np.int64) * np.where(k.values() % 2 == 0, 1, -1),
+                              valid=rng.random(n) > 0.1)
+    reqs = [(v, AGGS), (w, [Kind.SUM_OVERFLOW, Kind.COUNT_VALID])]
     for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
         st = None
         for b in range(3):
