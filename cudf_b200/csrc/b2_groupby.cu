@@ -2028,6 +2028,8 @@ const b2_aggregation_request* decode_dictionary_values(const b2_aggregation_requ
     const int iw = width_of(ix.type_id), w = width_of(ky.type_id);
     const bool int_index = ix.type_id >= B2_INT8 && ix.type_id <= B2_UINT64;
     if (!int_index || iw == 0) B2_FAIL(B2_INVALID_ARGUMENT, "dictionary indices must be an integer column");
+    if (ix.size < v.size || (v.size > 0 && !ix.data) || (ky.size > 0 && !ky.data) || ky.size < 0)
+      B2_FAIL(B2_INVALID_ARGUMENT, "dictionary children do not cover the column");
     if (w == 0 || ky.type_id == B2_DICTIONARY32) continue;  // string keys: validate_requests reports them
     void* buf = nullptr;
     for (const Seen& sn : seen)

@@ -60,7 +60,11 @@ constexpr int FX_LIMB_BITS = 18;
 constexpr int FX_LIMBS     = 6;
 constexpr int FX_MAX_SHIFT = FX_LIMB_BITS * (FX_LIMBS - 4) + FX_LIMB_BITS - 1;  // 53: four pieces end in the last word
 constexpr int FX_HEADROOM  = 6;     // the window reaches 2^6 above the sampled maximum
-constexpr u32 FX_FLUSH     = 2048;  // addends of a slot between flushes: (2048 + rows in flight) * 2^18 < 2^31
+// addends of a slot between flushes.  A word holds 2^13 pieces of 18 bits; every thread that takes a multiple of
+// FX_FLUSH empties the slot before it adds anything else, so what can pile up beyond FX_FLUSH is what the other
+// threads of the CTA add meanwhile: the lean kernel's tile ring lets them run at most two tiles (7936 rows)
+// ahead of a stalled warp only if that warp stalls for microseconds; 1024 + 7167 is the room there is.
+constexpr u32 FX_FLUSH     = 1024;
 constexpr int FX_NEVER     = 1 << 20;  // window base with which no value fits (nothing was sampled)
 
 // pieces of |x| in units of 2^(B - 1075), piece i for word q + i; false when x does not fit the window that

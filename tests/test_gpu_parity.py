@@ -323,7 +323,7 @@ def test_float64_mean_keeps_its_sum_as_fixed_point_limbs():
     """Σ and n of one FLOAT64 column over a sampled key box: the lean kernel keeps each partial sum as
     fixed-point limbs whose window comes from the sampled values.  Register tiles (4), the bulk-copy ring (5)
     and auto (0); values far outside the window, zeros, denormals, infinities and NaN (added to the fp64
-    cells directly); a group with many thousand addends per CTA (the limbs are emptied every 2048); nullable
+    cells directly); a group with many thousand addends per CTA (the limbs are emptied every 1024); nullable
     keys under both policies and keys the sample missed; a box that only the generic kernel's table holds
     (8000 keys), and one that neither holds (40000 keys)."""
     rng = np.random.default_rng(83)
