@@ -40,7 +40,9 @@ enum KeyMode : int { KM_PACKED = 0, KM_ROWS = 1 };
 // type classes used on the device (host maps b2_type_id onto these)
 enum ValClass : int {
   VC_I8 = 0, VC_I16, VC_I32, VC_I64, VC_U8, VC_U16, VC_U32, VC_U64, VC_F32, VC_F64, VC_BOOL,
-  VC_STRING, VC_NONE /* only the validity mask is used (COUNT of a non-numeric column) */
+  VC_STRING, VC_NONE /* only the validity mask is used (COUNT of a non-numeric column) */,
+  // the two 64-bit words of a 16-byte element (DECIMAL128 values take two value slots: `data` points at the word)
+  VC_U64X2 /* low word */, VC_I64X2 /* high word */
 };
 
 // accumulator cell operations; the decomposition of the requested aggregations into these follows
@@ -54,7 +56,8 @@ enum CellOp : int {
   OP_ARGMIN, OP_ARGMAX,
   // SUM_OVERFLOW of a 64-bit source: Σ(v >> 32) and Σ(v & 0xFFFFFFFF), each exact in 64 bits for fewer than 2^31
   // rows, so that the finisher knows the exact sum and whether it fits the source type
-  OP_SUM_HI, OP_SUM_LO
+  OP_SUM_HI, OP_SUM_LO,
+  OP_SUM_HIU  // Σ(v >> 32) of an unsigned word (the low word of a DECIMAL128 value)
 };
 __host__ __device__ __forceinline__ bool is_arg_op(int op) { return op == OP_ARGMIN || op == OP_ARGMAX; }
 constexpr unsigned long long ARG_NONE = 0xFFFFFFFFFFFFFFFFull;
@@ -441,6 +444,7 @@ __device__ __forceinline__ u64 load_value(const DValCol& c, i64 row)
     case VC_U32: return (u64)__ldg((const u32*)c.data + idx);
     case VC_F32: return (u64)__double_as_longlong((double)__ldg((const float*)c.data + idx));
     case VC_F64: return __ldg((const u64*)c.data + idx);
+    case VC_U64X2: case VC_I64X2: return __ldg((const u64*)c.data + 2 * idx);
     default: return 0;
   }
 }
@@ -484,6 +488,7 @@ __device__ __forceinline__ void cell_update(u64* cell, int op, u64 v)
     case OP_SUM_I: atomicAdd(cell, v); break;
     case OP_SUM_HI: atomicAdd(cell, (u64)((i64)v >> 32)); break;
     case OP_SUM_LO: atomicAdd(cell, v & 0xFFFFFFFFull); break;
+    case OP_SUM_HIU: atomicAdd(cell, v >> 32); break;
     case OP_SUM_F: atomicAdd((double*)cell, __longlong_as_double((i64)v)); break;
     case OP_SSQ_I: atomicAdd(cell, v * v); break;
     case OP_SSQ_F: { const double d = __longlong_as_double((i64)v); atomicAdd((double*)cell, d * d); break; }
@@ -566,7 +571,7 @@ __device__ inline void arg_update(u64* cell, int op, const DValCol& c, i64 row)
 __device__ __forceinline__ u64 cell_combine(int op, u64 a, u64 b)
 {
   switch (op) {
-    case OP_SUM_I: case OP_SSQ_I: case OP_CNT_V: case OP_CNT_A: case OP_SUM_HI: case OP_SUM_LO: return a + b;
+    case OP_SUM_I: case OP_SSQ_I: case OP_CNT_V: case OP_CNT_A: case OP_SUM_HI: case OP_SUM_LO: case OP_SUM_HIU: return a + b;
     case OP_SUM_F: case OP_SSQ_F:
       return (u64)__double_as_longlong(__longlong_as_double((i64)a) + __longlong_as_double((i64)b));
     case OP_MIN_I: return (i64)a < (i64)b ? a : b;
@@ -585,7 +590,7 @@ __device__ __forceinline__ u64 cell_combine(int op, u64 a, u64 b)
 __device__ __forceinline__ void cell_merge(u64* cell, int op, u64 part)
 {
   switch (op) {
-    case OP_SUM_I: case OP_SSQ_I: case OP_CNT_V: case OP_CNT_A: case OP_SUM_HI: case OP_SUM_LO: atomicAdd(cell, part); break;
+    case OP_SUM_I: case OP_SSQ_I: case OP_CNT_V: case OP_CNT_A: case OP_SUM_HI: case OP_SUM_LO: case OP_SUM_HIU: atomicAdd(cell, part); break;
     case OP_SUM_F: case OP_SSQ_F: atomicAdd((double*)cell, __longlong_as_double((i64)part)); break;
     case OP_MIN_I: atomicMin((i64*)cell, (i64)part); break;
     case OP_MIN_U: case OP_MIN_F: atomicMin(cell, part); break;

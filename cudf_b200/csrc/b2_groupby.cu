@@ -152,6 +152,9 @@ bool is_timestamp_t(int t) { return t >= B2_TIMESTAMP_DAYS && t <= B2_TIMESTAMP_
 bool is_numeric_t(int t) { return t >= B2_INT8 && t <= B2_BOOL8; }
 // DECIMAL32/64 are served as their integer representation + scale; DECIMAL128 is not (no 16-byte atomics here)
 bool is_decimal_t(int t) { return t == B2_DECIMAL32 || t == B2_DECIMAL64; }
+// DECIMAL128 values: SUM and SUM_OVERFLOW only, like the reference's hash path (cpp/src/groupby/hash/groupby.cu:82-85);
+// a column takes two value slots, its low and its high words.  The second slot carries this internal type.
+constexpr int VT_DEC128_HIGH = 1000;
 
 int width_of(int t)
 {
@@ -181,6 +184,8 @@ int vclass_of(int t)
     case B2_FLOAT64: return VC_F64;
     case B2_BOOL8: return VC_BOOL;
     case B2_STRING: return VC_STRING;
+    case B2_DECIMAL128: return VC_U64X2;
+    case VT_DEC128_HIGH: return VC_I64X2;
     default: return width_of(t) == 8 ? VC_I64 : VC_NONE;
   }
 }
@@ -191,7 +196,7 @@ int result_type(int src, int kind)
   switch (kind) {
     case B2_AGG_COUNT_VALID: case B2_AGG_COUNT_ALL: case B2_AGG_ARGMAX: case B2_AGG_ARGMIN: return B2_INT32;
     case B2_AGG_MIN: case B2_AGG_MAX: return src;
-    case B2_AGG_SUM: return (is_float_t(src) || is_duration_t(src) || is_decimal_t(src)) ? src : B2_INT64;  // decimals keep type and scale
+    case B2_AGG_SUM: return (is_float_t(src) || is_duration_t(src) || is_decimal_t(src) || src == B2_DECIMAL128) ? src : B2_INT64;  // decimals keep type and scale
     case B2_AGG_SUM_OVERFLOW: return B2_STRUCT;  // {sum: the source type, overflow: BOOL8} (aggregation.hpp:990-995)
     case B2_AGG_SUM_OF_SQUARES: case B2_AGG_PRODUCT: return is_float_t(src) ? src : B2_INT64;
     case B2_AGG_MEAN: return is_duration_t(src) ? src : B2_FLOAT64;
@@ -214,14 +219,15 @@ int classify_request(int src, int kind)
     case B2_AGG_SUM:
       // decimal SUM / MIN / MAX run on the hash path of the reference too
       // (cpp/tests/groupby/sum_tests.cpp:220-248, min_tests.cpp:271-292, max_tests.cpp:279-300)
-      if (is_numeric_t(src) || is_duration_t(src) || is_decimal_t(src)) return 0;
-      if (src == B2_DECIMAL128 || src == B2_DICTIONARY32) return 2;
+      if (is_numeric_t(src) || is_duration_t(src) || is_decimal_t(src) || src == B2_DECIMAL128) return 0;
+      if (src == B2_DICTIONARY32) return 2;
       return 1;
     case B2_AGG_SUM_OVERFLOW:
       // signed integers and decimals (cpp/include/cudf/detail/aggregation/aggregation.hpp:980-995,
       // cpp/tests/groupby/sum_overflow_tests.cpp:495-561: BOOL8 and the unsigned types throw)
-      if (src == B2_INT8 || src == B2_INT16 || src == B2_INT32 || src == B2_INT64 || is_decimal_t(src)) return 0;
-      if (src == B2_DECIMAL128) return 2;
+      if (src == B2_INT8 || src == B2_INT16 || src == B2_INT32 || src == B2_INT64 || is_decimal_t(src) ||
+          src == B2_DECIMAL128)
+        return 0;
       return 1;
     case B2_AGG_MEAN:
       if (is_numeric_t(src) || is_duration_t(src)) return 0;
@@ -418,6 +424,12 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
       seen.push_back(VKey{v.data, v.null_mask, v.offset, v.type_id});
       need.emplace_back();
       sc.val_types[slot] = v.type_id;
+      if (v.type_id == B2_DECIMAL128) {  // the slot of the high words follows
+        if ((int)seen.size() >= MAX_VALS) B2_FAIL(B2_UNSUPPORTED, "more than 16 distinct value columns");
+        seen.push_back(VKey{nullptr, nullptr, -1, VT_DEC128_HIGH});
+        need.emplace_back();
+        sc.val_types[slot + 1] = VT_DEC128_HIGH;
+      }
     }
     sc.req_val[(size_t)r] = slot;
     Need& nd = need[(size_t)slot];
@@ -428,7 +440,9 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
         case B2_AGG_SUM: nd.sum = true; break;
         // SUM_OVERFLOW: sources of up to 32 bits share the int64 Σ cell of SUM (it cannot wrap below 2^31 rows);
         // a 64-bit source gets two cells that hold its exact sum
-        case B2_AGG_SUM_OVERFLOW: if (width_of(v.type_id) == 8) nd.ovf8 = true; else nd.sum = true; break;
+        case B2_AGG_SUM_OVERFLOW:
+          if (width_of(v.type_id) == 8) nd.ovf8 = true; else nd.sum = true;  // (DECIMAL128: the four cells of its SUM)
+          break;
         case B2_AGG_COUNT_VALID: nd.cnt = true; break;
         case B2_AGG_COUNT_ALL: need_cnt_all = true; break;
         case B2_AGG_MIN: if (v.type_id == B2_STRING) nd.amin = true; else nd.mn = true; break;
@@ -460,7 +474,15 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
     if (nd.nulls && (nd.sum || nd.ssq || nd.mn || nd.mx || nd.prod || nd.ovf8)) nd.cnt = true;  // decides validity
     if (nd.amin) { idx[(size_t)s].amin = add_cell(OP_ARGMIN, s); sc.has_arg = true; }
     if (nd.amax) { idx[(size_t)s].amax = add_cell(OP_ARGMAX, s); sc.has_arg = true; }
-    if (nd.sum) idx[(size_t)s].sum = add_cell(f ? OP_SUM_F : OP_SUM_I, s);
+    if (nd.sum && t == B2_DECIMAL128) {
+      // four exact chunk sums over the two word slots, adjacent and in this order (sum128 on the device)
+      idx[(size_t)s].sum = add_cell(OP_SUM_LO, s);
+      add_cell(OP_SUM_HIU, s);
+      add_cell(OP_SUM_LO, s + 1);
+      add_cell(OP_SUM_HI, s + 1);
+    } else if (nd.sum) {
+      idx[(size_t)s].sum = add_cell(f ? OP_SUM_F : OP_SUM_I, s);
+    }
     if (nd.cnt) idx[(size_t)s].cnt = add_cell(OP_CNT_V, s);
     if (nd.ssq) idx[(size_t)s].ssq = add_cell(f ? OP_SSQ_F : OP_SSQ_I, s);
     if (nd.mn) idx[(size_t)s].mn = add_cell(f ? OP_MIN_F : uns ? OP_MIN_U : OP_MIN_I, s);
@@ -485,7 +507,7 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
       o.req = r; o.agg = a;
       const int kind = reqs[r].aggregations[a].kind;
       o.rtype = result_type(t, kind);
-      o.scale = is_decimal_t(o.rtype) ? reqs[r].values.scale : 0;
+      o.scale = (is_decimal_t(o.rtype) || o.rtype == B2_DECIMAL128) ? reqs[r].values.scale : 0;
       o.ddof = reqs[r].aggregations[a].ddof;
       o.src_float = f;
       o.c_cnt = has_nulls ? ci.cnt : -1;
@@ -494,10 +516,10 @@ Schema make_schema(const b2_groupby& gb, const b2_aggregation_request* reqs, int
         case B2_AGG_COUNT_VALID: o.kind = OK_COUNT; o.c_a = ci.cnt; o.c_cnt = -1; o.nullable = false; break;
         case B2_AGG_COUNT_ALL: o.kind = OK_COUNT; o.c_a = cnt_all; o.c_cnt = -1; o.nullable = false; break;
         case B2_AGG_SUM_OVERFLOW:
-          o.kind = OK_SUMOVF; o.ctype = t; o.scale = is_decimal_t(t) ? reqs[r].values.scale : 0;
+          o.kind = OK_SUMOVF; o.ctype = t; o.scale = (is_decimal_t(t) || t == B2_DECIMAL128) ? reqs[r].values.scale : 0;
           if (width_of(t) == 8) { o.c_a = ci.hi; o.c_b = ci.lo; } else { o.c_a = ci.sum; }
           break;
-        case B2_AGG_SUM: o.kind = f ? OK_FLT : OK_INT; o.c_a = ci.sum; break;
+        case B2_AGG_SUM: o.kind = t == B2_DECIMAL128 ? OK_SUM128 : f ? OK_FLT : OK_INT; o.c_a = ci.sum; break;
         case B2_AGG_SUM_OF_SQUARES: o.kind = f ? OK_FLT : OK_INT; o.c_a = ci.ssq; break;
         case B2_AGG_PRODUCT: o.kind = f ? OK_FLT : OK_INT; o.c_a = ci.prod; break;
         case B2_AGG_MIN:
@@ -584,6 +606,12 @@ void bind_plan_inputs(DPlan& P, const Schema& sc, const b2_groupby& gb, const b2
     P.vals[s].offset = v.offset;
     P.vals[s].offsets = nullptr;
     P.vals[s].offs64 = 0;
+    if (v.type_id == B2_DECIMAL128) {  // the high words: the same rows, 8 bytes further
+      P.vals[s + 1] = P.vals[s];
+      P.vals[s + 1].data = v.data ? (const unsigned char*)v.data + 8 : nullptr;
+      P.vals[s + 1].vclass = VC_I64X2;
+      bound[(size_t)s + 1] = true;
+    }
     if (v.type_id == B2_STRING) {
       if (v.size > 0 && (v.num_children < 1 || !v.children ||
                          (v.children[0].type_id != B2_INT32 && v.children[0].type_id != B2_INT64)))
@@ -1388,7 +1416,7 @@ void init_owned(b2_owned_column& c, int type_id, int64_t n, bool nullable, const
   std::memset(&c, 0, sizeof(c));
   c.type_id = type_id;
   c.size = (int32_t)n;
-  const int w = width_of(type_id);
+  const int w = type_id == B2_DECIMAL128 ? 16 : width_of(type_id);
   if (w > 0) {
     // results narrower than 4 bytes are padded to whole words like the reference's
     // (cpp/src/groupby/hash/output_utils.cu:71-82)
@@ -1883,6 +1911,7 @@ extern "C" b2_status b2_groupby_aggregate_noalloc(b2_groupby* gb, const b2_aggre
     for (const OutSpec& o : sc.outs) {
       if (o.kind == OK_STRARG) B2_FAIL(B2_UNSUPPORTED, "the no-allocation variant does not serve MIN / MAX of strings (their size is not known in advance)");
       if (o.kind == OK_SUMOVF) B2_FAIL(B2_UNSUPPORTED, "the no-allocation variant does not serve SUM_OVERFLOW (a struct result)");
+      if (o.kind == OK_SUM128) B2_FAIL(B2_UNSUPPORTED, "the no-allocation variant does not serve DECIMAL128 values");
     }
     DPlan P;
     fill_plan_schema(P, sc);

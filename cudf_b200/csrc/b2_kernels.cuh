@@ -1144,7 +1144,8 @@ enum OutKind : int {
   OK_MEAN, OK_M2, OK_VAR, OK_STD,
   OK_ARG,        // ARGMIN / ARGMAX: the row held by the cell as INT32, null when none
   OK_STRARG,     // MIN / MAX of strings: the row (or -1) into a scratch array the host gathers the strings by
-  OK_SUMOVF      // SUM_OVERFLOW: the sum in the source type into `data`, "the exact sum does not fit it" into `data2`
+  OK_SUMOVF,     // SUM_OVERFLOW: the sum in the source type into `data`, "the exact sum does not fit it" into `data2`
+  OK_SUM128      // SUM of DECIMAL128: 16-byte elements from the four exact-sum cells c_a .. c_a + 3
 };
 
 struct DOutCol {
@@ -1195,6 +1196,18 @@ __device__ __forceinline__ void clear_bit(u32* mask, i64 g, u32* counter)
   atomicAdd(counter, 1u);
 }
 
+// The sum of a DECIMAL128 column from its four exact cells {Σ(lo & 0xFFFFFFFF), Σ(lo >> 32), Σ(hi & 0xFFFFFFFF),
+// Σ(hi >> 32, signed)} (cell i at c[i * cstep]; each exact below 2^31 rows): the low and high words of the sum
+// modulo 2^128, and whether the exact sum leaves the 128-bit range.
+__device__ __forceinline__ bool sum128(const u64* c, i64 cstep, u64& lo, u64& hi)
+{
+  const unsigned __int128 a = (unsigned __int128)c[0] + ((unsigned __int128)c[cstep] << 32);                  // < 2^96
+  const __int128 b = (__int128)c[2 * cstep] + (__int128)(i64)c[3 * cstep] * ((__int128)1 << 32) + (__int128)(u64)(a >> 64);
+  lo = (u64)a;
+  hi = (u64)b;
+  return b < -((__int128)1 << 63) || b > (((__int128)1 << 63) - 1);
+}
+
 // One finished group -> output row g: key columns decoded from the key cell (packed keys) or the
 // representative row noted (row keys), then every requested aggregation from the accumulator cells
 // (cell c at cells[c * cstep]): COUNT as INT32, MEAN = Σx / n, M2 = Σx² − (Σx)²/n, VAR = M2 / (n − ddof),
@@ -1240,6 +1253,14 @@ __device__ __forceinline__ void write_group(const DPlan& P, const DOutPlan& O, u
         // sign, and what the order that alternates signs gives otherwise.
         bool ovf = false;
         u64 sum  = 0;
+        if (oc.rclass == VC_U64X2) {  // DECIMAL128
+          u64 lo = 0, hi = 0;
+          if (valid) ovf = sum128(cells + (i64)(oc.c_a) * cstep, cstep, lo, hi);
+          ((u64*)oc.data)[2 * g] = lo;
+          ((u64*)oc.data)[2 * g + 1] = hi;
+          ((unsigned char*)oc.data2)[g] = ovf ? 1 : 0;
+          break;
+        }
         if (valid) {
           if (oc.c_b >= 0) {
             const u64 lo = cells[(i64)(oc.c_b) * cstep];
@@ -1255,6 +1276,13 @@ __device__ __forceinline__ void write_group(const DPlan& P, const DOutPlan& O, u
         }
         store_int(oc.data, g, oc.rclass, sum);
         ((unsigned char*)oc.data2)[g] = ovf ? 1 : 0;
+        break;
+      }
+      case OK_SUM128: {
+        u64 lo = 0, hi = 0;
+        if (valid) sum128(cells + (i64)(oc.c_a) * cstep, cstep, lo, hi);
+        ((u64*)oc.data)[2 * g] = lo;
+        ((u64*)oc.data)[2 * g + 1] = hi;
         break;
       }
       case OK_MEAN: {

@@ -85,7 +85,25 @@ STORAGE_DTYPE = {
     TypeId.DURATION_MILLISECONDS: np.int64, TypeId.DURATION_MICROSECONDS: np.int64,
     TypeId.DURATION_NANOSECONDS: np.int64,
     TypeId.DECIMAL32: np.int32, TypeId.DECIMAL64: np.int64,
+    # a 16-byte two's-complement integer, little endian: the unsigned low word, then the signed high word
+    TypeId.DECIMAL128: np.dtype([("lo", "<u8"), ("hi", "<i8")]),
 }
+
+
+def int128_array(values) -> np.ndarray:
+    """Python integers -> an array of the DECIMAL128 storage type (values wrap modulo 2^128)."""
+    out = np.zeros(len(values), dtype=STORAGE_DTYPE[TypeId.DECIMAL128])
+    for i, v in enumerate(values):
+        u = int(v) & ((1 << 128) - 1)
+        out["lo"][i] = u & 0xFFFFFFFFFFFFFFFF
+        hi = u >> 64
+        out["hi"][i] = hi - (1 << 64) if hi >= (1 << 63) else hi
+    return out
+
+
+def int128_list(arr: np.ndarray) -> list:
+    """The Python integers of an array of the DECIMAL128 storage type."""
+    return [(int(h) << 64) + int(l) for l, h in zip(arr["lo"].tolist(), arr["hi"].tolist())]
 
 _NUMPY_TO_TYPE = {
     np.dtype(np.int8): TypeId.INT8, np.dtype(np.int16): TypeId.INT16,

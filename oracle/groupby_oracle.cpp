@@ -85,6 +85,7 @@ int width_of(int32_t t)
     case T_INT32: case T_UINT32: case T_FLOAT32: case T_TS_DAYS: case T_DUR_DAYS: case T_DEC32: return 4;
     case T_INT64: case T_UINT64: case T_FLOAT64: case T_TS_S: case T_TS_MS: case T_TS_US:
     case T_TS_NS: case T_DUR_S: case T_DUR_MS: case T_DUR_US: case T_DUR_NS: case T_DEC64: return 8;
+    case T_DEC128: return 16;
     default: return 0;
   }
 }
@@ -94,11 +95,11 @@ bool is_timestamp(int32_t t) { return t >= T_TS_DAYS && t <= T_TS_NS; }
 bool is_decimal(int32_t t) { return t == T_DEC32 || t == T_DEC64; }
 
 // value of element i as (int64 bit pattern | double)
-struct Val { int64_t i; double f; };
+struct Val { int64_t i; double f; unsigned __int128 w; };  // w: a DECIMAL128 element (two's complement)
 inline Val load(const Col& c, int64_t r)
 {
   const int64_t k = (int64_t)c.offset + r;
-  Val v{0, 0.0};
+  Val v{0, 0.0, 0};
   switch (c.type_id) {
     case T_INT8: v.i = ((const int8_t*)c.data)[k]; break;
     case T_INT16: v.i = ((const int16_t*)c.data)[k]; break;
@@ -112,6 +113,7 @@ inline Val load(const Col& c, int64_t r)
     case T_UINT64: v.i = (int64_t)((const uint64_t*)c.data)[k]; break;
     case T_FLOAT32: v.f = ((const float*)c.data)[k]; break;
     case T_FLOAT64: v.f = ((const double*)c.data)[k]; break;
+    case T_DEC128: std::memcpy(&v.w, (const char*)c.data + k * 16, 16); break;
     default: break;
   }
   return v;
@@ -169,6 +171,10 @@ struct Acc {  // per (group, request): every simple accumulator the supported ki
   // the values of a group share a sign (the reference's tests, cpp/tests/groupby/sum_overflow_tests.cpp:260-378),
   // and the flag of the order that alternates signs otherwise; the sum of a flagged group is not specified there.
   __int128 xsum = 0;
+  // DECIMAL128: Σ of the low words and Σ of the (signed) high words, each exact; the sum is their combination
+  // modulo 2^128 like the reference's __int128 adds, and it left the range iff hi128 + (lo128 >> 64) is no int64
+  unsigned __int128 lo128 = 0;
+  __int128 hi128 = 0;
 };
 
 struct Group {
@@ -215,7 +221,7 @@ int32_t result_type(int32_t src, int32_t kind)
     case K_MIN: case K_MAX: return src;
     case K_SUM:
       // fixed point sums keep their type (aggregation.hpp:956-963): a DECIMAL32 sum wraps at 32 bits
-      if (is_float(src) || is_duration(src) || is_decimal(src)) return src;
+      if (is_float(src) || is_duration(src) || is_decimal(src) || src == T_DEC128) return src;
       return T_INT64;
     case K_SUMSQ: case K_PRODUCT: return is_float(src) ? src : T_INT64;
     case K_MEAN: return is_duration(src) ? src : T_FLOAT64;
@@ -232,10 +238,12 @@ int check_combo(int32_t src, int32_t kind)
     case K_COUNT_VALID: case K_COUNT_ALL: return 0;
     case K_MIN: case K_MAX: case K_ARGMIN: case K_ARGMAX:
       return (numeric || is_timestamp(src) || is_duration(src) || is_decimal(src) || src == T_STRING) ? 0 : 1;
-    case K_SUM: return (numeric || is_duration(src) || is_decimal(src)) ? 0 : 1;  // PRODUCT of decimals throws (sum_tests.cpp:245-246)
+    // PRODUCT of decimals throws (sum_tests.cpp:245-246); DECIMAL128 sums run on the hash path
+    // (cpp/src/groupby/hash/groupby.cu:82-85), its other aggregations on the sort path (not restated here)
+    case K_SUM: return (numeric || is_duration(src) || is_decimal(src) || src == T_DEC128) ? 0 : 1;
     case K_MEAN: return (numeric || is_duration(src)) ? 0 : 1;
     case K_SUM_OVERFLOW:  // signed integers and decimals (aggregation.hpp:980-988)
-      return (src == T_INT8 || src == T_INT16 || src == T_INT32 || src == T_INT64 || is_decimal(src)) ? 0 : 1;
+      return (src == T_INT8 || src == T_INT16 || src == T_INT32 || src == T_INT64 || is_decimal(src) || src == T_DEC128) ? 0 : 1;
     case K_SUMSQ: case K_PRODUCT: case K_M2: case K_VAR: case K_STD: return numeric ? 0 : 1;
     default: return 1;
   }
@@ -306,7 +314,10 @@ void aggregate_range(Partial& P, int64_t lo, int64_t hi, const Col* keys, int nk
       const Val v = load(vc, r);
       const bool first = a.count == 0;
       a.count++;
-      if (is_float(vc.type_id)) {
+      if (vc.type_id == T_DEC128) {
+        a.lo128 += (unsigned __int128)(uint64_t)v.w;
+        a.hi128 += (__int128)(int64_t)(uint64_t)(v.w >> 64);
+      } else if (is_float(vc.type_id)) {
         a.fsum += v.f;
         a.fsumsq += (long double)v.f * (long double)v.f;
         a.fprod *= v.f;
@@ -342,6 +353,8 @@ void merge_acc(Acc& d, const Acc& s, const Col& vc)
   d.count += s.count;
   d.isum = (int64_t)((uint64_t)d.isum + (uint64_t)s.isum);
   d.xsum += s.xsum;
+  d.lo128 += s.lo128;
+  d.hi128 += s.hi128;
   d.isumsq = (int64_t)((uint64_t)d.isumsq + (uint64_t)s.isumsq);
   d.iprod = (int64_t)((uint64_t)d.iprod * (uint64_t)s.iprod);
   d.fsum += s.fsum; d.fsumsq += s.fsumsq; d.fprod *= s.fprod;
@@ -511,6 +524,13 @@ Result* run(const Col* keys, int nkeys, int null_policy, const Req* reqs, int nr
         for (int64_t g = 0; g < G; ++g) {
           const Acc& A = P.accs[(size_t)(g * nreqs + q)];
           if (A.count == 0) { if (nullable) set_null(o, g); continue; }
+          if (st == T_DEC128) {
+            const __int128 top = A.hi128 + (__int128)(uint64_t)(A.lo128 >> 64);
+            const unsigned __int128 sum = ((unsigned __int128)(uint64_t)top << 64) | (uint64_t)A.lo128;
+            std::memcpy(o.data.data() + g * 16, &sum, 16);
+            o.data2[(size_t)g] = (top < -((__int128)1 << 63) || top > (((__int128)1 << 63) - 1)) ? 1 : 0;
+            continue;
+          }
           const __int128 lo = -((__int128)1 << (8 * w - 1)), hi = ((__int128)1 << (8 * w - 1)) - 1;
           const int64_t wrapped = (int64_t)(uint64_t)A.xsum;  // low bits; write_typed narrows
           write_typed(o, g, st, wrapped, 0);
@@ -527,6 +547,12 @@ Result* run(const Col* keys, int nkeys, int null_policy, const Req* reqs, int nr
           case K_COUNT_ALL: put<int32_t>(o, g, (int32_t)P.groups[(size_t)g].rows); break;
           case K_SUM:
             if (cnt == 0) { if (nullable) set_null(o, g); break; }
+            if (rt == T_DEC128) {
+              const __int128 top = A.hi128 + (__int128)(uint64_t)(A.lo128 >> 64);
+              const unsigned __int128 sum = ((unsigned __int128)(uint64_t)top << 64) | (uint64_t)A.lo128;
+              std::memcpy(o.data.data() + g * 16, &sum, 16);
+              break;
+            }
             write_typed(o, g, rt, A.isum, A.fsum); break;
           case K_SUMSQ:
             if (cnt == 0) { if (nullable) set_null(o, g); break; }

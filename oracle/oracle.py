@@ -136,7 +136,7 @@ def groupby(keys: Sequence[HostColumn], requests: Sequence[Tuple[HostColumn, Seq
                 nb2 = lib.orc_col_bytes2(h, req, idx)
                 flags = np.ctypeslib.as_array((C.c_uint8 * nb2).from_address(lib.orc_col_data2(h, req, idx))).copy() \
                     if nb2 else np.zeros(0, np.uint8)
-                dec = ct in (TypeId.DECIMAL32, TypeId.DECIMAL64)
+                dec = ct in (TypeId.DECIMAL32, TypeId.DECIMAL64, TypeId.DECIMAL128)
                 kids = [HostColumn(ct, int(ngroups), raw.view(STORAGE_DTYPE[ct]), None, 0, None, scale if dec else 0),
                         HostColumn(TypeId.BOOL8, int(ngroups), flags, None, 0, None, 0)]
                 return HostColumn(t, int(ngroups), None, mask, 0, None, 0, kids)
@@ -145,7 +145,7 @@ def groupby(keys: Sequence[HostColumn], requests: Sequence[Tuple[HostColumn, Seq
                 offs = np.ctypeslib.as_array((C.c_int64 * (ngroups + 1)).from_address(op)).copy()
                 return HostColumn(t, int(ngroups), raw, mask, 0, offs)
             # decimal columns (keys, SUM / MIN / MAX results) keep the scale of their source
-            dec = t in (TypeId.DECIMAL32, TypeId.DECIMAL64)
+            dec = t in (TypeId.DECIMAL32, TypeId.DECIMAL64, TypeId.DECIMAL128)
             return HostColumn(t, int(ngroups), raw.view(STORAGE_DTYPE[t]), mask, 0, None, scale if dec else 0)
 
         out_keys = [fetch(-1, i, getattr(keys[i], "scale", 0)) for i in range(len(keys))]

@@ -122,11 +122,12 @@ family("PRODUCT", "cpp/tests/groupby/product_tests.cpp", [24, 47, 66, 85, 104], 
        [18, 36, 16, None], V11_D, NUMERIC)
 
 # fixed point values on the hash path: the representation is aggregated, type and scale are kept
-# (TYPED over decimal32/64/128 and scales 2..-2 in the reference; 128-bit is not served here)
+# (TYPED over decimal32/64/128 and scales 2..-2 in the reference; of the 128-bit instances the SUM runs on the
+# reference's hash path, cpp/src/groupby/hash/groupby.cu:82-85, MIN and MAX on its sort path)
 DECIMALS = ["DECIMAL32", "DECIMAL64"]
 for sc in (2, 1, 0, -1, -2):
     case(f"SUM.decimal_hash[scale={sc}]", "cpp/tests/groupby/sum_tests.cpp:220", K10, V10, "SUM", [1, 2, 3],
-         [9, 19, 17], DECIMALS, scale=sc)
+         [9, 19, 17], DECIMALS + ["DECIMAL128"], scale=sc)
     case(f"MIN.decimal_hash[scale={sc}]", "cpp/tests/groupby/min_tests.cpp:271", K10, V10, "MIN", [1, 2, 3],
          [0, 1, 2], DECIMALS, scale=sc)
     case(f"MAX.decimal_hash[scale={sc}]", "cpp/tests/groupby/max_tests.cpp:279", K10, V10, "MAX", [1, 2, 3],
@@ -167,10 +168,9 @@ case("KEYS.string_basic", "cpp/tests/groupby/keys_tests.cpp:306",
 case("COUNT_VALID.string_values", "cpp/tests/groupby/count_tests.cpp:134", [1, 3, 3, 5, 5, 0],
      ["1", "1", "1", "1", "1", "1"], "COUNT_VALID", [0, 1, 3, 5], [1, 1, 2, 2], value_type="STRING")
 
-# SUM_OVERFLOW: a struct {sum in the source type, overflow flag} per group (the DECIMAL128 instances of the
-# typed tests are left out: that type is not served)
+# SUM_OVERFLOW: a struct {sum in the source type, overflow flag} per group
 SOVF = "cpp/tests/groupby/sum_overflow_tests.cpp"
-SOVF_TYPES = ["INT8", "INT16", "INT32", "INT64", "DECIMAL32", "DECIMAL64"]
+SOVF_TYPES = ["INT8", "INT16", "INT32", "INT64", "DECIMAL32", "DECIMAL64", "DECIMAL128"]
 case("SUM_OVERFLOW.basic", f"{SOVF}:42", K10, V10, "SUM_OVERFLOW", [1, 2, 3], [9, 19, 17], SOVF_TYPES,
      expect_overflow=[False, False, False])
 case("SUM_OVERFLOW.empty_cols", f"{SOVF}:145", [], [], "SUM_OVERFLOW", [], [], SOVF_TYPES, expect_overflow=[])
@@ -180,7 +180,8 @@ case("SUM_OVERFLOW.zero_valid_values", f"{SOVF}:190", [1, 1, 1], [None, None, No
      SOVF_TYPES, expect_overflow=[False])
 case("SUM_OVERFLOW.null_keys_and_values", f"{SOVF}:222", K11N, V11_A, "SUM_OVERFLOW", [1, 2, 3, 4], [9, 14, 10, None],
      SOVF_TYPES, expect_overflow=[False, False, False, False])
-for vt, bits in (("INT8", 8), ("INT16", 16), ("INT32", 32), ("INT64", 64), ("DECIMAL32", 32), ("DECIMAL64", 64)):
+for vt, bits in (("INT8", 8), ("INT16", 16), ("INT32", 32), ("INT64", 64), ("DECIMAL32", 32), ("DECIMAL64", 64),
+                 ("DECIMAL128", 128)):
     # type_max - 5, + 10 (group 1); type_max - 5 twice (group 3); type_min + 5, - 10 (group 4): only the flags
     # are compared there
     mx, mn = 2 ** (bits - 1) - 1, -(2 ** (bits - 1))

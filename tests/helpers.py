@@ -8,7 +8,8 @@ from typing import List, Sequence
 
 import numpy as np
 
-from cudf_b200.types import HostColumn, Kind, NullPolicy, STORAGE_DTYPE, TypeId, is_floating, pack_mask, result_type
+from cudf_b200.types import (HostColumn, Kind, NullPolicy, STORAGE_DTYPE, TypeId, int128_array, is_floating, pack_mask,
+                             result_type)
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_known_answers.json")
 
@@ -68,7 +69,12 @@ def make_column(values: Sequence, type_name: str, offset: int = 0, scale: int = 
     if t == TypeId.STRING:
         return HostColumn.from_strings(list(values))
     filled = [0 if v is None else _num(v) for v in values]
-    arr = np.array(filled, dtype=np.float64 if is_floating(t) else np.int64).astype(STORAGE_DTYPE[t])
+    if t == TypeId.DECIMAL128:
+        arr = int128_array(filled)
+    elif is_floating(t) or all(-2 ** 63 <= v < 2 ** 63 for v in filled):
+        arr = np.array(filled, dtype=np.float64 if is_floating(t) else np.int64).astype(STORAGE_DTYPE[t])
+    else:  # a value outside int64 (a 128-bit extreme listed for a narrower type never is)
+        arr = np.array([v & (2 ** 64 - 1) for v in filled], dtype=np.uint64).astype(STORAGE_DTYPE[t])
     return HostColumn.from_numpy(arr, None if valid.all() and len(values) else (valid if len(values) else None),
                                  type_id=t, offset=offset, scale=scale)
 
@@ -263,7 +269,7 @@ def result_scales(keys, requests, null_policy, row_filters=(), row_filter_offset
     from oracle import oracle
     reqs = []
     for vals, _ in requests:
-        if vals.type_id == TypeId.STRING or vals.type_id not in STORAGE_DTYPE:
+        if vals.type_id in (TypeId.STRING, TypeId.DECIMAL128) or vals.type_id not in STORAGE_DTYPE:
             x = np.zeros(vals.size)
         else:
             x = vals.values().astype(np.float64)

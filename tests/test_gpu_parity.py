@@ -398,6 +398,47 @@ def test_sum_overflow_struct_results(vtype):
     assert (got[1][0][0].children[0].values() == 10).all() and not got[1][0][0].children[1].values().any()
 
 
+def test_decimal128_sums():
+    """SUM and SUM_OVERFLOW of DECIMAL128 values (the reference serves them on its hash path,
+    cpp/src/groupby/hash/groupby.cu:82-85; cpp/tests/groupby/sum_tests.cpp:220-247,250-290 sums a DECIMAL128
+    column beside an INT32 column): 16-byte elements read as two word columns, four exact chunk sums per
+    group.  Magnitudes up to 2^120 with one sign per group, so that some groups leave the 128-bit range; null
+    values, a sliced column, both null policies, the table paths and the partitioned path.  MIN of DECIMAL128
+    is the reference's sort path: not served."""
+    import cudf_b200 as cb
+    from cudf_b200 import aggregation as agg
+    from cudf_b200.types import int128_array, int128_list
+    rng = np.random.default_rng(101)
+    n = 120_000
+    kv = rng.integers(0, 400, n).astype(np.int32)
+    k = HostColumn.from_numpy(kv, valid=rng.random(n) > 0.02)
+    hi = rng.integers(0, 2 ** 56, n, dtype=np.int64).tolist()
+    lo = rng.integers(0, 2 ** 63, n, dtype=np.int64).tolist()
+    sign = np.where(kv % 3 == 0, -1, 1).tolist()
+    small = (kv % 5 == 0).tolist()                     # every fifth group stays far inside the range
+    ints = [sg * (l if sm else ((h << 64) | l)) for h, l, sg, sm in zip(hi, lo, sign, small)]
+    valid = rng.random(n) > 0.1
+    valid[kv == 17] = False
+    d = HostColumn.from_numpy(int128_array(ints), valid=valid, type_id=TypeId.DECIMAL128, offset=3, scale=-4)
+    w = HostColumn.from_numpy(rng.integers(-100, 100, n).astype(np.int32))
+    reqs = [(w, [Kind.SUM]), (d, [Kind.SUM, Kind.SUM_OVERFLOW, Kind.COUNT_VALID])]
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        for variant in (0, 1, 3, 6):
+            got = check([k], reqs, policy, table_variant=variant)
+            total, st = got[1][1][0], got[1][1][1]
+            assert total.type_id == TypeId.DECIMAL128 and total.scale == -4 and st.children[0].scale == -4
+            flags = st.children[1].values()[st.valid()]
+            assert 0 < int(flags.sum()) < flags.size
+    # one group against Python integers
+    gk, gr = H.gpu_groupby([k], reqs)
+    g0 = int(np.flatnonzero(gk[0].values() == 5)[0])
+    exact = sum(v for v, kk, ok, kok in zip(ints, kv.tolist(), valid.tolist(), k.valid().tolist()) if kk == 5 and ok and kok)
+    assert int128_list(gr[1][0].values())[g0] == exact
+    kk = cb.Column.from_host(k)
+    with pytest.raises(cb.UnsupportedError):
+        cb.GroupBy(cb.Table([kk])).aggregate([cb.GroupByRequest(cb.Column.from_host(d), [agg.min()])])
+
+
 def test_sum_overflow_rejects_bool_and_unsigned_values():
     # cpp/tests/groupby/sum_overflow_tests.cpp:495-561: cudf::logic_error for BOOL8, UINT32, UINT64
     import cudf_b200 as cb
