@@ -44,9 +44,12 @@ typedef enum b2_status {
 /* ---- element types: numeric values of cudf::type_id (cpp/include/cudf/types.hpp:185-217).
  *      Served as keys: integers, BOOL8, floats, timestamps, durations, DECIMAL32/64, STRING.
  *      Served as values: the same fixed-width types (which aggregation on which type follows
- *      cudf::detail::is_valid_aggregation; DECIMAL32/64: SUM, MIN, MAX, COUNT on the integer
- *      representation, result type and `scale` of the source kept).  DICTIONARY32, LIST, STRUCT,
- *      DECIMAL128 and STRING values return B2_UNSUPPORTED. */
+ *      cudf::detail::is_valid_aggregation; DECIMAL32/64: SUM, SUM_OVERFLOW, MIN, MAX, COUNT on the
+ *      integer representation, result type and `scale` of the source kept; DECIMAL128 (16-byte
+ *      little-endian elements): SUM, SUM_OVERFLOW, COUNT, like the reference's hash path), STRING
+ *      values for MIN / MAX / ARGMIN / ARGMAX / COUNT, and DICTIONARY32 values whose keys are
+ *      fixed-width (children {indices, keys}; one-shot aggregate only).  LIST and STRUCT values,
+ *      dictionaries of strings and the other aggregations of DECIMAL128 return B2_UNSUPPORTED. */
 typedef enum b2_type_id {
   B2_EMPTY = 0, B2_INT8 = 1, B2_INT16 = 2, B2_INT32 = 3, B2_INT64 = 4,
   B2_UINT8 = 5, B2_UINT16 = 6, B2_UINT32 = 7, B2_UINT64 = 8,
