@@ -196,6 +196,29 @@ def test_batchwise_updates_equal_one_shot():
         H.assert_same_result(got, exp, reqs, scales=H.result_scales([k], reqs, policy))
 
 
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_batchwise_mean_after_a_lean_first_batch(dtype):
+    """Σ and n of one float column: the first batch of a fresh state runs the lean kernel over the sampled key
+    box, the later batches the generic kernel on the same table (keys outside the first batch's box included)."""
+    import cudf_b200 as cb
+    rng = np.random.default_rng(43)
+    n = 300_000
+    keys = rng.integers(0, 800, n).astype(np.int64)
+    keys[n // 3:] += rng.integers(0, 3, n - n // 3) * 5000      # later batches bring keys far outside the box
+    k = HostColumn.from_numpy(keys)
+    v = HostColumn.from_numpy(rng.standard_normal(n).astype(dtype), valid=rng.random(n) > 0.1)
+    reqs = [(v, [Kind.SUM, Kind.COUNT_VALID, Kind.MEAN])]
+    st = None
+    for b in range(3):
+        gb, dreqs = _device_objects([k], reqs, NullPolicy.EXCLUDE, b * n // 3, (b + 1) * n // 3)
+        if st is None:
+            st = cb.GroupByState(gb, dreqs)
+        st.update(gb, dreqs)
+    got = _to_host(st.finalize())
+    exp = oracle.groupby([k], reqs)
+    H.assert_same_result(got, exp, reqs, scales=H.result_scales([k], reqs, NullPolicy.EXCLUDE))
+
+
 def test_state_with_string_keys_reports_unsupported_for_pack():
     import cudf_b200 as cb
     from cudf_b200 import aggregation as agg
