@@ -31,7 +31,8 @@ for config, strategy, n, python_exchange, variant in (
         (2, "partials", 200_000, False, 0), (2, "partials", 200_000, True, 0), (4, "partials", 200_000, False, 0),
         (3, "partials", 300_000, False, 0), (3, "partials", 300_000, True, 0), (3, "rows", 150_000, False, 0),
         (5, "rows", 40_000, False, 0), (5, "partials", 40_000, False, 0),
-        (4, "partials", 200_000, False, 6), (3, "partials", 300_000, False, 6)):
+        (4, "partials", 200_000, False, 6), (3, "partials", 300_000, False, 6),
+        (1, "partials", 200_000, False, 0)):   # Σ, n of one FLOAT64 column: the lean kernel's fixed-point limbs
     shards = [workloads.make(config, n, rank=r, scale_domain=(config in (3, 4))) for r in range(world)]
     w = shards[rank]
     keys = cb.Table([cb.Column.from_host(k) for k in w.keys])
@@ -100,7 +101,7 @@ def test_two_rank_distributed_groupby_matches_oracle(tmp_path):
                           "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)],
                          capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
-    assert out.stdout.count("OK") == 10
+    assert out.stdout.count("OK") == 11
     log_dir = os.environ.get("B2_TEST_LOG_DIR")   # keep rank 0's summary lines where the caller collects its logs
     if log_dir and os.path.isdir(log_dir):
         with open(os.path.join(log_dir, "two_rank_worker.log"), "w", encoding="utf-8") as f:
