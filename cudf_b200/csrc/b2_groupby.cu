@@ -2045,7 +2045,7 @@ const b2_aggregation_request* decode_dictionary_values(const b2_aggregation_requ
   for (int r = 0; reqs && r < nreqs; ++r) any = any || reqs[r].values.type_id == B2_DICTIONARY32;
   if (!any) return reqs;
   dv.reqs.assign(reqs, reqs + nreqs);
-  struct Seen { const void* idx; const void* keys; int off; void* buf; };
+  struct Seen { const void* idx; const void* keys; const void* mask; int off; void* buf; };
   std::vector<Seen> seen;
   for (int r = 0; r < nreqs; ++r) {
     b2_column_view& v = dv.reqs[(size_t)r].values;
@@ -2062,11 +2062,11 @@ const b2_aggregation_request* decode_dictionary_values(const b2_aggregation_requ
     if (w == 0 || ky.type_id == B2_DICTIONARY32) continue;  // string keys: validate_requests reports them
     void* buf = nullptr;
     for (const Seen& sn : seen)
-      if (sn.idx == ix.data && sn.keys == ky.data && sn.off == v.offset) buf = sn.buf;
+      if (sn.idx == ix.data && sn.keys == ky.data && sn.mask == v.null_mask && sn.off == v.offset) buf = sn.buf;
     if (!buf) {
       dv.bufs.emplace_back(std::max<size_t>(8, (size_t)((int64_t)v.offset + v.size) * (size_t)w), stream);
       buf = dv.bufs.back().p;
-      seen.push_back(Seen{ix.data, ky.data, v.offset, buf});
+      seen.push_back(Seen{ix.data, ky.data, v.null_mask, v.offset, buf});
       if (v.size > 0) {
         DDictDecode D{};
         D.indices = (const unsigned char*)ix.data; D.index_width = iw;

@@ -494,6 +494,18 @@ def test_dictionary_values_are_looked_up_by_key():
     got = H.gpu_groupby([keys], [(di, [Kind.SUM, Kind.SUM_OVERFLOW, Kind.PRODUCT, Kind.ARGMIN])], table_variant=6)
     exp = oracle.groupby([keys], [(pi, [Kind.SUM, Kind.SUM_OVERFLOW, Kind.PRODUCT, Kind.ARGMIN])])
     H.assert_same_result(got, exp, [(pi, [Kind.SUM, Kind.SUM_OVERFLOW, Kind.PRODUCT, Kind.ARGMIN])])
+    # the same indices and keys under two different masks in one call
+    valid2 = rng.random(n) > 0.5
+    full = cb.Column.from_host(HostColumn.from_dictionary(ints))     # every row's index is meaningful
+    m1 = cb.Column.from_host(pi).mask
+    m2 = cb.Column.from_host(HostColumn.from_numpy(ints, valid=valid2)).mask
+    c1 = cb.Column(TypeId.DICTIONARY32, n, None, m1, 0, int(n - valid.sum()), children=full.children)
+    c2 = cb.Column(TypeId.DICTIONARY32, n, None, m2, 0, int(n - valid2.sum()), children=full.children)
+    dk = cb.Table([cb.Column.from_host(keys)])
+    okeys, ores = cb.GroupBy(dk).aggregate([cb.GroupByRequest(c1, [agg.sum()]), cb.GroupByRequest(c2, [agg.sum()])])
+    got = ([c.to_host() for c in okeys.columns()], [[c.to_host() for c in t.columns()] for t in ores])
+    p2 = HostColumn.from_numpy(ints, valid=valid2)
+    H.assert_same_result(got, oracle.groupby([keys], [(pi, [Kind.SUM]), (p2, [Kind.SUM])]), [(pi, [Kind.SUM]), (p2, [Kind.SUM])])
     # a dictionary of strings: MIN / MAX would be dictionary columns (max_tests.cpp:198-224)
     words = HostColumn.from_strings(["a", "b"])
     sd = HostColumn(TypeId.DICTIONARY32, 2, None, None, 0, None, 0,
