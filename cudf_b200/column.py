@@ -76,7 +76,7 @@ class Column:
         def np_of(t, dtype):
             return None if t is None else t.cpu().numpy().view(dtype).copy()
         mask = np_of(self.mask, np.uint32)
-        if self.type_id == TypeId.STRUCT:
+        if self.type_id in (TypeId.STRUCT, TypeId.DICTIONARY32):
             return HostColumn(self.type_id, self.size, None, mask, self.offset, None, 0,
                               [c.to_host() for c in (self.children or [])])
         if self.type_id == TypeId.STRING:

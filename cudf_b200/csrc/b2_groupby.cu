@@ -2033,10 +2033,16 @@ void b2_groupby_destroy(b2_groupby* gb) { delete gb; }
 // DICTIONARY32 value columns with fixed-width keys, decoded once into plain columns of the keys' type (the
 // reference resolves the key at every update and produces results of the keys' type:
 // cpp/src/groupby/hash/output_utils.cu:65-66, cpp/tests/groupby/mean_tests.cpp:128-147, max_tests.cpp:226-246).
-// Dictionaries of strings are left as they are (their MIN / MAX are dictionary columns: not served).
+// A dictionary of strings takes part through its indices: the keys of a dictionary column are sorted and unique
+// (cpp/include/cudf/dictionary/dictionary_column_view.hpp:29-38), so MIN / MAX / ARGMIN / ARGMAX of the strings are
+// those of the indices; MIN / MAX results are handed back as dictionary columns over a copy of the same keys, like
+// the reference's (cpp/tests/groupby/max_tests.cpp:198-224, min_tests.cpp:190-216).  Other aggregations of a
+// dictionary of strings are not served.
 struct DecodedValues {
+  struct Wrap { int req; b2_column_view keys; };
   std::vector<b2_aggregation_request> reqs;
   std::vector<Scratch> bufs;
+  std::vector<Wrap> wraps;  // requests whose MIN / MAX results are indices into these keys
 };
 const b2_aggregation_request* decode_dictionary_values(const b2_aggregation_request* reqs, int nreqs, cudaStream_t stream,
                                                        DecodedValues& dv)
@@ -2059,7 +2065,19 @@ const b2_aggregation_request* decode_dictionary_values(const b2_aggregation_requ
     if (!int_index || iw == 0) B2_FAIL(B2_INVALID_ARGUMENT, "dictionary indices must be an integer column");
     if (ix.size < v.size || (v.size > 0 && !ix.data) || (ky.size > 0 && !ky.data) || ky.size < 0)
       B2_FAIL(B2_INVALID_ARGUMENT, "dictionary children do not cover the column");
-    if (w == 0 || ky.type_id == B2_DICTIONARY32) continue;  // string keys: validate_requests reports them
+    if (ky.type_id == B2_STRING) {
+      bool by_index = ix.offset == 0 && ky.null_mask == nullptr;
+      for (int a = 0; a < reqs[r].num_aggregations && reqs[r].aggregations; ++a) {
+        const int kind = reqs[r].aggregations[a].kind;
+        by_index = by_index && (kind == B2_AGG_MIN || kind == B2_AGG_MAX || kind == B2_AGG_ARGMIN || kind == B2_AGG_ARGMAX ||
+                                kind == B2_AGG_COUNT_VALID || kind == B2_AGG_COUNT_ALL);
+      }
+      if (!by_index) continue;  // validate_requests reports the column as not served
+      dv.wraps.push_back(DecodedValues::Wrap{r, ky});
+      v.type_id = ix.type_id; v.scale = 0; v.data = ix.data; v.num_children = 0; v.children = nullptr;
+      continue;
+    }
+    if (w == 0 || ky.type_id == B2_DICTIONARY32) continue;  // other keys: validate_requests reports them
     void* buf = nullptr;
     for (const Seen& sn : seen)
       if (sn.idx == ix.data && sn.keys == ky.data && sn.mask == v.null_mask && sn.off == v.offset) buf = sn.buf;
@@ -2086,6 +2104,47 @@ const b2_aggregation_request* decode_dictionary_values(const b2_aggregation_requ
   return dv.reqs.data();
 }
 
+// MIN / MAX results of a dictionary of strings: the column of winning indices becomes child 0 of a DICTIONARY32
+// column whose child 1 is a copy of the input's keys; the validity stays on the parent.
+void wrap_dictionary_results(const DecodedValues& dv, const b2_aggregation_request* reqs, b2_groupby_result* out,
+                             const b2_allocator* allocator, cudaStream_t stream)
+{
+  const b2_allocator al = resolve(allocator);
+  for (const DecodedValues::Wrap& w : dv.wraps) {
+    for (int a = 0; a < reqs[w.req].num_aggregations; ++a) {
+      const int kind = reqs[w.req].aggregations[a].kind;
+      if (kind != B2_AGG_MIN && kind != B2_AGG_MAX) continue;
+      b2_owned_column& c = out->results[w.req][a];
+      b2_owned_column* kids = (b2_owned_column*)std::calloc(2, sizeof(b2_owned_column));
+      if (!kids) B2_FAIL(B2_OUT_OF_MEMORY, "out of host memory");
+      kids[0] = c;  // the indices: data of the result, no mask of their own
+      kids[0].null_mask = nullptr; kids[0].null_mask_bytes = 0; kids[0].null_count = 0;
+      b2_owned_column parent{};
+      parent.type_id = B2_DICTIONARY32; parent.size = c.size; parent.null_count = c.null_count;
+      parent.null_mask = c.null_mask; parent.null_mask_bytes = c.null_mask_bytes;
+      parent.num_children = 2; parent.children = kids;
+      c = parent;  // (from here on b2_result_free releases the children with the rest)
+      const b2_column_view& ky = w.keys;
+      kids[1].type_id = B2_STRING; kids[1].size = ky.size;
+      if (ky.size > 0) {
+        if (ky.num_children < 1 || !ky.children) B2_FAIL(B2_INVALID_ARGUMENT, "STRING keys of a dictionary need their offsets child");
+        const b2_column_view& o = ky.children[0];
+        DKeyCol kc{};
+        kc.data = (const unsigned char*)ky.data; kc.mask = nullptr; kc.offset = ky.offset; kc.vclass = VC_STRING; kc.nullbit = -1;
+        kc.offsets = (const unsigned char*)o.data + (size_t)o.offset * (o.type_id == B2_INT64 ? 8 : 4);
+        kc.offs64 = o.type_id == B2_INT64;
+        Scratch rows((size_t)ky.size * sizeof(int), stream);
+        k_iota<<<grid_for(ky.size, 256, 8), 256, 0, stream>>>((int*)rows.p, (i64)ky.size);
+        CUDA_TRY(cudaGetLastError());
+        gather_strings(kc, (const int*)rows.p, ky.size, kids[1], nullptr, al, stream);
+      } else {
+        empty_strings(kids[1], al, stream);
+      }
+    }
+  }
+  if (!dv.wraps.empty()) CUDA_TRY(cudaStreamSynchronize(stream));
+}
+
 b2_status b2_groupby_aggregate(b2_groupby* gb, const b2_aggregation_request* requests, int32_t num_requests,
                                void* stream, const b2_allocator* allocator, b2_groupby_result* out)
 {
@@ -2107,6 +2166,11 @@ b2_status b2_groupby_aggregate(b2_groupby* gb, const b2_aggregation_request* req
     const std::function<void()> resume = [&] { aggregate_fresh(*st, use, (cudaStream_t)stream, true, false, /*resume=*/true); };
     finalize_state(*st, (cudaStream_t)stream, allocator, out, &resume);
     if (ek.active) restore_string_keys(ek, *gb, (cudaStream_t)stream, out);
+    if (!dv.wraps.empty()) {
+      OwnedGuard guard{out};  // a failure below frees what was finished
+      wrap_dictionary_results(dv, requests, out, allocator, (cudaStream_t)stream);
+      guard.armed = false;
+    }
   });
 }
 

@@ -1135,6 +1135,11 @@ __global__ void __launch_bounds__(256) k_dict_decode(const DDictDecode D, i64 n)
   }
 }
 
+__global__ void __launch_bounds__(256) k_iota(int* __restrict__ p, i64 n)
+{
+  for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (i64)gridDim.x * blockDim.x) p[i] = (int)i;
+}
+
 // ------------------------------------------------------------------------------ finalize
 enum OutKind : int {
   OK_COUNT = 0,  // int32 from a count cell

@@ -84,7 +84,7 @@ def _adopt_column(oc: _lib.OwnedColumn, alloc: TorchAllocator) -> Column:
         used = max(1, (oc.size + 511) // 512) * 64
         if mask.numel() > used:
             mask = mask[:used]
-    if oc.type_id == int(TypeId.STRUCT):
+    if oc.type_id in (int(TypeId.STRUCT), int(TypeId.DICTIONARY32)):  # children {sum, overflow} / {indices, keys}
         kids = [_adopt_column(oc.children[i], alloc) for i in range(oc.num_children)]
         oc.null_mask = None
         return Column(oc.type_id, oc.size, None, mask, 0, oc.null_count, children=kids)

@@ -47,9 +47,11 @@ typedef enum b2_status {
  *      cudf::detail::is_valid_aggregation; DECIMAL32/64: SUM, SUM_OVERFLOW, MIN, MAX, COUNT on the
  *      integer representation, result type and `scale` of the source kept; DECIMAL128 (16-byte
  *      little-endian elements): SUM, SUM_OVERFLOW, COUNT, like the reference's hash path), STRING
- *      values for MIN / MAX / ARGMIN / ARGMAX / COUNT, and DICTIONARY32 values whose keys are
- *      fixed-width (children {indices, keys}; one-shot aggregate only).  LIST and STRUCT values,
- *      dictionaries of strings and the other aggregations of DECIMAL128 return B2_UNSUPPORTED. */
+ *      values for MIN / MAX / ARGMIN / ARGMAX / COUNT, and DICTIONARY32 values (children {indices,
+ *      keys}, keys sorted and unique as cudf::dictionary guarantees; one-shot aggregate only):
+ *      fixed-width keys with every aggregation of the keys' type, STRING keys with MIN / MAX (results
+ *      are DICTIONARY32 columns over a copy of the keys), ARGMIN / ARGMAX and COUNT.  LIST and STRUCT
+ *      values and the other aggregations of DECIMAL128 return B2_UNSUPPORTED. */
 typedef enum b2_type_id {
   B2_EMPTY = 0, B2_INT8 = 1, B2_INT16 = 2, B2_INT32 = 3, B2_INT64 = 4,
   B2_UINT8 = 5, B2_UINT16 = 6, B2_UINT32 = 7, B2_UINT64 = 8,
