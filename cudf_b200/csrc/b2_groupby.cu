@@ -2104,45 +2104,86 @@ const b2_aggregation_request* decode_dictionary_values(const b2_aggregation_requ
   return dv.reqs.data();
 }
 
-// MIN / MAX results of a dictionary of strings: the column of winning indices becomes child 0 of a DICTIONARY32
-// column whose child 1 is a copy of the input's keys; the validity stays on the parent.
+// A finished column of dictionary indices `c` becomes child 0 of a DICTIONARY32 column whose child 1 is a copy of
+// the dictionary's keys `ky`; the validity stays on the parent (cpp/include/cudf/dictionary/dictionary_column_view.hpp:56-57).
+void make_dictionary_column(b2_owned_column& c, const b2_column_view& ky, const b2_allocator& al, cudaStream_t stream)
+{
+  b2_owned_column* kids = (b2_owned_column*)std::calloc(2, sizeof(b2_owned_column));
+  if (!kids) B2_FAIL(B2_OUT_OF_MEMORY, "out of host memory");
+  kids[0] = c;  // the indices: data of the finished column, no mask of their own
+  kids[0].null_mask = nullptr; kids[0].null_mask_bytes = 0; kids[0].null_count = 0;
+  b2_owned_column parent{};
+  parent.type_id = B2_DICTIONARY32; parent.size = c.size; parent.null_count = c.null_count;
+  parent.null_mask = c.null_mask; parent.null_mask_bytes = c.null_mask_bytes;
+  parent.num_children = 2; parent.children = kids;
+  c = parent;  // (from here on b2_result_free releases the children with the rest)
+  if (ky.type_id != B2_STRING) {
+    const int w = width_of(ky.type_id);
+    init_owned(kids[1], ky.type_id, ky.size, false, al, stream);
+    kids[1].scale = ky.scale;
+    if (ky.size > 0)
+      CUDA_TRY(cudaMemcpyAsync(kids[1].data, (const unsigned char*)ky.data + (size_t)ky.offset * (size_t)w, (size_t)ky.size * (size_t)w,
+                               cudaMemcpyDeviceToDevice, stream));
+    return;
+  }
+  kids[1].type_id = B2_STRING; kids[1].size = ky.size;
+  if (ky.size > 0) {
+    if (ky.num_children < 1 || !ky.children) B2_FAIL(B2_INVALID_ARGUMENT, "STRING keys of a dictionary need their offsets child");
+    const b2_column_view& o = ky.children[0];
+    DKeyCol kc{};
+    kc.data = (const unsigned char*)ky.data; kc.mask = nullptr; kc.offset = ky.offset; kc.vclass = VC_STRING; kc.nullbit = -1;
+    kc.offsets = (const unsigned char*)o.data + (size_t)o.offset * (o.type_id == B2_INT64 ? 8 : 4);
+    kc.offs64 = o.type_id == B2_INT64;
+    Scratch rows((size_t)ky.size * sizeof(int), stream);
+    k_iota<<<grid_for(ky.size, 256, 8), 256, 0, stream>>>((int*)rows.p, (i64)ky.size);
+    CUDA_TRY(cudaGetLastError());
+    gather_strings(kc, (const int*)rows.p, ky.size, kids[1], nullptr, al, stream);
+  } else {
+    empty_strings(kids[1], al, stream);
+  }
+}
+
+// MIN / MAX results of a dictionary of strings: the winning indices, handed back as dictionary columns
 void wrap_dictionary_results(const DecodedValues& dv, const b2_aggregation_request* reqs, b2_groupby_result* out,
                              const b2_allocator* allocator, cudaStream_t stream)
 {
   const b2_allocator al = resolve(allocator);
-  for (const DecodedValues::Wrap& w : dv.wraps) {
+  for (const DecodedValues::Wrap& w : dv.wraps)
     for (int a = 0; a < reqs[w.req].num_aggregations; ++a) {
       const int kind = reqs[w.req].aggregations[a].kind;
-      if (kind != B2_AGG_MIN && kind != B2_AGG_MAX) continue;
-      b2_owned_column& c = out->results[w.req][a];
-      b2_owned_column* kids = (b2_owned_column*)std::calloc(2, sizeof(b2_owned_column));
-      if (!kids) B2_FAIL(B2_OUT_OF_MEMORY, "out of host memory");
-      kids[0] = c;  // the indices: data of the result, no mask of their own
-      kids[0].null_mask = nullptr; kids[0].null_mask_bytes = 0; kids[0].null_count = 0;
-      b2_owned_column parent{};
-      parent.type_id = B2_DICTIONARY32; parent.size = c.size; parent.null_count = c.null_count;
-      parent.null_mask = c.null_mask; parent.null_mask_bytes = c.null_mask_bytes;
-      parent.num_children = 2; parent.children = kids;
-      c = parent;  // (from here on b2_result_free releases the children with the rest)
-      const b2_column_view& ky = w.keys;
-      kids[1].type_id = B2_STRING; kids[1].size = ky.size;
-      if (ky.size > 0) {
-        if (ky.num_children < 1 || !ky.children) B2_FAIL(B2_INVALID_ARGUMENT, "STRING keys of a dictionary need their offsets child");
-        const b2_column_view& o = ky.children[0];
-        DKeyCol kc{};
-        kc.data = (const unsigned char*)ky.data; kc.mask = nullptr; kc.offset = ky.offset; kc.vclass = VC_STRING; kc.nullbit = -1;
-        kc.offsets = (const unsigned char*)o.data + (size_t)o.offset * (o.type_id == B2_INT64 ? 8 : 4);
-        kc.offs64 = o.type_id == B2_INT64;
-        Scratch rows((size_t)ky.size * sizeof(int), stream);
-        k_iota<<<grid_for(ky.size, 256, 8), 256, 0, stream>>>((int*)rows.p, (i64)ky.size);
-        CUDA_TRY(cudaGetLastError());
-        gather_strings(kc, (const int*)rows.p, ky.size, kids[1], nullptr, al, stream);
-      } else {
-        empty_strings(kids[1], al, stream);
-      }
+      if (kind == B2_AGG_MIN || kind == B2_AGG_MAX) make_dictionary_column(out->results[w.req][a], w.keys, al, stream);
     }
-  }
   if (!dv.wraps.empty()) CUDA_TRY(cudaStreamSynchronize(stream));
+}
+
+// DICTIONARY32 key columns (cpp/tests/groupby/keys_tests.cpp:324-347): the keys of a dictionary are unique, so rows
+// group by their indices; the finished key column is handed back as a dictionary over a copy of the same keys.
+struct DictKeys {
+  b2_groupby gb;                              // the groupby with the indices in place of the dictionary columns
+  std::vector<std::pair<int, ColView>> wraps; // key column, the dictionary's keys child
+};
+bool substitute_dictionary_keys(const b2_groupby& gb, DictKeys& dk)
+{
+  bool any = false;
+  for (const ColView& c : gb.keys) any = any || c.v.type_id == B2_DICTIONARY32;
+  if (!any) return false;
+  dk.gb = gb;
+  for (size_t k = 0; k < dk.gb.keys.size(); ++k) {
+    const b2_column_view v = dk.gb.keys[k].v;
+    if (v.type_id != B2_DICTIONARY32) continue;
+    if (v.num_children != 2 || !v.children) B2_FAIL(B2_INVALID_ARGUMENT, "a DICTIONARY32 column needs its indices and keys children");
+    const b2_column_view ix = v.children[0];
+    const b2_column_view& ky = v.children[1];
+    const bool int_index = ix.type_id >= B2_INT8 && ix.type_id <= B2_UINT64;
+    if (!int_index || ix.offset != 0 || ix.size < v.size || (v.size > 0 && !ix.data))
+      B2_FAIL(B2_INVALID_ARGUMENT, "dictionary indices must be an unsliced integer column that covers the dictionary column");
+    if (ky.type_id != B2_STRING && width_of(ky.type_id) == 0) B2_FAIL(B2_UNSUPPORTED, "dictionary keys of this type are not served");
+    dk.wraps.emplace_back((int)k, ColView(ky));
+    b2_column_view nv = v;
+    nv.type_id = ix.type_id; nv.scale = 0; nv.data = ix.data; nv.num_children = 0; nv.children = nullptr;
+    dk.gb.keys[k] = ColView(nv);
+  }
+  return true;
 }
 
 b2_status b2_groupby_aggregate(b2_groupby* gb, const b2_aggregation_request* requests, int32_t num_requests,
@@ -2158,17 +2199,22 @@ b2_status b2_groupby_aggregate(b2_groupby* gb, const b2_aggregation_request* req
     DecodedValues dv;  // (lives until the results are finished)
     requests = decode_dictionary_values(requests, num_requests, (cudaStream_t)stream, dv);
     validate_requests(*gb, requests, num_requests);
+    DictKeys dk;
+    const b2_groupby& base = substitute_dictionary_keys(*gb, dk) ? dk.gb : *gb;
     EncodedKeys ek;
-    const b2_groupby& use = encode_string_keys(*gb, (cudaStream_t)stream, ek) ? ek.gb : *gb;
+    const b2_groupby& use = encode_string_keys(base, (cudaStream_t)stream, ek) ? ek.gb : base;
     std::unique_ptr<b2_groupby_state, void (*)(b2_groupby_state*)> st(make_state(use, requests, num_requests),
                                                                       b2_state_destroy);
     update_state(*st, use, requests, num_requests, (cudaStream_t)stream, /*may_partition=*/true, /*defer=*/true);
     const std::function<void()> resume = [&] { aggregate_fresh(*st, use, (cudaStream_t)stream, true, false, /*resume=*/true); };
     finalize_state(*st, (cudaStream_t)stream, allocator, out, &resume);
-    if (ek.active) restore_string_keys(ek, *gb, (cudaStream_t)stream, out);
-    if (!dv.wraps.empty()) {
+    if (ek.active) restore_string_keys(ek, base, (cudaStream_t)stream, out);
+    if (!dv.wraps.empty() || !dk.wraps.empty()) {
       OwnedGuard guard{out};  // a failure below frees what was finished
       wrap_dictionary_results(dv, requests, out, allocator, (cudaStream_t)stream);
+      const b2_allocator al = resolve(allocator);
+      for (auto& w : dk.wraps) make_dictionary_column(out->keys[w.first], w.second.v, al, (cudaStream_t)stream);
+      if (!dk.wraps.empty()) CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
       guard.armed = false;
     }
   });

@@ -42,7 +42,8 @@ typedef enum b2_status {
 } b2_status;
 
 /* ---- element types: numeric values of cudf::type_id (cpp/include/cudf/types.hpp:185-217).
- *      Served as keys: integers, BOOL8, floats, timestamps, durations, DECIMAL32/64, STRING.
+ *      Served as keys: integers, BOOL8, floats, timestamps, durations, DECIMAL32/64, STRING, and
+ *      DICTIONARY32 over any of these (one-shot aggregate; the key column comes back as a dictionary).
  *      Served as values: the same fixed-width types (which aggregation on which type follows
  *      cudf::detail::is_valid_aggregation; DECIMAL32/64: SUM, SUM_OVERFLOW, MIN, MAX, COUNT on the
  *      integer representation, result type and `scale` of the source kept; DECIMAL128 (16-byte

@@ -567,6 +567,49 @@ def test_dictionaries_of_strings_take_part_through_their_indices():
         cb.GroupBy(cb.Table([kk])).aggregate([cb.GroupByRequest(cb.Column.from_host(d), [agg.sum()])])
 
 
+def test_dictionary_key_columns_group_by_their_indices():
+    """DICTIONARY32 key columns (cpp/tests/groupby/keys_tests.cpp:324-347): the keys of a dictionary are unique, so
+    rows group by their indices, and the finished key column is a dictionary over the same keys.  The reference's
+    vector, then a nullable dictionary of strings beside an INT8 key and a dictionary of FLOAT64 under both null
+    policies, against the oracle on the plain columns."""
+    def decode(col):
+        idx, keys = col.children
+        words = keys.to_pylist()
+        return [words[i] if ok else None for i, ok in zip(idx.values().tolist(), col.valid().tolist())]
+
+    d, uniq = _string_dictionary(["aaa", "año", "₹1", "aaa", "año", "año", "aaa", "₹1", "₹1", "año"])
+    v = HostColumn.from_numpy(np.arange(10, dtype=np.int32))
+    gk, gr = H.gpu_groupby([d], [(v, [Kind.SUM])])
+    assert gk[0].type_id == TypeId.DICTIONARY32 and [w.decode() for w in gk[0].children[1].to_pylist()] == uniq
+    got = dict(zip([w.decode() for w in decode(gk[0])], gr[0][0].values().tolist()))
+    assert got == {"aaa": 9, "año": 19, "₹1": 17}
+
+    rng = np.random.default_rng(107)
+    n = 80_000
+    pool = ["k%03d" % i for i in range(400)] + ["", "é"]
+    words = [None if rng.random() < 0.05 else pool[i] for i in rng.integers(0, len(pool), n)]
+    d, _ = _string_dictionary(words, TypeId.UINT16)
+    k2 = HostColumn.from_numpy(rng.integers(0, 3, n).astype(np.int8))
+    x = rng.standard_normal(n)
+    val = HostColumn.from_numpy(x, valid=rng.random(n) > 0.1)
+    fpool = rng.standard_normal(50)
+    fvals = fpool[rng.integers(0, 50, n)]
+    fvalid = rng.random(n) > 0.03
+    fd = HostColumn.from_dictionary(fvals, valid=fvalid)
+    reqs = [(val, ALL_AGGS)]
+    for policy in (NullPolicy.EXCLUDE, NullPolicy.INCLUDE):
+        gk, gr = H.gpu_groupby([d, k2, fd], reqs, policy)
+        plain = [HostColumn.from_strings(words), k2, HostColumn.from_numpy(fvals, valid=fvalid)]
+        ek, er = oracle.groupby(plain, reqs, policy)
+        assert gk[0].type_id == TypeId.DICTIONARY32 and gk[2].type_id == TypeId.DICTIONARY32
+        f_dec = decode(gk[2])
+        back = [HostColumn.from_strings([None if w is None else w.decode() for w in decode(gk[0])]), gk[1],
+                HostColumn.from_numpy(np.array([0.0 if f is None else f for f in f_dec]),
+                                      valid=np.array([f is not None for f in f_dec]) if policy == NullPolicy.INCLUDE else None)]
+        H.assert_same_result((back, gr), (ek, er), reqs, check_nullable=False,
+                             scales=H.result_scales(plain, reqs, policy))
+
+
 def test_min_max_with_nan_and_infinity_terminate():
     # cpp/tests/groupby/min_tests.cpp:518-541, max_tests.cpp:526-549: all-NaN groups must not hang
     keys = HostColumn.from_numpy(np.array([1, 1, 2, 2, 2], dtype=np.int32))
